@@ -1,0 +1,79 @@
+// Shared helpers of the sm_100a kernel library: error reporting to the host,
+// element conversion, small reductions.  Every exported function is
+// `extern "C"`, takes raw device pointers and a stream, validates its
+// arguments on the host and returns 0 or a non-zero code whose text
+// sprout_last_error() gives.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define SPROUT_API extern "C" __attribute__((visibility("default")))
+
+enum SproutDtype : int { SPROUT_F32 = 0, SPROUT_BF16 = 1 };
+
+// Bits of the device status word that kernels set instead of faulting.
+enum SproutStatus : int {
+  SPROUT_STATUS_BAD_PAGE = 1,       // a block-table entry outside the pool
+  SPROUT_STATUS_BAD_TOKEN = 2,      // a token id outside the vocabulary
+  SPROUT_STATUS_NONFINITE = 4,      // non-finite logits met while sampling
+  SPROUT_STATUS_WAIT_TIMEOUT = 8,   // a bounded mbarrier wait ran out
+  SPROUT_STATUS_BAD_POSITION = 16,  // a position outside the rotary table
+};
+
+int sprout_fail(const char* fmt, ...);   // records the message, returns 1
+int sprout_check_launch(const char* what);
+
+#define SPROUT_REQUIRE(cond, ...) \
+  do { if (!(cond)) return sprout_fail(__VA_ARGS__); } while (0)
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum / max for blocks of up to 1024 threads; `scratch` holds 33 floats.
+// Every thread gets the result.  The order of the additions is fixed by the
+// block size alone.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float w = lane < warps ? scratch[lane] : 0.f;
+    w = warp_sum(w);
+    if (lane == 0) scratch[32] = w;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float w = lane < warps ? scratch[lane] : -INFINITY;
+    w = warp_max(w);
+    if (lane == 0) scratch[32] = w;
+  }
+  __syncthreads();
+  return scratch[32];
+}

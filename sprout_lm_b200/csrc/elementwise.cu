@@ -1,0 +1,187 @@
+// Memory-bound kernels of the decoder step: embedding gather, RMSNorm,
+// SwiGLU on an interleaved gate/up row, rotary position encoding fused with
+// the append of keys and values into the paged cache.  All arithmetic is
+// float32; the element type of activations (float or bfloat16) is a template
+// parameter.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+// x[t, :] = table[token[t], :] widened to float32 (the residual stream is float32).
+template <typename TW>
+__global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
+                             float* __restrict__ out, int hidden, int vocab, int* status) {
+  const int t = blockIdx.x;
+  int token = tokens[t];
+  if (token < 0 || token >= vocab) {
+    if (threadIdx.x == 0) atomicOr(status, SPROUT_STATUS_BAD_TOKEN);
+    token = 0;
+  }
+  const TW* row = table + (size_t)token * hidden;
+  float* dst = out + (size_t)t * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(row[i]);
+}
+
+SPROUT_API int sprout_embed(const void* table, int table_dtype, const int* tokens, float* out,
+                            int num_tokens, int hidden, int vocab, int* status, cudaStream_t stream) {
+  SPROUT_REQUIRE(num_tokens > 0 && hidden > 0 && vocab > 0, "embed: sizes must be positive");
+  SPROUT_REQUIRE(table && tokens && out && status, "embed: null pointer");
+  if (table_dtype == SPROUT_F32)
+    embed_kernel<float><<<num_tokens, 256, 0, stream>>>((const float*)table, tokens, out, hidden, vocab, status);
+  else if (table_dtype == SPROUT_BF16)
+    embed_kernel<__nv_bfloat16><<<num_tokens, 256, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, hidden, vocab, status);
+  else
+    return sprout_fail("embed: unknown dtype %d", table_dtype);
+  return sprout_check_launch("embed");
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// out[r, i] = (x[src(r), i] * rsqrt(mean(x^2) + eps)) * gain[i]; the normalised value is
+// rounded to float32 before the gain multiplies it.  `rows`, when given, selects source rows
+// (used to norm only the rows whose logits are wanted).
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
+                               TO* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const float* src = x + (size_t)(rows ? rows[r] : r) * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) { float v = src[i]; ss = fmaf(v, v, ss); }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+  TO* dst = out + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float n = src[i] * scale;
+    dst[i] = from_float<TO>(n * gain[i]);
+  }
+}
+
+SPROUT_API int sprout_rmsnorm(const float* x, const float* gain, void* out, int out_dtype, const int* rows,
+                              int num_rows, int hidden, float eps, cudaStream_t stream) {
+  SPROUT_REQUIRE(num_rows > 0 && hidden > 0, "rmsnorm: sizes must be positive");
+  SPROUT_REQUIRE(x && gain && out, "rmsnorm: null pointer");
+  SPROUT_REQUIRE(eps > 0.f, "rmsnorm: eps must be positive");
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (out_dtype == SPROUT_F32)
+    rmsnorm_kernel<float><<<num_rows, threads, 0, stream>>>(x, gain, (float*)out, rows, hidden, eps);
+  else if (out_dtype == SPROUT_BF16)
+    rmsnorm_kernel<__nv_bfloat16><<<num_rows, threads, 0, stream>>>(x, gain, (__nv_bfloat16*)out, rows, hidden, eps);
+  else
+    return sprout_fail("rmsnorm: unknown dtype %d", out_dtype);
+  return sprout_check_launch("rmsnorm");
+}
+
+// ---------------------------------------------------------------- SwiGLU
+// Input rows hold gate and up interleaved in blocks of 8: columns [16b, 16b+8) are gate
+// values 8b..8b+7 and [16b+8, 16b+16) the matching up values.  out = silu(gate) * up with the
+// SiLU rounded to the element type's float32 value first.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int tokens, int inter) {
+  const size_t total = (size_t)tokens * inter;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / inter), i = (int)(idx % inter);
+    const T* row = gu + (size_t)t * 2 * inter;
+    const int col = (i >> 3) * 16 + (i & 7);
+    const float g = to_float(row[col]), u = to_float(row[col + 8]);
+    const float s = g / (1.0f + expf(-g));
+    out[idx] = from_float<T>(s * u);
+  }
+}
+
+SPROUT_API int sprout_swiglu(const void* gate_up, void* out, int dtype, int tokens, int inter, cudaStream_t stream) {
+  SPROUT_REQUIRE(tokens > 0 && inter > 0, "swiglu: sizes must be positive");
+  SPROUT_REQUIRE(inter % 8 == 0, "swiglu: the intermediate size must be a multiple of 8 (got %d)", inter);
+  const size_t total = (size_t)tokens * inter;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  if (dtype == SPROUT_F32)
+    swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, tokens, inter);
+  else if (dtype == SPROUT_BF16)
+    swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, tokens, inter);
+  else
+    return sprout_fail("swiglu: unknown dtype %d", dtype);
+  return sprout_check_launch("swiglu");
+}
+
+// ---------------------------------------------------------------- rotary positions + cache append
+// One block per token.  qkv rows hold [q heads | k heads | v heads].  q and k are rotated by
+// the token's position with half-split pairs (d, d + head_dim/2); q is rotated in place, the
+// rotated k and the unrotated v go to the token's slot of the paged cache:
+//   page = block_table[seq, pos / page_tokens], slot = pos % page_tokens,
+//   element ((page * kv_heads + head) * page_tokens + slot) * head_dim + d.
+// cos/sin come from float32 tables [max_positions, head_dim/2] that the host fills from
+// float64 angles.  A page id outside the pool sets a status bit and skips the write.
+template <typename T>
+__global__ void rope_append_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                   const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
+                                   int table_stride, const float* __restrict__ cos_table,
+                                   const float* __restrict__ sin_table, int max_positions,
+                                   T* __restrict__ k_cache, T* __restrict__ v_cache, int heads, int kv_heads,
+                                   int head_dim, int page_tokens, int num_pages, int write_cache, int* status) {
+  const int t = blockIdx.x;
+  const int half = head_dim >> 1;
+  const int pos = positions[t];
+  const bool rotate = cos_table != nullptr;   // no tables: no position encoding, q and k stay as projected
+  if (pos < 0 || (rotate && pos >= max_positions)) {
+    if (threadIdx.x == 0) atomicOr(status, SPROUT_STATUS_BAD_POSITION);
+    return;
+  }
+  const int width = (heads + 2 * kv_heads) * head_dim;
+  T* row = qkv + (size_t)t * width;
+  const float* cs = rotate ? cos_table + (size_t)pos * half : nullptr;
+  const float* sn = rotate ? sin_table + (size_t)pos * half : nullptr;
+  // q heads, in place
+  for (int i = threadIdx.x; rotate && i < heads * half; i += blockDim.x) {
+    const int h = i / half, d = i % half;
+    T* x = row + h * head_dim;
+    const float a = to_float(x[d]), b = to_float(x[d + half]);
+    const float c = cs[d], s = sn[d];
+    x[d] = from_float<T>(a * c - b * s);
+    x[d + half] = from_float<T>(b * c + a * s);
+  }
+  if (!write_cache) return;
+  const int seq = seq_of_token[t];
+  const int page = block_table[(size_t)seq * table_stride + pos / page_tokens];
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) atomicOr(status, SPROUT_STATUS_BAD_PAGE);
+    return;
+  }
+  const int slot = pos % page_tokens;
+  const T* k_row = row + heads * head_dim;
+  const T* v_row = k_row + kv_heads * head_dim;
+  for (int i = threadIdx.x; i < kv_heads * half; i += blockDim.x) {
+    const int h = i / half, d = i % half;
+    const float a = to_float(k_row[h * head_dim + d]), b = to_float(k_row[h * head_dim + d + half]);
+    const float c = rotate ? cs[d] : 1.f, s = rotate ? sn[d] : 0.f;
+    T* dst = k_cache + (((size_t)page * kv_heads + h) * page_tokens + slot) * head_dim;
+    dst[d] = from_float<T>(a * c - b * s);
+    dst[d + half] = from_float<T>(b * c + a * s);
+  }
+  for (int i = threadIdx.x; i < kv_heads * head_dim; i += blockDim.x) {
+    const int h = i / head_dim, d = i % head_dim;
+    v_cache[(((size_t)page * kv_heads + h) * page_tokens + slot) * head_dim + d] = v_row[i];
+  }
+}
+
+SPROUT_API int sprout_rope_append(void* qkv, int dtype, const int* positions, const int* seq_of_token,
+                                  const int* block_table, int table_stride, const float* cos_table,
+                                  const float* sin_table, int max_positions, void* k_cache, void* v_cache,
+                                  int num_tokens, int heads, int kv_heads, int head_dim, int page_tokens,
+                                  int num_pages, int write_cache, int* status, cudaStream_t stream) {
+  SPROUT_REQUIRE(num_tokens > 0 && heads > 0 && kv_heads > 0 && page_tokens > 0 && num_pages > 0,
+                 "rope_append: sizes must be positive");
+  SPROUT_REQUIRE(head_dim > 0 && head_dim % 2 == 0, "rope_append: head_dim must be even (got %d)", head_dim);
+  SPROUT_REQUIRE(qkv && positions && seq_of_token && block_table && status, "rope_append: null pointer");
+  SPROUT_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "rope_append: cos and sin tables go together");
+  SPROUT_REQUIRE(!write_cache || (k_cache && v_cache), "rope_append: cache pointers missing");
+  if (dtype == SPROUT_F32)
+    rope_append_kernel<float><<<num_tokens, 128, 0, stream>>>(
+        (float*)qkv, positions, seq_of_token, block_table, table_stride, cos_table, sin_table, max_positions,
+        (float*)k_cache, (float*)v_cache, heads, kv_heads, head_dim, page_tokens, num_pages, write_cache, status);
+  else if (dtype == SPROUT_BF16)
+    rope_append_kernel<__nv_bfloat16><<<num_tokens, 128, 0, stream>>>(
+        (__nv_bfloat16*)qkv, positions, seq_of_token, block_table, table_stride, cos_table, sin_table,
+        max_positions, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, heads, kv_heads, head_dim, page_tokens,
+        num_pages, write_cache, status);
+  else
+    return sprout_fail("rope_append: unknown dtype %d", dtype);
+  return sprout_check_launch("rope_append");
+}

@@ -1,0 +1,30 @@
+// Host-side error text of the kernel library.
+#include <stdarg.h>
+#include <string.h>
+
+#include "common.cuh"
+
+static thread_local char g_error[512] = "";
+
+int sprout_fail(const char* fmt, ...) {
+  va_list args;
+  va_start(args, fmt);
+  vsnprintf(g_error, sizeof g_error, fmt, args);
+  va_end(args);
+  return 1;
+}
+
+int sprout_check_launch(const char* what) {
+  cudaError_t err = cudaPeekAtLastError();
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    return sprout_fail("%s: %s", what, cudaGetErrorString(err));
+  }
+  return 0;
+}
+
+// Text of the last failure on the calling thread.
+SPROUT_API const char* sprout_last_error() { return g_error; }
+
+// Version of the exported interface; the Python side checks it after loading.
+SPROUT_API int sprout_abi_version() { return 3; }

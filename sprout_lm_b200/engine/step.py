@@ -1,0 +1,117 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+``ModelRunner`` owns the model, the cache manager (host) and the cache storage (device).
+``step`` runs exactly the tokens it is given, as one batch: portions of prompts beside single
+decoded tokens, cut anywhere.  It appends their keys and values to the requests' pages and
+returns float32 logits at the wanted places.  It samples nothing and it does not advance the
+requests' lengths until the launches have been issued without error.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..cache.manager import CacheManager
+from ..cache.storage import CacheStorage, plan_groups, state_slot_count
+from .batch import BatchStager, StepContext, StepEntry
+
+
+class StepError(RuntimeError):
+    pass
+
+
+class ModelRunner:
+    def __init__(self, model, num_pages: int, page_tokens: int = 16, max_requests: int = 64,
+                 prefix_caching: bool = True):
+        if model.runtime is None:
+            raise StepError("the model has no weights loaded")
+        self.model = model
+        self.runtime = model.runtime
+        groups, slot_group = plan_groups(model)
+        self.manager = CacheManager(groups, num_pages, page_tokens,
+                                    state_slots=state_slot_count(model, max_requests),
+                                    prefix_caching=prefix_caching)
+        self.storage = CacheStorage(model, self.manager, slot_group)
+        self.stager = BatchStager(self.runtime.device, len(groups))
+        self.page_tokens = page_tokens
+        self.max_requests = max_requests
+        self.vocab_size = model.spec.vocab_size
+        self.max_positions = model.spec.max_positions
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ requests' caches
+    def new_sequence(self, tokens=None):
+        """A request's cache; with ``tokens`` and prefix caching, starting from the longest
+        published prefix of them."""
+        seq = self.manager.reuse_prefix(tokens) if tokens is not None else self.manager.create()
+        if seq.state_slot >= 0:
+            self.storage.clear_state(seq.state_slot)
+        return seq
+
+    def reserve(self, seq, upto: int) -> bool:
+        """Pages for all positions below ``upto`` in every group; False when the pool runs out
+        (pages taken so far stay with the request)."""
+        groups = range(len(self.manager.groups))
+        while True:
+            capacity = min(seq.capacity(g) for g in groups)
+            if capacity >= upto:
+                return True
+            if not self.manager.reserve(seq, min(upto, capacity + self.page_tokens)):
+                return False
+
+    def release(self, seq) -> None:
+        self.manager.release(seq)
+
+    # ------------------------------------------------------------------ the step
+    def validate(self, entries) -> None:
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        seen = set()
+        for e in entries:
+            if id(e.seq) in seen:
+                raise StepError("a request appears twice in one step")
+            seen.add(id(e.seq))
+            if e.seq.released:
+                raise StepError("a request's cache was released")
+            if not e.tokens:
+                raise StepError("an entry needs at least one token")
+            if any((not isinstance(t, int)) or t < 0 or t >= self.vocab_size for t in e.tokens):
+                raise StepError("Invalid token ID.")
+            end = e.seq.length + len(e.tokens)
+            if end > self.max_positions:
+                raise StepError("Invalid position: the request exceeds the model's context limit.")
+            for g in range(len(self.manager.groups)):
+                if self.storage.slot_group.count(g) and e.seq.capacity(g) < end:
+                    raise StepError("Reserve physical pages before running a token.")
+            if any((not isinstance(w, int)) or w < 0 or w >= len(e.tokens) for w in e.want):
+                raise StepError("a wanted place lies outside the entry's tokens")
+
+    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """Run one batch.  Returns float32 logits [wanted places, vocab] in the order of the
+        entries and of their ``want`` lists, or None when nothing is wanted.  The requests'
+        lengths are advanced."""
+        self.validate(entries)
+        ctx = self.stager.stage(entries, self.page_tokens)
+        logits = self.forward(ctx)
+        for e in entries:
+            e.seq.length += len(e.tokens)
+            self.manager.trim(e.seq)
+        self.steps_run += 1
+        return logits
+
+    def forward(self, ctx: StepContext):
+        return self.model.forward(ctx, self.storage)
+
+    def check_status(self) -> None:
+        """Read the device status word (synchronises); raise if a kernel flagged bad input."""
+        word = int(self.runtime.status.item())
+        if word:
+            self.runtime.status.zero_()
+            raise StepError("device status: " + kernels.describe_status(word))
+
+    # ------------------------------------------------------------------ sampling
+    def sample(self, logits: torch.Tensor, temperatures=None, uniforms=None) -> torch.Tensor:
+        """Token ids (int32, device) from float32 logits; greedy where the temperature is 0."""
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+        kernels.sample(logits, out, self.runtime.status, temperatures, uniforms)
+        return out

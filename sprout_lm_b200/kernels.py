@@ -1,0 +1,230 @@
+"""ctypes binding of the sm_100a kernel library.
+
+Every function takes torch CUDA tensors, checks dtype, contiguity and sizes on the host,
+and launches on torch's current stream.  There is no fallback: if the library cannot be
+built or loaded, or no CUDA device is present, calls raise.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from .csrc.build import BuildError, library_path
+
+F32, BF16 = 0, 1
+STATUS_BITS = {1: "a block-table entry outside the page pool", 2: "a token id outside the vocabulary",
+               4: "non-finite logits", 8: "a bounded device-side wait ran out", 16: "a position outside the rotary table"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_P, _I, _F = c_void_p, c_int, c_float
+_SIGNATURES = {
+    "sprout_embed": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
+    "sprout_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
+    "sprout_swiglu": [_P, _P, _I, _I, _I, _P],
+    "sprout_rope_append": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_gemm_simple": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "sprout_attention_simple": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_sample": [_P, _I, _P, _P, _P, _I, _I, _P, _P],
+}
+
+_lock = threading.Lock()
+_lib = None
+
+
+def load_library(verbose: bool = True):
+    """The loaded kernel library, built on first use."""
+    global _lib
+    with _lock:
+        if _lib is None:
+            path = library_path(build=True, verbose=verbose)
+            lib = ctypes.CDLL(str(path))
+            lib.sprout_last_error.restype = ctypes.c_char_p
+            lib.sprout_abi_version.restype = c_int
+            for name, argtypes in _SIGNATURES.items():
+                fn = getattr(lib, name)
+                fn.argtypes = argtypes
+                fn.restype = c_int
+            _lib = lib
+    return _lib
+
+
+def library_file() -> str:
+    return str(library_path(build=True, verbose=False))
+
+
+def _dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported element type {dtype}; the kernels take float32 and bfloat16")
+
+
+def _ptr(tensor, name, dtype=None, allow_none=False):
+    if tensor is None:
+        if allow_none:
+            return None
+        raise KernelError(f"{name} is missing")
+    if not tensor.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor; there is no CPU path")
+    if dtype is not None and tensor.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {tensor.dtype}")
+    return tensor.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _run(name, *args):
+    lib = load_library()
+    code = getattr(lib, name)(*args)
+    if code != 0:
+        raise KernelError(lib.sprout_last_error().decode())
+
+
+def _rows_contiguous(t, name):
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{name} must be 2-D with unit inner stride, got shape {tuple(t.shape)} strides {t.stride()}")
+
+
+# ---------------------------------------------------------------------------------- wrappers
+
+def embed(table, tokens, out, status):
+    """out[t] = table[tokens[t]] widened to float32."""
+    _rows_contiguous(table, "table")
+    if not table.is_contiguous() or not out.is_contiguous():
+        raise KernelError("embed: table and out must be contiguous")
+    T, H = out.shape
+    if tokens.numel() != T or table.shape[1] != H:
+        raise KernelError("embed: shapes do not fit")
+    _run("sprout_embed", _ptr(table, "table"), _dtype_code(table.dtype), _ptr(tokens, "tokens", torch.int32),
+         _ptr(out, "out", torch.float32), T, H, table.shape[0], _ptr(status, "status", torch.int32), _stream())
+
+
+def rmsnorm(x, gain, out, eps, rows=None):
+    """out[r] = rmsnorm(x[rows[r]] or x[r]) * gain; x float32, out float32 or bfloat16."""
+    if not x.is_contiguous() or not out.is_contiguous() or x.dim() != 2 or out.dim() != 2:
+        raise KernelError("rmsnorm: x and out must be contiguous 2-D")
+    R, H = out.shape
+    if x.shape[1] != H or gain.numel() != H or (rows is None and x.shape[0] != R) or (rows is not None and rows.numel() != R):
+        raise KernelError("rmsnorm: shapes do not fit")
+    _run("sprout_rmsnorm", _ptr(x, "x", torch.float32), _ptr(gain, "gain", torch.float32), _ptr(out, "out"),
+         _dtype_code(out.dtype), _ptr(rows, "rows", torch.int32, allow_none=True), R, H, float(eps), _stream())
+
+
+def swiglu(gate_up, out):
+    """out = silu(gate) * up for rows that interleave gate and up in blocks of 8."""
+    if not gate_up.is_contiguous() or not out.is_contiguous() or gate_up.dtype != out.dtype:
+        raise KernelError("swiglu: tensors must be contiguous and of one dtype")
+    T, I = out.shape
+    if tuple(gate_up.shape) != (T, 2 * I):
+        raise KernelError("swiglu: gate_up must be [tokens, 2 * intermediate]")
+    _run("sprout_swiglu", _ptr(gate_up, "gate_up"), _ptr(out, "out"), _dtype_code(out.dtype), T, I, _stream())
+
+
+def rope_append(qkv, positions, seq_of_token, block_table, cos_table, sin_table, k_cache, v_cache,
+                heads, kv_heads, head_dim, page_tokens, write_cache, status):
+    """Rotate q and k of every token by its position; store rotated k and v in the paged cache.
+
+    k_cache and v_cache are [pages, kv_heads, page_tokens, head_dim]."""
+    T = qkv.shape[0]
+    if not qkv.is_contiguous() or qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:
+        raise KernelError("rope_append: qkv must be contiguous [tokens, (heads + 2 kv_heads) * head_dim]")
+    if positions.numel() != T or seq_of_token.numel() != T:
+        raise KernelError("rope_append: one position and one sequence index per token")
+    if (cos_table is None) != (sin_table is None):
+        raise KernelError("rope_append: cos and sin tables go together")
+    if cos_table is not None and (cos_table.shape != sin_table.shape or cos_table.shape[1] != head_dim // 2
+                                  or not cos_table.is_contiguous() or not sin_table.is_contiguous()):
+        raise KernelError("rope_append: cos/sin tables must be contiguous [max_positions, head_dim / 2]")
+    num_pages = 1
+    if write_cache:
+        for name, cache in (("k_cache", k_cache), ("v_cache", v_cache)):
+            if cache.dtype != qkv.dtype or not cache.is_contiguous() or tuple(cache.shape[1:]) != (kv_heads, page_tokens, head_dim):
+                raise KernelError(f"rope_append: {name} must be contiguous [pages, kv_heads, page_tokens, head_dim] of {qkv.dtype}")
+        num_pages = k_cache.shape[0]
+    _rows_contiguous(block_table, "block_table")
+    _run("sprout_rope_append", _ptr(qkv, "qkv"), _dtype_code(qkv.dtype), _ptr(positions, "positions", torch.int32),
+         _ptr(seq_of_token, "seq_of_token", torch.int32), _ptr(block_table, "block_table", torch.int32),
+         block_table.stride(0), _ptr(cos_table, "cos", torch.float32, True), _ptr(sin_table, "sin", torch.float32, True),
+         cos_table.shape[0] if cos_table is not None else 0, _ptr(k_cache, "k_cache", allow_none=not write_cache),
+         _ptr(v_cache, "v_cache", allow_none=not write_cache), T, heads, kv_heads, head_dim, page_tokens,
+         num_pages, 1 if write_cache else 0, _ptr(status, "status", torch.int32), _stream())
+
+
+def gemm_simple(a, weight, out, bias=None, residual=None):
+    """out = a @ weight.T (+ bias) (+ residual) with float32 accumulation on CUDA cores."""
+    _rows_contiguous(a, "a")
+    _rows_contiguous(out, "out")
+    if not weight.is_contiguous() or weight.dim() != 2:
+        raise KernelError("gemm_simple: weight must be contiguous [N, K]")
+    M, K = a.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K or tuple(out.shape) != (M, N) or weight.dtype != a.dtype:
+        raise KernelError(f"gemm_simple: shapes/dtypes do not fit: a {tuple(a.shape)} {a.dtype}, "
+                          f"weight {tuple(weight.shape)} {weight.dtype}, out {tuple(out.shape)}")
+    if bias is not None and bias.numel() != N:
+        raise KernelError("gemm_simple: bias must have N entries")
+    if residual is not None and (tuple(residual.shape) != (M, N) or residual.stride(0) != out.stride(0)):
+        raise KernelError("gemm_simple: residual must have out's shape and row stride")
+    _run("sprout_gemm_simple", _ptr(a, "a"), _ptr(weight, "weight"), _ptr(bias, "bias", torch.float32, True),
+         _ptr(residual, "residual", torch.float32, True), _ptr(out, "out"), _dtype_code(a.dtype),
+         _dtype_code(out.dtype), M, N, K, a.stride(0), out.stride(0), _stream())
+
+
+def attention_simple(q, k_cache, v_cache, block_table, seq_of_token, positions, out, heads, kv_heads, head_dim, status):
+    """Paged causal attention with float32 arithmetic; q and out are [tokens, heads * head_dim] views."""
+    _rows_contiguous(q, "q")
+    _rows_contiguous(out, "out")
+    _rows_contiguous(block_table, "block_table")
+    T = q.shape[0]
+    if q.shape[1] != heads * head_dim or tuple(out.shape) != (T, heads * head_dim):
+        raise KernelError("attention_simple: q and out must be [tokens, heads * head_dim]")
+    if k_cache.shape != v_cache.shape or tuple(k_cache.shape[1:]) != (kv_heads, k_cache.shape[2], head_dim) \
+            or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise KernelError("attention_simple: caches must be contiguous [pages, kv_heads, page_tokens, head_dim]")
+    if not (q.dtype == out.dtype == k_cache.dtype == v_cache.dtype):
+        raise KernelError("attention_simple: q, out and the caches must share one dtype")
+    _run("sprout_attention_simple", _ptr(q, "q"), q.stride(0), _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"),
+         _ptr(block_table, "block_table", torch.int32), block_table.stride(0),
+         _ptr(seq_of_token, "seq_of_token", torch.int32), _ptr(positions, "positions", torch.int32),
+         _ptr(out, "out"), out.stride(0), _dtype_code(q.dtype), T, heads, kv_heads, head_dim, k_cache.shape[2],
+         k_cache.shape[0], _ptr(status, "status", torch.int32), _stream())
+
+
+def has_tensor_core_gemm() -> bool:
+    return False
+
+
+def paged_attention(q, cache, ctx, out, heads, kv_heads, head_dim, status):
+    """Causal attention of the step's queries over their requests' pages (``cache`` is a CacheView)."""
+    attention_simple(q, cache.k, cache.v, cache.block_table, ctx.seq_of_token, ctx.positions, out,
+                     heads, kv_heads, head_dim, status)
+
+
+def sample(logits, out, status, temperature=None, uniform=None):
+    """out[r] = argmax(logits[r]) where temperature[r] == 0 (or no temperature is given), else a
+    draw from softmax(logits[r] / temperature[r]) at the uniform number uniform[r]."""
+    _rows_contiguous(logits, "logits")
+    R, V = logits.shape
+    if out.numel() != R:
+        raise KernelError("sample: one output per row")
+    _run("sprout_sample", _ptr(logits, "logits", torch.float32), logits.stride(0),
+         _ptr(temperature, "temperature", torch.float32, True), _ptr(uniform, "uniform", torch.float32, True),
+         _ptr(out, "out", torch.int32), R, V, _ptr(status, "status", torch.int32), _stream())
+
+
+def describe_status(word: int) -> str:
+    return "; ".join(text for bit, text in STATUS_BITS.items() if word & bit) or "ok"
+
+
+__all__ = ["KernelError", "BuildError", "load_library", "library_file", "embed", "rmsnorm", "swiglu",
+           "rope_append", "gemm_simple", "attention_simple", "sample", "describe_status"]

@@ -1,0 +1,88 @@
+"""A decoder built from a ``ModelSpec``: embedding, layers, run order, final norm, head.
+
+Nothing here is specific to an architecture.  The run order is data
+(``ModelSpec.order``): each entry names a layer and the cache slot its mixer reads and,
+unless told otherwise, appends to; a layer may run more than once and may read a slot that
+another layer filled.
+"""
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+from ..config import ModelSpec, load_config
+from ..parts import CacheView, Runtime, StateView, WeightSource, build_block, build_part
+from ..weights.checkpoint import Checkpoint
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec):
+        self.spec = spec
+        self.embedding = build_part("embedding", spec.embedding)
+        self.blocks = [build_block(layer) for layer in spec.layers]
+        self.final_norm = build_part("norm", spec.final_norm)
+        self.head = build_part("head", spec.head)
+        self.runtime: Runtime | None = None
+
+    # ------------------------------------------------------------------ weights
+    def parts(self):
+        return [self.embedding, *self.blocks, self.final_norm, self.head]
+
+    def tensor_decls(self):
+        decls, seen = [], set()
+        for part in self.parts():
+            for decl in part.tensor_decls():
+                if decl.name in seen:
+                    raise ValueError(f"two parts declare the tensor {decl.name}")
+                seen.add(decl.name)
+                decls.append(decl)
+        return decls
+
+    def load(self, checkpoint: Checkpoint, runtime: Runtime) -> None:
+        expected = {decl.name: decl.shape for decl in self.tensor_decls()}
+        checkpoint.check(expected, ignorable=self.spec.ignorable_tensors)
+        source = WeightSource(lambda name: checkpoint.tensor(name, expected.get(name)), runtime)
+        for part in self.parts():
+            part.load(source)
+        self.runtime = runtime
+
+    # ------------------------------------------------------------------ what the cache manager must provide
+    def cache_specs(self):
+        """One CacheSpec (or None) per cache slot, taken from the layer that writes the slot."""
+        specs = [None] * self.spec.cache_slots
+        for call in self.spec.order:
+            if call.writes_cache and specs[call.cache] is None:
+                specs[call.cache] = self.blocks[call.layer].mixer.cache_spec()
+        return specs
+
+    def state_specs(self):
+        """One StateSpec (or None) per layer."""
+        return [block.mixer.state_spec() for block in self.blocks]
+
+    # ------------------------------------------------------------------ one step
+    def forward(self, ctx, storage) -> torch.Tensor:
+        """Run the step's tokens through the layers in run order; float32 logits
+        [len(ctx.logits_rows), vocab], or None when no logits are wanted.  ``storage`` is the device side of the cache
+        (``cache.storage.CacheStorage``)."""
+        x = self.embedding.forward(ctx.token_ids)
+        for call in self.spec.order:
+            cache = storage.view(call.cache, ctx, write=call.writes_cache)
+            state = storage.state_view(call.layer, ctx)
+            self.blocks[call.layer].forward(x, ctx, cache, state)
+        if ctx.logits_rows.numel() == 0:
+            return None             # nothing wanted: the layers have filled the cache, the head is skipped
+        return self.head.forward(self.final_norm.forward(x, rows=ctx.logits_rows))
+
+
+def load_model(directory, dtype=torch.bfloat16, device="cuda:0"):
+    """Model of a folder (config.json + model.safetensors or an index of shards), chosen by
+    the folder's config.json through the architecture registry."""
+    directory = Path(directory)
+    config = load_config(directory)
+    model = DecoderModel(config.model_spec())
+    runtime = Runtime(device, dtype)
+    with Checkpoint(directory) as checkpoint:
+        model.load(checkpoint, runtime)
+    model.config = config
+    return model

@@ -1,0 +1,81 @@
+"""Grouped-query attention over the paged cache (src/qwen.ts:166-195).
+
+q, k, v = W h + b in one fused product; q and k are rotated by the token's position
+(after the bias, before caching: the cache holds rotated keys and unrotated values); query head
+h reads key/value head h // (heads // kv_heads); the score is the dot divided by
+sqrt(head_dim); the mask is causal; the output projection has no bias unless ``out_bias``.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..config.specs import PartSpec
+from .base import CacheSpec, CacheView, Part, TensorDecl, WeightSource, build_part, register_part
+from .linear import Linear
+
+
+@register_part("mixer", "gqa_attention")
+class PagedGQAttention(Part):
+    def __init__(self, prefix: str, hidden_size: int, heads: int, kv_heads: int, head_dim: int,
+                 position: PartSpec, qkv_bias: bool = True, out_bias: bool = False, names: dict | None = None):
+        if heads % kv_heads:
+            raise ValueError(f"attention: heads ({heads}) must be a multiple of kv_heads ({kv_heads})")
+        if head_dim % 16 or head_dim > 256:
+            raise ValueError(f"attention: head_dim must be a multiple of 16 up to 256 (got {head_dim}); "
+                             "the kernels are written for head sizes in steps of 16")
+        self.hidden_size, self.heads, self.kv_heads, self.head_dim = hidden_size, heads, kv_heads, head_dim
+        self.qkv_bias, self.out_bias = qkv_bias, out_bias
+        names = names or {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj"}
+        self.names = {key: prefix + value for key, value in names.items()}
+        self.position = build_part("position", position)
+        self.qkv = self.out = None
+        self.tables = None
+        self.runtime = None
+
+    # ---- what it keeps
+    def cache_spec(self):
+        return CacheSpec(kv_heads=self.kv_heads, head_dim=self.head_dim, kind="full")
+
+    def state_spec(self):
+        return None
+
+    # ---- weights
+    def tensor_decls(self):
+        q_width, kv_width = self.heads * self.head_dim, self.kv_heads * self.head_dim
+        decls = [TensorDecl(self.names["q"] + ".weight", (q_width, self.hidden_size)),
+                 TensorDecl(self.names["k"] + ".weight", (kv_width, self.hidden_size)),
+                 TensorDecl(self.names["v"] + ".weight", (kv_width, self.hidden_size)),
+                 TensorDecl(self.names["o"] + ".weight", (self.hidden_size, q_width))]
+        if self.qkv_bias:
+            decls += [TensorDecl(self.names["q"] + ".bias", (q_width,), "bias"),
+                      TensorDecl(self.names["k"] + ".bias", (kv_width,), "bias"),
+                      TensorDecl(self.names["v"] + ".bias", (kv_width,), "bias")]
+        if self.out_bias:
+            decls.append(TensorDecl(self.names["o"] + ".bias", (self.hidden_size,), "bias"))
+        return decls
+
+    def load(self, source: WeightSource):
+        self.runtime = source.runtime
+        fused = torch.cat([source.raw(self.names[key] + ".weight") for key in ("q", "k", "v")], dim=0)
+        bias = None
+        if self.qkv_bias:
+            bias = torch.cat([source.raw(self.names[key] + ".bias").to(torch.float32) for key in ("q", "k", "v")])
+            bias = bias.to(source.runtime.device)
+        self.qkv = Linear(source.to_device_matrix(fused), bias)
+        out_bias = source.vector(self.names["o"] + ".bias") if self.out_bias else None
+        self.out = Linear(source.matrix(self.names["o"] + ".weight"), out_bias)
+        self.tables = self.position.rotary_tables(source.runtime)
+
+    # ---- the step
+    def forward(self, h, x, ctx, cache: CacheView, state=None):
+        qkv = self.qkv.forward(h)
+        cos, sin = self.tables if self.tables is not None else (None, None)
+        kernels.rope_append(qkv, ctx.positions, ctx.seq_of_token, cache.block_table, cos, sin, cache.k, cache.v,
+                            self.heads, self.kv_heads, self.head_dim, cache.page_tokens, cache.write,
+                            self.runtime.status)
+        q = qkv[:, :self.heads * self.head_dim]
+        attended = torch.empty((h.shape[0], self.heads * self.head_dim), dtype=qkv.dtype, device=qkv.device)
+        kernels.paged_attention(q, cache, ctx, attended, self.heads, self.kv_heads, self.head_dim,
+                                self.runtime.status)
+        self.out.forward(attended, residual=x)

@@ -1,0 +1,50 @@
+"""SwiGLU feed-forward: x += W_down (silu(W_gate h) * W_up h), no biases (src/qwen.ts:196-200).
+
+Gate and up are one fused product whose weight rows interleave the two in blocks of 8 (rows
+16b..16b+7 are gate rows 8b..8b+7, rows 16b+8..16b+15 the matching up rows), so that the
+activation sees a gate value and its up value side by side.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from .base import Part, TensorDecl, WeightSource, register_part
+from .linear import Linear
+
+INTERLEAVE = 8
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    inter, hidden = gate.shape
+    blocks = inter // INTERLEAVE
+    return torch.stack([gate.reshape(blocks, INTERLEAVE, hidden), up.reshape(blocks, INTERLEAVE, hidden)],
+                       dim=1).reshape(2 * inter, hidden).contiguous()
+
+
+@register_part("feed_forward", "swiglu_mlp")
+class SwiGLUMLP(Part):
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, names: dict | None = None):
+        if intermediate_size % INTERLEAVE:
+            raise ValueError(f"swiglu_mlp: intermediate_size must be a multiple of {INTERLEAVE} "
+                             f"(got {intermediate_size})")
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        names = names or {"gate": "gate_proj", "up": "up_proj", "down": "down_proj"}
+        self.names = {key: prefix + value for key, value in names.items()}
+        self.gate_up = self.down = None
+
+    def tensor_decls(self):
+        return [TensorDecl(self.names["gate"] + ".weight", (self.intermediate_size, self.hidden_size)),
+                TensorDecl(self.names["up"] + ".weight", (self.intermediate_size, self.hidden_size)),
+                TensorDecl(self.names["down"] + ".weight", (self.hidden_size, self.intermediate_size))]
+
+    def load(self, source: WeightSource):
+        fused = interleave_gate_up(source.raw(self.names["gate"] + ".weight"), source.raw(self.names["up"] + ".weight"))
+        self.gate_up = Linear(source.to_device_matrix(fused))
+        self.down = Linear(source.matrix(self.names["down"] + ".weight"))
+
+    def forward(self, h, x, ctx=None):
+        gate_up = self.gate_up.forward(h)
+        act = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
+        kernels.swiglu(gate_up, act)
+        self.down.forward(act, residual=x)

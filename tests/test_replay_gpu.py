@@ -1,0 +1,117 @@
+"""The engine against the plain implementation under every way of cutting the work.
+
+Each request alone and whole; most of it in one step and the last 32 tokens one by one; in
+portions of changing size; mixed, up to four live requests with so few pages that they are
+used again.  In true 32-bit and in bfloat16, on both tiny configurations, through the step
+function in process and through bin/trace_run.
+"""
+import numpy as np
+import pytest
+import torch
+
+import helpers
+from helpers import TOL
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+@pytest.fixture(scope="module")
+def model_dirs(tmp_path_factory):
+    base = tmp_path_factory.mktemp("models")
+    return {name: helpers.make_model_dir(base, name) for name in helpers.TINY}
+
+
+def make_requests(name, seed, lengths):
+    vocab = helpers.TINY[name][0]["vocab_size"]
+    rng = np.random.default_rng(seed)
+    return {f"r{i}": helpers.random_tokens(rng, n, vocab) for i, n in enumerate(lengths)}
+
+
+def make_runner(model_dir, dtype, pages, page_tokens):
+    from sprout_lm_b200.engine.step import ModelRunner
+    from sprout_lm_b200.models import load_model
+    model = load_model(model_dir, dtype=DTYPES[dtype])
+    return ModelRunner(model, num_pages=pages, page_tokens=page_tokens, max_requests=8, prefix_caching=False)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_all_cuttings_in_process(model_dirs, name, dtype):
+    page = helpers.TINY[name][2]
+    requests = make_requests(name, 11, [5, 17, 33, 70, 129])
+    rng = np.random.default_rng(5)
+    plans = {
+        "whole": helpers.plan_whole(requests),
+        "tail": helpers.plan_tail_decode(requests),
+        "portions": helpers.plan_portions(requests),
+        "mixed": helpers.plan_mixed(requests, rng),
+    }
+    for label, plan in plans.items():
+        budget = helpers.live_token_budget(plan, requests)
+        runner = make_runner(model_dirs[name], dtype, budget // page, page)
+        got = helpers.run_plan_in_process(runner, plan)
+        assert len(got) == sum(len(t) for t in requests.values())
+        helpers.compare_with_plain(model_dirs[name], requests, got, TOL[dtype], f"{name}/{dtype}/{label}")
+        runner.manager.check_invariants()
+        assert runner.manager.free_pages() == budget // page      # every page came back
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_reuses_pages(model_dirs, dtype):
+    """Seven requests through four live slots in a pool that holds four: pages of finished
+    requests are handed to later ones, block tables become non-contiguous."""
+    name = "B"
+    page = helpers.TINY[name][2]
+    requests = make_requests(name, 23, [40, 61, 24, 50, 33, 64, 47])
+    plan = helpers.plan_mixed(requests, np.random.default_rng(9))
+    budget = helpers.live_token_budget(plan, requests)
+    assert budget < sum(-(-len(t) // 64) * 64 for t in requests.values())   # the pool cannot hold all at once
+    runner = make_runner(model_dirs[name], dtype, budget // page, page)
+    got = helpers.run_plan_in_process(runner, plan)
+    helpers.compare_with_plain(model_dirs[name], requests, got, TOL[dtype], f"mixed-reuse/{dtype}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(model_dirs, tmp_path, dtype):
+    """bin/trace_run itself: whole, then tail decoding, then mixed, compared with the plain
+    implementation and with each other."""
+    name = "A"
+    requests = make_requests(name, 31, [9, 40, 75, 66])
+    results = {}
+    for label, plan in (("whole", helpers.plan_whole(requests)),
+                        ("tail", helpers.plan_tail_decode(requests)),
+                        ("mixed", helpers.plan_mixed(requests, np.random.default_rng(2)))):
+        budget = helpers.live_token_budget(plan, requests)
+        got = helpers.run_plan_with_trace_run(model_dirs[name], dtype, plan, tmp_path / f"{label}_{dtype}", budget)
+        helpers.compare_with_plain(model_dirs[name], requests, got, TOL[dtype], f"trace_run/{dtype}/{label}")
+        results[label] = got
+    # cutting changes nothing beyond rounding
+    for place, row in results["whole"].items():
+        for other in ("tail", "mixed"):
+            assert np.abs(results[other][place] - row).max() <= 2 * TOL[dtype]
+
+
+def test_long_decoding_float32(model_dirs):
+    """A short prompt, then several hundred tokens one by one across many page edges."""
+    name = "A"
+    requests = make_requests(name, 41, [400])
+    toks = requests["r0"]
+    plan = [{"entries": [("r0", toks[:6], list(range(6)))], "end": []}]
+    plan += [{"entries": [("r0", [t], [0])], "end": []} for t in toks[6:]]
+    runner = make_runner(model_dirs[name], "float32", 448 // 16, 16)
+    got = helpers.run_plan_in_process(runner, plan)
+    helpers.compare_with_plain(model_dirs[name], requests, got, TOL["float32"], "long-decode")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens(model_dirs, dtype):
+    """Positions 0, 1, 2: a sequence of one token, and the first tokens one by one."""
+    name = "B"
+    requests = make_requests(name, 51, [1, 3])
+    plan = [{"entries": [("r0", requests["r0"], [0])], "end": ["r0"]}]
+    plan += [{"entries": [("r1", [t], [0])], "end": []} for t in requests["r1"]]
+    runner = make_runner(model_dirs[name], dtype, 16, 8)
+    got = helpers.run_plan_in_process(runner, plan)
+    helpers.compare_with_plain(model_dirs[name], requests, got, TOL[dtype], "first-tokens")
