@@ -37,6 +37,7 @@ class ModelRunner:
         self.max_requests = max_requests
         self.vocab_size = model.spec.vocab_size
         self.max_positions = model.spec.max_positions
+        self.eos_token_ids = tuple(model.spec.eos_token_ids)
         self.steps_run = 0
 
     # ------------------------------------------------------------------ requests' caches
@@ -111,7 +112,15 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits: torch.Tensor, temperatures=None, uniforms=None) -> torch.Tensor:
-        """Token ids (int32, device) from float32 logits; greedy where the temperature is 0."""
+        """Token ids (int32, device) from float32 logits [rows, vocab]; a row is greedy where its
+        temperature is 0, else drawn from softmax(logits / temperature) at its uniform number.
+        ``temperatures`` and ``uniforms`` are tensors or sequences of floats, one per row."""
+        def on_device(values):
+            if values is None or isinstance(values, torch.Tensor):
+                return values
+            return torch.tensor(list(values), dtype=torch.float32).to(logits.device, non_blocking=True)
+        if temperatures is not None and not isinstance(temperatures, torch.Tensor) and not any(temperatures):
+            temperatures = uniforms = None
         out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-        kernels.sample(logits, out, self.runtime.status, temperatures, uniforms)
+        kernels.sample(logits, out, self.runtime.status, on_device(temperatures), on_device(uniforms))
         return out

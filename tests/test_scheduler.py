@@ -1,0 +1,242 @@
+"""The scheduler's decisions, on the host with a stand-in model: admission, budget, portions,
+decode-first order, prefix reuse, what happens when pages run out, cancel, validation, EOS,
+sampling that no batching can change.  After the reference's scenarios
+(test/engine.test.ts:45-155, test/qwen.test.ts:48-92)."""
+import pytest
+
+from sprout_lm_b200.engine import Engine, EngineOptions, uniform_for
+from stub_runner import StubRunner, reference_output
+
+
+def make(options=None, **runner_args):
+    options = options or EngineOptions(block_size=4, num_blocks=64, max_sequences=4, max_batch_tokens=8,
+                                       prefill_chunk_size=4)
+    options.validate()
+    runner = StubRunner(options.num_blocks, options.block_size, prefix_caching=options.prefix_caching, **runner_args)
+    return Engine(runner, options)
+
+
+def drain(engine, limit=2000):
+    reports = []
+    while engine.pending:
+        assert len(reports) < limit, "scheduler must make progress"
+        report = engine.step()
+        assert sum(w["tokens"] for w in report["work"]) <= engine.options.max_batch_tokens
+        assert all(p["refs"] >= 0 and p["activeRefs"] >= 0 for p in report["memory"]["pages"])
+        engine.cache.check_invariants()
+        reports.append(report)
+    return reports
+
+
+def test_continuous_batching_admits_a_late_request_and_mixes_phases():
+    engine = make(EngineOptions(block_size=4, num_blocks=64, max_sequences=3, max_batch_tokens=6, prefill_chunk_size=3))
+    prompts = [[1], list(range(2, 15)), [7, 8, 9, 10]]
+    engine.add("A", prompts[0], 6)
+    engine.add("B", prompts[1], 3)
+    engine.step()
+    engine.add("C", prompts[2], 2)
+    reports = drain(engine)
+    assert any(any(w["phase"] == "decode" for w in r["work"]) and any(w["phase"] == "prefill" for w in r["work"])
+               for r in reports)
+    for name, prompt, count in zip("ABC", prompts, (6, 3, 2)):
+        assert engine.result(name)["status"] == "finished"
+        assert engine.result(name)["output"] == reference_output(prompt, count, 50)
+    kinds = [(e["id"], e["type"]) for e in engine.trace]
+    assert kinds.index(("C", "admitted")) < kinds.index(("B", "finished"))
+    # one batch a step: the stand-in saw every step's work as one call
+    assert len(engine.runner.steps) == 1 + len([r for r in reports if r["work"]])
+
+
+def test_decode_goes_first_and_portions_respect_chunk_and_budget():
+    engine = make(EngineOptions(block_size=4, num_blocks=64, max_sequences=4, max_batch_tokens=6, prefill_chunk_size=4))
+    engine.add("A", [1, 2], 5)
+    engine.step()                                       # A prefilled, first token out
+    engine.add("B", list(range(1, 12)), 2)
+    report = engine.step()
+    assert [(w["id"], w["phase"], w["tokens"]) for w in report["work"]] == [("A", "decode", 1), ("B", "prefill", 4)]
+    report = engine.step()
+    assert [(w["id"], w["from"], w["tokens"]) for w in report["work"]] == [("A", 3, 1), ("B", 4, 4)]
+    engine.add("C", list(range(20, 30)), 1)
+    report = engine.step()                              # budget 6: A 1, B 3 (its rest), C 2
+    assert [(w["id"], w["tokens"]) for w in report["work"]] == [("A", 1), ("B", 3), ("C", 2)]
+    drain(engine)
+
+
+def test_prefix_sharing_reuses_pages_and_recomputes_the_last_prompt_token():
+    engine = make(EngineOptions(block_size=2, num_blocks=64, max_sequences=4, max_batch_tokens=8, prefill_chunk_size=8))
+    prompt = [3, 4, 5, 6]                               # exactly two pages
+    engine.add("A", prompt, 4)
+    engine.step()
+    a_pages = engine.result("A")["blockTable"]
+    engine.add("B", prompt, 4)
+    report = engine.step()
+    assert engine.result("B")["prefixHits"] == 2
+    assert engine.result("B")["blockTable"][0] == a_pages[0]
+    assert report["memory"]["pages"][a_pages[0]]["activeRefs"] == 2
+    drain(engine)
+    assert engine.result("A")["output"] == engine.result("B")["output"] == reference_output(prompt, 4, 50)
+    assert all(p["activeRefs"] == 0 for p in engine.cache.snapshot()["pages"])
+    engine.cache.clear_prefixes()
+    assert engine.cache.snapshot()["freePages"] == 64
+
+
+def test_same_suffix_after_other_context_does_not_hit():
+    engine = make(EngineOptions(block_size=2, num_blocks=64, max_sequences=4, max_batch_tokens=8, prefill_chunk_size=8))
+    engine.add("A", [1, 2, 3, 4, 5], 1)
+    drain(engine)
+    engine.add("B", [9, 8, 3, 4, 5], 1)
+    drain(engine)
+    assert engine.result("B")["prefixHits"] == 0
+    assert engine.result("B")["output"] == reference_output([9, 8, 3, 4, 5], 1, 50)
+
+
+@pytest.mark.parametrize("prefix_caching", [False, True])
+def test_pages_run_out_preempt_and_recompute_without_changing_outputs(prefix_caching):
+    options = EngineOptions(block_size=2, num_blocks=5, max_sequences=4, max_batch_tokens=6, prefill_chunk_size=2,
+                            prefix_caching=prefix_caching)
+    engine = make(options)
+    prompts = [[1, 1], [2, 2], [3, 3]]
+    for i, prompt in enumerate(prompts):
+        engine.add(str(i), prompt, 7)
+    reports = drain(engine)
+    assert any(e["type"] == "preempted" for e in engine.trace)
+    assert any(w["phase"] == "recompute" for r in reports for w in r["work"])
+    for i, prompt in enumerate(prompts):
+        assert engine.result(str(i))["output"] == reference_output(prompt, 7, 50)
+    # the oldest request is never preempted
+    assert not any(e["type"] == "preempted" and e["id"] == "0" for e in engine.trace)
+    engine.cache.clear_prefixes()
+    assert engine.cache.snapshot()["freePages"] == 5
+
+
+def test_a_preempted_request_goes_to_the_back_and_keeps_its_output():
+    options = EngineOptions(block_size=2, num_blocks=4, max_sequences=2, max_batch_tokens=4, prefill_chunk_size=2,
+                            prefix_caching=False)
+    engine = make(options)
+    engine.add("old", [1, 2, 3], 5)
+    engine.add("young", [4, 5, 6], 5)
+    engine.add("later", [7], 1)
+    seen = []
+    while engine.pending:
+        report = engine.step()
+        for e in report["events"]:
+            if e["type"] == "preempted":
+                seen.append((e["id"], list(engine.result(e["id"])["output"]), list(engine._waiting)))
+    assert seen and all(name != "old" for name, _, _ in seen)
+    name, kept, queue = seen[0]
+    assert queue[-1] == name                            # behind "later"
+    for ident, prompt, count in (("old", [1, 2, 3], 5), ("young", [4, 5, 6], 5), ("later", [7], 1)):
+        assert engine.result(ident)["output"] == reference_output(prompt, count, 50)
+    assert engine.result(name)["output"][:len(kept)] == kept
+
+
+def test_a_request_alone_that_cannot_continue_preempts_itself_only_when_others_hold_pages():
+    # two requests, pool of 3 pages of 2: the younger is preempted, the older always finishes
+    options = EngineOptions(block_size=2, num_blocks=3, max_sequences=2, max_batch_tokens=4, prefill_chunk_size=4,
+                            prefix_caching=False)
+    engine = make(options)
+    engine.add("a", [1, 2, 3], 4)                       # needs 6 slots = 3 pages: fits alone
+    engine.add("b", [4, 5, 6], 4)
+    drain(engine)
+    assert engine.result("a")["output"] == reference_output([1, 2, 3], 4, 50)
+    assert engine.result("b")["output"] == reference_output([4, 5, 6], 4, 50)
+
+
+def test_cancel_running_and_queued_without_harming_a_sibling():
+    engine = make(EngineOptions(block_size=2, num_blocks=16, max_sequences=2, max_batch_tokens=8, prefill_chunk_size=8))
+    prompt = [1, 2, 3, 4, 5]
+    engine.add("A", prompt, 6)
+    engine.add("B", prompt, 6)
+    engine.add("Q", [9], 3)
+    engine.step()
+    engine.step()
+    assert engine.cancel("B") and engine.cancel("Q")
+    assert not engine.cancel("B") and not engine.cancel("nope")
+    assert engine.result("B")["status"] == "cancelled" and engine.result("Q")["status"] == "cancelled"
+    drain(engine)
+    assert engine.result("A")["output"] == reference_output(prompt, 6, 50)
+    assert all(p["activeRefs"] == 0 for p in engine.cache.snapshot()["pages"])
+    assert engine.forget("B") and not engine.forget("B")
+    with pytest.raises(KeyError):
+        engine.result("B")
+
+
+def test_input_validation():
+    with pytest.raises(ValueError):
+        make(EngineOptions(block_size=0))
+    with pytest.raises(ValueError):
+        make(EngineOptions(prefix_caching=1))
+    engine = make(EngineOptions(block_size=2, num_blocks=4, max_sequences=2, max_batch_tokens=8, prefill_chunk_size=8),
+                  max_positions=64)
+    for bad in ([], [-1], [50], [1.5]):
+        with pytest.raises(ValueError, match="valid token IDs"):
+            engine.add("x", bad, 1)
+    with pytest.raises(ValueError, match="positive integer"):
+        engine.add("x", [1], 0)
+    with pytest.raises(ValueError, match="cannot fit alone"):
+        engine.add("x", [1] * 8, 2)                     # 9 slots > 8
+    with pytest.raises(ValueError, match="context limit"):
+        make(EngineOptions(block_size=16, num_blocks=64), max_positions=8).add("x", [1] * 8, 2)
+    engine.add("x", [1] * 8, 1)                         # 8 slots fit exactly
+    with pytest.raises(ValueError, match="unique"):
+        engine.add("x", [1], 1)
+    with pytest.raises(ValueError, match="unique"):
+        engine.add("", [1], 1)
+
+
+def test_eos_is_sampled_once_counted_and_frees_pages_early():
+    first = reference_output([5, 6], 3, 50)
+    engine = make(EngineOptions(block_size=2, num_blocks=8, max_sequences=2, max_batch_tokens=8, prefill_chunk_size=8),
+                  eos_token_ids=(first[1],))
+    engine.add("A", [5, 6], 10)
+    engine.add("B", [5, 6], 10, ignore_eos=True)
+    drain(engine)
+    a, b = engine.result("A"), engine.result("B")
+    assert a["output"] == first[:2] and a["finishReason"] == "eos"
+    assert b["output"][:3] == first and len(b["output"]) == 10 and b["finishReason"] == "length"
+    finished = [e for e in engine.trace if e["type"] == "finished" and e["id"] == "A"]
+    assert finished[0]["finishReason"] == "eos"
+
+
+def test_temperature_sampling_depends_on_seed_request_and_index_only():
+    assert uniform_for(1, "a", 0) == uniform_for(1, "a", 0)
+    assert len({uniform_for(1, "a", 0), uniform_for(2, "a", 0), uniform_for(1, "b", 0), uniform_for(1, "a", 1)}) == 4
+    assert all(0.0 <= uniform_for(s, "r", i) < 1.0 for s in range(20) for i in range(20))
+    outputs = []
+    for options in (EngineOptions(block_size=8, num_blocks=64, max_sequences=4, max_batch_tokens=64, prefill_chunk_size=64),
+                    EngineOptions(block_size=8, num_blocks=6, max_sequences=4, max_batch_tokens=5, prefill_chunk_size=3),
+                    EngineOptions(block_size=2, num_blocks=18, max_sequences=2, max_batch_tokens=3, prefill_chunk_size=7,
+                                  prefix_caching=False)):
+        engine = make(options)
+        prompts = {"p": [1, 2, 3], "q": list(range(1, 25)), "r": list(range(1, 17)) + [40]}
+        for name, prompt in prompts.items():
+            engine.add(name, prompt, 12, temperature=0.8, seed=5)
+        drain(engine)
+        outputs.append({name: engine.result(name)["output"] for name in prompts})
+    assert outputs[0] == outputs[1] == outputs[2]
+    greedy = make()
+    greedy.add("p", [1, 2, 3], 12)
+    drain(greedy)
+    assert greedy.result("p")["output"] != outputs[0]["p"]       # temperature does draw other tokens
+
+
+def test_a_model_failure_leaves_the_error_with_the_caller():
+    engine = make()
+    engine.runner.fail_after = 1
+    engine.add("A", [1, 2, 3], 4)
+    engine.step()
+    with pytest.raises(RuntimeError, match="model failure"):
+        engine.step()
+
+
+def test_step_report_has_the_reference_fields():
+    engine = make(EngineOptions(block_size=4, num_blocks=8, max_sequences=2, max_batch_tokens=8, prefill_chunk_size=4))
+    engine.add("A", [1, 2, 3, 4, 5], 2)
+    report = engine.step()
+    assert set(report) == {"tick", "work", "events", "memory"} and report["tick"] == 1
+    assert report["work"] == [{"id": "A", "phase": "prefill", "from": 0, "tokens": 4, "blockTable": [0]}]
+    assert [e["type"] for e in report["events"]] == ["admitted"]
+    assert set(report["memory"]) >= {"totalPages", "freePages", "cachedPages", "evictions", "pages"}
+    report = engine.step()
+    assert report["work"][0]["from"] == 4 and [e["type"] for e in report["events"]] == ["token"]
+    assert report["events"][0]["index"] == 0 and report["events"][0]["token"] == engine.result("A")["output"][0]
