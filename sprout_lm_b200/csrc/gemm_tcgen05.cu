@@ -1,0 +1,411 @@
+// bfloat16 matrix product on the 5th-generation tensor cores of sm_100a:
+//   out[m, n] = sum_k A[m, k] * W[n, k] (+ bias[n]) (+ residual[m, n])
+// A (activations, [M, K]) and W (weights, [N, K]) are both K-major, which is the layout
+// tcgen05.mma takes for both operands: no repacking.
+//
+// One CTA computes a 128 x BN tile of D: operand tiles of 64 K-elements (128 bytes, one
+// swizzle row) are staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle)
+// through a ring of stages guarded by mbarriers; one elected thread issues tcgen05.mma with
+// the float32 accumulator in tensor memory; four warps read the accumulator back with
+// tcgen05.ld and apply the epilogue.  Warp 0 produces (TMA), warp 1 issues MMAs and owns the
+// TMEM allocation, warps 2-5 run the epilogue.
+//
+// Two orientations share the pipeline:
+//   tokens on M  (prefill): D rows are tokens, D columns output features; BN = 128.
+//   weights on M (decode, "swap"): D rows are output features, D columns tokens; BN = the
+//       token count rounded up to 16..128.  A decode step streams every weight once and the
+//       128-row tensor-core tile is filled by weight rows instead of by a handful of tokens.
+//       With split_k > 1 the K range is divided among CTAs (grid.z) and the partial sums are
+//       added into the float32 output with atomics (residual epilogue only).
+//
+// Every wait on an mbarrier is bounded; a wait that runs out sets SPROUT_STATUS_WAIT_TIMEOUT,
+// the CTA stops issuing, waits (bounded) for its copies in flight, frees its TMEM and returns.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BLOCK_M = 128;        // rows of D per CTA == TMEM lanes
+constexpr int BLOCK_K = 64;         // bf16 elements per stage row: 128 bytes, one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;   // tries of mbarrier.try_wait (each blocks for a while)
+constexpr int SMEM_BUDGET = 200 * 1024;
+
+enum Epilogue : int { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_RESIDUAL_ATOMIC = 2 };
+
+struct Params {
+  const float* bias;     // [N] or null
+  void* out;             // [M, N] row stride ldo, bf16 or f32
+  int out_is_f32;
+  int epilogue;
+  int M, N, K;           // M tokens, N output features
+  int ldo;
+  int k_blocks_per_split;
+  int* status;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t tries = 0; tries < WAIT_LIMIT; tries++) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The mbarrier gets one arrival when every MMA this thread issued so far has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, swizzled in
+// 8-row groups of 1024 bytes (what TMA's 128-byte swizzle writes): start address / 16 in bits
+// 0-13, the 1024-byte stride between row groups / 16 in bits 32-45, descriptor version 1 in
+// bits 46-47, layout type 2 (128-byte swizzle) in bits 61-63.
+__device__ __forceinline__ uint64_t umma_smem_desc(const void* tile) {
+  uint64_t desc = 0;
+  desc |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);
+  desc |= (uint64_t)(1024 >> 4) << 32;
+  desc |= (uint64_t)1 << 46;
+  desc |= (uint64_t)2 << 61;
+  return desc;
+}
+// Instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, N and M sizes.
+__device__ __forceinline__ uint32_t umma_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <int BN>
+struct Layout {
+  static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
+  static constexpr int B_BYTES = BN * BLOCK_K * 2;
+  static constexpr int B_PADDED = (B_BYTES + 1023) / 1024 * 1024;
+  static constexpr int STAGE_BYTES = A_BYTES + B_PADDED;
+  static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) > 12 ? 12 : (SMEM_BUDGET / STAGE_BYTES);
+  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+// SWAP == false: map_rows is the activation map (rows = tokens), map_cols the weight map.
+// SWAP == true:  map_rows is the weight map (rows = output features), map_cols the activation map.
+template <int BN, bool SWAP>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
+                    const Params p) {
+  using L = Layout<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = (uint64_t*)(smem + L::STAGES * L::STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + L::STAGES;
+  uint64_t* acc_bar = empty_bar + L::STAGES;
+  uint32_t* tmem_slot = (uint32_t*)(acc_bar + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = blockIdx.y * BLOCK_M;          // first D row of this CTA
+  const int col0 = blockIdx.x * BN;               // first D column
+  const int total_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
+  const int kb_begin = blockIdx.z * p.k_blocks_per_split;
+  const int kb_end = min(total_kb, kb_begin + p.k_blocks_per_split);
+  const int num_kb = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L::STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(acc_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, L::TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  int issued = 0;
+  if (warp == 0 && lane == 0) {
+    // ---------------- producer: TMA loads of the two operand tiles, stage by stage
+    for (int i = 0; i < num_kb; i++) {
+      const int s = i % L::STAGES;
+      const uint32_t parity = ((i / L::STAGES) & 1) ^ 1;
+      if (*abort_flag || !mbar_wait(&empty_bar[s], parity)) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); break; }
+      uint8_t* a_tile = smem + s * L::STAGE_BYTES;
+      uint8_t* b_tile = a_tile + L::A_BYTES;
+      mbar_expect_tx(&full_bar[s], L::A_BYTES + L::B_BYTES);
+      tma_load_2d(a_tile, &map_rows, &full_bar[s], (kb_begin + i) * BLOCK_K, row0);
+      tma_load_2d(b_tile, &map_cols, &full_bar[s], (kb_begin + i) * BLOCK_K, col0);
+      issued = i + 1;
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- MMA issuer
+    const uint32_t idesc = umma_idesc(BLOCK_M, BN);
+    bool ok = true;
+    for (int i = 0; i < num_kb && ok; i++) {
+      const int s = i % L::STAGES;
+      const uint32_t parity = (i / L::STAGES) & 1;
+      if (*abort_flag || !mbar_wait(&full_bar[s], parity)) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); ok = false; break; }
+      tc_fence_after();
+      const uint8_t* a_tile = smem + s * L::STAGE_BYTES;
+      const uint64_t a_desc = umma_smem_desc(a_tile), b_desc = umma_smem_desc(a_tile + L::A_BYTES);
+#pragma unroll
+      for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
+        // advancing 16 elements (32 bytes) along K inside the swizzled row: +2 in the address field
+        umma_bf16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (i | k) != 0);
+      }
+      umma_commit(&empty_bar[s]);       // the stage is free once these MMAs have read it
+    }
+    umma_commit(acc_bar);               // the accumulator is complete once all MMAs are
+  } else if (warp >= 2) {
+    // ---------------- epilogue: TMEM -> registers -> global
+    const int quarter = warp & 3;       // a warp reads TMEM lanes 32 * (warp % 4) ..
+    const int row = row0 + quarter * 32 + lane;
+    bool ok = num_kb > 0;
+    if (ok && !mbar_wait(acc_bar, 0)) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); ok = false; }
+    ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld is warp-wide: all lanes or none
+    tc_fence_after();
+    if (ok) {
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      const bool first_split = blockIdx.z == 0;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        uint32_t raw[16];
+        tmem_load16(taddr + c, raw);
+        if (SWAP) {
+          // row = output feature, columns = tokens: lanes hold consecutive features
+          if (row < p.N) {
+            const float b = (p.bias && first_split) ? p.bias[row] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+              const int m = col0 + c + j;
+              if (m >= p.M) break;
+              const float v = __uint_as_float(raw[j]) + b;
+              const size_t at = (size_t)m * p.ldo + row;
+              if (p.epilogue == EPI_RESIDUAL_ATOMIC) atomicAdd((float*)p.out + at, v);
+              else if (p.epilogue == EPI_RESIDUAL) ((float*)p.out)[at] += v;
+              else if (p.out_is_f32) ((float*)p.out)[at] = v;
+              else ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(v);
+            }
+          }
+        } else {
+          // row = token, columns = output features: each lane writes a contiguous run of its row
+          if (row < p.M) {
+            const int n_base = col0 + c;
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) v[j] = __uint_as_float(raw[j]) + ((p.bias && n_base + j < p.N) ? p.bias[n_base + j] : 0.f);
+            const size_t at = (size_t)row * p.ldo + n_base;
+            const bool whole = n_base + 16 <= p.N;
+            if (p.epilogue == EPI_RESIDUAL) {
+              float* o = (float*)p.out + at;
+              if (whole && (at & 3) == 0) {
+#pragma unroll
+                for (int j = 0; j < 16; j += 4) {
+                  float4 r = *(float4*)(o + j);
+                  r.x += v[j]; r.y += v[j + 1]; r.z += v[j + 2]; r.w += v[j + 3];
+                  *(float4*)(o + j) = r;
+                }
+              } else {
+                for (int j = 0; j < 16 && n_base + j < p.N; j++) o[j] += v[j];
+              }
+            } else if (p.out_is_f32) {
+              float* o = (float*)p.out + at;
+              if (whole && (at & 3) == 0) {
+#pragma unroll
+                for (int j = 0; j < 16; j += 4) *(float4*)(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              } else {
+                for (int j = 0; j < 16 && n_base + j < p.N; j++) o[j] = v[j];
+              }
+            } else {
+              __nv_bfloat16* o = (__nv_bfloat16*)p.out + at;
+              if (whole && (at & 7) == 0) {
+                uint32_t packed[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                  packed[j] = *(uint32_t*)&h;
+                }
+                *(uint4*)(o) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                *(uint4*)(o + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+              } else {
+                for (int j = 0; j < 16 && n_base + j < p.N; j++) o[j] = __float2bfloat16_rn(v[j]);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && warp == 0 && lane == 0) {
+    // copies already issued still write shared memory: wait for them (bounded) before leaving
+    for (int i = max(0, issued - L::STAGES); i < issued; i++)
+      mbar_wait(&full_bar[i % L::STAGES], (i / L::STAGES) & 1);
+  }
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, L::TMEM_COLS);
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+  static EncodeTiled fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiled)ptr;
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr; int rows, cols, ld, box_rows;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
+};
+struct MapHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = (size_t)k.ptr;
+    for (int v : {k.rows, k.cols, k.ld, k.box_rows}) h = h * 1000003u ^ (size_t)v;
+    return h;
+  }
+};
+
+// A 2-D bf16 tensor map over [rows, cols] with row stride ld elements, boxes of box_rows x 64,
+// 128-byte swizzle, zero fill outside.  Maps are cached: an encode costs a few microseconds.
+int tensor_map(const void* ptr, int rows, int cols, int ld, int box_rows, CUtensorMap* out) {
+  static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
+  static std::mutex lock;
+  MapKey key{ptr, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> guard(lock);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return 0; }
+  EncodeTiled encode = encode_fn();
+  if (!encode) return sprout_fail("gemm_bf16: cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUtensorMap map;
+  CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return sprout_fail("gemm_bf16: cuTensorMapEncodeTiled failed with code %d", (int)rc);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, map);
+  *out = map;
+  return 0;
+}
+
+template <int BN, bool SWAP>
+int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const Params& p, dim3 grid, cudaStream_t stream) {
+  using L = Layout<BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
+    if (err != cudaSuccess) return sprout_fail("gemm_bf16: cannot reserve %d bytes of shared memory: %s", L::SMEM_BYTES, cudaGetErrorString(err));
+    configured = true;
+  }
+  gemm_tcgen05_kernel<BN, SWAP><<<grid, NUM_THREADS, L::SMEM_BYTES, stream>>>(rows_map, cols_map, p);
+  return sprout_check_launch("gemm_bf16");
+}
+
+}  // namespace
+
+// A [M, K] bf16 row stride lda; W [N, K] bf16 contiguous; out [M, N] row stride ldo, bf16 or
+// float32.  residual != 0: out is float32 and the product is added to it.  orientation: 0 picks
+// by M (weights on the MMA's M axis up to 128 tokens), 1 forces tokens on M, 2 weights on M.
+// split_k > 1 (weights-on-M, residual only) divides K among CTAs and adds with atomics.
+SPROUT_API int sprout_gemm_bf16(const void* A, const void* W, const float* bias, void* out, int out_dtype,
+                                int residual, int M, int N, int K, int lda, int ldo, int orientation,
+                                int split_k, int* status, cudaStream_t stream) {
+  SPROUT_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_bf16: sizes must be positive (M=%d N=%d K=%d)", M, N, K);
+  SPROUT_REQUIRE(A && W && out && status, "gemm_bf16: null pointer");
+  SPROUT_REQUIRE(K % 8 == 0 && lda % 8 == 0, "gemm_bf16: K (%d) and the row stride of A (%d) must be multiples of 8 "
+                 "(TMA rows start on 16-byte boundaries)", K, lda);
+  SPROUT_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_bf16: operands must be 16-byte aligned");
+  SPROUT_REQUIRE(lda >= K && ldo >= N, "gemm_bf16: row strides smaller than the rows");
+  SPROUT_REQUIRE(out_dtype == SPROUT_F32 || out_dtype == SPROUT_BF16, "gemm_bf16: unknown output dtype %d", out_dtype);
+  SPROUT_REQUIRE(!residual || out_dtype == SPROUT_F32, "gemm_bf16: a residual needs a float32 output");
+  const bool swap = orientation == 2 || (orientation == 0 && M <= 128);
+  SPROUT_REQUIRE(!swap || M <= 128, "gemm_bf16: weights-on-M takes at most 128 tokens (got %d)", M);
+  if (split_k < 1) split_k = 1;
+  SPROUT_REQUIRE(split_k == 1 || (swap && residual), "gemm_bf16: split_k needs weights-on-M with a residual output");
+
+  Params p;
+  p.bias = bias; p.out = out; p.out_is_f32 = out_dtype == SPROUT_F32;
+  p.epilogue = residual ? (split_k > 1 ? EPI_RESIDUAL_ATOMIC : EPI_RESIDUAL) : EPI_STORE;
+  p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.status = status;
+  const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+  if (split_k > total_kb) split_k = total_kb;
+  p.k_blocks_per_split = (total_kb + split_k - 1) / split_k;
+  split_k = (total_kb + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
+
+  CUtensorMap map_a, map_w;
+  if (swap) {
+    const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+    if (tensor_map(W, N, K, K, BLOCK_M, &map_w)) return 1;
+    if (tensor_map(A, M, K, lda, bn, &map_a)) return 1;
+    dim3 grid(1, (N + BLOCK_M - 1) / BLOCK_M, split_k);
+    switch (bn) {
+      case 16: return launch<16, true>(map_w, map_a, p, grid, stream);
+      case 32: return launch<32, true>(map_w, map_a, p, grid, stream);
+      case 64: return launch<64, true>(map_w, map_a, p, grid, stream);
+      default: return launch<128, true>(map_w, map_a, p, grid, stream);
+    }
+  }
+  if (tensor_map(A, M, K, lda, BLOCK_M, &map_a)) return 1;
+  if (tensor_map(W, N, K, K, 128, &map_w)) return 1;
+  dim3 grid((N + 127) / 128, (M + BLOCK_M - 1) / BLOCK_M, 1);
+  SPROUT_REQUIRE(grid.y <= 65535, "gemm_bf16: too many rows (%d)", M);
+  return launch<128, false>(map_a, map_w, p, grid, stream);
+}

@@ -32,6 +32,7 @@ _SIGNATURES = {
     "sprout_gemm_simple": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "sprout_attention_simple": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_sample": [_P, _I, _P, _P, _P, _I, _I, _P, _P],
+    "sprout_gemm_bf16": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
 }
 
 _lock = threading.Lock()
@@ -200,8 +201,29 @@ def attention_simple(q, k_cache, v_cache, block_table, seq_of_token, positions, 
          k_cache.shape[0], _ptr(status, "status", torch.int32), _stream())
 
 
-def has_tensor_core_gemm() -> bool:
-    return False
+def gemm_bf16(a, weight, out, status, bias=None, residual=None, orientation=0, split_k=1):
+    """out = a @ weight.T (+ bias) (+ residual) on the tcgen05 tensor cores; a and weight bfloat16.
+
+    ``residual`` must be ``out`` itself (float32): the product is added in place.  orientation 0
+    lets the kernel choose (weight rows on the MMA's M axis for up to 128 tokens), 1 forces
+    tokens on M, 2 weights on M.  ``split_k`` > 1 divides K among CTAs (weights on M with a
+    residual only; the partial sums are added with atomics)."""
+    _rows_contiguous(a, "a")
+    _rows_contiguous(out, "out")
+    if not weight.is_contiguous() or weight.dim() != 2:
+        raise KernelError("gemm_bf16: weight must be contiguous [N, K]")
+    M, K = a.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K or tuple(out.shape) != (M, N) or a.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_bf16: shapes/dtypes do not fit: a {tuple(a.shape)} {a.dtype}, "
+                          f"weight {tuple(weight.shape)} {weight.dtype}, out {tuple(out.shape)}")
+    if bias is not None and bias.numel() != N:
+        raise KernelError("gemm_bf16: bias must have N entries")
+    if residual is not None and residual.data_ptr() != out.data_ptr():
+        raise KernelError("gemm_bf16: the residual is added in place: pass out itself")
+    _run("sprout_gemm_bf16", _ptr(a, "a"), _ptr(weight, "weight"), _ptr(bias, "bias", torch.float32, True),
+         _ptr(out, "out"), _dtype_code(out.dtype), 1 if residual is not None else 0, M, N, K, a.stride(0),
+         out.stride(0), orientation, split_k, _ptr(status, "status", torch.int32), _stream())
 
 
 def paged_attention(q, cache, ctx, out, heads, kv_heads, head_dim, status):

@@ -62,9 +62,9 @@ class PagedGQAttention(Part):
         if self.qkv_bias:
             bias = torch.cat([source.raw(self.names[key] + ".bias").to(torch.float32) for key in ("q", "k", "v")])
             bias = bias.to(source.runtime.device)
-        self.qkv = Linear(source.to_device_matrix(fused), bias)
+        self.qkv = Linear(source.to_device_matrix(fused), bias, source.runtime.status)
         out_bias = source.vector(self.names["o"] + ".bias") if self.out_bias else None
-        self.out = Linear(source.matrix(self.names["o"] + ".weight"), out_bias)
+        self.out = Linear(source.matrix(self.names["o"] + ".weight"), out_bias, source.runtime.status)
         self.tables = self.position.rotary_tables(source.runtime)
 
     # ---- the step

@@ -43,7 +43,7 @@ class LMHead(Part):
         return [] if self.tied else [TensorDecl(self.tensor_name, (self.vocab_size, self.hidden_size))]
 
     def load(self, source: WeightSource):
-        self.linear = Linear(source.matrix(self.tensor_name))
+        self.linear = Linear(source.matrix(self.tensor_name), None, source.runtime.status)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         return self.linear.forward(h, out_dtype=torch.float32)

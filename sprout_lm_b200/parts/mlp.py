@@ -40,8 +40,8 @@ class SwiGLUMLP(Part):
 
     def load(self, source: WeightSource):
         fused = interleave_gate_up(source.raw(self.names["gate"] + ".weight"), source.raw(self.names["up"] + ".weight"))
-        self.gate_up = Linear(source.to_device_matrix(fused))
-        self.down = Linear(source.matrix(self.names["down"] + ".weight"))
+        self.gate_up = Linear(source.to_device_matrix(fused), None, source.runtime.status)
+        self.down = Linear(source.matrix(self.names["down"] + ".weight"), None, source.runtime.status)
 
     def forward(self, h, x, ctx=None):
         gate_up = self.gate_up.forward(h)

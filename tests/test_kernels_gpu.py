@@ -1,0 +1,328 @@
+"""Each kernel alone against a plain float32 reference of the same operation, at sizes other
+than the engine's: tails, odd widths, sizes that are no power of two."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def status():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+def rand(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+# ------------------------------------------------------------------------------- elementwise
+@pytest.mark.parametrize("table_dtype", [torch.float32, torch.bfloat16])
+def test_embed(status, table_dtype):
+    from sprout_lm_b200 import kernels
+    table = rand(101, 72, dtype=table_dtype)
+    tokens = torch.tensor([0, 100, 5, 5, 37], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 72, dtype=torch.float32, device=DEV)
+    kernels.embed(table, tokens, out, status)
+    assert torch.equal(out, table[tokens.long()].float())
+    assert int(status.item()) == 0
+    bad = torch.tensor([3, 101], dtype=torch.int32, device=DEV)
+    kernels.embed(table, bad, out[:2], status)                    # flagged, not faulted
+    assert int(status.item()) & 2
+    status.zero_()
+
+
+@pytest.mark.parametrize("hidden,eps", [(72, 1e-6), (896, 1e-5), (1000, 1e-6), (4100, 1e-5)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm(hidden, eps, out_dtype):
+    from sprout_lm_b200 import kernels
+    x = rand(7, hidden, scale=3.0)
+    gain = 1 + rand(hidden, scale=0.1, seed=1)
+    out = torch.empty(7, hidden, dtype=out_dtype, device=DEV)
+    kernels.rmsnorm(x, gain, out, eps)
+    x64 = x.double()
+    want = (x64 / torch.sqrt((x64 * x64).mean(-1, keepdim=True) + eps)).float().double() * gain.double()
+    tol = 2e-6 if out_dtype == torch.float32 else 8e-3
+    assert (out.double() - want).abs().max().item() <= tol * want.abs().max().item()
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    picked = torch.empty(3, hidden, dtype=out_dtype, device=DEV)
+    kernels.rmsnorm(x, gain, picked, eps, rows)
+    assert torch.equal(picked, out[rows.long()])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("inter", [8, 320, 4864])
+def test_swiglu_interleaved(dtype, inter):
+    from sprout_lm_b200 import kernels
+    from sprout_lm_b200.parts.mlp import interleave_gate_up
+    gate, up = rand(5, inter, dtype=dtype, scale=2.0), rand(5, inter, dtype=dtype, scale=2.0, seed=3)
+    fused = interleave_gate_up(gate.T.contiguous(), up.T.contiguous()).T.contiguous()   # columns interleaved like weight rows
+    out = torch.empty(5, inter, dtype=dtype, device=DEV)
+    kernels.swiglu(fused, out)
+    g = gate.double()
+    want = (g / (1 + torch.exp(-g))).float().double() * up.double()
+    tol = 1e-6 if dtype == torch.float32 else 8e-3
+    assert (out.double() - want).abs().max().item() <= tol * max(1.0, want.abs().max().item())
+    with pytest.raises(kernels.KernelError, match="multiple of 8"):
+        kernels.swiglu(torch.empty(2, 24, dtype=dtype, device=DEV), torch.empty(2, 12, dtype=dtype, device=DEV))
+
+
+def rope_reference(x, positions, head_dim, theta):
+    tokens = x.shape[0]
+    heads = x.shape[1] // head_dim
+    half = head_dim // 2
+    d = torch.arange(half, dtype=torch.float64)
+    angle = positions.double()[:, None, None] / theta ** (2 * d / head_dim)[None, None, :]
+    xs = x.double().cpu().reshape(tokens, heads, head_dim)
+    a, b = xs[..., :half], xs[..., half:]
+    return torch.cat([a * angle.cos() - b * angle.sin(), b * angle.cos() + a * angle.sin()], -1).reshape(tokens, -1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page,theta", [(4, 2, 16, 16, 1e4), (3, 1, 32, 8, 1e6), (5, 5, 48, 4, 5e5), (14, 2, 64, 16, 1e6)])
+def test_rope_append(status, dtype, heads, kv_heads, head_dim, page, theta):
+    from sprout_lm_b200 import kernels
+    from sprout_lm_b200.parts.rope import HalfSplitRotary
+    max_pos, pages = 4096, 40
+    rotary = HalfSplitRotary("", head_dim, theta, max_pos)
+
+    class RT:
+        device = torch.device(DEV)
+    cos, sin = rotary.rotary_tables(RT)
+    positions = torch.tensor([0, 1, page - 1, page, 3 * page + 1, 4095 % (pages * page // 2)], dtype=torch.int32)
+    T = positions.numel()
+    # two requests with scattered pages
+    seq_of_token = torch.tensor([0, 0, 0, 1, 1, 1], dtype=torch.int32)
+    max_pages = pages // 2
+    perm = torch.randperm(pages, generator=torch.Generator().manual_seed(1)).to(torch.int32)
+    table = perm.reshape(2, max_pages).contiguous()
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = rand(T, width, dtype=dtype)
+    original = qkv.clone()
+    k_cache = torch.zeros(pages, kv_heads, page, head_dim, dtype=dtype, device=DEV)
+    v_cache = torch.zeros_like(k_cache)
+    kernels.rope_append(qkv, positions.to(DEV), seq_of_token.to(DEV), table.to(DEV), cos, sin, k_cache, v_cache,
+                        heads, kv_heads, head_dim, page, True, status)
+    assert int(status.item()) == 0
+    q_want = rope_reference(original[:, :heads * head_dim], positions, head_dim, theta)
+    k_want = rope_reference(original[:, heads * head_dim:(heads + kv_heads) * head_dim], positions, head_dim, theta)
+    tol = 2e-6 if dtype == torch.float32 else 1.6e-2
+    assert (qkv[:, :heads * head_dim].double().cpu() - q_want).abs().max().item() <= tol * 4
+    for t in range(T):
+        pos = int(positions[t])
+        pg, slot = int(table[seq_of_token[t], pos // page]), pos % page
+        got_k = k_cache[pg, :, slot, :].reshape(-1).double().cpu()
+        assert (got_k - k_want[t]).abs().max().item() <= tol * 4
+        got_v = v_cache[pg, :, slot, :].reshape(-1)
+        assert torch.equal(got_v, original[t, (heads + kv_heads) * head_dim:])
+    # nothing else was touched
+    assert int((k_cache != 0).any(-1).any(1).sum().item()) == T
+    # a page id outside the pool is flagged and skipped
+    bad = table.clone()
+    bad[0, 0] = pages + 3
+    kernels.rope_append(original.clone(), positions.to(DEV), seq_of_token.to(DEV), bad.to(DEV), cos, sin, k_cache,
+                        v_cache, heads, kv_heads, head_dim, page, True, status)
+    assert int(status.item()) & 1
+    status.zero_()
+
+
+# ------------------------------------------------------------------------------- matrix products
+SHAPES = [(1, 1, 8), (1, 896, 896), (3, 130, 72), (8, 1152, 896), (17, 509, 96), (64, 256, 4864), (100, 77, 200),
+          (128, 896, 896), (129, 300, 136), (257, 1000, 328), (600, 1152, 896)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_gemm_simple_float32(M, N, K):
+    from sprout_lm_b200 import kernels
+    a, w, bias = rand(M, K), rand(N, K, seed=1), rand(N, seed=2)
+    out = torch.empty(M, N, device=DEV)
+    kernels.gemm_simple(a, w, out, bias=bias)
+    want = a.double() @ w.double().T + bias.double()
+    assert (out.double() - want).abs().max().item() <= 2e-6 * math.sqrt(K) * 4
+    # a row's result does not depend on the rows around it
+    if M > 2:
+        alone = torch.empty(1, N, device=DEV)
+        kernels.gemm_simple(a[M // 2:M // 2 + 1], w, alone, bias=bias)
+        assert torch.equal(alone[0], out[M // 2])
+    x = rand(M, N, seed=5)
+    want = x.double() + a.double() @ w.double().T
+    kernels.gemm_simple(a, w, x, residual=x)
+    assert (x.double() - want).abs().max().item() <= 2e-6 * math.sqrt(K) * 4
+
+
+@pytest.mark.parametrize("orientation", [0, 1, 2])
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_gemm_bf16_tensor_cores(status, M, N, K, orientation):
+    from sprout_lm_b200 import kernels
+    if orientation == 2 and M > 128:
+        pytest.skip("weights-on-M takes at most 128 tokens")
+    a, w, bias = rand(M, K, dtype=torch.bfloat16), rand(N, K, dtype=torch.bfloat16, seed=1), rand(N, seed=2)
+    want = a.double() @ w.double().T + bias.double()
+    scale = want.abs().max().item()
+    out = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    kernels.gemm_bf16(a, w, out, status, bias=bias, orientation=orientation)
+    assert (out.double() - want).abs().max().item() <= 1e-5 * scale + 1e-6       # float32 accumulation of exact products
+    out16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_bf16(a, w, out16, status, bias=bias, orientation=orientation)
+    assert (out16.double() - want).abs().max().item() <= 8e-3 * scale
+    x = rand(M, N, seed=5)
+    want_res = x.double() + a.double() @ w.double().T
+    kernels.gemm_bf16(a, w, x, status, residual=x, orientation=orientation)
+    assert (x.double() - want_res).abs().max().item() <= 1e-5 * scale + 1e-6
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("M,N,K,split", [(1, 896, 4864, 16), (8, 896, 896, 14), (64, 130, 1000, 5), (128, 256, 264, 9)])
+def test_gemm_bf16_split_k(status, M, N, K, split):
+    from sprout_lm_b200 import kernels
+    a, w = rand(M, K, dtype=torch.bfloat16), rand(N, K, dtype=torch.bfloat16, seed=1)
+    x = rand(M, N, seed=5)
+    want = x.double() + a.double() @ w.double().T
+    kernels.gemm_bf16(a, w, x, status, residual=x, orientation=2, split_k=split)
+    assert (x.double() - want).abs().max().item() <= 2e-5 * want.abs().max().item() + 1e-6
+    assert int(status.item()) == 0
+
+
+def test_gemm_bf16_refuses_unaligned_rows(status):
+    from sprout_lm_b200 import kernels
+    a, w = rand(4, 20, dtype=torch.bfloat16), rand(8, 20, dtype=torch.bfloat16)
+    with pytest.raises(kernels.KernelError, match="multiples of 8"):
+        kernels.gemm_bf16(a, w, torch.empty(4, 8, device=DEV), status)
+
+
+# ------------------------------------------------------------------------------- attention
+def attention_reference(q, keys, values, heads, kv_heads, head_dim):
+    """q [heads*hd]; keys, values [n, kv_heads*hd] (float64) -> [heads*hd]."""
+    out = torch.zeros(heads * head_dim, dtype=torch.float64)
+    group = heads // kv_heads
+    for h in range(heads):
+        g = h // group
+        s = keys[:, g * head_dim:(g + 1) * head_dim] @ q[h * head_dim:(h + 1) * head_dim] / math.sqrt(head_dim)
+        out[h * head_dim:(h + 1) * head_dim] = torch.softmax(s, 0) @ values[:, g * head_dim:(g + 1) * head_dim]
+    return out
+
+
+def build_paged_case(dtype, heads, kv_heads, head_dim, page, lengths, q_counts, seed=0, spike=None):
+    """Requests with ``lengths`` cached positions each (the last ``q_counts`` of them are this
+    step's queries), in pages scattered over the pool."""
+    g = torch.Generator().manual_seed(seed)
+    R = len(lengths)
+    pages_each = [-(-n // page) for n in lengths]
+    pool = sum(pages_each) + 3
+    order = torch.randperm(pool, generator=g)
+    table = torch.full((R, max(pages_each)), -1, dtype=torch.int32)
+    k_cache = torch.zeros(pool, kv_heads, page, head_dim)
+    v_cache = torch.zeros(pool, kv_heads, page, head_dim)
+    keys, values, at = [], [], 0
+    for r, n in enumerate(lengths):
+        k = torch.randn(n, kv_heads * head_dim, generator=g)
+        v = torch.randn(n, kv_heads * head_dim, generator=g)
+        if spike is not None and r == spike[0]:
+            k[spike[1]] *= 6.0                       # one far key whose score stands out
+        k, v = k.to(dtype).float(), v.to(dtype).float()
+        keys.append(k.double())
+        values.append(v.double())
+        for i in range(pages_each[r]):
+            pg = int(order[at]); at += 1
+            table[r, i] = pg
+            rows = slice(i * page, min(n, (i + 1) * page))
+            count = rows.stop - rows.start
+            k_cache[pg, :, :count] = k[rows].reshape(count, kv_heads, head_dim).transpose(0, 1)
+            v_cache[pg, :, :count] = v[rows].reshape(count, kv_heads, head_dim).transpose(0, 1)
+    positions, seq_of_token = [], []
+    for r, (n, c) in enumerate(zip(lengths, q_counts)):
+        positions += list(range(n - c, n))
+        seq_of_token += [r] * c
+    T = len(positions)
+    q = torch.randn(T, heads * head_dim, generator=g)
+    if spike is not None:
+        # queries of the spiked request look at the spiked key
+        for t in range(T):
+            if seq_of_token[t] == spike[0]:
+                group = heads // kv_heads
+                for h in range(heads):
+                    gk = h // group
+                    q[t, h * head_dim:(h + 1) * head_dim] = keys[spike[0]][spike[1], gk * head_dim:(gk + 1) * head_dim].float()
+    q = q.to(dtype)
+    want = torch.stack([attention_reference(q[t].double(), keys[seq_of_token[t]][:positions[t] + 1],
+                                            values[seq_of_token[t]][:positions[t] + 1], heads, kv_heads, head_dim)
+                        for t in range(T)])
+    dev = lambda x, dt=None: x.to(dt or x.dtype).to(DEV)
+    return dict(q=dev(q), k_cache=dev(k_cache, dtype), v_cache=dev(v_cache, dtype), table=dev(table),
+                positions=dev(torch.tensor(positions, dtype=torch.int32)),
+                seq_of_token=dev(torch.tensor(seq_of_token, dtype=torch.int32)), want=want, T=T,
+                q_start=dev(torch.tensor(np.cumsum([0] + list(q_counts)), dtype=torch.int32)),
+                context_lens=dev(torch.tensor(lengths, dtype=torch.int32)), lengths=lengths, q_counts=q_counts)
+
+
+ATTN_CASES = [
+    # heads, kv_heads, head_dim, page, cached lengths, queries of this step
+    (4, 2, 16, 16, [5, 17, 33], [5, 1, 33]),
+    (3, 1, 32, 8, [61, 1, 130], [7, 1, 1]),
+    (14, 2, 64, 16, [300, 129, 16], [1, 1, 16]),
+    (5, 5, 48, 4, [40, 9], [2, 9]),
+    (8, 2, 128, 16, [257, 64], [3, 64]),
+    (6, 3, 80, 32, [100], [100]),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page,lengths,q_counts", ATTN_CASES)
+def test_attention_simple(status, dtype, heads, kv_heads, head_dim, page, lengths, q_counts):
+    from sprout_lm_b200 import kernels
+    case = build_paged_case(dtype, heads, kv_heads, head_dim, page, lengths, q_counts)
+    out = torch.empty(case["T"], heads * head_dim, dtype=dtype, device=DEV)
+    kernels.attention_simple(case["q"], case["k_cache"], case["v_cache"], case["table"], case["seq_of_token"],
+                             case["positions"], out, heads, kv_heads, head_dim, status)
+    tol = 3e-6 if dtype == torch.float32 else 1.2e-2
+    assert (out.double().cpu() - case["want"]).abs().max().item() <= tol
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("where", [0, 15, 16, 255, 256, 383, 500])
+def test_attention_finds_one_far_key_among_hundreds(status, dtype, where):
+    """The query equals one key scaled up: nearly all the weight lies on that key, at a page's
+    first or last slot or far back; an attention that skips it returns something else."""
+    from sprout_lm_b200 import kernels
+    heads, kv_heads, head_dim, page = 4, 2, 32, 16
+    case = build_paged_case(dtype, heads, kv_heads, head_dim, page, [40, 501], [1, 1], seed=where, spike=(1, where))
+    out = torch.empty(case["T"], heads * head_dim, dtype=dtype, device=DEV)
+    kernels.attention_simple(case["q"], case["k_cache"], case["v_cache"], case["table"], case["seq_of_token"],
+                             case["positions"], out, heads, kv_heads, head_dim, status)
+    tol = 3e-6 if dtype == torch.float32 else 1.5e-2
+    assert (out.double().cpu() - case["want"]).abs().max().item() <= tol
+
+
+# ------------------------------------------------------------------------------- sampling
+@pytest.mark.parametrize("vocab", [7, 256, 509, 4099, 151936])
+def test_sampling(status, vocab):
+    from sprout_lm_b200 import kernels
+    logits = rand(6, vocab, scale=2.0)
+    logits[1, 3] = logits[1].max() + 1
+    logits[1, vocab - 1] = logits[1, 3]                           # a tie: the lowest index wins
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    kernels.sample(logits, out, status)
+    assert out.tolist() == logits.argmax(-1).tolist() or out[1].item() == 3
+    assert out[1].item() == 3
+    temperature = torch.tensor([0.0, 0.8, 0.8, 1.5, 0.3, 0.8], device=DEV)
+    for u in (0.0, 0.25, 0.5, 0.999999):
+        uniform = torch.full((6,), u, device=DEV)
+        kernels.sample(logits, out, status, temperature, uniform)
+        assert out[0].item() == int(logits[0].argmax())
+        for r in range(1, 6):
+            p = torch.softmax(logits[r].double() / temperature[r].double(), 0)
+            c = torch.cumsum(p, 0)
+            pick = out[r].item()
+            low = c[pick - 1].item() if pick else 0.0
+            assert low - 1e-4 <= u <= c[pick].item() + 1e-4, (r, u, pick)
+    assert int(status.item()) == 0
+    logits[2, 1] = float("nan")
+    kernels.sample(logits, out, status)
+    assert out[2].item() == -1 and int(status.item()) & 4
+    status.zero_()
