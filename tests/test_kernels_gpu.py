@@ -143,7 +143,9 @@ def test_gemm_simple_float32(M, N, K):
     out = torch.empty(M, N, device=DEV)
     kernels.gemm_simple(a, w, out, bias=bias)
     want = a.double() @ w.double().T + bias.double()
-    assert (out.double() - want).abs().max().item() <= 2e-6 * math.sqrt(K) * 4
+    # sequential float32 accumulation: error grows like eps * sqrt(K) times the magnitude of the sums
+    tol = 4 * 6e-8 * math.sqrt(K) * want.abs().max().item() + 1e-6
+    assert (out.double() - want).abs().max().item() <= tol
     # a row's result does not depend on the rows around it
     if M > 2:
         alone = torch.empty(1, N, device=DEV)
@@ -152,7 +154,7 @@ def test_gemm_simple_float32(M, N, K):
     x = rand(M, N, seed=5)
     want = x.double() + a.double() @ w.double().T
     kernels.gemm_simple(a, w, x, residual=x)
-    assert (x.double() - want).abs().max().item() <= 2e-6 * math.sqrt(K) * 4
+    assert (x.double() - want).abs().max().item() <= tol
 
 
 @pytest.mark.parametrize("orientation", [0, 1, 2])
