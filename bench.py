@@ -1,0 +1,320 @@
+"""Benchmark: decode tokens per second of the Qwen2.5-0.5B shape on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step.  The default run has the layer sizes of the 0.5B configuration
+(24 layers, hidden 896, 14/2 heads of 64, feed-forward 4864, vocabulary 151936, tied head)
+with random weights in bfloat16, a batch of 8 requests with 512-token random prompts and a
+4096-token context limit.  One JSON line is printed:
+
+* ``value``: decoded tokens per second with the step running wholly on the device (sampled
+  tokens fed back by a kernel, the step replayed as a CUDA graph), timed with CUDA events
+  over exactly K steps after W warm-up steps;
+* ``e2e``: the same through the Python entry point (``Engine.step``): every step copies the
+  batch's arrays from pinned host memory to the device and reads the new token ids back;
+* ``prefill``: one 2,048-token prompt in one step, tokens per second and the fraction of the
+  bfloat16 tensor-core peak its floating-point work reaches;
+* ``roofline``: bytes a decode step must read (every weight once, the cache of the live
+  requests) over its time, against the measured copy bandwidth;
+* ``points``: decode tokens per second at batch 1 and 64;
+* ``clocks``: SM clock and throttle reasons sampled during the timed region.
+
+Inputs are larger than the L2 cache (988 MB of weights are read every step), so no flush is
+needed between timed iterations.  ``--gpus N`` with N > 1 is refused with exit code 2: this
+engine runs on one GPU.  ``--impl reference`` reports why the reference cannot run here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+CONFIG_05B = dict(hidden_size=896, intermediate_size=4864, num_hidden_layers=24, num_attention_heads=14,
+                  num_key_value_heads=2, vocab_size=151936, max_position_embeddings=4096, rms_norm_eps=1e-6,
+                  rope_theta=1000000.0, tie_word_embeddings=True, eos_token_id=151645)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+REFERENCE_UNAVAILABLE = ("the reference is a TypeScript program for Node >= 24 with a Node-API CUDA module; it has no "
+                         "Python package to install (pip finds no setup.py or pyproject.toml) and node is not in this image")
+
+
+def peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            raw = json.loads(path.read_text())
+            found = {"source": "measured"}
+            for key in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+                value = raw.get(key)
+                if isinstance(value, dict):
+                    value = value.get("value")
+                if isinstance(value, (int, float)):
+                    found[key] = float(value)
+            if "hbm_gbs" in found and "bf16_tflops" in found:
+                return found
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples = []
+        self.process = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.process = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                             "--format=csv,noheader,nounits", "-lms", "100"],
+                                            stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.process.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self) -> dict:
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.process.terminate()
+        try:
+            self.process.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+        clocks = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        peak = [float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({name for s in self.samples for name, flag in zip(names, s[2:6]) if flag.lower().startswith("active")})
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max(peak) if peak else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def model_folder(layers: int) -> Path:
+    """The random-weights model folder of the benchmark shape (written once per temporary folder)."""
+    from sprout_lm_b200 import parse_config, write_random_model
+    sizes = dict(CONFIG_05B, num_hidden_layers=layers)
+    folder = Path(tempfile.gettempdir()) / f"sprout_lm_b200_bench_{os.getuid()}_L{layers}"
+    config = parse_config({"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu", **sizes})
+    marker = folder / "complete"
+    if not marker.exists():
+        print(f"[bench] writing random weights to {folder}", file=sys.stderr, flush=True)
+        write_random_model(folder, config, seed=0)
+        marker.write_text("ok")
+    return folder
+
+
+def weight_bytes(model) -> int:
+    """Bytes of every weight a decode step uses once (the tied head is the embedding matrix)."""
+    seen, total = set(), 0
+
+    def add(t):
+        nonlocal total
+        if t is not None and t.data_ptr() not in seen:
+            seen.add(t.data_ptr())
+            total += t.numel() * t.element_size()
+    for block in model.blocks:
+        for lin in (block.mixer.qkv, block.mixer.out, block.feed_forward.gate_up, block.feed_forward.down):
+            add(lin.weight)
+            add(lin.bias)
+        for norm in block.norms:
+            add(norm.gain)
+    add(model.final_norm.gain)
+    add(model.head.linear.weight)
+    return total
+
+
+def prefill_flops(cfg: dict, tokens: int) -> float:
+    h, i, l = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+    heads, kv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    hd = h // heads
+    per_token = l * 2 * (h * (heads + 2 * kv) * hd + heads * hd * h + 2 * h * i + i * h)
+    attention = l * 4 * heads * hd * tokens * (tokens + 1) / 2          # QK^T and PV over the causal half
+    head = 2 * h * cfg["vocab_size"]                                     # logits at one place
+    return per_token * tokens + attention + head
+
+
+def timed_decode(runner, batch: int, prompt_len: int, steps: int, warmup: int, rng, sampler=None):
+    """Prefill ``batch`` prompts, then time ``steps`` decode steps that run wholly on the device."""
+    import torch
+    from sprout_lm_b200.engine.batch import StepEntry
+    vocab = runner.vocab_size
+    seqs = []
+    for _ in range(batch):
+        seq = runner.new_sequence()
+        assert runner.reserve(seq, prompt_len)
+        seqs.append(seq)
+    chunk = max(1, 4096 // prompt_len)
+    first = []
+    for at in range(0, batch, chunk):
+        entries = [StepEntry(s, [int(t) for t in rng.integers(0, vocab, prompt_len)], [prompt_len - 1])
+                   for s in seqs[at:at + chunk]]
+        first += runner.step_and_sample(entries, [0.0] * len(entries), [0.0] * len(entries))
+    entries = [StepEntry(s, [t], [0]) for s, t in zip(seqs, first)]
+    loop = runner.decode_loop(entries, [0.0] * batch, [0.0] * batch, max_steps=steps + warmup + 2)
+    loop.run(max(warmup - 1, 0))                 # capture runs one more step
+    torch.cuda.synchronize()
+    if sampler:
+        sampler.start()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    loop.run(steps)
+    end.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler else None
+    ms = begin.elapsed_time(end)
+    mean_context = prompt_len + warmup + steps / 2
+    tokens = loop.finish()
+    runner.check_status()
+    assert tokens.shape[0] == steps + warmup and int(tokens.min()) >= 0
+    for s in seqs:
+        runner.release(s)
+    return {"ms_per_step": ms / steps, "tokens_per_s": batch * steps / (ms / 1000), "launches_per_step": loop.launches_per_step,
+            "mean_context": mean_context, "clocks": clocks}
+
+
+def timed_e2e(model, batch: int, prompt_len: int, steps: int, warmup: int, rng):
+    """The same workload through Engine.step: host token ids in, host token ids out, every step."""
+    import torch
+    from sprout_lm_b200 import EngineOptions, make_engine
+    pages = batch * (-(-(prompt_len + steps + warmup + 8) // 16)) + 8
+    engine = make_engine(model, EngineOptions(block_size=16, num_blocks=pages, max_sequences=max(batch, 1),
+                                              max_batch_tokens=8192, prefill_chunk_size=2048, prefix_caching=False,
+                                              record_trace=False))
+    for i in range(batch):
+        engine.add(f"r{i}", [int(t) for t in rng.integers(0, model.spec.vocab_size, prompt_len)],
+                   steps + warmup + 4, ignore_eos=True)
+    while any(w["phase"] != "decode" for w in engine.step()["work"]):
+        pass
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    before = dict(engine.runner.stats)
+    start = time.perf_counter()
+    produced = 0
+    for _ in range(steps):
+        report = engine.step()
+        produced += sum(1 for e in report["events"] if e["type"] == "token")
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - start
+    engine.runner.check_status()
+    assert produced == batch * steps
+    h2d = (engine.runner.stats["h2d_bytes"] - before["h2d_bytes"]) // steps
+    d2h = (engine.runner.stats["d2h_bytes"] - before["d2h_bytes"]) // steps
+    return {"value": produced / seconds, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "ms_per_step": seconds * 1000 / steps}
+
+
+def timed_prefill(runner, tokens: int, rng, repeats: int = 5):
+    import torch
+    from sprout_lm_b200.engine.batch import StepEntry
+    times = []
+    for _ in range(repeats + 2):
+        seq = runner.new_sequence()
+        assert runner.reserve(seq, tokens)
+        entry = StepEntry(seq, [int(t) for t in rng.integers(0, runner.vocab_size, tokens)], [tokens - 1])
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        ctx = runner.stager.stage([entry], runner.page_tokens)
+        logits = runner.forward(ctx)
+        end.record()
+        torch.cuda.synchronize()
+        assert bool(torch.isfinite(logits).all())
+        times.append(begin.elapsed_time(end))
+        runner.release(seq)
+    return statistics.median(times[2:])
+
+
+def run(args) -> dict:
+    import numpy as np
+    import torch
+    from sprout_lm_b200 import kernels, load_model
+    from sprout_lm_b200.cache.storage import cache_bytes_per_token
+    from sprout_lm_b200.engine.step import ModelRunner
+    kernels.load_library(verbose=True)
+    layers = args.layers or CONFIG_05B["num_hidden_layers"]
+    folder = model_folder(layers)
+    model = load_model(folder, dtype="bfloat16", device="cuda:0")
+    cfg = dict(CONFIG_05B, num_hidden_layers=layers)
+    peak = peaks()
+    rng = np.random.default_rng(0)
+    batch, prompt_len, context = args.batch, 512, CONFIG_05B["max_position_embeddings"]
+    pages = 64 * (-(-(prompt_len + args.steps + args.warmup + 16) // 16)) + 2048 // 16 + 16
+    runner = ModelRunner(model, num_pages=pages, page_tokens=16, max_requests=64, prefix_caching=False)
+
+    main = timed_decode(runner, batch, prompt_len, args.steps, args.warmup, rng, sampler=ClockSampler())
+    points = {}
+    for b in (1, 64):
+        side_steps = min(args.steps, 64)
+        points[f"decode_b{b}"] = round(timed_decode(runner, b, prompt_len, side_steps, args.warmup, rng)["tokens_per_s"], 1)
+    prefill_ms = timed_prefill(runner, 2048, rng)
+    flops = prefill_flops(cfg, 2048)
+    e2e = timed_e2e(model, batch, prompt_len, args.steps, args.warmup, rng)
+
+    step_bytes = weight_bytes(model) + batch * main["mean_context"] * cache_bytes_per_token(model, torch.bfloat16)
+    achieved = step_bytes / (main["ms_per_step"] / 1000) / 1e9
+    return {
+        "metric": "decode tokens/s, Qwen2.5-0.5B shape, batch 8 (also batch 1/64 and prefill of 2,048 tokens)",
+        "value": round(main["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), uniform random token ids)",
+        "impl": "ours",
+        "config": {"model": "Qwen2.5-0.5B shape", "layers": layers, "layers_of_model": CONFIG_05B["num_hidden_layers"],
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": 64, "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "tied_head": True, "global_batch": batch, "prompt_len": prompt_len, "seq_len": context,
+                   "page_tokens": 16, "parallelism": "single GPU", "l2": "inputs larger than L2 (weights 988 MB per step)"},
+        "e2e": {k: (round(v, 3) if isinstance(v, float) else v) for k, v in e2e.items()},
+        "gpu_launches": int(main["launches_per_step"] * args.steps),
+        "prefill": {"value": round(2048 / (prefill_ms / 1000), 1), "tokens": 2048, "ms": round(prefill_ms, 4),
+                    "frac": round(flops / (prefill_ms / 1000) / (peak["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peak["hbm_gbs"], 4), "peaks": peak["source"]},
+        "points": points,
+        "clocks": main["clocks"],
+    }
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    result = run(args)
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -126,3 +126,33 @@ SPROUT_API int sprout_sample(const float* logits, int ld, const float* temperatu
   sample_kernel<<<rows, THREADS, 0, stream>>>(logits, ld, temperature, uniform, out, vocab, status);
   return sprout_check_launch("sample");
 }
+
+// ------------------------------------------------------------------ feeding a decode step's output back
+// After a decode step on the device: every request's sampled token becomes its next input
+// token, its position and cache length grow by one, and the tokens are recorded in row
+// `*step_counter` of `history` ([max_steps, requests]); the counter then advances.  This lets
+// several decode steps run back to back (or as one replayed CUDA graph) without the host.
+__global__ void advance_decode_kernel(int* token_ids, int* positions, int* context_lens, const int* sampled,
+                                      int* history, int* step_counter, int requests, int max_steps) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  const int step = *step_counter;
+  if (r < requests) {
+    const int token = sampled[r];
+    token_ids[r] = token < 0 ? 0 : token;
+    positions[r] += 1;
+    context_lens[r] += 1;
+    if (step < max_steps) history[(size_t)step * requests + r] = token;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x == 0 && gridDim.x == 1) *step_counter = step + 1;
+}
+
+SPROUT_API int sprout_advance_decode(int* token_ids, int* positions, int* context_lens, const int* sampled,
+                                     int* history, int* step_counter, int requests, int max_steps,
+                                     cudaStream_t stream) {
+  SPROUT_REQUIRE(requests > 0 && requests <= 1024 && max_steps > 0, "advance_decode: 1..1024 requests, max_steps > 0");
+  SPROUT_REQUIRE(token_ids && positions && context_lens && sampled && history && step_counter, "advance_decode: null pointer");
+  advance_decode_kernel<<<1, 1024, 0, stream>>>(token_ids, positions, context_lens, sampled, history, step_counter,
+                                                requests, max_steps);
+  return sprout_check_launch("advance_decode");
+}

@@ -39,7 +39,7 @@ class StepContext:
     logits_rows: torch.Tensor
     block_tables: list
     page_tokens: int
-    scratch: dict = field(default_factory=dict)
+    floats: dict = field(default_factory=dict)      # extra float32 arrays staged with the batch (sampling)
 
     @property
     def all_decode(self) -> bool:
@@ -61,6 +61,7 @@ class BatchStager:
         self._events = [None, None]
         self._flip = 0
         self._device_buf = None
+        self.last_bytes = 0
         self._grow(capacity_ints)
 
     def _grow(self, ints: int):
@@ -69,9 +70,10 @@ class BatchStager:
         self._events = [None, None]
         self._device_buf = torch.empty(ints, dtype=torch.int32, device=self.device)
 
-    def layout(self, T: int, R: int, S: int, max_pages: int):
+    def layout(self, T: int, R: int, S: int, max_pages: int, floats=None):
         sizes = [("token_ids", T), ("positions", T), ("seq_of_token", T), ("q_start", R + 1),
                  ("context_lens", R), ("state_slots", R), ("logits_rows", S)]
+        sizes += [(f"float:{name}", len(values)) for name, values in (floats or {}).items()]
         sizes += [(f"table{g}", R * max_pages) for g in range(self.num_groups)]
         offsets, at = {}, 0
         for name, n in sizes:
@@ -79,7 +81,10 @@ class BatchStager:
             at += _pad4(max(n, 1))
         return offsets, at
 
-    def stage(self, entries, page_tokens: int, fixed_pages: int | None = None) -> StepContext:
+    def stage(self, entries, page_tokens: int, fixed_pages: int | None = None, floats=None) -> StepContext:
+        """Pack and copy.  ``fixed_pages`` fixes the block tables' width (a replayed CUDA graph
+        needs the same layout every time); ``floats`` are extra float32 arrays (name -> values)
+        that travel in the same copy."""
         R = len(entries)
         counts = [len(e.tokens) for e in entries]
         T = sum(counts)
@@ -91,7 +96,7 @@ class BatchStager:
             if max_pages > fixed_pages:
                 raise ValueError("block table longer than the fixed table width")
             max_pages = fixed_pages
-        offsets, total = self.layout(T, R, S, max_pages)
+        offsets, total = self.layout(T, R, S, max_pages, floats)
         if total > self._capacity:
             self._grow(max(total, 2 * self._capacity))
         self._flip ^= 1
@@ -116,6 +121,8 @@ class BatchStager:
         rows = [q_start[i] + w for i, e in enumerate(entries) for w in e.want]
         if rows:
             put("logits_rows", np.asarray(rows, dtype=np.int32))
+        for name, values in (floats or {}).items():
+            put(f"float:{name}", np.asarray(values, dtype=np.float32).view(np.int32))
         for g in range(self.num_groups):
             table = np.full((R, max_pages), -1, dtype=np.int32)
             for i, e in enumerate(entries):
@@ -123,6 +130,7 @@ class BatchStager:
                 table[i, :len(pages)] = pages
             put(f"table{g}", table.reshape(-1))
         self._device_buf[:total].copy_(host[:total], non_blocking=True)
+        self.last_bytes = total * 4
         event = torch.cuda.Event()
         event.record()
         self._events[self._flip] = event
@@ -138,4 +146,5 @@ class BatchStager:
             q_start=view("q_start"), context_lens=view("context_lens"), state_slots=view("state_slots"),
             logits_rows=view("logits_rows"),
             block_tables=[view(f"table{g}", (R, max_pages)) for g in range(self.num_groups)],
-            page_tokens=page_tokens)
+            page_tokens=page_tokens,
+            floats={name: view(f"float:{name}").view(torch.float32) for name in (floats or {})})

@@ -69,8 +69,9 @@ def uniform_for(seed: int, request_id: str, index: int) -> float:
 class Engine:
     """``runner`` provides the model side: ``vocab_size``, ``max_positions``, ``eos_token_ids``,
     ``manager`` (the cache manager), ``new_sequence(tokens | None)``, ``reserve(seq, upto)``,
-    ``release(seq)``, ``step(entries) -> logits`` and ``sample(logits, temperatures, uniforms)
-    -> token ids`` (a sequence of ints, or a tensor)."""
+    ``release(seq)`` and ``step_and_sample(entries, temperatures, uniforms) -> token ids``: run
+    the batch, sample at every wanted place (greedy where the temperature is 0, else at the
+    given uniform number) and return the new tokens in the order of the entries."""
 
     def __init__(self, runner, options: EngineOptions | None = None):
         self.options = options or EngineOptions()
@@ -188,8 +189,12 @@ class Engine:
         if planned:
             entries = [StepEntry(r.seq, tokens, [len(tokens) - 1] if wants else [])
                        for r, _, _, tokens, wants in planned]
-            logits = self.runner.step(entries)
-            sampled = self._sample(planned, logits)
+            rows = [(r, len(r.output)) for r, _, _, _, wants in planned if wants]
+            temperatures = [r.temperature for r, _ in rows]
+            uniforms = [uniform_for(r.seed, r.id, index) if r.temperature > 0 else 0.0 for r, index in rows]
+            sampled = [int(t) for t in self.runner.step_and_sample(entries, temperatures, uniforms)]
+            if len(sampled) != len(rows) or any(t < 0 or t >= self.runner.vocab_size for t in sampled):
+                raise RuntimeError("Runner returned invalid sampled token.")
             row = 0
             for request, phase, start, tokens, wants in planned:
                 seq = request.seq
@@ -202,19 +207,6 @@ class Engine:
                 work.append({"id": request.id, "phase": phase, "from": start, "tokens": len(tokens),
                              "blockTable": table})
         return {"tick": self._tick, "work": work, "events": events, "memory": self.cache.snapshot()}
-
-    def _sample(self, planned, logits):
-        rows = [(r, len(r.output)) for r, _, _, _, wants in planned if wants]
-        if not rows:
-            return []
-        temperatures = [r.temperature for r, _ in rows]
-        uniforms = [uniform_for(r.seed, r.id, index) if r.temperature > 0 else 0.0 for r, index in rows]
-        tokens = self.runner.sample(logits, temperatures, uniforms)
-        tokens = [int(t) for t in (tokens.tolist() if hasattr(tokens, "tolist") else tokens)]
-        for token in tokens:
-            if token < 0 or token >= self.runner.vocab_size:
-                raise RuntimeError("Runner returned invalid sampled token.")
-        return tokens
 
     def _accept(self, request: Request, token: int) -> None:
         request.output.append(token)

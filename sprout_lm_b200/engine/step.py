@@ -39,6 +39,10 @@ class ModelRunner:
         self.max_positions = model.spec.max_positions
         self.eos_token_ids = tuple(model.spec.eos_token_ids)
         self.steps_run = 0
+        # bytes copied to and from the device by steps (the batch's arrays up, token ids or logits down)
+        self.stats = {"h2d_bytes": 0, "d2h_bytes": 0}
+        from .graphs import GraphCache
+        self.graphs = GraphCache(self)
 
     # ------------------------------------------------------------------ requests' caches
     def new_sequence(self, tokens=None):
@@ -99,6 +103,44 @@ class ModelRunner:
             self.manager.trim(e.seq)
         self.steps_run += 1
         return logits
+
+    def step_and_sample(self, entries: list[StepEntry], temperatures, uniforms) -> list[int]:
+        """Run one batch and sample at every wanted place; the new token ids, in the order of the
+        entries.  Only token ids come back from the device.  A batch of single decode tokens
+        runs as a replayed CUDA graph."""
+        self.validate(entries)
+        decode_only = self.graphs.enabled and all(len(e.tokens) == 1 and e.want == [0] for e in entries)
+        if decode_only:
+            graph = self.graphs.get(entries)
+            tokens = graph.run(entries, temperatures, uniforms)
+            self.stats["h2d_bytes"] += graph.stager.last_bytes
+        else:
+            floats = {"temperature": temperatures, "uniform": uniforms} if temperatures else None
+            ctx = self.stager.stage(entries, self.page_tokens, floats=floats)
+            self.stats["h2d_bytes"] += self.stager.last_bytes
+            logits = self.forward(ctx)
+            tokens = None
+            if logits is not None:
+                tokens = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+                kernels.sample(logits, tokens, self.runtime.status, ctx.floats["temperature"], ctx.floats["uniform"])
+        for e in entries:
+            e.seq.length += len(e.tokens)
+            self.manager.trim(e.seq)
+        self.steps_run += 1
+        if tokens is None:
+            return []
+        self.stats["d2h_bytes"] += tokens.numel() * 4
+        return tokens.tolist()
+
+    def decode_loop(self, entries, temperatures, uniforms, max_steps: int):
+        """A device-side run of decode steps (see ``graphs.DecodeLoop``): pages for ``max_steps``
+        more tokens per request are reserved here."""
+        from .graphs import DecodeLoop
+        self.validate(entries)
+        for e in entries:
+            if not self.reserve(e.seq, e.seq.length + 1 + max_steps):
+                raise StepError("not enough pages for a device-side decode loop")
+        return DecodeLoop(self, entries, temperatures, uniforms, max_steps)
 
     def forward(self, ctx: StepContext):
         return self.model.forward(ctx, self.storage)

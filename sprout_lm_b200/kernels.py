@@ -15,6 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
+LAUNCHES = 0          # kernels launched through this module (one per call); benchmarks read the difference
 STATUS_BITS = {1: "a block-table entry outside the page pool", 2: "a token id outside the vocabulary",
                4: "non-finite logits", 8: "a bounded device-side wait ran out", 16: "a position outside the rotary table"}
 
@@ -32,6 +33,7 @@ _SIGNATURES = {
     "sprout_gemm_simple": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "sprout_attention_simple": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_sample": [_P, _I, _P, _P, _P, _I, _I, _P, _P],
+    "sprout_advance_decode": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
     "sprout_gemm_bf16": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
 }
 
@@ -85,7 +87,9 @@ def _stream() -> int:
 
 
 def _run(name, *args):
+    global LAUNCHES
     lib = load_library()
+    LAUNCHES += 1
     code = getattr(lib, name)(*args)
     if code != 0:
         raise KernelError(lib.sprout_last_error().decode())
@@ -242,6 +246,17 @@ def sample(logits, out, status, temperature=None, uniform=None):
     _run("sprout_sample", _ptr(logits, "logits", torch.float32), logits.stride(0),
          _ptr(temperature, "temperature", torch.float32, True), _ptr(uniform, "uniform", torch.float32, True),
          _ptr(out, "out", torch.int32), R, V, _ptr(status, "status", torch.int32), _stream())
+
+
+def advance_decode(token_ids, positions, context_lens, sampled, history, step_counter):
+    """Feed a decode step's sampled tokens back as the next step's inputs, on the device."""
+    R = token_ids.numel()
+    if history.dim() != 2 or history.shape[1] != R or not history.is_contiguous():
+        raise KernelError("advance_decode: history must be contiguous [max_steps, requests]")
+    _run("sprout_advance_decode", _ptr(token_ids, "token_ids", torch.int32), _ptr(positions, "positions", torch.int32),
+         _ptr(context_lens, "context_lens", torch.int32), _ptr(sampled, "sampled", torch.int32),
+         _ptr(history, "history", torch.int32), _ptr(step_counter, "step_counter", torch.int32), R,
+         history.shape[0], _stream())
 
 
 def describe_status(word: int) -> str:

@@ -85,5 +85,9 @@ class StubRunner:
             out.append(int(min(np.searchsorted(c, u, side="right"), len(row) - 1)))
         return out
 
+    def step_and_sample(self, entries, temperatures, uniforms):
+        logits = self.step(entries)
+        return self.sample(logits, temperatures, uniforms) if logits else []
+
     def check_status(self):
         pass
