@@ -1,0 +1,524 @@
+// bfloat16 paged attention for serving: scores, softmax and sums in float32.
+//
+// decode  (every request brings one query token): grid (splits, kv_heads, requests).  A CTA
+//   takes a run of `split_keys` keys of one key/value head of one request and serves all the
+//   query heads of that group from one read of the keys and values.  Partial results
+//   (running maximum, sum, unnormalised output) go to scratch memory; a second kernel merges
+//   the splits.  The work of a query does not depend on the batch around it.
+//
+// prefill (portions of prompts, possibly beside single tokens): tensor-core flash attention
+//   (mma.sync m16n8k16, float32 accumulation) over the pages.  The rows of a tile are (token,
+//   query head of one group) pairs, so a short portion still fills the 16-row MMA tiles and
+//   keys/values are read once per group; keys are walked in tiles of 64 with the causal limit
+//   of each row applied inside the tile.
+#include "common.cuh"
+
+namespace {
+
+// =============================================================================== decode
+constexpr int DEC_THREADS = 128;      // == keys per pass
+constexpr int MAX_GROUP = 16;         // query heads per key/value head served by one CTA pass
+
+struct DecodeParams {
+  const __nv_bfloat16* q; int q_stride;
+  const __nv_bfloat16* k_cache; const __nv_bfloat16* v_cache;
+  const int* block_table; int table_stride;
+  const int* context_lens;            // keys visible to the request's query: positions 0..len-1
+  __nv_bfloat16* out; int out_stride;
+  float* part_out;                    // [requests, heads, splits, head_dim]
+  float* part_ml;                     // [requests, heads, splits, 2]
+  int heads, kv_heads, head_dim, page_tokens, num_pages, split_keys, splits;
+  int* status;
+};
+
+__global__ void __launch_bounds__(DEC_THREADS)
+attention_decode_kernel(const DecodeParams p) {
+  extern __shared__ float dsm[];
+  const int group = p.heads / p.kv_heads;
+  float* qs = dsm;                                  // [group][head_dim]
+  float* probs = qs + group * p.head_dim;           // [group][DEC_THREADS]
+  float* red = probs + group * DEC_THREADS;         // [group][4] warp partials, then [group] results
+  long long* rows = (long long*)(red + MAX_GROUP * 8);   // [DEC_THREADS] value-row offsets
+
+  const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int len = p.context_lens[r];
+  const int begin = split * p.split_keys;
+  if (begin >= len) return;                          // the merge kernel knows which splits exist
+  const int end = min(len, begin + p.split_keys);
+  const int* table = p.block_table + (size_t)r * p.table_stride;
+  const float scale = 1.0f / sqrtf((float)p.head_dim);
+
+  for (int i = tid; i < group * p.head_dim; i += DEC_THREADS)
+    qs[i] = __bfloat162float(p.q[(size_t)r * p.q_stride + (size_t)g * group * p.head_dim + i]);
+  __syncthreads();
+
+  // thread t of warp w accumulates output dims {2*lane, 2*lane+1} (+64 per extra pass over
+  // head_dim) of the heads h with h % 4 == w
+  float m_run[MAX_GROUP / 4 + 1], l_run[MAX_GROUP / 4 + 1];
+  float acc[MAX_GROUP / 4 + 1][4][2];                // [head slot][dim chunk of 64][2]
+#pragma unroll
+  for (int a = 0; a < MAX_GROUP / 4 + 1; a++) {
+    m_run[a] = -INFINITY; l_run[a] = 0.f;
+#pragma unroll
+    for (int c = 0; c < 4; c++) acc[a][c][0] = acc[a][c][1] = 0.f;
+  }
+
+  for (int base = begin; base < end; base += DEC_THREADS) {
+    const int key = base + tid;
+    bool valid = key < end;
+    long long off = -1;
+    if (valid) {
+      const int page = table[key / p.page_tokens];
+      if (page < 0 || page >= p.num_pages) { atomicOr(p.status, SPROUT_STATUS_BAD_PAGE); valid = false; }
+      else off = (((long long)page * p.kv_heads + g) * p.page_tokens + key % p.page_tokens) * p.head_dim;
+    }
+    rows[tid] = off;
+    // scores of this thread's key against every head of the group
+    float s[MAX_GROUP];
+#pragma unroll
+    for (int h = 0; h < MAX_GROUP; h++) s[h] = 0.f;
+    if (valid) {
+      const uint4* kp = (const uint4*)(p.k_cache + off);
+      for (int c = 0; c < p.head_dim / 8; c++) {
+        const uint4 raw = kp[c];
+        const __nv_bfloat162* k2 = (const __nv_bfloat162*)&raw;
+        float kf[8];
+#pragma unroll
+        for (int j = 0; j < 4; j++) { const float2 f = __bfloat1622float2(k2[j]); kf[2 * j] = f.x; kf[2 * j + 1] = f.y; }
+#pragma unroll
+        for (int h = 0; h < MAX_GROUP; h++) {
+          if (h < group) {
+            const float* qh = qs + h * p.head_dim + c * 8;
+#pragma unroll
+            for (int j = 0; j < 8; j++) s[h] = fmaf(qh[j], kf[j], s[h]);
+          }
+        }
+      }
+    }
+    // per head: block maximum of the scores, exponentials into shared memory, block sum
+#pragma unroll
+    for (int h = 0; h < MAX_GROUP; h++) {
+      if (h < group) {
+        s[h] = valid ? s[h] * scale : -INFINITY;
+        const float wm = warp_max(s[h]);
+        if (lane == 0) red[h * 8 + warp] = wm;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < MAX_GROUP; h++) {
+      if (h < group) {
+        const float cm = fmaxf(fmaxf(red[h * 8], red[h * 8 + 1]), fmaxf(red[h * 8 + 2], red[h * 8 + 3]));
+        const float e = valid ? __expf(s[h] - cm) : 0.f;     // cm is finite: the pass has at least one valid key
+        probs[h * DEC_THREADS + tid] = e;
+        const float ws = warp_sum(e);
+        if (lane == 0) red[h * 8 + 4 + warp] = ws;
+      }
+    }
+    __syncthreads();
+    // output accumulation: warp w handles heads w, w+4, ...; lanes run over the dims
+    const int count = min(DEC_THREADS, end - base);
+#pragma unroll
+    for (int a = 0; a < MAX_GROUP / 4 + 1; a++) {
+      const int h = warp + 4 * a;
+      if (h < group) {
+        const float cm = fmaxf(fmaxf(red[h * 8], red[h * 8 + 1]), fmaxf(red[h * 8 + 2], red[h * 8 + 3]));
+        const float cs = (red[h * 8 + 4] + red[h * 8 + 5]) + (red[h * 8 + 6] + red[h * 8 + 7]);
+        const float m_new = fmaxf(m_run[a], cm);
+        const float alpha = m_run[a] == -INFINITY ? 0.f : __expf(m_run[a] - m_new);
+        const float beta = __expf(cm - m_new);
+        l_run[a] = l_run[a] * alpha + cs * beta;
+        const float* ph = probs + h * DEC_THREADS;
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          const int d = c * 64 + 2 * lane;
+          if (d < p.head_dim) {
+            float a0 = 0.f, a1 = 0.f;
+            for (int j = 0; j < count; j++) {
+              const long long ro = rows[j];
+              if (ro >= 0) {
+                const float2 v = __bfloat1622float2(*(const __nv_bfloat162*)(p.v_cache + ro + d));
+                a0 = fmaf(ph[j], v.x, a0);
+                a1 = fmaf(ph[j], v.y, a1);
+              }
+            }
+            acc[a][c][0] = acc[a][c][0] * alpha + a0 * beta;
+            acc[a][c][1] = acc[a][c][1] * alpha + a1 * beta;
+          }
+        }
+        m_run[a] = m_new;
+      }
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int a = 0; a < MAX_GROUP / 4 + 1; a++) {
+    const int h = warp + 4 * a;
+    if (h < group) {
+      const int head = g * group + h;
+      if (p.splits == 1) {
+        __nv_bfloat16* o = p.out + (size_t)r * p.out_stride + (size_t)head * p.head_dim;
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          const int d = c * 64 + 2 * lane;
+          if (d < p.head_dim)
+            *(__nv_bfloat162*)(o + d) = __floats2bfloat162_rn(acc[a][c][0] / l_run[a], acc[a][c][1] / l_run[a]);
+        }
+      } else {
+        const size_t slot = ((size_t)r * p.heads + head) * p.splits + split;
+        float* o = p.part_out + slot * p.head_dim;
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          const int d = c * 64 + 2 * lane;
+          if (d < p.head_dim) { o[d] = acc[a][c][0]; o[d + 1] = acc[a][c][1]; }
+        }
+        if (lane == 0) { p.part_ml[slot * 2] = m_run[a]; p.part_ml[slot * 2 + 1] = l_run[a]; }
+      }
+    }
+  }
+}
+
+// Merge the splits of one (request, head): grid (heads, requests), head_dim threads (rounded up to a warp).
+__global__ void attention_decode_merge_kernel(const DecodeParams p) {
+  const int head = blockIdx.x, r = blockIdx.y, d = threadIdx.x;
+  const int len = p.context_lens[r];
+  const int live = min(p.splits, (len + p.split_keys - 1) / p.split_keys);
+  const size_t slot0 = ((size_t)r * p.heads + head) * p.splits;
+  float m = -INFINITY;
+  for (int s = 0; s < live; s++) m = fmaxf(m, p.part_ml[(slot0 + s) * 2]);
+  float l = 0.f, o = 0.f;
+  for (int s = 0; s < live; s++) {
+    const float w = __expf(p.part_ml[(slot0 + s) * 2] - m);
+    l += p.part_ml[(slot0 + s) * 2 + 1] * w;
+    if (d < p.head_dim) o += p.part_out[(slot0 + s) * p.head_dim + d] * w;
+  }
+  if (d < p.head_dim) p.out[(size_t)r * p.out_stride + (size_t)head * p.head_dim + d] = __float2bfloat16_rn(o / l);
+}
+
+// =============================================================================== prefill
+constexpr int PF_THREADS = 128, PF_ROWS = 64, PF_KEYS = 64;
+
+struct PrefillParams {
+  const __nv_bfloat16* q; int q_stride;
+  const __nv_bfloat16* k_cache; const __nv_bfloat16* v_cache;
+  const int* block_table; int table_stride;
+  const int* q_start;                 // [requests + 1] first token of each request in the batch
+  const int* positions;               // [tokens]
+  __nv_bfloat16* out; int out_stride;
+  int requests, heads, kv_heads, page_tokens, num_pages;
+  float scale;
+  int* status;
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(smem)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(smem)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *(uint32_t*)&h;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(PF_THREADS)
+attention_prefill_kernel(const PrefillParams p) {
+  constexpr int STRIDE = HD + 8;                      // bf16 elements per shared-memory row (16 bytes of padding)
+  constexpr int CHUNKS = HD / 8;                      // 16-byte chunks per row
+  extern __shared__ __align__(16) uint8_t psm[];
+  __nv_bfloat16* sQ = (__nv_bfloat16*)psm;            // [64][STRIDE]
+  __nv_bfloat16* sK = sQ + PF_ROWS * STRIDE;          // [2][64][STRIDE]
+  __nv_bfloat16* sV = sK + 2 * PF_KEYS * STRIDE;      // [2][64][STRIDE]
+  __shared__ int s_limit[PF_ROWS];                    // last visible key of each row, -1 for no row
+  __shared__ int s_token[PF_ROWS];                    // batch index of the row's token
+  __shared__ int s_head[PF_ROWS];
+  __shared__ long long s_off[2][PF_KEYS];             // cache offsets of a tile's keys, -1 beyond the range
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = blockIdx.y;
+  const int group = p.heads / p.kv_heads;
+
+  // which request and which 64-row tile of it this CTA owns
+  int r = 0, tile = blockIdx.x;
+  for (; r < p.requests; r++) {
+    const int tiles = ((p.q_start[r + 1] - p.q_start[r]) * group + PF_ROWS - 1) / PF_ROWS;
+    if (tile < tiles) break;
+    tile -= tiles;
+  }
+  if (r >= p.requests) return;
+  const int q0 = p.q_start[r], q_count = p.q_start[r + 1] - q0;
+  const int rows_total = q_count * group;
+  const int row_base = tile * PF_ROWS;
+  const int* table = p.block_table + (size_t)r * p.table_stride;
+
+  if (tid < PF_ROWS) {
+    const int gi = row_base + tid;
+    if (gi < rows_total) {
+      const int tok = q0 + gi / group;
+      s_token[tid] = tok;
+      s_head[tid] = g * group + gi % group;
+      s_limit[tid] = p.positions[tok];
+    } else {
+      s_token[tid] = -1; s_head[tid] = 0; s_limit[tid] = -1;
+    }
+  }
+  __syncthreads();
+  const int last_row = min(rows_total, row_base + PF_ROWS) - 1 - row_base;
+  const int max_limit = s_limit[last_row];            // positions grow with the row index
+  const int kv_tiles = max_limit / PF_KEYS + 1;
+
+  // Q rows -> shared memory
+  for (int idx = tid; idx < PF_ROWS * CHUNKS; idx += PF_THREADS) {
+    const int row = idx / CHUNKS, c = idx % CHUNKS;
+    __nv_bfloat16* dst = sQ + row * STRIDE + c * 8;
+    if (s_token[row] >= 0) cp_async16(dst, p.q + (size_t)s_token[row] * p.q_stride + (size_t)s_head[row] * HD + c * 8);
+    else *(uint4*)dst = make_uint4(0, 0, 0, 0);
+  }
+
+  auto find_rows = [&](int t, int buf) {
+    if (tid < PF_KEYS) {
+      const int key = t * PF_KEYS + tid;
+      long long off = -1;
+      if (key <= max_limit) {
+        const int page = table[key / p.page_tokens];
+        if (page < 0 || page >= p.num_pages) atomicOr(p.status, SPROUT_STATUS_BAD_PAGE);
+        else off = (((long long)page * p.kv_heads + g) * p.page_tokens + key % p.page_tokens) * HD;
+      }
+      s_off[buf][tid] = off;
+    }
+  };
+  auto load_tile = [&](int buf) {
+    for (int idx = tid; idx < PF_KEYS * CHUNKS; idx += PF_THREADS) {
+      const int row = idx / CHUNKS, c = idx % CHUNKS;
+      const long long off = s_off[buf][row];
+      __nv_bfloat16* dk = sK + (buf * PF_KEYS + row) * STRIDE + c * 8;
+      __nv_bfloat16* dv = sV + (buf * PF_KEYS + row) * STRIDE + c * 8;
+      if (off >= 0) { cp_async16(dk, p.k_cache + off + c * 8); cp_async16(dv, p.v_cache + off + c * 8); }
+      else { *(uint4*)dk = make_uint4(0, 0, 0, 0); *(uint4*)dv = make_uint4(0, 0, 0, 0); }
+    }
+  };
+
+  find_rows(0, 0);
+  __syncthreads();
+  load_tile(0);
+  cp_async_commit();
+
+  const int gr = lane >> 2, qc = lane & 3;            // row within 8, column pair within the quad
+  const int my_row0 = warp * 16 + gr, my_row1 = my_row0 + 8;
+  const int limit0 = s_limit[my_row0], limit1 = s_limit[my_row1];
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  for (int t = 0; t < kv_tiles; t++) {
+    const int buf = t & 1;
+    if (t + 1 < kv_tiles) find_rows(t + 1, buf ^ 1);
+    __syncthreads();                                   // offsets visible; everyone is done with buffer buf^1
+    if (t + 1 < kv_tiles) load_tile(buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();                                // tile t (and Q) have landed
+    __syncthreads();
+
+    const __nv_bfloat16* tK = sK + buf * PF_KEYS * STRIDE;
+    const __nv_bfloat16* tV = sV + buf * PF_KEYS * STRIDE;
+    const int kv0 = t * PF_KEYS;
+    // skip a tile that no row of this warp can see
+    const int warp_limit = s_limit[min(warp * 16 + 15, last_row)];
+    if (warp * 16 <= last_row && kv0 <= warp_limit) {
+      float s[PF_KEYS / 8][4];
+#pragma unroll
+      for (int i = 0; i < PF_KEYS / 8; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; kk++) {
+        uint32_t a[4];
+        ldmatrix_x4(a, sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int n2 = 0; n2 < PF_KEYS / 16; n2++) {
+          uint32_t b[4];
+          ldmatrix_x4(b, tK + (n2 * 16 + (lane & 7) + (lane >> 4) * 8) * STRIDE + kk * 16 + ((lane >> 3) & 1) * 8);
+          mma_bf16(s[2 * n2], a, b[0], b[1]);
+          mma_bf16(s[2 * n2 + 1], a, b[2], b[3]);
+        }
+      }
+      // scale, causal mask, running maximum
+      float t_max0 = -INFINITY, t_max1 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < PF_KEYS / 8; i++) {
+        const int key = kv0 + i * 8 + qc * 2;
+        s[i][0] = key <= limit0 ? s[i][0] * p.scale : -INFINITY;
+        s[i][1] = key + 1 <= limit0 ? s[i][1] * p.scale : -INFINITY;
+        s[i][2] = key <= limit1 ? s[i][2] * p.scale : -INFINITY;
+        s[i][3] = key + 1 <= limit1 ? s[i][3] * p.scale : -INFINITY;
+        t_max0 = fmaxf(t_max0, fmaxf(s[i][0], s[i][1]));
+        t_max1 = fmaxf(t_max1, fmaxf(s[i][2], s[i][3]));
+      }
+      t_max0 = fmaxf(t_max0, __shfl_xor_sync(0xffffffffu, t_max0, 1));
+      t_max0 = fmaxf(t_max0, __shfl_xor_sync(0xffffffffu, t_max0, 2));
+      t_max1 = fmaxf(t_max1, __shfl_xor_sync(0xffffffffu, t_max1, 1));
+      t_max1 = fmaxf(t_max1, __shfl_xor_sync(0xffffffffu, t_max1, 2));
+      const float n0 = fmaxf(m0, t_max0), n1 = fmaxf(m1, t_max1);
+      const float base0 = n0 == -INFINITY ? 0.f : n0, base1 = n1 == -INFINITY ? 0.f : n1;
+      const float alpha0 = m0 == -INFINITY ? 0.f : __expf(m0 - base0), alpha1 = m1 == -INFINITY ? 0.f : __expf(m1 - base1);
+      m0 = n0; m1 = n1;
+      l0 *= alpha0; l1 *= alpha1;
+#pragma unroll
+      for (int i = 0; i < HD / 8; i++) { o[i][0] *= alpha0; o[i][1] *= alpha0; o[i][2] *= alpha1; o[i][3] *= alpha1; }
+#pragma unroll
+      for (int i = 0; i < PF_KEYS / 8; i++) {
+        s[i][0] = __expf(s[i][0] - base0); s[i][1] = __expf(s[i][1] - base0);
+        s[i][2] = __expf(s[i][2] - base1); s[i][3] = __expf(s[i][3] - base1);
+        l0 += s[i][0] + s[i][1];
+        l1 += s[i][2] + s[i][3];
+      }
+      // O += P V
+#pragma unroll
+      for (int kk = 0; kk < PF_KEYS / 16; kk++) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int d2 = 0; d2 < HD / 16; d2++) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, tV + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + d2 * 16 + (lane >> 4) * 8);
+          mma_bf16(o[2 * d2], a, b[0], b[1]);
+          mma_bf16(o[2 * d2 + 1], a, b[2], b[3]);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+  // sums across the quad, then the rows go out
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if (s_token[my_row0] >= 0) {
+    __nv_bfloat16* dst = p.out + (size_t)s_token[my_row0] * p.out_stride + (size_t)s_head[my_row0] * HD + qc * 2;
+    const float inv = 1.0f / l0;
+#pragma unroll
+    for (int i = 0; i < HD / 8; i++) *(__nv_bfloat162*)(dst + i * 8) = __floats2bfloat162_rn(o[i][0] * inv, o[i][1] * inv);
+  }
+  if (s_token[my_row1] >= 0) {
+    __nv_bfloat16* dst = p.out + (size_t)s_token[my_row1] * p.out_stride + (size_t)s_head[my_row1] * HD + qc * 2;
+    const float inv = 1.0f / l1;
+#pragma unroll
+    for (int i = 0; i < HD / 8; i++) *(__nv_bfloat162*)(dst + i * 8) = __floats2bfloat162_rn(o[i][2] * inv, o[i][3] * inv);
+  }
+}
+
+template <int HD>
+int launch_prefill(const PrefillParams& p, int grid_x, cudaStream_t stream) {
+  const int smem = (PF_ROWS + 4 * PF_KEYS) * (HD + 8) * 2;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(attention_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) return sprout_fail("attention_prefill: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(err));
+    configured = true;
+  }
+  attention_prefill_kernel<HD><<<dim3(grid_x, p.kv_heads), PF_THREADS, smem, stream>>>(p);
+  return sprout_check_launch("attention_prefill");
+}
+
+}  // namespace
+
+// Scratch floats that a decode call with `splits` splits needs: outputs and (max, sum) pairs.
+SPROUT_API long long sprout_attention_decode_scratch_floats(int requests, int heads, int head_dim, int splits) {
+  return (long long)requests * heads * splits * (head_dim + 2);
+}
+
+// One query token per request.  q, out: [requests, heads * head_dim] (row strides given);
+// context_lens[r] keys are visible to request r.  scratch: float32, at least
+// sprout_attention_decode_scratch_floats(...) long when splits > 1 (may be null when splits == 1).
+SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                       const int* block_table, int table_stride, const int* context_lens,
+                                       void* out, int out_stride, float* scratch, int requests, int heads,
+                                       int kv_heads, int head_dim, int page_tokens, int num_pages, int split_keys,
+                                       int splits, int* status, cudaStream_t stream) {
+  SPROUT_REQUIRE(requests > 0 && requests <= 65535 && heads > 0 && kv_heads > 0 && page_tokens > 0 && num_pages > 0,
+                 "attention_decode: sizes must be positive (at most 65535 requests)");
+  SPROUT_REQUIRE(heads % kv_heads == 0 && heads / kv_heads <= MAX_GROUP,
+                 "attention_decode: heads / kv_heads must be a whole number up to %d (got %d / %d)", MAX_GROUP, heads, kv_heads);
+  SPROUT_REQUIRE(head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 256,
+                 "attention_decode: head_dim must be a multiple of 16 between 16 and 256 (got %d)", head_dim);
+  SPROUT_REQUIRE(split_keys > 0 && split_keys % DEC_THREADS == 0 && splits > 0 && splits <= 65535,
+                 "attention_decode: split_keys must be a positive multiple of %d", DEC_THREADS);
+  SPROUT_REQUIRE(q && k_cache && v_cache && block_table && context_lens && out && status, "attention_decode: null pointer");
+  SPROUT_REQUIRE(splits == 1 || scratch, "attention_decode: scratch memory is needed for more than one split");
+  SPROUT_REQUIRE(q_stride % 2 == 0 && out_stride % 2 == 0 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0,
+                 "attention_decode: misaligned operands");
+  DecodeParams p;
+  p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride;
+  p.k_cache = (const __nv_bfloat16*)k_cache; p.v_cache = (const __nv_bfloat16*)v_cache;
+  p.block_table = block_table; p.table_stride = table_stride; p.context_lens = context_lens;
+  p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
+  p.part_out = scratch;
+  p.part_ml = scratch ? scratch + (size_t)requests * heads * splits * head_dim : nullptr;
+  p.heads = heads; p.kv_heads = kv_heads; p.head_dim = head_dim; p.page_tokens = page_tokens; p.num_pages = num_pages;
+  p.split_keys = split_keys; p.splits = splits; p.status = status;
+  const int group = heads / kv_heads;
+  const size_t smem = (size_t)(group * head_dim + group * DEC_THREADS + MAX_GROUP * 8) * sizeof(float) + DEC_THREADS * sizeof(long long);
+  SPROUT_REQUIRE(smem <= 48 * 1024, "attention_decode: group %d with head_dim %d needs %zu bytes of shared memory", group, head_dim, smem);
+  attention_decode_kernel<<<dim3(splits, kv_heads, requests), DEC_THREADS, smem, stream>>>(p);
+  if (sprout_check_launch("attention_decode")) return 1;
+  if (splits > 1) {
+    const int threads = (head_dim + 31) / 32 * 32;
+    attention_decode_merge_kernel<<<dim3(heads, requests), threads, 0, stream>>>(p);
+    return sprout_check_launch("attention_decode_merge");
+  }
+  return 0;
+}
+
+// Portions of prompts (and single tokens) of several requests in one launch.  q_start[r] is the
+// first token of request r in the batch; a token at position pos sees keys 0..pos of its request.
+SPROUT_API int sprout_attention_prefill(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                        const int* block_table, int table_stride, const int* q_start,
+                                        const int* positions, void* out, int out_stride, int num_tokens,
+                                        int requests, int heads, int kv_heads, int head_dim, int page_tokens,
+                                        int num_pages, int* status, cudaStream_t stream) {
+  SPROUT_REQUIRE(num_tokens > 0 && requests > 0 && heads > 0 && kv_heads > 0 && page_tokens > 0 && num_pages > 0,
+                 "attention_prefill: sizes must be positive");
+  SPROUT_REQUIRE(heads % kv_heads == 0, "attention_prefill: heads (%d) must be a multiple of kv_heads (%d)", heads, kv_heads);
+  SPROUT_REQUIRE(kv_heads <= 65535, "attention_prefill: too many kv heads");
+  SPROUT_REQUIRE(q && k_cache && v_cache && block_table && q_start && positions && out && status, "attention_prefill: null pointer");
+  SPROUT_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0
+                 && out_stride % 2 == 0, "attention_prefill: q rows and the caches must be 16-byte aligned");
+  PrefillParams p;
+  p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride;
+  p.k_cache = (const __nv_bfloat16*)k_cache; p.v_cache = (const __nv_bfloat16*)v_cache;
+  p.block_table = block_table; p.table_stride = table_stride; p.q_start = q_start; p.positions = positions;
+  p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
+  p.requests = requests; p.heads = heads; p.kv_heads = kv_heads; p.page_tokens = page_tokens; p.num_pages = num_pages;
+  p.scale = 1.0f / sqrtf((float)head_dim); p.status = status;
+  const int group = heads / kv_heads;
+  // every request has at most ceil(tokens * group / 64) tiles: an upper bound without reading q_start
+  const long long bound = ((long long)num_tokens * group + PF_ROWS - 1) / PF_ROWS + requests;
+  SPROUT_REQUIRE(bound <= 0x7fffffffLL, "attention_prefill: too many tokens");
+  switch (head_dim) {
+    case 16: return launch_prefill<16>(p, (int)bound, stream);
+    case 32: return launch_prefill<32>(p, (int)bound, stream);
+    case 48: return launch_prefill<48>(p, (int)bound, stream);
+    case 64: return launch_prefill<64>(p, (int)bound, stream);
+    case 80: return launch_prefill<80>(p, (int)bound, stream);
+    case 96: return launch_prefill<96>(p, (int)bound, stream);
+    case 112: return launch_prefill<112>(p, (int)bound, stream);
+    case 128: return launch_prefill<128>(p, (int)bound, stream);
+    default: return sprout_fail("attention_prefill: head_dim must be a multiple of 16 up to 128 (got %d)", head_dim);
+  }
+}

@@ -136,10 +136,10 @@ class ModelRunner:
         """A device-side run of decode steps (see ``graphs.DecodeLoop``): pages for ``max_steps``
         more tokens per request are reserved here."""
         from .graphs import DecodeLoop
-        self.validate(entries)
         for e in entries:
             if not self.reserve(e.seq, e.seq.length + 1 + max_steps):
                 raise StepError("not enough pages for a device-side decode loop")
+        self.validate(entries)
         return DecodeLoop(self, entries, temperatures, uniforms, max_steps)
 
     def forward(self, ctx: StepContext):

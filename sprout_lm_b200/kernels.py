@@ -34,6 +34,8 @@ _SIGNATURES = {
     "sprout_attention_simple": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_sample": [_P, _I, _P, _P, _P, _I, _I, _P, _P],
     "sprout_advance_decode": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
+    "sprout_attention_decode": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_gemm_bf16": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
 }
 
@@ -50,6 +52,8 @@ def load_library(verbose: bool = True):
             lib = ctypes.CDLL(str(path))
             lib.sprout_last_error.restype = ctypes.c_char_p
             lib.sprout_abi_version.restype = c_int
+            lib.sprout_attention_decode_scratch_floats.restype = ctypes.c_longlong
+            lib.sprout_attention_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
             for name, argtypes in _SIGNATURES.items():
                 fn = getattr(lib, name)
                 fn.argtypes = argtypes
@@ -230,8 +234,76 @@ def gemm_bf16(a, weight, out, status, bias=None, residual=None, orientation=0, s
          out.stride(0), orientation, split_k, _ptr(status, "status", torch.int32), _stream())
 
 
+def _check_paged(q, k_cache, v_cache, block_table, out, heads, head_dim, name):
+    _rows_contiguous(q, "q")
+    _rows_contiguous(out, "out")
+    _rows_contiguous(block_table, "block_table")
+    T = q.shape[0]
+    if q.shape[1] != heads * head_dim or tuple(out.shape) != (T, heads * head_dim):
+        raise KernelError(f"{name}: q and out must be [tokens, heads * head_dim]")
+    if k_cache.shape != v_cache.shape or k_cache.dim() != 4 or k_cache.shape[3] != head_dim \
+            or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise KernelError(f"{name}: caches must be contiguous [pages, kv_heads, page_tokens, head_dim]")
+    if not (q.dtype == out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16):
+        raise KernelError(f"{name}: q, out and the caches must be bfloat16")
+
+
+SM_COUNT = 148
+
+
+def decode_split_plan(requests: int, kv_heads: int, max_keys: int) -> tuple[int, int]:
+    """(keys per split, splits) for decode attention over at most ``max_keys`` keys: splits of 128
+    keys, doubled while the grid would exceed eight CTAs per SM."""
+    split_keys = 128
+    while requests * kv_heads * (-(-max_keys // split_keys)) > 8 * SM_COUNT and split_keys < max_keys:
+        split_keys *= 2
+    return split_keys, max(1, -(-max_keys // split_keys))
+
+
+def attention_decode(q, k_cache, v_cache, block_table, context_lens, out, heads, kv_heads, head_dim, status,
+                     split_keys=None, scratch=None):
+    """One query token per request over its pages (bfloat16, float32 softmax): keys are split
+    among CTAs, partial results go through float32 scratch memory and are merged."""
+    _check_paged(q, k_cache, v_cache, block_table, out, heads, head_dim, "attention_decode")
+    R = q.shape[0]
+    max_keys = block_table.shape[1] * k_cache.shape[2]
+    if split_keys is None:
+        split_keys, splits = decode_split_plan(R, kv_heads, max_keys)
+    else:
+        splits = max(1, -(-max_keys // split_keys))
+    need = load_library().sprout_attention_decode_scratch_floats(R, heads, head_dim, splits)
+    if splits > 1 and scratch is None:
+        scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+    if scratch is not None and (scratch.dtype != torch.float32 or scratch.numel() < need):
+        raise KernelError(f"attention_decode: scratch must hold {need} float32 values")
+    _run("sprout_attention_decode", _ptr(q, "q"), q.stride(0), _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"),
+         _ptr(block_table, "block_table", torch.int32), block_table.stride(0),
+         _ptr(context_lens, "context_lens", torch.int32), _ptr(out, "out"), out.stride(0),
+         _ptr(scratch, "scratch", torch.float32, True), R, heads, kv_heads, head_dim, k_cache.shape[2],
+         k_cache.shape[0], split_keys, splits, _ptr(status, "status", torch.int32), _stream())
+
+
+def attention_prefill(q, k_cache, v_cache, block_table, q_start, positions, out, heads, kv_heads, head_dim, status):
+    """Tensor-core flash attention of the step's queries (portions of prompts, single tokens) over
+    their requests' pages (bfloat16, float32 softmax)."""
+    _check_paged(q, k_cache, v_cache, block_table, out, heads, head_dim, "attention_prefill")
+    _run("sprout_attention_prefill", _ptr(q, "q"), q.stride(0), _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"),
+         _ptr(block_table, "block_table", torch.int32), block_table.stride(0), _ptr(q_start, "q_start", torch.int32),
+         _ptr(positions, "positions", torch.int32), _ptr(out, "out"), out.stride(0), q.shape[0], q_start.numel() - 1,
+         heads, kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], _ptr(status, "status", torch.int32), _stream())
+
+
 def paged_attention(q, cache, ctx, out, heads, kv_heads, head_dim, status):
-    """Causal attention of the step's queries over their requests' pages (``cache`` is a CacheView)."""
+    """Causal attention of the step's queries over their requests' pages (``cache`` is a
+    CacheView).  float32 runs the plain kernel (the true 32-bit path); bfloat16 runs the split-key
+    kernel when every request brings one token and the tensor-core kernel otherwise."""
+    if q.dtype == torch.bfloat16:
+        if ctx.max_q_len == 1 and heads // kv_heads <= 16:
+            return attention_decode(q, cache.k, cache.v, cache.block_table, ctx.context_lens, out,
+                                    heads, kv_heads, head_dim, status)
+        if head_dim <= 128:
+            return attention_prefill(q, cache.k, cache.v, cache.block_table, ctx.q_start, ctx.positions, out,
+                                     heads, kv_heads, head_dim, status)
     attention_simple(q, cache.k, cache.v, cache.block_table, ctx.seq_of_token, ctx.positions, out,
                      heads, kv_heads, head_dim, status)
 
@@ -264,4 +336,5 @@ def describe_status(word: int) -> str:
 
 
 __all__ = ["KernelError", "BuildError", "load_library", "library_file", "embed", "rmsnorm", "swiglu",
-           "rope_append", "gemm_simple", "attention_simple", "sample", "describe_status"]
+           "rope_append", "gemm_simple", "gemm_bf16", "attention_simple", "attention_decode", "attention_prefill",
+           "paged_attention", "sample", "advance_decode", "describe_status"]

@@ -301,6 +301,59 @@ def test_attention_finds_one_far_key_among_hundreds(status, dtype, where):
     assert (out.double().cpu() - case["want"]).abs().max().item() <= tol
 
 
+DECODE_CASES = [
+    (4, 2, 16, 16, [5, 17, 33, 1]), (3, 1, 32, 8, [61, 1, 130]), (14, 2, 64, 16, [300, 129, 16, 640, 513]),
+    (5, 5, 48, 4, [40, 9]), (8, 2, 128, 16, [257, 64, 1000]), (6, 3, 80, 32, [100]), (16, 1, 256, 16, [70, 200]),
+]
+
+
+@pytest.mark.parametrize("split_keys", [None, 128, 256])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page,lengths", DECODE_CASES)
+def test_attention_decode_split_keys(status, heads, kv_heads, head_dim, page, lengths, split_keys):
+    from sprout_lm_b200 import kernels
+    case = build_paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, lengths, [1] * len(lengths))
+    out = torch.full((case["T"], heads * head_dim), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.attention_decode(case["q"], case["k_cache"], case["v_cache"], case["table"], case["context_lens"], out,
+                             heads, kv_heads, head_dim, status, split_keys=split_keys)
+    assert (out.double().cpu() - case["want"]).abs().max().item() <= 1.2e-2
+    # a wider block table (as under a captured graph) changes the split count, not the result
+    wide = torch.full((len(lengths), case["table"].shape[1] + 19), -1, dtype=torch.int32, device=DEV)
+    wide[:, :case["table"].shape[1]] = case["table"]
+    again = torch.empty_like(out)
+    kernels.attention_decode(case["q"], case["k_cache"], case["v_cache"], wide, case["context_lens"], again,
+                             heads, kv_heads, head_dim, status, split_keys=split_keys)
+    assert (again.double().cpu() - case["want"]).abs().max().item() <= 1.2e-2
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page,lengths,q_counts", ATTN_CASES + [
+    (14, 2, 64, 16, [700, 650, 2, 90], [700, 1, 2, 9]), (2, 1, 112, 8, [75], [75]), (7, 7, 96, 16, [33, 64], [2, 64])])
+def test_attention_prefill_tensor_cores(status, heads, kv_heads, head_dim, page, lengths, q_counts):
+    from sprout_lm_b200 import kernels
+    case = build_paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, lengths, q_counts)
+    out = torch.full((case["T"], heads * head_dim), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.attention_prefill(case["q"], case["k_cache"], case["v_cache"], case["table"], case["q_start"],
+                              case["positions"], out, heads, kv_heads, head_dim, status)
+    assert (out.double().cpu() - case["want"]).abs().max().item() <= 1.5e-2
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("where", [0, 15, 16, 63, 64, 255, 256, 383, 500])
+def test_fast_attention_finds_one_far_key(status, where):
+    from sprout_lm_b200 import kernels
+    heads, kv_heads, head_dim, page = 4, 2, 32, 16
+    case = build_paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, [40, 501], [1, 1], seed=where, spike=(1, where))
+    for name in ("decode", "prefill"):
+        out = torch.empty(case["T"], heads * head_dim, dtype=torch.bfloat16, device=DEV)
+        if name == "decode":
+            kernels.attention_decode(case["q"], case["k_cache"], case["v_cache"], case["table"], case["context_lens"],
+                                     out, heads, kv_heads, head_dim, status)
+        else:
+            kernels.attention_prefill(case["q"], case["k_cache"], case["v_cache"], case["table"], case["q_start"],
+                                      case["positions"], out, heads, kv_heads, head_dim, status)
+        assert (out.double().cpu() - case["want"]).abs().max().item() <= 1.5e-2, name
+
+
 # ------------------------------------------------------------------------------- sampling
 @pytest.mark.parametrize("vocab", [7, 256, 509, 4099, 151936])
 def test_sampling(status, vocab):
