@@ -261,7 +261,13 @@ def run(args) -> dict:
     pages = 64 * (-(-(prompt_len + args.steps + args.warmup + 16) // 16)) + 2048 // 16 + 16
     runner = ModelRunner(model, num_pages=pages, page_tokens=16, max_requests=64, prefix_caching=False)
 
+    if args.only == "prefill":
+        prefill_ms = timed_prefill(runner, 2048, rng, repeats=1)
+        return {"impl": "ours", "only": "prefill", "layers": layers, "ms": round(prefill_ms, 4)}
     main = timed_decode(runner, batch, prompt_len, args.steps, args.warmup, rng, sampler=ClockSampler())
+    if args.only == "decode":
+        return {"impl": "ours", "only": "decode", "layers": layers, "batch": batch, "ms_per_step": round(main["ms_per_step"], 4),
+                "launches_per_step": main["launches_per_step"]}
     points = {}
     for b in (1, 64):
         side_steps = min(args.steps, 64)
@@ -302,6 +308,8 @@ def main() -> int:
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
+    parser.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
+                        help="measure one part only (for profiling captures); the JSON line then holds that part")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))

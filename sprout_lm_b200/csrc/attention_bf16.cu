@@ -73,15 +73,18 @@ attention_decode_kernel(const DecodeParams p) {
       if (page < 0 || page >= p.num_pages) { atomicOr(p.status, SPROUT_STATUS_BAD_PAGE); valid = false; }
       else off = (((long long)page * p.kv_heads + g) * p.page_tokens + key % p.page_tokens) * p.head_dim;
     }
-    rows[tid] = off;
+    // value rows of keys outside the range point at the cache's first row (readable memory) and
+    // carry probability 0, so that the accumulation loop below needs no branch
+    rows[tid] = valid ? off : 0;
     // scores of this thread's key against every head of the group
     float s[MAX_GROUP];
 #pragma unroll
     for (int h = 0; h < MAX_GROUP; h++) s[h] = 0.f;
     if (valid) {
       const uint4* kp = (const uint4*)(p.k_cache + off);
+#pragma unroll 4
       for (int c = 0; c < p.head_dim / 8; c++) {
-        const uint4 raw = kp[c];
+        const uint4 raw = __ldg(kp + c);
         const __nv_bfloat162* k2 = (const __nv_bfloat162*)&raw;
         float kf[8];
 #pragma unroll
@@ -89,9 +92,12 @@ attention_decode_kernel(const DecodeParams p) {
 #pragma unroll
         for (int h = 0; h < MAX_GROUP; h++) {
           if (h < group) {
-            const float* qh = qs + h * p.head_dim + c * 8;
-#pragma unroll
-            for (int j = 0; j < 8; j++) s[h] = fmaf(qh[j], kf[j], s[h]);
+            const float4* qh = (const float4*)(qs + h * p.head_dim + c * 8);
+            const float4 qa = qh[0], qb = qh[1];
+            s[h] = fmaf(qa.x, kf[0], s[h]); s[h] = fmaf(qa.y, kf[1], s[h]);
+            s[h] = fmaf(qa.z, kf[2], s[h]); s[h] = fmaf(qa.w, kf[3], s[h]);
+            s[h] = fmaf(qb.x, kf[4], s[h]); s[h] = fmaf(qb.y, kf[5], s[h]);
+            s[h] = fmaf(qb.z, kf[6], s[h]); s[h] = fmaf(qb.w, kf[7], s[h]);
           }
         }
       }
@@ -135,13 +141,19 @@ attention_decode_kernel(const DecodeParams p) {
           const int d = c * 64 + 2 * lane;
           if (d < p.head_dim) {
             float a0 = 0.f, a1 = 0.f;
-            for (int j = 0; j < count; j++) {
-              const long long ro = rows[j];
-              if (ro >= 0) {
-                const float2 v = __bfloat1622float2(*(const __nv_bfloat162*)(p.v_cache + ro + d));
-                a0 = fmaf(ph[j], v.x, a0);
-                a1 = fmaf(ph[j], v.y, a1);
-              }
+            const __nv_bfloat16* vd = p.v_cache + d;
+            int j = 0;
+            for (; j + 8 <= count; j += 8) {            // eight independent loads in flight
+              float2 v[8];
+#pragma unroll
+              for (int u = 0; u < 8; u++) v[u] = __bfloat1622float2(*(const __nv_bfloat162*)(vd + rows[j + u]));
+#pragma unroll
+              for (int u = 0; u < 8; u++) { a0 = fmaf(ph[j + u], v[u].x, a0); a1 = fmaf(ph[j + u], v[u].y, a1); }
+            }
+            for (; j < count; j++) {
+              const float2 v = __bfloat1622float2(*(const __nv_bfloat162*)(vd + rows[j]));
+              a0 = fmaf(ph[j], v.x, a0);
+              a1 = fmaf(ph[j], v.y, a1);
             }
             acc[a][c][0] = acc[a][c][0] * alpha + a0 * beta;
             acc[a][c][1] = acc[a][c][1] * alpha + a1 * beta;
