@@ -31,14 +31,26 @@ struct DecodeParams {
   int* status;
 };
 
+__device__ __forceinline__ void dec_cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+
+// Shared memory: q of the group as float32, the pass's probabilities, reduction slots, the
+// pass's key rows' offsets, and the pass's keys and values themselves (copied with cp.async so
+// that all of a pass's loads are in flight at once; rows padded by 16 bytes against bank
+// conflicts).
 __global__ void __launch_bounds__(DEC_THREADS)
 attention_decode_kernel(const DecodeParams p) {
-  extern __shared__ float dsm[];
+  extern __shared__ __align__(16) float dsm[];
   const int group = p.heads / p.kv_heads;
+  const int stride = p.head_dim + 8;                // bf16 elements per staged row
+  const int chunks = p.head_dim / 8;                // 16-byte chunks per row
   float* qs = dsm;                                  // [group][head_dim]
   float* probs = qs + group * p.head_dim;           // [group][DEC_THREADS]
-  float* red = probs + group * DEC_THREADS;         // [group][4] warp partials, then [group] results
-  long long* rows = (long long*)(red + MAX_GROUP * 8);   // [DEC_THREADS] value-row offsets
+  float* red = probs + group * DEC_THREADS;         // [MAX_GROUP][8]: 4 warp maxima, 4 warp sums
+  long long* rows = (long long*)(red + MAX_GROUP * 8);            // [DEC_THREADS]
+  __nv_bfloat16* sK = (__nv_bfloat16*)(rows + DEC_THREADS);       // [DEC_THREADS][stride]
+  __nv_bfloat16* sV = sK + DEC_THREADS * stride;
 
   const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -51,14 +63,13 @@ attention_decode_kernel(const DecodeParams p) {
 
   for (int i = tid; i < group * p.head_dim; i += DEC_THREADS)
     qs[i] = __bfloat162float(p.q[(size_t)r * p.q_stride + (size_t)g * group * p.head_dim + i]);
-  __syncthreads();
 
-  // thread t of warp w accumulates output dims {2*lane, 2*lane+1} (+64 per extra pass over
-  // head_dim) of the heads h with h % 4 == w
-  float m_run[MAX_GROUP / 4 + 1], l_run[MAX_GROUP / 4 + 1];
-  float acc[MAX_GROUP / 4 + 1][4][2];                // [head slot][dim chunk of 64][2]
+  // warp w accumulates output dims {2*lane, 2*lane+1} (+64 per chunk of 64 dims) of the heads
+  // h = w, w + 4, ...
+  float m_run[MAX_GROUP / 4], l_run[MAX_GROUP / 4];
+  float acc[MAX_GROUP / 4][4][2];
 #pragma unroll
-  for (int a = 0; a < MAX_GROUP / 4 + 1; a++) {
+  for (int a = 0; a < MAX_GROUP / 4; a++) {
     m_run[a] = -INFINITY; l_run[a] = 0.f;
 #pragma unroll
     for (int c = 0; c < 4; c++) acc[a][c][0] = acc[a][c][1] = 0.f;
@@ -73,18 +84,28 @@ attention_decode_kernel(const DecodeParams p) {
       if (page < 0 || page >= p.num_pages) { atomicOr(p.status, SPROUT_STATUS_BAD_PAGE); valid = false; }
       else off = (((long long)page * p.kv_heads + g) * p.page_tokens + key % p.page_tokens) * p.head_dim;
     }
-    // value rows of keys outside the range point at the cache's first row (readable memory) and
-    // carry probability 0, so that the accumulation loop below needs no branch
-    rows[tid] = valid ? off : 0;
+    rows[tid] = off;
+    __syncthreads();                                  // offsets (and, first time, q) visible; staging buffers free
+    for (int idx = tid; idx < DEC_THREADS * chunks; idx += DEC_THREADS) {
+      const int row = idx / chunks, c = idx % chunks;
+      const long long ro = rows[row];
+      __nv_bfloat16* dk = sK + row * stride + c * 8;
+      __nv_bfloat16* dv = sV + row * stride + c * 8;
+      if (ro >= 0) { dec_cp_async16(dk, p.k_cache + ro + c * 8); dec_cp_async16(dv, p.v_cache + ro + c * 8); }
+      else { *(uint4*)dk = make_uint4(0, 0, 0, 0); *(uint4*)dv = make_uint4(0, 0, 0, 0); }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+
     // scores of this thread's key against every head of the group
     float s[MAX_GROUP];
 #pragma unroll
     for (int h = 0; h < MAX_GROUP; h++) s[h] = 0.f;
-    if (valid) {
-      const uint4* kp = (const uint4*)(p.k_cache + off);
-#pragma unroll 4
-      for (int c = 0; c < p.head_dim / 8; c++) {
-        const uint4 raw = __ldg(kp + c);
+    {
+      const uint4* kp = (const uint4*)(sK + tid * stride);
+      for (int c = 0; c < chunks; c++) {
+        const uint4 raw = kp[c];
         const __nv_bfloat162* k2 = (const __nv_bfloat162*)&raw;
         float kf[8];
 #pragma unroll
@@ -123,10 +144,10 @@ attention_decode_kernel(const DecodeParams p) {
       }
     }
     __syncthreads();
-    // output accumulation: warp w handles heads w, w+4, ...; lanes run over the dims
+    // output accumulation from the staged values: warp w handles heads w, w+4, ...; lanes run over the dims
     const int count = min(DEC_THREADS, end - base);
 #pragma unroll
-    for (int a = 0; a < MAX_GROUP / 4 + 1; a++) {
+    for (int a = 0; a < MAX_GROUP / 4; a++) {
       const int h = warp + 4 * a;
       if (h < group) {
         const float cm = fmaxf(fmaxf(red[h * 8], red[h * 8 + 1]), fmaxf(red[h * 8 + 2], red[h * 8 + 3]));
@@ -141,17 +162,10 @@ attention_decode_kernel(const DecodeParams p) {
           const int d = c * 64 + 2 * lane;
           if (d < p.head_dim) {
             float a0 = 0.f, a1 = 0.f;
-            const __nv_bfloat16* vd = p.v_cache + d;
-            int j = 0;
-            for (; j + 8 <= count; j += 8) {            // eight independent loads in flight
-              float2 v[8];
-#pragma unroll
-              for (int u = 0; u < 8; u++) v[u] = __bfloat1622float2(*(const __nv_bfloat162*)(vd + rows[j + u]));
-#pragma unroll
-              for (int u = 0; u < 8; u++) { a0 = fmaf(ph[j + u], v[u].x, a0); a1 = fmaf(ph[j + u], v[u].y, a1); }
-            }
-            for (; j < count; j++) {
-              const float2 v = __bfloat1622float2(*(const __nv_bfloat162*)(vd + rows[j]));
+            const __nv_bfloat16* vd = sV + d;
+#pragma unroll 4
+            for (int j = 0; j < count; j++) {
+              const float2 v = __bfloat1622float2(*(const __nv_bfloat162*)(vd + j * stride));
               a0 = fmaf(ph[j], v.x, a0);
               a1 = fmaf(ph[j], v.y, a1);
             }
@@ -162,11 +176,10 @@ attention_decode_kernel(const DecodeParams p) {
         m_run[a] = m_new;
       }
     }
-    __syncthreads();
   }
 
 #pragma unroll
-  for (int a = 0; a < MAX_GROUP / 4 + 1; a++) {
+  for (int a = 0; a < MAX_GROUP / 4; a++) {
     const int h = warp + 4 * a;
     if (h < group) {
       const int head = g * group + h;
@@ -485,8 +498,15 @@ SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* 
   p.heads = heads; p.kv_heads = kv_heads; p.head_dim = head_dim; p.page_tokens = page_tokens; p.num_pages = num_pages;
   p.split_keys = split_keys; p.splits = splits; p.status = status;
   const int group = heads / kv_heads;
-  const size_t smem = (size_t)(group * head_dim + group * DEC_THREADS + MAX_GROUP * 8) * sizeof(float) + DEC_THREADS * sizeof(long long);
-  SPROUT_REQUIRE(smem <= 48 * 1024, "attention_decode: group %d with head_dim %d needs %zu bytes of shared memory", group, head_dim, smem);
+  const size_t smem = (size_t)(group * head_dim + group * DEC_THREADS + MAX_GROUP * 8) * sizeof(float)
+      + DEC_THREADS * sizeof(long long) + (size_t)2 * DEC_THREADS * (head_dim + 8) * sizeof(__nv_bfloat16);
+  static size_t configured = 48 * 1024;
+  if (smem > configured) {
+    cudaError_t err = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return sprout_fail("attention_decode: group %d with head_dim %d needs %zu bytes of shared memory: %s",
+                                               group, head_dim, smem, cudaGetErrorString(err));
+    configured = smem;
+  }
   attention_decode_kernel<<<dim3(splits, kv_heads, requests), DEC_THREADS, smem, stream>>>(p);
   if (sprout_check_launch("attention_decode")) return 1;
   if (splits > 1) {

@@ -55,18 +55,63 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
   }
 }
 
+// Fast path for hidden sizes that are multiples of 4: 256 threads, each holding up to VEC float4
+// of the row in registers between the sum of squares and the scaling (one read of x).
+template <typename TO, int VEC>
+__global__ void __launch_bounds__(256)
+rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ gain, TO* __restrict__ out,
+                   const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x, quads = hidden >> 2;
+  const float4* src = (const float4*)(x + (size_t)(rows ? rows[r] : r) * hidden);
+  float4 v[VEC];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VEC; k++) {
+    const int i = threadIdx.x + k * 256;
+    v[k] = i < quads ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
+  for (int k = 0; k < VEC; k++) ss += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+  TO* dst = out + (size_t)r * hidden;
+#pragma unroll
+  for (int k = 0; k < VEC; k++) {
+    const int i = threadIdx.x + k * 256;
+    if (i < quads) {
+      const float4 g = ((const float4*)gain)[i];
+      const float a = (v[k].x * scale) * g.x, b = (v[k].y * scale) * g.y, c = (v[k].z * scale) * g.z, d = (v[k].w * scale) * g.w;
+      if (sizeof(TO) == 4) {
+        ((float4*)dst)[i] = make_float4(a, b, c, d);
+      } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        ((uint2*)dst)[i] = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+      }
+    }
+  }
+}
+
+template <typename TO>
+static void launch_rmsnorm(const float* x, const float* gain, TO* out, const int* rows, int num_rows, int hidden,
+                           float eps, cudaStream_t stream) {
+  const int quads = hidden / 4;
+  const bool aligned = hidden % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)gain & 15) == 0 && ((uintptr_t)out & 15) == 0;
+  if (aligned && quads <= 256) rmsnorm_vec_kernel<TO, 1><<<num_rows, 256, 0, stream>>>(x, gain, out, rows, hidden, eps);
+  else if (aligned && quads <= 512) rmsnorm_vec_kernel<TO, 2><<<num_rows, 256, 0, stream>>>(x, gain, out, rows, hidden, eps);
+  else if (aligned && quads <= 1024) rmsnorm_vec_kernel<TO, 4><<<num_rows, 256, 0, stream>>>(x, gain, out, rows, hidden, eps);
+  else if (aligned && quads <= 2048) rmsnorm_vec_kernel<TO, 8><<<num_rows, 256, 0, stream>>>(x, gain, out, rows, hidden, eps);
+  else rmsnorm_kernel<TO><<<num_rows, hidden >= 1024 ? 256 : 128, 0, stream>>>(x, gain, out, rows, hidden, eps);
+}
+
 SPROUT_API int sprout_rmsnorm(const float* x, const float* gain, void* out, int out_dtype, const int* rows,
                               int num_rows, int hidden, float eps, cudaStream_t stream) {
   SPROUT_REQUIRE(num_rows > 0 && hidden > 0, "rmsnorm: sizes must be positive");
   SPROUT_REQUIRE(x && gain && out, "rmsnorm: null pointer");
   SPROUT_REQUIRE(eps > 0.f, "rmsnorm: eps must be positive");
-  const int threads = hidden >= 1024 ? 256 : 128;
-  if (out_dtype == SPROUT_F32)
-    rmsnorm_kernel<float><<<num_rows, threads, 0, stream>>>(x, gain, (float*)out, rows, hidden, eps);
-  else if (out_dtype == SPROUT_BF16)
-    rmsnorm_kernel<__nv_bfloat16><<<num_rows, threads, 0, stream>>>(x, gain, (__nv_bfloat16*)out, rows, hidden, eps);
-  else
-    return sprout_fail("rmsnorm: unknown dtype %d", out_dtype);
+  if (out_dtype == SPROUT_F32) launch_rmsnorm<float>(x, gain, (float*)out, rows, num_rows, hidden, eps, stream);
+  else if (out_dtype == SPROUT_BF16) launch_rmsnorm<__nv_bfloat16>(x, gain, (__nv_bfloat16*)out, rows, num_rows, hidden, eps, stream);
+  else return sprout_fail("rmsnorm: unknown dtype %d", out_dtype);
   return sprout_check_launch("rmsnorm");
 }
 
@@ -128,36 +173,40 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const int* __restrict__ 
   T* row = qkv + (size_t)t * width;
   const float* cs = rotate ? cos_table + (size_t)pos * half : nullptr;
   const float* sn = rotate ? sin_table + (size_t)pos * half : nullptr;
-  // q heads, in place
-  for (int i = threadIdx.x; rotate && i < heads * half; i += blockDim.x) {
-    const int h = i / half, d = i % half;
-    T* x = row + h * head_dim;
-    const float a = to_float(x[d]), b = to_float(x[d + half]);
-    const float c = cs[d], s = sn[d];
-    x[d] = from_float<T>(a * c - b * s);
-    x[d + half] = from_float<T>(b * c + a * s);
+  int page = 0, slot = 0;
+  bool page_ok = false;
+  if (write_cache) {
+    const int seq = seq_of_token[t];
+    page = block_table[(size_t)seq * table_stride + pos / page_tokens];
+    slot = pos % page_tokens;
+    page_ok = page >= 0 && page < num_pages;
+    if (!page_ok && threadIdx.x == 0) atomicOr(status, SPROUT_STATUS_BAD_PAGE);
   }
-  if (!write_cache) return;
-  const int seq = seq_of_token[t];
-  const int page = block_table[(size_t)seq * table_stride + pos / page_tokens];
-  if (page < 0 || page >= num_pages) {
-    if (threadIdx.x == 0) atomicOr(status, SPROUT_STATUS_BAD_PAGE);
-    return;
-  }
-  const int slot = pos % page_tokens;
-  const T* k_row = row + heads * head_dim;
-  const T* v_row = k_row + kv_heads * head_dim;
-  for (int i = threadIdx.x; i < kv_heads * half; i += blockDim.x) {
+  // one thread per rotated pair: q heads in place, k heads into the cache
+  for (int i = threadIdx.x; i < (heads + kv_heads) * half; i += blockDim.x) {
     const int h = i / half, d = i % half;
-    const float a = to_float(k_row[h * head_dim + d]), b = to_float(k_row[h * head_dim + d + half]);
     const float c = rotate ? cs[d] : 1.f, s = rotate ? sn[d] : 0.f;
-    T* dst = k_cache + (((size_t)page * kv_heads + h) * page_tokens + slot) * head_dim;
-    dst[d] = from_float<T>(a * c - b * s);
-    dst[d + half] = from_float<T>(b * c + a * s);
+    if (h < heads) {
+      if (!rotate) continue;
+      T* x = row + h * head_dim;
+      const float a = to_float(x[d]), b = to_float(x[d + half]);
+      x[d] = from_float<T>(a * c - b * s);
+      x[d + half] = from_float<T>(b * c + a * s);
+    } else if (page_ok) {
+      const int kh = h - heads;
+      const T* x = row + h * head_dim;
+      const float a = to_float(x[d]), b = to_float(x[d + half]);
+      T* dst = k_cache + (((size_t)page * kv_heads + kh) * page_tokens + slot) * head_dim;
+      dst[d] = from_float<T>(a * c - b * s);
+      dst[d + half] = from_float<T>(b * c + a * s);
+    }
   }
-  for (int i = threadIdx.x; i < kv_heads * head_dim; i += blockDim.x) {
-    const int h = i / head_dim, d = i % head_dim;
-    v_cache[(((size_t)page * kv_heads + h) * page_tokens + slot) * head_dim + d] = v_row[i];
+  if (page_ok) {
+    const T* v_row = row + (heads + kv_heads) * head_dim;
+    for (int i = threadIdx.x; i < kv_heads * head_dim; i += blockDim.x) {
+      const int h = i / head_dim, d = i % head_dim;
+      v_cache[(((size_t)page * kv_heads + h) * page_tokens + slot) * head_dim + d] = v_row[i];
+    }
   }
 }
 
@@ -172,12 +221,14 @@ SPROUT_API int sprout_rope_append(void* qkv, int dtype, const int* positions, co
   SPROUT_REQUIRE(qkv && positions && seq_of_token && block_table && status, "rope_append: null pointer");
   SPROUT_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "rope_append: cos and sin tables go together");
   SPROUT_REQUIRE(!write_cache || (k_cache && v_cache), "rope_append: cache pointers missing");
+  const int pairs = (heads + kv_heads) * (head_dim / 2);
+  const int threads = pairs >= 1024 ? 1024 : (pairs + 31) / 32 * 32;
   if (dtype == SPROUT_F32)
-    rope_append_kernel<float><<<num_tokens, 128, 0, stream>>>(
+    rope_append_kernel<float><<<num_tokens, threads, 0, stream>>>(
         (float*)qkv, positions, seq_of_token, block_table, table_stride, cos_table, sin_table, max_positions,
         (float*)k_cache, (float*)v_cache, heads, kv_heads, head_dim, page_tokens, num_pages, write_cache, status);
   else if (dtype == SPROUT_BF16)
-    rope_append_kernel<__nv_bfloat16><<<num_tokens, 128, 0, stream>>>(
+    rope_append_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(
         (__nv_bfloat16*)qkv, positions, seq_of_token, block_table, table_stride, cos_table, sin_table,
         max_positions, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, heads, kv_heads, head_dim, page_tokens,
         num_pages, write_cache, status);

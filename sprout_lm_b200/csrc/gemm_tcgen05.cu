@@ -36,7 +36,12 @@ constexpr int NUM_THREADS = 192;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;   // tries of mbarrier.try_wait (each blocks for a while)
 constexpr int SMEM_BUDGET = 200 * 1024;
 
-enum Epilogue : int { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_RESIDUAL_ATOMIC = 2 };
+enum Epilogue : int { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_RESIDUAL_ATOMIC = 2, EPI_SWIGLU = 3 };
+
+// SwiGLU epilogue: the weight rows interleave gate and up in blocks of 8 (rows 16b..16b+7 gate,
+// 16b+8..16b+15 up), so output feature 8b+j is silu(D[.., 16b+j]) * D[.., 16b+8+j]; the output
+// has N/2 features and is bfloat16.
+__device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + __expf(-g))) * u; }
 
 struct Params {
   const float* bias;     // [N] or null
@@ -216,7 +221,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
         tmem_load16(taddr + c, raw);
         if (SWAP) {
           // row = output feature, columns = tokens: lanes hold consecutive features
-          if (row < p.N) {
+          if (p.epilogue == EPI_SWIGLU) {
+            // lanes l and l ^ 8 hold a gate row and its up row (128-row tiles start on multiples of 16)
+            const int out_n = (row >> 4) * 8 + (row & 7);
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+              const float mine = __uint_as_float(raw[j]);
+              const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
+              const int m = col0 + c + j;
+              if ((lane & 8) == 0 && row < p.N && m < p.M)
+                ((__nv_bfloat16*)p.out)[(size_t)m * p.ldo + out_n] = __float2bfloat16_rn(silu_mul(mine, other));
+            }
+          } else if (row < p.N) {
             const float b = (p.bias && first_split) ? p.bias[row] : 0.f;
 #pragma unroll
             for (int j = 0; j < 16; j++) {
@@ -239,7 +255,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             for (int j = 0; j < 16; j++) v[j] = __uint_as_float(raw[j]) + ((p.bias && n_base + j < p.N) ? p.bias[n_base + j] : 0.f);
             const size_t at = (size_t)row * p.ldo + n_base;
             const bool whole = n_base + 16 <= p.N;
-            if (p.epilogue == EPI_RESIDUAL) {
+            if (p.epilogue == EPI_SWIGLU) {
+              if (n_base < p.N) {
+                uint32_t packed[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(silu_mul(v[2 * j], v[2 * j + 8]), silu_mul(v[2 * j + 1], v[2 * j + 9]));
+                  packed[j] = *(uint32_t*)&h;
+                }
+                __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)row * p.ldo + (n_base >> 1);
+                if ((((size_t)row * p.ldo + (n_base >> 1)) & 7) == 0) *(uint4*)o = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                else { for (int j = 0; j < 4; j++) ((uint32_t*)o)[j] = packed[j]; }
+              }
+            } else if (p.epilogue == EPI_RESIDUAL) {
               float* o = (float*)p.out + at;
               if (whole && (at & 3) == 0) {
 #pragma unroll
@@ -365,15 +393,22 @@ int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const Param
 // float32.  residual != 0: out is float32 and the product is added to it.  orientation: 0 picks
 // by M (weights on the MMA's M axis up to 128 tokens), 1 forces tokens on M, 2 weights on M.
 // split_k > 1 (weights-on-M, residual only) divides K among CTAs and adds with atomics.
+// residual == 2: the SwiGLU epilogue (no bias; out is bfloat16 [M, N/2]; N a multiple of 16).
 SPROUT_API int sprout_gemm_bf16(const void* A, const void* W, const float* bias, void* out, int out_dtype,
                                 int residual, int M, int N, int K, int lda, int ldo, int orientation,
                                 int split_k, int* status, cudaStream_t stream) {
+  const bool swiglu = residual == 2;
+  if (swiglu) {
+    residual = 0;
+    SPROUT_REQUIRE(N % 16 == 0 && !bias && out_dtype == SPROUT_BF16 && ldo >= N / 2 && ldo % 2 == 0,
+                   "gemm_bf16: the SwiGLU epilogue needs N %% 16 == 0, no bias and a bfloat16 output [M, N/2]");
+  }
   SPROUT_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_bf16: sizes must be positive (M=%d N=%d K=%d)", M, N, K);
   SPROUT_REQUIRE(A && W && out && status, "gemm_bf16: null pointer");
   SPROUT_REQUIRE(K % 8 == 0 && lda % 8 == 0, "gemm_bf16: K (%d) and the row stride of A (%d) must be multiples of 8 "
                  "(TMA rows start on 16-byte boundaries)", K, lda);
   SPROUT_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_bf16: operands must be 16-byte aligned");
-  SPROUT_REQUIRE(lda >= K && ldo >= N, "gemm_bf16: row strides smaller than the rows");
+  SPROUT_REQUIRE(lda >= K && (swiglu || ldo >= N), "gemm_bf16: row strides smaller than the rows");
   SPROUT_REQUIRE(out_dtype == SPROUT_F32 || out_dtype == SPROUT_BF16, "gemm_bf16: unknown output dtype %d", out_dtype);
   SPROUT_REQUIRE(!residual || out_dtype == SPROUT_F32, "gemm_bf16: a residual needs a float32 output");
   const bool swap = orientation == 2 || (orientation == 0 && M <= 128);
@@ -383,7 +418,7 @@ SPROUT_API int sprout_gemm_bf16(const void* A, const void* W, const float* bias,
 
   Params p;
   p.bias = bias; p.out = out; p.out_is_f32 = out_dtype == SPROUT_F32;
-  p.epilogue = residual ? (split_k > 1 ? EPI_RESIDUAL_ATOMIC : EPI_RESIDUAL) : EPI_STORE;
+  p.epilogue = swiglu ? EPI_SWIGLU : residual ? (split_k > 1 ? EPI_RESIDUAL_ATOMIC : EPI_RESIDUAL) : EPI_STORE;
   p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.status = status;
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
   if (split_k > total_kb) split_k = total_kb;

@@ -1,83 +1,126 @@
-// Sampling from float32 logits on the device, one block per row.
+// Sampling from float32 logits on the device.
 //   greedy: the lowest index among the maxima; a row with a non-finite logit gives -1
 //           and sets a status bit (the reference's argmax rule and failure).
 //   temperature: p = softmax(logits / T) in float32, then the inverse of the cumulative
 //           distribution at a uniform number u in [0, 1) that the host derives from
 //           (seed, request, index of the output token), so the draw does not depend on
 //           the batch.  Rows with T == 0 are greedy.
+// Two launches: the vocabulary of every row is cut into CHUNKS runs, one block per (run, row)
+// finds the run's maximum, its first index and (for T > 0) the sum of exp((v - max) / T) with
+// coalesced reads; one block per row then merges the runs in index order and, for T > 0, scans
+// the one run in which the draw falls.  The partial results live in a buffer the caller gives.
 #include "common.cuh"
 
 namespace {
 
-constexpr int THREADS = 1024;
+constexpr int CHUNKS = 64, PART_THREADS = 256, FINAL_THREADS = 1024;
 
-__global__ void __launch_bounds__(THREADS)
-sample_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ temperature,
-              const float* __restrict__ uniform, int* __restrict__ out, int vocab, int* status) {
+struct Partial { float max; int index; float sum; int bad; };
+
+__device__ __forceinline__ void better(float& v, int& i, float ov, int oi) {
+  if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+}
+
+__global__ void __launch_bounds__(PART_THREADS)
+sample_partial_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ temperature,
+                      Partial* __restrict__ partials, int vocab) {
+  __shared__ float s_val[PART_THREADS / 32];
+  __shared__ int s_idx[PART_THREADS / 32];
   __shared__ float scratch[33];
-  __shared__ float s_val[32];
-  __shared__ int s_idx[32];
-  __shared__ float s_prefix[THREADS];
-  __shared__ int s_result;
-  const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int chunk = blockIdx.x, r = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int len = (vocab + CHUNKS - 1) / CHUNKS;
+  const int begin = min(chunk * len, vocab), end = min(begin + len, vocab);
   const float* row = logits + (size_t)r * ld;
-
-  // every thread owns a contiguous segment, so that cumulative sums follow index order
-  const int seg = (vocab + THREADS - 1) / THREADS;
-  const int begin = min(tid * seg, vocab), end = min(begin + seg, vocab);
-
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  bool bad = false;
-  for (int i = begin; i < end; i++) {
+  int bad = 0;
+  for (int i = begin + tid; i < end; i += PART_THREADS) {
     const float v = row[i];
-    if (!isfinite(v)) bad = true;
-    if (v > best) { best = v; best_i = i; }
+    if (!isfinite(v)) bad = 1;
+    if (v > best) { best = v; best_i = i; }        // ascending i: the first maximum stays
   }
-  // argmax with the lowest index winning ties
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-    if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
-  }
-  const int any_bad = __syncthreads_or(bad ? 1 : 0);
+  for (int o = 16; o > 0; o >>= 1)
+    better(best, best_i, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, best_i, o));
+  bad = __syncthreads_or(bad);
   if (lane == 0) { s_val[warp] = best; s_idx[warp] = best_i; }
   __syncthreads();
-  if (warp == 0) {
-    best = s_val[lane];
-    best_i = s_idx[lane];
+  best = s_val[0]; best_i = s_idx[0];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-      if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+  for (int w = 1; w < PART_THREADS / 32; w++) better(best, best_i, s_val[w], s_idx[w]);
+  float sum = 0.f;
+  const float temp = temperature ? temperature[r] : 0.f;
+  if (temp > 0.f && !bad && begin < end) {
+    for (int i = begin + tid; i < end; i += PART_THREADS) sum += __expf((row[i] - best) / temp);
+    sum = block_sum(sum, scratch);
+  }
+  if (tid == 0) partials[(size_t)r * CHUNKS + chunk] = Partial{best, best_i, sum, bad};
+}
+
+__global__ void __launch_bounds__(FINAL_THREADS)
+sample_final_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ temperature,
+                    const float* __restrict__ uniform, const Partial* __restrict__ partials,
+                    int* __restrict__ out, int vocab, int* status) {
+  __shared__ Partial s_part[CHUNKS];
+  __shared__ float s_prefix[FINAL_THREADS];
+  __shared__ int s_chunk, s_result;
+  __shared__ float s_before, s_top;
+  const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float* row = logits + (size_t)r * ld;
+  if (tid < CHUNKS) s_part[tid] = partials[(size_t)r * CHUNKS + tid];
+  __syncthreads();
+  const float temp = temperature ? temperature[r] : 0.f;
+  if (tid == 0) {
+    float best = -INFINITY, total = 0.f;
+    int best_i = 0x7fffffff, bad = 0;
+    for (int c = 0; c < CHUNKS; c++) { better(best, best_i, s_part[c].max, s_part[c].index); bad |= s_part[c].bad; }
+    s_top = best;
+    s_chunk = -1;
+    if (bad) {
+      out[r] = -1;
+      atomicOr(status, SPROUT_STATUS_NONFINITE);
+    } else if (!(temp > 0.f)) {
+      out[r] = best_i;
+    } else {
+      // weights of the runs against the row's maximum, in index order; the run the draw falls in
+      for (int c = 0; c < CHUNKS; c++) total += s_part[c].sum * __expf((s_part[c].max - best) / temp);
+      const float target = uniform[r] * total;
+      float before = 0.f;
+      int pick = -1, last = 0;
+      for (int c = 0; c < CHUNKS; c++) {
+        const float w = s_part[c].sum * __expf((s_part[c].max - best) / temp);
+        if (w > 0.f) last = c;
+        if (pick < 0 && target < before + w) { pick = c; break; }
+        before += w;
+      }
+      if (pick < 0) {                  // rounding pushed the target past the end: the last run with weight
+        pick = last;
+        before = 0.f;
+        for (int c = 0; c < last; c++) before += s_part[c].sum * __expf((s_part[c].max - best) / temp);
+      }
+      s_chunk = pick;
+      s_before = target - before;      // the draw, counted from the run's start
+      s_result = -1;
     }
-    if (lane == 0) { s_val[0] = best; s_idx[0] = best_i; }
   }
   __syncthreads();
-  if (any_bad) {
-    if (tid == 0) { out[r] = -1; atomicOr(status, SPROUT_STATUS_NONFINITE); }
-    return;
-  }
-  const float top = s_val[0];
-  const float temp = temperature ? temperature[r] : 0.f;
-  if (!(temp > 0.f)) {
-    if (tid == 0) out[r] = s_idx[0];
-    return;
-  }
-  // softmax(logits / T): weights exp((v - top) / T), summed per segment then across segments
+  const int chunk = s_chunk;
+  if (chunk < 0) return;
+  // scan the run: each thread owns a contiguous piece, pieces are summed in index order
+  const int len = (vocab + CHUNKS - 1) / CHUNKS;
+  const int c_begin = min(chunk * len, vocab), c_end = min(c_begin + len, vocab);
+  const int seg = (c_end - c_begin + FINAL_THREADS - 1) / FINAL_THREADS;
+  const int begin = min(c_begin + tid * seg, c_end), end = min(begin + seg, c_end);
+  const float top = s_top, target = s_before;
   float local = 0.f;
-  for (int i = begin; i < end; i++) local += expf((row[i] - top) / temp);
+  for (int i = begin; i < end; i++) local += __expf((row[i] - top) / temp);
   s_prefix[tid] = local;
   __syncthreads();
-  const float total = block_sum(local, scratch);
-  // exclusive prefix over segments, done by one warp over 32 values per lane (fixed order)
   if (warp == 0) {
     float run = 0.f;
-    float mine[THREADS / 32];
+    float mine[FINAL_THREADS / 32];
 #pragma unroll
-    for (int j = 0; j < THREADS / 32; j++) { mine[j] = s_prefix[lane * (THREADS / 32) + j]; run += mine[j]; }
+    for (int j = 0; j < FINAL_THREADS / 32; j++) { mine[j] = s_prefix[lane * (FINAL_THREADS / 32) + j]; run += mine[j]; }
     float incl = run;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -86,45 +129,42 @@ sample_kernel(const float* __restrict__ logits, int ld, const float* __restrict_
     }
     float excl = incl - run;
 #pragma unroll
-    for (int j = 0; j < THREADS / 32; j++) { s_prefix[lane * (THREADS / 32) + j] = excl; excl += mine[j]; }
+    for (int j = 0; j < FINAL_THREADS / 32; j++) { s_prefix[lane * (FINAL_THREADS / 32) + j] = excl; excl += mine[j]; }
   }
-  if (tid == 0) s_result = -1;
   __syncthreads();
-  const float target = uniform[r] * total;
-  // segment intervals [prefix[tid], prefix[tid + 1]) cover [0, inf) without gap or overlap
+  // piece intervals [prefix[tid], prefix[tid + 1]) cover [0, inf) without gap or overlap
   const float before = s_prefix[tid];
-  const bool last_segment = (tid == THREADS - 1) || ((tid + 1) * seg >= vocab);
-  const float after = last_segment ? INFINITY : s_prefix[tid + 1];
+  const bool last_piece = (tid == FINAL_THREADS - 1) || (c_begin + (tid + 1) * seg >= c_end);
+  const float after = last_piece ? INFINITY : s_prefix[tid + 1];
   if (begin < end && target >= before && target < after) {
     float run = before;
     int pick = end - 1;
     for (int i = begin; i < end; i++) {
-      run += expf((row[i] - top) / temp);
+      run += __expf((row[i] - top) / temp);
       if (target < run) { pick = i; break; }
     }
     atomicMax(&s_result, pick);
   }
   __syncthreads();
-  if (tid == 0) {
-    int pick = s_result;
-    if (pick < 0) {
-      // rounding left the target beyond the last segment's end: take the last index with weight
-      pick = vocab - 1;
-    }
-    out[r] = pick;
-  }
+  if (tid == 0) out[r] = s_result >= 0 ? s_result : c_end - 1;
 }
 
 }  // namespace
 
-// logits [rows, vocab] with row stride ld; temperature and uniform may be null (all greedy).
+// Bytes of scratch that sampling `rows` rows needs.
+SPROUT_API long long sprout_sample_scratch_bytes(int rows) { return (long long)rows * CHUNKS * sizeof(Partial); }
+
+// logits [rows, vocab] with row stride ld; temperature and uniform may be null (all greedy);
+// scratch: sprout_sample_scratch_bytes(rows) bytes, 16-byte aligned.
 SPROUT_API int sprout_sample(const float* logits, int ld, const float* temperature, const float* uniform,
-                             int* out, int rows, int vocab, int* status, cudaStream_t stream) {
-  SPROUT_REQUIRE(rows > 0 && vocab > 0 && ld >= vocab, "sample: bad sizes rows=%d vocab=%d ld=%d", rows, vocab, ld);
-  SPROUT_REQUIRE(logits && out && status, "sample: null pointer");
+                             int* out, void* scratch, int rows, int vocab, int* status, cudaStream_t stream) {
+  SPROUT_REQUIRE(rows > 0 && rows <= 65535 && vocab > 0 && ld >= vocab, "sample: bad sizes rows=%d vocab=%d ld=%d", rows, vocab, ld);
+  SPROUT_REQUIRE(logits && out && status && scratch, "sample: null pointer");
   SPROUT_REQUIRE((temperature == nullptr) == (uniform == nullptr), "sample: temperature and uniform go together");
-  sample_kernel<<<rows, THREADS, 0, stream>>>(logits, ld, temperature, uniform, out, vocab, status);
-  return sprout_check_launch("sample");
+  sample_partial_kernel<<<dim3(CHUNKS, rows), PART_THREADS, 0, stream>>>(logits, ld, temperature, (Partial*)scratch, vocab);
+  if (sprout_check_launch("sample_partial")) return 1;
+  sample_final_kernel<<<rows, FINAL_THREADS, 0, stream>>>(logits, ld, temperature, uniform, (const Partial*)scratch, out, vocab, status);
+  return sprout_check_launch("sample_final");
 }
 
 // ------------------------------------------------------------------ feeding a decode step's output back

@@ -32,7 +32,7 @@ _SIGNATURES = {
     "sprout_rope_append": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_gemm_simple": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "sprout_attention_simple": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
-    "sprout_sample": [_P, _I, _P, _P, _P, _I, _I, _P, _P],
+    "sprout_sample": [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P],
     "sprout_advance_decode": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
     "sprout_attention_decode": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
@@ -52,6 +52,8 @@ def load_library(verbose: bool = True):
             lib = ctypes.CDLL(str(path))
             lib.sprout_last_error.restype = ctypes.c_char_p
             lib.sprout_abi_version.restype = c_int
+            lib.sprout_sample_scratch_bytes.restype = ctypes.c_longlong
+            lib.sprout_sample_scratch_bytes.argtypes = [c_int]
             lib.sprout_attention_decode_scratch_floats.restype = ctypes.c_longlong
             lib.sprout_attention_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
             for name, argtypes in _SIGNATURES.items():
@@ -209,20 +211,22 @@ def attention_simple(q, k_cache, v_cache, block_table, seq_of_token, positions, 
          k_cache.shape[0], _ptr(status, "status", torch.int32), _stream())
 
 
-def gemm_bf16(a, weight, out, status, bias=None, residual=None, orientation=0, split_k=1):
+def gemm_bf16(a, weight, out, status, bias=None, residual=None, orientation=0, split_k=1, swiglu=False):
     """out = a @ weight.T (+ bias) (+ residual) on the tcgen05 tensor cores; a and weight bfloat16.
 
     ``residual`` must be ``out`` itself (float32): the product is added in place.  orientation 0
     lets the kernel choose (weight rows on the MMA's M axis for up to 128 tokens), 1 forces
     tokens on M, 2 weights on M.  ``split_k`` > 1 divides K among CTAs (weights on M with a
-    residual only; the partial sums are added with atomics)."""
+    residual only; the partial sums are added with atomics).  ``swiglu``: weight rows interleave
+    gate and up in blocks of 8 and ``out`` is bfloat16 [M, N/2] = silu(gate) * up."""
     _rows_contiguous(a, "a")
     _rows_contiguous(out, "out")
     if not weight.is_contiguous() or weight.dim() != 2:
         raise KernelError("gemm_bf16: weight must be contiguous [N, K]")
     M, K = a.shape
     N = weight.shape[0]
-    if weight.shape[1] != K or tuple(out.shape) != (M, N) or a.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+    if weight.shape[1] != K or tuple(out.shape) != (M, N // 2 if swiglu else N) or a.dtype != torch.bfloat16 \
+            or weight.dtype != torch.bfloat16:
         raise KernelError(f"gemm_bf16: shapes/dtypes do not fit: a {tuple(a.shape)} {a.dtype}, "
                           f"weight {tuple(weight.shape)} {weight.dtype}, out {tuple(out.shape)}")
     if bias is not None and bias.numel() != N:
@@ -230,7 +234,7 @@ def gemm_bf16(a, weight, out, status, bias=None, residual=None, orientation=0, s
     if residual is not None and residual.data_ptr() != out.data_ptr():
         raise KernelError("gemm_bf16: the residual is added in place: pass out itself")
     _run("sprout_gemm_bf16", _ptr(a, "a"), _ptr(weight, "weight"), _ptr(bias, "bias", torch.float32, True),
-         _ptr(out, "out"), _dtype_code(out.dtype), 1 if residual is not None else 0, M, N, K, a.stride(0),
+         _ptr(out, "out"), _dtype_code(out.dtype), 2 if swiglu else (1 if residual is not None else 0), M, N, K, a.stride(0),
          out.stride(0), orientation, split_k, _ptr(status, "status", torch.int32), _stream())
 
 
@@ -315,9 +319,10 @@ def sample(logits, out, status, temperature=None, uniform=None):
     R, V = logits.shape
     if out.numel() != R:
         raise KernelError("sample: one output per row")
+    scratch = torch.empty(load_library().sprout_sample_scratch_bytes(R), dtype=torch.uint8, device=logits.device)
     _run("sprout_sample", _ptr(logits, "logits", torch.float32), logits.stride(0),
          _ptr(temperature, "temperature", torch.float32, True), _ptr(uniform, "uniform", torch.float32, True),
-         _ptr(out, "out", torch.int32), R, V, _ptr(status, "status", torch.int32), _stream())
+         _ptr(out, "out", torch.int32), _ptr(scratch, "scratch"), R, V, _ptr(status, "status", torch.int32), _stream())
 
 
 def advance_decode(token_ids, positions, context_lens, sampled, history, step_counter):

@@ -32,6 +32,17 @@ class Linear:
         k_blocks = -(-self.in_features // 64)
         return max(1, min(k_blocks, SM_COUNT // tiles))
 
+    def forward_swiglu(self, a: torch.Tensor) -> torch.Tensor:
+        """silu(gate) * up of a fused, interleaved gate/up matrix: fused into the product's epilogue
+        on the tensor-core path, a separate kernel on the 32-bit path."""
+        half = self.out_features // 2
+        out = torch.empty((a.shape[0], half), dtype=a.dtype, device=a.device)
+        if self.weight.dtype == torch.bfloat16:
+            kernels.gemm_bf16(a, self.weight, out, self.status, swiglu=True)
+        else:
+            kernels.swiglu(self.forward(a), out)
+        return out
+
     def forward(self, a: torch.Tensor, out_dtype: torch.dtype | None = None,
                 residual: torch.Tensor | None = None) -> torch.Tensor:
         """``residual`` (float32 [rows, out_features]) is added to in place and returned."""

@@ -8,7 +8,6 @@ from __future__ import annotations
 
 import torch
 
-from .. import kernels
 from .base import Part, TensorDecl, WeightSource, register_part
 from .linear import Linear
 
@@ -44,7 +43,4 @@ class SwiGLUMLP(Part):
         self.down = Linear(source.matrix(self.names["down"] + ".weight"), None, source.runtime.status)
 
     def forward(self, h, x, ctx=None):
-        gate_up = self.gate_up.forward(h)
-        act = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
-        kernels.swiglu(gate_up, act)
-        self.down.forward(act, residual=x)
+        self.down.forward(self.gate_up.forward_swiglu(h), residual=x)
