@@ -52,6 +52,8 @@ attention_decode_kernel(const DecodeParams p) {
   __nv_bfloat16* sK = (__nv_bfloat16*)(rows + DEC_THREADS);       // [DEC_THREADS][stride]
   __nv_bfloat16* sV = sK + DEC_THREADS * stride;
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int len = p.context_lens[r];
@@ -207,6 +209,8 @@ attention_decode_kernel(const DecodeParams p) {
 
 // Merge the splits of one (request, head): grid (heads, requests), head_dim threads (rounded up to a warp).
 __global__ void attention_decode_merge_kernel(const DecodeParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int head = blockIdx.x, r = blockIdx.y, d = threadIdx.x;
   const int len = p.context_lens[r];
   const int live = min(p.splits, (len + p.split_keys - 1) / p.split_keys);
@@ -274,6 +278,8 @@ attention_prefill_kernel(const PrefillParams p) {
   __shared__ int s_head[PF_ROWS];
   __shared__ long long s_off[2][PF_KEYS];             // cache offsets of a tile's keys, -1 beyond the range
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = blockIdx.y;
   const int group = p.heads / p.kv_heads;
@@ -457,7 +463,7 @@ int launch_prefill(const PrefillParams& p, int grid_x, cudaStream_t stream) {
     if (err != cudaSuccess) return sprout_fail("attention_prefill: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(err));
     configured = true;
   }
-  attention_prefill_kernel<HD><<<dim3(grid_x, p.kv_heads), PF_THREADS, smem, stream>>>(p);
+  sprout_launch(attention_prefill_kernel<HD>, dim3(grid_x, p.kv_heads), dim3(PF_THREADS), smem, stream, p);
   return sprout_check_launch("attention_prefill");
 }
 
@@ -507,11 +513,11 @@ SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* 
                                                group, head_dim, smem, cudaGetErrorString(err));
     configured = smem;
   }
-  attention_decode_kernel<<<dim3(splits, kv_heads, requests), DEC_THREADS, smem, stream>>>(p);
+  sprout_launch(attention_decode_kernel, dim3(splits, kv_heads, requests), dim3(DEC_THREADS), smem, stream, p);
   if (sprout_check_launch("attention_decode")) return 1;
   if (splits > 1) {
     const int threads = (head_dim + 31) / 32 * 32;
-    attention_decode_merge_kernel<<<dim3(heads, requests), threads, 0, stream>>>(p);
+    sprout_launch(attention_decode_merge_kernel, dim3(heads, requests), dim3(threads), 0, stream, p);
     return sprout_check_launch("attention_decode_merge");
   }
   return 0;

@@ -24,6 +24,8 @@ attention_simple_kernel(const T* __restrict__ q, int q_stride, const T* __restri
   float* scratch = probs + CHUNK;         // 33
   long long* row_offset = (long long*)(scratch + 34);   // CHUNK (8-byte aligned: sizes below are even)
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
   const int g = h / (heads / kv_heads);
   const int seq = seq_of_token[t];
@@ -106,11 +108,11 @@ SPROUT_API int sprout_attention_simple(const void* q, int q_stride, const void* 
   const size_t smem = (size_t)(head_dim + CHUNK + 34) * sizeof(float) + CHUNK * sizeof(long long);
   dim3 grid(num_tokens, heads);
   if (dtype == SPROUT_F32)
-    attention_simple_kernel<float><<<grid, CHUNK, smem, stream>>>(
+    sprout_launch(attention_simple_kernel<float>, grid, dim3(CHUNK), smem, stream, 
         (const float*)q, q_stride, (const float*)k_cache, (const float*)v_cache, block_table, table_stride,
         seq_of_token, positions, (float*)out, out_stride, heads, kv_heads, head_dim, page_tokens, num_pages, status);
   else if (dtype == SPROUT_BF16)
-    attention_simple_kernel<__nv_bfloat16><<<grid, CHUNK, smem, stream>>>(
+    sprout_launch(attention_simple_kernel<__nv_bfloat16>, grid, dim3(CHUNK), smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
         block_table, table_stride, seq_of_token, positions, (__nv_bfloat16*)out, out_stride, heads, kv_heads,
         head_dim, page_tokens, num_pages, status);

@@ -116,6 +116,12 @@ def library_path(build: bool = True, verbose: bool = True, extra_flags: tuple[st
     if done.returncode != 0:
         raise BuildError(f"linking failed:\n{done.stdout}\n{done.stderr}")
     os.replace(partial, target)          # atomic: a concurrent builder sees nothing or the whole file
+    for stale in out_dir.glob("libsprout_kernels_*.so"):
+        if stale != target:
+            try:
+                stale.unlink()               # libraries of older sources
+            except OSError:
+                pass
     _say(f"built {target.name} in {time.time() - started:.1f}s", verbose)
     return target
 

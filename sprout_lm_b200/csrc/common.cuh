@@ -10,6 +10,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <utility>
+
 #define SPROUT_API extern "C" __attribute__((visibility("default")))
 
 enum SproutDtype : int { SPROUT_F32 = 0, SPROUT_BF16 = 1 };
@@ -25,6 +27,34 @@ enum SproutStatus : int {
 
 int sprout_fail(const char* fmt, ...);   // records the message, returns 1
 int sprout_check_launch(const char* what);
+
+// Programmatic dependent launch.  Every kernel of the library is launched so that it may start
+// while the kernel before it in the stream still runs: it calls pdl_launch_dependents() at entry
+// (its successor may be scheduled), does what does not depend on earlier kernels (set-up,
+// loads of weights and tables) and calls pdl_wait() before it reads or writes anything an
+// earlier kernel may have written.  pdl_wait() returns once all earlier kernels have completed
+// and their writes are visible; every block executes it, so a kernel never completes before its
+// predecessors.  sprout_set_pdl(0) turns the launch attribute off (the calls then do nothing).
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+int sprout_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t sprout_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = sprout_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
+}
 
 #define SPROUT_REQUIRE(cond, ...) \
   do { if (!(cond)) return sprout_fail(__VA_ARGS__); } while (0)

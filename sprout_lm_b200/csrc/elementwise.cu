@@ -10,6 +10,8 @@
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ out, int hidden, int vocab, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   int token = tokens[t];
   if (token < 0 || token >= vocab) {
@@ -26,9 +28,9 @@ SPROUT_API int sprout_embed(const void* table, int table_dtype, const int* token
   SPROUT_REQUIRE(num_tokens > 0 && hidden > 0 && vocab > 0, "embed: sizes must be positive");
   SPROUT_REQUIRE(table && tokens && out && status, "embed: null pointer");
   if (table_dtype == SPROUT_F32)
-    embed_kernel<float><<<num_tokens, 256, 0, stream>>>((const float*)table, tokens, out, hidden, vocab, status);
+    sprout_launch(embed_kernel<float>, dim3(num_tokens), dim3(256), 0, stream, (const float*)table, tokens, out, hidden, vocab, status);
   else if (table_dtype == SPROUT_BF16)
-    embed_kernel<__nv_bfloat16><<<num_tokens, 256, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, hidden, vocab, status);
+    sprout_launch(embed_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(256), 0, stream, (const __nv_bfloat16*)table, tokens, out, hidden, vocab, status);
   else
     return sprout_fail("embed: unknown dtype %d", table_dtype);
   return sprout_check_launch("embed");
@@ -42,6 +44,8 @@ template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
                                TO* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
   __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* src = x + (size_t)(rows ? rows[r] : r) * hidden;
   float ss = 0.f;
@@ -62,6 +66,8 @@ __global__ void __launch_bounds__(256)
 rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ gain, TO* __restrict__ out,
                    const int* __restrict__ rows, int hidden, float eps) {
   __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x, quads = hidden >> 2;
   const float4* src = (const float4*)(x + (size_t)(rows ? rows[r] : r) * hidden);
   float4 v[VEC];
@@ -97,11 +103,11 @@ static void launch_rmsnorm(const float* x, const float* gain, TO* out, const int
                            float eps, cudaStream_t stream) {
   const int quads = hidden / 4;
   const bool aligned = hidden % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)gain & 15) == 0 && ((uintptr_t)out & 15) == 0;
-  if (aligned && quads <= 256) rmsnorm_vec_kernel<TO, 1><<<num_rows, 256, 0, stream>>>(x, gain, out, rows, hidden, eps);
-  else if (aligned && quads <= 512) rmsnorm_vec_kernel<TO, 2><<<num_rows, 256, 0, stream>>>(x, gain, out, rows, hidden, eps);
-  else if (aligned && quads <= 1024) rmsnorm_vec_kernel<TO, 4><<<num_rows, 256, 0, stream>>>(x, gain, out, rows, hidden, eps);
-  else if (aligned && quads <= 2048) rmsnorm_vec_kernel<TO, 8><<<num_rows, 256, 0, stream>>>(x, gain, out, rows, hidden, eps);
-  else rmsnorm_kernel<TO><<<num_rows, hidden >= 1024 ? 256 : 128, 0, stream>>>(x, gain, out, rows, hidden, eps);
+  if (aligned && quads <= 256) sprout_launch(rmsnorm_vec_kernel<TO, 1>, dim3(num_rows), dim3(256), 0, stream, x, gain, out, rows, hidden, eps);
+  else if (aligned && quads <= 512) sprout_launch(rmsnorm_vec_kernel<TO, 2>, dim3(num_rows), dim3(256), 0, stream, x, gain, out, rows, hidden, eps);
+  else if (aligned && quads <= 1024) sprout_launch(rmsnorm_vec_kernel<TO, 4>, dim3(num_rows), dim3(256), 0, stream, x, gain, out, rows, hidden, eps);
+  else if (aligned && quads <= 2048) sprout_launch(rmsnorm_vec_kernel<TO, 8>, dim3(num_rows), dim3(256), 0, stream, x, gain, out, rows, hidden, eps);
+  else sprout_launch(rmsnorm_kernel<TO>, dim3(num_rows), dim3(hidden >= 1024 ? 256 : 128), 0, stream, x, gain, out, rows, hidden, eps);
 }
 
 SPROUT_API int sprout_rmsnorm(const float* x, const float* gain, void* out, int out_dtype, const int* rows,
@@ -121,6 +127,8 @@ SPROUT_API int sprout_rmsnorm(const float* x, const float* gain, void* out, int 
 // SiLU rounded to the element type's float32 value first.
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int tokens, int inter) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t total = (size_t)tokens * inter;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const int t = (int)(idx / inter), i = (int)(idx % inter);
@@ -138,9 +146,9 @@ SPROUT_API int sprout_swiglu(const void* gate_up, void* out, int dtype, int toke
   const size_t total = (size_t)tokens * inter;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   if (dtype == SPROUT_F32)
-    swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, tokens, inter);
+    sprout_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, (float*)out, tokens, inter);
   else if (dtype == SPROUT_BF16)
-    swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, tokens, inter);
+    sprout_launch(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, tokens, inter);
   else
     return sprout_fail("swiglu: unknown dtype %d", dtype);
   return sprout_check_launch("swiglu");
@@ -161,6 +169,8 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const int* __restrict__ 
                                    const float* __restrict__ sin_table, int max_positions,
                                    T* __restrict__ k_cache, T* __restrict__ v_cache, int heads, int kv_heads,
                                    int head_dim, int page_tokens, int num_pages, int write_cache, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int half = head_dim >> 1;
   const int pos = positions[t];
@@ -224,11 +234,11 @@ SPROUT_API int sprout_rope_append(void* qkv, int dtype, const int* positions, co
   const int pairs = (heads + kv_heads) * (head_dim / 2);
   const int threads = pairs >= 1024 ? 1024 : (pairs + 31) / 32 * 32;
   if (dtype == SPROUT_F32)
-    rope_append_kernel<float><<<num_tokens, threads, 0, stream>>>(
+    sprout_launch(rope_append_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream, 
         (float*)qkv, positions, seq_of_token, block_table, table_stride, cos_table, sin_table, max_positions,
         (float*)k_cache, (float*)v_cache, heads, kv_heads, head_dim, page_tokens, num_pages, write_cache, status);
   else if (dtype == SPROUT_BF16)
-    rope_append_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(
+    sprout_launch(rope_append_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, stream, 
         (__nv_bfloat16*)qkv, positions, seq_of_token, block_table, table_stride, cos_table, sin_table,
         max_positions, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, heads, kv_heads, head_dim, page_tokens,
         num_pages, write_cache, status);

@@ -26,5 +26,10 @@ int sprout_check_launch(const char* what) {
 // Text of the last failure on the calling thread.
 SPROUT_API const char* sprout_last_error() { return g_error; }
 
+static int g_pdl = 1;
+int sprout_pdl_enabled() { return g_pdl; }
+// Turn programmatic dependent launch on (default) or off for all later launches.
+SPROUT_API void sprout_set_pdl(int enabled) { g_pdl = enabled ? 1 : 0; }
+
 // Version of the exported interface; the Python side checks it after loading.
-SPROUT_API int sprout_abi_version() { return 3; }
+SPROUT_API int sprout_abi_version() { return 4; }

@@ -15,6 +15,8 @@ gemm_simple_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const flo
                    const float* residual, TO* out, int M, int N, int K, int lda, int ldo) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
+  pdl_launch_dependents();
+  pdl_wait();
   const int tid = threadIdx.x;
   const int ty = tid / 16, tx = tid % 16;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -68,8 +70,8 @@ template <typename TA, typename TW, typename TO>
 int launch(const void* A, const void* W, const float* bias, const float* residual, void* out, int M, int N,
            int K, int lda, int ldo, cudaStream_t stream) {
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  gemm_simple_kernel<TA, TW, TO><<<grid, THREADS, 0, stream>>>((const TA*)A, (const TW*)W, bias, residual,
-                                                               (TO*)out, M, N, K, lda, ldo);
+  sprout_launch(gemm_simple_kernel<TA, TW, TO>, grid, dim3(THREADS), 0, stream, (const TA*)A, (const TW*)W, bias, residual,
+                (TO*)out, M, N, K, lda, ldo);
   return sprout_check_launch("gemm_simple");
 }
 

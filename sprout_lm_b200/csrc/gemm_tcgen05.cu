@@ -159,6 +159,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
   const int kb_end = min(total_kb, kb_begin + p.k_blocks_per_split);
   const int num_kb = kb_end - kb_begin;
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     mbar_init(acc_bar, 1);
@@ -173,16 +174,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
 
   int issued = 0;
   if (warp == 0 && lane == 0) {
-    // ---------------- producer: TMA loads of the two operand tiles, stage by stage
+    // ---------------- producer: TMA loads of the two operand tiles, stage by stage.
+    // The weights were written before any kernel of the step ran: their tiles for the first
+    // round of stages are requested before waiting for the kernel that produces the activations.
+    const CUtensorMap* weight_map = SWAP ? &map_rows : &map_cols;
+    const CUtensorMap* act_map = SWAP ? &map_cols : &map_rows;
+    const int weight_row = SWAP ? row0 : col0, act_row = SWAP ? col0 : row0;
+    const int early = min(num_kb, L::STAGES);
+    for (int i = 0; i < early; i++) {
+      uint8_t* a_tile = smem + i * L::STAGE_BYTES;
+      mbar_expect_tx(&full_bar[i], L::A_BYTES + L::B_BYTES);
+      tma_load_2d(SWAP ? a_tile : a_tile + L::A_BYTES, weight_map, &full_bar[i], (kb_begin + i) * BLOCK_K, weight_row);
+    }
+    pdl_wait();
     for (int i = 0; i < num_kb; i++) {
       const int s = i % L::STAGES;
-      const uint32_t parity = ((i / L::STAGES) & 1) ^ 1;
-      if (*abort_flag || !mbar_wait(&empty_bar[s], parity)) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); break; }
       uint8_t* a_tile = smem + s * L::STAGE_BYTES;
-      uint8_t* b_tile = a_tile + L::A_BYTES;
-      mbar_expect_tx(&full_bar[s], L::A_BYTES + L::B_BYTES);
-      tma_load_2d(a_tile, &map_rows, &full_bar[s], (kb_begin + i) * BLOCK_K, row0);
-      tma_load_2d(b_tile, &map_cols, &full_bar[s], (kb_begin + i) * BLOCK_K, col0);
+      uint8_t* w_dst = SWAP ? a_tile : a_tile + L::A_BYTES;
+      uint8_t* x_dst = SWAP ? a_tile + L::A_BYTES : a_tile;
+      if (i >= early) {
+        const uint32_t parity = ((i / L::STAGES) & 1) ^ 1;
+        if (*abort_flag || !mbar_wait(&empty_bar[s], parity)) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); break; }
+        mbar_expect_tx(&full_bar[s], L::A_BYTES + L::B_BYTES);
+        tma_load_2d(w_dst, weight_map, &full_bar[s], (kb_begin + i) * BLOCK_K, weight_row);
+      }
+      tma_load_2d(x_dst, act_map, &full_bar[s], (kb_begin + i) * BLOCK_K, act_row);
       issued = i + 1;
     }
   } else if (warp == 1 && lane == 0) {
@@ -206,6 +222,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     umma_commit(acc_bar);               // the accumulator is complete once all MMAs are
   } else if (warp >= 2) {
     // ---------------- epilogue: TMEM -> registers -> global
+    pdl_wait();                         // the epilogue reads and writes `out`
     const int quarter = warp & 3;       // a warp reads TMEM lanes 32 * (warp % 4) ..
     const int row = row0 + quarter * 32 + lane;
     bool ok = num_kb > 0;
@@ -383,7 +400,7 @@ int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const Param
     if (err != cudaSuccess) return sprout_fail("gemm_bf16: cannot reserve %d bytes of shared memory: %s", L::SMEM_BYTES, cudaGetErrorString(err));
     configured = true;
   }
-  gemm_tcgen05_kernel<BN, SWAP><<<grid, NUM_THREADS, L::SMEM_BYTES, stream>>>(rows_map, cols_map, p);
+  sprout_launch(gemm_tcgen05_kernel<BN, SWAP>, grid, dim3(NUM_THREADS), L::SMEM_BYTES, stream, rows_map, cols_map, p);
   return sprout_check_launch("gemm_bf16");
 }
 

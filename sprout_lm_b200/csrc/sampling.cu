@@ -27,6 +27,8 @@ sample_partial_kernel(const float* __restrict__ logits, int ld, const float* __r
   __shared__ float s_val[PART_THREADS / 32];
   __shared__ int s_idx[PART_THREADS / 32];
   __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
   const int chunk = blockIdx.x, r = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int len = (vocab + CHUNKS - 1) / CHUNKS;
   const int begin = min(chunk * len, vocab), end = min(begin + len, vocab);
@@ -65,6 +67,8 @@ sample_final_kernel(const float* __restrict__ logits, int ld, const float* __res
   __shared__ float s_prefix[FINAL_THREADS];
   __shared__ int s_chunk, s_result;
   __shared__ float s_before, s_top;
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* row = logits + (size_t)r * ld;
   if (tid < CHUNKS) s_part[tid] = partials[(size_t)r * CHUNKS + tid];
@@ -161,9 +165,9 @@ SPROUT_API int sprout_sample(const float* logits, int ld, const float* temperatu
   SPROUT_REQUIRE(rows > 0 && rows <= 65535 && vocab > 0 && ld >= vocab, "sample: bad sizes rows=%d vocab=%d ld=%d", rows, vocab, ld);
   SPROUT_REQUIRE(logits && out && status && scratch, "sample: null pointer");
   SPROUT_REQUIRE((temperature == nullptr) == (uniform == nullptr), "sample: temperature and uniform go together");
-  sample_partial_kernel<<<dim3(CHUNKS, rows), PART_THREADS, 0, stream>>>(logits, ld, temperature, (Partial*)scratch, vocab);
+  sprout_launch(sample_partial_kernel, dim3(CHUNKS, rows), dim3(PART_THREADS), 0, stream, logits, ld, temperature, (Partial*)scratch, vocab);
   if (sprout_check_launch("sample_partial")) return 1;
-  sample_final_kernel<<<rows, FINAL_THREADS, 0, stream>>>(logits, ld, temperature, uniform, (const Partial*)scratch, out, vocab, status);
+  sprout_launch(sample_final_kernel, dim3(rows), dim3(FINAL_THREADS), 0, stream, logits, ld, temperature, uniform, (const Partial*)scratch, out, vocab, status);
   return sprout_check_launch("sample_final");
 }
 
@@ -174,6 +178,8 @@ SPROUT_API int sprout_sample(const float* logits, int ld, const float* temperatu
 // several decode steps run back to back (or as one replayed CUDA graph) without the host.
 __global__ void advance_decode_kernel(int* token_ids, int* positions, int* context_lens, const int* sampled,
                                       int* history, int* step_counter, int requests, int max_steps) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   const int step = *step_counter;
   if (r < requests) {
@@ -192,7 +198,7 @@ SPROUT_API int sprout_advance_decode(int* token_ids, int* positions, int* contex
                                      cudaStream_t stream) {
   SPROUT_REQUIRE(requests > 0 && requests <= 1024 && max_steps > 0, "advance_decode: 1..1024 requests, max_steps > 0");
   SPROUT_REQUIRE(token_ids && positions && context_lens && sampled && history && step_counter, "advance_decode: null pointer");
-  advance_decode_kernel<<<1, 1024, 0, stream>>>(token_ids, positions, context_lens, sampled, history, step_counter,
-                                                requests, max_steps);
+  sprout_launch(advance_decode_kernel, dim3(1), dim3(1024), 0, stream, token_ids, positions, context_lens, sampled, history,
+                step_counter, requests, max_steps);
   return sprout_check_launch("advance_decode");
 }

@@ -60,8 +60,18 @@ def load_library(verbose: bool = True):
                 fn = getattr(lib, name)
                 fn.argtypes = argtypes
                 fn.restype = c_int
+            lib.sprout_set_pdl.argtypes = [c_int]
+            lib.sprout_set_pdl.restype = None
+            import os
+            if os.environ.get("SPROUT_PDL", "1") == "0":
+                lib.sprout_set_pdl(0)
             _lib = lib
     return _lib
+
+
+def set_pdl(enabled: bool) -> None:
+    """Programmatic dependent launch of all kernels on (the default) or off."""
+    load_library().sprout_set_pdl(1 if enabled else 0)
 
 
 def library_file() -> str:
