@@ -10,10 +10,29 @@ next inputs on the device, so the steps replay back to back.
 """
 from __future__ import annotations
 
+import contextlib
+import gc
+
 import torch
 
 from .. import kernels
 from .batch import BatchStager
+
+
+@contextlib.contextmanager
+def guarded_capture(graph: "torch.cuda.CUDAGraph"):
+    """Stream capture that the garbage collector cannot disturb: freeing an older graph while a
+    new one is being captured is a CUDA call that invalidates the capture, so garbage is
+    collected before and the collector rests meanwhile."""
+    gc.collect()
+    was_enabled = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph, capture_error_mode="relaxed"):
+            yield
+    finally:
+        if was_enabled:
+            gc.enable()
 
 
 def _round_up(value: int, multiple: int) -> int:
@@ -53,7 +72,7 @@ class DecodeGraph:
             torch.cuda.synchronize()
             before = kernels.LAUNCHES
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            with guarded_capture(graph):
                 self.logits, self.tokens = self._forward(ctx)
             self.launches = kernels.LAUNCHES - before
             self.graph = graph
@@ -108,7 +127,7 @@ class DecodeLoop:
         torch.cuda.synchronize()
         before = kernels.LAUNCHES
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with guarded_capture(graph):
             self._one_step()
         self.launches_per_step = kernels.LAUNCHES - before
         self.graph = graph
