@@ -3,8 +3,8 @@
 // decode  (every request brings one query token): grid (splits, kv_heads, requests).  A CTA
 //   takes a run of `split_keys` keys of one key/value head of one request and serves all the
 //   query heads of that group from one read of the keys and values.  Partial results
-//   (running maximum, sum, unnormalised output) go to scratch memory; the CTA that finishes last
-//   for a (request, key/value head) merges its splits.  The work of a query does not depend on the batch around it.
+//   (running maximum, sum, unnormalised output) go to scratch memory; a second kernel merges
+//   the splits.  The work of a query does not depend on the batch around it.
 //
 // prefill (portions of prompts, possibly beside single tokens): tensor-core flash attention
 //   (mma.sync m16n8k16, float32 accumulation) over the pages.  The rows of a tile are (token,
@@ -27,7 +27,6 @@ struct DecodeParams {
   __nv_bfloat16* out; int out_stride;
   float* part_out;                    // [requests, heads, splits, head_dim]
   float* part_ml;                     // [requests, heads, splits, 2]
-  int* arrivals;                      // [requests, kv_heads] zero between calls: splits that have finished
   int heads, kv_heads, head_dim, page_tokens, num_pages, split_keys, splits;
   int* status;
 };
@@ -206,35 +205,25 @@ attention_decode_kernel(const DecodeParams p) {
       }
     }
   }
-  if (p.splits == 1) return;
+}
 
-  // The split that finishes last merges all splits of its (request, key/value head): every CTA
-  // publishes its partial results, then counts itself in; the counter returns to zero.
-  __shared__ int s_last;
+// Merge the splits of one (request, head): grid (heads, requests), head_dim threads (rounded up to a warp).
+__global__ void attention_decode_merge_kernel(const DecodeParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int head = blockIdx.x, r = blockIdx.y, d = threadIdx.x;
+  const int len = p.context_lens[r];
   const int live = min(p.splits, (len + p.split_keys - 1) / p.split_keys);
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const int arrived = atomicAdd(&p.arrivals[r * p.kv_heads + g], 1) + 1;
-    s_last = arrived == live;
-    if (s_last) p.arrivals[r * p.kv_heads + g] = 0;
+  const size_t slot0 = ((size_t)r * p.heads + head) * p.splits;
+  float m = -INFINITY;
+  for (int s = 0; s < live; s++) m = fmaxf(m, p.part_ml[(slot0 + s) * 2]);
+  float l = 0.f, o = 0.f;
+  for (int s = 0; s < live; s++) {
+    const float w = __expf(p.part_ml[(slot0 + s) * 2] - m);
+    l += p.part_ml[(slot0 + s) * 2 + 1] * w;
+    if (d < p.head_dim) o += p.part_out[(slot0 + s) * p.head_dim + d] * w;
   }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  for (int i = tid; i < group * p.head_dim; i += DEC_THREADS) {
-    const int head = g * group + i / p.head_dim, d = i % p.head_dim;
-    const size_t slot0 = ((size_t)r * p.heads + head) * p.splits;
-    float m = -INFINITY;
-    for (int sp = 0; sp < live; sp++) m = fmaxf(m, __ldcg(&p.part_ml[(slot0 + sp) * 2]));
-    float l = 0.f, o = 0.f;
-    for (int sp = 0; sp < live; sp++) {
-      const float w = __expf(__ldcg(&p.part_ml[(slot0 + sp) * 2]) - m);
-      l += __ldcg(&p.part_ml[(slot0 + sp) * 2 + 1]) * w;
-      o += __ldcg(&p.part_out[(slot0 + sp) * p.head_dim + d]) * w;
-    }
-    p.out[(size_t)r * p.out_stride + (size_t)head * p.head_dim + d] = __float2bfloat16_rn(o / l);
-  }
+  if (d < p.head_dim) p.out[(size_t)r * p.out_stride + (size_t)head * p.head_dim + d] = __float2bfloat16_rn(o / l);
 }
 
 // =============================================================================== prefill
@@ -487,11 +476,10 @@ SPROUT_API long long sprout_attention_decode_scratch_floats(int requests, int he
 
 // One query token per request.  q, out: [requests, heads * head_dim] (row strides given);
 // context_lens[r] keys are visible to request r.  scratch: float32, at least
-// sprout_attention_decode_scratch_floats(...) long when splits > 1 (may be null when splits == 1);
-// arrivals: requests * kv_heads int32 counters that are zero before the call and zero again after it.
+// sprout_attention_decode_scratch_floats(...) long when splits > 1 (may be null when splits == 1).
 SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                        const int* block_table, int table_stride, const int* context_lens,
-                                       void* out, int out_stride, float* scratch, int* arrivals, int requests, int heads,
+                                       void* out, int out_stride, float* scratch, int requests, int heads,
                                        int kv_heads, int head_dim, int page_tokens, int num_pages, int split_keys,
                                        int splits, int* status, cudaStream_t stream) {
   SPROUT_REQUIRE(requests > 0 && requests <= 65535 && heads > 0 && kv_heads > 0 && page_tokens > 0 && num_pages > 0,
@@ -503,7 +491,7 @@ SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* 
   SPROUT_REQUIRE(split_keys > 0 && split_keys % DEC_THREADS == 0 && splits > 0 && splits <= 65535,
                  "attention_decode: split_keys must be a positive multiple of %d", DEC_THREADS);
   SPROUT_REQUIRE(q && k_cache && v_cache && block_table && context_lens && out && status, "attention_decode: null pointer");
-  SPROUT_REQUIRE(splits == 1 || (scratch && arrivals), "attention_decode: scratch memory and arrival counters are needed for more than one split");
+  SPROUT_REQUIRE(splits == 1 || scratch, "attention_decode: scratch memory is needed for more than one split");
   SPROUT_REQUIRE(q_stride % 2 == 0 && out_stride % 2 == 0 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0,
                  "attention_decode: misaligned operands");
   DecodeParams p;
@@ -513,7 +501,6 @@ SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* 
   p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
   p.part_out = scratch;
   p.part_ml = scratch ? scratch + (size_t)requests * heads * splits * head_dim : nullptr;
-  p.arrivals = arrivals;
   p.heads = heads; p.kv_heads = kv_heads; p.head_dim = head_dim; p.page_tokens = page_tokens; p.num_pages = num_pages;
   p.split_keys = split_keys; p.splits = splits; p.status = status;
   const int group = heads / kv_heads;
@@ -527,7 +514,13 @@ SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* 
     configured = smem;
   }
   sprout_launch(attention_decode_kernel, dim3(splits, kv_heads, requests), dim3(DEC_THREADS), smem, stream, p);
-  return sprout_check_launch("attention_decode");
+  if (sprout_check_launch("attention_decode")) return 1;
+  if (splits > 1) {
+    const int threads = (head_dim + 31) / 32 * 32;
+    sprout_launch(attention_decode_merge_kernel, dim3(heads, requests), dim3(threads), 0, stream, p);
+    return sprout_check_launch("attention_decode_merge");
+  }
+  return 0;
 }
 
 // Portions of prompts (and single tokens) of several requests in one launch.  q_start[r] is the

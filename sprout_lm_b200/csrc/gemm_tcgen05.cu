@@ -131,10 +131,7 @@ struct Layout {
   static constexpr int B_BYTES = BN * BLOCK_K * 2;
   static constexpr int B_PADDED = (B_BYTES + 1023) / 1024 * 1024;
   static constexpr int STAGE_BYTES = A_BYTES + B_PADDED;
-  // small token tiles (decode): half the shared memory, so that two CTAs share an SM and the
-  // next kernel's CTAs can stream their weights while this kernel's still compute
-  static constexpr int BUDGET = BN <= 64 ? SMEM_BUDGET / 2 : SMEM_BUDGET;
-  static constexpr int STAGES = BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) > 12 ? 12 : (SMEM_BUDGET / STAGE_BYTES);
   static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 };

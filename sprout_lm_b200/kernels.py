@@ -34,7 +34,7 @@ _SIGNATURES = {
     "sprout_attention_simple": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_sample": [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P],
     "sprout_advance_decode": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
-    "sprout_attention_decode": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_attention_decode": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_gemm_bf16": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
 }
@@ -274,18 +274,6 @@ def decode_split_plan(requests: int, kv_heads: int, max_keys: int) -> tuple[int,
     return split_keys, max(1, -(-max_keys // split_keys))
 
 
-_arrival_counters: dict = {}
-
-
-def _arrivals(device, count: int):
-    """Per-device int32 counters for the split-key attention's last-arriver merge; the kernel
-    leaves them zero, so one zeroed buffer serves every call."""
-    buffer = _arrival_counters.get(device)
-    if buffer is None or buffer.numel() < count:
-        buffer = _arrival_counters[device] = torch.zeros(max(count, 4096), dtype=torch.int32, device=device)
-    return buffer
-
-
 def attention_decode(q, k_cache, v_cache, block_table, context_lens, out, heads, kv_heads, head_dim, status,
                      split_keys=None, scratch=None):
     """One query token per request over its pages (bfloat16, float32 softmax): keys are split
@@ -305,8 +293,7 @@ def attention_decode(q, k_cache, v_cache, block_table, context_lens, out, heads,
     _run("sprout_attention_decode", _ptr(q, "q"), q.stride(0), _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"),
          _ptr(block_table, "block_table", torch.int32), block_table.stride(0),
          _ptr(context_lens, "context_lens", torch.int32), _ptr(out, "out"), out.stride(0),
-         _ptr(scratch, "scratch", torch.float32, True), _ptr(_arrivals(q.device, R * kv_heads), "arrivals"),
-         R, heads, kv_heads, head_dim, k_cache.shape[2],
+         _ptr(scratch, "scratch", torch.float32, True), R, heads, kv_heads, head_dim, k_cache.shape[2],
          k_cache.shape[0], split_keys, splits, _ptr(status, "status", torch.int32), _stream())
 
 
