@@ -560,3 +560,53 @@ SPROUT_API int sprout_attention_prefill(const void* q, int q_stride, const void*
     default: return sprout_fail("attention_prefill: head_dim must be a multiple of 16 up to 128 (got %d)", head_dim);
   }
 }
+
+// =============================================================================== allocation-free variant
+#include "no_alloc.h"
+
+namespace {
+
+// Partial results of the key splits for callers that cannot hand over scratch memory.  In host
+// code this name stands for the symbol only; the device address comes from cudaGetSymbolAddress.
+static __device__ __align__(256) float g_static_decode_scratch[SPROUT_STATIC_SCRATCH_FLOATS];
+
+constexpr int MAX_DEVICES = 64;
+float* g_static_scratch_address[MAX_DEVICES] = {};
+
+// Device address of the scratch array on the current device, looked up on first use.
+int static_scratch(float** address) {
+  int device = -1;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return sprout_fail("attention_decode_static: cudaGetDevice failed: %s", cudaGetErrorString(err));
+  if (device < 0 || device >= MAX_DEVICES) return sprout_fail("attention_decode_static: device %d out of range", device);
+  if (!g_static_scratch_address[device]) {
+    float* found = nullptr;
+    err = cudaGetSymbolAddress((void**)&found, g_static_decode_scratch);
+    if (err != cudaSuccess || !found)
+      return sprout_fail("attention_decode_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(err));
+    g_static_scratch_address[device] = found;
+  }
+  *address = g_static_scratch_address[device];
+  return 0;
+}
+
+}  // namespace
+
+// See no_alloc.h.  Same computation as sprout_attention_decode with the library's own scratch.
+SPROUT_API int sprout_attention_decode_static(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                              const int* block_table, int table_stride, const int* context_lens,
+                                              void* out, int out_stride, int requests, int heads, int kv_heads,
+                                              int head_dim, int page_tokens, int num_pages, int split_keys,
+                                              int splits, int* status, cudaStream_t stream) {
+  SPROUT_REQUIRE(requests > 0 && heads > 0 && head_dim > 0 && splits > 0, "attention_decode_static: sizes must be positive");
+  const long long need = sprout_attention_decode_scratch_floats(requests, heads, head_dim, splits);
+  SPROUT_REQUIRE(need <= (long long)SPROUT_STATIC_SCRATCH_FLOATS,
+                 "attention_decode_static: %d requests x %d heads x %d splits of head_dim %d need %lld floats of scratch; "
+                 "the built-in array holds %d (use fewer splits or sprout_attention_decode with your own scratch)",
+                 requests, heads, splits, head_dim, need, SPROUT_STATIC_SCRATCH_FLOATS);
+  float* scratch = nullptr;
+  if (static_scratch(&scratch)) return 1;
+  return sprout_attention_decode(q, q_stride, k_cache, v_cache, block_table, table_stride, context_lens, out, out_stride,
+                                 scratch, requests, heads, kv_heads, head_dim, page_tokens, num_pages, split_keys, splits,
+                                 status, stream);
+}
