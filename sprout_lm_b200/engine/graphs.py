@@ -66,16 +66,18 @@ class DecodeGraph:
         """Stage the batch and run the step; the sampled tokens (int32, device)."""
         ctx = self.stage(entries, temperatures, uniforms)
         if self.graph is None:
-            # warm-up outside capture (first-use set-up of kernels), then capture; both really run the
-            # step on this batch, which is harmless: a step recomputes the same cache entries
-            self._forward(ctx)
-            torch.cuda.synchronize()
+            # First use: this call's step runs eagerly (that also does the kernels' first-use
+            # set-up), then the same launches are captured for later calls.  Capturing records
+            # without running, so the step has run exactly once: a mixer that updates
+            # per-request state must not see a step twice.
+            _, tokens = self._forward(ctx)
             before = kernels.LAUNCHES
             graph = torch.cuda.CUDAGraph()
             with guarded_capture(graph):
                 self.logits, self.tokens = self._forward(ctx)
             self.launches = kernels.LAUNCHES - before
             self.graph = graph
+            return tokens
         self.graph.replay()
         return self.tokens
 
