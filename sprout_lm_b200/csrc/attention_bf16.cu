@@ -3,15 +3,22 @@
 // decode  (every request brings one query token): grid (splits, kv_heads, requests).  A CTA
 //   takes a run of `split_keys` keys of one key/value head of one request and serves all the
 //   query heads of that group from one read of the keys and values.  Partial results
-//   (running maximum, sum, unnormalised output) go to scratch memory; a second kernel merges
-//   the splits.  The work of a query does not depend on the batch around it.
+//   (running maximum, sum, unnormalised output) are merged in one of two ways: with up to 8
+//   splits the CTAs of a (request, key/value head) form a thread-block cluster and the first
+//   of them reads the others' partial results through distributed shared memory; with more
+//   splits they go to scratch memory and a second kernel merges them.  The work of a query
+//   does not depend on the batch around it.
 //
 // prefill (portions of prompts, possibly beside single tokens): tensor-core flash attention
 //   (mma.sync m16n8k16, float32 accumulation) over the pages.  The rows of a tile are (token,
 //   query head of one group) pairs, so a short portion still fills the 16-row MMA tiles and
 //   keys/values are read once per group; keys are walked in tiles of 64 with the causal limit
 //   of each row applied inside the tile.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -39,6 +46,7 @@ __device__ __forceinline__ void dec_cp_async16(void* smem, const void* gmem) {
 // pass's key rows' offsets, and the pass's keys and values themselves (copied with cp.async so
 // that all of a pass's loads are in flight at once; rows padded by 16 bytes against bank
 // conflicts).
+template <bool CLUSTER>
 __global__ void __launch_bounds__(DEC_THREADS)
 attention_decode_kernel(const DecodeParams p) {
   extern __shared__ __align__(16) float dsm[];
@@ -51,20 +59,25 @@ attention_decode_kernel(const DecodeParams p) {
   long long* rows = (long long*)(red + MAX_GROUP * 8);            // [DEC_THREADS]
   __nv_bfloat16* sK = (__nv_bfloat16*)(rows + DEC_THREADS);       // [DEC_THREADS][stride]
   __nv_bfloat16* sV = sK + DEC_THREADS * stride;
+  float* part_acc = (float*)(sV + DEC_THREADS * stride);          // [group][head_dim] this CTA's partial output (cluster merge)
+  float* part_ml = part_acc + group * p.head_dim;                  // [group][2] its running maximum and sum
 
   pdl_launch_dependents();
   pdl_wait();
   const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int len = p.context_lens[r];
-  const int begin = split * p.split_keys;
-  if (begin >= len) return;                          // the merge kernel knows which splits exist
-  const int end = min(len, begin + p.split_keys);
+  // independent loads first: the length, this thread's first page, the queries
   const int* table = p.block_table + (size_t)r * p.table_stride;
+  const int begin = split * p.split_keys;
+  const int len = p.context_lens[r];
+  const int first_page = table[min((begin + tid) / p.page_tokens, p.table_stride - 1)];
+  for (int i = tid; i < group * p.head_dim / 2; i += DEC_THREADS) {
+    const float2 f = __bfloat1622float2(*(const __nv_bfloat162*)(p.q + (size_t)r * p.q_stride + (size_t)g * group * p.head_dim + 2 * i));
+    qs[2 * i] = f.x; qs[2 * i + 1] = f.y;
+  }
+  if (!CLUSTER && begin >= len) return;              // the merge kernel knows which splits exist
+  const int end = min(len, begin + p.split_keys);
   const float scale = 1.0f / sqrtf((float)p.head_dim);
-
-  for (int i = tid; i < group * p.head_dim; i += DEC_THREADS)
-    qs[i] = __bfloat162float(p.q[(size_t)r * p.q_stride + (size_t)g * group * p.head_dim + i]);
 
   // warp w accumulates output dims {2*lane, 2*lane+1} (+64 per chunk of 64 dims) of the heads
   // h = w, w + 4, ...
@@ -82,7 +95,7 @@ attention_decode_kernel(const DecodeParams p) {
     bool valid = key < end;
     long long off = -1;
     if (valid) {
-      const int page = table[key / p.page_tokens];
+      const int page = base == begin ? first_page : table[key / p.page_tokens];
       if (page < 0 || page >= p.num_pages) { atomicOr(p.status, SPROUT_STATUS_BAD_PAGE); valid = false; }
       else off = (((long long)page * p.kv_heads + g) * p.page_tokens + key % p.page_tokens) * p.head_dim;
     }
@@ -180,6 +193,51 @@ attention_decode_kernel(const DecodeParams p) {
     }
   }
 
+  if constexpr (CLUSTER) {
+    // every split leaves its partial results in its own shared memory; the cluster's first CTA
+    // reads them all through distributed shared memory and writes the rows out
+    cg::cluster_group cluster = cg::this_cluster();
+#pragma unroll
+    for (int a = 0; a < MAX_GROUP / 4; a++) {
+      const int h = warp + 4 * a;
+      if (h < group) {
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          const int d = c * 64 + 2 * lane;
+          if (d < p.head_dim) { part_acc[h * p.head_dim + d] = acc[a][c][0]; part_acc[h * p.head_dim + d + 1] = acc[a][c][1]; }
+        }
+        if (lane == 0) { part_ml[2 * h] = m_run[a]; part_ml[2 * h + 1] = l_run[a]; }
+      }
+    }
+    cluster.sync();
+    if (cluster.block_rank() == 0) {
+      const int count = (int)cluster.num_blocks();
+      for (int i = tid; i < group * p.head_dim; i += DEC_THREADS) {
+        const int h = i / p.head_dim;
+        float ms[8], ls[8], os[8];
+#pragma unroll
+        for (int sp = 0; sp < 8; sp++) {
+          if (sp < count) {
+            const float* their_ml = cluster.map_shared_rank(part_ml, sp);
+            const float* their_acc = cluster.map_shared_rank(part_acc, sp);
+            ms[sp] = their_ml[2 * h]; ls[sp] = their_ml[2 * h + 1]; os[sp] = their_acc[i];
+          } else { ms[sp] = -INFINITY; ls[sp] = 0.f; os[sp] = 0.f; }
+        }
+        float m = ms[0];
+#pragma unroll
+        for (int sp = 1; sp < 8; sp++) m = fmaxf(m, ms[sp]);
+        float l = 0.f, o = 0.f;
+#pragma unroll
+        for (int sp = 0; sp < 8; sp++) {
+          const float w = ms[sp] == -INFINITY ? 0.f : __expf(ms[sp] - m);
+          l += ls[sp] * w;
+          o += os[sp] * w;
+        }
+        p.out[(size_t)r * p.out_stride + (size_t)(g * group + h) * p.head_dim + (i % p.head_dim)] = __float2bfloat16_rn(o / l);
+      }
+    }
+    cluster.sync();                                  // nobody leaves while its shared memory is being read
+  } else {
 #pragma unroll
   for (int a = 0; a < MAX_GROUP / 4; a++) {
     const int h = warp + 4 * a;
@@ -205,6 +263,7 @@ attention_decode_kernel(const DecodeParams p) {
       }
     }
   }
+  }
 }
 
 // Merge the splits of one (request, head): grid (heads, requests), head_dim threads (rounded up to a warp).
@@ -215,13 +274,28 @@ __global__ void attention_decode_merge_kernel(const DecodeParams p) {
   const int len = p.context_lens[r];
   const int live = min(p.splits, (len + p.split_keys - 1) / p.split_keys);
   const size_t slot0 = ((size_t)r * p.heads + head) * p.splits;
-  float m = -INFINITY;
-  for (int s = 0; s < live; s++) m = fmaxf(m, p.part_ml[(slot0 + s) * 2]);
-  float l = 0.f, o = 0.f;
-  for (int s = 0; s < live; s++) {
-    const float w = __expf(p.part_ml[(slot0 + s) * 2] - m);
-    l += p.part_ml[(slot0 + s) * 2 + 1] * w;
-    if (d < p.head_dim) o += p.part_out[(slot0 + s) * p.head_dim + d] * w;
+  float m = -INFINITY, l = 0.f, o = 0.f;
+  for (int s0 = 0; s0 < live; s0 += 8) {             // eight splits' values in flight at a time
+    float ms[8], ls[8], os[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const bool on = s0 + j < live;
+      ms[j] = on ? p.part_ml[(slot0 + s0 + j) * 2] : -INFINITY;
+      ls[j] = on ? p.part_ml[(slot0 + s0 + j) * 2 + 1] : 0.f;
+      os[j] = (on && d < p.head_dim) ? p.part_out[(slot0 + s0 + j) * p.head_dim + d] : 0.f;
+    }
+    float m_new = m;
+#pragma unroll
+    for (int j = 0; j < 8; j++) m_new = fmaxf(m_new, ms[j]);
+    const float keep = m == -INFINITY ? 0.f : __expf(m - m_new);
+    l *= keep; o *= keep;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const float w = ms[j] == -INFINITY ? 0.f : __expf(ms[j] - m_new);
+      l += ls[j] * w;
+      o += os[j] * w;
+    }
+    m = m_new;
   }
   if (d < p.head_dim) p.out[(size_t)r * p.out_stride + (size_t)head * p.head_dim + d] = __float2bfloat16_rn(o / l);
 }
@@ -476,7 +550,8 @@ SPROUT_API long long sprout_attention_decode_scratch_floats(int requests, int he
 
 // One query token per request.  q, out: [requests, heads * head_dim] (row strides given);
 // context_lens[r] keys are visible to request r.  scratch: float32, at least
-// sprout_attention_decode_scratch_floats(...) long when splits > 1 (may be null when splits == 1).
+// sprout_attention_decode_scratch_floats(...) long; it may be null for up to 8 splits, which are
+// then merged inside a thread-block cluster instead of through memory.
 SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                        const int* block_table, int table_stride, const int* context_lens,
                                        void* out, int out_stride, float* scratch, int requests, int heads,
@@ -491,7 +566,6 @@ SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* 
   SPROUT_REQUIRE(split_keys > 0 && split_keys % DEC_THREADS == 0 && splits > 0 && splits <= 65535,
                  "attention_decode: split_keys must be a positive multiple of %d", DEC_THREADS);
   SPROUT_REQUIRE(q && k_cache && v_cache && block_table && context_lens && out && status, "attention_decode: null pointer");
-  SPROUT_REQUIRE(splits == 1 || scratch, "attention_decode: scratch memory is needed for more than one split");
   SPROUT_REQUIRE(q_stride % 2 == 0 && out_stride % 2 == 0 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0,
                  "attention_decode: misaligned operands");
   DecodeParams p;
@@ -505,15 +579,39 @@ SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* 
   p.split_keys = split_keys; p.splits = splits; p.status = status;
   const int group = heads / kv_heads;
   const size_t smem = (size_t)(group * head_dim + group * DEC_THREADS + MAX_GROUP * 8) * sizeof(float)
-      + DEC_THREADS * sizeof(long long) + (size_t)2 * DEC_THREADS * (head_dim + 8) * sizeof(__nv_bfloat16);
-  static size_t configured = 48 * 1024;
-  if (smem > configured) {
-    cudaError_t err = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      + DEC_THREADS * sizeof(long long) + (size_t)2 * DEC_THREADS * (head_dim + 8) * sizeof(__nv_bfloat16)
+      + (size_t)(group * head_dim + 2 * group) * sizeof(float);
+  // no scratch given and at most 8 splits: the splits of a (request, key/value head) are a cluster
+  const bool cluster = scratch == nullptr && splits > 1 && splits <= 8;
+  SPROUT_REQUIRE(splits == 1 || cluster || scratch, "attention_decode: scratch memory is needed for more than 8 splits");
+  static size_t configured[2] = {48 * 1024, 48 * 1024};
+  if (smem > configured[cluster]) {
+    cudaError_t err = cluster
+        ? cudaFuncSetAttribute(attention_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+        : cudaFuncSetAttribute(attention_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return sprout_fail("attention_decode: group %d with head_dim %d needs %zu bytes of shared memory: %s",
                                                group, head_dim, smem, cudaGetErrorString(err));
-    configured = smem;
+    configured[cluster] = smem;
   }
-  sprout_launch(attention_decode_kernel, dim3(splits, kv_heads, requests), dim3(DEC_THREADS), smem, stream, p);
+  if (cluster) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(splits, kv_heads, requests);
+    config.blockDim = dim3(DEC_THREADS);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2];
+    attributes[0].id = cudaLaunchAttributeClusterDimension;
+    attributes[0].val.clusterDim.x = splits;
+    attributes[0].val.clusterDim.y = 1;
+    attributes[0].val.clusterDim.z = 1;
+    attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attributes;
+    config.numAttrs = sprout_pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&config, attention_decode_kernel<true>, p);
+    return sprout_check_launch("attention_decode (cluster)");
+  }
+  sprout_launch(attention_decode_kernel<false>, dim3(splits, kv_heads, requests), dim3(DEC_THREADS), smem, stream, p);
   if (sprout_check_launch("attention_decode")) return 1;
   if (splits > 1) {
     const int threads = (head_dim + 31) / 32 * 32;

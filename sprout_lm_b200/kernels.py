@@ -265,28 +265,37 @@ def _check_paged(q, k_cache, v_cache, block_table, out, heads, head_dim, name):
 SM_COUNT = 148
 
 
-def decode_split_plan(requests: int, kv_heads: int, max_keys: int) -> tuple[int, int]:
-    """(keys per split, splits) for decode attention over at most ``max_keys`` keys: splits of 128
-    keys, doubled while the grid would exceed eight CTAs per SM."""
+def decode_split_plan(requests: int, kv_heads: int, max_keys: int) -> tuple[int, int, bool]:
+    """(keys per split, splits, whether scratch memory is needed) for decode attention over at
+    most ``max_keys`` keys.  Up to 8 splits are merged inside a thread-block cluster; splits are
+    128 keys, made longer while there would be more than 8 of them, unless the batch is too
+    small to fill the GPU that way, in which case many short splits go through scratch memory."""
     split_keys = 128
-    while requests * kv_heads * (-(-max_keys // split_keys)) > 8 * SM_COUNT and split_keys < max_keys:
-        split_keys *= 2
-    return split_keys, max(1, -(-max_keys // split_keys))
+    while -(-max_keys // split_keys) > 8:
+        split_keys += 128
+    if requests * kv_heads * 8 < SM_COUNT and max_keys > 8 * 128:
+        split_keys = 128
+        while requests * kv_heads * (-(-max_keys // split_keys)) > 4 * SM_COUNT:
+            split_keys *= 2
+    splits = max(1, -(-max_keys // split_keys))
+    return split_keys, splits, splits > 8
 
 
 def attention_decode(q, k_cache, v_cache, block_table, context_lens, out, heads, kv_heads, head_dim, status,
                      split_keys=None, scratch=None):
     """One query token per request over its pages (bfloat16, float32 softmax): keys are split
-    among CTAs, partial results go through float32 scratch memory and are merged."""
+    among CTAs; up to 8 splits merge inside a thread-block cluster, more (or a given
+    ``scratch``) go through float32 scratch memory and a merge kernel."""
     _check_paged(q, k_cache, v_cache, block_table, out, heads, head_dim, "attention_decode")
     R = q.shape[0]
     max_keys = block_table.shape[1] * k_cache.shape[2]
     if split_keys is None:
-        split_keys, splits = decode_split_plan(R, kv_heads, max_keys)
+        split_keys, splits, through_memory = decode_split_plan(R, kv_heads, max_keys)
     else:
         splits = max(1, -(-max_keys // split_keys))
+        through_memory = splits > 8
     need = load_library().sprout_attention_decode_scratch_floats(R, heads, head_dim, splits)
-    if splits > 1 and scratch is None:
+    if through_memory and scratch is None:
         scratch = torch.empty(need, dtype=torch.float32, device=q.device)
     if scratch is not None and (scratch.dtype != torch.float32 or scratch.numel() < need):
         raise KernelError(f"attention_decode: scratch must hold {need} float32 values")
