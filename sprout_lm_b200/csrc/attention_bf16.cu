@@ -22,6 +22,30 @@ namespace cg = cooperative_groups;
 
 namespace {
 
+// =============================================================================== tensor-core helpers
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(smem)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(smem)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *(uint32_t*)&h;
+}
+
 // =============================================================================== decode
 constexpr int DEC_THREADS = 128;      // == keys per pass
 constexpr int MAX_GROUP = 16;         // query heads per key/value head served by one CTA pass
@@ -266,6 +290,243 @@ attention_decode_kernel(const DecodeParams p) {
   }
 }
 
+// Decode attention on tensor cores (head sizes up to 128, up to 16 query heads per key/value
+// head).  The query heads of the group are the 16 rows of an m16n8k16 tile (rows beyond the
+// group are zero); each of the 4 warps takes 32 keys of a 128-key pass: S = Q K^T, running
+// softmax, O += P V, all as mma.sync on keys and values staged in shared memory by cp.async.
+// The warps' partial results are merged through shared memory into the CTA's partial result
+// (maximum, sum, unnormalised output), which then goes the same ways as in the kernel above.
+template <int HD, bool CLUSTER>
+__global__ void __launch_bounds__(DEC_THREADS)
+attention_decode_mma_kernel(const DecodeParams p) {
+  constexpr int STRIDE = HD + 8, CHUNKS = HD / 8;
+  extern __shared__ __align__(16) uint8_t dmm[];
+  __nv_bfloat16* sQ = (__nv_bfloat16*)dmm;            // [16][STRIDE]
+  __nv_bfloat16* sK = sQ + 16 * STRIDE;               // [128][STRIDE]
+  __nv_bfloat16* sV = sK + DEC_THREADS * STRIDE;      // [128][STRIDE]
+  float* part_acc = (float*)(sV + DEC_THREADS * STRIDE);   // [16][HD]
+  float* part_ml = part_acc + 16 * HD;                // [16][2]
+  long long* rows = (long long*)(part_ml + 32);       // [128]
+  float* wO = (float*)sK;                             // [4][16][HD]  (the keys' space, once they are done with)
+  float* wm = wO + 4 * 16 * HD;                       // [4][16]
+  float* wl = wm + 64;                                // [4][16]
+
+  pdl_launch_dependents();
+  pdl_wait();
+  const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int group = p.heads / p.kv_heads;
+  const int* table = p.block_table + (size_t)r * p.table_stride;
+  const int begin = split * p.split_keys;
+  const int len = p.context_lens[r];
+  const int first_page = table[min((begin + tid) / p.page_tokens, p.table_stride - 1)];
+  for (int idx = tid; idx < 16 * CHUNKS; idx += DEC_THREADS) {
+    const int row = idx / CHUNKS, c = idx % CHUNKS;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < group) v = *(const uint4*)(p.q + (size_t)r * p.q_stride + (size_t)(g * group + row) * HD + c * 8);
+    *(uint4*)(sQ + row * STRIDE + c * 8) = v;
+  }
+  if (!CLUSTER && begin >= len) return;
+  const int end = min(len, begin + p.split_keys);
+  const float scale = 1.0f / sqrtf((float)HD);
+
+  const int gr = lane >> 2, qc = lane & 3;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  for (int base = begin; base < end; base += DEC_THREADS) {
+    const int key = base + tid;
+    long long off = -1;
+    if (key < end) {
+      const int page = base == begin ? first_page : table[key / p.page_tokens];
+      if (page < 0 || page >= p.num_pages) atomicOr(p.status, SPROUT_STATUS_BAD_PAGE);
+      else off = (((long long)page * p.kv_heads + g) * p.page_tokens + key % p.page_tokens) * HD;
+    }
+    rows[tid] = off;
+    __syncthreads();                                   // offsets and q visible; the staging buffers are free
+    for (int idx = tid; idx < DEC_THREADS * CHUNKS; idx += DEC_THREADS) {
+      const int row = idx / CHUNKS, c = idx % CHUNKS;
+      const long long ro = rows[row];
+      __nv_bfloat16* dk = sK + row * STRIDE + c * 8;
+      __nv_bfloat16* dv = sV + row * STRIDE + c * 8;
+      if (ro >= 0) { cp_async16(dk, p.k_cache + ro + c * 8); cp_async16(dv, p.v_cache + ro + c * 8); }
+      else { *(uint4*)dk = make_uint4(0, 0, 0, 0); *(uint4*)dv = make_uint4(0, 0, 0, 0); }
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+
+    const int key0 = base + warp * 32;                 // this warp's 32 keys
+    if (key0 < end) {
+      const __nv_bfloat16* wK = sK + warp * 32 * STRIDE;
+      const __nv_bfloat16* wV = sV + warp * 32 * STRIDE;
+      float s[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; kk++) {
+        uint32_t a[4];
+        ldmatrix_x4(a, sQ + ((lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int n2 = 0; n2 < 2; n2++) {
+          uint32_t b[4];
+          ldmatrix_x4(b, wK + (n2 * 16 + (lane & 7) + (lane >> 4) * 8) * STRIDE + kk * 16 + ((lane >> 3) & 1) * 8);
+          mma_bf16(s[2 * n2], a, b[0], b[1]);
+          mma_bf16(s[2 * n2 + 1], a, b[2], b[3]);
+        }
+      }
+      float t0 = -INFINITY, t1 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const int k = key0 + i * 8 + qc * 2;
+        s[i][0] = k < end ? s[i][0] * scale : -INFINITY;
+        s[i][1] = k + 1 < end ? s[i][1] * scale : -INFINITY;
+        s[i][2] = k < end ? s[i][2] * scale : -INFINITY;
+        s[i][3] = k + 1 < end ? s[i][3] * scale : -INFINITY;
+        t0 = fmaxf(t0, fmaxf(s[i][0], s[i][1]));
+        t1 = fmaxf(t1, fmaxf(s[i][2], s[i][3]));
+      }
+      t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 1)); t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 2));
+      t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 1)); t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 2));
+      const float n0 = fmaxf(m0, t0), n1 = fmaxf(m1, t1);       // finite: key0 < end, so every row has a key
+      const float alpha0 = m0 == -INFINITY ? 0.f : __expf(m0 - n0), alpha1 = m1 == -INFINITY ? 0.f : __expf(m1 - n1);
+      m0 = n0; m1 = n1;
+      l0 *= alpha0; l1 *= alpha1;
+#pragma unroll
+      for (int i = 0; i < HD / 8; i++) { o[i][0] *= alpha0; o[i][1] *= alpha0; o[i][2] *= alpha1; o[i][3] *= alpha1; }
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        s[i][0] = __expf(s[i][0] - n0); s[i][1] = __expf(s[i][1] - n0);
+        s[i][2] = __expf(s[i][2] - n1); s[i][3] = __expf(s[i][3] - n1);
+        l0 += s[i][0] + s[i][1];
+        l1 += s[i][2] + s[i][3];
+      }
+#pragma unroll
+      for (int kk = 0; kk < 2; kk++) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int d2 = 0; d2 < HD / 16; d2++) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, wV + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + d2 * 16 + (lane >> 4) * 8);
+          mma_bf16(o[2 * d2], a, b[0], b[1]);
+          mma_bf16(o[2 * d2 + 1], a, b[2], b[3]);
+        }
+      }
+    }
+  }
+
+  // the warps' partial results -> shared memory (over the keys, which are no longer needed)
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  __syncthreads();
+  {
+    float* mine = wO + warp * 16 * HD;
+#pragma unroll
+    for (int i = 0; i < HD / 8; i++) {
+      *(float2*)(mine + gr * HD + i * 8 + qc * 2) = make_float2(o[i][0], o[i][1]);
+      *(float2*)(mine + (gr + 8) * HD + i * 8 + qc * 2) = make_float2(o[i][2], o[i][3]);
+    }
+    if (qc == 0) {
+      wm[warp * 16 + gr] = m0; wm[warp * 16 + gr + 8] = m1;
+      wl[warp * 16 + gr] = l0; wl[warp * 16 + gr + 8] = l1;
+    }
+  }
+  __syncthreads();
+  // merge the 4 warps: the CTA's partial result for every (head, dim)
+  for (int idx = tid; idx < group * HD; idx += DEC_THREADS) {
+    const int row = idx / HD, d = idx % HD;
+    const float a0 = wm[row], a1 = wm[16 + row], a2 = wm[32 + row], a3 = wm[48 + row];
+    const float m = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
+    const float w0 = a0 == -INFINITY ? 0.f : __expf(a0 - m), w1 = a1 == -INFINITY ? 0.f : __expf(a1 - m);
+    const float w2 = a2 == -INFINITY ? 0.f : __expf(a2 - m), w3 = a3 == -INFINITY ? 0.f : __expf(a3 - m);
+    const float l = (wl[row] * w0 + wl[16 + row] * w1) + (wl[32 + row] * w2 + wl[48 + row] * w3);
+    const float acc = (wO[row * HD + d] * w0 + wO[(16 + row) * HD + d] * w1)
+                    + (wO[(32 + row) * HD + d] * w2 + wO[(48 + row) * HD + d] * w3);
+    const int head = g * group + row;
+    if constexpr (CLUSTER) {
+      part_acc[idx] = acc;
+      if (d == 0) { part_ml[2 * row] = m; part_ml[2 * row + 1] = l; }
+    } else if (p.splits == 1) {
+      p.out[(size_t)r * p.out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc / l);
+    } else {
+      const size_t slot = ((size_t)r * p.heads + head) * p.splits + split;
+      p.part_out[slot * HD + d] = acc;
+      if (d == 0) { p.part_ml[slot * 2] = m; p.part_ml[slot * 2 + 1] = l; }
+    }
+  }
+  if constexpr (CLUSTER) {
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    if (cluster.block_rank() == 0) {
+      const int count = (int)cluster.num_blocks();
+      for (int i = tid; i < group * HD; i += DEC_THREADS) {
+        const int h = i / HD;
+        float ms[8], ls[8], os[8];
+#pragma unroll
+        for (int sp = 0; sp < 8; sp++) {
+          if (sp < count) {
+            const float* their_ml = cluster.map_shared_rank(part_ml, sp);
+            const float* their_acc = cluster.map_shared_rank(part_acc, sp);
+            ms[sp] = their_ml[2 * h]; ls[sp] = their_ml[2 * h + 1]; os[sp] = their_acc[i];
+          } else { ms[sp] = -INFINITY; ls[sp] = 0.f; os[sp] = 0.f; }
+        }
+        float m = ms[0];
+#pragma unroll
+        for (int sp = 1; sp < 8; sp++) m = fmaxf(m, ms[sp]);
+        float l = 0.f, acc = 0.f;
+#pragma unroll
+        for (int sp = 0; sp < 8; sp++) {
+          const float w = ms[sp] == -INFINITY ? 0.f : __expf(ms[sp] - m);
+          l += ls[sp] * w;
+          acc += os[sp] * w;
+        }
+        p.out[(size_t)r * p.out_stride + (size_t)(g * group + h) * HD + (i % HD)] = __float2bfloat16_rn(acc / l);
+      }
+    }
+    cluster.sync();                                    // nobody leaves while its shared memory is being read
+  }
+}
+
+template <int HD>
+int launch_decode_mma(const DecodeParams& p, bool cluster, int requests, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)(16 + 2 * DEC_THREADS) * (HD + 8) * 2 + (size_t)(16 * HD + 32) * 4 + DEC_THREADS * 8;
+  static bool configured[2] = {false, false};
+  if (smem > 48 * 1024 && !configured[cluster]) {
+    cudaError_t err = cluster
+        ? cudaFuncSetAttribute(attention_decode_mma_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+        : cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return sprout_fail("attention_decode: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
+    configured[cluster] = true;
+  }
+  const dim3 grid(p.splits, p.kv_heads, requests);
+  if (cluster) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = dim3(DEC_THREADS);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2];
+    attributes[0].id = cudaLaunchAttributeClusterDimension;
+    attributes[0].val.clusterDim.x = p.splits;
+    attributes[0].val.clusterDim.y = 1;
+    attributes[0].val.clusterDim.z = 1;
+    attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attributes;
+    config.numAttrs = sprout_pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&config, attention_decode_mma_kernel<HD, true>, p);
+    return sprout_check_launch("attention_decode (tensor cores, cluster)");
+  }
+  sprout_launch(attention_decode_mma_kernel<HD, false>, grid, dim3(DEC_THREADS), smem, stream, p);
+  return sprout_check_launch("attention_decode (tensor cores)");
+}
+
 // Merge the splits of one (request, head): grid (heads, requests), head_dim threads (rounded up to a warp).
 __global__ void attention_decode_merge_kernel(const DecodeParams p) {
   pdl_launch_dependents();
@@ -314,29 +575,6 @@ struct PrefillParams {
   float scale;
   int* status;
 };
-
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(smem)));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(smem)));
-}
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-  return *(uint32_t*)&h;
-}
 
 template <int HD>
 __global__ void __launch_bounds__(PF_THREADS)
@@ -584,6 +822,20 @@ SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* 
   // no scratch given and at most 8 splits: the splits of a (request, key/value head) are a cluster
   const bool cluster = scratch == nullptr && splits > 1 && splits <= 8;
   SPROUT_REQUIRE(splits == 1 || cluster || scratch, "attention_decode: scratch memory is needed for more than 8 splits");
+  if (head_dim <= 128) {
+    int rc = 1;
+    switch (head_dim) {
+      case 16: rc = launch_decode_mma<16>(p, cluster, requests, stream); break;
+      case 32: rc = launch_decode_mma<32>(p, cluster, requests, stream); break;
+      case 48: rc = launch_decode_mma<48>(p, cluster, requests, stream); break;
+      case 64: rc = launch_decode_mma<64>(p, cluster, requests, stream); break;
+      case 80: rc = launch_decode_mma<80>(p, cluster, requests, stream); break;
+      case 96: rc = launch_decode_mma<96>(p, cluster, requests, stream); break;
+      case 112: rc = launch_decode_mma<112>(p, cluster, requests, stream); break;
+      case 128: rc = launch_decode_mma<128>(p, cluster, requests, stream); break;
+    }
+    if (rc) return rc;
+  } else {
   static size_t configured[2] = {48 * 1024, 48 * 1024};
   if (smem > configured[cluster]) {
     cudaError_t err = cluster
@@ -609,10 +861,13 @@ SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* 
     config.attrs = attributes;
     config.numAttrs = sprout_pdl_enabled() ? 2 : 1;
     cudaLaunchKernelEx(&config, attention_decode_kernel<true>, p);
-    return sprout_check_launch("attention_decode (cluster)");
+    if (sprout_check_launch("attention_decode (cluster)")) return 1;
+  } else {
+    sprout_launch(attention_decode_kernel<false>, dim3(splits, kv_heads, requests), dim3(DEC_THREADS), smem, stream, p);
+    if (sprout_check_launch("attention_decode")) return 1;
   }
-  sprout_launch(attention_decode_kernel<false>, dim3(splits, kv_heads, requests), dim3(DEC_THREADS), smem, stream, p);
-  if (sprout_check_launch("attention_decode")) return 1;
+  }
+  if (cluster) return 0;
   if (splits > 1) {
     const int threads = (head_dim + 31) / 32 * 32;
     sprout_launch(attention_decode_merge_kernel, dim3(heads, requests), dim3(threads), 0, stream, p);
