@@ -26,7 +26,7 @@ class Linear:
     def split_k(self, tokens: int, residual: bool) -> int:
         """How many CTAs share the K range of a small-batch product into a float32 residual:
         enough to put a CTA on most SMs when the matrix has few 128-row tiles."""
-        if not residual or tokens > 128:
+        if not residual or tokens > 256:
             return 1
         tiles = -(-self.out_features // 128)
         k_blocks = -(-self.in_features // 64)
