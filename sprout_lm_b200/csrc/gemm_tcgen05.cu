@@ -6,9 +6,9 @@
 // One CTA computes a 128 x BN tile of D: operand tiles of 64 K-elements (128 bytes, one
 // swizzle row) are staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle)
 // through a ring of stages guarded by mbarriers; one elected thread issues tcgen05.mma with
-// the float32 accumulator in tensor memory; four warps read the accumulator back with
+// the float32 accumulator in tensor memory; eight warps read the accumulator back with
 // tcgen05.ld and apply the epilogue.  Warp 0 produces (TMA), warp 1 issues MMAs and owns the
-// TMEM allocation, warps 2-5 run the epilogue.
+// TMEM allocation, warps 2-9 run the epilogue (two per 32-lane quarter of tensor memory).
 //
 // Two orientations share the pipeline:
 //   tokens on M (prefill): D rows are tokens, D columns output features; BN = 256 where that
@@ -33,7 +33,7 @@ namespace {
 constexpr int BLOCK_M = 128;        // rows of D per CTA == TMEM lanes
 constexpr int BLOCK_K = 64;         // bf16 elements per stage row: 128 bytes, one swizzle row
 constexpr int UMMA_K = 16;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;      // TMA warp, MMA warp, 8 epilogue warps
 constexpr uint32_t WAIT_LIMIT = 1u << 22;   // tries of mbarrier.try_wait (each blocks for a while)
 constexpr int SMEM_BUDGET = 200 * 1024;
 
@@ -42,7 +42,7 @@ enum Epilogue : int { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_RESIDUAL_ATOMIC = 2, 
 // SwiGLU epilogue: the weight rows interleave gate and up in blocks of 8 (rows 16b..16b+7 gate,
 // 16b+8..16b+15 up), so output feature 8b+j is silu(D[.., 16b+j]) * D[.., 16b+8+j]; the output
 // has N/2 features and is bfloat16.
-__device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + __expf(-g))) * u; }
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
 struct Params {
   const float* bias;     // [N] or null
@@ -185,7 +185,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+    for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -264,6 +264,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     // ---------------- epilogue: TMEM -> registers -> global
     pdl_wait();                         // the epilogue reads and writes `out`
     const int quarter = warp & 3;       // a warp reads TMEM lanes 32 * (warp % 4) ..
+    const int half = (warp - 2) >> 2;   // two warps per lane quarter take alternate 16-column chunks
     int tiles_done = 0;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x, tiles_done++) {
       const Work k = work_at(w);
@@ -278,7 +279,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
       const bool first_split = k.split == 0;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
+      for (int c = half * 16; c < BN; c += 32) {
         uint32_t raw[16];
         tmem_load16(taddr + c, raw);
         if (SWAP) {
