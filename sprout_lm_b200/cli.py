@@ -70,7 +70,7 @@ def run_demo(args) -> int:
         iterations += 1
         if iterations > 2000:
             raise RuntimeError("Demo did not converge.")
-        report = engine.step()
+        report = engine.step().resolve()      # take the page snapshot now, before the next tick changes it
         reports.append(report)
         if not args.json:
             memory = report["memory"]

@@ -16,7 +16,7 @@ import gc
 import torch
 
 from .. import kernels
-from .batch import BatchStager
+from .batch import StepContext
 
 
 @contextlib.contextmanager
@@ -40,27 +40,111 @@ def _round_up(value: int, multiple: int) -> int:
 
 
 class DecodeGraph:
-    """One captured decode step for ``requests`` requests and block tables ``table_pages`` wide."""
+    """One captured decode step for ``requests`` requests and block tables ``table_pages`` wide.
+
+    The step's arrays live in one device buffer with a fixed layout, mirrored by one pinned host
+    buffer that is updated in place: token ids, positions and lengths every step, block-table
+    cells only where a request's table grew (or wholly, when the requests of the step changed)."""
 
     def __init__(self, runner, requests: int, table_pages: int):
         self.runner = runner
-        self.requests = requests
+        self.requests = R = requests
         self.table_pages = table_pages
-        self.stager = BatchStager(runner.runtime.device, len(runner.manager.groups))
+        self.groups = len(runner.manager.groups)
+        device = runner.runtime.device
+        sizes = [("token_ids", R), ("positions", R), ("seq_of_token", R), ("q_start", R + 1), ("context_lens", R),
+                 ("state_slots", R), ("logits_rows", R), ("temperature", R), ("uniform", R)]
+        sizes += [(f"table{g}", R * table_pages) for g in range(self.groups)]
+        self.offsets, at = {}, 0
+        for name, n in sizes:
+            self.offsets[name] = (at, n)
+            at += (n + 3) & ~3
+        self.total = at
+        self.host = torch.zeros(at, dtype=torch.int32).pin_memory()
+        self.array = self.host.numpy()
+        self.floats = self.array.view("float32")
+        self.device_buf = torch.zeros(at, dtype=torch.int32, device=device)
+        self.copied = None
+        self.last_bytes = at * 4
+        put = self._put
+        put("seq_of_token", range(R))
+        put("q_start", range(R + 1))
+        put("logits_rows", range(R))
+        for g in range(self.groups):
+            put(f"table{g}", [-1] * (R * table_pages))
+        view = self._view
+        self.ctx = StepContext(
+            num_tokens=R, num_seqs=R, max_q_len=1, max_context=table_pages * runner.page_tokens,
+            token_ids=view("token_ids"), positions=view("positions"), seq_of_token=view("seq_of_token"),
+            q_start=view("q_start"), context_lens=view("context_lens"), state_slots=view("state_slots"),
+            logits_rows=view("logits_rows"),
+            block_tables=[view(f"table{g}").view(R, table_pages) for g in range(self.groups)],
+            page_tokens=runner.page_tokens,
+            floats={"temperature": view("temperature").view(torch.float32), "uniform": view("uniform").view(torch.float32)})
+        self._seqs = None
+        self._known = None                # pages of each request's tables already in the host mirror
         self.graph = None
         self.tokens = None
         self.logits = None
         self.launches = 0
+
+    def _put(self, name, values):
+        at, n = self.offsets[name]
+        self.array[at:at + n] = values
+
+    def _view(self, name):
+        at, n = self.offsets[name]
+        return self.device_buf[at:at + n]
+
+    @property
+    def stager(self):                     # the bytes of the last copy, for the runner's statistics
+        return self
+
+    def stage(self, entries, temperatures, uniforms) -> StepContext:
+        if self.copied is not None:
+            self.copied.synchronize()     # the previous copy has read the host buffer
+        R, P = self.requests, self.table_pages
+        lengths = [e.seq.length for e in entries]
+        self._put("token_ids", [e.tokens[0] for e in entries])
+        self._put("positions", lengths)
+        self._put("context_lens", [n + 1 for n in lengths])
+        at, n = self.offsets["temperature"]
+        self.floats[at:at + n] = temperatures
+        at, n = self.offsets["uniform"]
+        self.floats[at:at + n] = uniforms
+        same = self._seqs is not None and all(e.seq is s for e, s in zip(entries, self._seqs))
+        if not same:
+            self._seqs = [e.seq for e in entries]
+            self._known = [[0] * R for _ in range(self.groups)]
+            self._put("state_slots", [e.seq.state_slot for e in entries])
+            for g in range(self.groups):
+                self._put(f"table{g}", [-1] * (R * P))
+        for g in range(self.groups):
+            base = self.offsets[f"table{g}"][0]
+            known = self._known[g]
+            for i, e in enumerate(entries):
+                pages = e.seq.tables[g]
+                count = len(pages)
+                if count > P:
+                    raise ValueError("block table longer than the graph's table width")
+                if count != known[i] or not same:
+                    # window groups rewrite cells that were given back (-1): take the whole row then
+                    lo = 0 if self.runner.manager.groups[g].kind == "window" else known[i]
+                    self.array[base + i * P + lo:base + i * P + count] = pages[lo:]
+                    known[i] = count
+                elif self.runner.manager.groups[g].kind == "window":
+                    self.array[base + i * P:base + i * P + count] = pages
+        self.device_buf.copy_(self.host, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self.copied = event
+        return self.ctx
 
     def _forward(self, ctx):
         logits = self.runner.model.forward(ctx, self.runner.storage)
         tokens = torch.empty(self.requests, dtype=torch.int32, device=logits.device)
         kernels.sample(logits, tokens, self.runner.runtime.status, ctx.floats["temperature"], ctx.floats["uniform"])
         return logits, tokens
-
-    def stage(self, entries, temperatures, uniforms):
-        return self.stager.stage(entries, self.runner.page_tokens, fixed_pages=self.table_pages,
-                                 floats={"temperature": temperatures, "uniform": uniforms})
 
     def run(self, entries, temperatures, uniforms) -> torch.Tensor:
         """Stage the batch and run the step; the sampled tokens (int32, device)."""
@@ -83,7 +167,7 @@ class DecodeGraph:
 
 
 class GraphCache:
-    def __init__(self, runner, page_multiple: int = 8):
+    def __init__(self, runner, page_multiple: int = 64):
         self.runner = runner
         self.page_multiple = page_multiple
         self.graphs: dict = {}

@@ -59,6 +59,39 @@ class Request:
     finish_reason: str | None = None
 
 
+class StepReport(dict):
+    """What a step did: ``tick``, ``work``, ``events`` and ``memory`` (the page accounting after
+    the step, src/engine.ts:189).  ``memory`` lists every page, so it is taken when the step ends
+    only if someone reads it."""
+
+    def __init__(self, tick, work, events, cache):
+        super().__init__(tick=tick, work=work, events=events)
+        self._cache = cache
+
+    def __missing__(self, key):
+        if key == "memory":
+            self["memory"] = self._cache.snapshot()
+            return self["memory"]
+        raise KeyError(key)
+
+    def resolve(self) -> "StepReport":
+        """Take the memory snapshot now (before the next step changes the pages)."""
+        self["memory"]
+        return self
+
+    def keys(self):
+        self.resolve()
+        return super().keys()
+
+    def __iter__(self):
+        self.resolve()
+        return super().__iter__()
+
+    def items(self):
+        self.resolve()
+        return super().items()
+
+
 def uniform_for(seed: int, request_id: str, index: int) -> float:
     """The uniform number in [0, 1) that draws output token ``index`` of a request: a function of
     (seed, request id, index) alone, so batching, chunking and recomputation cannot change it."""
@@ -206,7 +239,7 @@ class Engine:
                     row += 1
                 work.append({"id": request.id, "phase": phase, "from": start, "tokens": len(tokens),
                              "blockTable": table})
-        return {"tick": self._tick, "work": work, "events": events, "memory": self.cache.snapshot()}
+        return StepReport(tick=self._tick, work=work, events=events, cache=self.cache)
 
     def _accept(self, request: Request, token: int) -> None:
         request.output.append(token)
