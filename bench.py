@@ -191,6 +191,73 @@ def timed_decode(runner, batch: int, prompt_len: int, steps: int, warmup: int, r
             "mean_context": mean_context, "clocks": clocks}
 
 
+def ablation(model, batch: int, prompt_len: int, steps: int, warmup: int) -> dict:
+    """Marginal cost of each kind of kernel in the decode step: the step is captured and timed
+    with one kind replaced by a no-op (its outputs are then garbage; only the time is used).
+    Shows where the step's time goes under the real launch pipeline, warm caches included."""
+    import numpy as np
+    import torch
+    from sprout_lm_b200 import kernels
+    from sprout_lm_b200.engine.batch import StepEntry
+    from sprout_lm_b200.engine.step import ModelRunner
+    real = {name: getattr(kernels, name) for name in ("attention_decode", "rmsnorm", "rope_append", "gemm_bf16", "sample")}
+    gemm = real["gemm_bf16"]
+    hidden, inter = model.spec.hidden_size, model.blocks[0].feed_forward.intermediate_size
+    qkv_rows = model.blocks[0].mixer.qkv.out_features
+
+    def gemm_without(skip):
+        def call(a, w, out, status, **kw):
+            return None if skip(w, kw) else gemm(a, w, out, status, **kw)
+        return call
+
+    variants = {
+        "baseline": {},
+        "attention": {"attention_decode": lambda *a, **k: None},
+        "rmsnorm": {"rmsnorm": lambda *a, **k: None},
+        "rope_append": {"rope_append": lambda *a, **k: None},
+        "gemm_qkv": {"gemm_bf16": gemm_without(lambda w, kw: w.shape[0] == qkv_rows)},
+        "gemm_o": {"gemm_bf16": gemm_without(lambda w, kw: tuple(w.shape) == (hidden, hidden))},
+        "gemm_gate_up": {"gemm_bf16": gemm_without(lambda w, kw: bool(kw.get("swiglu")))},
+        "gemm_down": {"gemm_bf16": gemm_without(lambda w, kw: tuple(w.shape) == (hidden, inter))},
+        "gemm_lm_head": {"gemm_bf16": gemm_without(lambda w, kw: w.shape[0] == model.spec.vocab_size)},
+        "sample": {"sample": lambda *a, **k: None},
+        "all_gemms": {"gemm_bf16": lambda *a, **k: None},
+    }
+    out = {}
+    for label, patches in variants.items():
+        rng = np.random.default_rng(0)
+        runner = ModelRunner(model, num_pages=batch * (-(-(prompt_len + steps + warmup + 16) // 16)) + 16, page_tokens=16,
+                             max_requests=max(batch, 1), prefix_caching=False)
+        seqs = []
+        for _ in range(batch):
+            seq = runner.new_sequence()
+            assert runner.reserve(seq, prompt_len)
+            seqs.append(seq)
+        first = []
+        for at in range(0, batch, 8):
+            entries = [StepEntry(s, [int(t) for t in rng.integers(0, 1000, prompt_len)], [prompt_len - 1]) for s in seqs[at:at + 8]]
+            first += runner.step_and_sample(entries, [0.0] * len(entries), [0.0] * len(entries))
+        for name, fn in patches.items():
+            setattr(kernels, name, fn)
+        try:
+            loop = runner.decode_loop([StepEntry(s, [t], [0]) for s, t in zip(seqs, first)], [0.0] * batch, [0.0] * batch,
+                                      max_steps=steps + warmup + 2)
+            loop.run(warmup)
+            torch.cuda.synchronize()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            loop.run(steps)
+            end.record()
+            torch.cuda.synchronize()
+        finally:
+            for name, fn in real.items():
+                setattr(kernels, name, fn)
+        runner.runtime.status.zero_()
+        out[label] = round(begin.elapsed_time(end) / steps * 1000, 1)
+    base = out["baseline"]
+    return {"us_per_step": base, "saved_us_without": {k: round(base - v, 1) for k, v in out.items() if k != "baseline"}}
+
+
 def timed_e2e(model, batch: int, prompt_len: int, steps: int, warmup: int, rng):
     """The same workload through Engine.step: host token ids in, host token ids out, every step."""
     import torch
@@ -261,6 +328,9 @@ def run(args) -> dict:
     pages = 64 * (-(-(prompt_len + args.steps + args.warmup + 16) // 16)) + 2048 // 16 + 16
     runner = ModelRunner(model, num_pages=pages, page_tokens=16, max_requests=64, prefix_caching=False)
 
+    if args.only == "ablate":
+        return {"impl": "ours", "only": "ablate", "layers": layers, "batch": batch,
+                **ablation(model, batch, prompt_len, min(args.steps, 60), args.warmup)}
     if args.only == "prefill":
         prefill_ms = timed_prefill(runner, 2048, rng, repeats=1)
         return {"impl": "ours", "only": "prefill", "layers": layers, "ms": round(prefill_ms, 4)}
@@ -308,7 +378,7 @@ def main() -> int:
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
-    parser.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
+    parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate"], default="all",
                         help="measure one part only (for profiling captures); the JSON line then holds that part")
     args = parser.parse_args()
     if args.impl == "reference":
