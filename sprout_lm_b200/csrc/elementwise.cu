@@ -162,8 +162,12 @@ SPROUT_API int sprout_swiglu(const void* gate_up, void* out, int dtype, int toke
 //   element ((page * kv_heads + head) * page_tokens + slot) * head_dim + d.
 // cos/sin come from float32 tables [max_positions, head_dim/2] that the host fills from
 // float64 angles.  A page id outside the pool sets a status bit and skips the write.
+// With `acc` given, the projections come from there instead: float32 sums [tokens, width] that a
+// split-K product accumulated, to which `bias` is added here; q is then written (rotated) to
+// qkv, and every element of acc that was read is set back to zero for the next product.
 template <typename T>
-__global__ void rope_append_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+__global__ void rope_append_kernel(T* __restrict__ qkv, float* acc, const float* __restrict__ bias,
+                                   const int* __restrict__ positions,
                                    const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
                                    int table_stride, const float* __restrict__ cos_table,
                                    const float* __restrict__ sin_table, int max_positions,
@@ -192,35 +196,44 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const int* __restrict__ 
     page_ok = page >= 0 && page < num_pages;
     if (!page_ok && threadIdx.x == 0) atomicOr(status, SPROUT_STATUS_BAD_PAGE);
   }
+  float* acc_row = acc ? acc + (size_t)t * width : nullptr;
+  auto value = [&](int i) -> float {
+    if (!acc_row) return to_float(row[i]);
+    const float v = acc_row[i] + (bias ? bias[i] : 0.f);
+    acc_row[i] = 0.f;
+    return v;
+  };
   // one thread per rotated pair: q heads in place, k heads into the cache
   for (int i = threadIdx.x; i < (heads + kv_heads) * half; i += blockDim.x) {
     const int h = i / half, d = i % half;
     const float c = rotate ? cs[d] : 1.f, s = rotate ? sn[d] : 0.f;
     if (h < heads) {
-      if (!rotate) continue;
+      if (!rotate && !acc_row) continue;
+      const float a = value(h * head_dim + d), b = value(h * head_dim + d + half);
       T* x = row + h * head_dim;
-      const float a = to_float(x[d]), b = to_float(x[d + half]);
       x[d] = from_float<T>(a * c - b * s);
       x[d + half] = from_float<T>(b * c + a * s);
-    } else if (page_ok) {
+    } else {
       const int kh = h - heads;
-      const T* x = row + h * head_dim;
-      const float a = to_float(x[d]), b = to_float(x[d + half]);
-      T* dst = k_cache + (((size_t)page * kv_heads + kh) * page_tokens + slot) * head_dim;
-      dst[d] = from_float<T>(a * c - b * s);
-      dst[d + half] = from_float<T>(b * c + a * s);
+      const float a = value(h * head_dim + d), b = value(h * head_dim + d + half);
+      if (page_ok) {
+        T* dst = k_cache + (((size_t)page * kv_heads + kh) * page_tokens + slot) * head_dim;
+        dst[d] = from_float<T>(a * c - b * s);
+        dst[d + half] = from_float<T>(b * c + a * s);
+      }
     }
   }
-  if (page_ok) {
-    const T* v_row = row + (heads + kv_heads) * head_dim;
+  if (page_ok || acc_row) {
+    const int v0 = (heads + kv_heads) * head_dim;
     for (int i = threadIdx.x; i < kv_heads * head_dim; i += blockDim.x) {
       const int h = i / head_dim, d = i % head_dim;
-      v_cache[(((size_t)page * kv_heads + h) * page_tokens + slot) * head_dim + d] = v_row[i];
+      const T v = acc_row ? from_float<T>(value(v0 + i)) : row[v0 + i];
+      if (page_ok) v_cache[(((size_t)page * kv_heads + h) * page_tokens + slot) * head_dim + d] = v;
     }
   }
 }
 
-SPROUT_API int sprout_rope_append(void* qkv, int dtype, const int* positions, const int* seq_of_token,
+SPROUT_API int sprout_rope_append(void* qkv, float* acc, const float* bias, int dtype, const int* positions, const int* seq_of_token,
                                   const int* block_table, int table_stride, const float* cos_table,
                                   const float* sin_table, int max_positions, void* k_cache, void* v_cache,
                                   int num_tokens, int heads, int kv_heads, int head_dim, int page_tokens,
@@ -234,12 +247,12 @@ SPROUT_API int sprout_rope_append(void* qkv, int dtype, const int* positions, co
   const int pairs = (heads + kv_heads) * (head_dim / 2);
   const int threads = pairs >= 1024 ? 1024 : (pairs + 31) / 32 * 32;
   if (dtype == SPROUT_F32)
-    sprout_launch(rope_append_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream, 
-        (float*)qkv, positions, seq_of_token, block_table, table_stride, cos_table, sin_table, max_positions,
+    sprout_launch(rope_append_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream,
+        (float*)qkv, acc, bias, positions, seq_of_token, block_table, table_stride, cos_table, sin_table, max_positions,
         (float*)k_cache, (float*)v_cache, heads, kv_heads, head_dim, page_tokens, num_pages, write_cache, status);
   else if (dtype == SPROUT_BF16)
-    sprout_launch(rope_append_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, stream, 
-        (__nv_bfloat16*)qkv, positions, seq_of_token, block_table, table_stride, cos_table, sin_table,
+    sprout_launch(rope_append_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, stream,
+        (__nv_bfloat16*)qkv, acc, bias, positions, seq_of_token, block_table, table_stride, cos_table, sin_table,
         max_positions, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, heads, kv_heads, head_dim, page_tokens,
         num_pages, write_cache, status);
   else

@@ -29,7 +29,7 @@ _SIGNATURES = {
     "sprout_embed": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
     "sprout_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
     "sprout_swiglu": [_P, _P, _I, _I, _I, _P],
-    "sprout_rope_append": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_rope_append": [_P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_gemm_simple": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "sprout_attention_simple": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_sample": [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P],
@@ -152,10 +152,12 @@ def swiglu(gate_up, out):
 
 
 def rope_append(qkv, positions, seq_of_token, block_table, cos_table, sin_table, k_cache, v_cache,
-                heads, kv_heads, head_dim, page_tokens, write_cache, status):
+                heads, kv_heads, head_dim, page_tokens, write_cache, status, acc=None, bias=None):
     """Rotate q and k of every token by its position; store rotated k and v in the paged cache.
 
-    k_cache and v_cache are [pages, kv_heads, page_tokens, head_dim]."""
+    k_cache and v_cache are [pages, kv_heads, page_tokens, head_dim].  With ``acc`` (float32
+    [tokens, width], row stride = width) the projections are read from there plus ``bias``
+    instead of from ``qkv``, which then receives the rotated q; ``acc`` is left zeroed."""
     T = qkv.shape[0]
     if not qkv.is_contiguous() or qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:
         raise KernelError("rope_append: qkv must be contiguous [tokens, (heads + 2 kv_heads) * head_dim]")
@@ -173,7 +175,13 @@ def rope_append(qkv, positions, seq_of_token, block_table, cos_table, sin_table,
                 raise KernelError(f"rope_append: {name} must be contiguous [pages, kv_heads, page_tokens, head_dim] of {qkv.dtype}")
         num_pages = k_cache.shape[0]
     _rows_contiguous(block_table, "block_table")
-    _run("sprout_rope_append", _ptr(qkv, "qkv"), _dtype_code(qkv.dtype), _ptr(positions, "positions", torch.int32),
+    if acc is not None and (acc.dtype != torch.float32 or acc.dim() != 2 or acc.shape[0] < T
+                            or acc.shape[1] != qkv.shape[1] or not acc.is_contiguous()):
+        raise KernelError("rope_append: acc must be contiguous float32 [>= tokens, width]")
+    if bias is not None and (acc is None or bias.numel() != qkv.shape[1]):
+        raise KernelError("rope_append: a bias goes with acc and has one entry per column")
+    _run("sprout_rope_append", _ptr(qkv, "qkv"), _ptr(acc, "acc", torch.float32, True),
+         _ptr(bias, "bias", torch.float32, True), _dtype_code(qkv.dtype), _ptr(positions, "positions", torch.int32),
          _ptr(seq_of_token, "seq_of_token", torch.int32), _ptr(block_table, "block_table", torch.int32),
          block_table.stride(0), _ptr(cos_table, "cos", torch.float32, True), _ptr(sin_table, "sin", torch.float32, True),
          cos_table.shape[0] if cos_table is not None else 0, _ptr(k_cache, "k_cache", allow_none=not write_cache),

@@ -122,6 +122,20 @@ def test_rope_append(status, dtype, heads, kv_heads, head_dim, page, theta):
         assert torch.equal(got_v, original[t, (heads + kv_heads) * head_dim:])
     # nothing else was touched
     assert int((k_cache != 0).any(-1).any(1).sum().item()) == T
+    # the same from float32 sums plus a bias (what a split-K product leaves): same rotation, the
+    # rotated q lands in qkv, the sums are cleared
+    bias = rand(width, seed=9)
+    acc = torch.zeros(T + 2, width, device=DEV)
+    acc[:T] = original.float() - bias
+    out_q = torch.zeros_like(original)
+    k2, v2 = torch.zeros_like(k_cache), torch.zeros_like(v_cache)
+    kernels.rope_append(out_q, positions.to(DEV), seq_of_token.to(DEV), table.to(DEV), cos, sin, k2, v2,
+                        heads, kv_heads, head_dim, page, True, status, acc=acc[:T], bias=bias)
+    slack = 1e-5 if dtype == torch.float32 else 2e-2
+    assert (out_q[:, :heads * head_dim].float() - qkv[:, :heads * head_dim].float()).abs().max().item() <= slack
+    assert (k2.float() - k_cache.float()).abs().max().item() <= slack
+    assert (v2.float() - v_cache.float()).abs().max().item() <= slack
+    assert float(acc.abs().max()) == 0.0
     # a page id outside the pool is flagged and skipped
     bad = table.clone()
     bad[0, 0] = pages + 3
