@@ -520,7 +520,6 @@ int launch_decode_mma(const DecodeParams& p, bool cluster, int requests, cudaStr
     attributes[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attributes;
     config.numAttrs = sprout_pdl_enabled() ? 2 : 1;
-    sprout_prefer_max_shared((const void*)attention_decode_mma_kernel<HD, true>);
     cudaLaunchKernelEx(&config, attention_decode_mma_kernel<HD, true>, p);
     return sprout_check_launch("attention_decode (tensor cores, cluster)");
   }
@@ -861,7 +860,6 @@ SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* 
     attributes[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attributes;
     config.numAttrs = sprout_pdl_enabled() ? 2 : 1;
-    sprout_prefer_max_shared((const void*)attention_decode_kernel<true>);
     cudaLaunchKernelEx(&config, attention_decode_kernel<true>, p);
     if (sprout_check_launch("attention_decode (cluster)")) return 1;
   } else {

@@ -40,14 +40,9 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 
 int sprout_pdl_enabled();
 
-// Every kernel asks for the same split of the SM's L1 / shared memory (all of it shared), so that
-// an SM never has to drain and re-partition between a small kernel and a GEMM that needs 200 KB.
-void sprout_prefer_max_shared(const void* kernel);
-
 template <typename... KArgs, typename... Args>
 inline cudaError_t sprout_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                  Args&&... args) {
-  sprout_prefer_max_shared((const void*)kernel);
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;

@@ -140,35 +140,6 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
   }
 }
 
-// The same from float32 sums that a split-K product accumulated ([tokens, 2 * inter], gate and
-// up interleaved in blocks of 8): out = silu(gate) * up in bfloat16, and the sums are set back
-// to zero for the next product.
-__global__ void swiglu_acc_kernel(float* __restrict__ acc, __nv_bfloat16* __restrict__ out, int tokens, int inter) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const size_t quads = (size_t)tokens * inter / 4;     // four outputs per thread: one float4 of gate, one of up
-  for (size_t q = (size_t)blockIdx.x * blockDim.x + threadIdx.x; q < quads; q += (size_t)gridDim.x * blockDim.x) {
-    const size_t first = q * 4;
-    const int t = (int)(first / inter), i = (int)(first % inter);
-    float* row = acc + (size_t)t * 2 * inter + (i >> 3) * 16 + (i & 7);
-    const float4 g = *(float4*)row, u = *(float4*)(row + 8);
-    *(float4*)row = make_float4(0.f, 0.f, 0.f, 0.f);
-    *(float4*)(row + 8) = make_float4(0.f, 0.f, 0.f, 0.f);
-    __nv_bfloat162 lo = __floats2bfloat162_rn(__fdividef(g.x, 1.0f + __expf(-g.x)) * u.x, __fdividef(g.y, 1.0f + __expf(-g.y)) * u.y);
-    __nv_bfloat162 hi = __floats2bfloat162_rn(__fdividef(g.z, 1.0f + __expf(-g.z)) * u.z, __fdividef(g.w, 1.0f + __expf(-g.w)) * u.w);
-    *(uint2*)(out + first) = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
-  }
-}
-
-SPROUT_API int sprout_swiglu_acc(float* acc, void* out, int tokens, int inter, cudaStream_t stream) {
-  SPROUT_REQUIRE(tokens > 0 && inter > 0 && inter % 8 == 0, "swiglu_acc: the intermediate size must be a positive multiple of 8 (got %d)", inter);
-  SPROUT_REQUIRE(acc && out && ((uintptr_t)acc & 15) == 0 && ((uintptr_t)out & 7) == 0, "swiglu_acc: null or misaligned pointer");
-  const size_t quads = (size_t)tokens * inter / 4;
-  const int blocks = (int)((quads + 255) / 256 < 148 * 8 ? (quads + 255) / 256 : 148 * 8);
-  sprout_launch(swiglu_acc_kernel, dim3(blocks), dim3(256), 0, stream, acc, (__nv_bfloat16*)out, tokens, inter);
-  return sprout_check_launch("swiglu_acc");
-}
-
 SPROUT_API int sprout_swiglu(const void* gate_up, void* out, int dtype, int tokens, int inter, cudaStream_t stream) {
   SPROUT_REQUIRE(tokens > 0 && inter > 0, "swiglu: sizes must be positive");
   SPROUT_REQUIRE(inter % 8 == 0, "swiglu: the intermediate size must be a multiple of 8 (got %d)", inter);

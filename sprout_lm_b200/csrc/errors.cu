@@ -26,17 +26,6 @@ int sprout_check_launch(const char* what) {
 // Text of the last failure on the calling thread.
 SPROUT_API const char* sprout_last_error() { return g_error; }
 
-#include <mutex>
-#include <unordered_set>
-
-void sprout_prefer_max_shared(const void* kernel) {
-  static std::unordered_set<const void*> done;
-  static std::mutex lock;
-  std::lock_guard<std::mutex> guard(lock);
-  if (done.insert(kernel).second)
-    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-}
-
 static int g_pdl = 1;
 int sprout_pdl_enabled() { return g_pdl; }
 // Turn programmatic dependent launch on (default) or off for all later launches.

@@ -183,10 +183,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
   };
 
   pdl_launch_dependents();
-  if (threadIdx.x == 32) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_rows) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_cols) : "memory");
-  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }

@@ -29,7 +29,6 @@ _SIGNATURES = {
     "sprout_embed": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
     "sprout_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
     "sprout_swiglu": [_P, _P, _I, _I, _I, _P],
-    "sprout_swiglu_acc": [_P, _P, _I, _I, _P],
     "sprout_rope_append": [_P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_gemm_simple": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "sprout_attention_simple": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
@@ -150,16 +149,6 @@ def swiglu(gate_up, out):
     if tuple(gate_up.shape) != (T, 2 * I):
         raise KernelError("swiglu: gate_up must be [tokens, 2 * intermediate]")
     _run("sprout_swiglu", _ptr(gate_up, "gate_up"), _ptr(out, "out"), _dtype_code(out.dtype), T, I, _stream())
-
-
-def swiglu_acc(acc, out):
-    """out = silu(gate) * up (bfloat16) from float32 sums [tokens, 2 * intermediate] with gate and
-    up interleaved in blocks of 8; the sums are left zeroed."""
-    T, I = out.shape
-    if acc.dtype != torch.float32 or out.dtype != torch.bfloat16 or tuple(acc.shape) != (T, 2 * I) \
-            or not acc.is_contiguous() or not out.is_contiguous():
-        raise KernelError("swiglu_acc: acc must be contiguous float32 [tokens, 2 * intermediate], out bfloat16 [tokens, intermediate]")
-    _run("sprout_swiglu_acc", _ptr(acc, "acc"), _ptr(out, "out"), T, I, _stream())
 
 
 def rope_append(qkv, positions, seq_of_token, block_table, cos_table, sin_table, k_cache, v_cache,

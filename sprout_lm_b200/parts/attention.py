@@ -12,7 +12,10 @@ import torch
 from .. import kernels
 from ..config.specs import PartSpec
 from .base import CacheSpec, CacheView, Part, TensorDecl, WeightSource, build_part, register_part
-from .linear import SPLIT_TOKENS, Linear, split_workspace
+from .linear import Linear
+
+
+_WORKSPACES: dict = {}
 
 
 @register_part("mixer", "gqa_attention")
@@ -68,14 +71,27 @@ class PagedGQAttention(Part):
         self.tables = self.position.rotary_tables(source.runtime)
 
     # ---- the step
+    SPLIT_TOKENS = 256          # up to this many tokens the q/k/v product is split along K
+
+    def _workspace(self, device):
+        """A zeroed float32 buffer [SPLIT_TOKENS, width] that split-K products accumulate into;
+        the rotary kernel reads it and sets it back to zero, so one buffer per device and width
+        serves every layer and every step."""
+        key = (str(device), self.qkv.out_features)
+        buffer = _WORKSPACES.get(key)
+        if buffer is None:
+            buffer = _WORKSPACES[key] = torch.zeros((self.SPLIT_TOKENS, self.qkv.out_features), dtype=torch.float32,
+                                                    device=device)
+        return buffer
+
     def forward(self, h, x, ctx, cache: CacheView, state=None):
         cos, sin = self.tables if self.tables is not None else (None, None)
         tokens = h.shape[0]
-        if h.dtype == torch.bfloat16 and tokens <= SPLIT_TOKENS:
+        if h.dtype == torch.bfloat16 and tokens <= self.SPLIT_TOKENS:
             # few tokens: the product is a stream of weights, and a CTA streams only about 1/148 of
             # the memory bandwidth; split K so that every SM streams a share, accumulate in float32
             # and let the rotary kernel add the bias, rotate, convert and clear
-            acc = split_workspace(h.device, tokens, self.qkv.out_features)
+            acc = self._workspace(h.device)[:tokens]
             kernels.gemm_bf16(h, self.qkv.weight, acc, self.runtime.status, residual=acc,
                               split_k=self.qkv.split_k(tokens, True))
             qkv = torch.empty((tokens, self.qkv.out_features), dtype=h.dtype, device=h.device)

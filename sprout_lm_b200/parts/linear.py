@@ -11,19 +11,6 @@ import torch
 from .. import kernels
 
 SM_COUNT = 148
-SPLIT_TOKENS = 256          # up to this many tokens, products are split along K into float32 sums
-_WORKSPACES: dict = {}
-
-
-def split_workspace(device, tokens: int, width: int) -> torch.Tensor:
-    """``tokens`` rows of a zeroed float32 buffer [SPLIT_TOKENS, width] that split-K products
-    accumulate into.  Whoever reads the sums sets them back to zero, so one buffer per device and
-    width serves every layer and every step."""
-    key = (str(device), width)
-    buffer = _WORKSPACES.get(key)
-    if buffer is None:
-        buffer = _WORKSPACES[key] = torch.zeros((SPLIT_TOKENS, width), dtype=torch.float32, device=device)
-    return buffer[:tokens]
 
 
 class Linear:
@@ -39,25 +26,18 @@ class Linear:
     def split_k(self, tokens: int, residual: bool) -> int:
         """How many CTAs share the K range of a small-batch product into a float32 residual:
         enough to put a CTA on most SMs when the matrix has few 128-row tiles."""
-        if not residual or tokens > SPLIT_TOKENS:
+        if not residual or tokens > 256:
             return 1
         tiles = -(-self.out_features // 128)
         k_blocks = -(-self.in_features // 64)
-        return max(1, min(k_blocks, round(SM_COUNT / tiles)))
+        return max(1, min(k_blocks, SM_COUNT // tiles))
 
     def forward_swiglu(self, a: torch.Tensor) -> torch.Tensor:
         """silu(gate) * up of a fused, interleaved gate/up matrix: fused into the product's epilogue
         on the tensor-core path, a separate kernel on the 32-bit path."""
         half = self.out_features // 2
         out = torch.empty((a.shape[0], half), dtype=a.dtype, device=a.device)
-        tokens = a.shape[0]
-        if self.weight.dtype == torch.bfloat16 and tokens <= SPLIT_TOKENS and self.split_k(tokens, True) > 1:
-            # few tokens and fewer row tiles than SMs: split K so that every SM streams weights,
-            # sum in float32, then activate (and clear the sums) in a small kernel
-            acc = split_workspace(a.device, tokens, self.out_features)
-            kernels.gemm_bf16(a, self.weight, acc, self.status, residual=acc, split_k=self.split_k(tokens, True))
-            kernels.swiglu_acc(acc, out)
-        elif self.weight.dtype == torch.bfloat16:
+        if self.weight.dtype == torch.bfloat16:
             kernels.gemm_bf16(a, self.weight, out, self.status, swiglu=True)
         else:
             kernels.swiglu(self.forward(a), out)

@@ -68,14 +68,6 @@ def test_swiglu_interleaved(dtype, inter):
     want = (g / (1 + torch.exp(-g))).float().double() * up.double()
     tol = 1e-6 if dtype == torch.float32 else 8e-3
     assert (out.double() - want).abs().max().item() <= tol * max(1.0, want.abs().max().item())
-    if dtype == torch.bfloat16:
-        # the same from float32 sums (what a split-K product leaves), which are cleared
-        acc = torch.zeros(7, 2 * inter, device=DEV)
-        acc[:5] = fused.float()
-        again = torch.empty(5, inter, dtype=dtype, device=DEV)
-        kernels.swiglu_acc(acc[:5], again)
-        assert (again.double() - want).abs().max().item() <= 8e-3 * max(1.0, want.abs().max().item())
-        assert float(acc.abs().max()) == 0.0
     with pytest.raises(kernels.KernelError, match="multiple of 8"):
         kernels.swiglu(torch.empty(2, 24, dtype=dtype, device=DEV), torch.empty(2, 12, dtype=dtype, device=DEV))
 
