@@ -326,8 +326,6 @@ attention_decode_mma_kernel(const DecodeParams p) {
     if (row < group) v = *(const uint4*)(p.q + (size_t)r * p.q_stride + (size_t)(g * group + row) * HD + c * 8);
     *(uint4*)(sQ + row * STRIDE + c * 8) = v;
   }
-  if (!CLUSTER && begin >= len) return;
-  const int end = min(len, begin + p.split_keys);
   const float scale = 1.0f / sqrtf((float)HD);
 
   const int gr = lane >> 2, qc = lane & 3;
@@ -336,13 +334,18 @@ attention_decode_mma_kernel(const DecodeParams p) {
 #pragma unroll
   for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
+  // The first pass's keys and values are requested before the request's length is known (its load
+  // is still in flight): whatever lies in an allocated page beyond the length is finite and gets
+  // probability zero.  Later passes know the length.
+  int end = begin + p.split_keys;
   for (int base = begin; base < end; base += DEC_THREADS) {
+    const bool first = base == begin;
     const int key = base + tid;
     long long off = -1;
-    if (key < end) {
-      const int page = base == begin ? first_page : table[key / p.page_tokens];
-      if (page < 0 || page >= p.num_pages) atomicOr(p.status, SPROUT_STATUS_BAD_PAGE);
-      else off = (((long long)page * p.kv_heads + g) * p.page_tokens + key % p.page_tokens) * HD;
+    if (first || key < end) {
+      const int page = first ? first_page : table[key / p.page_tokens];
+      if (page >= 0 && page < p.num_pages) off = (((long long)page * p.kv_heads + g) * p.page_tokens + key % p.page_tokens) * HD;
+      else if (!first || key < len) atomicOr(p.status, SPROUT_STATUS_BAD_PAGE);
     }
     rows[tid] = off;
     __syncthreads();                                   // offsets and q visible; the staging buffers are free
@@ -355,6 +358,10 @@ attention_decode_mma_kernel(const DecodeParams p) {
       else { *(uint4*)dk = make_uint4(0, 0, 0, 0); *(uint4*)dv = make_uint4(0, 0, 0, 0); }
     }
     cp_async_commit();
+    if (first) {
+      end = min(len, begin + p.split_keys);
+      if (!CLUSTER && begin >= len) { cp_async_wait<0>(); return; }   // the merge kernel knows which splits exist
+    }
     cp_async_wait<0>();
     __syncthreads();
 

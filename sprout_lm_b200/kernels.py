@@ -279,11 +279,14 @@ def decode_split_plan(requests: int, kv_heads: int, max_keys: int) -> tuple[int,
     128 keys, made longer while there would be more than 8 of them, unless the batch is too
     small to fill the GPU that way, in which case many short splits go through scratch memory."""
     split_keys = 128
-    while -(-max_keys // split_keys) > 8:
+    pairs = requests * kv_heads
+    # at most 8 splits (a cluster), and no more CTAs than about two per SM: a large batch fills
+    # the GPU with few, long splits
+    while -(-max_keys // split_keys) > 8 or (pairs * -(-max_keys // split_keys) > 2 * SM_COUNT and split_keys < max_keys):
         split_keys += 128
-    if requests * kv_heads * 8 < SM_COUNT and max_keys > 8 * 128:
+    if pairs * 8 < SM_COUNT and max_keys > 8 * 128:
         split_keys = 128
-        while requests * kv_heads * (-(-max_keys // split_keys)) > 4 * SM_COUNT:
+        while pairs * (-(-max_keys // split_keys)) > 4 * SM_COUNT:
             split_keys *= 2
     splits = max(1, -(-max_keys // split_keys))
     return split_keys, splits, splits > 8
