@@ -280,9 +280,9 @@ def decode_split_plan(requests: int, kv_heads: int, max_keys: int) -> tuple[int,
     small to fill the GPU that way, in which case many short splits go through scratch memory."""
     split_keys = 128
     pairs = requests * kv_heads
-    # at most 8 splits (a cluster), and no more CTAs than about two per SM: a large batch fills
-    # the GPU with few, long splits
-    while -(-max_keys // split_keys) > 8 or (pairs * -(-max_keys // split_keys) > 2 * SM_COUNT and split_keys < max_keys):
+    # at most 8 splits (a cluster); short splits stay best even for large batches (a CTA's passes
+    # run one after the other)
+    while -(-max_keys // split_keys) > 8:
         split_keys += 128
     if pairs * 8 < SM_COUNT and max_keys > 8 * 128:
         split_keys = 128
