@@ -607,7 +607,12 @@ attention_prefill_kernel(const PrefillParams p) {
   int r = 0, tile = blockIdx.x;
   for (; r < p.requests; r++) {
     const int tiles = ((p.q_start[r + 1] - p.q_start[r]) * group + PF_ROWS - 1) / PF_ROWS;
-    if (tile < tiles) break;
+    if (tile < tiles) {
+      // causal work grows with the tile index; CTAs are handed to SMs in launch order, so deal the
+      // tiles out alternately from both ends: every SM gets a mix of short and long ones
+      tile = (tile & 1) ? tiles - 1 - (tile >> 1) : (tile >> 1);
+      break;
+    }
     tile -= tiles;
   }
   if (r >= p.requests) return;
@@ -676,6 +681,12 @@ attention_prefill_kernel(const PrefillParams p) {
 #pragma unroll
   for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
+  // exp(s * scale - m * scale) as exp2 with the scale folded in: one multiply-add per score
+  const float scale_log2 = p.scale * 1.4426950408889634f;
+  const int warp_min_limit = s_limit[min(warp * 16, last_row)];   // the smallest limit among this warp's rows
+  constexpr bool Q_IN_REGISTERS = HD <= 64;
+  uint32_t qf[Q_IN_REGISTERS ? HD / 16 : 1][4];
+
   for (int t = 0; t < kv_tiles; t++) {
     const int buf = t & 1;
     if (t + 1 < kv_tiles) find_rows(t + 1, buf ^ 1);
@@ -684,6 +695,11 @@ attention_prefill_kernel(const PrefillParams p) {
     cp_async_commit();
     cp_async_wait<1>();                                // tile t (and Q) have landed
     __syncthreads();
+    if (Q_IN_REGISTERS && t == 0) {
+#pragma unroll
+      for (int kk = 0; kk < (Q_IN_REGISTERS ? HD / 16 : 1); kk++)
+        ldmatrix_x4(qf[kk], sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + kk * 16 + (lane >> 4) * 8);
+    }
 
     const __nv_bfloat16* tK = sK + buf * PF_KEYS * STRIDE;
     const __nv_bfloat16* tV = sV + buf * PF_KEYS * STRIDE;
@@ -696,8 +712,10 @@ attention_prefill_kernel(const PrefillParams p) {
       for (int i = 0; i < PF_KEYS / 8; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
 #pragma unroll
       for (int kk = 0; kk < HD / 16; kk++) {
-        uint32_t a[4];
-        ldmatrix_x4(a, sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + kk * 16 + (lane >> 4) * 8);
+        uint32_t a_local[4];
+        if (!Q_IN_REGISTERS)
+          ldmatrix_x4(a_local, sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + kk * 16 + (lane >> 4) * 8);
+        const uint32_t (&a)[4] = Q_IN_REGISTERS ? qf[Q_IN_REGISTERS ? kk : 0] : a_local;
 #pragma unroll
         for (int n2 = 0; n2 < PF_KEYS / 16; n2++) {
           uint32_t b[4];
@@ -706,15 +724,21 @@ attention_prefill_kernel(const PrefillParams p) {
           mma_bf16(s[2 * n2 + 1], a, b[2], b[3]);
         }
       }
-      // scale, causal mask, running maximum
+      // causal mask (only on tiles that reach past some row's limit), running maximum; scores stay
+      // unscaled, the scale is applied inside the exponential
       float t_max0 = -INFINITY, t_max1 = -INFINITY;
+      if (kv0 + PF_KEYS - 1 > warp_min_limit) {
+#pragma unroll
+        for (int i = 0; i < PF_KEYS / 8; i++) {
+          const int key = kv0 + i * 8 + qc * 2;
+          if (key > limit0) s[i][0] = -INFINITY;
+          if (key + 1 > limit0) s[i][1] = -INFINITY;
+          if (key > limit1) s[i][2] = -INFINITY;
+          if (key + 1 > limit1) s[i][3] = -INFINITY;
+        }
+      }
 #pragma unroll
       for (int i = 0; i < PF_KEYS / 8; i++) {
-        const int key = kv0 + i * 8 + qc * 2;
-        s[i][0] = key <= limit0 ? s[i][0] * p.scale : -INFINITY;
-        s[i][1] = key + 1 <= limit0 ? s[i][1] * p.scale : -INFINITY;
-        s[i][2] = key <= limit1 ? s[i][2] * p.scale : -INFINITY;
-        s[i][3] = key + 1 <= limit1 ? s[i][3] * p.scale : -INFINITY;
         t_max0 = fmaxf(t_max0, fmaxf(s[i][0], s[i][1]));
         t_max1 = fmaxf(t_max1, fmaxf(s[i][2], s[i][3]));
       }
@@ -722,17 +746,18 @@ attention_prefill_kernel(const PrefillParams p) {
       t_max0 = fmaxf(t_max0, __shfl_xor_sync(0xffffffffu, t_max0, 2));
       t_max1 = fmaxf(t_max1, __shfl_xor_sync(0xffffffffu, t_max1, 1));
       t_max1 = fmaxf(t_max1, __shfl_xor_sync(0xffffffffu, t_max1, 2));
-      const float n0 = fmaxf(m0, t_max0), n1 = fmaxf(m1, t_max1);
-      const float base0 = n0 == -INFINITY ? 0.f : n0, base1 = n1 == -INFINITY ? 0.f : n1;
-      const float alpha0 = m0 == -INFINITY ? 0.f : __expf(m0 - base0), alpha1 = m1 == -INFINITY ? 0.f : __expf(m1 - base1);
+      const float n0 = fmaxf(m0, t_max0), n1 = fmaxf(m1, t_max1);     // running maxima of the unscaled scores
+      const float base0 = n0 == -INFINITY ? 0.f : n0 * scale_log2, base1 = n1 == -INFINITY ? 0.f : n1 * scale_log2;
+      const float alpha0 = m0 == -INFINITY ? 0.f : exp2f(m0 * scale_log2 - base0);
+      const float alpha1 = m1 == -INFINITY ? 0.f : exp2f(m1 * scale_log2 - base1);
       m0 = n0; m1 = n1;
       l0 *= alpha0; l1 *= alpha1;
 #pragma unroll
       for (int i = 0; i < HD / 8; i++) { o[i][0] *= alpha0; o[i][1] *= alpha0; o[i][2] *= alpha1; o[i][3] *= alpha1; }
 #pragma unroll
       for (int i = 0; i < PF_KEYS / 8; i++) {
-        s[i][0] = __expf(s[i][0] - base0); s[i][1] = __expf(s[i][1] - base0);
-        s[i][2] = __expf(s[i][2] - base1); s[i][3] = __expf(s[i][3] - base1);
+        s[i][0] = exp2f(fmaf(s[i][0], scale_log2, -base0)); s[i][1] = exp2f(fmaf(s[i][1], scale_log2, -base0));
+        s[i][2] = exp2f(fmaf(s[i][2], scale_log2, -base1)); s[i][3] = exp2f(fmaf(s[i][3], scale_log2, -base1));
         l0 += s[i][0] + s[i][1];
         l1 += s[i][2] + s[i][3];
       }
