@@ -1,0 +1,74 @@
+"""The layer sizes of the 0.5B configuration (hidden 896, 14 query / 2 key-value heads of 64,
+feed-forward 4864, vocabulary 151936, tied head), with two layers to keep the plain
+implementation affordable: whole, in portions, decoded one by one (the captured decode graph),
+in true 32-bit and in bfloat16.
+
+Tolerance in 32-bit: the reference project's own bar for the real 0.5B model against an
+independent float32 implementation, 1e-3 + 1e-4 |ref| (test/model.integration.ts:69)."""
+import numpy as np
+import pytest
+import torch
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+SIZES = dict(hidden_size=896, intermediate_size=4864, num_hidden_layers=2, num_attention_heads=14,
+             num_key_value_heads=2, vocab_size=151936, max_position_embeddings=4096, rms_norm_eps=1e-6,
+             rope_theta=1000000.0, tie_word_embeddings=True, eos_token_id=151645)
+
+
+@pytest.fixture(scope="module")
+def folder(tmp_path_factory):
+    from sprout_lm_b200.config import parse_config
+    from sprout_lm_b200.weights import write_random_model
+    config = parse_config(helpers.raw_config(SIZES))
+    return write_random_model(tmp_path_factory.mktemp("real") / "model", config, seed=2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_real_layer_sizes_under_all_cuttings(folder, dtype):
+    from sprout_lm_b200 import load_model
+    from sprout_lm_b200.engine.batch import StepEntry
+    from sprout_lm_b200.engine.step import ModelRunner
+    rng = np.random.default_rng(0)
+    requests = {"a": helpers.random_tokens(rng, 40, SIZES["vocab_size"]), "b": helpers.random_tokens(rng, 23, SIZES["vocab_size"])}
+    want = {rid: helpers.plain_logits(folder, toks) for rid, toks in requests.items()}
+    model = load_model(folder, dtype=dtype)
+    scale = max(float(np.abs(w).max()) for w in want.values())
+
+    def check(got, label):
+        for rid, toks in requests.items():
+            for pos in range(len(toks)):
+                if (rid, pos) not in got:
+                    continue
+                ref = want[rid][pos]
+                err = np.abs(got[(rid, pos)] - ref)
+                if dtype == "float32":
+                    assert (err <= 1e-3 + 1e-4 * np.abs(ref)).all(), (label, rid, pos, float(err.max()))
+                else:
+                    assert float(err.max()) <= 0.02 * scale, (label, rid, pos, float(err.max()), scale)
+
+    for label, plan in (("whole", helpers.plan_whole(requests)), ("portions", helpers.plan_portions(requests)),
+                        ("mixed", helpers.plan_mixed(requests, np.random.default_rng(1)))):
+        runner = ModelRunner(model, num_pages=8, page_tokens=16, max_requests=4, prefix_caching=False)
+        check(helpers.run_plan_in_process(runner, plan), label)
+
+    # the captured decode graph: prompts in one step each, then both requests decoded together with
+    # their own tokens forced; the sampled token of every step must be the plain argmax
+    runner = ModelRunner(model, num_pages=8, page_tokens=16, max_requests=4, prefix_caching=False)
+    seqs = {rid: runner.new_sequence() for rid in requests}
+    head = 12
+    for rid, toks in requests.items():
+        assert runner.reserve(seqs[rid], len(toks))
+        runner.step([StepEntry(seqs[rid], toks[:head], [])])
+    for at in range(head, 23):
+        entries = [StepEntry(seqs[rid], [requests[rid][at]], [0]) for rid in requests]
+        tokens = runner.step_and_sample(entries, [0.0, 0.0], [0.0, 0.0])
+        for rid, token in zip(requests, tokens):
+            row = want[rid][at]
+            top2 = np.sort(row)[-2:]
+            if dtype == "float32" or top2[1] - top2[0] > 0.04 * scale:
+                assert token == int(np.argmax(row)), (rid, at)
+    assert len(runner.graphs.graphs) == 1 and next(iter(runner.graphs.graphs.values())).graph is not None
+    runner.check_status()
