@@ -134,6 +134,62 @@ def test_attention_part_whole_then_token_by_token(dtype, heads, kv_heads, head_d
     assert int(runtime.status.item()) == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tied", [True, False])
+def test_embedding_and_head_parts(dtype, tied):
+    from sprout_lm_b200.config import PartSpec
+    from sprout_lm_b200.parts import build_part
+    vocab, hidden = 509, 72
+    emb = build_part("embedding", PartSpec("token_embedding", {"vocab_size": vocab, "hidden_size": hidden, "name": "emb"}))
+    head = build_part("head", PartSpec("lm_head", {"vocab_size": vocab, "hidden_size": hidden,
+                                                  "tied_to": "emb" if tied else None, "name": "out"}))
+    assert [d.name for d in head.tensor_decls()] == ([] if tied else ["out.weight"])
+    tensors = {"emb.weight": (torch.randn(vocab, hidden) * 0.1).to(torch.bfloat16).float(),
+               "out.weight": (torch.randn(vocab, hidden) * 0.1).to(torch.bfloat16).float()}
+    source, runtime = source_for(tensors, dtype)
+    emb.load(source)
+    head.load(source)
+    if tied:
+        assert head.linear.weight.data_ptr() == emb.table.data_ptr()      # the same matrix, not a copy
+    tokens = torch.tensor([0, 508, 17, 17], dtype=torch.int32, device=DEV)
+    x = emb.forward(tokens)
+    assert x.dtype == torch.float32
+    np.testing.assert_array_equal(x.cpu().numpy(), plain.embed(tensors["emb.weight"].numpy(), tokens.cpu().numpy()))
+    h = torch.randn(3, hidden).to(torch.bfloat16).float()
+    logits = head.forward(h.to(dtype).to(DEV))
+    want = plain.linear(h.numpy(), tensors["emb.weight" if tied else "out.weight"].numpy())
+    assert logits.dtype == torch.float32 and logits.shape == (3, vocab)
+    assert np.abs(logits.cpu().numpy() - want).max() <= 1e-5
+    assert int(runtime.status.item()) == 0
+
+
+def test_pre_norm_block_arranges_its_parts():
+    """A whole block (norm, attention, norm, feed-forward with both residuals) against the plain
+    layer function, on a fresh cache."""
+    from sprout_lm_b200.config import parse_config
+    from sprout_lm_b200.engine.batch import StepEntry
+    from sprout_lm_b200.parts import CacheView, build_block
+    config = parse_config(helpers.raw_config(helpers.TINY_B))
+    layer = config.model_spec().layers[1]
+    block = build_block(layer)
+    tensors = {d.name: ((1 if d.init == "gain" else 0) + torch.randn(*d.shape) * 0.05).to(torch.bfloat16).float()
+               for d in block.tensor_decls()}
+    source, runtime = source_for(tensors, torch.float32)
+    block.load(source)
+    tokens, page = 21, 8
+    x0 = torch.randn(tokens, config.hidden_size)
+    seq = FakeSeq([3, 0, 5], 0)
+    ctx = stage([StepEntry(seq, [0] * tokens, [])], page)
+    k_cache = torch.zeros(6, config.num_key_value_heads, page, config.head_dim, device=DEV)
+    cache = CacheView(k_cache, torch.zeros_like(k_cache), ctx.block_tables[0], page, True)
+    x = x0.clone().to(DEV)
+    block.forward(x, ctx, cache, None)
+    raw = helpers.raw_config(helpers.TINY_B)
+    want = plain.decoder_layer(x0.numpy(), {n: t.numpy() for n, t in tensors.items()}, layer.prefix, raw, np.arange(tokens))
+    assert np.abs(x.cpu().numpy() - want).max() <= 2e-5
+    assert int(runtime.status.item()) == 0
+
+
 # ------------------------------------------------------------------------------------ the toy architecture
 def toy_angles(head_dim, max_positions):
     d = np.arange(head_dim // 2, dtype=np.float64)

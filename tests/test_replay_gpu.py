@@ -93,16 +93,67 @@ def test_trace_run_program(model_dirs, tmp_path, dtype):
             assert np.abs(results[other][place] - row).max() <= 2 * TOL[dtype]
 
 
-def test_long_decoding_float32(model_dirs):
-    """A short prompt, then several hundred tokens one by one across many page edges."""
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(model_dirs, dtype):
+    """A short prompt, then several hundred tokens one by one across many page edges (in
+    bfloat16 through the tensor-core decode attention, its splits and their merge)."""
     name = "A"
     requests = make_requests(name, 41, [400])
     toks = requests["r0"]
     plan = [{"entries": [("r0", toks[:6], list(range(6)))], "end": []}]
     plan += [{"entries": [("r0", [t], [0])], "end": []} for t in toks[6:]]
-    runner = make_runner(model_dirs[name], "float32", 448 // 16, 16)
+    runner = make_runner(model_dirs[name], dtype, 448 // 16, 16)
     got = helpers.run_plan_in_process(runner, plan)
-    helpers.compare_with_plain(model_dirs[name], requests, got, TOL["float32"], "long-decode")
+    helpers.compare_with_plain(model_dirs[name], requests, got, TOL[dtype], "long-decode")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sharp_attention_shows_every_key(model_dirs, tmp_path, dtype):
+    """Random weights make attention nearly uniform, which hides a lost or misplaced key under
+    bfloat16 rounding.  Here the query and key projections are scaled up so that the softmax is
+    peaked: each position leans on a few particular keys, near and far, and an engine that
+    misses one of them (a page's edge, a reused page, the start of a portion) moves the logits
+    far beyond the tolerance."""
+    import plain_qwen2 as plain
+    from sprout_lm_b200.weights import Checkpoint, write_safetensors
+    import shutil
+    name = "B"
+    page = helpers.TINY[name][2]
+    folder = tmp_path / "sharp"
+    shutil.copytree(model_dirs[name], folder)
+    with Checkpoint(model_dirs[name]) as ck:
+        tensors = {n: ck.tensor(n) for n in ck.inventory()}
+    for n in tensors:
+        if n.endswith("q_proj.weight") or n.endswith("k_proj.weight"):
+            tensors[n] = (tensors[n].float() * 7.0).to(tensors[n].dtype)
+    write_safetensors(folder / "model.safetensors", tensors)
+    requests = make_requests(name, 77, [150, 97, 64, 120])
+    cfg, w = plain.read_model_folder(folder)
+    # the attention really is peaked: in the last layer's input the largest probability is far from uniform
+    logits_ref = {rid: plain.logits(cfg, w, toks) for rid, toks in requests.items()}
+    plans = {"portions": helpers.plan_portions(requests), "mixed": helpers.plan_mixed(requests, np.random.default_rng(4)),
+             "tail": helpers.plan_tail_decode(requests)}
+    scale = max(float(np.abs(v).max()) for v in logits_ref.values())
+    tol = 1e-4 if dtype == "float32" else 0.03 * scale
+    for label, plan in plans.items():
+        budget = helpers.live_token_budget(plan, requests)
+        runner = make_runner(folder, dtype, budget // page, page)
+        got = helpers.run_plan_in_process(runner, plan)
+        for rid, toks in requests.items():
+            for pos in range(len(toks)):
+                err = float(np.abs(got[(rid, pos)] - logits_ref[rid][pos]).max())
+                assert err <= tol, f"{label}/{dtype}: request {rid} position {pos} (% {page} = {pos % page}) differs by {err:.3e}"
+    # and the test can fail: dropping one far key of one head changes the plain logits by more than the tolerance
+    toks = requests["r0"]
+    x = plain.hidden_states(cfg, w, toks, layers=0)
+    heads, kv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["hidden_size"] // cfg["num_attention_heads"]
+    h = plain.rms_norm(x, w["model.layers.0.input_layernorm.weight"], cfg["rms_norm_eps"])
+    q = plain.rope_half_split(plain.linear(h, w["model.layers.0.self_attn.q_proj.weight"], w["model.layers.0.self_attn.q_proj.bias"]), range(len(toks)), hd, cfg["rope_theta"])
+    k = plain.rope_half_split(plain.linear(h, w["model.layers.0.self_attn.k_proj.weight"], w["model.layers.0.self_attn.k_proj.bias"]), range(len(toks)), hd, cfg["rope_theta"])
+    scores = (q[-1, :hd].astype(np.float64) @ k[:, :hd].astype(np.float64).T) / np.sqrt(hd)
+    p = np.exp(scores - scores.max())
+    p /= p.sum()
+    assert p.max() > 10.0 / len(toks), "the attention of the sharpened model is not peaked"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
