@@ -18,6 +18,38 @@ SIZES = dict(hidden_size=896, intermediate_size=4864, num_hidden_layers=2, num_a
              rope_theta=1000000.0, tie_word_embeddings=True, eos_token_id=151645)
 
 
+SIZES_7B_LAYER = dict(hidden_size=3584, intermediate_size=18944, num_hidden_layers=1, num_attention_heads=28,
+                      num_key_value_heads=4, vocab_size=1000, max_position_embeddings=4096, rms_norm_eps=1e-6,
+                      rope_theta=1000000.0, tie_word_embeddings=False, eos_token_id=999)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_7b_layer_sizes(tmp_path, dtype):
+    """One layer with the 7B configuration's sizes (head size 128, 28 / 4 heads, feed-forward
+    18944; a small vocabulary keeps the plain implementation affordable): a portion, then tokens
+    one by one."""
+    from sprout_lm_b200 import load_model
+    from sprout_lm_b200.config import parse_config
+    from sprout_lm_b200.engine.step import ModelRunner
+    from sprout_lm_b200.weights import write_random_model
+    folder = write_random_model(tmp_path / "m7", parse_config(helpers.raw_config(SIZES_7B_LAYER)), seed=3)
+    rng = np.random.default_rng(0)
+    requests = {"a": helpers.random_tokens(rng, 30, 1000), "b": helpers.random_tokens(rng, 19, 1000)}
+    want = {rid: helpers.plain_logits(folder, toks) for rid, toks in requests.items()}
+    scale = max(float(np.abs(w).max()) for w in want.values())
+    model = load_model(folder, dtype=dtype)
+    runner = ModelRunner(model, num_pages=8, page_tokens=16, max_requests=4, prefix_caching=False)
+    got = helpers.run_plan_in_process(runner, helpers.plan_tail_decode(requests, tail=8))
+    for rid, toks in requests.items():
+        for pos in range(len(toks)):
+            ref = want[rid][pos]
+            err = np.abs(got[(rid, pos)] - ref)
+            if dtype == "float32":
+                assert (err <= 1e-3 + 1e-4 * np.abs(ref)).all(), (rid, pos, float(err.max()))
+            else:
+                assert float(err.max()) <= 0.02 * scale, (rid, pos, float(err.max()), scale)
+
+
 @pytest.fixture(scope="module")
 def folder(tmp_path_factory):
     from sprout_lm_b200.config import parse_config
