@@ -60,6 +60,12 @@ struct DecodeParams {
   float* part_ml;                     // [requests, heads, splits, 2]
   int heads, kv_heads, head_dim, page_tokens, num_pages, split_keys, splits;
   int* status;
+  // fused projection tail (tensor-core kernel, FUSED): q, k, v of the new token come as float32
+  // sums [requests, heads + 2 kv_heads, head_dim] from a split-K product, plus a bias; the
+  // kernel rotates q and k by the token's position (tables [max_positions, head_dim / 2], may be
+  // null), appends k and v to the cache and leaves the sums zeroed
+  float* acc; const float* bias; const float* cos_table; const float* sin_table; int max_positions;
+  __nv_bfloat16* k_append; __nv_bfloat16* v_append;
 };
 
 __device__ __forceinline__ void dec_cp_async16(void* smem, const void* gmem) {
@@ -296,7 +302,7 @@ attention_decode_kernel(const DecodeParams p) {
 // softmax, O += P V, all as mma.sync on keys and values staged in shared memory by cp.async.
 // The warps' partial results are merged through shared memory into the CTA's partial result
 // (maximum, sum, unnormalised output), which then goes the same ways as in the kernel above.
-template <int HD, bool CLUSTER>
+template <int HD, bool CLUSTER, bool FUSED>
 __global__ void __launch_bounds__(DEC_THREADS)
 attention_decode_mma_kernel(const DecodeParams p) {
   constexpr int STRIDE = HD + 8, CHUNKS = HD / 8;
@@ -320,11 +326,15 @@ attention_decode_mma_kernel(const DecodeParams p) {
   const int begin = split * p.split_keys;
   const int len = p.context_lens[r];
   const int first_page = table[min((begin + tid) / p.page_tokens, p.table_stride - 1)];
-  for (int idx = tid; idx < 16 * CHUNKS; idx += DEC_THREADS) {
-    const int row = idx / CHUNKS, c = idx % CHUNKS;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (row < group) v = *(const uint4*)(p.q + (size_t)r * p.q_stride + (size_t)(g * group + row) * HD + c * 8);
-    *(uint4*)(sQ + row * STRIDE + c * 8) = v;
+  const int width = (p.heads + 2 * p.kv_heads) * HD;
+  const int pos = len - 1;                             // FUSED: the new token's position
+  if (!FUSED) {
+    for (int idx = tid; idx < 16 * CHUNKS; idx += DEC_THREADS) {
+      const int row = idx / CHUNKS, c = idx % CHUNKS;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (row < group) v = *(const uint4*)(p.q + (size_t)r * p.q_stride + (size_t)(g * group + row) * HD + c * 8);
+      *(uint4*)(sQ + row * STRIDE + c * 8) = v;
+    }
   }
   const float scale = 1.0f / sqrtf((float)HD);
 
@@ -347,6 +357,7 @@ attention_decode_mma_kernel(const DecodeParams p) {
       if (page >= 0 && page < p.num_pages) off = (((long long)page * p.kv_heads + g) * p.page_tokens + key % p.page_tokens) * HD;
       else if (!first || key < len) atomicOr(p.status, SPROUT_STATUS_BAD_PAGE);
     }
+    if (FUSED && !first && key == pos) off = -2;       // the new token's row is written below, not loaded
     rows[tid] = off;
     __syncthreads();                                   // offsets and q visible; the staging buffers are free
     for (int idx = tid; idx < DEC_THREADS * CHUNKS; idx += DEC_THREADS) {
@@ -355,14 +366,67 @@ attention_decode_mma_kernel(const DecodeParams p) {
       __nv_bfloat16* dk = sK + row * STRIDE + c * 8;
       __nv_bfloat16* dv = sV + row * STRIDE + c * 8;
       if (ro >= 0) { cp_async16(dk, p.k_cache + ro + c * 8); cp_async16(dv, p.v_cache + ro + c * 8); }
-      else { *(uint4*)dk = make_uint4(0, 0, 0, 0); *(uint4*)dv = make_uint4(0, 0, 0, 0); }
+      else if (ro == -1) { *(uint4*)dk = make_uint4(0, 0, 0, 0); *(uint4*)dv = make_uint4(0, 0, 0, 0); }
     }
     cp_async_commit();
+    if (FUSED && first) {
+      // while the first pass's keys and values are on their way:
+      // q of the group's heads: sums + bias, rotated by the position, to shared memory as bfloat16
+      const bool rotate = p.cos_table != nullptr;
+      if (pos < 0 || (rotate && pos >= p.max_positions)) { if (tid == 0) atomicOr(p.status, SPROUT_STATUS_BAD_POSITION); }
+      const int safe = min(max(pos, 0), max(p.max_positions - 1, 0));
+      constexpr int HALF = HD / 2;
+      for (int idx = tid; idx < 16 * HALF; idx += DEC_THREADS) {
+        const int row = idx / HALF, d = idx % HALF;
+        float lo = 0.f, hi = 0.f;
+        if (row < group) {
+          const int at = (g * group + row) * HD + d;
+          const float a = p.acc[(size_t)r * width + at] + (p.bias ? p.bias[at] : 0.f);
+          const float b = p.acc[(size_t)r * width + at + HALF] + (p.bias ? p.bias[at + HALF] : 0.f);
+          const float c = rotate ? p.cos_table[(size_t)safe * HALF + d] : 1.f, sn = rotate ? p.sin_table[(size_t)safe * HALF + d] : 0.f;
+          lo = a * c - b * sn;
+          hi = b * c + a * sn;
+        }
+        sQ[row * STRIDE + d] = __float2bfloat16_rn(lo);
+        sQ[row * STRIDE + d + HALF] = __float2bfloat16_rn(hi);
+      }
+    }
     if (first) {
       end = min(len, begin + p.split_keys);
       if (!CLUSTER && begin >= len) { cp_async_wait<0>(); return; }   // the merge kernel knows which splits exist
     }
     cp_async_wait<0>();
+    if (FUSED && pos >= base && pos < base + DEC_THREADS && pos < begin + p.split_keys) {
+      // This split holds the new token: its key (rotated) and value come from the sums, go to the
+      // cache and, over whatever the first pass's early load brought, into this pass's tile.
+      __syncthreads();                                 // the early loads of that row have landed
+      const bool rotate = p.cos_table != nullptr;
+      const int safe = min(max(pos, 0), max(p.max_positions - 1, 0));
+      constexpr int HALF = HD / 2;
+      const int page = table[pos / p.page_tokens];
+      const bool page_ok = page >= 0 && page < p.num_pages;
+      if (!page_ok && tid == 0) atomicOr(p.status, SPROUT_STATUS_BAD_PAGE);
+      const long long dst = page_ok ? (((long long)page * p.kv_heads + g) * p.page_tokens + pos % p.page_tokens) * HD : 0;
+      float* k_acc = p.acc + (size_t)r * width + (p.heads + g) * HD;
+      float* v_acc = p.acc + (size_t)r * width + (p.heads + p.kv_heads + g) * HD;
+      const float* k_bias = p.bias ? p.bias + (p.heads + g) * HD : nullptr;
+      const float* v_bias = p.bias ? p.bias + (p.heads + p.kv_heads + g) * HD : nullptr;
+      const int row = pos - base;
+      for (int d = tid; d < HALF; d += DEC_THREADS) {
+        const float a = k_acc[d] + (k_bias ? k_bias[d] : 0.f), b = k_acc[d + HALF] + (k_bias ? k_bias[d + HALF] : 0.f);
+        k_acc[d] = 0.f; k_acc[d + HALF] = 0.f;
+        const float c = rotate ? p.cos_table[(size_t)safe * HALF + d] : 1.f, sn = rotate ? p.sin_table[(size_t)safe * HALF + d] : 0.f;
+        const __nv_bfloat16 lo = __float2bfloat16_rn(a * c - b * sn), hi = __float2bfloat16_rn(b * c + a * sn);
+        sK[row * STRIDE + d] = lo; sK[row * STRIDE + d + HALF] = hi;
+        if (page_ok) { p.k_append[dst + d] = lo; p.k_append[dst + d + HALF] = hi; }
+      }
+      for (int d = tid; d < HD; d += DEC_THREADS) {
+        const __nv_bfloat16 v = __float2bfloat16_rn(v_acc[d] + (v_bias ? v_bias[d] : 0.f));
+        v_acc[d] = 0.f;
+        sV[row * STRIDE + d] = v;
+        if (page_ok) p.v_append[dst + d] = v;
+      }
+    }
     __syncthreads();
 
     const int key0 = base + warp * 32;                 // this warp's 32 keys
@@ -470,6 +534,9 @@ attention_decode_mma_kernel(const DecodeParams p) {
   if constexpr (CLUSTER) {
     cg::cluster_group cluster = cg::this_cluster();
     cluster.sync();
+    if (FUSED && cluster.block_rank() == 0) {          // every split has read the q sums: clear them
+      for (int i = tid; i < group * HD; i += DEC_THREADS) p.acc[(size_t)r * width + g * group * HD + i] = 0.f;
+    }
     if (cluster.block_rank() == 0) {
       const int count = (int)cluster.num_blocks();
       for (int i = tid; i < group * HD; i += DEC_THREADS) {
@@ -500,14 +567,14 @@ attention_decode_mma_kernel(const DecodeParams p) {
   }
 }
 
-template <int HD>
+template <int HD, bool FUSED>
 int launch_decode_mma(const DecodeParams& p, bool cluster, int requests, cudaStream_t stream) {
   constexpr size_t smem = (size_t)(16 + 2 * DEC_THREADS) * (HD + 8) * 2 + (size_t)(16 * HD + 32) * 4 + DEC_THREADS * 8;
   static bool configured[2] = {false, false};
   if (smem > 48 * 1024 && !configured[cluster]) {
     cudaError_t err = cluster
-        ? cudaFuncSetAttribute(attention_decode_mma_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-        : cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        ? cudaFuncSetAttribute(attention_decode_mma_kernel<HD, true, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+        : cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return sprout_fail("attention_decode: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
     configured[cluster] = true;
   }
@@ -527,10 +594,10 @@ int launch_decode_mma(const DecodeParams& p, bool cluster, int requests, cudaStr
     attributes[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attributes;
     config.numAttrs = sprout_pdl_enabled() ? 2 : 1;
-    cudaLaunchKernelEx(&config, attention_decode_mma_kernel<HD, true>, p);
+    cudaLaunchKernelEx(&config, attention_decode_mma_kernel<HD, true, FUSED>, p);
     return sprout_check_launch("attention_decode (tensor cores, cluster)");
   }
-  sprout_launch(attention_decode_mma_kernel<HD, false>, grid, dim3(DEC_THREADS), smem, stream, p);
+  sprout_launch(attention_decode_mma_kernel<HD, false, false>, grid, dim3(DEC_THREADS), smem, stream, p);
   return sprout_check_launch("attention_decode (tensor cores)");
 }
 
@@ -818,15 +885,16 @@ SPROUT_API long long sprout_attention_decode_scratch_floats(int requests, int he
   return (long long)requests * heads * splits * (head_dim + 2);
 }
 
-// One query token per request.  q, out: [requests, heads * head_dim] (row strides given);
-// context_lens[r] keys are visible to request r.  scratch: float32, at least
-// sprout_attention_decode_scratch_floats(...) long; it may be null for up to 8 splits, which are
-// then merged inside a thread-block cluster instead of through memory.
-SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
-                                       const int* block_table, int table_stride, const int* context_lens,
-                                       void* out, int out_stride, float* scratch, int requests, int heads,
-                                       int kv_heads, int head_dim, int page_tokens, int num_pages, int split_keys,
-                                       int splits, int* status, cudaStream_t stream) {
+struct FusedTail { float* acc; const float* bias; const float* cos_table; const float* sin_table; int max_positions; };
+
+static int decode_launch(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                         const int* block_table, int table_stride, const int* context_lens, void* out, int out_stride,
+                         float* scratch, int requests, int heads, int kv_heads, int head_dim, int page_tokens,
+                         int num_pages, int split_keys, int splits, int* status, cudaStream_t stream,
+                         const FusedTail* extra) {
+  const bool fused_early = extra != nullptr;
+  (void)fused_early;
+
   SPROUT_REQUIRE(requests > 0 && requests <= 65535 && heads > 0 && kv_heads > 0 && page_tokens > 0 && num_pages > 0,
                  "attention_decode: sizes must be positive (at most 65535 requests)");
   SPROUT_REQUIRE(heads % kv_heads == 0 && heads / kv_heads <= MAX_GROUP,
@@ -835,7 +903,7 @@ SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* 
                  "attention_decode: head_dim must be a multiple of 16 between 16 and 256 (got %d)", head_dim);
   SPROUT_REQUIRE(split_keys > 0 && split_keys % DEC_THREADS == 0 && splits > 0 && splits <= 65535,
                  "attention_decode: split_keys must be a positive multiple of %d", DEC_THREADS);
-  SPROUT_REQUIRE(q && k_cache && v_cache && block_table && context_lens && out && status, "attention_decode: null pointer");
+  SPROUT_REQUIRE((q || fused_early) && k_cache && v_cache && block_table && context_lens && out && status, "attention_decode: null pointer");
   SPROUT_REQUIRE(q_stride % 2 == 0 && out_stride % 2 == 0 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0,
                  "attention_decode: misaligned operands");
   DecodeParams p;
@@ -847,24 +915,34 @@ SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* 
   p.part_ml = scratch ? scratch + (size_t)requests * heads * splits * head_dim : nullptr;
   p.heads = heads; p.kv_heads = kv_heads; p.head_dim = head_dim; p.page_tokens = page_tokens; p.num_pages = num_pages;
   p.split_keys = split_keys; p.splits = splits; p.status = status;
+  p.acc = nullptr; p.bias = nullptr; p.cos_table = nullptr; p.sin_table = nullptr; p.max_positions = 0;
+  p.k_append = nullptr; p.v_append = nullptr;
+  const bool fused = fused_early;
+  if (fused) {
+    SPROUT_REQUIRE(extra->acc && head_dim <= 128 && splits <= 8, "attention_decode_fused: needs the sums, head_dim <= 128 and at most 8 splits");
+    SPROUT_REQUIRE((extra->cos_table == nullptr) == (extra->sin_table == nullptr), "attention_decode_fused: cos and sin tables go together");
+    p.acc = extra->acc; p.bias = extra->bias; p.cos_table = extra->cos_table; p.sin_table = extra->sin_table;
+    p.max_positions = extra->max_positions;
+    p.k_append = (__nv_bfloat16*)k_cache; p.v_append = (__nv_bfloat16*)v_cache;
+  }
   const int group = heads / kv_heads;
   const size_t smem = (size_t)(group * head_dim + group * DEC_THREADS + MAX_GROUP * 8) * sizeof(float)
       + DEC_THREADS * sizeof(long long) + (size_t)2 * DEC_THREADS * (head_dim + 8) * sizeof(__nv_bfloat16)
       + (size_t)(group * head_dim + 2 * group) * sizeof(float);
   // no scratch given and at most 8 splits: the splits of a (request, key/value head) are a cluster
-  const bool cluster = scratch == nullptr && splits > 1 && splits <= 8;
+  const bool cluster = fused || (scratch == nullptr && splits > 1 && splits <= 8);
   SPROUT_REQUIRE(splits == 1 || cluster || scratch, "attention_decode: scratch memory is needed for more than 8 splits");
   if (head_dim <= 128) {
     int rc = 1;
     switch (head_dim) {
-      case 16: rc = launch_decode_mma<16>(p, cluster, requests, stream); break;
-      case 32: rc = launch_decode_mma<32>(p, cluster, requests, stream); break;
-      case 48: rc = launch_decode_mma<48>(p, cluster, requests, stream); break;
-      case 64: rc = launch_decode_mma<64>(p, cluster, requests, stream); break;
-      case 80: rc = launch_decode_mma<80>(p, cluster, requests, stream); break;
-      case 96: rc = launch_decode_mma<96>(p, cluster, requests, stream); break;
-      case 112: rc = launch_decode_mma<112>(p, cluster, requests, stream); break;
-      case 128: rc = launch_decode_mma<128>(p, cluster, requests, stream); break;
+      case 16: rc = fused ? launch_decode_mma<16, true>(p, true, requests, stream) : launch_decode_mma<16, false>(p, cluster, requests, stream); break;
+      case 32: rc = fused ? launch_decode_mma<32, true>(p, true, requests, stream) : launch_decode_mma<32, false>(p, cluster, requests, stream); break;
+      case 48: rc = fused ? launch_decode_mma<48, true>(p, true, requests, stream) : launch_decode_mma<48, false>(p, cluster, requests, stream); break;
+      case 64: rc = fused ? launch_decode_mma<64, true>(p, true, requests, stream) : launch_decode_mma<64, false>(p, cluster, requests, stream); break;
+      case 80: rc = fused ? launch_decode_mma<80, true>(p, true, requests, stream) : launch_decode_mma<80, false>(p, cluster, requests, stream); break;
+      case 96: rc = fused ? launch_decode_mma<96, true>(p, true, requests, stream) : launch_decode_mma<96, false>(p, cluster, requests, stream); break;
+      case 112: rc = fused ? launch_decode_mma<112, true>(p, true, requests, stream) : launch_decode_mma<112, false>(p, cluster, requests, stream); break;
+      case 128: rc = fused ? launch_decode_mma<128, true>(p, true, requests, stream) : launch_decode_mma<128, false>(p, cluster, requests, stream); break;
     }
     if (rc) return rc;
   } else {
@@ -906,6 +984,35 @@ SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* 
     return sprout_check_launch("attention_decode_merge");
   }
   return 0;
+}
+
+
+// One query token per request.  q, out: [requests, heads * head_dim] (row strides given);
+// context_lens[r] keys are visible to request r.  scratch: float32, at least
+// sprout_attention_decode_scratch_floats(...) long; it may be null for up to 8 splits, which are
+// then merged inside a thread-block cluster instead of through memory.
+SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                       const int* block_table, int table_stride, const int* context_lens,
+                                       void* out, int out_stride, float* scratch, int requests, int heads,
+                                       int kv_heads, int head_dim, int page_tokens, int num_pages, int split_keys,
+                                       int splits, int* status, cudaStream_t stream) {
+  return decode_launch(q, q_stride, k_cache, v_cache, block_table, table_stride, context_lens, out, out_stride, scratch,
+                       requests, heads, kv_heads, head_dim, page_tokens, num_pages, split_keys, splits, status, stream, nullptr);
+}
+
+// The decode step's attention with the projection's tail folded in: instead of q and an already
+// appended cache it takes the float32 sums of the q/k/v product for each request's new token
+// (acc [requests, (heads + 2 kv_heads) * head_dim], contiguous) and their bias; it rotates q and k
+// by the token's position context_lens[r] - 1 (tables may be null: no rotation), appends k and v
+// to the cache, attends, and leaves acc zeroed.  head_dim <= 128, at most 8 splits.
+SPROUT_API int sprout_attention_decode_fused(float* acc, const float* bias, const float* cos_table, const float* sin_table,
+                                             int max_positions, void* k_cache, void* v_cache, const int* block_table,
+                                             int table_stride, const int* context_lens, void* out, int out_stride,
+                                             int requests, int heads, int kv_heads, int head_dim, int page_tokens,
+                                             int num_pages, int split_keys, int splits, int* status, cudaStream_t stream) {
+  FusedTail extra{acc, bias, cos_table, sin_table, max_positions};
+  return decode_launch(nullptr, 0, k_cache, v_cache, block_table, table_stride, context_lens, out, out_stride, nullptr,
+                       requests, heads, kv_heads, head_dim, page_tokens, num_pages, split_keys, splits, status, stream, &extra);
 }
 
 // Portions of prompts (and single tokens) of several requests in one launch.  q_start[r] is the

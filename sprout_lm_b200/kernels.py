@@ -35,6 +35,7 @@ _SIGNATURES = {
     "sprout_sample": [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P],
     "sprout_advance_decode": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
     "sprout_attention_decode": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_attention_decode_fused": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_gemm_bf16": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
 }
@@ -317,6 +318,44 @@ def attention_decode(q, k_cache, v_cache, block_table, context_lens, out, heads,
          k_cache.shape[0], split_keys, splits, _ptr(status, "status", torch.int32), _stream())
 
 
+def decode_fusable(requests: int, heads: int, kv_heads: int, head_dim: int, max_keys: int) -> bool:
+    """Whether the decode step's attention can take the projection's tail (bias, rotation, cache
+    append) into its own kernel: tensor-core kernel sizes and at most 8 splits."""
+    return head_dim <= 128 and head_dim % 16 == 0 and heads // kv_heads <= 16 \
+        and not decode_split_plan(requests, kv_heads, max_keys)[2]
+
+
+def attention_decode_fused(acc, bias, cos_table, sin_table, k_cache, v_cache, block_table, context_lens, out,
+                           heads, kv_heads, head_dim, status):
+    """Decode attention with the q/k/v projection's tail folded in.  ``acc`` holds, for each
+    request's new token, the float32 sums [requests, (heads + 2 kv_heads) * head_dim] of a split-K
+    product; the kernel adds ``bias``, rotates q and k by the position context_lens - 1 (tables
+    may be None), appends k and v to the paged cache, attends over context_lens keys and leaves
+    ``acc`` zeroed.  ``out`` is bfloat16 [requests, heads * head_dim]."""
+    R = out.shape[0]
+    width = (heads + 2 * kv_heads) * head_dim
+    if acc.dtype != torch.float32 or tuple(acc.shape) != (R, width) or not acc.is_contiguous():
+        raise KernelError("attention_decode_fused: acc must be contiguous float32 [requests, (heads + 2 kv_heads) * head_dim]")
+    if out.dtype != torch.bfloat16 or out.shape[1] != heads * head_dim or out.stride(1) != 1:
+        raise KernelError("attention_decode_fused: out must be bfloat16 [requests, heads * head_dim]")
+    if k_cache.shape != v_cache.shape or k_cache.dim() != 4 or k_cache.shape[3] != head_dim or k_cache.shape[1] != kv_heads \
+            or k_cache.dtype != torch.bfloat16 or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise KernelError("attention_decode_fused: caches must be contiguous bfloat16 [pages, kv_heads, page_tokens, head_dim]")
+    if bias is not None and bias.numel() != width:
+        raise KernelError("attention_decode_fused: bias must have one entry per column of acc")
+    _rows_contiguous(block_table, "block_table")
+    max_keys = block_table.shape[1] * k_cache.shape[2]
+    split_keys, splits, through_memory = decode_split_plan(R, kv_heads, max_keys)
+    if through_memory or not decode_fusable(R, heads, kv_heads, head_dim, max_keys):
+        raise KernelError("attention_decode_fused: these sizes need the separate kernels (see decode_fusable)")
+    _run("sprout_attention_decode_fused", _ptr(acc, "acc"), _ptr(bias, "bias", torch.float32, True),
+         _ptr(cos_table, "cos", torch.float32, True), _ptr(sin_table, "sin", torch.float32, True),
+         cos_table.shape[0] if cos_table is not None else 0, _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"),
+         _ptr(block_table, "block_table", torch.int32), block_table.stride(0),
+         _ptr(context_lens, "context_lens", torch.int32), _ptr(out, "out"), out.stride(0), R, heads, kv_heads, head_dim,
+         k_cache.shape[2], k_cache.shape[0], split_keys, splits, _ptr(status, "status", torch.int32), _stream())
+
+
 def attention_prefill(q, k_cache, v_cache, block_table, q_start, positions, out, heads, kv_heads, head_dim, status):
     """Tensor-core flash attention of the step's queries (portions of prompts, single tokens) over
     their requests' pages (bfloat16, float32 softmax)."""
@@ -371,5 +410,5 @@ def describe_status(word: int) -> str:
 
 
 __all__ = ["KernelError", "BuildError", "load_library", "library_file", "embed", "rmsnorm", "swiglu",
-           "rope_append", "gemm_simple", "gemm_bf16", "attention_simple", "attention_decode", "attention_prefill",
+           "rope_append", "gemm_simple", "gemm_bf16", "attention_simple", "attention_decode", "attention_decode_fused", "decode_fusable", "attention_prefill",
            "paged_attention", "sample", "advance_decode", "describe_status"]

@@ -94,6 +94,16 @@ class PagedGQAttention(Part):
             acc = self._workspace(h.device)[:tokens]
             kernels.gemm_bf16(h, self.qkv.weight, acc, self.runtime.status, residual=acc,
                               split_k=self.qkv.split_k(tokens, True))
+            attended = torch.empty((tokens, self.heads * self.head_dim), dtype=h.dtype, device=h.device)
+            max_keys = cache.block_table.shape[1] * cache.page_tokens
+            if ctx.max_q_len == 1 and cache.write and kernels.decode_fusable(tokens, self.heads, self.kv_heads,
+                                                                             self.head_dim, max_keys):
+                # one token per request: bias, rotation and the cache append happen inside the attention kernel
+                kernels.attention_decode_fused(acc, self.qkv.bias, cos, sin, cache.k, cache.v, cache.block_table,
+                                               ctx.context_lens, attended, self.heads, self.kv_heads, self.head_dim,
+                                               self.runtime.status)
+                self.out.forward(attended, residual=x)
+                return
             qkv = torch.empty((tokens, self.qkv.out_features), dtype=h.dtype, device=h.device)
             kernels.rope_append(qkv, ctx.positions, ctx.seq_of_token, cache.block_table, cos, sin, cache.k, cache.v,
                                 self.heads, self.kv_heads, self.head_dim, cache.page_tokens, cache.write,

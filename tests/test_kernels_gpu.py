@@ -338,6 +338,49 @@ def test_attention_decode_split_keys(status, heads, kv_heads, head_dim, page, le
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("rotate", [False, True])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page,lengths", DECODE_CASES[:6])
+def test_attention_decode_fused_projection_tail(status, heads, kv_heads, head_dim, page, lengths, rotate):
+    """The decode kernel that also finishes the projection: the new token's q, k, v arrive as
+    float32 sums plus a bias; the kernel rotates, appends to the cache, attends and clears the sums.
+    Compared with the separate rotary kernel followed by the decode kernel."""
+    from sprout_lm_b200 import kernels
+    from sprout_lm_b200.parts.rope import HalfSplitRotary
+    R = len(lengths)
+    case = build_paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, lengths, [1] * R, seed=3)
+    width = (heads + 2 * kv_heads) * head_dim
+    g = torch.Generator().manual_seed(11)
+    sums = torch.randn(R, width, generator=g).to(DEV)
+    bias = (torch.randn(width, generator=g) * 0.3).to(DEV)
+
+    class RT:
+        device = torch.device(DEV)
+    cos, sin = HalfSplitRotary("", head_dim, 1e4, 1024).rotary_tables(RT) if rotate else (None, None)
+    positions = (case["context_lens"] - 1).to(torch.int32)
+    seq_of_token = torch.arange(R, dtype=torch.int32, device=DEV)
+    # the separate path
+    k1, v1 = case["k_cache"].clone(), case["v_cache"].clone()
+    acc1 = torch.zeros(R + 1, width, device=DEV)
+    acc1[:R] = sums
+    qkv = torch.zeros(R, width, dtype=torch.bfloat16, device=DEV)
+    kernels.rope_append(qkv, positions, seq_of_token, case["table"], cos, sin, k1, v1, heads, kv_heads, head_dim, page,
+                        True, status, acc=acc1[:R], bias=bias)
+    want = torch.empty(R, heads * head_dim, dtype=torch.bfloat16, device=DEV)
+    kernels.attention_decode(qkv[:, :heads * head_dim], k1, v1, case["table"], case["context_lens"], want, heads,
+                             kv_heads, head_dim, status)
+    # the fused kernel
+    k2, v2 = case["k_cache"].clone(), case["v_cache"].clone()
+    acc2 = sums.clone()
+    got = torch.full_like(want, float("nan"))
+    assert kernels.decode_fusable(R, heads, kv_heads, head_dim, case["table"].shape[1] * page)
+    kernels.attention_decode_fused(acc2, bias, cos, sin, k2, v2, case["table"], case["context_lens"], got, heads,
+                                   kv_heads, head_dim, status)
+    assert torch.equal(k2, k1) and torch.equal(v2, v1)                 # the same append, bit for bit
+    assert float(acc2.abs().max()) == 0.0                               # the sums are cleared
+    assert (got.float() - want.float()).abs().max().item() <= 1.2e-2
+    assert int(status.item()) == 0
+
+
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page,lengths,q_counts", ATTN_CASES + [
     (14, 2, 64, 16, [700, 650, 2, 90], [700, 1, 2, 9]), (2, 1, 112, 8, [75], [75]), (7, 7, 96, 16, [33, 64], [2, 64])])
 def test_attention_prefill_tensor_cores(status, heads, kv_heads, head_dim, page, lengths, q_counts):
