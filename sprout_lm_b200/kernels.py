@@ -274,6 +274,9 @@ def _check_paged(q, k_cache, v_cache, block_table, out, heads, head_dim, name):
 SM_COUNT = 148
 
 
+CLUSTER_CTA_LIMIT = 3 * SM_COUNT
+
+
 def decode_split_plan(requests: int, kv_heads: int, max_keys: int) -> tuple[int, int, bool]:
     """(keys per split, splits, whether scratch memory is needed) for decode attention over at
     most ``max_keys`` keys.  Up to 8 splits are merged inside a thread-block cluster; splits are
@@ -290,7 +293,10 @@ def decode_split_plan(requests: int, kv_heads: int, max_keys: int) -> tuple[int,
         while pairs * (-(-max_keys // split_keys)) > 4 * SM_COUNT:
             split_keys *= 2
     splits = max(1, -(-max_keys // split_keys))
-    return split_keys, splits, splits > 8
+    # clusters must be co-scheduled: about 110 clusters of 5 fit the GPU at once, so a large batch
+    # would run its clusters in waves; independent CTAs merged through memory fill it evenly
+    through_memory = splits > 8 or (splits > 1 and pairs * splits > CLUSTER_CTA_LIMIT)
+    return split_keys, splits, through_memory
 
 
 def attention_decode(q, k_cache, v_cache, block_table, context_lens, out, heads, kv_heads, head_dim, status,
