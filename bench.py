@@ -200,7 +200,8 @@ def ablation(model, batch: int, prompt_len: int, steps: int, warmup: int) -> dic
     from sprout_lm_b200 import kernels
     from sprout_lm_b200.engine.batch import StepEntry
     from sprout_lm_b200.engine.step import ModelRunner
-    real = {name: getattr(kernels, name) for name in ("attention_decode", "rmsnorm", "rope_append", "gemm_bf16", "sample")}
+    real = {name: getattr(kernels, name) for name in ("attention_decode", "attention_decode_fused", "rmsnorm", "rope_append",
+                                                      "gemm_bf16", "sample")}
     gemm = real["gemm_bf16"]
     hidden, inter = model.spec.hidden_size, model.blocks[0].feed_forward.intermediate_size
     qkv_rows = model.blocks[0].mixer.qkv.out_features
@@ -212,7 +213,7 @@ def ablation(model, batch: int, prompt_len: int, steps: int, warmup: int) -> dic
 
     variants = {
         "baseline": {},
-        "attention": {"attention_decode": lambda *a, **k: None},
+        "attention": {"attention_decode": lambda *a, **k: None, "attention_decode_fused": lambda *a, **k: None},
         "rmsnorm": {"rmsnorm": lambda *a, **k: None},
         "rope_append": {"rope_append": lambda *a, **k: None},
         "gemm_qkv": {"gemm_bf16": gemm_without(lambda w, kw: w.shape[0] == qkv_rows)},
