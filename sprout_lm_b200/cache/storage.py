@@ -44,9 +44,23 @@ def cache_bytes_per_token(model, dtype: torch.dtype) -> int:
     return sum(2 * spec.kv_heads * spec.head_dim * item for spec in model.cache_specs() if spec is not None)
 
 
+class CapacityError(RuntimeError):
+    """The cache pool asked for does not fit the device's free memory."""
+
+
 class CacheStorage:
+    RESERVE_BYTES = 1 << 30          # left free for activations, logits and graph pools
+
     def __init__(self, model, manager: CacheManager, slot_group: list[int]):
         runtime = model.runtime
+        item = torch.empty((), dtype=runtime.dtype).element_size()
+        need = sum(2 * manager.pools[slot_group[slot]].num_pages * spec.kv_heads * manager.page_tokens * spec.head_dim * item
+                   for slot, spec in enumerate(model.cache_specs()) if spec is not None)
+        free, _ = torch.cuda.mem_get_info(runtime.device)
+        if need + self.RESERVE_BYTES > free:
+            raise CapacityError(f"the cache pool needs {need / 2**30:.2f} GiB ({manager.pools[0].num_pages} pages of "
+                                f"{manager.page_tokens} tokens) but only {free / 2**30:.2f} GiB of device memory is free "
+                                f"(1 GiB is kept for activations); use fewer pages")
         self.manager = manager
         self.slot_group = slot_group
         self.page_tokens = manager.page_tokens

@@ -109,6 +109,39 @@ def test_eos_stops_generation(model_dirs):
     assert result["output"] == want[:stop] and result["finish_reason"] == "eos"
 
 
+def test_sharded_folder_generates_like_the_single_file(model_dirs, tmp_path):
+    """A folder with an index of two shards against the single file it was split from
+    (after the reference's test/weight-files.test.ts:12-29)."""
+    from sprout_lm_b200 import generate, load_model
+    from sprout_lm_b200.weights import Checkpoint, write_safetensors
+    import shutil
+    single = model_dirs["B"]
+    sharded = tmp_path / "sharded"
+    sharded.mkdir()
+    shutil.copy(single / "config.json", sharded / "config.json")
+    with Checkpoint(single) as ck:
+        tensors = {n: ck.tensor(n) for n in ck.inventory()}
+    names = sorted(tensors)
+    weight_map = {}
+    for shard, members in (("model-00001-of-00002.safetensors", names[::2]), ("model-00002-of-00002.safetensors", names[1::2])):
+        write_safetensors(sharded / shard, {n: tensors[n] for n in members})
+        weight_map.update({n: shard for n in members})
+    (sharded / "model.safetensors.index.json").write_text(json.dumps({"weight_map": weight_map}))
+    rng = np.random.default_rng(6)
+    prompts = [helpers.random_tokens(rng, n, 509) for n in (7, 30)]
+    outs = [[r["output"] for r in generate(load_model(folder, dtype="float32"), prompts, max_new_tokens=6, ignore_eos=True)]
+            for folder in (single, sharded)]
+    assert outs[0] == outs[1]
+
+
+def test_a_pool_larger_than_the_device_is_refused(model_dirs):
+    from sprout_lm_b200 import EngineOptions, load_model, make_engine
+    from sprout_lm_b200.cache.storage import CapacityError
+    model = load_model(model_dirs["A"], dtype="float32")
+    with pytest.raises(CapacityError, match="device memory"):
+        make_engine(model, EngineOptions(block_size=16, num_blocks=2_000_000_000, max_sequences=2))
+
+
 def test_command_line_demo_and_generate(model_dirs):
     root = helpers.ROOT
     done = subprocess.run([sys.executable, "-m", "sprout_lm_b200", "demo", "--json", "--pressure", "--dtype", "float32",

@@ -108,6 +108,29 @@ def test_long_decoding(model_dirs, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_context(tmp_path, dtype):
+    """2,500 tokens of history: the prompt in portions of 512 (prefill over a long cache), then
+    tokens one by one with the keys of a request split over several passes per CTA and several
+    CTAs, against the plain implementation at the last 24 positions."""
+    folder = helpers.make_model_dir(tmp_path, "A", max_position_embeddings=4096)
+    requests = make_requests("A", 91, [2524])
+    toks = requests["r0"]
+    want = helpers.plain_logits(folder, toks)
+    plan, at = [], 0
+    while at < 2500:
+        n = min(512, 2500 - at)
+        plan.append({"entries": [("r0", toks[at:at + n], [n - 1])], "end": []})
+        at += n
+    plan += [{"entries": [("r0", [t], [0])], "end": []} for t in toks[2500:]]
+    runner = make_runner(folder, dtype, 2560 // 16, 16)
+    got = helpers.run_plan_in_process(runner, plan)
+    assert len(got) == 5 + 24
+    for (rid, pos), row in got.items():
+        err = float(np.abs(row - want[pos]).max())
+        assert err <= TOL[dtype], (pos, err)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_sharp_attention_shows_every_key(model_dirs, tmp_path, dtype):
     """Random weights make attention nearly uniform, which hides a lost or misplaced key under
     bfloat16 rounding.  Here the query and key projections are scaled up so that the softmax is
