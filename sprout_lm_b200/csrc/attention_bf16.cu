@@ -1015,13 +1015,22 @@ SPROUT_API int sprout_attention_decode_fused(float* acc, const float* bias, cons
                        requests, heads, kv_heads, head_dim, page_tokens, num_pages, split_keys, splits, status, stream, &extra);
 }
 
+// The tcgen05 kernel of attention_tcgen05.cu.
+SPROUT_API int sprout_attention_prefill_tc_supported(int head_dim, int page_tokens, int out_stride);
+int sprout_attention_prefill_tc(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                const int* block_table, int table_stride, const int* q_start, const int* positions,
+                                void* out, int out_stride, int num_tokens, int requests, int heads, int kv_heads,
+                                int head_dim, int page_tokens, int num_pages, int* status, cudaStream_t stream);
+
 // Portions of prompts (and single tokens) of several requests in one launch.  q_start[r] is the
 // first token of request r in the batch; a token at position pos sees keys 0..pos of its request.
+// variant: 0 chooses (the tcgen05 kernel where it takes the sizes and the requests bring 128 rows
+// each on average, else the mma.sync kernel), 1 forces mma.sync, 2 forces tcgen05.
 SPROUT_API int sprout_attention_prefill(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                         const int* block_table, int table_stride, const int* q_start,
                                         const int* positions, void* out, int out_stride, int num_tokens,
                                         int requests, int heads, int kv_heads, int head_dim, int page_tokens,
-                                        int num_pages, int* status, cudaStream_t stream) {
+                                        int num_pages, int variant, int* status, cudaStream_t stream) {
   SPROUT_REQUIRE(num_tokens > 0 && requests > 0 && heads > 0 && kv_heads > 0 && page_tokens > 0 && num_pages > 0,
                  "attention_prefill: sizes must be positive");
   SPROUT_REQUIRE(heads % kv_heads == 0, "attention_prefill: heads (%d) must be a multiple of kv_heads (%d)", heads, kv_heads);
@@ -1037,6 +1046,14 @@ SPROUT_API int sprout_attention_prefill(const void* q, int q_stride, const void*
   p.requests = requests; p.heads = heads; p.kv_heads = kv_heads; p.page_tokens = page_tokens; p.num_pages = num_pages;
   p.scale = 1.0f / sqrtf((float)head_dim); p.status = status;
   const int group = heads / kv_heads;
+  SPROUT_REQUIRE(variant >= 0 && variant <= 2, "attention_prefill: unknown variant %d", variant);
+  const bool tc_takes = sprout_attention_prefill_tc_supported(head_dim, page_tokens, out_stride) && ((uintptr_t)out & 15) == 0;
+  SPROUT_REQUIRE(variant != 2 || tc_takes, "attention_prefill: the tcgen05 kernel takes head_dim 64 or 128, pages of 8, 16, 32, 64 "
+                 "or a multiple of 128 tokens and 16-byte aligned output rows (head_dim %d, page %d)", head_dim, page_tokens);
+  if (variant == 2 || (variant == 0 && tc_takes && (long long)num_tokens * group >= 128LL * requests))
+    return sprout_attention_prefill_tc(q, q_stride, k_cache, v_cache, block_table, table_stride, q_start, positions, out,
+                                       out_stride, num_tokens, requests, heads, kv_heads, head_dim, page_tokens, num_pages,
+                                       status, stream);
   // every request has at most ceil(tokens * group / 64) tiles: an upper bound without reading q_start
   const long long bound = ((long long)num_tokens * group + PF_ROWS - 1) / PF_ROWS + requests;
   SPROUT_REQUIRE(bound <= 0x7fffffffLL, "attention_prefill: too many tokens");

@@ -23,6 +23,7 @@ enum SproutStatus : int {
   SPROUT_STATUS_NONFINITE = 4,      // non-finite logits met while sampling
   SPROUT_STATUS_WAIT_TIMEOUT = 8,   // a bounded mbarrier wait ran out
   SPROUT_STATUS_BAD_POSITION = 16,  // a position outside the rotary table
+  SPROUT_STATUS_BAD_LAYOUT = 32,    // a kernel's shared memory did not start where its tiles need it
 };
 
 int sprout_fail(const char* fmt, ...);   // records the message, returns 1

@@ -23,10 +23,9 @@
 // the CTA stops issuing, waits (bounded) for its copies in flight, frees its TMEM and returns.
 #include <cuda.h>
 
-#include <mutex>
-#include <unordered_map>
 
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 
@@ -34,7 +33,6 @@ constexpr int BLOCK_M = 128;        // rows of D per CTA == TMEM lanes
 constexpr int BLOCK_K = 64;         // bf16 elements per stage row: 128 bytes, one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 320;      // TMA warp, MMA warp, 8 epilogue warps
-constexpr uint32_t WAIT_LIMIT = 1u << 22;   // tries of mbarrier.try_wait (each blocks for a while)
 constexpr int SMEM_BUDGET = 200 * 1024;
 
 enum Epilogue : int { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_RESIDUAL_ATOMIC = 2, EPI_SWIGLU = 3 };
@@ -55,77 +53,6 @@ struct Params {
   int* status;
 };
 
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Bounded wait for the phase with the given parity; false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t tries = 0; tries < WAIT_LIMIT; tries++) {
-    uint32_t done;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// The mbarrier gets one arrival when every MMA this thread issued so far has completed.
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, swizzled in
-// 8-row groups of 1024 bytes (what TMA's 128-byte swizzle writes): start address / 16 in bits
-// 0-13, the 1024-byte stride between row groups / 16 in bits 32-45, descriptor version 1 in
-// bits 46-47, layout type 2 (128-byte swizzle) in bits 61-63.
-__device__ __forceinline__ uint64_t umma_smem_desc(const void* tile) {
-  uint64_t desc = 0;
-  desc |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);
-  desc |= (uint64_t)(1024 >> 4) << 32;
-  desc |= (uint64_t)1 << 46;
-  desc |= (uint64_t)2 << 61;
-  return desc;
-}
-// Instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, N and M sizes.
-__device__ __forceinline__ uint32_t umma_idesc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
 template <int BN>
 struct Layout {
   static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
@@ -136,10 +63,6 @@ struct Layout {
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;     // two accumulators
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 };
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 
 // One unit of work: a 128 x BN tile of D over a range of K blocks.
 struct Work { int row0, col0, kb_begin, num_kb, split; };
@@ -386,71 +309,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_fn() {
-  static EncodeTiled fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
-        result == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiled)ptr;
-  });
-  return fn;
-}
-
-struct MapKey {
-  const void* ptr; int rows, cols, ld, box_rows;
-  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
-};
-struct MapHash {
-  size_t operator()(const MapKey& k) const {
-    size_t h = (size_t)k.ptr;
-    for (int v : {k.rows, k.cols, k.ld, k.box_rows}) h = h * 1000003u ^ (size_t)v;
-    return h;
-  }
-};
-
-// A 2-D bf16 tensor map over [rows, cols] with row stride ld elements, boxes of box_rows x 64,
-// 128-byte swizzle, zero fill outside.  Maps are cached: an encode costs a few microseconds.
-int tensor_map(const void* ptr, int rows, int cols, int ld, int box_rows, CUtensorMap* out) {
-  static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
-  static std::mutex lock;
-  MapKey key{ptr, rows, cols, ld, box_rows};
-  std::lock_guard<std::mutex> guard(lock);
-  auto it = cache.find(key);
-  if (it != cache.end()) { *out = it->second; return 0; }
-  EncodeTiled encode = encode_fn();
-  if (!encode) return sprout_fail("gemm_bf16: cuTensorMapEncodeTiled is not available from the driver");
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
-  cuuint32_t elem[2] = {1, 1};
-  CUtensorMap map;
-  CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (rc != CUDA_SUCCESS) return sprout_fail("gemm_bf16: cuTensorMapEncodeTiled failed with code %d", (int)rc);
-  if (cache.size() > 4096) cache.clear();
-  cache.emplace(key, map);
-  *out = map;
-  return 0;
-}
-
-int sm_count() {
-  static int count = 0;
-  if (!count) {
-    int device = 0;
-    cudaGetDevice(&device);
-    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0) count = 148;
-  }
-  return count;
-}
-
 // `work` = tiles x K splits; the grid is one CTA per SM at most, each walking the work list.
 template <int BN, bool SWAP>
 int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const Params& p, int work, cudaStream_t stream) {

@@ -17,7 +17,8 @@ from .csrc.build import BuildError, library_path
 F32, BF16 = 0, 1
 LAUNCHES = 0          # kernels launched through this module (one per call); benchmarks read the difference
 STATUS_BITS = {1: "a block-table entry outside the page pool", 2: "a token id outside the vocabulary",
-               4: "non-finite logits", 8: "a bounded device-side wait ran out", 16: "a position outside the rotary table"}
+               4: "non-finite logits", 8: "a bounded device-side wait ran out", 16: "a position outside the rotary table",
+               32: "a kernel's shared memory was not aligned for its tiles"}
 
 
 class KernelError(RuntimeError):
@@ -36,7 +37,9 @@ _SIGNATURES = {
     "sprout_advance_decode": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
     "sprout_attention_decode": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_attention_decode_fused": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
-    "sprout_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_attention_prefill_tc_supported": [_I, _I, _I],
+    "sprout_attention_prefill_tc_occupancy": [_I],
     "sprout_gemm_bf16": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
 }
 
@@ -362,14 +365,22 @@ def attention_decode_fused(acc, bias, cos_table, sin_table, k_cache, v_cache, bl
          k_cache.shape[2], k_cache.shape[0], split_keys, splits, _ptr(status, "status", torch.int32), _stream())
 
 
-def attention_prefill(q, k_cache, v_cache, block_table, q_start, positions, out, heads, kv_heads, head_dim, status):
+PREFILL_VARIANTS = {"auto": 0, "mma_sync": 1, "tcgen05": 2}
+
+
+def attention_prefill(q, k_cache, v_cache, block_table, q_start, positions, out, heads, kv_heads, head_dim, status,
+                      variant="auto"):
     """Tensor-core flash attention of the step's queries (portions of prompts, single tokens) over
-    their requests' pages (bfloat16, float32 softmax)."""
+    their requests' pages (bfloat16, float32 softmax).  ``variant``: "tcgen05" (S and P V in tensor
+    memory, K and V pages by TMA; head_dim 64 or 128, pages of 8..64 or a multiple of 128 tokens),
+    "mma_sync" (every head_dim up to 128 in steps of 16, every page size), or "auto": tcgen05
+    where it takes the sizes and the requests bring 128 (token, head) rows each on average."""
     _check_paged(q, k_cache, v_cache, block_table, out, heads, head_dim, "attention_prefill")
     _run("sprout_attention_prefill", _ptr(q, "q"), q.stride(0), _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"),
          _ptr(block_table, "block_table", torch.int32), block_table.stride(0), _ptr(q_start, "q_start", torch.int32),
          _ptr(positions, "positions", torch.int32), _ptr(out, "out"), out.stride(0), q.shape[0], q_start.numel() - 1,
-         heads, kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], _ptr(status, "status", torch.int32), _stream())
+         heads, kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], PREFILL_VARIANTS[variant],
+         _ptr(status, "status", torch.int32), _stream())
 
 
 def paged_attention(q, cache, ctx, out, heads, kv_heads, head_dim, status):

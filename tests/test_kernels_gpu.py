@@ -221,17 +221,18 @@ def attention_reference(q, keys, values, heads, kv_heads, head_dim):
     return out
 
 
-def build_paged_case(dtype, heads, kv_heads, head_dim, page, lengths, q_counts, seed=0, spike=None):
+def build_paged_case(dtype, heads, kv_heads, head_dim, page, lengths, q_counts, seed=0, spike=None, poison=False):
     """Requests with ``lengths`` cached positions each (the last ``q_counts`` of them are this
-    step's queries), in pages scattered over the pool."""
+    step's queries), in pages scattered over the pool.  ``poison``: every slot that holds no key
+    of a request (the rest of a last page, pages nobody owns) is NaN instead of zero."""
     g = torch.Generator().manual_seed(seed)
     R = len(lengths)
     pages_each = [-(-n // page) for n in lengths]
     pool = sum(pages_each) + 3
     order = torch.randperm(pool, generator=g)
     table = torch.full((R, max(pages_each)), -1, dtype=torch.int32)
-    k_cache = torch.zeros(pool, kv_heads, page, head_dim)
-    v_cache = torch.zeros(pool, kv_heads, page, head_dim)
+    k_cache = torch.full((pool, kv_heads, page, head_dim), float("nan") if poison else 0.0)
+    v_cache = torch.full((pool, kv_heads, page, head_dim), float("nan") if poison else 0.0)
     keys, values, at = [], [], 0
     for r, n in enumerate(lengths):
         k = torch.randn(n, kv_heads * head_dim, generator=g)
@@ -391,6 +392,59 @@ def test_attention_prefill_tensor_cores(status, heads, kv_heads, head_dim, page,
                               case["positions"], out, heads, kv_heads, head_dim, status)
     assert (out.double().cpu() - case["want"]).abs().max().item() <= 1.5e-2
     assert int(status.item()) == 0
+
+
+TC_PREFILL_CASES = [
+    # heads, kv_heads, head_dim, page, cached lengths, queries of this step
+    (14, 2, 64, 16, [700, 650, 2, 90], [700, 1, 2, 9]),       # several key tiles, rows of several requests
+    (4, 2, 64, 8, [129, 128, 127], [129, 128, 1]),            # the edges of a key tile
+    (8, 2, 128, 16, [300, 64], [37, 64]),                     # head_dim 128: two 64-element blocks, one P buffer
+    (3, 1, 64, 32, [513], [200]),                             # a portion in the middle of a long request
+    (2, 2, 128, 64, [260, 5], [260, 5]),
+    (5, 1, 64, 128, [400], [400]),                            # a page as long as a key tile
+    (2, 1, 64, 256, [600, 100], [90, 100]),                   # pages longer than a key tile
+    (16, 1, 64, 16, [45], [45]),                              # many heads per key head: a tile holds few tokens
+]
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page,lengths,q_counts", TC_PREFILL_CASES)
+def test_attention_prefill_tcgen05(status, heads, kv_heads, head_dim, page, lengths, q_counts):
+    """The tcgen05 prefill kernel against the float64 reference, with NaN in every cache slot
+    that holds no key: a kernel that lets one of them into a product shows it."""
+    from sprout_lm_b200 import kernels
+    case = build_paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, lengths, q_counts, seed=5, poison=True)
+    out = torch.full((case["T"], heads * head_dim), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.attention_prefill(case["q"], case["k_cache"], case["v_cache"], case["table"], case["q_start"],
+                              case["positions"], out, heads, kv_heads, head_dim, status, variant="tcgen05")
+    assert int(status.item()) == 0
+    err = (out.double().cpu() - case["want"]).abs().max(dim=1).values
+    assert float(err.max()) <= 1.5e-2, f"token {int(err.argmax())} of {case['T']} differs by {float(err.max()):.3e}"
+    # the other kernel on the same case (it must not read the poisoned slots either)
+    again = torch.full_like(out, float("nan"))
+    kernels.attention_prefill(case["q"], case["k_cache"], case["v_cache"], case["table"], case["q_start"],
+                              case["positions"], again, heads, kv_heads, head_dim, status, variant="mma_sync")
+    assert float((again.double().cpu() - case["want"]).abs().max()) <= 1.5e-2
+
+
+def test_attention_prefill_tcgen05_refuses_other_sizes(status):
+    from sprout_lm_b200 import kernels
+    case = build_paged_case(torch.bfloat16, 4, 2, 48, 16, [40], [40])
+    out = torch.empty(case["T"], 4 * 48, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(kernels.KernelError, match="head_dim 64 or 128"):
+        kernels.attention_prefill(case["q"], case["k_cache"], case["v_cache"], case["table"], case["q_start"],
+                                  case["positions"], out, 4, 2, 48, status, variant="tcgen05")
+
+
+@pytest.mark.parametrize("where", [0, 127, 128, 255, 256, 700, 1023])
+def test_tcgen05_prefill_finds_one_far_key(status, where):
+    """One key among 1,024 whose score stands out, at the edges of the 128-key tiles."""
+    from sprout_lm_b200 import kernels
+    heads, kv_heads, head_dim, page = 4, 2, 64, 16
+    case = build_paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, [1024], [40], seed=where, spike=(0, where))
+    out = torch.empty(case["T"], heads * head_dim, dtype=torch.bfloat16, device=DEV)
+    kernels.attention_prefill(case["q"], case["k_cache"], case["v_cache"], case["table"], case["q_start"],
+                              case["positions"], out, heads, kv_heads, head_dim, status, variant="tcgen05")
+    assert (out.double().cpu() - case["want"]).abs().max().item() <= 1.5e-2
 
 
 @pytest.mark.parametrize("where", [0, 15, 16, 63, 64, 255, 256, 383, 500])
