@@ -1,26 +1,30 @@
 // Prefill attention over the paged cache on the fifth-generation tensor cores (sm_100a).
 //
-// One CTA owns 128 rows, a row being a (token, query head) pair of one request and one key/value
-// head, and walks the request's keys in tiles of 128:
+// One CTA owns 256 rows, a row being a (token, query head) pair of one request and one key/value
+// head, as two Q tiles of 128 rows, and walks the request's keys in tiles (128 keys for head_dim
+// 64, 64 keys for head_dim 128).  For each Q tile and key tile:
 //
-//   S = Q K^T      tcgen05.mma, Q and K K-major in shared memory, S in tensor memory (2 buffers)
-//   softmax        four warps, one thread per row: tcgen05.ld of its row of S, running maximum and
-//                  sum in float32, P = exp2(..) written as bfloat16 into shared memory in the
-//                  K-major swizzled layout the next product reads
+//   S = Q K^T      tcgen05.mma, Q and K K-major in shared memory, S in tensor memory
+//   softmax        a warpgroup per Q tile, one thread per row: tcgen05.ld of its row of S, running
+//                  maximum and sum in float32, P = exp2(..) written as bfloat16 into shared memory
+//                  in the K-major swizzled layout the next product reads
 //   O_tile = P V   tcgen05.mma, V as it lies in the cache ([key, head_dim]: MN-major B operand),
 //                  the tile's product in tensor memory; the row's thread adds it to its float32
 //                  accumulator in registers, rescaled when the maximum moved
 //
+// The two Q tiles alternate: while the softmax warpgroup of one works on its S, the tensor cores
+// run P V and the next S of the other.  (A kernel that allocates tensor memory gets one CTA per
+// SM, so the overlap has to happen inside the CTA.)  The softmax warpgroups take the registers
+// that the copy/MMA warpgroup gives up: a row's thread holds head_dim accumulators and a whole
+// row of S.
+//
 // K and V tiles come by TMA, one box per page (a page of one head is `page_tokens` contiguous
 // rows of the cache), through a two-stage ring.  One warp looks the pages up and issues the
-// copies (a lane per box), one thread issues the MMAs.  With head_dim 64 two CTAs share an SM, and
-// the softmax of one runs under the MMAs of the other; with head_dim 128 there is one CTA per SM,
-// S has two buffers and S(j+1) is issued before P(j) V(j), so that it runs under the softmax of
-// tile j.
-// Every mbarrier wait is bounded: on a timeout the CTA sets the status word, waits (bounded) for
-// its copies in flight, frees its tensor memory and returns.
+// copies (a lane per box), one thread issues the MMAs.  Every mbarrier wait is bounded: on a
+// timeout the CTA sets the status word, waits (bounded) for its copies in flight, frees its
+// tensor memory and returns.
 //
-// Takes head_dim 64 or 128 and page sizes that divide 128 (from 8) or are multiples of 128; the
+// Takes head_dim 64 or 128 and page sizes of 8, 16, 32, 64 or a multiple of 128 tokens; the
 // mma.sync kernel in attention_bf16.cu takes everything else.
 #include <cuda_bf16.h>
 
@@ -29,9 +33,12 @@
 
 namespace {
 
-constexpr int TC_ROWS = 128, TC_KEYS = 128, KV_STAGES = 2;
-constexpr int TC_THREADS = 256;           // warpgroup 0: copy warp, MMA warp (two warps idle); warpgroup 1: softmax
-constexpr int ATOM_BYTES = 128 * 128;     // a [128 rows, 64 bf16] swizzled tile
+constexpr int TC_ROWS = 128;              // rows of a Q tile == TMEM lanes
+constexpr int TC_QTILES = 2;              // Q tiles of a CTA
+constexpr int KV_STAGES = 2;
+constexpr int TC_THREADS = 384;           // warpgroup 0: copy warp, MMA warp (two warps idle); 1, 2: softmax of Q tile 0, 1
+constexpr int TC_TMEM_COLS = 512;
+constexpr int Q_ATOM_BYTES = 128 * 128;   // a [128 rows, 64 bf16] swizzled tile
 
 struct TcParams {
   const __nv_bfloat16* q; int q_stride;
@@ -44,37 +51,73 @@ struct TcParams {
   int* status;
 };
 
-// head_dim 64: one S buffer, 112 KB of shared memory, 256 columns of tensor memory and 128
-// registers a thread at launch, so that two CTAs share an SM and one's softmax runs under the
-// other's MMAs; the softmax warpgroup takes the registers that the other warpgroup gives up.
-// head_dim 128: the row's 128 accumulators leave room for one CTA per SM; S has two buffers,
-// and S(j+1) runs under the softmax of tile j.
 template <int HD>
 struct TcLayout {
   static constexpr int KB = HD / 64;                       // 64-element blocks along head_dim
-  static constexpr int CTAS_PER_SM = HD == 64 ? 2 : 1;
-  static constexpr int S_BUFFERS = HD == 64 ? 1 : 2;
-  static constexpr int TMEM_COLS = HD == 64 ? 256 : 512;   // S buffers, then the O tile
-  static constexpr int O_COLUMN = S_BUFFERS * TC_KEYS;
-  static constexpr int Q_BYTES = KB * ATOM_BYTES;
-  static constexpr int KV_BYTES = KB * ATOM_BYTES;         // one stage of K (or of V)
-  static constexpr int P_BYTES = 2 * ATOM_BYTES;           // [128 rows, 128 keys]
-  static constexpr int OFF_K = Q_BYTES;
+  static constexpr int KEYS = HD == 64 ? 128 : 64;         // keys of a tile: a softmax thread holds HD + KEYS floats
+  static constexpr int KV_ATOM_BYTES = KEYS * 128;         // [KEYS rows, 64 bf16]
+  static constexpr int Q_BYTES = KB * Q_ATOM_BYTES;        // one Q tile
+  static constexpr int KV_BYTES = KB * KV_ATOM_BYTES;      // one stage of K (or of V)
+  static constexpr int P_BYTES = (KEYS / 64) * Q_ATOM_BYTES;   // [128 rows, KEYS keys] of one Q tile
+  static constexpr int OFF_K = TC_QTILES * Q_BYTES;
   static constexpr int OFF_V = OFF_K + KV_STAGES * KV_BYTES;
   static constexpr int OFF_P = OFF_V + KV_STAGES * KV_BYTES;
-  static constexpr int OFF_BAR = OFF_P + P_BYTES;
-  static constexpr int SMEM_BYTES = OFF_BAR + 128;
+  static constexpr int OFF_BAR = OFF_P + TC_QTILES * P_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256;
+  static constexpr int O_COLUMN = TC_QTILES * KEYS;        // tensor memory: S of the Q tiles, then their O tiles
+  static_assert(O_COLUMN + TC_QTILES * HD <= TC_TMEM_COLS, "tensor memory columns");
 };
 
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// Two float32 in one 64-bit register pair: sm_100a adds, multiplies and fuses them pairwise in
+// one instruction, which halves the FMA-pipe work of the softmax.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_pack(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// 2^x for x <= 0 (a probability): the hardware approximation, results below the normal range are zero
+__device__ __forceinline__ float exp2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int HD>
-__global__ void __launch_bounds__(TC_THREADS, TcLayout<HD>::CTAS_PER_SM)
+__global__ void __launch_bounds__(TC_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const TcParams p) {
   using L = TcLayout<HD>;
-  // no static shared memory and no slack: the swizzled tiles need the dynamic region to start on
-  // a 1024-byte boundary, which is checked below
+  constexpr int KEYS = L::KEYS;
+  // no static shared memory: the swizzled tiles need the dynamic region to start on a 1024-byte
+  // boundary, which is checked below
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;
   uint8_t* sK = smem + L::OFF_K;
@@ -85,10 +128,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   uint64_t* k_empty = bars + 2;       // [2] the MMAs that read a K stage have completed
   uint64_t* v_full = bars + 4;
   uint64_t* v_empty = bars + 6;
-  uint64_t* s_full = bars + 8;        // [2] S of a tile is complete in tensor memory
-  uint64_t* p_full = bars + 10;       // [1] P of a tile is written to shared memory (4 warps arrive)
-  uint64_t* o_full = bars + 11;       // [1] P V of a tile is complete in tensor memory
-  uint32_t* tmem_slot = (uint32_t*)(bars + 12);
+  uint64_t* s_full = bars + 8;        // [2] S of a Q tile's key tile is complete in tensor memory
+  uint64_t* o_full = bars + 10;       // [2] P V of a Q tile's key tile is complete in tensor memory
+  uint64_t* p_full = bars + 12;       // [2] P of a Q tile's key tile is written to shared memory (4 warps arrive)
+  uint32_t* tmem_slot = (uint32_t*)(bars + 14);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   pdl_launch_dependents();
@@ -96,14 +139,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = blockIdx.x % p.kv_heads;
   const int group = p.heads / p.kv_heads;
+  constexpr int CTA_ROWS = TC_QTILES * TC_ROWS;
 
-  // which request and which 128-row tile of it: the tiles of a request are handed out from the
-  // last (the longest under the causal mask) to the first, the heads of a tile side by side
-  int r = 0, tile = blockIdx.x / p.kv_heads;
+  // which request and which 256-row piece of it: the pieces of a request are handed out from the
+  // last (the longest under the causal mask) to the first, the heads of a piece side by side
+  int r = 0, piece = blockIdx.x / p.kv_heads;
   for (; r < p.requests; r++) {
-    const int tiles = ((p.q_start[r + 1] - p.q_start[r]) * group + TC_ROWS - 1) / TC_ROWS;
-    if (tile < tiles) { tile = tiles - 1 - tile; break; }
-    tile -= tiles;
+    const int pieces = ((p.q_start[r + 1] - p.q_start[r]) * group + CTA_ROWS - 1) / CTA_ROWS;
+    if (piece < pieces) { piece = pieces - 1 - piece; break; }
+    piece -= pieces;
   }
   if (r >= p.requests) return;
   if ((smem_u32(smem) & 1023) != 0) {
@@ -112,34 +156,37 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   }
   const int q0 = p.q_start[r], q_count = p.q_start[r + 1] - q0;
   const int rows_total = q_count * group;
-  const int row_base = tile * TC_ROWS;
+  const int row_base = piece * CTA_ROWS;
   const int* table = p.block_table + (size_t)r * p.table_stride;
-  // positions grow with the row index: the last row of the tile sees the most keys
-  const int max_limit = p.positions[q0 + (min(rows_total, row_base + TC_ROWS) - 1) / group];
-  const int n_tiles = max_limit / TC_KEYS + 1;
+  // positions grow with the row index: the last row of a Q tile sees the most keys
+  const bool two = row_base + TC_ROWS < rows_total;       // the second Q tile has rows
+  const int limit_a = p.positions[q0 + (min(rows_total, row_base + TC_ROWS) - 1) / group];
+  const int max_limit = two ? p.positions[q0 + (min(rows_total, row_base + CTA_ROWS) - 1) / group] : limit_a;
+  const int tiles_a = limit_a / KEYS + 1;                  // key tiles that Q tile 0 needs
+  const int n_tiles = max_limit / KEYS + 1;                // and Q tile 1 (or the CTA)
 
   // rows of a stage that no copy fills (keys beyond the request) must hold finite numbers: their
   // probabilities are zero, and zero times a stale NaN is not
   for (int i = tid; i < 2 * KV_STAGES * L::KV_BYTES / 16; i += TC_THREADS) ((uint4*)sK)[i] = make_uint4(0, 0, 0, 0);
   if (tid == 0) {
-    for (int i = 0; i < 10; i++) mbar_init(&bars[i], 1);
-    mbar_init(&p_full[0], 4);
-    mbar_init(&o_full[0], 1);
+    for (int i = 0; i < 12; i++) mbar_init(&bars[i], 1);
+    mbar_init(&p_full[0], 4); mbar_init(&p_full[1], 4);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(tmem_slot, L::TMEM_COLS);
+  if (warp == 1) tmem_alloc(tmem_slot, TC_TMEM_COLS);
 
   // Q rows -> shared memory, K-major with the 128-byte swizzle (16-byte chunk c of row r at chunk
-  // position c ^ (r & 7)), one 16 KB atom per 64 elements of head_dim; a row is a (token, head) pair
+  // position c ^ (r & 7)), one 16 KB atom per Q tile and 64 elements of head_dim
   constexpr int CHUNKS = HD / 8;
-  for (int idx = tid; idx < TC_ROWS * CHUNKS; idx += TC_THREADS) {
-    const int row = idx / CHUNKS, c = idx % CHUNKS;
-    const int gi = row_base + row;
+  for (int idx = tid; idx < CTA_ROWS * CHUNKS; idx += TC_THREADS) {
+    const int crow = idx / CHUNKS, c = idx % CHUNKS;
+    const int gi = row_base + crow;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (gi < rows_total)
       v = *(const uint4*)(p.q + (size_t)(q0 + gi / group) * p.q_stride + (size_t)(g * group + gi % group) * HD + c * 8);
-    *(uint4*)(sQ + (c >> 3) * ATOM_BYTES + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = v;
+    const int row = crow & (TC_ROWS - 1);
+    *(uint4*)(sQ + (crow >> 7) * L::Q_BYTES + (c >> 3) * Q_ATOM_BYTES + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = v;
   }
   fence_proxy_async();
   tc_fence_before();
@@ -147,228 +194,262 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  int k_issued = 0, v_issued = 0;                     // tiles whose copies were issued (lane 0 of the producer warp)
+  int k_issued = 0, v_issued = 0;                     // tiles whose copies were issued (lane 0 of the copy warp)
   if (warp < 4) {
-#ifndef PROBE_NO_SETMAXNREG
-  if (L::CTAS_PER_SM == 2) warpgroup_regs_give<56>();
-#endif
-  if (warp == 0) {
-    // ---------------- producer: one TMA box per page (or per 128 keys of a larger page); lane b
-    // looks box b's page up and issues its copies, lane 0 waits for the stage and posts the bytes
-    const int boxes = TC_KEYS / p.box_rows;
-    auto box_row = [&](int j) {
-      const int key = j * TC_KEYS + lane * p.box_rows;
-      if (lane >= boxes || j >= n_tiles || key > max_limit) return -1;
-      const int page = table[key / p.page_tokens];
-      if (page < 0 || page >= p.num_pages) { atomicOr(p.status, SPROUT_STATUS_BAD_PAGE); return -1; }
-      return (page * p.kv_heads + g) * p.page_tokens + key % p.page_tokens;
-    };
-    int next_row = box_row(0);
-    for (int j = 0; j < n_tiles; j++) {
-      const int s = j % KV_STAGES;
-      const uint32_t parity = ((j / KV_STAGES) & 1) ^ 1;
-      const int row_at = next_row;
-      const uint32_t bytes = (uint32_t)__popc(__ballot_sync(0xffffffffu, row_at >= 0)) * p.box_rows * 128 * L::KB;
+    warpgroup_regs_give<56>();
+    if (warp == 0) {
+      // ---------------- copies: one TMA box per page (or per KEYS keys of a larger page); lane b
+      // looks box b's page up and issues its copies, lane 0 waits for the stage and posts the bytes
+      const int boxes = KEYS / p.box_rows;
+      auto box_row = [&](int j) {
+        const int key = j * KEYS + lane * p.box_rows;
+        if (lane >= boxes || j >= n_tiles || key > max_limit) return -1;
+        const int page = table[key / p.page_tokens];
+        if (page < 0 || page >= p.num_pages) { atomicOr(p.status, SPROUT_STATUS_BAD_PAGE); return -1; }
+        return (page * p.kv_heads + g) * p.page_tokens + key % p.page_tokens;
+      };
+      int next_row = box_row(0);
+      for (int j = 0; j < n_tiles; j++) {
+        const int s = j % KV_STAGES;
+        const uint32_t parity = ((j / KV_STAGES) & 1) ^ 1;
+        const int row_at = next_row;
+        const uint32_t bytes = (uint32_t)__popc(__ballot_sync(0xffffffffu, row_at >= 0)) * p.box_rows * 128 * L::KB;
+        bool ok = true;
+        if (lane == 0) {
+          ok = !*abort_flag && mbar_wait(&k_empty[s], parity);
+          if (ok) mbar_expect_tx(&k_full[s], bytes);
+          else { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); }
+        }
+        if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+        if (row_at >= 0)
+          for (int kb = 0; kb < L::KB; kb++)
+            tma_load_2d(sK + s * L::KV_BYTES + kb * L::KV_ATOM_BYTES + lane * p.box_rows * 128, &map_k, &k_full[s], kb * 64, row_at);
+        k_issued = j + 1;
+        next_row = box_row(j + 1);                    // the lookup runs under the wait below
+        if (lane == 0) {
+          ok = !*abort_flag && mbar_wait(&v_empty[s], parity);
+          if (ok) mbar_expect_tx(&v_full[s], bytes);
+          else { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); }
+        }
+        if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+        if (row_at >= 0)
+          for (int kb = 0; kb < L::KB; kb++)
+            tma_load_2d(sV + s * L::KV_BYTES + kb * L::KV_ATOM_BYTES + lane * p.box_rows * 128, &map_v, &v_full[s], kb * 64, row_at);
+        v_issued = j + 1;
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ---------------- MMA issuer.  Order: S0(0) S1(0), then for every key tile
+      //   [P0(j)] P0 V(j), S0(j+1), [P1(j)] P1 V(j), S1(j+1)
+      // so that the products of one Q tile run under the softmax of the other.  S of a Q tile has
+      // one buffer: S(j+1) follows the wait for P(j), by which the softmax warps have read S(j).
+      const uint32_t idesc_s = umma_idesc(TC_ROWS, KEYS);
+      const uint32_t idesc_o = umma_idesc_b_mn(TC_ROWS, HD);
       bool ok = true;
-      if (lane == 0) {
-        ok = !*abort_flag && mbar_wait(&k_empty[s], parity);
-        if (ok) mbar_expect_tx(&k_full[s], bytes);
-        else { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); }
+      auto fail = [&]() { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); ok = false; };
+      auto issue_s = [&](int q, int j) {             // the K stage of tile j has been waited for
+        const int s = j % KV_STAGES;
+#pragma unroll
+        for (int kb = 0; kb < L::KB; kb++) {
+          const uint64_t a = umma_smem_desc(sQ + q * L::Q_BYTES + kb * Q_ATOM_BYTES);
+          const uint64_t b = umma_smem_desc(sK + s * L::KV_BYTES + kb * L::KV_ATOM_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < 4; kk++) umma_bf16(tmem_base + q * KEYS, a + 2 * kk, b + 2 * kk, idesc_s, (kb | kk) != 0);
+        }
+        umma_commit(&s_full[q]);
+      };
+      auto issue_pv = [&](int q, int j) {
+        const int s = j % KV_STAGES;
+#pragma unroll
+        for (int ks = 0; ks < KEYS / 16; ks++) {
+          const uint64_t a = umma_smem_desc(sP + q * L::P_BYTES + (ks >> 2) * Q_ATOM_BYTES) + 2 * (ks & 3);
+          const uint64_t b = umma_smem_desc_mn(sV + s * L::KV_BYTES + ks * 2048, L::KV_ATOM_BYTES);
+          umma_bf16(tmem_base + L::O_COLUMN + q * HD, a, b, idesc_o, ks != 0);
+        }
+        umma_commit(&o_full[q]);
+      };
+      // the last product that reads a stage releases it: S1 (or S0 where Q tile 1 has no rows)
+      // for K, P1 V (or P0 V) for V; Q tile 0 stops after tiles_a tiles
+      if (*abort_flag || !mbar_wait(&k_full[0], 0)) fail();
+      if (ok) {
+        tc_fence_after();
+        issue_s(0, 0);
+        if (two) issue_s(1, 0);
+        umma_commit(&k_empty[0]);
       }
-      if (!__shfl_sync(0xffffffffu, ok, 0)) break;
-      if (row_at >= 0)
-        for (int kb = 0; kb < L::KB; kb++)
-          tma_load_2d(sK + s * L::KV_BYTES + kb * ATOM_BYTES + lane * p.box_rows * 128, &map_k, &k_full[s], kb * 64, row_at);
-      k_issued = j + 1;
-      next_row = box_row(j + 1);                      // the lookup runs under the wait below
-      if (lane == 0) {
-        ok = !*abort_flag && mbar_wait(&v_empty[s], parity);
-        if (ok) mbar_expect_tx(&v_full[s], bytes);
-        else { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); }
+      for (int j = 0; j < n_tiles && ok; j++) {
+        const int s = j % KV_STAGES, s_next = (j + 1) % KV_STAGES;
+        const bool more = j + 1 < n_tiles;
+        if (*abort_flag || !mbar_wait(&v_full[s], (j / KV_STAGES) & 1)) { fail(); break; }
+        if (j < tiles_a) {
+          if (*abort_flag || !mbar_wait(&p_full[0], j & 1)) { fail(); break; }
+          tc_fence_after();
+          issue_pv(0, j);
+          if (!two) umma_commit(&v_empty[s]);
+        }
+        if (more && (*abort_flag || !mbar_wait(&k_full[s_next], ((j + 1) / KV_STAGES) & 1))) { fail(); break; }
+        if (more && j + 1 < tiles_a) {
+          tc_fence_after();
+          issue_s(0, j + 1);
+          if (!two) umma_commit(&k_empty[s_next]);
+        }
+        if (two) {
+          if (*abort_flag || !mbar_wait(&p_full[1], j & 1)) { fail(); break; }
+          tc_fence_after();
+          issue_pv(1, j);
+          umma_commit(&v_empty[s]);
+          if (more) {
+            issue_s(1, j + 1);
+            umma_commit(&k_empty[s_next]);
+          }
+        }
       }
-      if (!__shfl_sync(0xffffffffu, ok, 0)) break;
-      if (row_at >= 0)
-        for (int kb = 0; kb < L::KB; kb++)
-          tma_load_2d(sV + s * L::KV_BYTES + kb * ATOM_BYTES + lane * p.box_rows * 128, &map_v, &v_full[s], kb * 64, row_at);
-      v_issued = j + 1;
     }
-  } else if (warp == 1 && lane == 0) {
-    // ---------------- MMA issuer
-    const uint32_t idesc_s = umma_idesc(TC_ROWS, TC_KEYS);
-    const uint32_t idesc_o = umma_idesc_b_mn(TC_ROWS, HD);
-    bool ok = true;
-    auto issue_s = [&](int j) {
-      const int s = j % KV_STAGES;
-      if (*abort_flag || !mbar_wait(&k_full[s], (j / KV_STAGES) & 1)) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); ok = false; return; }
-      tc_fence_after();
-      const uint32_t d = tmem_base + (j % L::S_BUFFERS) * TC_KEYS;
-#pragma unroll
-      for (int kb = 0; kb < L::KB; kb++) {
-        const uint64_t a = umma_smem_desc(sQ + kb * ATOM_BYTES), b = umma_smem_desc(sK + s * L::KV_BYTES + kb * ATOM_BYTES);
-#pragma unroll
-        for (int kk = 0; kk < 4; kk++) umma_bf16(d, a + 2 * kk, b + 2 * kk, idesc_s, (kb | kk) != 0);
-      }
-      umma_commit(&k_empty[s]);
-      umma_commit(&s_full[j % L::S_BUFFERS]);
-    };
-    issue_s(0);
-    for (int j = 0; j < n_tiles && ok; j++) {
-      // with two S buffers, S of the next tile runs under the softmax of this one (its buffer held
-      // S(j-1), which the softmax warps had read before they signalled P(j-1)); with one, it
-      // follows P(j) V(j), after the softmax warps have read S(j)
-      if (L::S_BUFFERS == 2 && j + 1 < n_tiles) { issue_s(j + 1); if (!ok) break; }
-      const int s = j % KV_STAGES;
-      if (*abort_flag || !mbar_wait(&p_full[0], j & 1) || !mbar_wait(&v_full[s], (j / KV_STAGES) & 1)) {
-        *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); break;
-      }
-      tc_fence_after();
-#pragma unroll
-      for (int ks = 0; ks < TC_KEYS / 16; ks++) {
-        const uint64_t a = umma_smem_desc(sP + (ks >> 2) * ATOM_BYTES) + 2 * (ks & 3);
-        const uint64_t b = umma_smem_desc_mn(sV + s * L::KV_BYTES + ks * 2048, ATOM_BYTES);
-        umma_bf16(tmem_base + L::O_COLUMN, a, b, idesc_o, ks != 0);
-      }
-      umma_commit(&v_empty[s]);
-      umma_commit(&o_full[0]);
-      if (L::S_BUFFERS == 1 && j + 1 < n_tiles) issue_s(j + 1);
-    }
-  }
   } else {
-    // ---------------- softmax and accumulation: one thread per row
-#ifndef PROBE_NO_SETMAXNREG
-    if (L::CTAS_PER_SM == 2) warpgroup_regs_take<200>();
-#endif
+    // ---------------- softmax and accumulation: a warpgroup per Q tile, one thread per row
+    warpgroup_regs_take<224>();
+    const int q = (warp >> 2) - 1;
+    const int my_tiles = q == 0 ? tiles_a : (two ? n_tiles : 0);
     const int quarter = warp & 3;                      // a warp reads TMEM lanes 32 * (warp % 4) ..
     const int row = quarter * 32 + lane;
-    const int gi = row_base + row;
+    const int gi = row_base + q * TC_ROWS + row;
     const bool row_valid = gi < rows_total;
     const int token = q0 + (row_valid ? gi / group : 0), head = g * group + gi % group;
     const int limit = row_valid ? p.positions[token] : -1;   // last visible key of the row
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t s_addr = lane_addr + q * KEYS, o_addr = lane_addr + L::O_COLUMN + q * HD;
     const float scale_log2 = p.scale * 1.4426950408889634f;
-    float o[HD];
+    uint8_t* p_row = sP + q * L::P_BYTES + row * 128;
+    uint64_t o2[HD / 2];                               // the row's accumulators, in pairs
 #pragma unroll
-    for (int i = 0; i < HD; i++) o[i] = 0.f;
-    float m = -INFINITY, l = 0.f;                      // running maximum of the unscaled scores, running sum
+    for (int i = 0; i < HD / 2; i++) o2[i] = 0ull;
+    float m = -INFINITY;                               // running maximum of the unscaled scores
+    uint64_t l2 = 0ull;                                // running sum, as two partial sums
     bool ok = true;
-    for (int j = 0; j < n_tiles; j++) {
-      ok = !*abort_flag && mbar_wait(&s_full[j % L::S_BUFFERS], (j / L::S_BUFFERS) & 1);
-      if (!ok) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); }
-      ok = __all_sync(0xffffffffu, ok);                // tcgen05.ld is warp-wide: all lanes or none
-      if (!ok) break;
-      tc_fence_after();
-      const int kv0 = j * TC_KEYS;
-      const uint32_t s_addr = lane_addr + (j % L::S_BUFFERS) * TC_KEYS;
-      const bool masked = kv0 + TC_KEYS - 1 > limit;   // some key of the tile lies beyond this row's limit
-      // first pass over the row: its maximum
-      float t_max = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < TC_KEYS / 64; c++) {
+    auto add_o_tile = [&]() {                          // o += the product in tensor memory
+#pragma unroll
+      for (int c = 0; c < HD / 64; c++) {
         uint32_t ra[32], rb[32];
-        tmem_load32_issue(s_addr + c * 64, ra);
-        tmem_load32_issue(s_addr + c * 64 + 32, rb);
+        tmem_load32_issue(o_addr + c * 64, ra);
+        tmem_load32_issue(o_addr + c * 64 + 32, rb);
         tmem_load_wait(ra);
         tmem_load_wait(rb);
-        if (masked) {
 #pragma unroll
-          for (int i = 0; i < 32; i++) {
-            if (kv0 + c * 64 + i <= limit) t_max = fmaxf(t_max, __uint_as_float(ra[i]));
-            if (kv0 + c * 64 + 32 + i <= limit) t_max = fmaxf(t_max, __uint_as_float(rb[i]));
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i++) t_max = fmaxf(t_max, fmaxf(__uint_as_float(ra[i]), __uint_as_float(rb[i])));
+        for (int i = 0; i < 16; i++) {
+          o2[c * 32 + i] = f2_add(o2[c * 32 + i], f2_pack(ra[2 * i], ra[2 * i + 1]));
+          o2[c * 32 + 16 + i] = f2_add(o2[c * 32 + 16 + i], f2_pack(rb[2 * i], rb[2 * i + 1]));
         }
       }
-      const float n = fmaxf(m, t_max);
-      const float base = n == -INFINITY ? 0.f : n * scale_log2;
-      const float alpha = m == -INFINITY ? 0.f : exp2f(m * scale_log2 - base);
-      m = n;
-      // the previous tile's P V: add it, then bring everything to the new maximum
+    };
+    for (int j = 0; j < my_tiles; j++) {
       if (j > 0) {
-        ok = !*abort_flag && mbar_wait(&o_full[0], (j - 1) & 1);
+        // the previous tile's P V (it also frees the P buffer)
+        ok = !*abort_flag && mbar_wait(&o_full[q], (j - 1) & 1);
         if (!ok) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); }
-        ok = __all_sync(0xffffffffu, ok);
+        ok = __all_sync(0xffffffffu, ok);              // tcgen05.ld is warp-wide: all lanes or none
         if (!ok) break;
         tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < HD / 32; c++) {
-          uint32_t raw[32];
-          tmem_load32(lane_addr + L::O_COLUMN + c * 32, raw);
-#pragma unroll
-          for (int i = 0; i < 32; i++) o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(raw[i])) * alpha;
-        }
+        add_o_tile();
       }
-      l *= alpha;
-      // second pass: probabilities, their sum, and P as bfloat16 into shared memory (the P V
-      // product of the previous tile, which read the buffer, is complete: o_full above)
-      uint8_t* p_row = sP + row * 128;
-#pragma unroll 1
-      for (int c = 0; c < TC_KEYS / 32; c++) {
-        uint32_t raw[32];
-        tmem_load32(s_addr + c * 32, raw);
+      ok = !*abort_flag && mbar_wait(&s_full[q], j & 1);
+      if (!ok) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int kv0 = j * KEYS;
+      // the whole row of S
+      uint32_t sc[KEYS / 32][32];
+#pragma unroll
+      for (int c = 0; c < KEYS / 32; c++) tmem_load32_issue(s_addr + c * 32, sc[c]);
+#pragma unroll
+      for (int c = 0; c < KEYS / 32; c++) tmem_load_wait(sc[c]);
+      if (kv0 + KEYS - 1 > limit) {                    // some key of the tile lies beyond this row's limit
+#pragma unroll
+        for (int c = 0; c < KEYS / 32; c++)
+#pragma unroll
+          for (int i = 0; i < 32; i++) if (kv0 + c * 32 + i > limit) sc[c][i] = 0xff800000u;   // -inf
+      }
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < KEYS / 32; c++)
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          mx[0] = max3(mx[0], __uint_as_float(sc[c][i]), __uint_as_float(sc[c][i + 1]));
+          mx[1] = max3(mx[1], __uint_as_float(sc[c][i + 2]), __uint_as_float(sc[c][i + 3]));
+          mx[2] = max3(mx[2], __uint_as_float(sc[c][i + 4]), __uint_as_float(sc[c][i + 5]));
+          mx[3] = max3(mx[3], __uint_as_float(sc[c][i + 6]), __uint_as_float(sc[c][i + 7]));
+        }
+      const float n = max3(m, fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      const float base = n == -INFINITY ? 0.f : n * scale_log2;
+      const float alpha = m == -INFINITY ? 0.f : exp2_fast(m * scale_log2 - base);
+      m = n;
+      if (!__all_sync(0xffffffffu, alpha == 1.0f)) {   // the maximum moved for some row: bring the sums to it
+        const uint64_t alpha2 = f2_pack(alpha, alpha);
+        l2 = f2_mul(l2, alpha2);
+#pragma unroll
+        for (int i = 0; i < HD / 2; i++) o2[i] = f2_mul(o2[i], alpha2);
+      }
+      // probabilities, their sum, and P as bfloat16 into shared memory
+      const uint64_t scale2 = f2_pack(scale_log2, scale_log2), nbase2 = f2_pack(-base, -base);
+#pragma unroll
+      for (int c = 0; c < KEYS / 32; c++) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(fmaf(__uint_as_float(raw[i]), scale_log2, -base));
-          float p1 = exp2f(fmaf(__uint_as_float(raw[i + 1]), scale_log2, -base));
-          if (masked) {
-            if (kv0 + c * 32 + i > limit) p0 = 0.f;
-            if (kv0 + c * 32 + i + 1 > limit) p1 = 0.f;
-          }
-          l += p0 + p1;
+          float x0, x1;
+          f2_unpack(f2_fma(f2_pack(sc[c][i], sc[c][i + 1]), scale2, nbase2), x0, x1);
+          const float p0 = exp2_fast(x0), p1 = exp2_fast(x1);
+          l2 = f2_add(l2, f2_pack(p0, p1));
           __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
           packed[i >> 1] = *(uint32_t*)&h;
         }
-        uint8_t* atom = p_row + (c >> 1) * ATOM_BYTES;
+        uint8_t* atom = p_row + (c >> 1) * Q_ATOM_BYTES;
 #pragma unroll
         for (int q4 = 0; q4 < 4; q4++) {
           const int chunk = (c & 1) * 4 + q4;
           *(uint4*)(atom + ((chunk ^ (row & 7)) << 4)) = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
         }
       }
-      if (j == n_tiles - 1 && kv0 + row > max_limit) {
+      if (j == n_tiles - 1 && row < KEYS && kv0 + row > max_limit) {
         // the last tile's pages may reach beyond the request's keys, into slots that hold whatever
         // was there before: their probabilities are zero, but zero times a NaN is not, so the V
-        // row of such a key is cleared once its copy has landed
+        // row of such a key is cleared once its copy has landed (by each Q tile that reads the
+        // tile, before it signals its P: whichever P V comes first finds the rows cleared)
         const int s = j % KV_STAGES;
         if (*abort_flag || !mbar_wait(&v_full[s], (j / KV_STAGES) & 1)) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); }
 #pragma unroll
         for (int kb = 0; kb < L::KB; kb++)
 #pragma unroll
-          for (int c = 0; c < 8; c++) *(uint4*)(sV + s * L::KV_BYTES + kb * ATOM_BYTES + row * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+          for (int c = 0; c < 8; c++) *(uint4*)(sV + s * L::KV_BYTES + kb * L::KV_ATOM_BYTES + row * 128 + c * 16) = make_uint4(0, 0, 0, 0);
       }
       fence_proxy_async();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[0]);
+      if (lane == 0) mbar_arrive(&p_full[q]);
     }
-    if (ok) {
-      ok = !*abort_flag && mbar_wait(&o_full[0], (n_tiles - 1) & 1);
+    if (ok && my_tiles > 0) {
+      ok = !*abort_flag && mbar_wait(&o_full[q], (my_tiles - 1) & 1);
       if (!ok) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); }
       ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
-      tc_fence_after();
+      if (ok) {
+        tc_fence_after();
+        add_o_tile();
+        if (row_valid) {
+          float l_lo, l_hi;
+          f2_unpack(l2, l_lo, l_hi);
+          const float inv = 1.0f / (l_lo + l_hi);
+          __nv_bfloat16* dst = p.out + (size_t)token * p.out_stride + (size_t)head * HD;
 #pragma unroll
-      for (int c = 0; c < HD / 32; c++) {
-        uint32_t raw[32];
-        tmem_load32(lane_addr + L::O_COLUMN + c * 32, raw);
+          for (int i = 0; i < HD; i += 8) {
+            uint32_t packed[4];
 #pragma unroll
-        for (int i = 0; i < 32; i++) o[c * 32 + i] += __uint_as_float(raw[i]);
-      }
-      if (row_valid) {
-        const float inv = 1.0f / l;
-        __nv_bfloat16* dst = p.out + (size_t)token * p.out_stride + (size_t)head * HD;
-#pragma unroll
-        for (int i = 0; i < HD; i += 8) {
-          uint32_t packed[4];
-#pragma unroll
-          for (int k2 = 0; k2 < 4; k2++) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(o[i + 2 * k2] * inv, o[i + 2 * k2 + 1] * inv);
-            packed[k2] = *(uint32_t*)&h;
+            for (int k2 = 0; k2 < 4; k2++) {
+              float lo, hi;
+              f2_unpack(o2[i / 2 + k2], lo, hi);
+              __nv_bfloat162 h = __floats2bfloat162_rn(lo * inv, hi * inv);
+              packed[k2] = *(uint32_t*)&h;
+            }
+            *(uint4*)(dst + i) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
           }
-          *(uint4*)(dst + i) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
         }
       }
     }
@@ -381,7 +462,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     for (int j = max(0, v_issued - KV_STAGES); j < v_issued; j++) mbar_wait(&v_full[j % KV_STAGES], (j / KV_STAGES) & 1);
   }
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, L::TMEM_COLS);
+  if (warp == 1) tmem_dealloc(tmem_base, TC_TMEM_COLS);
 }
 
 template <int HD>
@@ -391,8 +472,6 @@ int launch_tc(const CUtensorMap& map_k, const CUtensorMap& map_v, const TcParams
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
     if (err != cudaSuccess) return sprout_fail("attention_prefill: cannot reserve %d bytes of shared memory: %s", L::SMEM_BYTES, cudaGetErrorString(err));
-    // all of the SM's memory as shared memory: two CTAs of the head_dim 64 kernel fit only then
-    cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
   sprout_launch(attention_prefill_tc_kernel<HD>, dim3(grid), dim3(TC_THREADS), L::SMEM_BYTES, stream, map_k, map_v, p);
@@ -403,25 +482,9 @@ int launch_tc(const CUtensorMap& map_k, const CUtensorMap& map_v, const TcParams
 
 // Whether the tcgen05 kernel takes these sizes.
 SPROUT_API int sprout_attention_prefill_tc_supported(int head_dim, int page_tokens, int out_stride) {
-  const bool pages_ok = page_tokens >= 8 && (TC_KEYS % page_tokens == 0 || page_tokens % TC_KEYS == 0);
+  const bool pages_ok = page_tokens == 8 || page_tokens == 16 || page_tokens == 32 || page_tokens == 64 ||
+                        (page_tokens > 0 && page_tokens % 128 == 0);
   return (head_dim == 64 || head_dim == 128) && pages_ok && out_stride % 8 == 0;
-}
-
-// CTAs of the kernel that one SM holds at a time (2 for head_dim 64 when all of the SM's memory
-// is shared memory), 0 for a head_dim the kernel does not take; -1 with the error text set.
-SPROUT_API int sprout_attention_prefill_tc_occupancy(int head_dim) {
-  int blocks = 0;
-  cudaError_t err = cudaSuccess;
-  if (head_dim == 64) {
-    cudaFuncSetAttribute(attention_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcLayout<64>::SMEM_BYTES);
-    cudaFuncSetAttribute(attention_prefill_tc_kernel<64>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_prefill_tc_kernel<64>, TC_THREADS, TcLayout<64>::SMEM_BYTES);
-  } else if (head_dim == 128) {
-    cudaFuncSetAttribute(attention_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcLayout<128>::SMEM_BYTES);
-    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_prefill_tc_kernel<128>, TC_THREADS, TcLayout<128>::SMEM_BYTES);
-  }
-  if (err != cudaSuccess) { sprout_fail("attention_prefill: occupancy query failed: %s", cudaGetErrorString(err)); return -1; }
-  return blocks;
 }
 
 // The arguments of sprout_attention_prefill, checked there.
@@ -438,13 +501,15 @@ int sprout_attention_prefill_tc(const void* q, int q_stride, const void* k_cache
   p.block_table = block_table; p.table_stride = table_stride; p.q_start = q_start; p.positions = positions;
   p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
   p.requests = requests; p.heads = heads; p.kv_heads = kv_heads; p.page_tokens = page_tokens; p.num_pages = num_pages;
-  p.box_rows = page_tokens < TC_KEYS ? page_tokens : TC_KEYS;
+  const int keys = head_dim == 64 ? TcLayout<64>::KEYS : TcLayout<128>::KEYS;
+  p.box_rows = page_tokens < keys ? page_tokens : keys;
   p.scale = 1.0f / sqrtf((float)head_dim); p.status = status;
   CUtensorMap map_k, map_v;
   if (tensor_map(k_cache, (int)cache_rows, head_dim, head_dim, p.box_rows, &map_k)) return 1;
   if (tensor_map(v_cache, (int)cache_rows, head_dim, head_dim, p.box_rows, &map_v)) return 1;
   const int group = heads / kv_heads;
-  const long long bound = (((long long)num_tokens * group + TC_ROWS - 1) / TC_ROWS + requests) * kv_heads;
+  const int cta_rows = TC_QTILES * TC_ROWS;
+  const long long bound = (((long long)num_tokens * group + cta_rows - 1) / cta_rows + requests) * kv_heads;
   SPROUT_REQUIRE(bound <= 0x7fffffffLL, "attention_prefill: too many tokens");
   if (head_dim == 64) return launch_tc<64>(map_k, map_v, p, (int)bound, stream);
   return launch_tc<128>(map_k, map_v, p, (int)bound, stream);

@@ -39,7 +39,6 @@ _SIGNATURES = {
     "sprout_attention_decode_fused": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_attention_prefill_tc_supported": [_I, _I, _I],
-    "sprout_attention_prefill_tc_occupancy": [_I],
     "sprout_gemm_bf16": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
 }
 

@@ -404,6 +404,9 @@ TC_PREFILL_CASES = [
     (5, 1, 64, 128, [400], [400]),                            # a page as long as a key tile
     (2, 1, 64, 256, [600, 100], [90, 100]),                   # pages longer than a key tile
     (16, 1, 64, 16, [45], [45]),                              # many heads per key head: a tile holds few tokens
+    (4, 1, 128, 128, [300, 129], [300, 70]),                  # head_dim 128 with pages of two key tiles
+    (14, 2, 64, 16, [1500], [1500]),                          # Q tile 0 of a piece ends a key tile before Q tile 1
+    (2, 2, 64, 16, [40, 128, 200], [40, 128, 129]),           # pieces with one Q tile and with two
 ]
 
 
