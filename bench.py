@@ -312,6 +312,45 @@ def timed_prefill(runner, tokens: int, rng, repeats: int = 5):
     return statistics.median(times[2:])
 
 
+def timed_attention(tokens: int, repeats: int = 20) -> dict:
+    """The prefill attention kernels alone, at the model's head sizes, over a paged cache: one
+    request of ``tokens`` tokens attending to itself (causal), both kernels."""
+    import torch
+    from sprout_lm_b200 import kernels
+    heads, kv_heads = CONFIG_05B["num_attention_heads"], CONFIG_05B["num_key_value_heads"]
+    head_dim, page = CONFIG_05B["hidden_size"] // heads, 16
+    pages = -(-tokens // page)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    k = torch.randn(pages + 1, kv_heads, page, head_dim, device="cuda", generator=g).to(torch.bfloat16)
+    v = torch.randn(pages + 1, kv_heads, page, head_dim, device="cuda", generator=g).to(torch.bfloat16)
+    table = torch.randperm(pages, device="cuda", generator=g).to(torch.int32).reshape(1, pages)
+    q = torch.randn(tokens, heads * head_dim, device="cuda", generator=g).to(torch.bfloat16)
+    q_start = torch.tensor([0, tokens], dtype=torch.int32, device="cuda")
+    positions = torch.arange(tokens, dtype=torch.int32, device="cuda")
+    out = torch.empty_like(q)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    flops = 4.0 * heads * head_dim * tokens * (tokens + 1) / 2
+    result = {"impl": "ours", "only": "attention", "tokens": tokens, "heads": heads, "kv_heads": kv_heads,
+              "head_dim": head_dim, "page_tokens": page}
+    for variant in ("mma_sync", "tcgen05"):
+        call = lambda: kernels.attention_prefill(q, k, v, table, q_start, positions, out, heads, kv_heads, head_dim,
+                                                 status, variant=variant)
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(repeats):
+            call()
+        end.record()
+        torch.cuda.synchronize()
+        us = begin.elapsed_time(end) * 1000 / repeats
+        result[f"{variant}_us"] = round(us, 1)
+        result[f"{variant}_tflops"] = round(flops / us / 1e6, 1)
+    assert int(status.item()) == 0
+    return result
+
+
 def run(args) -> dict:
     import numpy as np
     import torch
@@ -319,6 +358,8 @@ def run(args) -> dict:
     from sprout_lm_b200.cache.storage import cache_bytes_per_token
     from sprout_lm_b200.engine.step import ModelRunner
     kernels.load_library(verbose=True)
+    if args.only == "attention":
+        return timed_attention(args.tokens)
     layers = args.layers or CONFIG_05B["num_hidden_layers"]
     folder = model_folder(layers)
     model = load_model(folder, dtype="bfloat16", device="cuda:0")
@@ -379,8 +420,9 @@ def main() -> int:
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
-    parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate"], default="all",
+    parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate", "attention"], default="all",
                         help="measure one part only (for profiling captures); the JSON line then holds that part")
+    parser.add_argument("--tokens", type=int, default=2048, help="with --only attention: tokens of the one request")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))

@@ -31,7 +31,6 @@ namespace {
 
 constexpr int BLOCK_M = 128;        // rows of D per CTA == TMEM lanes
 constexpr int BLOCK_K = 64;         // bf16 elements per stage row: 128 bytes, one swizzle row
-constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 320;      // TMA warp, MMA warp, 8 epilogue warps
 constexpr int SMEM_BUDGET = 200 * 1024;
 
@@ -118,6 +117,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // The copy thread and the MMA thread each run one thread's worth of dependent instructions per
+  // k-block, and the tensor cores finish a k-block in under 300 cycles: their loops keep the
+  // stage, its phase, the barrier addresses and the descriptors in running variables, and read
+  // the abort flag only while a wait is not satisfied at once.
+  const uint32_t smem_base = smem_u32(smem), full_base = smem_u32(full_bar), empty_base = smem_u32(empty_bar);
   int issued = 0;
   if (warp == 0 && lane == 0) {
     // ---------------- producer: TMA loads of the two operand tiles, stage by stage.
@@ -125,7 +129,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     // round of stages are requested before waiting for the kernel that produces the activations.
     const CUtensorMap* weight_map = SWAP ? &map_rows : &map_cols;
     const CUtensorMap* act_map = SWAP ? &map_cols : &map_rows;
-    int it = 0;                                   // k-blocks issued so far, across tiles
+    constexpr uint32_t W_OFF = SWAP ? 0 : L::A_BYTES, X_OFF = SWAP ? L::A_BYTES : 0;
+    uint32_t s = 0, parity = 1;                   // stage and the parity of its "empty" phase to wait for
+    uint32_t stage_addr = smem_base;
+    int it = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
       const Work k = work_at(w);
@@ -134,52 +141,52 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
       if (w == (int)blockIdx.x) {
         early = min(k.num_kb, L::STAGES);
         for (int i = 0; i < early; i++) {
-          uint8_t* a_tile = smem + i * L::STAGE_BYTES;
-          mbar_expect_tx(&full_bar[i], L::A_BYTES + L::B_BYTES);
-          tma_load_2d(SWAP ? a_tile : a_tile + L::A_BYTES, weight_map, &full_bar[i], (k.kb_begin + i) * BLOCK_K, weight_row);
+          mbar_expect_tx_addr(full_base + 8 * i, L::A_BYTES + L::B_BYTES);
+          tma_load_2d_addr(smem_base + i * L::STAGE_BYTES + W_OFF, weight_map, full_base + 8 * i, (k.kb_begin + i) * BLOCK_K, weight_row);
         }
         pdl_wait();
       }
-      for (int i = 0; i < k.num_kb; i++, it++) {
-        const int s = it % L::STAGES;
-        uint8_t* a_tile = smem + s * L::STAGE_BYTES;
-        uint8_t* w_dst = SWAP ? a_tile : a_tile + L::A_BYTES;
-        uint8_t* x_dst = SWAP ? a_tile + L::A_BYTES : a_tile;
+      int x = k.kb_begin * BLOCK_K;
+      for (int i = 0; i < k.num_kb; i++, it++, x += BLOCK_K) {
+        const uint32_t full_addr = full_base + 8 * s;
         if (i >= early) {
-          const uint32_t parity = ((it / L::STAGES) & 1) ^ 1;
-          if (*abort_flag || !mbar_wait(&empty_bar[s], parity)) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); ok = false; break; }
-          mbar_expect_tx(&full_bar[s], L::A_BYTES + L::B_BYTES);
-          tma_load_2d(w_dst, weight_map, &full_bar[s], (k.kb_begin + i) * BLOCK_K, weight_row);
+          if (!mbar_wait_addr(empty_base + 8 * s, parity, abort_flag)) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); ok = false; break; }
+          mbar_expect_tx_addr(full_addr, L::A_BYTES + L::B_BYTES);
+          tma_load_2d_addr(stage_addr + W_OFF, weight_map, full_addr, x, weight_row);
         }
-        tma_load_2d(x_dst, act_map, &full_bar[s], (k.kb_begin + i) * BLOCK_K, act_row);
+        tma_load_2d_addr(stage_addr + X_OFF, act_map, full_addr, x, act_row);
         issued = it + 1;
+        if (++s == L::STAGES) { s = 0; parity ^= 1; stage_addr = smem_base; } else stage_addr += L::STAGE_BYTES;
       }
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------- MMA issuer
     const uint32_t idesc = umma_idesc(BLOCK_M, BN);
+    const uint64_t a_desc0 = umma_smem_desc(smem), b_desc0 = umma_smem_desc(smem + L::A_BYTES);
+    constexpr uint64_t STAGE_STEP = L::STAGE_BYTES >> 4;      // a stage further in the descriptor's address field
+    uint64_t a_desc = a_desc0, b_desc = b_desc0;
+    uint32_t s = 0, parity = 0;
     bool ok = true;
-    int it = 0, tiles_done = 0;
+    int tiles_done = 0;
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, tiles_done++) {
       const Work k = work_at(w);
       const int acc = tiles_done & 1;
       // the epilogue must have read this accumulator's previous tile out
-      if (*abort_flag || !mbar_wait(&acc_empty[acc], ((tiles_done >> 1) & 1) ^ 1)) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); break; }
+      if (!mbar_wait(&acc_empty[acc], ((tiles_done >> 1) & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); break; }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * BN;
-      for (int i = 0; i < k.num_kb; i++, it++) {
-        const int s = it % L::STAGES;
-        const uint32_t parity = (it / L::STAGES) & 1;
-        if (*abort_flag || !mbar_wait(&full_bar[s], parity)) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); ok = false; break; }
+      uint32_t accumulate = 0;
+      for (int i = 0; i < k.num_kb; i++) {
+        if (!mbar_wait_addr(full_base + 8 * s, parity, abort_flag)) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); ok = false; break; }
         tc_fence_after();
-        const uint8_t* a_tile = smem + s * L::STAGE_BYTES;
-        const uint64_t a_desc = umma_smem_desc(a_tile), b_desc = umma_smem_desc(a_tile + L::A_BYTES);
-#pragma unroll
-        for (int kk = 0; kk < BLOCK_K / UMMA_K; kk++) {
-          // advancing 16 elements (32 bytes) along K inside the swizzled row: +2 in the address field
-          umma_bf16(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (i | kk) != 0);
-        }
-        umma_commit(&empty_bar[s]);       // the stage is free once these MMAs have read it
+        // advancing 16 elements (32 bytes) along K inside the swizzled row: +2 in the address field
+        umma_bf16(d_tmem, a_desc, b_desc, idesc, accumulate);
+        umma_bf16(d_tmem, a_desc + 2, b_desc + 2, idesc, 1);
+        umma_bf16(d_tmem, a_desc + 4, b_desc + 4, idesc, 1);
+        umma_bf16(d_tmem, a_desc + 6, b_desc + 6, idesc, 1);
+        accumulate = 1;
+        umma_commit_addr(empty_base + 8 * s);   // the stage is free once these MMAs have read it
+        if (++s == L::STAGES) { s = 0; parity ^= 1; a_desc = a_desc0; b_desc = b_desc0; } else { a_desc += STAGE_STEP; b_desc += STAGE_STEP; }
       }
       if (ok) umma_commit(&acc_full[acc]);   // the accumulator is complete once all MMAs are
     }
@@ -194,9 +201,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
       const int acc = tiles_done & 1;
       const int row = k.row0 + quarter * 32 + lane;
       const int col0 = k.col0;
-      bool ok = !*abort_flag && mbar_wait(&acc_full[acc], (tiles_done >> 1) & 1);
-      if (!ok) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); }
-      ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld is warp-wide: all lanes or none
+      // one lane waits for the barrier; tcgen05.ld is warp-wide: all lanes go on or none
+      bool ok = true;
+      if (lane == 0) {
+        ok = mbar_wait(&acc_full[acc], (tiles_done >> 1) & 1, abort_flag);
+        if (!ok) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); }
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
