@@ -98,12 +98,58 @@ rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ gain, 
   }
 }
 
+// Many rows (a prefill): a warp per row, the row in registers, no block-wide barrier.
+template <typename TO, int VEC>
+__global__ void __launch_bounds__(256)
+rmsnorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ gain, TO* __restrict__ out,
+                    const int* __restrict__ rows, int num_rows, int hidden, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 8 + (threadIdx.x >> 5), quads = hidden >> 2;
+  if (r >= num_rows) return;
+  const float4* src = (const float4*)(x + (size_t)(rows ? rows[r] : r) * hidden);
+  float4 v[VEC];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VEC; k++) {
+    const int i = lane + k * 32;
+    v[k] = i < quads ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
+  for (int k = 0; k < VEC; k++) ss += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+  TO* dst = out + (size_t)r * hidden;
+#pragma unroll
+  for (int k = 0; k < VEC; k++) {
+    const int i = lane + k * 32;
+    if (i < quads) {
+      const float4 g = ((const float4*)gain)[i];
+      const float a = (v[k].x * scale) * g.x, b = (v[k].y * scale) * g.y, c = (v[k].z * scale) * g.z, d = (v[k].w * scale) * g.w;
+      if (sizeof(TO) == 4) {
+        ((float4*)dst)[i] = make_float4(a, b, c, d);
+      } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        ((uint2*)dst)[i] = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+      }
+    }
+  }
+}
+
 template <typename TO>
 static void launch_rmsnorm(const float* x, const float* gain, TO* out, const int* rows, int num_rows, int hidden,
                            float eps, cudaStream_t stream) {
   const int quads = hidden / 4;
   const bool aligned = hidden % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)gain & 15) == 0 && ((uintptr_t)out & 15) == 0;
-  if (aligned && quads <= 256) sprout_launch(rmsnorm_vec_kernel<TO, 1>, dim3(num_rows), dim3(256), 0, stream, x, gain, out, rows, hidden, eps);
+  if (aligned && num_rows >= 64 && quads <= 512) {
+    const dim3 grid((num_rows + 7) / 8);
+    if (quads <= 128) sprout_launch(rmsnorm_warp_kernel<TO, 4>, grid, dim3(256), 0, stream, x, gain, out, rows, num_rows, hidden, eps);
+    else if (quads <= 256) sprout_launch(rmsnorm_warp_kernel<TO, 8>, grid, dim3(256), 0, stream, x, gain, out, rows, num_rows, hidden, eps);
+    else sprout_launch(rmsnorm_warp_kernel<TO, 16>, grid, dim3(256), 0, stream, x, gain, out, rows, num_rows, hidden, eps);
+  }
+  else if (aligned && quads <= 256) sprout_launch(rmsnorm_vec_kernel<TO, 1>, dim3(num_rows), dim3(256), 0, stream, x, gain, out, rows, hidden, eps);
   else if (aligned && quads <= 512) sprout_launch(rmsnorm_vec_kernel<TO, 2>, dim3(num_rows), dim3(256), 0, stream, x, gain, out, rows, hidden, eps);
   else if (aligned && quads <= 1024) sprout_launch(rmsnorm_vec_kernel<TO, 4>, dim3(num_rows), dim3(256), 0, stream, x, gain, out, rows, hidden, eps);
   else if (aligned && quads <= 2048) sprout_launch(rmsnorm_vec_kernel<TO, 8>, dim3(num_rows), dim3(256), 0, stream, x, gain, out, rows, hidden, eps);
@@ -233,6 +279,81 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, float* acc, const float*
   }
 }
 
+// bfloat16 without float32 sums, head_dim a multiple of 16: a thread takes 8 consecutive elements
+// of a head's first half with the matching 8 of its second half (16-byte loads and stores), or 8
+// elements of a v head; the items of all tokens are spread over the grid.
+__global__ void __launch_bounds__(256)
+rope_append_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                       const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int table_stride,
+                       const float* __restrict__ cos_table, const float* __restrict__ sin_table, int max_positions,
+                       __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int num_tokens,
+                       int heads, int kv_heads, int head_dim, int page_tokens, int num_pages, int write_cache,
+                       int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int half = head_dim >> 1, half_chunks = half >> 3;
+  const int rot_items = (heads + kv_heads) * half_chunks;        // rotated pairs of 8
+  const int v_items = write_cache ? kv_heads * (head_dim >> 3) : 0;
+  const int per_token = rot_items + v_items;
+  const int width = (heads + 2 * kv_heads) * head_dim;
+  const bool rotate = cos_table != nullptr;
+  const long long total = (long long)num_tokens * per_token;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / per_token), item = (int)(idx % per_token);
+    const int pos = positions[t];
+    if (pos < 0 || (rotate && pos >= max_positions)) {
+      if (item == 0) atomicOr(status, SPROUT_STATUS_BAD_POSITION);
+      continue;
+    }
+    __nv_bfloat16* row = qkv + (size_t)t * width;
+    int page = 0;
+    bool page_ok = false;
+    const bool to_cache = item >= heads * half_chunks;
+    if (to_cache && write_cache) {
+      page = block_table[(size_t)seq_of_token[t] * table_stride + pos / page_tokens];
+      page_ok = page >= 0 && page < num_pages;
+      if (!page_ok && item == heads * half_chunks) atomicOr(status, SPROUT_STATUS_BAD_PAGE);
+    }
+    const int slot = pos % page_tokens;
+    if (item < rot_items) {
+      const int h = item / half_chunks, d = (item % half_chunks) * 8;
+      if (h < heads && !rotate) continue;                       // q stays as projected
+      if (h >= heads && !page_ok) continue;
+      const uint4 ra = *(const uint4*)(row + h * head_dim + d), rb = *(const uint4*)(row + h * head_dim + half + d);
+      float c[8], sn[8];
+      if (rotate) {
+        const float4* cp = (const float4*)(cos_table + (size_t)pos * half + d);
+        const float4* sp = (const float4*)(sin_table + (size_t)pos * half + d);
+        const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+        c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
+        sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; i++) { c[i] = 1.f; sn[i] = 0.f; }
+      }
+      const __nv_bfloat16* pa = (const __nv_bfloat16*)&ra;
+      const __nv_bfloat16* pb = (const __nv_bfloat16*)&rb;
+      uint4 oa, ob;
+      __nv_bfloat16* qa = (__nv_bfloat16*)&oa;
+      __nv_bfloat16* qb = (__nv_bfloat16*)&ob;
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const float a = __bfloat162float(pa[i]), b = __bfloat162float(pb[i]);
+        qa[i] = __float2bfloat16_rn(a * c[i] - b * sn[i]);
+        qb[i] = __float2bfloat16_rn(b * c[i] + a * sn[i]);
+      }
+      __nv_bfloat16* dst = h < heads ? row + h * head_dim
+                                     : k_cache + (((size_t)page * kv_heads + (h - heads)) * page_tokens + slot) * head_dim;
+      *(uint4*)(dst + d) = oa;
+      *(uint4*)(dst + half + d) = ob;
+    } else if (page_ok) {
+      const int vi = item - rot_items, h = vi / (head_dim >> 3), d = (vi % (head_dim >> 3)) * 8;
+      *(uint4*)(v_cache + (((size_t)page * kv_heads + h) * page_tokens + slot) * head_dim + d) =
+          *(const uint4*)(row + (heads + kv_heads + h) * head_dim + d);
+    }
+  }
+}
+
 SPROUT_API int sprout_rope_append(void* qkv, float* acc, const float* bias, int dtype, const int* positions, const int* seq_of_token,
                                   const int* block_table, int table_stride, const float* cos_table,
                                   const float* sin_table, int max_positions, void* k_cache, void* v_cache,
@@ -246,6 +367,16 @@ SPROUT_API int sprout_rope_append(void* qkv, float* acc, const float* bias, int 
   SPROUT_REQUIRE(!write_cache || (k_cache && v_cache), "rope_append: cache pointers missing");
   const int pairs = (heads + kv_heads) * (head_dim / 2);
   const int threads = pairs >= 1024 ? 1024 : (pairs + 31) / 32 * 32;
+  const bool aligned = ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0 &&
+                       ((uintptr_t)cos_table & 15) == 0 && ((uintptr_t)sin_table & 15) == 0;
+  if (dtype == SPROUT_BF16 && !acc && head_dim % 16 == 0 && aligned && num_tokens >= 64) {
+    const long long items = (long long)num_tokens * ((heads + kv_heads) * (head_dim / 16) + kv_heads * (head_dim / 8));
+    const int blocks = (int)((items + 255) / 256 < 148 * 8 ? (items + 255) / 256 : 148 * 8);
+    sprout_launch(rope_append_vec_kernel, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)qkv, positions, seq_of_token,
+        block_table, table_stride, cos_table, sin_table, max_positions, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
+        num_tokens, heads, kv_heads, head_dim, page_tokens, num_pages, write_cache, status);
+    return sprout_check_launch("rope_append");
+  }
   if (dtype == SPROUT_F32)
     sprout_launch(rope_append_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream,
         (float*)qkv, acc, bias, positions, seq_of_token, block_table, table_stride, cos_table, sin_table, max_positions,

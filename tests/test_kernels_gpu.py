@@ -55,6 +55,86 @@ def test_rmsnorm(hidden, eps, out_dtype):
     assert torch.equal(picked, out[rows.long()])
 
 
+@pytest.mark.parametrize("hidden", [72, 896, 1000, 2048])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_many_rows(hidden, out_dtype):
+    """A prefill's worth of rows takes the warp-per-row kernel: the same numbers as the
+    block-per-row kernel gives for a few rows, to the last bit of the output's rounding."""
+    from sprout_lm_b200 import kernels
+    rows, eps = 203, 1e-6
+    x = rand(rows, hidden, scale=3.0, seed=4)
+    gain = 1 + rand(hidden, scale=0.1, seed=1)
+    out = torch.empty(rows, hidden, dtype=out_dtype, device=DEV)
+    kernels.rmsnorm(x, gain, out, eps)
+    x64 = x.double()
+    want = (x64 / torch.sqrt((x64 * x64).mean(-1, keepdim=True) + eps)).float().double() * gain.double()
+    tol = 2e-6 if out_dtype == torch.float32 else 8e-3
+    assert (out.double() - want).abs().max().item() <= tol * want.abs().max().item()
+    few = torch.empty(5, hidden, dtype=out_dtype, device=DEV)
+    kernels.rmsnorm(x[100:105].contiguous(), gain, few, eps)
+    assert (few.double() - out[100:105].double()).abs().max().item() <= tol * want.abs().max().item()
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page,theta", [(14, 2, 64, 16, 1e6), (8, 2, 128, 32, 1e4), (4, 2, 16, 8, 1e4), (3, 1, 48, 16, 1e5)])
+@pytest.mark.parametrize("rotate", [True, False])
+def test_rope_append_many_tokens(status, heads, kv_heads, head_dim, page, theta, rotate):
+    """A prefill's worth of tokens takes the vectorised kernel (bfloat16): checked against the
+    float64 rotation and against the cache slots that the block tables name."""
+    from sprout_lm_b200 import kernels
+    from sprout_lm_b200.parts.rope import HalfSplitRotary
+    dtype = torch.bfloat16
+    lengths = [97, 3, 130]                                   # tokens of three requests, from position 5, 0 and 40
+    starts = [5, 0, 40]
+    pages_each = [-(-(s0 + n) // page) for s0, n in zip(starts, lengths)]
+    pool = sum(pages_each) + 2
+    perm = torch.randperm(pool, generator=torch.Generator().manual_seed(3)).to(torch.int32)
+    table = torch.full((3, max(pages_each)), -1, dtype=torch.int32)
+    at = 0
+    for r, n in enumerate(pages_each):
+        table[r, :n] = perm[at:at + n]
+        at += n
+    positions = torch.cat([torch.arange(s0, s0 + n, dtype=torch.int32) for s0, n in zip(starts, lengths)])
+    seq_of_token = torch.cat([torch.full((n,), r, dtype=torch.int32) for r, n in enumerate(lengths)])
+    T = positions.numel()
+
+    class RT:
+        device = torch.device(DEV)
+    cos, sin = HalfSplitRotary("", head_dim, theta, 512).rotary_tables(RT) if rotate else (None, None)
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = rand(T, width, dtype=dtype, seed=8)
+    original = qkv.clone()
+    k_cache = torch.zeros(pool, kv_heads, page, head_dim, dtype=dtype, device=DEV)
+    v_cache = torch.zeros_like(k_cache)
+    kernels.rope_append(qkv, positions.to(DEV), seq_of_token.to(DEV), table.to(DEV), cos, sin, k_cache, v_cache,
+                        heads, kv_heads, head_dim, page, True, status)
+    assert int(status.item()) == 0
+    q0, k0 = original[:, :heads * head_dim], original[:, heads * head_dim:(heads + kv_heads) * head_dim]
+    q_want = rope_reference(q0, positions, head_dim, theta) if rotate else q0.double().cpu()
+    k_want = rope_reference(k0, positions, head_dim, theta) if rotate else k0.double().cpu()
+    assert (qkv[:, :heads * head_dim].double().cpu() - q_want).abs().max().item() <= 6.4e-2
+    assert torch.equal(qkv[:, heads * head_dim:], original[:, heads * head_dim:])       # k and v stay in qkv as projected
+    pg = table[seq_of_token.long(), (positions // page).long()].long()
+    slot = (positions % page).long()
+    got_k = k_cache[pg.to(DEV), :, slot.to(DEV), :].reshape(T, -1).double().cpu()
+    assert (got_k - k_want).abs().max().item() <= 6.4e-2
+    assert torch.equal(v_cache[pg.to(DEV), :, slot.to(DEV), :].reshape(T, -1), original[:, (heads + kv_heads) * head_dim:])
+    assert int((k_cache != 0).any(-1).any(1).sum().item()) == T                      # no other slot was touched
+    # the few-token kernel gives the same bits
+    few_q = original[:6].clone()
+    k2, v2 = torch.zeros_like(k_cache), torch.zeros_like(v_cache)
+    kernels.rope_append(few_q, positions[:6].to(DEV), seq_of_token[:6].to(DEV), table.to(DEV), cos, sin, k2, v2,
+                        heads, kv_heads, head_dim, page, True, status)
+    assert torch.equal(few_q, qkv[:6])
+    assert torch.equal(k2[pg[:6].to(DEV), :, slot[:6].to(DEV), :], k_cache[pg[:6].to(DEV), :, slot[:6].to(DEV), :])
+    # without the cache write only q changes
+    k3 = torch.zeros_like(k_cache)
+    only_q = original.clone()
+    kernels.rope_append(only_q, positions.to(DEV), seq_of_token.to(DEV), table.to(DEV), cos, sin, k3, v2.zero_(),
+                        heads, kv_heads, head_dim, page, False, status)
+    assert torch.equal(only_q, qkv) and float(k3.abs().max()) == 0.0 and float(v2.abs().max()) == 0.0
+    assert int(status.item()) == 0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("inter", [8, 320, 4864])
 def test_swiglu_interleaved(dtype, inter):
