@@ -32,9 +32,10 @@ namespace {
 constexpr int BLOCK_M = 128;        // rows of D per CTA == TMEM lanes
 constexpr int BLOCK_K = 64;         // bf16 elements per stage row: 128 bytes, one swizzle row
 constexpr int NUM_THREADS = 320;      // TMA warp, MMA warp, 8 epilogue warps
-constexpr int SMEM_BUDGET = 200 * 1024;
+constexpr int SMEM_BUDGET = 196 * 1024;    // for the operand stages; the staging tiles and barriers come on top
 
-enum Epilogue : int { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_RESIDUAL_ATOMIC = 2, EPI_SWIGLU = 3 };
+enum Epilogue : int { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_RESIDUAL_ATOMIC = 2, EPI_SWIGLU = 3, EPI_RESIDUAL_TMA = 4 };
+constexpr int STAGING_BYTES = 2 * 128 * 128;    // two [128 rows, 32 float32] tiles for the TMA reduction of the residual epilogue
 
 // SwiGLU epilogue: the weight rows interleave gate and up in blocks of 8 (rows 16b..16b+7 gate,
 // 16b+8..16b+15 up), so output feature 8b+j is silu(D[.., 16b+j]) * D[.., 16b+8+j]; the output
@@ -60,7 +61,7 @@ struct Layout {
   static constexpr int STAGE_BYTES = A_BYTES + B_PADDED;
   static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) > 12 ? 12 : (SMEM_BUDGET / STAGE_BYTES);
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;     // two accumulators
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
 // One unit of work: a 128 x BN tile of D over a range of K blocks.
@@ -74,15 +75,17 @@ struct Work { int row0, col0, kb_begin, num_kb, split; };
 template <int BN, bool SWAP>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
-                    const Params p) {
+                    const __grid_constant__ CUtensorMap map_out, const Params p) {
   using L = Layout<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* full_bar = (uint64_t*)(smem + L::STAGES * L::STAGE_BYTES);
+  uint8_t* staging = smem + L::STAGES * L::STAGE_BYTES;
+  uint64_t* full_bar = (uint64_t*)(staging + STAGING_BYTES);
   uint64_t* empty_bar = full_bar + L::STAGES;
   uint64_t* acc_full = empty_bar + L::STAGES;     // [2] accumulator complete (MMA -> epilogue)
   uint64_t* acc_empty = acc_full + 2;             // [2] accumulator read out (epilogue -> MMA)
-  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  uint64_t* epi_bar = acc_empty + 2;              // the 8 epilogue warps meet here (bounded, unlike bar.sync)
+  uint32_t* tmem_slot = (uint32_t*)(epi_bar + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -108,6 +111,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+    mbar_init(epi_bar, 8);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -196,6 +200,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     const int quarter = warp & 3;       // a warp reads TMEM lanes 32 * (warp % 4) ..
     const int half = (warp - 2) >> 2;   // two warps per lane quarter take alternate 16-column chunks
     int tiles_done = 0;
+    uint32_t groups_done = 0, epi_phase = 0;
+    const bool issuer = warp == 2 && lane == 0;   // issues the reductions of the residual epilogue
+    // all 8 warps meet; false when the wait ran out
+    auto epi_sync = [&]() {
+      bool met = true;
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(epi_bar);
+        met = mbar_wait(epi_bar, epi_phase, abort_flag);
+        if (!met) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); }
+      }
+      epi_phase ^= 1;
+      return (bool)__shfl_sync(0xffffffffu, met, 0);
+    };
     for (int w = blockIdx.x; w < total_work; w += gridDim.x, tiles_done++) {
       const Work k = work_at(w);
       const int acc = tiles_done & 1;
@@ -212,6 +230,48 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
       const bool first_split = k.split == 0;
+      if (!SWAP && p.epilogue == EPI_RESIDUAL_TMA) {
+        // out += D through shared memory: the 8 warps fill a [128 rows, 32 columns] float32 tile
+        // in the swizzled layout of the output's tensor map, one thread hands it to the TMA unit,
+        // which adds it to the output in L2 (rows and columns beyond the matrix are clipped).
+        // Two tiles alternate; a tile is written again once the reduction before last has read it.
+        const int tile_row = quarter * 32 + lane;
+        bool met = true;
+#pragma unroll 1
+        for (int c = half * 16; c < BN && met; c += 32, groups_done++) {
+          uint32_t raw[16];
+          tmem_load16(taddr + c, raw);
+          const int n_base = col0 + c;
+          uint8_t* tile = staging + (groups_done & 1) * (STAGING_BYTES / 2);
+          if (groups_done >= 2) {
+            if (issuer) bulk_wait_group_read<1>();
+            met = epi_sync();
+            if (!met) break;
+          }
+#pragma unroll
+          for (int q4 = 0; q4 < 4; q4++) {
+            float4 v;
+            v.x = __uint_as_float(raw[4 * q4]) + ((p.bias && n_base + 4 * q4 < p.N) ? p.bias[n_base + 4 * q4] : 0.f);
+            v.y = __uint_as_float(raw[4 * q4 + 1]) + ((p.bias && n_base + 4 * q4 + 1 < p.N) ? p.bias[n_base + 4 * q4 + 1] : 0.f);
+            v.z = __uint_as_float(raw[4 * q4 + 2]) + ((p.bias && n_base + 4 * q4 + 2 < p.N) ? p.bias[n_base + 4 * q4 + 2] : 0.f);
+            v.w = __uint_as_float(raw[4 * q4 + 3]) + ((p.bias && n_base + 4 * q4 + 3 < p.N) ? p.bias[n_base + 4 * q4 + 3] : 0.f);
+            const int chunk = half * 4 + q4;
+            *(float4*)(tile + tile_row * 128 + ((chunk ^ (tile_row & 7)) << 4)) = v;
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          met = epi_sync();
+          if (!met) break;
+          if (issuer) {
+            tma_reduce_add_2d(&map_out, smem_u32(tile), col0 + (c & ~31), k.row0);
+            bulk_commit_group();
+          }
+        }
+        if (!met) break;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        continue;
+      }
 #pragma unroll 1
       for (int c = half * 16; c < BN; c += 32) {
         uint32_t raw[16];
@@ -308,6 +368,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
     }
   }
+  if (warp == 2 && lane == 0) bulk_wait_group<0>();     // the reductions have been performed
   tc_fence_before();
   __syncthreads();
   if (*abort_flag && warp == 0 && lane == 0) {
@@ -322,7 +383,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
 // ------------------------------------------------------------------ host side
 // `work` = tiles x K splits; the grid is one CTA per SM at most, each walking the work list.
 template <int BN, bool SWAP>
-int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const Params& p, int work, cudaStream_t stream) {
+int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const CUtensorMap& out_map, const Params& p, int work,
+           cudaStream_t stream) {
   using L = Layout<BN>;
   const dim3 grid(work < sm_count() ? work : sm_count());
   static bool configured = false;
@@ -331,7 +393,7 @@ int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const Param
     if (err != cudaSuccess) return sprout_fail("gemm_bf16: cannot reserve %d bytes of shared memory: %s", L::SMEM_BYTES, cudaGetErrorString(err));
     configured = true;
   }
-  sprout_launch(gemm_tcgen05_kernel<BN, SWAP>, grid, dim3(NUM_THREADS), L::SMEM_BYTES, stream, rows_map, cols_map, p);
+  sprout_launch(gemm_tcgen05_kernel<BN, SWAP>, grid, dim3(NUM_THREADS), L::SMEM_BYTES, stream, rows_map, cols_map, out_map, p);
   return sprout_check_launch("gemm_bf16");
 }
 
@@ -382,11 +444,11 @@ SPROUT_API int sprout_gemm_bf16(const void* A, const void* W, const float* bias,
     const long long work = (long long)((N + BLOCK_M - 1) / BLOCK_M) * ((M + bn - 1) / bn) * split_k;
     SPROUT_REQUIRE(work <= 0x7fffffffLL, "gemm_bf16: too many tiles");
     switch (bn) {
-      case 16: return launch<16, true>(map_w, map_a, p, (int)work, stream);
-      case 32: return launch<32, true>(map_w, map_a, p, (int)work, stream);
-      case 64: return launch<64, true>(map_w, map_a, p, (int)work, stream);
-      case 128: return launch<128, true>(map_w, map_a, p, (int)work, stream);
-      default: return launch<256, true>(map_w, map_a, p, (int)work, stream);
+      case 16: return launch<16, true>(map_w, map_a, map_a, p, (int)work, stream);
+      case 32: return launch<32, true>(map_w, map_a, map_a, p, (int)work, stream);
+      case 64: return launch<64, true>(map_w, map_a, map_a, p, (int)work, stream);
+      case 128: return launch<128, true>(map_w, map_a, map_a, p, (int)work, stream);
+      default: return launch<256, true>(map_w, map_a, map_a, p, (int)work, stream);
     }
   }
   // tokens on M: 128 x 256 tiles where they tile N exactly (a quarter less operand traffic from
@@ -396,6 +458,12 @@ SPROUT_API int sprout_gemm_bf16(const void* A, const void* W, const float* bias,
   if (tensor_map(W, N, K, K, bn, &map_w)) return 1;
   const long long work = (long long)((N + bn - 1) / bn) * ((M + BLOCK_M - 1) / BLOCK_M);
   SPROUT_REQUIRE(work <= 0x7fffffffLL, "gemm_bf16: too many tiles");
-  if (bn == 256) return launch<256, false>(map_a, map_w, p, (int)work, stream);
-  return launch<128, false>(map_a, map_w, p, (int)work, stream);
+  // the residual epilogue goes through the TMA unit where the output's rows allow a tensor map
+  CUtensorMap map_out = map_a;
+  if (p.epilogue == EPI_RESIDUAL && ldo % 4 == 0 && ((uintptr_t)out & 15) == 0) {
+    if (tensor_map(out, M, N, ldo, BLOCK_M, &map_out, 4)) return 1;
+    p.epilogue = EPI_RESIDUAL_TMA;
+  }
+  if (bn == 256) return launch<256, false>(map_a, map_w, map_out, p, (int)work, stream);
+  return launch<128, false>(map_a, map_w, map_out, p, (int)work, stream);
 }

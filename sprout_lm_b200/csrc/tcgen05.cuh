@@ -59,6 +59,16 @@ __device__ __forceinline__ void tma_load_2d_addr(uint32_t dst, const CUtensorMap
 __device__ __forceinline__ void umma_commit_addr(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// Adds a [box_rows, 32] float32 tile in shared memory (128-byte swizzle) to the tensor at column x,
+// row y; rows and columns outside the tensor are clipped.  Completion goes by bulk groups.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"((uint64_t)map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Until at most N of this thread's bulk groups still read their shared memory / are incomplete.
+template <int N> __device__ __forceinline__ void bulk_wait_group_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_group() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
   asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -180,36 +190,39 @@ EncodeTiled encode_fn() {
 }
 
 struct MapKey {
-  const void* ptr; int rows, cols, ld, box_rows;
-  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
+  const void* ptr; int rows, cols, ld, box_rows, elem;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows && elem == o.elem;
+  }
 };
 struct MapHash {
   size_t operator()(const MapKey& k) const {
     size_t h = (size_t)k.ptr;
-    for (int v : {k.rows, k.cols, k.ld, k.box_rows}) h = h * 1000003u ^ (size_t)v;
+    for (int v : {k.rows, k.cols, k.ld, k.box_rows, k.elem}) h = h * 1000003u ^ (size_t)v;
     return h;
   }
 };
 
-// A 2-D bf16 tensor map over [rows, cols] with row stride ld elements, boxes of box_rows x 64,
-// 128-byte swizzle, zero fill outside.  Maps are cached: an encode costs a few microseconds.
-int tensor_map(const void* ptr, int rows, int cols, int ld, int box_rows, CUtensorMap* out) {
+// A 2-D tensor map over [rows, cols] of bfloat16 (elem 2) or float32 (elem 4) with row stride ld
+// elements, boxes of box_rows x 128 bytes, 128-byte swizzle, zero fill outside (a store or a
+// reduction clips there).  Maps are cached: an encode costs a few microseconds.
+int tensor_map(const void* ptr, int rows, int cols, int ld, int box_rows, CUtensorMap* out, int elem = 2) {
   static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
   static std::mutex lock;
-  MapKey key{ptr, rows, cols, ld, box_rows};
+  MapKey key{ptr, rows, cols, ld, box_rows, elem};
   std::lock_guard<std::mutex> guard(lock);
   auto it = cache.find(key);
   if (it != cache.end()) { *out = it->second; return 0; }
   EncodeTiled encode = encode_fn();
   if (!encode) return sprout_fail("tensor map: cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-  cuuint32_t elem[2] = {1, 1};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * elem};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / elem), (cuuint32_t)box_rows};
+  cuuint32_t elems[2] = {1, 1};
   CUtensorMap map;
-  CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult rc = encode(&map, elem == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                       const_cast<void*>(ptr), dims, strides, box, elems, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS) return sprout_fail("tensor map: cuTensorMapEncodeTiled failed with code %d", (int)rc);
   if (cache.size() > 4096) cache.clear();
   cache.emplace(key, map);
