@@ -1020,17 +1020,21 @@ SPROUT_API int sprout_attention_prefill_tc_supported(int head_dim, int page_toke
 int sprout_attention_prefill_tc(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                 const int* block_table, int table_stride, const int* q_start, const int* positions,
                                 void* out, int out_stride, int num_tokens, int requests, int heads, int kv_heads,
-                                int head_dim, int page_tokens, int num_pages, int* status, cudaStream_t stream);
+                                int head_dim, int page_tokens, int num_pages, float* scratch, long long scratch_floats,
+                                int* counters, int* status, cudaStream_t stream);
 
 // Portions of prompts (and single tokens) of several requests in one launch.  q_start[r] is the
 // first token of request r in the batch; a token at position pos sees keys 0..pos of its request.
 // variant: 0 chooses (the tcgen05 kernel where it takes the sizes and the requests bring 128 rows
-// each on average, else the mma.sync kernel), 1 forces mma.sync, 2 forces tcgen05.
+// each on average, else the mma.sync kernel), 1 forces mma.sync, 2 forces tcgen05.  scratch
+// (float32) and counters (int32, zero, left zero) are optional: with them the tcgen05 kernel
+// spreads a launch that is too small for the GPU over more SMs.
 SPROUT_API int sprout_attention_prefill(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                         const int* block_table, int table_stride, const int* q_start,
                                         const int* positions, void* out, int out_stride, int num_tokens,
                                         int requests, int heads, int kv_heads, int head_dim, int page_tokens,
-                                        int num_pages, int variant, int* status, cudaStream_t stream) {
+                                        int num_pages, int variant, float* scratch, long long scratch_floats,
+                                        int* counters, int* status, cudaStream_t stream) {
   SPROUT_REQUIRE(num_tokens > 0 && requests > 0 && heads > 0 && kv_heads > 0 && page_tokens > 0 && num_pages > 0,
                  "attention_prefill: sizes must be positive");
   SPROUT_REQUIRE(heads % kv_heads == 0, "attention_prefill: heads (%d) must be a multiple of kv_heads (%d)", heads, kv_heads);
@@ -1053,7 +1057,7 @@ SPROUT_API int sprout_attention_prefill(const void* q, int q_stride, const void*
   if (variant == 2 || (variant == 0 && tc_takes && (long long)num_tokens * group >= 128LL * requests))
     return sprout_attention_prefill_tc(q, q_stride, k_cache, v_cache, block_table, table_stride, q_start, positions, out,
                                        out_stride, num_tokens, requests, heads, kv_heads, head_dim, page_tokens, num_pages,
-                                       status, stream);
+                                       scratch, scratch_floats, counters, status, stream);
   // every request has at most ceil(tokens * group / 64) tiles: an upper bound without reading q_start
   const long long bound = ((long long)num_tokens * group + PF_ROWS - 1) / PF_ROWS + requests;
   SPROUT_REQUIRE(bound <= 0x7fffffffLL, "attention_prefill: too many tokens");

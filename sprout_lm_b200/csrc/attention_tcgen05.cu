@@ -38,6 +38,7 @@ constexpr int TC_QTILES = 2;              // Q tiles of a CTA
 constexpr int KV_STAGES = 2;
 constexpr int TC_THREADS = 384;           // warpgroup 0: copy warp, MMA warp (two warps idle); 1, 2: softmax of Q tile 0, 1
 constexpr int TC_TMEM_COLS = 512;
+constexpr int SPROUT_PREFILL_SPLIT_MAX = 160;   // pieces that can get a second CTA (fewer than the SMs of any GPU this runs on)
 constexpr int Q_ATOM_BYTES = 128 * 128;   // a [128 rows, 64 bf16] swizzled tile
 
 struct TcParams {
@@ -47,6 +48,9 @@ struct TcParams {
   const int* positions;               // [tokens]
   __nv_bfloat16* out; int out_stride;
   int requests, heads, kv_heads, page_tokens, num_pages, box_rows;
+  int split_pieces;                   // SPLIT kernel: pieces (in launch order) that two CTAs share
+  float* scratch;                     // [split_pieces][2][256 rows][head_dim + 4] partial results
+  int* counters;                      // [split_pieces][2 Q tiles], zero between launches
   float scale;
   int* status;
 };
@@ -110,7 +114,12 @@ __device__ __forceinline__ float exp2_fast(float x) {
   return y;
 }
 
-template <int HD>
+// SPLIT: the launch has fewer 256-row pieces than the GPU has SMs.  The first `split_pieces`
+// pieces of the launch (the longest) then get two CTAs each, which take alternate key tiles.
+// Each leaves its partial result (maximum, sum and accumulators of every row) in global scratch
+// memory and counts itself in; the one that finds the other already counted merges the two and
+// writes the rows.  Nobody waits for anybody.
+template <int HD, bool SPLIT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const TcParams p) {
@@ -137,13 +146,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   pdl_launch_dependents();
   pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int g = blockIdx.x % p.kv_heads;
+  const bool paired = SPLIT && (int)blockIdx.x < 2 * p.split_pieces;      // one of the two CTAs of a piece
+  const int piece_index = !SPLIT ? (int)blockIdx.x : paired ? (int)blockIdx.x >> 1 : (int)blockIdx.x - p.split_pieces;
+  const int rank = paired ? blockIdx.x & 1 : 0;
+  const int g = piece_index % p.kv_heads;
   const int group = p.heads / p.kv_heads;
   constexpr int CTA_ROWS = TC_QTILES * TC_ROWS;
 
   // which request and which 256-row piece of it: the pieces of a request are handed out from the
   // last (the longest under the causal mask) to the first, the heads of a piece side by side
-  int r = 0, piece = blockIdx.x / p.kv_heads;
+  int r = 0, piece = piece_index / p.kv_heads;
   for (; r < p.requests; r++) {
     const int pieces = ((p.q_start[r + 1] - p.q_start[r]) * group + CTA_ROWS - 1) / CTA_ROWS;
     if (piece < pieces) { piece = pieces - 1 - piece; break; }
@@ -162,8 +174,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const bool two = row_base + TC_ROWS < rows_total;       // the second Q tile has rows
   const int limit_a = p.positions[q0 + (min(rows_total, row_base + TC_ROWS) - 1) / group];
   const int max_limit = two ? p.positions[q0 + (min(rows_total, row_base + CTA_ROWS) - 1) / group] : limit_a;
-  const int tiles_a = limit_a / KEYS + 1;                  // key tiles that Q tile 0 needs
-  const int n_tiles = max_limit / KEYS + 1;                // and Q tile 1 (or the CTA)
+  const int all_tiles = max_limit / KEYS + 1;              // key tiles of the piece
+  // this CTA's share: all of them, or every second one from its rank; below, j counts the CTA's
+  // own tiles and first + step * j is the tile among the piece's
+  const bool split = paired && all_tiles >= 4;
+  if (paired && !split && rank == 1) return;
+  const int first = split ? rank : 0, step = split ? 2 : 1;
+  const int tiles_a = (limit_a / KEYS + 1 - first + step - 1) / step;     // own key tiles that Q tile 0 needs
+  const int n_tiles = (all_tiles - first + step - 1) / step;              // and Q tile 1 (or the CTA)
 
   // rows of a stage that no copy fills (keys beyond the request) must hold finite numbers: their
   // probabilities are zero, and zero times a stale NaN is not
@@ -202,7 +220,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       // looks box b's page up and issues its copies, lane 0 waits for the stage and posts the bytes
       const int boxes = KEYS / p.box_rows;
       auto box_row = [&](int j) {
-        const int key = j * KEYS + lane * p.box_rows;
+        const int key = (first + step * j) * KEYS + lane * p.box_rows;
         if (lane >= boxes || j >= n_tiles || key > max_limit) return -1;
         const int page = table[key / p.page_tokens];
         if (page < 0 || page >= p.num_pages) { atomicOr(p.status, SPROUT_STATUS_BAD_PAGE); return -1; }
@@ -272,7 +290,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       if (*abort_flag || !mbar_wait(&k_full[0], 0)) fail();
       if (ok) {
         tc_fence_after();
-        issue_s(0, 0);
+        if (tiles_a > 0) issue_s(0, 0);
         if (two) issue_s(1, 0);
         umma_commit(&k_empty[0]);
       }
@@ -355,7 +373,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int kv0 = j * KEYS;
+      const int kv0 = (first + step * j) * KEYS;
       // the whole row of S
       uint32_t sc[KEYS / 32][32];
 #pragma unroll
@@ -409,7 +427,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
           *(uint4*)(atom + ((chunk ^ (row & 7)) << 4)) = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
         }
       }
-      if (j == n_tiles - 1 && row < KEYS && kv0 + row > max_limit) {
+      if (first + step * j == all_tiles - 1 && row < KEYS && kv0 + row > max_limit) {
         // the last tile's pages may reach beyond the request's keys, into slots that hold whatever
         // was there before: their probabilities are zero, but zero times a NaN is not, so the V
         // row of such a key is cleared once its copy has landed (by each Q tile that reads the
@@ -433,24 +451,65 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       if (ok) {
         tc_fence_after();
         add_o_tile();
-        if (row_valid) {
-          float l_lo, l_hi;
-          f2_unpack(l2, l_lo, l_hi);
-          const float inv = 1.0f / (l_lo + l_hi);
-          __nv_bfloat16* dst = p.out + (size_t)token * p.out_stride + (size_t)head * HD;
+      }
+    }
+    float l_lo, l_hi;
+    f2_unpack(l2, l_lo, l_hi);
+    float l = l_lo + l_hi;
+    bool writes = !split;                              // this thread writes its row out
+    if (SPLIT && split) {
+      // this CTA's rows go to scratch memory; the warpgroup then counts itself in for its Q tile,
+      // and if the other CTA was there before, it merges that CTA's rows into its own
+      constexpr int ROW_FLOATS = HD + 4;
+      float* mine = p.scratch + ((size_t)(piece_index * 2 + rank) * CTA_ROWS + q * TC_ROWS + row) * ROW_FLOATS;
+      const float* theirs = p.scratch + ((size_t)(piece_index * 2 + (rank ^ 1)) * CTA_ROWS + q * TC_ROWS + row) * ROW_FLOATS;
 #pragma unroll
-          for (int i = 0; i < HD; i += 8) {
-            uint32_t packed[4];
+      for (int i = 0; i < HD / 4; i++) {
+        float a, b, c, d;
+        f2_unpack(o2[2 * i], a, b);
+        f2_unpack(o2[2 * i + 1], c, d);
+        ((float4*)mine)[i] = make_float4(a, b, c, d);
+      }
+      *(float2*)(mine + HD) = make_float2(ok ? m : -INFINITY, l);
+      __threadfence();
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + q) : "memory");          // the warpgroup's rows are written
+      int* counter = p.counters + piece_index * TC_QTILES + q;
+      int* seen = (int*)(smem + L::OFF_BAR + 192) + q;                     // behind the barriers and the TMEM slot
+      if ((tid & 127) == 0) *seen = atomicAdd(counter, 1);
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + q) : "memory");
+      if (*seen == 1) {
+        __threadfence();
+        if ((tid & 127) == 0) *counter = 0;                                // ready for the next launch
+        const float2 ml = __ldcg((const float2*)(theirs + HD));
+        const float m1 = ml.x, l1 = ml.y;
+        const float top = fmaxf(m, m1);
+        const float a0 = m == -INFINITY ? 0.f : exp2_fast((m - top) * scale_log2);
+        const float a1 = m1 == -INFINITY ? 0.f : exp2_fast((m1 - top) * scale_log2);
+        l = l * a0 + l1 * a1;
+        const uint64_t a0_2 = f2_pack(a0, a0), a1_2 = f2_pack(a1, a1);
 #pragma unroll
-            for (int k2 = 0; k2 < 4; k2++) {
-              float lo, hi;
-              f2_unpack(o2[i / 2 + k2], lo, hi);
-              __nv_bfloat162 h = __floats2bfloat162_rn(lo * inv, hi * inv);
-              packed[k2] = *(uint32_t*)&h;
-            }
-            *(uint4*)(dst + i) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          }
+        for (int i = 0; i < HD / 4; i++) {
+          const float4 t = __ldcg((const float4*)theirs + i);
+          o2[2 * i] = f2_fma(o2[2 * i], a0_2, f2_mul(f2_pack(t.x, t.y), a1_2));
+          o2[2 * i + 1] = f2_fma(o2[2 * i + 1], a0_2, f2_mul(f2_pack(t.z, t.w), a1_2));
         }
+        writes = true;
+      }
+    }
+    if (ok && row_valid && writes) {
+      const float inv = 1.0f / l;
+      __nv_bfloat16* dst = p.out + (size_t)token * p.out_stride + (size_t)head * HD;
+#pragma unroll
+      for (int i = 0; i < HD; i += 8) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int k2 = 0; k2 < 4; k2++) {
+          float lo, hi;
+          f2_unpack(o2[i / 2 + k2], lo, hi);
+          __nv_bfloat162 h = __floats2bfloat162_rn(lo * inv, hi * inv);
+          packed[k2] = *(uint32_t*)&h;
+        }
+        *(uint4*)(dst + i) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
     }
   }
@@ -465,16 +524,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   if (warp == 1) tmem_dealloc(tmem_base, TC_TMEM_COLS);
 }
 
+// `pieces` bounds the 256-row pieces of the launch (times key/value heads).
 template <int HD>
-int launch_tc(const CUtensorMap& map_k, const CUtensorMap& map_v, const TcParams& p, int grid, cudaStream_t stream) {
+int launch_tc(const CUtensorMap& map_k, const CUtensorMap& map_v, TcParams p, int pieces, cudaStream_t stream) {
   using L = TcLayout<HD>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
+    cudaError_t err = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
     if (err != cudaSuccess) return sprout_fail("attention_prefill: cannot reserve %d bytes of shared memory: %s", L::SMEM_BYTES, cudaGetErrorString(err));
     configured = true;
   }
-  sprout_launch(attention_prefill_tc_kernel<HD>, dim3(grid), dim3(TC_THREADS), L::SMEM_BYTES, stream, map_k, map_v, p);
+  if (p.split_pieces > 0) {
+    sprout_launch(attention_prefill_tc_kernel<HD, true>, dim3(pieces + p.split_pieces), dim3(TC_THREADS), L::SMEM_BYTES, stream, map_k, map_v, p);
+    return sprout_check_launch("attention_prefill (tcgen05, split)");
+  }
+  sprout_launch(attention_prefill_tc_kernel<HD, false>, dim3(pieces), dim3(TC_THREADS), L::SMEM_BYTES, stream, map_k, map_v, p);
   return sprout_check_launch("attention_prefill (tcgen05)");
 }
 
@@ -487,11 +553,19 @@ SPROUT_API int sprout_attention_prefill_tc_supported(int head_dim, int page_toke
   return (head_dim == 64 || head_dim == 128) && pages_ok && out_stride % 8 == 0;
 }
 
-// The arguments of sprout_attention_prefill, checked there.
+// Scratch floats and counters that let the kernel give the longest pieces of a small launch two
+// CTAs each (at most SPROUT_PREFILL_SPLIT_MAX pieces).
+SPROUT_API long long sprout_attention_prefill_scratch_floats(int head_dim) {
+  return (long long)SPROUT_PREFILL_SPLIT_MAX * 2 * TC_QTILES * TC_ROWS * (head_dim + 4);
+}
+SPROUT_API int sprout_attention_prefill_counters() { return SPROUT_PREFILL_SPLIT_MAX * TC_QTILES; }
+
+// The arguments of sprout_attention_prefill, checked there; scratch and counters may be null.
 int sprout_attention_prefill_tc(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                 const int* block_table, int table_stride, const int* q_start, const int* positions,
                                 void* out, int out_stride, int num_tokens, int requests, int heads, int kv_heads,
-                                int head_dim, int page_tokens, int num_pages, int* status, cudaStream_t stream) {
+                                int head_dim, int page_tokens, int num_pages, float* scratch, long long scratch_floats,
+                                int* counters, int* status, cudaStream_t stream) {
   SPROUT_REQUIRE(sprout_attention_prefill_tc_supported(head_dim, page_tokens, out_stride) && ((uintptr_t)out & 15) == 0,
                  "attention_prefill (tcgen05): head_dim %d, page size %d or the output's alignment is not taken", head_dim, page_tokens);
   const long long cache_rows = (long long)num_pages * kv_heads * page_tokens;
@@ -511,6 +585,16 @@ int sprout_attention_prefill_tc(const void* q, int q_stride, const void* k_cache
   const int cta_rows = TC_QTILES * TC_ROWS;
   const long long bound = (((long long)num_tokens * group + cta_rows - 1) / cta_rows + requests) * kv_heads;
   SPROUT_REQUIRE(bound <= 0x7fffffffLL, "attention_prefill: too many tokens");
+  // fewer pieces than SMs: the longest pieces get a second CTA each, as far as SMs and scratch memory go
+  p.split_pieces = 0; p.scratch = scratch; p.counters = counters;
+  if (scratch && counters && bound < sm_count()) {
+    const long long per_piece = 2LL * cta_rows * (head_dim + 4);
+    long long n = sm_count() - bound;
+    if (n > bound) n = bound;
+    if (n > scratch_floats / per_piece) n = scratch_floats / per_piece;
+    if (n > SPROUT_PREFILL_SPLIT_MAX) n = SPROUT_PREFILL_SPLIT_MAX;
+    p.split_pieces = (int)n;
+  }
   if (head_dim == 64) return launch_tc<64>(map_k, map_v, p, (int)bound, stream);
   return launch_tc<128>(map_k, map_v, p, (int)bound, stream);
 }

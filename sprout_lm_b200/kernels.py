@@ -37,7 +37,7 @@ _SIGNATURES = {
     "sprout_advance_decode": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
     "sprout_attention_decode": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_attention_decode_fused": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
-    "sprout_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, ctypes.c_longlong, _P, _P, _P],
     "sprout_attention_prefill_tc_supported": [_I, _I, _I],
     "sprout_gemm_bf16": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
 }
@@ -372,6 +372,22 @@ def attention_decode_fused(acc, bias, cos_table, sin_table, k_cache, v_cache, bl
 
 
 PREFILL_VARIANTS = {"auto": 0, "mma_sync": 1, "tcgen05": 2}
+_prefill_scratch: dict = {}      # (device, head_dim) -> (float32 scratch, int32 counters) of the tcgen05 prefill kernel
+
+
+def _prefill_workspace(device, head_dim):
+    key = (device, head_dim)
+    held = _prefill_scratch.get(key)
+    if held is None:
+        lib = load_library()
+        lib.sprout_attention_prefill_scratch_floats.restype = ctypes.c_longlong
+        lib.sprout_attention_prefill_scratch_floats.argtypes = [c_int]
+        lib.sprout_attention_prefill_counters.restype = c_int
+        lib.sprout_attention_prefill_counters.argtypes = []
+        held = (torch.empty(lib.sprout_attention_prefill_scratch_floats(head_dim), dtype=torch.float32, device=device),
+                torch.zeros(lib.sprout_attention_prefill_counters(), dtype=torch.int32, device=device))
+        _prefill_scratch[key] = held
+    return held
 
 
 def attention_prefill(q, k_cache, v_cache, block_table, q_start, positions, out, heads, kv_heads, head_dim, status,
@@ -382,11 +398,15 @@ def attention_prefill(q, k_cache, v_cache, block_table, q_start, positions, out,
     "mma_sync" (every head_dim up to 128 in steps of 16, every page size), or "auto": tcgen05
     where it takes the sizes and the requests bring 128 (token, head) rows each on average."""
     _check_paged(q, k_cache, v_cache, block_table, out, heads, head_dim, "attention_prefill")
+    scratch = counters = None
+    if variant != "mma_sync" and head_dim in (64, 128):
+        scratch, counters = _prefill_workspace(q.device, head_dim)
     _run("sprout_attention_prefill", _ptr(q, "q"), q.stride(0), _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"),
          _ptr(block_table, "block_table", torch.int32), block_table.stride(0), _ptr(q_start, "q_start", torch.int32),
          _ptr(positions, "positions", torch.int32), _ptr(out, "out"), out.stride(0), q.shape[0], q_start.numel() - 1,
          heads, kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], PREFILL_VARIANTS[variant],
-         _ptr(status, "status", torch.int32), _stream())
+         _ptr(scratch, "scratch", torch.float32, True), scratch.numel() if scratch is not None else 0,
+         _ptr(counters, "counters", torch.int32, True), _ptr(status, "status", torch.int32), _stream())
 
 
 def paged_attention(q, cache, ctx, out, heads, kv_heads, head_dim, status):
