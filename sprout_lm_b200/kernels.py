@@ -7,6 +7,7 @@ built or loaded, or no CUDA device is present, calls raise.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from ctypes import c_float, c_int, c_void_p
 
@@ -372,6 +373,8 @@ def attention_decode_fused(acc, bias, cos_table, sin_table, k_cache, v_cache, bl
 
 
 PREFILL_VARIANTS = {"auto": 0, "mma_sync": 1, "tcgen05": 2}
+# which prefill attention kernel the engine's steps use (measurements compare them)
+PREFILL_VARIANT = os.environ.get("SPROUT_PREFILL_ATTENTION", "auto")
 _prefill_scratch: dict = {}      # (device, head_dim) -> (float32 scratch, int32 counters) of the tcgen05 prefill kernel
 
 
@@ -418,8 +421,11 @@ def paged_attention(q, cache, ctx, out, heads, kv_heads, head_dim, status):
             return attention_decode(q, cache.k, cache.v, cache.block_table, ctx.context_lens, out,
                                     heads, kv_heads, head_dim, status)
         if head_dim <= 128:
+            variant = PREFILL_VARIANT
+            if variant == "tcgen05" and not load_library().sprout_attention_prefill_tc_supported(head_dim, cache.k.shape[2], out.stride(0)):
+                variant = "mma_sync"
             return attention_prefill(q, cache.k, cache.v, cache.block_table, ctx.q_start, ctx.positions, out,
-                                     heads, kv_heads, head_dim, status)
+                                     heads, kv_heads, head_dim, status, variant=variant)
     attention_simple(q, cache.k, cache.v, cache.block_table, ctx.seq_of_token, ctx.positions, out,
                      heads, kv_heads, head_dim, status)
 

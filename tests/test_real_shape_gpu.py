@@ -104,3 +104,68 @@ def test_real_layer_sizes_under_all_cuttings(folder, dtype):
                 assert token == int(np.argmax(row)), (rid, at)
     assert len(runner.graphs.graphs) == 1 and next(iter(runner.graphs.graphs.values())).graph is not None
     runner.check_status()
+
+
+LONG_PREFILL = {
+    # head size 64 as in the 0.5B configuration, 7 query heads per key/value head
+    "hd64": dict(hidden_size=896, intermediate_size=512, num_hidden_layers=1, num_attention_heads=14,
+                 num_key_value_heads=2, vocab_size=600, max_position_embeddings=2048, rms_norm_eps=1e-6,
+                 rope_theta=1000000.0, tie_word_embeddings=False, eos_token_id=599),
+    # head size 128 as in the 7B configuration
+    "hd128": dict(hidden_size=1024, intermediate_size=512, num_hidden_layers=1, num_attention_heads=8,
+                  num_key_value_heads=2, vocab_size=600, max_position_embeddings=2048, rms_norm_eps=1e-5,
+                  rope_theta=10000.0, tie_word_embeddings=False, eos_token_id=599),
+}
+
+
+@pytest.mark.parametrize("name", ["hd64", "hd128"])
+def test_long_prefill_on_the_tcgen05_attention(tmp_path, name):
+    """Prompts of several key tiles through the tcgen05 prefill attention (bfloat16): whole (the
+    longest pieces get two CTAs each), in large portions over a growing cache, and two requests
+    in one step, against the plain implementation at every position.  The query and key
+    projections are scaled up so that the softmax leans on particular keys; the bar is the one of
+    the sharpened model in test_replay_gpu.py (0.03 of the largest logit: bfloat16 rounding of
+    peaked scores; the mma.sync kernel lands at the same 0.017 and 0.022 on these two models)."""
+    from sprout_lm_b200 import load_model
+    from sprout_lm_b200.config import parse_config
+    from sprout_lm_b200.engine.step import ModelRunner
+    from sprout_lm_b200.weights import Checkpoint, write_random_model, write_safetensors
+    sizes = LONG_PREFILL[name]
+    folder = write_random_model(tmp_path / name, parse_config(helpers.raw_config(sizes)), seed=7)
+    with Checkpoint(folder) as ck:
+        tensors = {n: ck.tensor(n) for n in ck.inventory()}
+    for n in tensors:
+        if n.endswith("q_proj.weight") or n.endswith("k_proj.weight"):
+            tensors[n] = (tensors[n].float() * 4.0).to(tensors[n].dtype)
+    write_safetensors(folder / "model.safetensors", tensors)
+    rng = np.random.default_rng(3)
+    requests = {"a": helpers.random_tokens(rng, 700, sizes["vocab_size"]), "b": helpers.random_tokens(rng, 333, sizes["vocab_size"])}
+    want = {rid: helpers.plain_logits(folder, toks) for rid, toks in requests.items()}
+    scale = max(float(np.abs(w).max()) for w in want.values())
+    model = load_model(folder, dtype="bfloat16")
+
+    def portions(toks, rid, sizes_):
+        steps, at = [], 0
+        for n in sizes_:
+            n = min(n, len(toks) - at)
+            if n <= 0:
+                break
+            steps.append({"entries": [(rid, toks[at:at + n], list(range(n)))], "end": []})
+            at += n
+        assert at == len(toks)
+        return steps
+
+    plans = {
+        "whole": helpers.plan_whole(requests),
+        "portions": portions(requests["a"], "a", (300, 256, 144)) + portions(requests["b"], "b", (129, 204)),
+        "together": [{"entries": [("a", requests["a"][:400], list(range(400))), ("b", requests["b"][:200], list(range(200)))], "end": []},
+                     {"entries": [("a", requests["a"][400:], list(range(300))), ("b", requests["b"][200:], list(range(133)))], "end": []}],
+    }
+    for label, plan in plans.items():
+        runner = ModelRunner(model, num_pages=80, page_tokens=16, max_requests=4, prefix_caching=False)
+        got = helpers.run_plan_in_process(runner, plan)
+        runner.check_status()
+        for rid, toks in requests.items():
+            for pos in range(len(toks)):
+                err = float(np.abs(got[(rid, pos)] - want[rid][pos]).max())
+                assert err <= 0.03 * scale, (label, rid, pos, err, scale)
