@@ -53,10 +53,11 @@ struct Params {
   int* status;
 };
 
-template <int BN>
+// PAIR: two CTAs share a 256 x BN tile; each holds its own 128 rows of A and half of B's rows.
+template <int BN, bool PAIR = false>
 struct Layout {
   static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
-  static constexpr int B_BYTES = BN * BLOCK_K * 2;
+  static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * BLOCK_K * 2;
   static constexpr int B_PADDED = (B_BYTES + 1023) / 1024 * 1024;
   static constexpr int STAGE_BYTES = A_BYTES + B_PADDED;
   static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) > 12 ? 12 : (SMEM_BUDGET / STAGE_BYTES);
@@ -72,11 +73,25 @@ struct Work { int row0, col0, kb_begin, num_kb, split; };
 // The kernel is persistent: a CTA walks the work list with stride gridDim.x.  The TMA ring runs
 // on across tiles, and two accumulators in tensor memory alternate, so that the epilogue of one
 // tile overlaps the MMAs of the next.
-template <int BN, bool SWAP>
+//
+// PAIR (tokens on M only): the CTAs come in clusters of two that work on 256 x BN tiles with
+// tcgen05.mma.cta_group::2.  Each CTA copies its own 128 rows of A and half of the tile's rows of
+// B (so a pair moves 2 x (16 + BN / 8) KB per k-block from L2 where two single CTAs move
+// 2 x (16 + BN / 4) KB: the operand traffic from L2 is what bounds these products); the first
+// CTA's thread issues the MMAs for both, each CTA's epilogue warps drain its own 128 rows from
+// its own tensor memory.  The copies of both CTAs count on the first CTA's "full" barriers; the
+// commits arrive on the "empty" and "accumulator full" barriers of both CTAs; the second CTA's
+// epilogue warps arrive on the first CTA's "accumulator empty" barriers.
+template <int BN, bool SWAP, bool PAIR = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
                     const __grid_constant__ CUtensorMap map_out, const Params p) {
-  using L = Layout<BN>;
+  static_assert(!(PAIR && SWAP), "pairs work on token tiles");
+  using L = Layout<BN, PAIR>;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0;                       // 0 issues the MMAs
+  const int first_work = PAIR ? (int)blockIdx.x >> 1 : (int)blockIdx.x;     // this CTA's (pair's) first item and stride
+  const int work_stride = PAIR ? (int)gridDim.x >> 1 : (int)gridDim.x;
+  constexpr int TILE_M = PAIR ? 2 * BLOCK_M : BLOCK_M;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* staging = smem + L::STAGES * L::STAGE_BYTES;
@@ -90,7 +105,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
-  const int row_tiles = ((SWAP ? p.N : p.M) + BLOCK_M - 1) / BLOCK_M;
+  const int row_tiles = ((SWAP ? p.N : p.M) + TILE_M - 1) / TILE_M;
   const int col_tiles = ((SWAP ? p.M : p.N) + BN - 1) / BN;
   const int splits = (total_kb + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
   const int total_work = row_tiles * col_tiles * splits;
@@ -101,7 +116,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     k.split = w % splits;
     const int tile = w / splits;
     if (SWAP) { k.row0 = (tile / col_tiles) * BLOCK_M; k.col0 = (tile % col_tiles) * BN; }   // token tiles of one weight tile side by side
-    else { k.row0 = (tile % row_tiles) * BLOCK_M; k.col0 = (tile / row_tiles) * BN; }
+    else { k.row0 = (tile % row_tiles) * TILE_M + (int)rank * BLOCK_M; k.col0 = (tile / row_tiles) * BN; }   // this CTA's rows
     k.kb_begin = k.split * p.k_blocks_per_split;
     k.num_kb = min(total_kb, k.kb_begin + p.k_blocks_per_split) - k.kb_begin;
     return k;
@@ -110,7 +125,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+    for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], PAIR ? 16 : 8); }
     mbar_init(epi_bar, 8);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -120,6 +135,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (PAIR) {
+    // The pair's MMAs write both CTAs' tensor memory at one address.  Each CTA has its SM to
+    // itself (its shared memory leaves no room for another) and has allocated from an empty tensor
+    // memory, so both got column 0; anything else is refused.  Nobody counts on the other CTA's
+    // barriers before they are initialised: the cluster meets first.
+    if (tmem_base != 0 && threadIdx.x == 0) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_BAD_LAYOUT); }
+    cluster_barrier();
+  }
 
   // The copy thread and the MMA thread each run one thread's worth of dependent instructions per
   // k-block, and the tensor cores finish a k-block in under 300 cycles: their loops keep the
@@ -138,45 +161,53 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     uint32_t stage_addr = smem_base;
     int it = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+    // pairs: both CTAs' copies count on the first CTA's barrier, which expects both CTAs' bytes
+    const uint32_t count_base = PAIR ? cluster_map_shared(full_base, 0) : full_base;
+    constexpr uint32_t STAGE_TX = (PAIR ? 2 : 1) * (L::A_BYTES + L::B_BYTES);
+    auto copy = [&](uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+      if (PAIR) tma_load_2d_pair(dst, map, bar, x, y); else tma_load_2d_addr(dst, map, bar, x, y);
+    };
+    for (int w = first_work; w < total_work && ok; w += work_stride) {
       const Work k = work_at(w);
-      const int weight_row = SWAP ? k.row0 : k.col0, act_row = SWAP ? k.col0 : k.row0;
+      const int weight_row = SWAP ? k.row0 : k.col0 + (PAIR ? (int)rank * (BN / 2) : 0), act_row = SWAP ? k.col0 : k.row0;
       int early = 0;
-      if (w == (int)blockIdx.x) {
+      if (w == first_work) {
         early = min(k.num_kb, L::STAGES);
         for (int i = 0; i < early; i++) {
-          mbar_expect_tx_addr(full_base + 8 * i, L::A_BYTES + L::B_BYTES);
-          tma_load_2d_addr(smem_base + i * L::STAGE_BYTES + W_OFF, weight_map, full_base + 8 * i, (k.kb_begin + i) * BLOCK_K, weight_row);
+          if (rank == 0) mbar_expect_tx_addr(full_base + 8 * i, STAGE_TX);
+          copy(smem_base + i * L::STAGE_BYTES + W_OFF, weight_map, count_base + 8 * i, (k.kb_begin + i) * BLOCK_K, weight_row);
         }
         pdl_wait();
       }
       int x = k.kb_begin * BLOCK_K;
       for (int i = 0; i < k.num_kb; i++, it++, x += BLOCK_K) {
-        const uint32_t full_addr = full_base + 8 * s;
+        const uint32_t count_addr = count_base + 8 * s;
         if (i >= early) {
           if (!mbar_wait_addr(empty_base + 8 * s, parity, abort_flag)) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); ok = false; break; }
-          mbar_expect_tx_addr(full_addr, L::A_BYTES + L::B_BYTES);
-          tma_load_2d_addr(stage_addr + W_OFF, weight_map, full_addr, x, weight_row);
+          if (rank == 0) mbar_expect_tx_addr(full_base + 8 * s, STAGE_TX);
+          copy(stage_addr + W_OFF, weight_map, count_addr, x, weight_row);
         }
-        tma_load_2d_addr(stage_addr + X_OFF, act_map, full_addr, x, act_row);
+        copy(stage_addr + X_OFF, act_map, count_addr, x, act_row);
         issued = it + 1;
         if (++s == L::STAGES) { s = 0; parity ^= 1; stage_addr = smem_base; } else stage_addr += L::STAGE_BYTES;
       }
     }
-  } else if (warp == 1 && lane == 0) {
-    // ---------------- MMA issuer
-    const uint32_t idesc = umma_idesc(BLOCK_M, BN);
+  } else if (warp == 1 && lane == 0 && rank == 0) {
+    // ---------------- MMA issuer (of a pair: the first CTA's)
+    const uint32_t idesc = umma_idesc(TILE_M, BN);
     const uint64_t a_desc0 = umma_smem_desc(smem), b_desc0 = umma_smem_desc(smem + L::A_BYTES);
     constexpr uint64_t STAGE_STEP = L::STAGE_BYTES >> 4;      // a stage further in the descriptor's address field
     uint64_t a_desc = a_desc0, b_desc = b_desc0;
     uint32_t s = 0, parity = 0;
     bool ok = true;
     int tiles_done = 0;
-    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, tiles_done++) {
+    for (int w = first_work; w < total_work && ok; w += work_stride, tiles_done++) {
       const Work k = work_at(w);
       const int acc = tiles_done & 1;
-      // the epilogue must have read this accumulator's previous tile out
-      if (!mbar_wait(&acc_empty[acc], ((tiles_done >> 1) & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); break; }
+      // the epilogue (of both CTAs) must have read this accumulator's previous tile out
+      const bool drained = PAIR ? mbar_wait_cluster(smem_u32(&acc_empty[acc]), ((tiles_done >> 1) & 1) ^ 1, abort_flag)
+                                : mbar_wait(&acc_empty[acc], ((tiles_done >> 1) & 1) ^ 1, abort_flag);
+      if (!drained) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); break; }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * BN;
       uint32_t accumulate = 0;
@@ -184,15 +215,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
         if (!mbar_wait_addr(full_base + 8 * s, parity, abort_flag)) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); ok = false; break; }
         tc_fence_after();
         // advancing 16 elements (32 bytes) along K inside the swizzled row: +2 in the address field
-        umma_bf16(d_tmem, a_desc, b_desc, idesc, accumulate);
-        umma_bf16(d_tmem, a_desc + 2, b_desc + 2, idesc, 1);
-        umma_bf16(d_tmem, a_desc + 4, b_desc + 4, idesc, 1);
-        umma_bf16(d_tmem, a_desc + 6, b_desc + 6, idesc, 1);
+        if (PAIR) {
+          umma_bf16_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
+          umma_bf16_pair(d_tmem, a_desc + 2, b_desc + 2, idesc, 1);
+          umma_bf16_pair(d_tmem, a_desc + 4, b_desc + 4, idesc, 1);
+          umma_bf16_pair(d_tmem, a_desc + 6, b_desc + 6, idesc, 1);
+          umma_commit_pair(empty_base + 8 * s, 3);   // the stage is free in both CTAs once these MMAs have read it
+        } else {
+          umma_bf16(d_tmem, a_desc, b_desc, idesc, accumulate);
+          umma_bf16(d_tmem, a_desc + 2, b_desc + 2, idesc, 1);
+          umma_bf16(d_tmem, a_desc + 4, b_desc + 4, idesc, 1);
+          umma_bf16(d_tmem, a_desc + 6, b_desc + 6, idesc, 1);
+          umma_commit_addr(empty_base + 8 * s);   // the stage is free once these MMAs have read it
+        }
         accumulate = 1;
-        umma_commit_addr(empty_base + 8 * s);   // the stage is free once these MMAs have read it
         if (++s == L::STAGES) { s = 0; parity ^= 1; a_desc = a_desc0; b_desc = b_desc0; } else { a_desc += STAGE_STEP; b_desc += STAGE_STEP; }
       }
-      if (ok) umma_commit(&acc_full[acc]);   // the accumulator is complete once all MMAs are
+      if (ok) {                              // the accumulator is complete once all MMAs are
+        if (PAIR) umma_commit_pair(smem_u32(&acc_full[acc]), 3); else umma_commit(&acc_full[acc]);
+      }
     }
   } else if (warp >= 2) {
     // ---------------- epilogue: TMEM -> registers -> global
@@ -214,7 +255,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
       epi_phase ^= 1;
       return (bool)__shfl_sync(0xffffffffu, met, 0);
     };
-    for (int w = blockIdx.x; w < total_work; w += gridDim.x, tiles_done++) {
+    // the accumulator goes back to the MMA issuer: of a pair's second CTA, to the first CTA's barrier
+    auto release_accumulator = [&](int acc) {
+      if (PAIR && rank == 1) mbar_arrive_cluster(cluster_map_shared(smem_u32(&acc_empty[acc]), 0));
+      else mbar_arrive(&acc_empty[acc]);
+    };
+    for (int w = first_work; w < total_work; w += work_stride, tiles_done++) {
       const Work k = work_at(w);
       const int acc = tiles_done & 1;
       const int row = k.row0 + quarter * 32 + lane;
@@ -269,7 +315,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
         if (!met) break;
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        if (lane == 0) release_accumulator(acc);
         continue;
       }
 #pragma unroll 1
@@ -365,7 +411,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
       // this warp has read the accumulator out: hand it back to the MMA issuer
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (lane == 0) release_accumulator(acc);
     }
   }
   if (warp == 2 && lane == 0) bulk_wait_group<0>();     // the reductions have been performed
@@ -377,11 +423,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
       mbar_wait(&full_bar[i % L::STAGES], (i / L::STAGES) & 1);
   }
   __syncthreads();
+  if (PAIR) cluster_barrier();      // neither CTA leaves while the other may still count on its barriers or read its memory
   if (warp == 1) tmem_dealloc(tmem_base, L::TMEM_COLS);
 }
 
 // ------------------------------------------------------------------ host side
 // `work` = tiles x K splits; the grid is one CTA per SM at most, each walking the work list.
+// Pairs: `work` counts 256 x BN tiles; the grid is one cluster of two CTAs per two SMs at most.
+template <int BN>
+int launch_pair(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const CUtensorMap& out_map, const Params& p, int work,
+                cudaStream_t stream) {
+  using L = Layout<BN, true>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
+    if (err != cudaSuccess) return sprout_fail("gemm_bf16: cannot reserve %d bytes of shared memory: %s", L::SMEM_BYTES, cudaGetErrorString(err));
+    configured = true;
+  }
+  const int pairs = work < sm_count() / 2 ? work : sm_count() / 2;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(2 * pairs);
+  config.blockDim = dim3(NUM_THREADS);
+  config.dynamicSmemBytes = L::SMEM_BYTES;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  attributes[0].id = cudaLaunchAttributeClusterDimension;
+  attributes[0].val.clusterDim.x = 2;
+  attributes[0].val.clusterDim.y = 1;
+  attributes[0].val.clusterDim.z = 1;
+  attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attributes;
+  config.numAttrs = sprout_pdl_enabled() ? 2 : 1;
+  cudaLaunchKernelEx(&config, gemm_tcgen05_kernel<BN, false, true>, rows_map, cols_map, out_map, p);
+  return sprout_check_launch("gemm_bf16 (pairs)");
+}
+
 template <int BN, bool SWAP>
 int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const CUtensorMap& out_map, const Params& p, int work,
            cudaStream_t stream) {
@@ -402,7 +479,8 @@ int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const CUten
 // A [M, K] bf16 row stride lda; W [N, K] bf16 contiguous; out [M, N] row stride ldo, bf16 or
 // float32.  residual != 0: out is float32 and the product is added to it.  orientation: 0 picks
 // by M (weight rows on the MMA's M axis up to 256 tokens, tokens on M beyond), 1 forces tokens
-// on M (128 x 128 or 128 x 256 tiles), 2 weights on M (tokens in tiles of 16..256).
+// on M (128 x 128 tiles, or 256 x 256 tiles of CTA pairs where N is a multiple of 256), 2 weights
+// on M (tokens in tiles of 16..256), 3 tokens on M with single CTAs only, 4 with CTA pairs only.
 // split_k > 1 (weights on M, residual, at most 256 tokens) divides K among CTAs and adds with
 // atomics.
 // residual == 2: the SwiGLU epilogue (no bias; out is bfloat16 [M, N/2]; N a multiple of 16).
@@ -423,7 +501,7 @@ SPROUT_API int sprout_gemm_bf16(const void* A, const void* W, const float* bias,
   SPROUT_REQUIRE(lda >= K && (swiglu || ldo >= N), "gemm_bf16: row strides smaller than the rows");
   SPROUT_REQUIRE(out_dtype == SPROUT_F32 || out_dtype == SPROUT_BF16, "gemm_bf16: unknown output dtype %d", out_dtype);
   SPROUT_REQUIRE(!residual || out_dtype == SPROUT_F32, "gemm_bf16: a residual needs a float32 output");
-  const bool swap = orientation == 2 || (orientation == 0 && M <= 256);
+  const bool swap = orientation == 2 || (orientation == 0 && M <= 256);    // 1: tokens on M in CTA pairs, 3: single CTAs
   if (split_k < 1) split_k = 1;
   SPROUT_REQUIRE(split_k == 1 || (swap && residual && M <= 256), "gemm_bf16: split_k needs weights-on-M with a residual output and at most 256 tokens");
 
@@ -454,15 +532,22 @@ SPROUT_API int sprout_gemm_bf16(const void* A, const void* W, const float* bias,
   // tokens on M: 128 x 256 tiles where they tile N exactly (a quarter less operand traffic from
   // L2 than 128 x 128), else 128 x 128
   const int bn = (N % 256 == 0) ? 256 : 128;
+  // CTA pairs pay where the tile is 256 wide (measured: gate/up 2048 x 9728 x 896 41 -> 39 us,
+  // 8192 tokens 145 -> 134 us); on 128-wide tiles single CTAs are as fast and launch more cheaply
+  const bool pair = orientation == 4 || (orientation != 3 && bn == 256);
   if (tensor_map(A, M, K, lda, BLOCK_M, &map_a)) return 1;
-  if (tensor_map(W, N, K, K, bn, &map_w)) return 1;
-  const long long work = (long long)((N + bn - 1) / bn) * ((M + BLOCK_M - 1) / BLOCK_M);
+  if (tensor_map(W, N, K, K, pair ? bn / 2 : bn, &map_w)) return 1;
+  const long long work = (long long)((N + bn - 1) / bn) * ((M + (pair ? 2 : 1) * BLOCK_M - 1) / ((pair ? 2 : 1) * BLOCK_M));
   SPROUT_REQUIRE(work <= 0x7fffffffLL, "gemm_bf16: too many tiles");
   // the residual epilogue goes through the TMA unit where the output's rows allow a tensor map
   CUtensorMap map_out = map_a;
   if (p.epilogue == EPI_RESIDUAL && ldo % 4 == 0 && ((uintptr_t)out & 15) == 0) {
     if (tensor_map(out, M, N, ldo, BLOCK_M, &map_out, 4)) return 1;
     p.epilogue = EPI_RESIDUAL_TMA;
+  }
+  if (pair) {
+    if (bn == 256) return launch_pair<256>(map_a, map_w, map_out, p, (int)work, stream);
+    return launch_pair<128>(map_a, map_w, map_out, p, (int)work, stream);
   }
   if (bn == 256) return launch<256, false>(map_a, map_w, map_out, p, (int)work, stream);
   return launch<128, false>(map_a, map_w, map_out, p, (int)work, stream);

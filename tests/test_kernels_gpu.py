@@ -227,7 +227,8 @@ def test_rope_append(status, dtype, heads, kv_heads, head_dim, page, theta):
 
 # ------------------------------------------------------------------------------- matrix products
 SHAPES = [(1, 1, 8), (1, 896, 896), (3, 130, 72), (8, 1152, 896), (17, 509, 96), (64, 256, 4864), (100, 77, 200),
-          (128, 896, 896), (129, 300, 136), (257, 1000, 328), (600, 1152, 896), (2048, 896, 4864)]
+          (128, 896, 896), (129, 300, 136), (257, 1000, 328), (600, 1152, 896), (2048, 896, 4864), (300, 512, 200),
+          (1100, 1024, 896)]
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
@@ -251,9 +252,11 @@ def test_gemm_simple_float32(M, N, K):
     assert (x.double() - want).abs().max().item() <= tol
 
 
-@pytest.mark.parametrize("orientation", [0, 1, 2])
+@pytest.mark.parametrize("orientation", [0, 1, 2, 3, 4])
 @pytest.mark.parametrize("M,N,K", SHAPES)
 def test_gemm_bf16_tensor_cores(status, M, N, K, orientation):
+    """orientation 0: the kernel's own choice; 1: tokens on the MMA's M axis; 2: weight rows on M;
+    3: tokens on M with single CTAs; 4: with CTA pairs (tcgen05.mma.cta_group::2)."""
     from sprout_lm_b200 import kernels
     a, w, bias = rand(M, K, dtype=torch.bfloat16), rand(N, K, dtype=torch.bfloat16, seed=1), rand(N, seed=2)
     want = a.double() @ w.double().T + bias.double()
@@ -268,6 +271,25 @@ def test_gemm_bf16_tensor_cores(status, M, N, K, orientation):
     want_res = x.double() + a.double() @ w.double().T
     kernels.gemm_bf16(a, w, x, status, residual=x, orientation=orientation)
     assert (x.double() - want_res).abs().max().item() <= 1e-5 * scale + 1e-6
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("orientation", [0, 2, 3, 4])
+@pytest.mark.parametrize("M,inter,K", [(5, 200, 72), (300, 256, 136), (2048, 384, 896), (513, 4864, 96)])
+def test_gemm_bf16_swiglu_epilogue(status, M, inter, K, orientation):
+    """gate and up rows interleaved in blocks of 8; the epilogue writes silu(gate) * up."""
+    from sprout_lm_b200 import kernels
+    from sprout_lm_b200.parts.mlp import interleave_gate_up
+    if orientation == 2 and M > 256:
+        pytest.skip("weights on M takes up to 256 tokens")
+    a = rand(M, K, dtype=torch.bfloat16)
+    gate, up = rand(inter, K, dtype=torch.bfloat16, seed=1), rand(inter, K, dtype=torch.bfloat16, seed=2)
+    w = interleave_gate_up(gate, up)
+    out = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_bf16(a, w, out, status, swiglu=True, orientation=orientation)
+    g, u = a.double() @ gate.double().T, a.double() @ up.double().T
+    want = g / (1 + torch.exp(-g)) * u
+    assert (out.double() - want).abs().max().item() <= 8e-3 * max(1.0, want.abs().max().item())
     assert int(status.item()) == 0
 
 
