@@ -351,6 +351,60 @@ def timed_attention(tokens: int, repeats: int = 20) -> dict:
     return result
 
 
+def timed_gemms(tokens: int, repeats: int = 20) -> dict:
+    """The model's four projections at ``tokens`` tokens, each alone: 20 launches replayed from a
+    CUDA graph (no host time between them), beside the library's plain bfloat16 product of the
+    same shape for scale (it fuses nothing and is not on the engine's path)."""
+    import torch
+    from sprout_lm_b200 import kernels
+    from sprout_lm_b200.parts.mlp import interleave_gate_up
+    hidden, inter = CONFIG_05B["hidden_size"], CONFIG_05B["intermediate_size"]
+    heads, kv_heads = CONFIG_05B["num_attention_heads"], CONFIG_05B["num_key_value_heads"]
+    qkv = (heads + 2 * kv_heads) * (hidden // heads)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(0)
+    rand = lambda *shape: (torch.randn(*shape, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+
+    def replayed(call):
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        graph, stream = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(graph, stream=stream):
+                for _ in range(repeats):
+                    call()
+        graph.replay()
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        return begin.elapsed_time(end) * 1000 / repeats
+
+    result = {"impl": "ours", "only": "gemm", "tokens": tokens}
+    cases = [("qkv", qkv, hidden, "bias"), ("o", hidden, hidden, "residual"), ("gate_up", 2 * inter, hidden, "swiglu"),
+             ("down", hidden, inter, "residual")]
+    for name, n, k, kind in cases:
+        a, w = rand(tokens, k), rand(n, k)
+        kw = {}
+        if kind == "bias":
+            out, kw = torch.empty(tokens, n, dtype=torch.bfloat16, device="cuda"), {"bias": torch.zeros(n, device="cuda")}
+        elif kind == "residual":
+            out = torch.zeros(tokens, n, device="cuda")
+            kw = {"residual": out}
+        else:
+            w = interleave_gate_up(w[:n // 2].contiguous(), w[n // 2:].contiguous())
+            out, kw = torch.empty(tokens, n // 2, dtype=torch.bfloat16, device="cuda"), {"swiglu": True}
+        us = replayed(lambda: kernels.gemm_bf16(a, w, out, status, **kw))
+        library = replayed(lambda: torch.matmul(a, w.t()))
+        result[name] = {"shape": [tokens, n, k], "epilogue": kind, "us": round(us, 1),
+                        "tflops": round(2.0 * tokens * n * k / us / 1e6), "library_plain_us": round(library, 1)}
+    assert int(status.item()) == 0
+    return result
+
+
 def run(args) -> dict:
     import numpy as np
     import torch
@@ -360,6 +414,8 @@ def run(args) -> dict:
     kernels.load_library(verbose=True)
     if args.only == "attention":
         return timed_attention(args.tokens)
+    if args.only == "gemm":
+        return timed_gemms(args.tokens)
     layers = args.layers or CONFIG_05B["num_hidden_layers"]
     folder = model_folder(layers)
     model = load_model(folder, dtype="bfloat16", device="cuda:0")
@@ -420,9 +476,9 @@ def main() -> int:
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
-    parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate", "attention"], default="all",
+    parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate", "attention", "gemm"], default="all",
                         help="measure one part only (for profiling captures); the JSON line then holds that part")
-    parser.add_argument("--tokens", type=int, default=2048, help="with --only attention: tokens of the one request")
+    parser.add_argument("--tokens", type=int, default=2048, help="with --only attention or gemm: tokens of the one request")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
