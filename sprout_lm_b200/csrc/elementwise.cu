@@ -354,6 +354,91 @@ rope_append_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ 
   }
 }
 
+// The same from float32 sums (what a split-K product leaves) plus a bias: the sums are read as
+// float4, cleared, rotated; q goes to qkv as bfloat16, k and v to the cache.
+__global__ void __launch_bounds__(256)
+rope_append_acc_vec_kernel(__nv_bfloat16* __restrict__ qkv, float* __restrict__ acc, const float* __restrict__ bias,
+                           const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                           const int* __restrict__ block_table, int table_stride, const float* __restrict__ cos_table,
+                           const float* __restrict__ sin_table, int max_positions, __nv_bfloat16* __restrict__ k_cache,
+                           __nv_bfloat16* __restrict__ v_cache, int num_tokens, int heads, int kv_heads, int head_dim,
+                           int page_tokens, int num_pages, int write_cache, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int half = head_dim >> 1, half_chunks = half >> 3;
+  const int rot_items = (heads + kv_heads) * half_chunks;
+  const int v_items = kv_heads * (head_dim >> 3);                // the v sums are cleared even when nothing is stored
+  const int per_token = rot_items + v_items;
+  const int width = (heads + 2 * kv_heads) * head_dim;
+  const bool rotate = cos_table != nullptr;
+  const long long total = (long long)num_tokens * per_token;
+  auto take8 = [&](float* src, const float* b, float (&v)[8]) {   // sums + bias, and the sums cleared
+    const float4 lo = ((const float4*)src)[0], hi = ((const float4*)src)[1];
+    ((float4*)src)[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    ((float4*)src)[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+    if (b) {
+      const float4 blo = ((const float4*)b)[0], bhi = ((const float4*)b)[1];
+      v[0] += blo.x; v[1] += blo.y; v[2] += blo.z; v[3] += blo.w; v[4] += bhi.x; v[5] += bhi.y; v[6] += bhi.z; v[7] += bhi.w;
+    }
+  };
+  auto pack8 = [](const float (&v)[8]) {
+    uint4 o;
+    __nv_bfloat16* q = (__nv_bfloat16*)&o;
+#pragma unroll
+    for (int i = 0; i < 8; i++) q[i] = __float2bfloat16_rn(v[i]);
+    return o;
+  };
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / per_token), item = (int)(idx % per_token);
+    const int pos = positions[t];
+    if (pos < 0 || (rotate && pos >= max_positions)) {
+      if (item == 0) atomicOr(status, SPROUT_STATUS_BAD_POSITION);
+      continue;
+    }
+    float* acc_row = acc + (size_t)t * width;
+    int page = 0;
+    bool page_ok = false;
+    const bool to_cache = item >= heads * half_chunks;
+    if (to_cache && write_cache) {
+      page = block_table[(size_t)seq_of_token[t] * table_stride + pos / page_tokens];
+      page_ok = page >= 0 && page < num_pages;
+      if (!page_ok && item == heads * half_chunks) atomicOr(status, SPROUT_STATUS_BAD_PAGE);
+    }
+    const int slot = pos % page_tokens;
+    if (item < rot_items) {
+      const int h = item / half_chunks, d = (item % half_chunks) * 8;
+      float a[8], b[8];
+      take8(acc_row + h * head_dim + d, bias ? bias + h * head_dim + d : nullptr, a);
+      take8(acc_row + h * head_dim + half + d, bias ? bias + h * head_dim + half + d : nullptr, b);
+      if (h >= heads && !page_ok) continue;
+      float ra[8], rb[8];
+      if (rotate) {
+        const float4* cp = (const float4*)(cos_table + (size_t)pos * half + d);
+        const float4* sp = (const float4*)(sin_table + (size_t)pos * half + d);
+        const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+        const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) { ra[i] = a[i] * c[i] - b[i] * sn[i]; rb[i] = b[i] * c[i] + a[i] * sn[i]; }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; i++) { ra[i] = a[i]; rb[i] = b[i]; }
+      }
+      __nv_bfloat16* dst = h < heads ? qkv + (size_t)t * width + h * head_dim
+                                     : k_cache + (((size_t)page * kv_heads + (h - heads)) * page_tokens + slot) * head_dim;
+      *(uint4*)(dst + d) = pack8(ra);
+      *(uint4*)(dst + half + d) = pack8(rb);
+    } else {
+      const int vi = item - rot_items, h = vi / (head_dim >> 3), d = (vi % (head_dim >> 3)) * 8;
+      float v[8];
+      const int col = (heads + kv_heads + h) * head_dim + d;
+      take8(acc_row + col, bias ? bias + col : nullptr, v);
+      if (page_ok) *(uint4*)(v_cache + (((size_t)page * kv_heads + h) * page_tokens + slot) * head_dim + d) = pack8(v);
+    }
+  }
+}
+
 SPROUT_API int sprout_rope_append(void* qkv, float* acc, const float* bias, int dtype, const int* positions, const int* seq_of_token,
                                   const int* block_table, int table_stride, const float* cos_table,
                                   const float* sin_table, int max_positions, void* k_cache, void* v_cache,
@@ -369,6 +454,15 @@ SPROUT_API int sprout_rope_append(void* qkv, float* acc, const float* bias, int 
   const int threads = pairs >= 1024 ? 1024 : (pairs + 31) / 32 * 32;
   const bool aligned = ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0 &&
                        ((uintptr_t)cos_table & 15) == 0 && ((uintptr_t)sin_table & 15) == 0;
+  if (dtype == SPROUT_BF16 && acc && head_dim % 16 == 0 && aligned && ((uintptr_t)acc & 15) == 0 && ((uintptr_t)bias & 15) == 0 &&
+      num_tokens >= 16) {
+    const long long items = (long long)num_tokens * ((heads + kv_heads) * (head_dim / 16) + kv_heads * (head_dim / 8));
+    const int blocks = (int)((items + 255) / 256 < 148 * 8 ? (items + 255) / 256 : 148 * 8);
+    sprout_launch(rope_append_acc_vec_kernel, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)qkv, acc, bias, positions,
+        seq_of_token, block_table, table_stride, cos_table, sin_table, max_positions, (__nv_bfloat16*)k_cache,
+        (__nv_bfloat16*)v_cache, num_tokens, heads, kv_heads, head_dim, page_tokens, num_pages, write_cache, status);
+    return sprout_check_launch("rope_append");
+  }
   if (dtype == SPROUT_BF16 && !acc && head_dim % 16 == 0 && aligned && num_tokens >= 64) {
     const long long items = (long long)num_tokens * ((heads + kv_heads) * (head_dim / 16) + kv_heads * (head_dim / 8));
     const int blocks = (int)((items + 255) / 256 < 148 * 8 ? (items + 255) / 256 : 148 * 8);

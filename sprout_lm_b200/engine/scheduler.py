@@ -204,10 +204,12 @@ class Engine:
                 break
             if request.status != "running":
                 continue                   # preempted by an older request while planning
-            history = request.prompt + request.output
+            # the request's history is prompt + output; it is sliced below without being built
+            prompt, output = request.prompt, request.output
+            total = len(prompt) + len(output)
             phase = self._phase(request)
             start = request.seq.length
-            remaining = len(history) - start - (1 if phase == "recompute" else 0)
+            remaining = total - start - (1 if phase == "recompute" else 0)
             count = min(budget, 1 if phase == "decode" else self.options.prefill_chunk_size, remaining)
             computed = 0
             for i in range(count):
@@ -216,8 +218,14 @@ class Engine:
                 computed += 1
             budget -= computed
             if computed and request.status == "running":
-                planned.append((request, phase, start, history[start:start + computed],
-                                start + computed == len(history)))
+                end = start + computed
+                if start >= len(prompt):
+                    tokens = output[start - len(prompt):end - len(prompt)]
+                elif end <= len(prompt):
+                    tokens = prompt[start:end]
+                else:
+                    tokens = prompt[start:] + output[:end - len(prompt)]
+                planned.append((request, phase, start, tokens, end == total))
         work = []
         if planned:
             entries = [StepEntry(r.seq, tokens, [len(tokens) - 1] if wants else [])

@@ -126,6 +126,20 @@ def test_rope_append_many_tokens(status, heads, kv_heads, head_dim, page, theta,
                         heads, kv_heads, head_dim, page, True, status)
     assert torch.equal(few_q, qkv[:6])
     assert torch.equal(k2[pg[:6].to(DEV), :, slot[:6].to(DEV), :], k_cache[pg[:6].to(DEV), :, slot[:6].to(DEV), :])
+    # the same from float32 sums plus a bias (what a split-K product leaves): the rotated q lands in
+    # qkv, k and v in the cache, the sums are cleared
+    bias = rand(width, seed=9)
+    acc = torch.zeros(T + 2, width, device=DEV)
+    acc[:T] = original.float() - bias
+    out_q = torch.zeros_like(original)
+    k4, v4 = torch.zeros_like(k_cache), torch.zeros_like(v_cache)
+    kernels.rope_append(out_q, positions.to(DEV), seq_of_token.to(DEV), table.to(DEV), cos, sin, k4, v4,
+                        heads, kv_heads, head_dim, page, True, status, acc=acc[:T], bias=bias)
+    assert (out_q[:, :heads * head_dim].float() - qkv[:, :heads * head_dim].float()).abs().max().item() <= 2e-2
+    assert (k4.float() - k_cache.float()).abs().max().item() <= 2e-2
+    assert (v4.float() - v_cache.float()).abs().max().item() <= 2e-2
+    assert float(acc.abs().max()) == 0.0
+    assert int((k4 != 0).any(-1).any(1).sum().item()) == T
     # without the cache write only q changes
     k3 = torch.zeros_like(k_cache)
     only_q = original.clone()
