@@ -100,9 +100,12 @@ class DecodeGraph:
     def stager(self):                     # the bytes of the last copy, for the runner's statistics
         return self
 
-    def stage(self, entries, temperatures, uniforms) -> StepContext:
+    def stage(self, entries, temperatures, uniforms, copy: bool = True) -> StepContext:
+        """Fill the pinned mirror; with ``copy`` also send it to the device (``run`` leaves that
+        to the captured graph, whose first node is the same copy)."""
         if self.copied is not None:
             self.copied.synchronize()     # the previous copy has read the host buffer
+            self.copied = None
         R, P = self.requests, self.table_pages
         lengths = [e.seq.length for e in entries]
         self._put("token_ids", [e.tokens[0] for e in entries])
@@ -134,10 +137,11 @@ class DecodeGraph:
                     known[i] = count
                 elif self.runner.manager.groups[g].kind == "window":
                     self.array[base + i * P:base + i * P + count] = pages
-        self.device_buf.copy_(self.host, non_blocking=True)
-        event = torch.cuda.Event()
-        event.record()
-        self.copied = event
+        if copy:
+            self.device_buf.copy_(self.host, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record()
+            self.copied = event
         return self.ctx
 
     def _forward(self, ctx):
@@ -146,24 +150,33 @@ class DecodeGraph:
         kernels.sample(logits, tokens, self.runner.runtime.status, ctx.floats["temperature"], ctx.floats["uniform"])
         return logits, tokens
 
-    def run(self, entries, temperatures, uniforms) -> torch.Tensor:
-        """Stage the batch and run the step; the sampled tokens (int32, device)."""
-        ctx = self.stage(entries, temperatures, uniforms)
+    def run(self, entries, temperatures, uniforms) -> list:
+        """Stage the batch and run the step; the sampled token ids, on the host.  The captured
+        graph holds the whole round trip: the copy of the pinned mirror to the device, the step's
+        kernels, and the copy of the sampled tokens into pinned host memory; the host launches it
+        and waits for the stream."""
         if self.graph is None:
             # First use: this call's step runs eagerly (that also does the kernels' first-use
             # set-up), then the same launches are captured for later calls.  Capturing records
             # without running, so the step has run exactly once: a mixer that updates
             # per-request state must not see a step twice.
+            ctx = self.stage(entries, temperatures, uniforms)
             _, tokens = self._forward(ctx)
+            result = tokens.tolist()
+            self.host_tokens = torch.zeros(self.requests, dtype=torch.int32).pin_memory()
             before = kernels.LAUNCHES
             graph = torch.cuda.CUDAGraph()
             with guarded_capture(graph):
+                self.device_buf.copy_(self.host, non_blocking=True)
                 self.logits, self.tokens = self._forward(ctx)
+                self.host_tokens.copy_(self.tokens, non_blocking=True)
             self.launches = kernels.LAUNCHES - before
             self.graph = graph
-            return tokens
+            return result
+        self.stage(entries, temperatures, uniforms, copy=False)
         self.graph.replay()
-        return self.tokens
+        torch.cuda.current_stream().synchronize()      # the tokens are in pinned memory, the mirror has been read
+        return self.host_tokens.tolist()
 
 
 class GraphCache:

@@ -112,17 +112,22 @@ class ModelRunner:
         decode_only = self.graphs.enabled and all(len(e.tokens) == 1 and e.want == [0] for e in entries)
         if decode_only:
             graph = self.graphs.get(entries)
-            tokens = graph.run(entries, temperatures, uniforms)
+            sampled = graph.run(entries, temperatures, uniforms)
             self.stats["h2d_bytes"] += graph.stager.last_bytes
-        else:
-            floats = {"temperature": temperatures, "uniform": uniforms} if temperatures else None
-            ctx = self.stager.stage(entries, self.page_tokens, floats=floats)
-            self.stats["h2d_bytes"] += self.stager.last_bytes
-            logits = self.forward(ctx)
-            tokens = None
-            if logits is not None:
-                tokens = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-                kernels.sample(logits, tokens, self.runtime.status, ctx.floats["temperature"], ctx.floats["uniform"])
+            self.stats["d2h_bytes"] += len(sampled) * 4
+            for e in entries:
+                e.seq.length += 1
+                self.manager.trim(e.seq)
+            self.steps_run += 1
+            return sampled
+        floats = {"temperature": temperatures, "uniform": uniforms} if temperatures else None
+        ctx = self.stager.stage(entries, self.page_tokens, floats=floats)
+        self.stats["h2d_bytes"] += self.stager.last_bytes
+        logits = self.forward(ctx)
+        tokens = None
+        if logits is not None:
+            tokens = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+            kernels.sample(logits, tokens, self.runtime.status, ctx.floats["temperature"], ctx.floats["uniform"])
         for e in entries:
             e.seq.length += len(e.tokens)
             self.manager.trim(e.seq)
