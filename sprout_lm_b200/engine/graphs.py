@@ -187,8 +187,12 @@ class GraphCache:
         self.enabled = True
 
     def get(self, entries) -> DecodeGraph:
-        pages = max(max((len(t) for t in e.seq.tables), default=1) for e in entries)
-        key = (len(entries), _round_up(max(pages, 1), self.page_multiple))
+        pages = 1
+        for e in entries:
+            for table in e.seq.tables:
+                if len(table) > pages:
+                    pages = len(table)
+        key = (len(entries), _round_up(pages, self.page_multiple))
         graph = self.graphs.get(key)
         if graph is None:
             graph = self.graphs[key] = DecodeGraph(self.runner, *key)

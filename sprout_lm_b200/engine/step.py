@@ -33,6 +33,7 @@ class ModelRunner:
                                     prefix_caching=prefix_caching)
         self.storage = CacheStorage(model, self.manager, slot_group)
         self.stager = BatchStager(self.runtime.device, len(groups))
+        self._groups_in_use = [g for g in range(len(groups)) if self.storage.slot_group.count(g)]   # groups that hold some layer's cache
         self.page_tokens = page_tokens
         self.max_requests = max_requests
         self.vocab_size = model.spec.vocab_size
@@ -72,24 +73,29 @@ class ModelRunner:
         if not entries:
             raise StepError("a step needs at least one entry")
         seen = set()
+        vocab = self.vocab_size
+        groups = self._groups_in_use
         for e in entries:
             if id(e.seq) in seen:
                 raise StepError("a request appears twice in one step")
             seen.add(id(e.seq))
             if e.seq.released:
                 raise StepError("a request's cache was released")
-            if not e.tokens:
+            tokens = e.tokens
+            if not tokens:
                 raise StepError("an entry needs at least one token")
-            if any((not isinstance(t, int)) or t < 0 or t >= self.vocab_size for t in e.tokens):
-                raise StepError("Invalid token ID.")
-            end = e.seq.length + len(e.tokens)
+            for t in tokens:
+                if type(t) is not int or t < 0 or t >= vocab:
+                    raise StepError("Invalid token ID.")
+            end = e.seq.length + len(tokens)
             if end > self.max_positions:
                 raise StepError("Invalid position: the request exceeds the model's context limit.")
-            for g in range(len(self.manager.groups)):
-                if self.storage.slot_group.count(g) and e.seq.capacity(g) < end:
+            for g in groups:
+                if e.seq.capacity(g) < end:
                     raise StepError("Reserve physical pages before running a token.")
-            if any((not isinstance(w, int)) or w < 0 or w >= len(e.tokens) for w in e.want):
-                raise StepError("a wanted place lies outside the entry's tokens")
+            for w in e.want:
+                if type(w) is not int or w < 0 or w >= len(tokens):
+                    raise StepError("a wanted place lies outside the entry's tokens")
 
     def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
         """Run one batch.  Returns float32 logits [wanted places, vocab] in the order of the
