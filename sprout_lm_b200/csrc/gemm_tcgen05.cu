@@ -61,7 +61,8 @@ struct Layout {
   static constexpr int B_PADDED = (B_BYTES + 1023) / 1024 * 1024;
   static constexpr int STAGE_BYTES = A_BYTES + B_PADDED;
   static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) > 12 ? 12 : (SMEM_BUDGET / STAGE_BYTES);
-  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;     // two accumulators
+  // two accumulators; allocations are powers of two from 32 columns
+  static constexpr int TMEM_COLS = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
@@ -297,10 +298,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
 #pragma unroll
           for (int q4 = 0; q4 < 4; q4++) {
             float4 v;
-            v.x = __uint_as_float(raw[4 * q4]) + ((p.bias && n_base + 4 * q4 < p.N) ? p.bias[n_base + 4 * q4] : 0.f);
-            v.y = __uint_as_float(raw[4 * q4 + 1]) + ((p.bias && n_base + 4 * q4 + 1 < p.N) ? p.bias[n_base + 4 * q4 + 1] : 0.f);
-            v.z = __uint_as_float(raw[4 * q4 + 2]) + ((p.bias && n_base + 4 * q4 + 2 < p.N) ? p.bias[n_base + 4 * q4 + 2] : 0.f);
-            v.w = __uint_as_float(raw[4 * q4 + 3]) + ((p.bias && n_base + 4 * q4 + 3 < p.N) ? p.bias[n_base + 4 * q4 + 3] : 0.f);
+            const bool biased = p.bias && first_split;     // the K splits of a tile all add into the output: one brings the bias
+            v.x = __uint_as_float(raw[4 * q4]) + ((biased && n_base + 4 * q4 < p.N) ? p.bias[n_base + 4 * q4] : 0.f);
+            v.y = __uint_as_float(raw[4 * q4 + 1]) + ((biased && n_base + 4 * q4 + 1 < p.N) ? p.bias[n_base + 4 * q4 + 1] : 0.f);
+            v.z = __uint_as_float(raw[4 * q4 + 2]) + ((biased && n_base + 4 * q4 + 2 < p.N) ? p.bias[n_base + 4 * q4 + 2] : 0.f);
+            v.w = __uint_as_float(raw[4 * q4 + 3]) + ((biased && n_base + 4 * q4 + 3 < p.N) ? p.bias[n_base + 4 * q4 + 3] : 0.f);
             const int chunk = half * 4 + q4;
             *(float4*)(tile + tile_row * 128 + ((chunk ^ (tile_row & 7)) << 4)) = v;
           }
@@ -503,7 +505,8 @@ SPROUT_API int sprout_gemm_bf16(const void* A, const void* W, const float* bias,
   SPROUT_REQUIRE(!residual || out_dtype == SPROUT_F32, "gemm_bf16: a residual needs a float32 output");
   const bool swap = orientation == 2 || (orientation == 0 && M <= 256);    // 1: tokens on M in CTA pairs, 3: single CTAs
   if (split_k < 1) split_k = 1;
-  SPROUT_REQUIRE(split_k == 1 || (swap && residual && M <= 256), "gemm_bf16: split_k needs weights-on-M with a residual output and at most 256 tokens");
+  SPROUT_REQUIRE(split_k == 1 || (swap && residual && M <= 256), "gemm_bf16: split_k needs weights-on-M with a residual output and at most 256 tokens "
+                 "(with tokens on M the kernel splits K by itself where that pays)");
 
   Params p;
   p.bias = bias; p.out = out; p.out_is_f32 = out_dtype == SPROUT_F32;
@@ -529,19 +532,44 @@ SPROUT_API int sprout_gemm_bf16(const void* A, const void* W, const float* bias,
       default: return launch<256, true>(map_w, map_a, map_a, p, (int)work, stream);
     }
   }
-  // tokens on M: 128 x 256 tiles where they tile N exactly (a quarter less operand traffic from
-  // L2 than 128 x 128), else 128 x 128
-  const int bn = (N % 256 == 0) ? 256 : 128;
-  // CTA pairs pay where the tile is 256 wide (measured: gate/up 2048 x 9728 x 896 41 -> 39 us,
-  // 8192 tokens 145 -> 134 us); on 128-wide tiles single CTAs are as fast and launch more cheaply
-  const bool pair = orientation == 4 || (orientation != 3 && bn == 256);
+  // Tokens on M.  The residual epilogue goes through the TMA unit where the output's rows allow a
+  // tensor map; its additions are atomic in L2, so a tile's K range may then be split among CTAs.
+  const bool reduce = p.epilogue == EPI_RESIDUAL && ldo % 4 == 0 && ((uintptr_t)out & 15) == 0;
+  // Tile width and K split: a k-block of a 128 x bn tile moves (128 + bn) x 128 bytes into shared
+  // memory and out again, which is what its time follows; wider tiles move less per product but
+  // make fewer CTAs.  The pick minimises rounds x k-blocks x (128 + bn) over the widths that
+  // divide N (128 always) and, for the reducing epilogue, splits of at least 4 k-blocks.
+  // N a multiple of 256: 256 x 256 tiles of CTA pairs (measured: gate/up 2048 x 9728 x 896
+  // 41 -> 39 us, 8192 tokens 145 -> 134 us; on narrower tiles single CTAs are as fast).
+  int bn = 128;
+  split_k = 1;
+  const bool pair = orientation == 4 || (orientation != 3 && N % 256 == 0);
+  if (pair) {
+    bn = N % 256 == 0 ? 256 : 128;
+  } else if (orientation != 3) {
+    const int widths[4] = {128, 192, 224, 256};
+    const long long row_tiles = (M + BLOCK_M - 1) / BLOCK_M;
+    long long best = -1;
+    for (int width : widths) {
+      if (width != 128 && N % width != 0) continue;
+      for (int split = 1; split <= (reduce ? 4 : 1); split++) {
+        const int kb = (total_kb + split - 1) / split;
+        if (split > 1 && kb < 4) break;
+        const long long items = row_tiles * ((N + width - 1) / width) * split;
+        const long long rounds = (items + sm_count() - 1) / sm_count();
+        const long long cost = rounds * (kb + 4 * (split > 1)) * (128 + width);   // a split costs another epilogue and its reduction
+        if (best < 0 || cost < best) { best = cost; bn = width; split_k = split; }
+      }
+    }
+  }
+  p.k_blocks_per_split = (total_kb + split_k - 1) / split_k;
+  split_k = (total_kb + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
   if (tensor_map(A, M, K, lda, BLOCK_M, &map_a)) return 1;
   if (tensor_map(W, N, K, K, pair ? bn / 2 : bn, &map_w)) return 1;
-  const long long work = (long long)((N + bn - 1) / bn) * ((M + (pair ? 2 : 1) * BLOCK_M - 1) / ((pair ? 2 : 1) * BLOCK_M));
+  const long long work = (long long)((N + bn - 1) / bn) * ((M + (pair ? 2 : 1) * BLOCK_M - 1) / ((pair ? 2 : 1) * BLOCK_M)) * split_k;
   SPROUT_REQUIRE(work <= 0x7fffffffLL, "gemm_bf16: too many tiles");
-  // the residual epilogue goes through the TMA unit where the output's rows allow a tensor map
   CUtensorMap map_out = map_a;
-  if (p.epilogue == EPI_RESIDUAL && ldo % 4 == 0 && ((uintptr_t)out & 15) == 0) {
+  if (reduce) {
     if (tensor_map(out, M, N, ldo, BLOCK_M, &map_out, 4)) return 1;
     p.epilogue = EPI_RESIDUAL_TMA;
   }
@@ -549,6 +577,10 @@ SPROUT_API int sprout_gemm_bf16(const void* A, const void* W, const float* bias,
     if (bn == 256) return launch_pair<256>(map_a, map_w, map_out, p, (int)work, stream);
     return launch_pair<128>(map_a, map_w, map_out, p, (int)work, stream);
   }
-  if (bn == 256) return launch<256, false>(map_a, map_w, map_out, p, (int)work, stream);
-  return launch<128, false>(map_a, map_w, map_out, p, (int)work, stream);
+  switch (bn) {
+    case 256: return launch<256, false>(map_a, map_w, map_out, p, (int)work, stream);
+    case 224: return launch<224, false>(map_a, map_w, map_out, p, (int)work, stream);
+    case 192: return launch<192, false>(map_a, map_w, map_out, p, (int)work, stream);
+    default: return launch<128, false>(map_a, map_w, map_out, p, (int)work, stream);
+  }
 }
