@@ -292,24 +292,27 @@ def timed_e2e(model, batch: int, prompt_len: int, steps: int, warmup: int, rng):
 
 
 def timed_prefill(runner, tokens: int, rng, repeats: int = 5):
+    """A prompt of ``tokens`` tokens in one step through ``ModelRunner.step`` (what the scheduler
+    calls): token ids from the host, the last position's logits on the device.  The same sizes
+    come every time, so from the third step on the runner replays its capture of the step."""
+    import numpy as np
     import torch
     from sprout_lm_b200.engine.batch import StepEntry
     times = []
-    for _ in range(repeats + 2):
+    for _ in range(repeats + 3):
         seq = runner.new_sequence()
         assert runner.reserve(seq, tokens)
-        entry = StepEntry(seq, [int(t) for t in rng.integers(0, runner.vocab_size, tokens)], [tokens - 1])
+        entry = StepEntry(seq, rng.integers(0, runner.vocab_size, tokens).astype(np.int32), [tokens - 1])
         torch.cuda.synchronize()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         begin.record()
-        ctx = runner.stager.stage([entry], runner.page_tokens)
-        logits = runner.forward(ctx)
+        logits = runner.step([entry])
         end.record()
         torch.cuda.synchronize()
         assert bool(torch.isfinite(logits).all())
         times.append(begin.elapsed_time(end))
         runner.release(seq)
-    return statistics.median(times[2:])
+    return statistics.median(times[3:])
 
 
 def timed_attention(tokens: int, repeats: int = 20) -> dict:

@@ -17,8 +17,9 @@ import torch
 
 @dataclass
 class StepEntry:
-    """One request's share of a step: ``tokens`` continue the request's cache (``seq``) from
-    position ``seq.length``; ``want`` are indices into ``tokens`` whose logits are asked for."""
+    """One request's share of a step: ``tokens`` (a list of ints, or a 1-D integer numpy array for
+    a long portion) continue the request's cache (``seq``) from position ``seq.length``; ``want``
+    are indices into ``tokens`` whose logits are asked for."""
     seq: object
     tokens: list
     want: list = field(default_factory=list)
@@ -69,6 +70,11 @@ class BatchStager:
         self._host = [torch.empty(ints, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._events = [None, None]
         self._device_buf = torch.empty(ints, dtype=torch.int32, device=self.device)
+
+    @property
+    def device_buffer(self) -> torch.Tensor:
+        """The device image of the step's arrays (replaced when a larger one is needed)."""
+        return self._device_buf
 
     def layout(self, T: int, R: int, S: int, max_pages: int, floats=None):
         sizes = [("token_ids", T), ("positions", T), ("seq_of_token", T), ("q_start", R + 1),

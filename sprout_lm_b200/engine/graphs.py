@@ -199,6 +199,77 @@ class GraphCache:
         return graph
 
 
+class StepGraphs:
+    """Steps with prompt portions, replayed when their shape comes again.
+
+    A prefill step of a small model is two hundred launches that the host enqueues more slowly
+    than the device runs them.  A step whose sizes (tokens, requests, wanted rows, block-table
+    width rounded up to ``page_multiple``) have been seen before is captured after it has run,
+    and later steps of the same sizes replay the capture: the batch's arrays live at fixed
+    offsets of the stager's device buffer, so only their contents change.  Chunked prefill at a
+    fixed chunk size makes such steps common.  A few captures are kept (each holds its own
+    activations); steps that ask for many logits rows are not captured."""
+
+    def __init__(self, runner, limit: int = 4, min_tokens: int = 128, max_rows: int = 64, page_multiple: int = 64):
+        self.runner = runner
+        self.limit, self.min_tokens, self.max_rows, self.page_multiple = limit, min_tokens, max_rows, page_multiple
+        self.seen: dict = {}              # key -> times run eagerly
+        self.captured: dict = {}          # key -> (graph, logits, tokens, device buffer), in order of last use
+        self.enabled = True
+        self.replays = 0
+
+    def plan(self, entries, sample: bool):
+        """(key, table width) for a step that may be captured, else (None, None)."""
+        if not self.enabled:
+            return None, None
+        tokens = sum(len(e.tokens) for e in entries)
+        rows = sum(len(e.want) for e in entries)
+        if tokens < self.min_tokens or rows > self.max_rows or all(len(e.tokens) == 1 for e in entries):
+            return None, None
+        pages = 1
+        for e in entries:
+            for table in e.seq.tables:
+                pages = max(pages, len(table))
+        width = _round_up(pages, self.page_multiple)
+        return (tokens, len(entries), rows, width, sample), width
+
+    def run(self, key, ctx, sample: bool):
+        """Run the staged step ``ctx``; (logits or None, sampled tokens or None), both on the
+        device and valid until the next step of the same sizes."""
+        runner = self.runner
+        buffer = runner.stager.device_buffer
+        held = self.captured.get(key)
+        if held is not None and held[3] is buffer:
+            self.captured[key] = self.captured.pop(key)          # most recently used last
+            held[0].replay()
+            self.replays += 1
+            return held[1], held[2]
+        logits, tokens = self._forward(ctx, sample)
+        if len(self.seen) > 4096:
+            self.seen.clear()
+        self.seen[key] = self.seen.get(key, 0) + 1
+        if self.seen[key] >= 2:
+            # the step has run; record the same launches for the next time these sizes come
+            if held is not None:
+                del self.captured[key]
+            while len(self.captured) >= self.limit:
+                self.captured.pop(next(iter(self.captured)))
+            graph = torch.cuda.CUDAGraph()
+            with guarded_capture(graph):
+                recorded = self._forward(ctx, sample)
+            self.captured[key] = (graph, recorded[0], recorded[1], buffer)
+        return logits, tokens
+
+    def _forward(self, ctx, sample: bool):
+        runner = self.runner
+        logits = runner.forward(ctx)
+        tokens = None
+        if sample and logits is not None:
+            tokens = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+            kernels.sample(logits, tokens, runner.runtime.status, ctx.floats["temperature"], ctx.floats["uniform"])
+        return logits, tokens
+
+
 class DecodeLoop:
     """``steps`` decode steps on the device without the host in between: after each step a
     kernel makes the sampled tokens the next inputs.  Pages for all the steps must have been

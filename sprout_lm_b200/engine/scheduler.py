@@ -20,6 +20,8 @@ from __future__ import annotations
 import hashlib
 from dataclasses import asdict, dataclass, field
 
+import numpy as np
+
 from .batch import StepEntry
 
 
@@ -57,6 +59,7 @@ class Request:
     seq: object = None
     prefix_hits: int = 0
     finish_reason: str | None = None
+    prompt_array: object = None        # the prompt as an int32 numpy array
 
 
 class StepReport(dict):
@@ -139,7 +142,8 @@ class Engine:
         if slots > self.options.num_blocks * self.options.block_size:
             raise ValueError("Request cannot fit alone in the KV pool. Increase numBlocks or shorten it.")
         request = Request(id=id, order=self._next_order, prompt=prompt, max_new_tokens=max_new_tokens,
-                          temperature=float(temperature), seed=int(seed), ignore_eos=bool(ignore_eos))
+                          temperature=float(temperature), seed=int(seed), ignore_eos=bool(ignore_eos),
+                          prompt_array=np.asarray(prompt, dtype=np.int32))
         self._next_order += 1
         self._requests[id] = request
         self._waiting.append(id)
@@ -222,7 +226,8 @@ class Engine:
                 if start >= len(prompt):
                     tokens = output[start - len(prompt):end - len(prompt)]
                 elif end <= len(prompt):
-                    tokens = prompt[start:end]
+                    # a long portion travels as a view of the prompt's array (no per-token work on the host)
+                    tokens = request.prompt_array[start:end] if computed >= 64 else prompt[start:end]
                 else:
                     tokens = prompt[start:] + output[:end - len(prompt)]
                 planned.append((request, phase, start, tokens, end == total))

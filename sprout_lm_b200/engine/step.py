@@ -8,6 +8,7 @@ requests' lengths until the launches have been issued without error.
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from .. import kernels
@@ -42,8 +43,9 @@ class ModelRunner:
         self.steps_run = 0
         # bytes copied to and from the device by steps (the batch's arrays up, token ids or logits down)
         self.stats = {"h2d_bytes": 0, "d2h_bytes": 0}
-        from .graphs import GraphCache
+        from .graphs import GraphCache, StepGraphs
         self.graphs = GraphCache(self)
+        self.step_graphs = StepGraphs(self)
 
     # ------------------------------------------------------------------ requests' caches
     def new_sequence(self, tokens=None):
@@ -82,11 +84,15 @@ class ModelRunner:
             if e.seq.released:
                 raise StepError("a request's cache was released")
             tokens = e.tokens
-            if not tokens:
+            if len(tokens) == 0:
                 raise StepError("an entry needs at least one token")
-            for t in tokens:
-                if type(t) is not int or t < 0 or t >= vocab:
+            if isinstance(tokens, np.ndarray):                   # a long portion, checked at once
+                if tokens.ndim != 1 or tokens.dtype.kind != "i" or int(tokens.min()) < 0 or int(tokens.max()) >= vocab:
                     raise StepError("Invalid token ID.")
+            else:
+                for t in tokens:
+                    if type(t) is not int or t < 0 or t >= vocab:
+                        raise StepError("Invalid token ID.")
             end = e.seq.length + len(tokens)
             if end > self.max_positions:
                 raise StepError("Invalid position: the request exceeds the model's context limit.")
@@ -102,8 +108,14 @@ class ModelRunner:
         entries and of their ``want`` lists, or None when nothing is wanted.  The requests'
         lengths are advanced."""
         self.validate(entries)
-        ctx = self.stager.stage(entries, self.page_tokens)
-        logits = self.forward(ctx)
+        key, width = self.step_graphs.plan(entries, sample=False)
+        ctx = self.stager.stage(entries, self.page_tokens, fixed_pages=width)
+        if key is None:
+            logits = self.forward(ctx)
+        else:
+            logits, _ = self.step_graphs.run(key, ctx, sample=False)
+            if logits is not None:
+                logits = logits.clone()       # a replay of the same sizes writes the same memory again
         for e in entries:
             e.seq.length += len(e.tokens)
             self.manager.trim(e.seq)
@@ -127,13 +139,17 @@ class ModelRunner:
             self.steps_run += 1
             return sampled
         floats = {"temperature": temperatures, "uniform": uniforms} if temperatures else None
-        ctx = self.stager.stage(entries, self.page_tokens, floats=floats)
+        key, width = self.step_graphs.plan(entries, sample=bool(temperatures))
+        ctx = self.stager.stage(entries, self.page_tokens, fixed_pages=width, floats=floats)
         self.stats["h2d_bytes"] += self.stager.last_bytes
-        logits = self.forward(ctx)
-        tokens = None
-        if logits is not None:
-            tokens = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-            kernels.sample(logits, tokens, self.runtime.status, ctx.floats["temperature"], ctx.floats["uniform"])
+        if key is not None:
+            _, tokens = self.step_graphs.run(key, ctx, sample=bool(temperatures))
+        else:
+            logits = self.forward(ctx)
+            tokens = None
+            if logits is not None:
+                tokens = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+                kernels.sample(logits, tokens, self.runtime.status, ctx.floats["temperature"], ctx.floats["uniform"])
         for e in entries:
             e.seq.length += len(e.tokens)
             self.manager.trim(e.seq)

@@ -163,3 +163,50 @@ def test_command_line_demo_and_generate(model_dirs):
     final = json.loads(done.stdout.strip().splitlines()[-1])
     want = plain.greedy(*plain.read_model_folder(model_dirs["A"]), [1, 2, 3, 4, 5], 4)
     assert final["report"]["results"][0]["output"] == want
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_repeated_step_shapes_replay(tmp_path, dtype):
+    """Steps with prompt portions whose sizes come again (tokens, requests, wanted rows) are
+    replayed from a capture.  Only the sizes are fixed in it: other requests, other splits of the
+    tokens between the requests and other pages give the logits of a runner that never captures."""
+    import numpy as np
+    import helpers
+    from sprout_lm_b200 import load_model
+    from sprout_lm_b200.engine.batch import StepEntry
+    from sprout_lm_b200.engine.step import ModelRunner
+    folder = helpers.make_model_dir(tmp_path, "A", max_position_embeddings=1024)
+    model = load_model(folder, dtype={"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype])
+    vocab = helpers.TINY["A"][0]["vocab_size"]
+    rng = np.random.default_rng(12)
+    rounds = [(200, 56), (100, 156), (31, 225), (128, 128), (255, 1)]       # 256 tokens of two requests each time
+
+    def run(capturing: bool):
+        runner = ModelRunner(model, num_pages=200, page_tokens=16, max_requests=8, prefix_caching=False)
+        runner.step_graphs.enabled = capturing
+        out = []
+        local = np.random.default_rng(5)
+        for a, b in rounds:
+            seqs = [runner.new_sequence(), runner.new_sequence()]
+            history = [helpers.random_tokens(local, 40, vocab), helpers.random_tokens(local, 7, vocab)]
+            for seq, tokens in zip(seqs, history):                          # some cache before the step of interest
+                assert runner.reserve(seq, len(tokens))
+                runner.step([StepEntry(seq, tokens, [])])
+            entries = []
+            for seq, n in zip(seqs, (a, b)):
+                assert runner.reserve(seq, seq.length + n)
+                entries.append(StepEntry(seq, helpers.random_tokens(local, n, vocab), [0, n - 1]))
+            out.append(runner.step(entries).cpu().numpy())
+            if len(out) == 3:
+                runner.release(seqs[0])                                     # later rounds get other pages
+            else:
+                for seq in seqs:
+                    runner.release(seq)
+        runner.check_status()
+        return out, runner.step_graphs.replays
+
+    plain, none = run(False)
+    replayed, count = run(True)
+    assert none == 0 and count == len(rounds) - 2            # the third round and later replay the second's capture
+    for want, got in zip(plain, replayed):
+        assert np.abs(want - got).max() <= (1e-5 if dtype == "float32" else 2 * helpers.TOL["bfloat16"])
