@@ -318,7 +318,11 @@ attention_decode_mma_kernel(const DecodeParams p) {
   float* wl = wm + 64;                                // [4][16]
 
   pdl_launch_dependents();
-  pdl_wait();
+  // What this step's earlier kernels wrote is the query (or the float32 sums) and the newest
+  // position's key and value.  The block table and the lengths were copied before the step's first
+  // kernel, and the keys and values of earlier positions were written in earlier steps (a step
+  // ends with a copy to the host or a graph's end, which nothing overtakes): the first pass's
+  // loads go out before the wait for the earlier kernels, the rest is read after it.
   const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = p.heads / p.kv_heads;
@@ -328,14 +332,6 @@ attention_decode_mma_kernel(const DecodeParams p) {
   const int first_page = table[min((begin + tid) / p.page_tokens, p.table_stride - 1)];
   const int width = (p.heads + 2 * p.kv_heads) * HD;
   const int pos = len - 1;                             // FUSED: the new token's position
-  if (!FUSED) {
-    for (int idx = tid; idx < 16 * CHUNKS; idx += DEC_THREADS) {
-      const int row = idx / CHUNKS, c = idx % CHUNKS;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (row < group) v = *(const uint4*)(p.q + (size_t)r * p.q_stride + (size_t)(g * group + row) * HD + c * 8);
-      *(uint4*)(sQ + row * STRIDE + c * 8) = v;
-    }
-  }
   const float scale = 1.0f / sqrtf((float)HD);
 
   const int gr = lane >> 2, qc = lane & 3;
@@ -369,8 +365,16 @@ attention_decode_mma_kernel(const DecodeParams p) {
       else if (ro == -1) { *(uint4*)dk = make_uint4(0, 0, 0, 0); *(uint4*)dv = make_uint4(0, 0, 0, 0); }
     }
     cp_async_commit();
+    if (first) pdl_wait();                             // the first pass's keys and values are on their way
+    if (!FUSED && first) {
+      for (int idx = tid; idx < 16 * CHUNKS; idx += DEC_THREADS) {
+        const int row = idx / CHUNKS, c = idx % CHUNKS;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < group) v = *(const uint4*)(p.q + (size_t)r * p.q_stride + (size_t)(g * group + row) * HD + c * 8);
+        *(uint4*)(sQ + row * STRIDE + c * 8) = v;
+      }
+    }
     if (FUSED && first) {
-      // while the first pass's keys and values are on their way:
       // q of the group's heads: sums + bias, rotated by the position, to shared memory as bfloat16
       const bool rotate = p.cos_table != nullptr;
       if (pos < 0 || (rotate && pos >= p.max_positions)) { if (tid == 0) atomicOr(p.status, SPROUT_STATUS_BAD_POSITION); }
@@ -396,6 +400,16 @@ attention_decode_mma_kernel(const DecodeParams p) {
       if (!CLUSTER && begin >= len) { cp_async_wait<0>(); return; }   // the merge kernel knows which splits exist
     }
     cp_async_wait<0>();
+    if (!FUSED && first && pos >= base && pos < base + DEC_THREADS && pos < begin + p.split_keys) {
+      // the newest position's key and value may have been written after the early loads read them
+      __syncthreads();                                 // the early loads of that row have landed
+      const long long ro = rows[pos - base];
+      if (ro >= 0)
+        for (int c = tid; c < CHUNKS; c += DEC_THREADS) {
+          *(uint4*)(sK + (pos - base) * STRIDE + c * 8) = *(const uint4*)(p.k_cache + ro + c * 8);
+          *(uint4*)(sV + (pos - base) * STRIDE + c * 8) = *(const uint4*)(p.v_cache + ro + c * 8);
+        }
+    }
     if (FUSED && pos >= base && pos < base + DEC_THREADS && pos < begin + p.split_keys) {
       // This split holds the new token: its key (rotated) and value come from the sums, go to the
       // cache and, over whatever the first pass's early load brought, into this pass's tile.
