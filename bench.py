@@ -42,6 +42,11 @@ sys.path.insert(0, str(ROOT))
 CONFIG_05B = dict(hidden_size=896, intermediate_size=4864, num_hidden_layers=24, num_attention_heads=14,
                   num_key_value_heads=2, vocab_size=151936, max_position_embeddings=4096, rms_norm_eps=1e-6,
                   rope_theta=1000000.0, tie_word_embeddings=True, eos_token_id=151645)
+# the 7B shape of the reference's second workload (continuous batching over mixed prompt lengths)
+CONFIG_7B = dict(hidden_size=3584, intermediate_size=18944, num_hidden_layers=28, num_attention_heads=28,
+                 num_key_value_heads=4, vocab_size=152064, max_position_embeddings=4096, rms_norm_eps=1e-6,
+                 rope_theta=1000000.0, tie_word_embeddings=False, eos_token_id=151645)
+SHAPES = {"0.5b": CONFIG_05B, "7b": CONFIG_7B}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 REFERENCE_UNAVAILABLE = ("the reference is a TypeScript program for Node >= 24 with a Node-API CUDA module; it has no "
                          "Python package to install (pip finds no setup.py or pyproject.toml) and node is not in this image")
@@ -108,11 +113,12 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.samples)}
 
 
-def model_folder(layers: int) -> Path:
+def model_folder(layers: int, shape: str = "0.5b") -> Path:
     """The random-weights model folder of the benchmark shape (written once per temporary folder)."""
     from sprout_lm_b200 import parse_config, write_random_model
-    sizes = dict(CONFIG_05B, num_hidden_layers=layers)
-    folder = Path(tempfile.gettempdir()) / f"sprout_lm_b200_bench_{os.getuid()}_L{layers}"
+    sizes = dict(SHAPES[shape], num_hidden_layers=layers)
+    tag = "" if shape == "0.5b" else "_" + shape
+    folder = Path(tempfile.gettempdir()) / f"sprout_lm_b200_bench_{os.getuid()}{tag}_L{layers}"
     config = parse_config({"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu", **sizes})
     marker = folder / "complete"
     if not marker.exists():
@@ -315,6 +321,56 @@ def timed_prefill(runner, tokens: int, rng, repeats: int = 5):
     return statistics.median(times[3:])
 
 
+def timed_serving(shape: str, layers: int, requests: int, seed: int = 0) -> dict:
+    """Continuous batching through ``Engine.step``: ``requests`` requests with uniform-random prompt
+    lengths in [128, 2048] arrive at once, prompts are prefilled in portions beside the decoding
+    of the others, every request generates 128 tokens.  Host tokens in and out every step."""
+    import numpy as np
+    import torch
+    from sprout_lm_b200 import EngineOptions, load_model, make_engine
+    sizes = SHAPES[shape]
+    layers = layers or sizes["num_hidden_layers"]
+    model = load_model(model_folder(layers, shape), dtype="bfloat16", device="cuda:0")
+    rng = np.random.default_rng(seed)
+    lengths = [int(n) for n in rng.integers(128, 2049, requests)]
+    new_tokens = 128
+    pages = sum(-(-(n + new_tokens) // 16) for n in lengths) + 64
+    options = EngineOptions(block_size=16, num_blocks=pages, max_sequences=requests, max_batch_tokens=2048,
+                            prefill_chunk_size=1024, prefix_caching=False, record_trace=False)
+
+    engine = make_engine(model, options)                 # one engine for both rounds: the second finds the graphs captured
+
+    def run_once(tag):
+        for i, n in enumerate(lengths):
+            engine.add(f"{tag}{i}", [int(t) for t in rng.integers(0, model.spec.vocab_size, n)], new_tokens, ignore_eos=True)
+        times, kinds, preempted = [], {"prefill": 0, "mixed": 0, "decode": 0}, 0
+        torch.cuda.synchronize()
+        begin = time.perf_counter()
+        while engine.pending:
+            t0 = time.perf_counter()
+            report = engine.step()
+            times.append((time.perf_counter() - t0) * 1000)
+            phases = {w["phase"] for w in report["work"]}
+            kinds["decode" if phases == {"decode"} else "prefill" if "decode" not in phases else "mixed"] += 1
+            preempted += sum(1 for e in report["events"] if e["type"] == "preempted")
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - begin
+        engine.runner.check_status()
+        assert all(len(engine.result(f"{tag}{i}")["output"]) == new_tokens for i in range(requests))
+        return seconds, times, kinds, preempted, engine.runner.step_graphs.replays
+
+    run_once("warm")                                     # first use: kernel set-up, graph captures
+    seconds, times, kinds, preempted, replays = run_once("r")
+    times.sort()
+    pick = lambda q: round(times[min(len(times) - 1, int(q * len(times)))], 3)
+    return {"impl": "ours", "only": "serve", "shape": shape, "layers": layers, "layers_of_model": sizes["num_hidden_layers"],
+            "requests": requests, "prompt_tokens": sum(lengths), "new_tokens": requests * new_tokens,
+            "seconds": round(seconds, 4), "generated_tokens_per_s": round(requests * new_tokens / seconds, 1),
+            "all_tokens_per_s": round((sum(lengths) + requests * new_tokens) / seconds, 1),
+            "steps": len(times), "step_kinds": kinds, "step_ms": {"p50": pick(0.5), "p95": pick(0.95), "max": times[-1].__round__(3)},
+            "preempted": preempted, "prefill_steps_replayed": replays}
+
+
 def timed_attention(tokens: int, repeats: int = 20) -> dict:
     """The prefill attention kernels alone, at the model's head sizes, over a paged cache: one
     request of ``tokens`` tokens attending to itself (causal), both kernels."""
@@ -419,6 +475,8 @@ def run(args) -> dict:
         return timed_attention(args.tokens)
     if args.only == "gemm":
         return timed_gemms(args.tokens)
+    if args.only == "serve":
+        return timed_serving(args.shape, args.layers, args.requests)
     layers = args.layers or CONFIG_05B["num_hidden_layers"]
     folder = model_folder(layers)
     model = load_model(folder, dtype="bfloat16", device="cuda:0")
@@ -479,8 +537,10 @@ def main() -> int:
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
-    parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate", "attention", "gemm"], default="all",
+    parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate", "attention", "gemm", "serve"], default="all",
                         help="measure one part only (for profiling captures); the JSON line then holds that part")
+    parser.add_argument("--shape", choices=sorted(SHAPES), default="0.5b", help="with --only serve: the model's sizes")
+    parser.add_argument("--requests", type=int, default=64, help="with --only serve: requests of the workload")
     parser.add_argument("--tokens", type=int, default=2048, help="with --only attention or gemm: tokens of the one request")
     args = parser.parse_args()
     if args.impl == "reference":

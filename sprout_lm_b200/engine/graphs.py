@@ -21,15 +21,26 @@ from .batch import StepContext
 
 @contextlib.contextmanager
 def guarded_capture(graph: "torch.cuda.CUDAGraph"):
-    """Stream capture that the garbage collector cannot disturb: freeing an older graph while a
-    new one is being captured is a CUDA call that invalidates the capture, so garbage is
-    collected before and the collector rests meanwhile."""
-    gc.collect()
+    """Stream capture into ``graph`` on a side stream.
+
+    Freeing an older graph while a new one is being captured is a CUDA call that invalidates the
+    capture, so the garbage collector rests meanwhile (objects freed by reference count are the
+    caller's business).  The capture is begun and ended directly: ``torch.cuda.graph`` would
+    synchronise the device, collect garbage and empty the allocator's cache first, some 30 ms that
+    a serving loop which captures new step shapes as they come cannot afford."""
     was_enabled = gc.isenabled()
     gc.disable()
+    current = torch.cuda.current_stream()
+    side = torch.cuda.Stream()
+    side.wait_stream(current)
     try:
-        with torch.cuda.graph(graph, capture_error_mode="relaxed"):
-            yield
+        with torch.cuda.stream(side):
+            graph.capture_begin(capture_error_mode="relaxed")
+            try:
+                yield
+            finally:
+                graph.capture_end()
+        current.wait_stream(side)
     finally:
         if was_enabled:
             gc.enable()

@@ -216,10 +216,15 @@ class Engine:
             remaining = total - start - (1 if phase == "recompute" else 0)
             count = min(budget, 1 if phase == "decode" else self.options.prefill_chunk_size, remaining)
             computed = 0
-            for i in range(count):
-                if not self._reserve(request, start + i + 1, planned):
-                    break
-                computed += 1
+            if count > 1 and self.runner.reserve(request.seq, start + count):
+                computed = count           # the whole portion has its pages: nothing to decide
+            else:
+                # token by token (src/engine.ts:153-156): where the pool runs out, younger
+                # requests are preempted, or this one stops at the tokens it has pages for
+                for i in range(count):
+                    if not self._reserve(request, start + i + 1, planned):
+                        break
+                    computed += 1
             budget -= computed
             if computed and request.status == "running":
                 end = start + computed
