@@ -300,12 +300,12 @@ def timed_e2e(model, batch: int, prompt_len: int, steps: int, warmup: int, rng):
 def timed_prefill(runner, tokens: int, rng, repeats: int = 5):
     """A prompt of ``tokens`` tokens in one step through ``ModelRunner.step`` (what the scheduler
     calls): token ids from the host, the last position's logits on the device.  The same sizes
-    come every time, so from the third step on the runner replays its capture of the step."""
+    come every time, so from the fourth step on the runner replays its capture of the step."""
     import numpy as np
     import torch
     from sprout_lm_b200.engine.batch import StepEntry
     times = []
-    for _ in range(repeats + 3):
+    for _ in range(repeats + 4):
         seq = runner.new_sequence()
         assert runner.reserve(seq, tokens)
         entry = StepEntry(seq, rng.integers(0, runner.vocab_size, tokens).astype(np.int32), [tokens - 1])
@@ -318,7 +318,7 @@ def timed_prefill(runner, tokens: int, rng, repeats: int = 5):
         assert bool(torch.isfinite(logits).all())
         times.append(begin.elapsed_time(end))
         runner.release(seq)
-    return statistics.median(times[3:])
+    return statistics.median(times[4:])
 
 
 def timed_serving(shape: str, layers: int, requests: int, seed: int = 0) -> dict:

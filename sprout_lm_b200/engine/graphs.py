@@ -215,15 +215,19 @@ class StepGraphs:
 
     A prefill step of a small model is two hundred launches that the host enqueues more slowly
     than the device runs them.  A step whose sizes (tokens, requests, wanted rows, block-table
-    width rounded up to ``page_multiple``) have been seen before is captured after it has run,
-    and later steps of the same sizes replay the capture: the batch's arrays live at fixed
-    offsets of the stager's device buffer, so only their contents change.  Chunked prefill at a
-    fixed chunk size makes such steps common.  A few captures are kept (each holds its own
-    activations); steps that ask for many logits rows are not captured."""
+    width rounded up to ``page_multiple``) have come ``after`` times is captured after it has
+    run, and later steps of the same sizes replay the capture: the batch's arrays live at fixed
+    offsets of the stager's device buffer, so only their contents change.  Chunked prefill of
+    long prompts at a fixed chunk size makes such steps; the mixed steps of a busy server rarely
+    repeat their sizes, and a capture costs milliseconds and holds its own activations, so sizes
+    must have come three times first, a few captures are kept, and steps that ask for many
+    logits rows are not captured."""
 
-    def __init__(self, runner, limit: int = 4, min_tokens: int = 128, max_rows: int = 64, page_multiple: int = 64):
+    def __init__(self, runner, limit: int = 4, min_tokens: int = 128, max_rows: int = 64, page_multiple: int = 64,
+                 after: int = 3):
         self.runner = runner
         self.limit, self.min_tokens, self.max_rows, self.page_multiple = limit, min_tokens, max_rows, page_multiple
+        self.after = after
         self.seen: dict = {}              # key -> times run eagerly
         self.captured: dict = {}          # key -> (graph, logits, tokens, device buffer), in order of last use
         self.enabled = True
@@ -259,7 +263,7 @@ class StepGraphs:
         if len(self.seen) > 4096:
             self.seen.clear()
         self.seen[key] = self.seen.get(key, 0) + 1
-        if self.seen[key] >= 2:
+        if self.seen[key] >= self.after:
             # the step has run; record the same launches for the next time these sizes come
             if held is not None:
                 del self.captured[key]

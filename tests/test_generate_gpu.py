@@ -179,7 +179,7 @@ def test_repeated_step_shapes_replay(tmp_path, dtype):
     model = load_model(folder, dtype={"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype])
     vocab = helpers.TINY["A"][0]["vocab_size"]
     rng = np.random.default_rng(12)
-    rounds = [(200, 56), (100, 156), (31, 225), (128, 128), (255, 1)]       # 256 tokens of two requests each time
+    rounds = [(200, 56), (100, 156), (31, 225), (128, 128), (255, 1), (7, 249)]   # 256 tokens of two requests each time
 
     def run(capturing: bool):
         runner = ModelRunner(model, num_pages=200, page_tokens=16, max_requests=8, prefix_caching=False)
@@ -197,7 +197,7 @@ def test_repeated_step_shapes_replay(tmp_path, dtype):
                 assert runner.reserve(seq, seq.length + n)
                 entries.append(StepEntry(seq, helpers.random_tokens(local, n, vocab), [0, n - 1]))
             out.append(runner.step(entries).cpu().numpy())
-            if len(out) == 3:
+            if len(out) == 4:
                 runner.release(seqs[0])                                     # later rounds get other pages
             else:
                 for seq in seqs:
@@ -207,6 +207,6 @@ def test_repeated_step_shapes_replay(tmp_path, dtype):
 
     plain, none = run(False)
     replayed, count = run(True)
-    assert none == 0 and count == len(rounds) - 2            # the third round and later replay the second's capture
+    assert none == 0 and count == len(rounds) - 3            # the fourth round and later replay the third's capture
     for want, got in zip(plain, replayed):
         assert np.abs(want - got).max() <= (1e-5 if dtype == "float32" else 2 * helpers.TOL["bfloat16"])
