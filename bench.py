@@ -46,7 +46,11 @@ CONFIG_05B = dict(hidden_size=896, intermediate_size=4864, num_hidden_layers=24,
 CONFIG_7B = dict(hidden_size=3584, intermediate_size=18944, num_hidden_layers=28, num_attention_heads=28,
                  num_key_value_heads=4, vocab_size=152064, max_position_embeddings=4096, rms_norm_eps=1e-6,
                  rope_theta=1000000.0, tie_word_embeddings=False, eos_token_id=151645)
-SHAPES = {"0.5b": CONFIG_05B, "7b": CONFIG_7B}
+# the 14B shape of its third (a shared prefix, a pool too small for all requests)
+CONFIG_14B = dict(hidden_size=5120, intermediate_size=13824, num_hidden_layers=48, num_attention_heads=40,
+                  num_key_value_heads=8, vocab_size=152064, max_position_embeddings=8192, rms_norm_eps=1e-5,
+                  rope_theta=1000000.0, tie_word_embeddings=False, eos_token_id=151645)
+SHAPES = {"0.5b": CONFIG_05B, "7b": CONFIG_7B, "14b": CONFIG_14B}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 REFERENCE_UNAVAILABLE = ("the reference is a TypeScript program for Node >= 24 with a Node-API CUDA module; it has no "
                          "Python package to install (pip finds no setup.py or pyproject.toml) and node is not in this image")
@@ -321,10 +325,16 @@ def timed_prefill(runner, tokens: int, rng, repeats: int = 5):
     return statistics.median(times[4:])
 
 
-def timed_serving(shape: str, layers: int, requests: int, seed: int = 0) -> dict:
-    """Continuous batching through ``Engine.step``: ``requests`` requests with uniform-random prompt
-    lengths in [128, 2048] arrive at once, prompts are prefilled in portions beside the decoding
-    of the others, every request generates 128 tokens.  Host tokens in and out every step."""
+def timed_serving(shape: str, layers: int, requests: int, workload: str = "mixed", seed: int = 0) -> dict:
+    """Continuous batching through ``Engine.step``, host tokens in and out every step.
+
+    ``mixed``: ``requests`` requests with uniform-random prompt lengths in [128, 2048] arrive at
+    once, prompts are prefilled in portions beside the decoding of the others, every request
+    generates 128 tokens.  ``shared-prefix``: prompts of 4,096 tokens whose first 1,024 are the
+    same, 256 generated tokens each, prefix reuse on, and a pool that holds 60 % of what all
+    requests need at their longest, so that requests wait or are preempted and recomputed
+    (requests are admitted when the pool can take them; SPROUT_REFERENCE_ADMISSION=1 admits
+    as the reference does, whenever a sequence slot is free)."""
     import numpy as np
     import torch
     from sprout_lm_b200 import EngineOptions, load_model, make_engine
@@ -332,17 +342,28 @@ def timed_serving(shape: str, layers: int, requests: int, seed: int = 0) -> dict
     layers = layers or sizes["num_hidden_layers"]
     model = load_model(model_folder(layers, shape), dtype="bfloat16", device="cuda:0")
     rng = np.random.default_rng(seed)
-    lengths = [int(n) for n in rng.integers(128, 2049, requests)]
-    new_tokens = 128
-    pages = sum(-(-(n + new_tokens) // 16) for n in lengths) + 64
+    shared = workload == "shared-prefix"
+    if shared:
+        lengths, new_tokens = [4096] * requests, 256
+        if 4096 + new_tokens - 1 > sizes["max_position_embeddings"]:
+            raise SystemExit(f"bench.py: the shared-prefix workload needs a context of 4,351 positions; shape {shape} has "
+                             f"{sizes['max_position_embeddings']}")
+        pages = int(0.6 * requests * -(-(4096 + new_tokens) // 16))
+    else:
+        lengths, new_tokens = [int(n) for n in rng.integers(128, 2049, requests)], 128
+        pages = sum(-(-(n + new_tokens) // 16) for n in lengths) + 64
     options = EngineOptions(block_size=16, num_blocks=pages, max_sequences=requests, max_batch_tokens=2048,
-                            prefill_chunk_size=1024, prefix_caching=False, record_trace=False)
-
+                            prefill_chunk_size=1024, prefix_caching=shared, record_trace=False,
+                            admit_within_pool=shared and os.environ.get("SPROUT_REFERENCE_ADMISSION") != "1")
     engine = make_engine(model, options)                 # one engine for both rounds: the second finds the graphs captured
 
     def run_once(tag):
+        prefix = [int(t) for t in rng.integers(0, model.spec.vocab_size, 1024)]     # a new one each round: no hits across rounds
         for i, n in enumerate(lengths):
-            engine.add(f"{tag}{i}", [int(t) for t in rng.integers(0, model.spec.vocab_size, n)], new_tokens, ignore_eos=True)
+            tokens = [int(t) for t in rng.integers(0, model.spec.vocab_size, n)]
+            if shared:
+                tokens[:1024] = prefix
+            engine.add(f"{tag}{i}", tokens, new_tokens, ignore_eos=True)
         times, kinds, preempted = [], {"prefill": 0, "mixed": 0, "decode": 0}, 0
         torch.cuda.synchronize()
         begin = time.perf_counter()
@@ -356,15 +377,16 @@ def timed_serving(shape: str, layers: int, requests: int, seed: int = 0) -> dict
         torch.cuda.synchronize()
         seconds = time.perf_counter() - begin
         engine.runner.check_status()
-        assert all(len(engine.result(f"{tag}{i}")["output"]) == new_tokens for i in range(requests))
-        return seconds, times, kinds, preempted, engine.runner.step_graphs.replays
+        results = [engine.result(f"{tag}{i}") for i in range(requests)]
+        assert all(len(r["output"]) == new_tokens for r in results)
+        return seconds, times, kinds, preempted, engine.runner.step_graphs.replays, sum(r["prefixHits"] for r in results)
 
     run_once("warm")                                     # first use: kernel set-up, graph captures
-    seconds, times, kinds, preempted, replays = run_once("r")
+    seconds, times, kinds, preempted, replays, hits = run_once("r")
     times.sort()
     pick = lambda q: round(times[min(len(times) - 1, int(q * len(times)))], 3)
-    return {"impl": "ours", "only": "serve", "shape": shape, "layers": layers, "layers_of_model": sizes["num_hidden_layers"],
-            "requests": requests, "prompt_tokens": sum(lengths), "new_tokens": requests * new_tokens,
+    return {"impl": "ours", "only": "serve", "workload": workload, "shape": shape, "layers": layers,
+            "layers_of_model": sizes["num_hidden_layers"], "requests": requests, "pool_pages": pages, "prefix_hit_tokens": hits, "prompt_tokens": sum(lengths), "new_tokens": requests * new_tokens,
             "seconds": round(seconds, 4), "generated_tokens_per_s": round(requests * new_tokens / seconds, 1),
             "all_tokens_per_s": round((sum(lengths) + requests * new_tokens) / seconds, 1),
             "steps": len(times), "step_kinds": kinds, "step_ms": {"p50": pick(0.5), "p95": pick(0.95), "max": times[-1].__round__(3)},
@@ -476,7 +498,7 @@ def run(args) -> dict:
     if args.only == "gemm":
         return timed_gemms(args.tokens)
     if args.only == "serve":
-        return timed_serving(args.shape, args.layers, args.requests)
+        return timed_serving(args.shape, args.layers, args.requests, args.workload)
     layers = args.layers or CONFIG_05B["num_hidden_layers"]
     folder = model_folder(layers)
     model = load_model(folder, dtype="bfloat16", device="cuda:0")
@@ -541,6 +563,8 @@ def main() -> int:
                         help="measure one part only (for profiling captures); the JSON line then holds that part")
     parser.add_argument("--shape", choices=sorted(SHAPES), default="0.5b", help="with --only serve: the model's sizes")
     parser.add_argument("--requests", type=int, default=64, help="with --only serve: requests of the workload")
+    parser.add_argument("--workload", choices=["mixed", "shared-prefix"], default="mixed",
+                        help="with --only serve: mixed prompt lengths, or long prompts that share a prefix in a pool too small for all")
     parser.add_argument("--tokens", type=int, default=2048, help="with --only attention or gemm: tokens of the one request")
     args = parser.parse_args()
     if args.impl == "reference":

@@ -19,6 +19,7 @@ This module holds no device memory; it decides which page holds what.
 """
 from __future__ import annotations
 
+import heapq
 from dataclasses import dataclass, field
 from typing import Sequence
 
@@ -84,6 +85,7 @@ class _PrefixEntry:
     tokens: tuple[int, ...]         # this page's tokens
     last_used: int
     ident: int
+    children: int = 0               # entries that continue this one (only an entry without any may be evicted)
 
 
 class SequenceCache:
@@ -132,6 +134,12 @@ class CacheManager:
         self._entry_by_id: dict[int, _PrefixEntry] = {}
         self._next_entry = 1
         self._clock = 0
+        # For eviction without a walk over all entries: which entry a page (of group 0) belongs to,
+        # a heap of (last_used, ident) records pushed whenever an entry becomes evictable (stale
+        # records are skipped when popped), and the number of pages that only the map holds.
+        self._entry_of_page: dict[int, _PrefixEntry] = {}
+        self._evict_heap: list[tuple[int, int]] = []
+        self._cached_only = 0
         self.evictions = 0
         self.state_slot_count = state_slots
         self._free_state = list(range(state_slots - 1, -1, -1))
@@ -164,6 +172,8 @@ class CacheManager:
             entry = self._prefixes.get((parent, tuple(tokens[end - self.page_tokens:end])))
             if entry is None:
                 break
+            if self.pools[0].refs[entry.pages[0]] == 1:
+                self._cached_only -= 1                 # a request holds it again
             for group, page in enumerate(entry.pages):
                 self.pools[group].share(page)
                 seq.tables[group].append(page)
@@ -200,6 +210,10 @@ class CacheManager:
                 self._next_entry += 1
                 self._prefixes[key] = entry
                 self._entry_by_id[entry.ident] = entry
+                self._entry_of_page[pages[0]] = entry
+                parent = self._entry_by_id.get(entry.parent)       # gone if the map was cleared meanwhile
+                if parent is not None:
+                    parent.children += 1
             seq._prefix_tail = entry.ident
             seq._published_pages += 1
 
@@ -242,11 +256,17 @@ class CacheManager:
         """Drop the request's reference on each of its pages and give back its state slot."""
         if seq.released:
             return
+        first = list(seq.tables[0])
         for group, table in enumerate(seq.tables):
             for page in table:
                 if page >= 0:
                     self.pools[group].release(page)
             table.clear()
+        for page in first:                             # pages that only the prefix map holds now
+            entry = self._entry_of_page.get(page) if page >= 0 else None
+            if entry is not None and self.pools[0].refs[page] == 1:
+                self._cached_only += 1
+                self._consider(entry)
         if seq.state_slot >= 0:
             self._free_state.append(seq.state_slot)
             seq.state_slot = -1
@@ -260,26 +280,34 @@ class CacheManager:
             self._evict_one()
         return pool.take()
 
+    def _consider(self, entry: _PrefixEntry) -> None:
+        """Note ``entry`` as evictable if no live request holds its pages and no entry continues it."""
+        if entry.children == 0 and all(self.pools[g].refs[p] == 1 for g, p in enumerate(entry.pages)):
+            heapq.heappush(self._evict_heap, (entry.last_used, entry.ident))
+
     def _evict_one(self) -> bool:
         """Evict the least recently used prefix entry none of whose pages a live request holds
-        and which no other entry continues."""
-        continued = {e.parent for e in self._prefixes.values()}
-        candidate = None
-        for entry in self._prefixes.values():
-            if any(self.pools[g].refs[p] != 1 for g, p in enumerate(entry.pages)):
+        and which no other entry continues (of two used at the same time, the older entry)."""
+        while self._evict_heap:
+            last_used, ident = heapq.heappop(self._evict_heap)
+            candidate = self._entry_by_id.get(ident)
+            if candidate is None or candidate.last_used != last_used or candidate.children:
+                continue                               # a stale record
+            if any(self.pools[g].refs[p] != 1 for g, p in enumerate(candidate.pages)):
                 continue
-            if entry.ident in continued:
-                continue
-            if candidate is None or entry.last_used < candidate.last_used:
-                candidate = entry
-        if candidate is None:
-            return False
-        del self._prefixes[(candidate.parent, candidate.tokens)]
-        del self._entry_by_id[candidate.ident]
-        for group, page in enumerate(candidate.pages):
-            self.pools[group].release(page)
-        self.evictions += 1
-        return True
+            del self._prefixes[(candidate.parent, candidate.tokens)]
+            del self._entry_by_id[candidate.ident]
+            del self._entry_of_page[candidate.pages[0]]
+            self._cached_only -= 1
+            for group, page in enumerate(candidate.pages):
+                self.pools[group].release(page)
+            parent = self._entry_by_id.get(candidate.parent)
+            if parent is not None:
+                parent.children -= 1
+                self._consider(parent)
+            self.evictions += 1
+            return True
+        return False
 
     def clear_prefixes(self) -> None:
         for entry in self._prefixes.values():
@@ -287,10 +315,18 @@ class CacheManager:
                 self.pools[group].release(page)
         self._prefixes.clear()
         self._entry_by_id.clear()
+        self._entry_of_page.clear()
+        self._evict_heap.clear()
+        self._cached_only = 0
 
     # ------------------------------------------------------------------ reporting
     def free_pages(self, group: int = 0) -> int:
         return len(self.pools[group].free)
+
+    def available_pages(self, group: int = 0) -> int:
+        """Pages that a request could get now: the free ones and those that only the prefix map
+        holds (they are evicted on demand, leaves first)."""
+        return len(self.pools[group].free) + self._cached_only
 
     def snapshot(self) -> dict:
         """Page accounting in the reference's form (src/kv-cache.ts:162-171); with more than one
@@ -324,3 +360,20 @@ class CacheManager:
                     raise CacheError(f"page {page}: refs {refs} but free={page in pool.free}")
         if len(set(self._free_state)) != len(self._free_state):
             raise CacheError("a state slot is free twice.")
+        # the eviction bookkeeping against a recount
+        entries = list(self._entry_by_id.values())
+        refs = self.pools[0].refs
+        if self._cached_only != sum(1 for e in entries if refs[e.pages[0]] == 1):
+            raise CacheError("the count of pages that only the prefix map holds is off.")
+        children: dict[int, int] = {}
+        for e in entries:
+            children[e.parent] = children.get(e.parent, 0) + 1
+        records = set(self._evict_heap)
+        for e in entries:
+            if e.children != children.get(e.ident, 0):
+                raise CacheError(f"prefix entry {e.ident}: {e.children} children noted, {children.get(e.ident, 0)} found.")
+            if self._entry_of_page.get(e.pages[0]) is not e:
+                raise CacheError(f"prefix entry {e.ident} is not found by its page.")
+            evictable = e.children == 0 and all(self.pools[g].refs[p] == 1 for g, p in enumerate(e.pages))
+            if evictable and (e.last_used, e.ident) not in records:
+                raise CacheError(f"prefix entry {e.ident} could be evicted but is not noted for it.")

@@ -35,10 +35,15 @@ class EngineOptions:
     prefill_chunk_size: int = 512
     prefix_caching: bool = True
     record_trace: bool = True
+    # Not in the reference, which admits a waiting request whenever a sequence slot is free: with a
+    # pool that cannot hold all requests a preempted request then comes straight back, takes pages
+    # and is preempted again, tick after tick.  With this option a request waits in the queue
+    # until the pool can hold its history beside what the running requests still have to take.
+    admit_within_pool: bool = False
 
     def validate(self):
         for name, value in asdict(self).items():
-            if name in ("prefix_caching", "record_trace"):
+            if name in ("prefix_caching", "record_trace", "admit_within_pool"):
                 if not isinstance(value, bool):
                     raise ValueError(f"{name} must be a boolean.")
             elif not isinstance(value, int) or isinstance(value, bool) or value <= 0:
@@ -275,6 +280,8 @@ class Engine:
         while len(self._active) < self.options.max_sequences and self._waiting:
             if not self.cache.can_create():
                 break
+            if self.options.admit_within_pool and self._active and not self._fits(self._requests[self._waiting[0]]):
+                break                      # first come, first served: nobody overtakes the head of the queue
             request = self._requests[self._waiting.pop(0)]
             history = request.prompt + request.output
             request.seq = self.runner.new_sequence(history if self.options.prefix_caching else None)
@@ -283,6 +290,14 @@ class Engine:
             self._active[request.id] = request
             self._emit("admitted", request,
                        f"Reused {request.seq.length} prefix tokens; pages [{','.join(map(str, request.seq.blocks))}]")
+
+    def _fits(self, request: Request) -> bool:
+        """Whether the pool can hold the request's history (and a page to grow into) beside the
+        pages that the running requests have yet to take for theirs."""
+        page = self.options.block_size
+        pages_for = lambda r: -(-(len(r.prompt) + len(r.output)) // page) + 1
+        owed = sum(max(0, pages_for(r) - len(r.seq.blocks)) for r in self._active.values())
+        return self.cache.available_pages() - owed >= pages_for(request)
 
     def _reserve(self, request: Request, upto: int, planned: list) -> bool:
         while not self.runner.reserve(request.seq, upto):

@@ -206,3 +206,44 @@ def test_random_orders_keep_every_page_accounted_for(seed):
     m.clear_prefixes()
     assert m.free_pages() == m.pools[0].num_pages
     m.check_invariants()
+
+
+def test_eviction_takes_the_least_recently_used_leaf_and_a_parent_only_after_its_children():
+    """Three published chains; pages are asked for until the map has to give way.  The order of
+    eviction: least recently used first, and within a chain the last page before the first."""
+    manager = CacheManager([GroupSpec("full", "full", None, (0,))], 8, 2)
+    chains = {"a": [1, 2, 3, 4], "b": [5, 6], "c": [7, 8, 9, 10]}
+    for tokens in chains.values():                      # a: 2 pages, b: 1 page, c: 2 pages
+        seq = manager.create()
+        for upto in range(2, len(tokens) + 1, 2):
+            assert manager.reserve(seq, upto)
+        seq.length = len(tokens)
+        manager.publish(tokens, seq)
+        manager.release(seq)
+    assert manager.free_pages() == 3 and manager.available_pages() == 8
+    hit = manager.reuse_prefix(chains["a"] + [0])       # a is used again: now the most recent
+    assert hit.length == 4
+    manager.release(hit)
+    manager.check_invariants()
+    taker = manager.create()
+    for upto in range(2, 7, 2):                         # the three free pages
+        assert manager.reserve(taker, upto)
+    assert manager.evictions == 0
+
+    def cached(tokens):
+        probe = manager.reuse_prefix(tokens + [0])
+        length = probe.length
+        manager.release(probe)
+        return length
+
+    assert manager.reserve(taker, 8) and manager.evictions == 1
+    assert cached(chains["b"]) == 0 and cached(chains["c"]) == 4 and cached(chains["a"]) == 4     # b was used least recently
+    manager.check_invariants()
+    # the probes above made c then a the most recent; c's second page goes before its first
+    assert manager.reserve(taker, 10) and manager.evictions == 2
+    assert cached(chains["c"]) == 2
+    # that probe used c's first page again; the least recently used leaf is now a's second page
+    assert manager.reserve(taker, 12) and manager.evictions == 3
+    assert cached(chains["a"]) == 2 and cached(chains["c"]) == 2
+    manager.check_invariants()
+    assert manager.available_pages() == 2

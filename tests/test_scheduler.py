@@ -240,3 +240,28 @@ def test_step_report_has_the_reference_fields():
     report = engine.step()
     assert report["work"][0]["from"] == 4 and [e["type"] for e in report["events"]] == ["token"]
     assert report["events"][0]["index"] == 0 and report["events"][0]["token"] == engine.result("A")["output"][0]
+
+
+@pytest.mark.parametrize("prefix_caching", [False, True])
+def test_admission_within_the_pool_stops_the_preemption_loop(prefix_caching):
+    """A pool that holds about half of what eight long requests need.  With the reference's
+    admission a preempted request comes straight back and is preempted again; held back until the
+    pool can take it, requests wait instead.  The outputs are the same either way."""
+    prompts = [[(7 * i + j) % 40 + 1 for j in range(30)] for i in range(8)]
+
+    def run(admit_within_pool):
+        options = EngineOptions(block_size=4, num_blocks=40, max_sequences=8, max_batch_tokens=64, prefill_chunk_size=16,
+                                prefix_caching=prefix_caching, admit_within_pool=admit_within_pool)
+        engine = make(options)
+        for i, prompt in enumerate(prompts):
+            engine.add(f"r{i}", prompt, 20)
+        reports = drain(engine, limit=5000)
+        preempted = sum(1 for r in reports for e in r["events"] if e["type"] == "preempted")
+        assert engine.cache.snapshot()["freePages"] + engine.cache.snapshot()["cachedPages"] == 40
+        return [engine.result(f"r{i}")["output"] for i in range(8)], preempted, len(reports)
+
+    plain, plain_preempted, plain_ticks = run(False)
+    held, held_preempted, held_ticks = run(True)
+    assert held == plain == [reference_output(p, 20, 50) for p in prompts]
+    assert plain_preempted > 3 * max(held_preempted, 1)          # the loop is gone
+    assert held_ticks <= plain_ticks
