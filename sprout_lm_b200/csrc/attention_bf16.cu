@@ -539,6 +539,7 @@ attention_decode_mma_kernel(const DecodeParams p) {
       if (d == 0) { part_ml[2 * row] = m; part_ml[2 * row + 1] = l; }
     } else if (p.splits == 1) {
       p.out[(size_t)r * p.out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc / l);
+      if (FUSED) p.acc[(size_t)r * width + (size_t)head * HD + d] = 0.f;      // the only reader of these q sums
     } else {
       const size_t slot = ((size_t)r * p.heads + head) * p.splits + split;
       p.part_out[slot * HD + d] = acc;
@@ -588,7 +589,7 @@ int launch_decode_mma(const DecodeParams& p, bool cluster, int requests, cudaStr
   if (smem > 48 * 1024 && !configured[cluster]) {
     cudaError_t err = cluster
         ? cudaFuncSetAttribute(attention_decode_mma_kernel<HD, true, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-        : cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        : cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return sprout_fail("attention_decode: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
     configured[cluster] = true;
   }
@@ -611,7 +612,7 @@ int launch_decode_mma(const DecodeParams& p, bool cluster, int requests, cudaStr
     cudaLaunchKernelEx(&config, attention_decode_mma_kernel<HD, true, FUSED>, p);
     return sprout_check_launch("attention_decode (tensor cores, cluster)");
   }
-  sprout_launch(attention_decode_mma_kernel<HD, false, false>, grid, dim3(DEC_THREADS), smem, stream, p);
+  sprout_launch(attention_decode_mma_kernel<HD, false, FUSED>, grid, dim3(DEC_THREADS), smem, stream, p);
   return sprout_check_launch("attention_decode (tensor cores)");
 }
 
@@ -646,7 +647,11 @@ __global__ void attention_decode_merge_kernel(const DecodeParams p) {
     }
     m = m_new;
   }
-  if (d < p.head_dim) p.out[(size_t)r * p.out_stride + (size_t)head * p.head_dim + d] = __float2bfloat16_rn(o / l);
+  if (d < p.head_dim) {
+    p.out[(size_t)r * p.out_stride + (size_t)head * p.head_dim + d] = __float2bfloat16_rn(o / l);
+    // the fused kernel's splits have all read the q sums by now: clear them for the next product
+    if (p.acc) p.acc[(size_t)r * (p.heads + 2 * p.kv_heads) * p.head_dim + (size_t)head * p.head_dim + d] = 0.f;
+  }
 }
 
 // =============================================================================== prefill
@@ -933,7 +938,8 @@ static int decode_launch(const void* q, int q_stride, const void* k_cache, const
   p.k_append = nullptr; p.v_append = nullptr;
   const bool fused = fused_early;
   if (fused) {
-    SPROUT_REQUIRE(extra->acc && head_dim <= 128 && splits <= 8, "attention_decode_fused: needs the sums, head_dim <= 128 and at most 8 splits");
+    SPROUT_REQUIRE(extra->acc && head_dim <= 128 && (splits <= 8 || scratch), "attention_decode_fused: needs the sums, head_dim <= 128 and, "
+                   "without scratch memory, at most 8 splits");
     SPROUT_REQUIRE((extra->cos_table == nullptr) == (extra->sin_table == nullptr), "attention_decode_fused: cos and sin tables go together");
     p.acc = extra->acc; p.bias = extra->bias; p.cos_table = extra->cos_table; p.sin_table = extra->sin_table;
     p.max_positions = extra->max_positions;
@@ -944,19 +950,19 @@ static int decode_launch(const void* q, int q_stride, const void* k_cache, const
       + DEC_THREADS * sizeof(long long) + (size_t)2 * DEC_THREADS * (head_dim + 8) * sizeof(__nv_bfloat16)
       + (size_t)(group * head_dim + 2 * group) * sizeof(float);
   // no scratch given and at most 8 splits: the splits of a (request, key/value head) are a cluster
-  const bool cluster = fused || (scratch == nullptr && splits > 1 && splits <= 8);
+  const bool cluster = fused ? scratch == nullptr : (scratch == nullptr && splits > 1 && splits <= 8);
   SPROUT_REQUIRE(splits == 1 || cluster || scratch, "attention_decode: scratch memory is needed for more than 8 splits");
   if (head_dim <= 128) {
     int rc = 1;
     switch (head_dim) {
-      case 16: rc = fused ? launch_decode_mma<16, true>(p, true, requests, stream) : launch_decode_mma<16, false>(p, cluster, requests, stream); break;
-      case 32: rc = fused ? launch_decode_mma<32, true>(p, true, requests, stream) : launch_decode_mma<32, false>(p, cluster, requests, stream); break;
-      case 48: rc = fused ? launch_decode_mma<48, true>(p, true, requests, stream) : launch_decode_mma<48, false>(p, cluster, requests, stream); break;
-      case 64: rc = fused ? launch_decode_mma<64, true>(p, true, requests, stream) : launch_decode_mma<64, false>(p, cluster, requests, stream); break;
-      case 80: rc = fused ? launch_decode_mma<80, true>(p, true, requests, stream) : launch_decode_mma<80, false>(p, cluster, requests, stream); break;
-      case 96: rc = fused ? launch_decode_mma<96, true>(p, true, requests, stream) : launch_decode_mma<96, false>(p, cluster, requests, stream); break;
-      case 112: rc = fused ? launch_decode_mma<112, true>(p, true, requests, stream) : launch_decode_mma<112, false>(p, cluster, requests, stream); break;
-      case 128: rc = fused ? launch_decode_mma<128, true>(p, true, requests, stream) : launch_decode_mma<128, false>(p, cluster, requests, stream); break;
+      case 16: rc = fused ? launch_decode_mma<16, true>(p, cluster, requests, stream) : launch_decode_mma<16, false>(p, cluster, requests, stream); break;
+      case 32: rc = fused ? launch_decode_mma<32, true>(p, cluster, requests, stream) : launch_decode_mma<32, false>(p, cluster, requests, stream); break;
+      case 48: rc = fused ? launch_decode_mma<48, true>(p, cluster, requests, stream) : launch_decode_mma<48, false>(p, cluster, requests, stream); break;
+      case 64: rc = fused ? launch_decode_mma<64, true>(p, cluster, requests, stream) : launch_decode_mma<64, false>(p, cluster, requests, stream); break;
+      case 80: rc = fused ? launch_decode_mma<80, true>(p, cluster, requests, stream) : launch_decode_mma<80, false>(p, cluster, requests, stream); break;
+      case 96: rc = fused ? launch_decode_mma<96, true>(p, cluster, requests, stream) : launch_decode_mma<96, false>(p, cluster, requests, stream); break;
+      case 112: rc = fused ? launch_decode_mma<112, true>(p, cluster, requests, stream) : launch_decode_mma<112, false>(p, cluster, requests, stream); break;
+      case 128: rc = fused ? launch_decode_mma<128, true>(p, cluster, requests, stream) : launch_decode_mma<128, false>(p, cluster, requests, stream); break;
     }
     if (rc) return rc;
   } else {
@@ -1018,14 +1024,16 @@ SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* 
 // appended cache it takes the float32 sums of the q/k/v product for each request's new token
 // (acc [requests, (heads + 2 kv_heads) * head_dim], contiguous) and their bias; it rotates q and k
 // by the token's position context_lens[r] - 1 (tables may be null: no rotation), appends k and v
-// to the cache, attends, and leaves acc zeroed.  head_dim <= 128, at most 8 splits.
+// to the cache, attends, and leaves acc zeroed.  head_dim <= 128; without scratch memory (as for
+// sprout_attention_decode) at most 8 splits, merged inside a cluster.
 SPROUT_API int sprout_attention_decode_fused(float* acc, const float* bias, const float* cos_table, const float* sin_table,
                                              int max_positions, void* k_cache, void* v_cache, const int* block_table,
                                              int table_stride, const int* context_lens, void* out, int out_stride,
-                                             int requests, int heads, int kv_heads, int head_dim, int page_tokens,
-                                             int num_pages, int split_keys, int splits, int* status, cudaStream_t stream) {
+                                             float* scratch, int requests, int heads, int kv_heads, int head_dim,
+                                             int page_tokens, int num_pages, int split_keys, int splits, int* status,
+                                             cudaStream_t stream) {
   FusedTail extra{acc, bias, cos_table, sin_table, max_positions};
-  return decode_launch(nullptr, 0, k_cache, v_cache, block_table, table_stride, context_lens, out, out_stride, nullptr,
+  return decode_launch(nullptr, 0, k_cache, v_cache, block_table, table_stride, context_lens, out, out_stride, scratch,
                        requests, heads, kv_heads, head_dim, page_tokens, num_pages, split_keys, splits, status, stream, &extra);
 }
 

@@ -37,7 +37,7 @@ _SIGNATURES = {
     "sprout_sample": [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P],
     "sprout_advance_decode": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
     "sprout_attention_decode": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
-    "sprout_attention_decode_fused": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_attention_decode_fused": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, ctypes.c_longlong, _P, _P, _P],
     "sprout_attention_prefill_tc_supported": [_I, _I, _I],
     "sprout_gemm_bf16": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
@@ -336,9 +336,8 @@ def attention_decode(q, k_cache, v_cache, block_table, context_lens, out, heads,
 
 def decode_fusable(requests: int, heads: int, kv_heads: int, head_dim: int, max_keys: int) -> bool:
     """Whether the decode step's attention can take the projection's tail (bias, rotation, cache
-    append) into its own kernel: tensor-core kernel sizes and at most 8 splits."""
-    return head_dim <= 128 and head_dim % 16 == 0 and heads // kv_heads <= 16 \
-        and not decode_split_plan(requests, kv_heads, max_keys)[2]
+    append) into its own kernel: the tensor-core kernel's sizes."""
+    return head_dim <= 128 and head_dim % 16 == 0 and heads // kv_heads <= 16
 
 
 def attention_decode_fused(acc, bias, cos_table, sin_table, k_cache, v_cache, block_table, context_lens, out,
@@ -362,13 +361,18 @@ def attention_decode_fused(acc, bias, cos_table, sin_table, k_cache, v_cache, bl
     _rows_contiguous(block_table, "block_table")
     max_keys = block_table.shape[1] * k_cache.shape[2]
     split_keys, splits, through_memory = decode_split_plan(R, kv_heads, max_keys)
-    if through_memory or not decode_fusable(R, heads, kv_heads, head_dim, max_keys):
+    if not decode_fusable(R, heads, kv_heads, head_dim, max_keys):
         raise KernelError("attention_decode_fused: these sizes need the separate kernels (see decode_fusable)")
+    scratch = None
+    if through_memory:            # many splits or a large batch: independent CTAs and a merge kernel
+        need = load_library().sprout_attention_decode_scratch_floats(R, heads, head_dim, splits)
+        scratch = torch.empty(need, dtype=torch.float32, device=out.device)
     _run("sprout_attention_decode_fused", _ptr(acc, "acc"), _ptr(bias, "bias", torch.float32, True),
          _ptr(cos_table, "cos", torch.float32, True), _ptr(sin_table, "sin", torch.float32, True),
          cos_table.shape[0] if cos_table is not None else 0, _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"),
          _ptr(block_table, "block_table", torch.int32), block_table.stride(0),
-         _ptr(context_lens, "context_lens", torch.int32), _ptr(out, "out"), out.stride(0), R, heads, kv_heads, head_dim,
+         _ptr(context_lens, "context_lens", torch.int32), _ptr(out, "out"), out.stride(0),
+         _ptr(scratch, "scratch", torch.float32, True), R, heads, kv_heads, head_dim,
          k_cache.shape[2], k_cache.shape[0], split_keys, splits, _ptr(status, "status", torch.int32), _stream())
 
 

@@ -96,7 +96,7 @@ class PagedGQAttention(Part):
                               split_k=self.qkv.split_k(tokens, True))
             attended = torch.empty((tokens, self.heads * self.head_dim), dtype=h.dtype, device=h.device)
             max_keys = cache.block_table.shape[1] * cache.page_tokens
-            if ctx.max_q_len == 1 and tokens <= 32 and cache.write and kernels.decode_fusable(tokens, self.heads, self.kv_heads,
+            if ctx.max_q_len == 1 and cache.write and kernels.decode_fusable(tokens, self.heads, self.kv_heads,
                                                                              self.head_dim, max_keys):
                 # one token per request: bias, rotation and the cache append happen inside the attention kernel
                 kernels.attention_decode_fused(acc, self.qkv.bias, cos, sin, cache.k, cache.v, cache.block_table,

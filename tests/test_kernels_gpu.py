@@ -456,7 +456,10 @@ def test_attention_decode_split_keys(status, heads, kv_heads, head_dim, page, le
 
 
 @pytest.mark.parametrize("rotate", [False, True])
-@pytest.mark.parametrize("heads,kv_heads,head_dim,page,lengths", DECODE_CASES[:6])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page,lengths", DECODE_CASES[:6] + [
+    (14, 2, 64, 16, [37 + 13 * i for i in range(70)]),        # a large batch: independent CTAs, merged through memory
+    (4, 2, 64, 16, [3000, 1500]),                              # more than 8 splits: through memory too
+])
 def test_attention_decode_fused_projection_tail(status, heads, kv_heads, head_dim, page, lengths, rotate):
     """The decode kernel that also finishes the projection: the new token's q, k, v arrive as
     float32 sums plus a bias; the kernel rotates, appends to the cache, attends and clears the sums.
@@ -472,7 +475,7 @@ def test_attention_decode_fused_projection_tail(status, heads, kv_heads, head_di
 
     class RT:
         device = torch.device(DEV)
-    cos, sin = HalfSplitRotary("", head_dim, 1e4, 1024).rotary_tables(RT) if rotate else (None, None)
+    cos, sin = HalfSplitRotary("", head_dim, 1e4, max(1024, max(lengths))).rotary_tables(RT) if rotate else (None, None)
     positions = (case["context_lens"] - 1).to(torch.int32)
     seq_of_token = torch.arange(R, dtype=torch.int32, device=DEV)
     # the separate path
@@ -490,6 +493,8 @@ def test_attention_decode_fused_projection_tail(status, heads, kv_heads, head_di
     acc2 = sums.clone()
     got = torch.full_like(want, float("nan"))
     assert kernels.decode_fusable(R, heads, kv_heads, head_dim, case["table"].shape[1] * page)
+    if R >= 70 or max(lengths) > 2000:
+        assert kernels.decode_split_plan(R, kv_heads, case["table"].shape[1] * page)[2]      # this case goes through memory
     kernels.attention_decode_fused(acc2, bias, cos, sin, k2, v2, case["table"], case["context_lens"], got, heads,
                                    kv_heads, head_dim, status)
     assert torch.equal(k2, k1) and torch.equal(v2, v1)                 # the same append, bit for bit
