@@ -393,13 +393,13 @@ def timed_serving(shape: str, layers: int, requests: int, workload: str = "mixed
             "preempted": preempted, "prefill_steps_replayed": replays}
 
 
-def timed_attention(tokens: int, repeats: int = 20) -> dict:
+def timed_attention(tokens: int, shape: str = "0.5b", repeats: int = 20) -> dict:
     """The prefill attention kernels alone, at the model's head sizes, over a paged cache: one
     request of ``tokens`` tokens attending to itself (causal), both kernels."""
     import torch
     from sprout_lm_b200 import kernels
-    heads, kv_heads = CONFIG_05B["num_attention_heads"], CONFIG_05B["num_key_value_heads"]
-    head_dim, page = CONFIG_05B["hidden_size"] // heads, 16
+    heads, kv_heads = SHAPES[shape]["num_attention_heads"], SHAPES[shape]["num_key_value_heads"]
+    head_dim, page = SHAPES[shape]["hidden_size"] // heads, 16
     pages = -(-tokens // page)
     g = torch.Generator(device="cuda").manual_seed(0)
     k = torch.randn(pages + 1, kv_heads, page, head_dim, device="cuda", generator=g).to(torch.bfloat16)
@@ -411,7 +411,7 @@ def timed_attention(tokens: int, repeats: int = 20) -> dict:
     out = torch.empty_like(q)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     flops = 4.0 * heads * head_dim * tokens * (tokens + 1) / 2
-    result = {"impl": "ours", "only": "attention", "tokens": tokens, "heads": heads, "kv_heads": kv_heads,
+    result = {"impl": "ours", "only": "attention", "shape": shape, "tokens": tokens, "heads": heads, "kv_heads": kv_heads,
               "head_dim": head_dim, "page_tokens": page}
     for variant in ("mma_sync", "tcgen05"):
         call = lambda: kernels.attention_prefill(q, k, v, table, q_start, positions, out, heads, kv_heads, head_dim,
@@ -432,15 +432,16 @@ def timed_attention(tokens: int, repeats: int = 20) -> dict:
     return result
 
 
-def timed_gemms(tokens: int, repeats: int = 20) -> dict:
+def timed_gemms(tokens: int, shape: str = "0.5b", repeats: int = 20) -> dict:
     """The model's four projections at ``tokens`` tokens, each alone: 20 launches replayed from a
     CUDA graph (no host time between them), beside the library's plain bfloat16 product of the
     same shape for scale (it fuses nothing and is not on the engine's path)."""
     import torch
     from sprout_lm_b200 import kernels
+    from sprout_lm_b200.parts.linear import small_batch_split_k
     from sprout_lm_b200.parts.mlp import interleave_gate_up
-    hidden, inter = CONFIG_05B["hidden_size"], CONFIG_05B["intermediate_size"]
-    heads, kv_heads = CONFIG_05B["num_attention_heads"], CONFIG_05B["num_key_value_heads"]
+    hidden, inter = SHAPES[shape]["hidden_size"], SHAPES[shape]["intermediate_size"]
+    heads, kv_heads = SHAPES[shape]["num_attention_heads"], SHAPES[shape]["num_key_value_heads"]
     qkv = (heads + 2 * kv_heads) * (hidden // heads)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     g = torch.Generator(device="cuda").manual_seed(0)
@@ -464,9 +465,10 @@ def timed_gemms(tokens: int, repeats: int = 20) -> dict:
         torch.cuda.synchronize()
         return begin.elapsed_time(end) * 1000 / repeats
 
-    result = {"impl": "ours", "only": "gemm", "tokens": tokens}
-    cases = [("qkv", qkv, hidden, "bias"), ("o", hidden, hidden, "residual"), ("gate_up", 2 * inter, hidden, "swiglu"),
-             ("down", hidden, inter, "residual")]
+    result = {"impl": "ours", "only": "gemm", "shape": shape, "tokens": tokens}
+    # up to 256 tokens the engine sums q/k/v in float32 over a split K range (bias and rotation follow in attention)
+    cases = [("qkv", qkv, hidden, "bias" if tokens > 256 else "residual"), ("o", hidden, hidden, "residual"),
+             ("gate_up", 2 * inter, hidden, "swiglu"), ("down", hidden, inter, "residual")]
     for name, n, k, kind in cases:
         a, w = rand(tokens, k), rand(n, k)
         kw = {}
@@ -474,14 +476,15 @@ def timed_gemms(tokens: int, repeats: int = 20) -> dict:
             out, kw = torch.empty(tokens, n, dtype=torch.bfloat16, device="cuda"), {"bias": torch.zeros(n, device="cuda")}
         elif kind == "residual":
             out = torch.zeros(tokens, n, device="cuda")
-            kw = {"residual": out}
+            kw = {"residual": out, "split_k": small_batch_split_k(n, k, tokens, True)}
         else:
             w = interleave_gate_up(w[:n // 2].contiguous(), w[n // 2:].contiguous())
             out, kw = torch.empty(tokens, n // 2, dtype=torch.bfloat16, device="cuda"), {"swiglu": True}
         us = replayed(lambda: kernels.gemm_bf16(a, w, out, status, **kw))
         library = replayed(lambda: torch.matmul(a, w.t()))
-        result[name] = {"shape": [tokens, n, k], "epilogue": kind, "us": round(us, 1),
-                        "tflops": round(2.0 * tokens * n * k / us / 1e6), "library_plain_us": round(library, 1)}
+        result[name] = {"shape": [tokens, n, k], "epilogue": kind, "split_k": kw.get("split_k", 1), "us": round(us, 1),
+                        "tflops": round(2.0 * tokens * n * k / us / 1e6), "weight_gbs": round(2.0 * n * k / us / 1e3),
+                        "library_plain_us": round(library, 1)}
     assert int(status.item()) == 0
     return result
 
@@ -494,31 +497,37 @@ def run(args) -> dict:
     from sprout_lm_b200.engine.step import ModelRunner
     kernels.load_library(verbose=True)
     if args.only == "attention":
-        return timed_attention(args.tokens)
+        return timed_attention(args.tokens, args.shape)
     if args.only == "gemm":
-        return timed_gemms(args.tokens)
+        return timed_gemms(args.tokens, args.shape)
     if args.only == "serve":
         return timed_serving(args.shape, args.layers, args.requests, args.workload)
-    layers = args.layers or CONFIG_05B["num_hidden_layers"]
-    folder = model_folder(layers)
+    if args.only == "all" and args.shape != "0.5b":
+        raise SystemExit("bench.py: the full line is measured at the 0.5b shape; give --only with another --shape")
+    base = SHAPES[args.shape]
+    layers = args.layers or base["num_hidden_layers"]
+    folder = model_folder(layers, args.shape)
     model = load_model(folder, dtype="bfloat16", device="cuda:0")
-    cfg = dict(CONFIG_05B, num_hidden_layers=layers)
+    cfg = dict(base, num_hidden_layers=layers)
     peak = peaks()
     rng = np.random.default_rng(0)
-    batch, prompt_len, context = args.batch, 512, CONFIG_05B["max_position_embeddings"]
+    batch, prompt_len, context = args.batch, 512, base["max_position_embeddings"]
     pages = 64 * (-(-(prompt_len + args.steps + args.warmup + 16) // 16)) + 2048 // 16 + 16
     runner = ModelRunner(model, num_pages=pages, page_tokens=16, max_requests=64, prefix_caching=False)
 
     if args.only == "ablate":
-        return {"impl": "ours", "only": "ablate", "layers": layers, "batch": batch,
+        return {"impl": "ours", "only": "ablate", "shape": args.shape, "layers": layers, "batch": batch,
                 **ablation(model, batch, prompt_len, min(args.steps, 60), args.warmup)}
     if args.only == "prefill":
         prefill_ms = timed_prefill(runner, 2048, rng, repeats=1)
-        return {"impl": "ours", "only": "prefill", "layers": layers, "ms": round(prefill_ms, 4)}
+        return {"impl": "ours", "only": "prefill", "shape": args.shape, "layers": layers, "ms": round(prefill_ms, 4),
+                "frac": round(prefill_flops(cfg, 2048) / (prefill_ms / 1000) / (peak["bf16_tflops"] * 1e12), 4)}
     main = timed_decode(runner, batch, prompt_len, args.steps, args.warmup, rng, sampler=ClockSampler())
     if args.only == "decode":
-        return {"impl": "ours", "only": "decode", "layers": layers, "batch": batch, "ms_per_step": round(main["ms_per_step"], 4),
-                "launches_per_step": main["launches_per_step"]}
+        step_bytes = weight_bytes(model) + batch * main["mean_context"] * cache_bytes_per_token(model, torch.bfloat16)
+        return {"impl": "ours", "only": "decode", "shape": args.shape, "layers": layers, "batch": batch,
+                "ms_per_step": round(main["ms_per_step"], 4), "launches_per_step": main["launches_per_step"],
+                "gbs": round(step_bytes / (main["ms_per_step"] / 1000) / 1e9, 1)}
     points = {}
     for b in (1, 64):
         side_steps = min(args.steps, 64)
@@ -561,7 +570,7 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate", "attention", "gemm", "serve"], default="all",
                         help="measure one part only (for profiling captures); the JSON line then holds that part")
-    parser.add_argument("--shape", choices=sorted(SHAPES), default="0.5b", help="with --only serve: the model's sizes")
+    parser.add_argument("--shape", choices=sorted(SHAPES), default="0.5b", help="with --only: the model's sizes")
     parser.add_argument("--requests", type=int, default=64, help="with --only serve: requests of the workload")
     parser.add_argument("--workload", choices=["mixed", "shared-prefix"], default="mixed",
                         help="with --only serve: mixed prompt lengths, or long prompts that share a prefix in a pool too small for all")

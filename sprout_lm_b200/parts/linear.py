@@ -13,6 +13,16 @@ from .. import kernels
 SM_COUNT = 148
 
 
+def small_batch_split_k(out_features: int, in_features: int, tokens: int, residual: bool) -> int:
+    """How many CTAs share the K range of a small-batch product into a float32 residual:
+    enough to put a CTA on most SMs when the matrix has few 128-row tiles."""
+    if not residual or tokens > 256:
+        return 1
+    tiles = -(-out_features // 128)
+    k_blocks = -(-in_features // 64)
+    return max(1, min(k_blocks, SM_COUNT // tiles))
+
+
 class Linear:
     def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None, status: torch.Tensor):
         self.weight = weight
@@ -24,13 +34,7 @@ class Linear:
                              "its rows must start on 16-byte boundaries")
 
     def split_k(self, tokens: int, residual: bool) -> int:
-        """How many CTAs share the K range of a small-batch product into a float32 residual:
-        enough to put a CTA on most SMs when the matrix has few 128-row tiles."""
-        if not residual or tokens > 256:
-            return 1
-        tiles = -(-self.out_features // 128)
-        k_blocks = -(-self.in_features // 64)
-        return max(1, min(k_blocks, SM_COUNT // tiles))
+        return small_batch_split_k(self.out_features, self.in_features, tokens, residual)
 
     def forward_swiglu(self, a: torch.Tensor) -> torch.Tensor:
         """silu(gate) * up of a fused, interleaved gate/up matrix: fused into the product's epilogue
