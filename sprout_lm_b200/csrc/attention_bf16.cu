@@ -4,8 +4,8 @@
 //   takes a run of `split_keys` keys of one key/value head of one request and serves all the
 //   query heads of that group from one read of the keys and values.  Partial results
 //   (running maximum, sum, unnormalised output) are merged in one of two ways: with up to 8
-//   splits the CTAs of a (request, key/value head) form a thread-block cluster and the first
-//   of them reads the others' partial results through distributed shared memory; with more
+//   splits the CTAs of a (request, key/value head) form a thread-block cluster and each of
+//   them merges a share of the output from all partial results through distributed shared memory; with more
 //   splits they go to scratch memory and a second kernel merges them.  The work of a query
 //   does not depend on the batch around it.
 //
@@ -356,13 +356,36 @@ attention_decode_mma_kernel(const DecodeParams p) {
     if (FUSED && !first && key == pos) off = -2;       // the new token's row is written below, not loaded
     rows[tid] = off;
     __syncthreads();                                   // offsets and q visible; the staging buffers are free
-    for (int idx = tid; idx < DEC_THREADS * CHUNKS; idx += DEC_THREADS) {
-      const int row = idx / CHUNKS, c = idx % CHUNKS;
-      const long long ro = rows[row];
-      __nv_bfloat16* dk = sK + row * STRIDE + c * 8;
-      __nv_bfloat16* dv = sV + row * STRIDE + c * 8;
-      if (ro >= 0) { cp_async16(dk, p.k_cache + ro + c * 8); cp_async16(dv, p.v_cache + ro + c * 8); }
-      else if (ro == -1) { *(uint4*)dk = make_uint4(0, 0, 0, 0); *(uint4*)dv = make_uint4(0, 0, 0, 0); }
+    if constexpr (DEC_THREADS % CHUNKS == 0) {
+      // a thread keeps its 16-byte column and walks down the rows: neighbours in a warp copy
+      // neighbouring pieces of a row, and nothing but the row's offset changes between copies
+      constexpr int ROWS_AT_ONCE = DEC_THREADS / CHUNKS;
+      const int c8 = (tid % CHUNKS) * 8, r0 = tid / CHUNKS;
+      const uint32_t dk0 = (uint32_t)__cvta_generic_to_shared(sK + r0 * STRIDE + c8);
+      const uint32_t dv0 = (uint32_t)__cvta_generic_to_shared(sV + r0 * STRIDE + c8);
+      const __nv_bfloat16* kg = p.k_cache + c8;
+      const __nv_bfloat16* vg = p.v_cache + c8;
+#pragma unroll
+      for (int k = 0; k < CHUNKS; k++) {
+        const long long ro = rows[r0 + k * ROWS_AT_ONCE];
+        const uint32_t step = (uint32_t)(k * ROWS_AT_ONCE * STRIDE * 2);
+        if (ro >= 0) {
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dk0 + step), "l"(kg + ro));
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dv0 + step), "l"(vg + ro));
+        } else if (ro == -1) {
+          asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dk0 + step), "r"(0) : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dv0 + step), "r"(0) : "memory");
+        }
+      }
+    } else {
+      for (int idx = tid; idx < DEC_THREADS * CHUNKS; idx += DEC_THREADS) {
+        const int row = idx / CHUNKS, c = idx % CHUNKS;
+        const long long ro = rows[row];
+        __nv_bfloat16* dk = sK + row * STRIDE + c * 8;
+        __nv_bfloat16* dv = sV + row * STRIDE + c * 8;
+        if (ro >= 0) { cp_async16(dk, p.k_cache + ro + c * 8); cp_async16(dv, p.v_cache + ro + c * 8); }
+        else if (ro == -1) { *(uint4*)dk = make_uint4(0, 0, 0, 0); *(uint4*)dv = make_uint4(0, 0, 0, 0); }
+      }
     }
     cp_async_commit();
     if (first) pdl_wait();                             // the first pass's keys and values are on their way
@@ -380,20 +403,19 @@ attention_decode_mma_kernel(const DecodeParams p) {
       if (pos < 0 || (rotate && pos >= p.max_positions)) { if (tid == 0) atomicOr(p.status, SPROUT_STATUS_BAD_POSITION); }
       const int safe = min(max(pos, 0), max(p.max_positions - 1, 0));
       constexpr int HALF = HD / 2;
-      for (int idx = tid; idx < 16 * HALF; idx += DEC_THREADS) {
+      const float* sums = p.acc + (size_t)r * width + (size_t)g * group * HD;
+      const float* bias = p.bias ? p.bias + (size_t)g * group * HD : nullptr;
+      for (int idx = tid; idx < group * HALF; idx += DEC_THREADS) {
         const int row = idx / HALF, d = idx % HALF;
-        float lo = 0.f, hi = 0.f;
-        if (row < group) {
-          const int at = (g * group + row) * HD + d;
-          const float a = p.acc[(size_t)r * width + at] + (p.bias ? p.bias[at] : 0.f);
-          const float b = p.acc[(size_t)r * width + at + HALF] + (p.bias ? p.bias[at + HALF] : 0.f);
-          const float c = rotate ? p.cos_table[(size_t)safe * HALF + d] : 1.f, sn = rotate ? p.sin_table[(size_t)safe * HALF + d] : 0.f;
-          lo = a * c - b * sn;
-          hi = b * c + a * sn;
-        }
-        sQ[row * STRIDE + d] = __float2bfloat16_rn(lo);
-        sQ[row * STRIDE + d + HALF] = __float2bfloat16_rn(hi);
+        const int at = row * HD + d;
+        const float a = sums[at] + (bias ? bias[at] : 0.f);
+        const float b = sums[at + HALF] + (bias ? bias[at + HALF] : 0.f);
+        const float c = rotate ? p.cos_table[(size_t)safe * HALF + d] : 1.f, sn = rotate ? p.sin_table[(size_t)safe * HALF + d] : 0.f;
+        sQ[row * STRIDE + d] = __float2bfloat16_rn(a * c - b * sn);
+        sQ[row * STRIDE + d + HALF] = __float2bfloat16_rn(b * c + a * sn);
       }
+      for (int idx = group * CHUNKS + tid; idx < 16 * CHUNKS; idx += DEC_THREADS)      // the tile's unused rows
+        *(uint4*)(sQ + (idx / CHUNKS) * STRIDE + (idx % CHUNKS) * 8) = make_uint4(0, 0, 0, 0);
     }
     if (first) {
       end = min(len, begin + p.split_keys);
@@ -506,44 +528,65 @@ attention_decode_mma_kernel(const DecodeParams p) {
     }
   }
 
-  // the warps' partial results -> shared memory (over the keys, which are no longer needed)
+  // The warps' partial results -> shared memory (over the keys, which are no longer needed), in
+  // the layout the MMA left them in: a lane holds the same (row, column) places in every warp.
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
   __syncthreads();
+  float4* frag = (float4*)wO;                          // [4 warps][HD / 8 column blocks][32 lanes]
   {
-    float* mine = wO + warp * 16 * HD;
+    float4* mine = frag + warp * (HD / 8) * 32 + lane;
 #pragma unroll
-    for (int i = 0; i < HD / 8; i++) {
-      *(float2*)(mine + gr * HD + i * 8 + qc * 2) = make_float2(o[i][0], o[i][1]);
-      *(float2*)(mine + (gr + 8) * HD + i * 8 + qc * 2) = make_float2(o[i][2], o[i][3]);
-    }
+    for (int i = 0; i < HD / 8; i++) mine[i * 32] = make_float4(o[i][0], o[i][1], o[i][2], o[i][3]);
     if (qc == 0) {
       wm[warp * 16 + gr] = m0; wm[warp * 16 + gr + 8] = m1;
       wl[warp * 16 + gr] = l0; wl[warp * 16 + gr + 8] = l1;
     }
   }
   __syncthreads();
-  // merge the 4 warps: the CTA's partial result for every (head, dim)
-  for (int idx = tid; idx < group * HD; idx += DEC_THREADS) {
-    const int row = idx / HD, d = idx % HD;
-    const float a0 = wm[row], a1 = wm[16 + row], a2 = wm[32 + row], a3 = wm[48 + row];
-    const float m = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
-    const float w0 = a0 == -INFINITY ? 0.f : __expf(a0 - m), w1 = a1 == -INFINITY ? 0.f : __expf(a1 - m);
-    const float w2 = a2 == -INFINITY ? 0.f : __expf(a2 - m), w3 = a3 == -INFINITY ? 0.f : __expf(a3 - m);
-    const float l = (wl[row] * w0 + wl[16 + row] * w1) + (wl[32 + row] * w2 + wl[48 + row] * w3);
-    const float acc = (wO[row * HD + d] * w0 + wO[(16 + row) * HD + d] * w1)
-                    + (wO[(32 + row) * HD + d] * w2 + wO[(48 + row) * HD + d] * w3);
-    const int head = g * group + row;
-    if constexpr (CLUSTER) {
-      part_acc[idx] = acc;
-      if (d == 0) { part_ml[2 * row] = m; part_ml[2 * row + 1] = l; }
-    } else if (p.splits == 1) {
-      p.out[(size_t)r * p.out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc / l);
-      if (FUSED) p.acc[(size_t)r * width + (size_t)head * HD + d] = 0.f;      // the only reader of these q sums
-    } else {
-      const size_t slot = ((size_t)r * p.heads + head) * p.splits + split;
-      p.part_out[slot * HD + d] = acc;
-      if (d == 0) { p.part_ml[slot * 2] = m; p.part_ml[slot * 2 + 1] = l; }
+  // merge the 4 warps: each warp takes every fourth block of 8 columns, a lane its two rows
+  {
+    float wa[4], wb[4];                                // the warps' weights for rows gr and gr + 8
+    float ma = -INFINITY, mb = -INFINITY, la = 0.f, lb = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; w++) { wa[w] = wm[w * 16 + gr]; wb[w] = wm[w * 16 + gr + 8]; ma = fmaxf(ma, wa[w]); mb = fmaxf(mb, wb[w]); }
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+      wa[w] = wa[w] == -INFINITY ? 0.f : __expf(wa[w] - ma);
+      wb[w] = wb[w] == -INFINITY ? 0.f : __expf(wb[w] - mb);
+    }
+    la = (wl[gr] * wa[0] + wl[16 + gr] * wa[1]) + (wl[32 + gr] * wa[2] + wl[48 + gr] * wa[3]);
+    lb = (wl[gr + 8] * wb[0] + wl[24 + gr] * wb[1]) + (wl[40 + gr] * wb[2] + wl[56 + gr] * wb[3]);
+    const bool row_a = gr < group, row_b = gr + 8 < group;
+    auto emit = [&](int row, int d, float x, float y, float l) {
+      const int head = g * group + row;
+      if constexpr (CLUSTER) {
+        *(float2*)(part_acc + row * HD + d) = make_float2(x, y);
+      } else if (p.splits == 1) {
+        *(__nv_bfloat162*)(p.out + (size_t)r * p.out_stride + (size_t)head * HD + d) = __floats2bfloat162_rn(x / l, y / l);
+        if (FUSED) *(float2*)(p.acc + (size_t)r * width + (size_t)head * HD + d) = make_float2(0.f, 0.f);   // the only reader of these q sums
+      } else {
+        const size_t slot = ((size_t)r * p.heads + head) * p.splits + split;
+        *(float2*)(p.part_out + slot * HD + d) = make_float2(x, y);
+      }
+    };
+    for (int i = warp; i < HD / 8; i += 4) {
+      const float4 f0 = frag[(0 * (HD / 8) + i) * 32 + lane], f1 = frag[(1 * (HD / 8) + i) * 32 + lane];
+      const float4 f2 = frag[(2 * (HD / 8) + i) * 32 + lane], f3 = frag[(3 * (HD / 8) + i) * 32 + lane];
+      const int d = i * 8 + qc * 2;
+      if (row_a) emit(gr, d, (f0.x * wa[0] + f1.x * wa[1]) + (f2.x * wa[2] + f3.x * wa[3]),
+                      (f0.y * wa[0] + f1.y * wa[1]) + (f2.y * wa[2] + f3.y * wa[3]), la);
+      if (row_b) emit(gr + 8, d, (f0.z * wb[0] + f1.z * wb[1]) + (f2.z * wb[2] + f3.z * wb[3]),
+                      (f0.w * wb[0] + f1.w * wb[1]) + (f2.w * wb[2] + f3.w * wb[3]), lb);
+    }
+    if (warp == 0 && qc == 0) {                        // each row's maximum and sum, once
+      if constexpr (CLUSTER) {
+        if (row_a) { part_ml[2 * gr] = ma; part_ml[2 * gr + 1] = la; }
+        if (row_b) { part_ml[2 * (gr + 8)] = mb; part_ml[2 * (gr + 8) + 1] = lb; }
+      } else if (p.splits > 1) {
+        if (row_a) { const size_t slot = ((size_t)r * p.heads + g * group + gr) * p.splits + split; p.part_ml[slot * 2] = ma; p.part_ml[slot * 2 + 1] = la; }
+        if (row_b) { const size_t slot = ((size_t)r * p.heads + g * group + gr + 8) * p.splits + split; p.part_ml[slot * 2] = mb; p.part_ml[slot * 2 + 1] = lb; }
+      }
     }
   }
   if constexpr (CLUSTER) {
@@ -552,9 +595,10 @@ attention_decode_mma_kernel(const DecodeParams p) {
     if (FUSED && cluster.block_rank() == 0) {          // every split has read the q sums: clear them
       for (int i = tid; i < group * HD; i += DEC_THREADS) p.acc[(size_t)r * width + g * group * HD + i] = 0.f;
     }
-    if (cluster.block_rank() == 0) {
+    {
+      // every CTA of the cluster merges its share of the (head, dim) places from all the splits
       const int count = (int)cluster.num_blocks();
-      for (int i = tid; i < group * HD; i += DEC_THREADS) {
+      for (int i = (int)cluster.block_rank() * DEC_THREADS + tid; i < group * HD; i += count * DEC_THREADS) {
         const int h = i / HD;
         float ms[8], ls[8], os[8];
 #pragma unroll
