@@ -7,6 +7,7 @@ built or loaded, or no CUDA device is present, calls raise.
 from __future__ import annotations
 
 import ctypes
+import functools
 import os
 import threading
 from ctypes import c_float, c_int, c_void_p
@@ -284,29 +285,44 @@ def _check_paged(q, k_cache, v_cache, block_table, out, heads, head_dim, name):
 SM_COUNT = 148
 
 
-CLUSTER_CTA_LIMIT = 3 * SM_COUNT
-
-
-def decode_split_plan(requests: int, kv_heads: int, max_keys: int) -> tuple[int, int, bool]:
+@functools.lru_cache(maxsize=4096)
+def decode_split_plan(requests: int, kv_heads: int, max_keys: int, head_dim: int = 64) -> tuple[int, int, bool]:
     """(keys per split, splits, whether scratch memory is needed) for decode attention over at
-    most ``max_keys`` keys.  Up to 8 splits are merged inside a thread-block cluster; splits are
-    128 keys, made longer while there would be more than 8 of them, unless the batch is too
-    small to fill the GPU that way, in which case many short splits go through scratch memory."""
-    split_keys = 128
+    most ``max_keys`` keys.  A CTA takes its split in passes of 128 keys, one after the other; up
+    to 8 splits of a (request, key/value head) merge inside a thread-block cluster, more go
+    through scratch memory and a merge kernel.
+
+    The pick minimises a small model of the kernel's time, fitted to measurements on a B200: the
+    CTAs run in waves of as many as fit the SMs at once; a wave costs a fixed start and, per
+    pass, the longer of a pass's latency and the time to bring the wave's keys and values in; a
+    merge costs a little inside a cluster and more through memory, growing with the splits.  So a
+    small batch gets many short splits (latency), a large one few long ones (no idle waves, no
+    merge kernel), and a long context as many splits as keep the SMs busy."""
     pairs = requests * kv_heads
-    # at most 8 splits (a cluster); short splits stay best even for large batches (a CTA's passes
-    # run one after the other)
-    while -(-max_keys // split_keys) > 8:
-        split_keys += 128
-    if pairs * 8 < SM_COUNT and max_keys > 8 * 128:
-        split_keys = 128
-        while pairs * (-(-max_keys // split_keys)) > 4 * SM_COUNT:
-            split_keys *= 2
-    splits = max(1, -(-max_keys // split_keys))
-    # clusters must be co-scheduled: about 110 clusters of 5 fit the GPU at once, so a large batch
-    # would run its clusters in waves; independent CTAs merged through memory fill it evenly
-    through_memory = splits > 8 or (splits > 1 and pairs * splits > CLUSTER_CTA_LIMIT)
-    return split_keys, splits, through_memory
+    shared = (16 + 256) * (head_dim + 8) * 2 + (16 * head_dim + 32) * 4 + 128 * 8      # the tensor-core kernel's, per CTA
+    slots = SM_COUNT * max(1, min(16, (227 * 1024) // (shared + 1024)))
+    total_passes = max(1, -(-max_keys // 128))
+    best, best_cost, last_splits = (128 * total_passes, 1), None, 0
+    for passes in range(1, total_passes + 1):
+        splits = -(-total_passes // passes)
+        if splits == last_splits:
+            continue                       # the same splits with longer passes: never better
+        last_splits = splits
+        ctas = pairs * splits
+        waves = -(-ctas // slots)
+        wave_mb = min(ctas, slots) * 128 * head_dim * 4 / 1e6
+        # a pass takes 1.6 to 2.3 us (by the head size) when little is in flight, 3.5 us once about
+        # 12 MB are (the latency under load), and never less than the wave's bytes at 5.8 TB/s
+        idle_us = 1.0 + head_dim / 100.0
+        pass_us = max(idle_us + (3.5 - idle_us) * min(1.0, wave_mb / 12.0), wave_mb / 5.8)
+        merge_us = 0.0 if splits == 1 else 1.0 if splits <= 8 else 1.5 + 0.085 * splits
+        cost = waves * (2.2 + passes * pass_us) + merge_us
+        if 1 < splits <= 8 and ctas > slots:
+            cost *= 1.1                    # clusters have to find room for all their CTAs at once
+        if best_cost is None or cost < best_cost:
+            best, best_cost = (128 * passes, splits), cost
+    split_keys, splits = best
+    return split_keys, splits, splits > 8
 
 
 def attention_decode(q, k_cache, v_cache, block_table, context_lens, out, heads, kv_heads, head_dim, status,
@@ -318,7 +334,7 @@ def attention_decode(q, k_cache, v_cache, block_table, context_lens, out, heads,
     R = q.shape[0]
     max_keys = block_table.shape[1] * k_cache.shape[2]
     if split_keys is None:
-        split_keys, splits, through_memory = decode_split_plan(R, kv_heads, max_keys)
+        split_keys, splits, through_memory = decode_split_plan(R, kv_heads, max_keys, head_dim)
     else:
         splits = max(1, -(-max_keys // split_keys))
         through_memory = splits > 8
@@ -360,7 +376,7 @@ def attention_decode_fused(acc, bias, cos_table, sin_table, k_cache, v_cache, bl
         raise KernelError("attention_decode_fused: bias must have one entry per column of acc")
     _rows_contiguous(block_table, "block_table")
     max_keys = block_table.shape[1] * k_cache.shape[2]
-    split_keys, splits, through_memory = decode_split_plan(R, kv_heads, max_keys)
+    split_keys, splits, through_memory = decode_split_plan(R, kv_heads, max_keys, head_dim)
     if not decode_fusable(R, heads, kv_heads, head_dim, max_keys):
         raise KernelError("attention_decode_fused: these sizes need the separate kernels (see decode_fusable)")
     scratch = None

@@ -493,8 +493,8 @@ def test_attention_decode_fused_projection_tail(status, heads, kv_heads, head_di
     acc2 = sums.clone()
     got = torch.full_like(want, float("nan"))
     assert kernels.decode_fusable(R, heads, kv_heads, head_dim, case["table"].shape[1] * page)
-    if R >= 70 or max(lengths) > 2000:
-        assert kernels.decode_split_plan(R, kv_heads, case["table"].shape[1] * page)[2]      # this case goes through memory
+    if max(lengths) > 2000:
+        assert kernels.decode_split_plan(R, kv_heads, case["table"].shape[1] * page, head_dim)[2]      # this case goes through memory
     kernels.attention_decode_fused(acc2, bias, cos, sin, k2, v2, case["table"], case["context_lens"], got, heads,
                                    kv_heads, head_dim, status)
     assert torch.equal(k2, k1) and torch.equal(v2, v1)                 # the same append, bit for bit
