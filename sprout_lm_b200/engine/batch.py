@@ -41,6 +41,9 @@ class StepContext:
     block_tables: list
     page_tokens: int
     floats: dict = field(default_factory=dict)      # extra float32 arrays staged with the batch (sampling)
+    # the longest context that the step's launches should be laid out for: the step's own, or, in a
+    # captured graph, that of the steps it is replayed for (0: max_context)
+    planned_context: int = 0
 
     @property
     def all_decode(self) -> bool:

@@ -57,7 +57,7 @@ class DecodeGraph:
     buffer that is updated in place: token ids, positions and lengths every step, block-table
     cells only where a request's table grew (or wholly, when the requests of the step changed)."""
 
-    def __init__(self, runner, requests: int, table_pages: int):
+    def __init__(self, runner, requests: int, table_pages: int, planned_context: int = 0):
         self.runner = runner
         self.requests = R = requests
         self.table_pages = table_pages
@@ -91,7 +91,8 @@ class DecodeGraph:
             logits_rows=view("logits_rows"),
             block_tables=[view(f"table{g}").view(R, table_pages) for g in range(self.groups)],
             page_tokens=runner.page_tokens,
-            floats={"temperature": view("temperature").view(torch.float32), "uniform": view("uniform").view(torch.float32)})
+            floats={"temperature": view("temperature").view(torch.float32), "uniform": view("uniform").view(torch.float32)},
+            planned_context=planned_context)
         self._seqs = None
         self._known = None                # pages of each request's tables already in the host mirror
         self.graph = None
@@ -203,10 +204,17 @@ class GraphCache:
             for table in e.seq.tables:
                 if len(table) > pages:
                     pages = len(table)
-        key = (len(entries), _round_up(pages, self.page_multiple))
+        # A graph serves the steps of its number of requests and table width whose parts lay their
+        # launches out alike: the parts say what theirs depend on (decode attention: how it
+        # divides the keys, which follows the contexts' length in steps of 128).
+        width = _round_up(pages, self.page_multiple)
+        longest = 1 + max(e.seq.length for e in entries)
+        planned = min(width * self.runner.page_tokens, _round_up(longest, 128))
+        plan = self.runner.model.decode_plan(len(entries), width * self.runner.page_tokens, planned)
+        key = (len(entries), width, plan)
         graph = self.graphs.get(key)
         if graph is None:
-            graph = self.graphs[key] = DecodeGraph(self.runner, *key)
+            graph = self.graphs[key] = DecodeGraph(self.runner, len(entries), width, planned)
         return graph
 
 
@@ -295,7 +303,10 @@ class DecodeLoop:
         self.runner = runner
         self.requests = len(entries)
         pages = max(max((len(t) for t in e.seq.tables), default=1) for e in entries)
-        self.inner = DecodeGraph(runner, self.requests, _round_up(pages, 8))
+        # one graph for all the steps: laid out for the contexts half-way through them
+        width = _round_up(pages, 8)
+        half_way = 1 + max(e.seq.length for e in entries) + max_steps // 2
+        self.inner = DecodeGraph(runner, self.requests, width, min(width * runner.page_tokens, _round_up(half_way, 128)))
         self.entries = entries
         device = runner.runtime.device
         self.history = torch.zeros((max_steps, self.requests), dtype=torch.int32, device=device)

@@ -285,12 +285,14 @@ def _check_paged(q, k_cache, v_cache, block_table, out, heads, head_dim, name):
 SM_COUNT = 148
 
 
-@functools.lru_cache(maxsize=4096)
-def decode_split_plan(requests: int, kv_heads: int, max_keys: int, head_dim: int = 64) -> tuple[int, int, bool]:
+def decode_split_plan(requests: int, kv_heads: int, max_keys: int, head_dim: int = 64,
+                      live_keys: int | None = None) -> tuple[int, int, bool]:
     """(keys per split, splits, whether scratch memory is needed) for decode attention over at
-    most ``max_keys`` keys.  A CTA takes its split in passes of 128 keys, one after the other; up
-    to 8 splits of a (request, key/value head) merge inside a thread-block cluster, more go
-    through scratch memory and a merge kernel.
+    most ``max_keys`` keys (the block tables' width), of which about ``live_keys`` are expected
+    to hold keys (a replayed graph's tables are wider than its contexts; splits beyond a
+    request's length cost next to nothing).  A CTA takes its split in passes of 128 keys, one
+    after the other; up to 8 splits of a (request, key/value head) merge inside a thread-block
+    cluster, more go through scratch memory and a merge kernel.
 
     The pick minimises a small model of the kernel's time, fitted to measurements on a B200: the
     CTAs run in waves of as many as fit the SMs at once; a wave costs a fixed start and, per
@@ -298,35 +300,45 @@ def decode_split_plan(requests: int, kv_heads: int, max_keys: int, head_dim: int
     merge costs a little inside a cluster and more through memory, growing with the splits.  So a
     small batch gets many short splits (latency), a large one few long ones (no idle waves, no
     merge kernel), and a long context as many splits as keep the SMs busy."""
-    pairs = requests * kv_heads
+    live = max_keys if live_keys is None else max(1, min(max_keys, live_keys))
+    return _decode_split_plan(requests * kv_heads, -(-max_keys // 128), -(-live // 128), head_dim)
+
+
+@functools.lru_cache(maxsize=4096)
+def _decode_split_plan(pairs: int, total_passes: int, live_passes: int, head_dim: int) -> tuple[int, int, bool]:
     shared = (16 + 256) * (head_dim + 8) * 2 + (16 * head_dim + 32) * 4 + 128 * 8      # the tensor-core kernel's, per CTA
     slots = SM_COUNT * max(1, min(16, (227 * 1024) // (shared + 1024)))
-    total_passes = max(1, -(-max_keys // 128))
-    best, best_cost, last_splits = (128 * total_passes, 1), None, 0
+    total_passes = max(1, total_passes)
+    best, best_cost, last_splits = (128 * total_passes, 1, False), None, 0
     for passes in range(1, total_passes + 1):
         splits = -(-total_passes // passes)
         if splits == last_splits:
             continue                       # the same splits with longer passes: never better
         last_splits = splits
-        ctas = pairs * splits
-        waves = -(-ctas // slots)
-        wave_mb = min(ctas, slots) * 128 * head_dim * 4 / 1e6
+        live_splits = -(-live_passes // passes)
         # a pass takes 1.6 to 2.3 us (by the head size) when little is in flight, 3.5 us once about
-        # 12 MB are (the latency under load), and never less than the wave's bytes at 5.8 TB/s
+        # 16 MB are (the latency under load), and never less than the wave's bytes at 5.8 TB/s
         idle_us = 1.0 + head_dim / 100.0
-        pass_us = max(idle_us + (3.5 - idle_us) * min(1.0, wave_mb / 12.0), wave_mb / 5.8)
-        merge_us = 0.0 if splits == 1 else 1.0 if splits <= 8 else 1.5 + 0.085 * splits
-        cost = waves * (2.2 + passes * pass_us) + merge_us
-        if 1 < splits <= 8 and ctas > slots:
-            cost *= 1.1                    # clusters have to find room for all their CTAs at once
-        if best_cost is None or cost < best_cost:
-            best, best_cost = (128 * passes, splits), cost
-    split_keys, splits = best
-    return split_keys, splits, splits > 8
+        for through_memory in (False, True):
+            if (through_memory and splits == 1) or (not through_memory and splits > 8):
+                continue
+            # the CTAs that hold a slot: a cluster is placed whole, of independent CTAs those that find keys
+            ctas = pairs * (live_splits if through_memory else splits)
+            # a cluster needs room for all its CTAs at once in one part of the GPU: larger clusters pack worse
+            room = slots if through_memory else int(slots * (1.0 - 0.06 * (splits - 1)))
+            # a last wave that is not full costs less than a full one: half-way between the two counts
+            waves = max(1.0, (-(-ctas // room) + ctas / room) / 2)
+            wave_mb = min(ctas, room) * 128 * head_dim * 4 / 1e6
+            pass_us = max(idle_us + (3.5 - idle_us) * min(1.0, wave_mb / 16.0), wave_mb / 5.8)
+            merge_us = 0.0 if splits == 1 else 3.5 + 0.085 * splits if through_memory else 1.0
+            cost = waves * (2.2 + min(passes, live_passes) * pass_us) + merge_us
+            if best_cost is None or cost < best_cost:
+                best, best_cost = (128 * -(-total_passes // splits), splits, through_memory), cost
+    return best
 
 
 def attention_decode(q, k_cache, v_cache, block_table, context_lens, out, heads, kv_heads, head_dim, status,
-                     split_keys=None, scratch=None):
+                     split_keys=None, scratch=None, live_keys=None):
     """One query token per request over its pages (bfloat16, float32 softmax): keys are split
     among CTAs; up to 8 splits merge inside a thread-block cluster, more (or a given
     ``scratch``) go through float32 scratch memory and a merge kernel."""
@@ -334,7 +346,7 @@ def attention_decode(q, k_cache, v_cache, block_table, context_lens, out, heads,
     R = q.shape[0]
     max_keys = block_table.shape[1] * k_cache.shape[2]
     if split_keys is None:
-        split_keys, splits, through_memory = decode_split_plan(R, kv_heads, max_keys, head_dim)
+        split_keys, splits, through_memory = decode_split_plan(R, kv_heads, max_keys, head_dim, live_keys)
     else:
         splits = max(1, -(-max_keys // split_keys))
         through_memory = splits > 8
@@ -357,7 +369,7 @@ def decode_fusable(requests: int, heads: int, kv_heads: int, head_dim: int, max_
 
 
 def attention_decode_fused(acc, bias, cos_table, sin_table, k_cache, v_cache, block_table, context_lens, out,
-                           heads, kv_heads, head_dim, status):
+                           heads, kv_heads, head_dim, status, live_keys=None):
     """Decode attention with the q/k/v projection's tail folded in.  ``acc`` holds, for each
     request's new token, the float32 sums [requests, (heads + 2 kv_heads) * head_dim] of a split-K
     product; the kernel adds ``bias``, rotates q and k by the position context_lens - 1 (tables
@@ -376,7 +388,7 @@ def attention_decode_fused(acc, bias, cos_table, sin_table, k_cache, v_cache, bl
         raise KernelError("attention_decode_fused: bias must have one entry per column of acc")
     _rows_contiguous(block_table, "block_table")
     max_keys = block_table.shape[1] * k_cache.shape[2]
-    split_keys, splits, through_memory = decode_split_plan(R, kv_heads, max_keys, head_dim)
+    split_keys, splits, through_memory = decode_split_plan(R, kv_heads, max_keys, head_dim, live_keys)
     if not decode_fusable(R, heads, kv_heads, head_dim, max_keys):
         raise KernelError("attention_decode_fused: these sizes need the separate kernels (see decode_fusable)")
     scratch = None
@@ -439,7 +451,7 @@ def paged_attention(q, cache, ctx, out, heads, kv_heads, head_dim, status):
     if q.dtype == torch.bfloat16:
         if ctx.max_q_len == 1 and heads // kv_heads <= 16:
             return attention_decode(q, cache.k, cache.v, cache.block_table, ctx.context_lens, out,
-                                    heads, kv_heads, head_dim, status)
+                                    heads, kv_heads, head_dim, status, live_keys=ctx.planned_context or ctx.max_context)
         if head_dim <= 128:
             variant = PREFILL_VARIANT
             if variant == "tcgen05" and not load_library().sprout_attention_prefill_tc_supported(head_dim, cache.k.shape[2], out.stride(0)):

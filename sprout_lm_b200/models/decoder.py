@@ -24,6 +24,7 @@ class DecoderModel:
         self.final_norm = build_part("norm", spec.final_norm)
         self.head = build_part("head", spec.head)
         self.runtime: Runtime | None = None
+        self._decode_plans: dict = {}
 
     # ------------------------------------------------------------------ weights
     def parts(self):
@@ -59,6 +60,16 @@ class DecoderModel:
     def state_specs(self):
         """One StateSpec (or None) per layer."""
         return [block.mixer.state_spec() for block in self.blocks]
+
+    def decode_plan(self, requests: int, max_keys: int, planned_context: int):
+        """The parts' plans for a step of one token per request (see ``Part.decode_plan``)."""
+        key = (requests, max_keys, planned_context)
+        plan = self._decode_plans.get(key)
+        if plan is None:
+            if len(self._decode_plans) > 4096:
+                self._decode_plans.clear()
+            plan = self._decode_plans[key] = tuple(block.mixer.decode_plan(*key) for block in self.blocks)
+        return plan
 
     # ------------------------------------------------------------------ one step
     def forward(self, ctx, storage) -> torch.Tensor:

@@ -43,6 +43,13 @@ class PagedGQAttention(Part):
     def state_spec(self):
         return None
 
+    def decode_plan(self, requests: int, max_keys: int, planned_context: int):
+        """How the decode kernel divides the keys among CTAs: it follows the contexts' length, not
+        only the block tables' width."""
+        if self.heads // self.kv_heads > 16:
+            return None
+        return kernels.decode_split_plan(requests, self.kv_heads, max_keys, self.head_dim, planned_context)
+
     # ---- weights
     def tensor_decls(self):
         q_width, kv_width = self.heads * self.head_dim, self.kv_heads * self.head_dim
@@ -101,7 +108,7 @@ class PagedGQAttention(Part):
                 # one token per request: bias, rotation and the cache append happen inside the attention kernel
                 kernels.attention_decode_fused(acc, self.qkv.bias, cos, sin, cache.k, cache.v, cache.block_table,
                                                ctx.context_lens, attended, self.heads, self.kv_heads, self.head_dim,
-                                               self.runtime.status)
+                                               self.runtime.status, live_keys=ctx.planned_context or ctx.max_context)
                 self.out.forward(attended, residual=x)
                 return
             qkv = torch.empty((tokens, self.qkv.out_features), dtype=h.dtype, device=h.device)

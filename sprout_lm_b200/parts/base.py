@@ -169,3 +169,9 @@ class Part:
 
     def load(self, source: WeightSource) -> None:
         pass
+
+    def decode_plan(self, requests: int, max_keys: int, planned_context: int):
+        """What this part's launches for a step of one token per request depend on beyond the
+        number of requests and the block tables' width (something hashable, or None): a captured
+        step is replayed only for steps with the same plan."""
+        return None

@@ -1,0 +1,62 @@
+"""How decode attention divides a request's keys among CTAs (no GPU needed: the plan is host
+arithmetic), and that a captured decode step is keyed by it."""
+import pytest
+
+from sprout_lm_b200 import kernels
+
+
+@pytest.mark.parametrize("head_dim,kv_heads", [(16, 1), (64, 2), (128, 4), (128, 8)])
+@pytest.mark.parametrize("requests", [1, 3, 8, 33, 64, 200])
+def test_plan_covers_every_key(head_dim, kv_heads, requests):
+    for max_keys in (16, 128, 640, 1000, 4096, 33000):
+        for live in (None, 1, max_keys // 2, max_keys, 10 * max_keys):
+            split_keys, splits, through_memory = kernels.decode_split_plan(requests, kv_heads, max_keys, head_dim, live)
+            assert split_keys % 128 == 0 and split_keys >= 128
+            assert split_keys * splits >= max_keys                  # every key has a split
+            assert split_keys * (splits - 1) < max(max_keys, 128)   # and no split is wholly beyond the table
+            assert through_memory or splits <= 8                    # a cluster holds at most 8 CTAs
+            assert not (through_memory and splits == 1)             # nothing to merge
+
+
+def test_plan_follows_the_batch_and_the_context():
+    # a small batch with a short context: many short splits (latency)
+    assert kernels.decode_split_plan(8, 2, 640, 64)[0] == 128
+    # a large batch of wide heads: one CTA per (request, head) takes the whole context, no merge
+    assert kernels.decode_split_plan(64, 4, 640, 128) == (640, 1, False)
+    # one request with a long context: many splits, merged through memory
+    split_keys, splits, through_memory = kernels.decode_split_plan(1, 2, 32768, 64)
+    assert through_memory and 16 <= splits <= 128
+    # a wide table with short contexts is planned for the contexts
+    assert kernels.decode_split_plan(64, 4, 4096, 128, 600) == kernels.decode_split_plan(64, 4, 4096, 128, 640)
+    assert kernels.decode_split_plan(64, 4, 4096, 128, 600) != kernels.decode_split_plan(64, 4, 4096, 128, 4096)
+
+
+def test_captured_decode_steps_are_keyed_by_the_parts_plans(monkeypatch):
+    """A graph is reused while the parts lay their launches out alike, and only then."""
+    from types import SimpleNamespace
+    from sprout_lm_b200.engine import graphs
+
+    made = []
+
+    class FakeGraph:
+        def __init__(self, runner, requests, table_pages, planned_context=0):
+            made.append((requests, table_pages, planned_context))
+
+    monkeypatch.setattr(graphs, "DecodeGraph", FakeGraph)
+    asked = []
+
+    def decode_plan(requests, max_keys, planned):
+        asked.append((requests, max_keys, planned))
+        return ("short",) if planned <= 256 else ("long",)
+
+    runner = SimpleNamespace(page_tokens=16, model=SimpleNamespace(decode_plan=decode_plan))
+    cache = graphs.GraphCache(runner, page_multiple=64)
+    entry = lambda length: SimpleNamespace(seq=SimpleNamespace(length=length, tables=[[0] * (-(-(length + 1) // 16))]))
+    first = cache.get([entry(100), entry(40)])
+    assert cache.get([entry(101), entry(41)]) is first            # same plan: same graph
+    assert asked[0] == (2, 1024, 128) and asked[1] == (2, 1024, 128)
+    assert cache.get([entry(200), entry(41)]) is first            # planned for 256 keys: still the short plan
+    other = cache.get([entry(300), entry(41)])
+    assert other is not first and made == [(2, 64, 128), (2, 64, 384)]
+    assert cache.get([entry(100), entry(40), entry(7)]) is not first      # another number of requests
+    assert cache.get([entry(1030), entry(40)]) not in (first, other)      # a wider table

@@ -457,8 +457,8 @@ def test_attention_decode_split_keys(status, heads, kv_heads, head_dim, page, le
 
 @pytest.mark.parametrize("rotate", [False, True])
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page,lengths", DECODE_CASES[:6] + [
-    (14, 2, 64, 16, [37 + 13 * i for i in range(70)]),        # a large batch: independent CTAs, merged through memory
-    (4, 2, 64, 16, [3000, 1500]),                              # more than 8 splits: through memory too
+    (14, 2, 64, 16, [37 + 13 * i for i in range(70)]),        # a large batch: longer splits, few per request
+    (4, 2, 64, 16, [6000, 1500]),                              # more than 8 splits: through memory too
 ])
 def test_attention_decode_fused_projection_tail(status, heads, kv_heads, head_dim, page, lengths, rotate):
     """The decode kernel that also finishes the projection: the new token's q, k, v arrive as
@@ -493,7 +493,7 @@ def test_attention_decode_fused_projection_tail(status, heads, kv_heads, head_di
     acc2 = sums.clone()
     got = torch.full_like(want, float("nan"))
     assert kernels.decode_fusable(R, heads, kv_heads, head_dim, case["table"].shape[1] * page)
-    if max(lengths) > 2000:
+    if max(lengths) > 5000:
         assert kernels.decode_split_plan(R, kv_heads, case["table"].shape[1] * page, head_dim)[2]      # this case goes through memory
     kernels.attention_decode_fused(acc2, bias, cos, sin, k2, v2, case["table"], case["context_lens"], got, heads,
                                    kv_heads, head_dim, status)
