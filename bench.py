@@ -26,6 +26,7 @@ engine runs on one GPU.  ``--impl reference`` reports why the reference cannot r
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -365,6 +366,10 @@ def timed_serving(shape: str, layers: int, requests: int, workload: str = "mixed
                 tokens[:1024] = prefix
             engine.add(f"{tag}{i}", tokens, new_tokens, ignore_eos=True)
         times, kinds, preempted = [], {"prefill": 0, "mixed": 0, "decode": 0}, 0
+        # the prompts are millions of Python integers: a full collection walking them in the middle
+        # of the run would cost hundreds of milliseconds; collect now and set them aside
+        gc.collect()
+        gc.freeze()
         torch.cuda.synchronize()
         begin = time.perf_counter()
         while engine.pending:
@@ -376,6 +381,7 @@ def timed_serving(shape: str, layers: int, requests: int, workload: str = "mixed
             preempted += sum(1 for e in report["events"] if e["type"] == "preempted")
         torch.cuda.synchronize()
         seconds = time.perf_counter() - begin
+        gc.unfreeze()
         engine.runner.check_status()
         results = [engine.result(f"{tag}{i}") for i in range(requests)]
         assert all(len(r["output"]) == new_tokens for r in results)
@@ -428,6 +434,64 @@ def timed_attention(tokens: int, shape: str = "0.5b", repeats: int = 20) -> dict
         us = begin.elapsed_time(end) * 1000 / repeats
         result[f"{variant}_us"] = round(us, 1)
         result[f"{variant}_tflops"] = round(flops / us / 1e6, 1)
+    assert int(status.item()) == 0
+    return result
+
+
+def timed_decode_attention(shape: str, batch: int, context: int, repeats: int = 10) -> dict:
+    """The decode attention kernel alone (one query token per request, ``context`` keys each, pages
+    scattered over the pool, block tables as wide as a replayed decode graph's): with the split
+    plan the engine would pick, and with other split sizes for comparison.  Bytes are the keys and
+    values read."""
+    import torch
+    from sprout_lm_b200 import kernels
+    heads, kv_heads = SHAPES[shape]["num_attention_heads"], SHAPES[shape]["num_key_value_heads"]
+    head_dim, page = SHAPES[shape]["hidden_size"] // heads, 16
+    width = -(-(-(-context // page)) // 64) * 64
+    total = batch * width
+    g = torch.Generator(device="cuda").manual_seed(0)
+    k = torch.randn(total, kv_heads, page, head_dim, device="cuda", generator=g).to(torch.bfloat16)
+    v = torch.randn(total, kv_heads, page, head_dim, device="cuda", generator=g).to(torch.bfloat16)
+    table = torch.randperm(total, device="cuda", generator=g).to(torch.int32).reshape(batch, width)
+    lens = torch.full((batch,), context, dtype=torch.int32, device="cuda")
+    q = torch.randn(batch, heads * head_dim, device="cuda", generator=g).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    planned = -(-context // 128) * 128
+
+    def replayed(split_keys):
+        call = lambda: kernels.attention_decode(q, k, v, table, lens, out, heads, kv_heads, head_dim, status,
+                                                split_keys=split_keys, live_keys=planned)
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        graph, stream = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(graph, stream=stream):
+                for _ in range(repeats):
+                    call()
+        graph.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(5):
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            graph.replay()
+            end.record()
+            torch.cuda.synchronize()
+            times.append(begin.elapsed_time(end) * 1000 / repeats)
+        return statistics.median(times)
+
+    megabytes = 2.0 * batch * context * kv_heads * head_dim * 2 / 1e6
+    plan = kernels.decode_split_plan(batch, kv_heads, width * page, head_dim, planned)
+    us = replayed(None)
+    result = {"impl": "ours", "only": "decode-attention", "shape": shape, "batch": batch, "context": context,
+              "heads": heads, "kv_heads": kv_heads, "head_dim": head_dim, "table_keys": width * page,
+              "plan": {"split_keys": plan[0], "splits": plan[1], "through_memory": plan[2]},
+              "us": round(us, 1), "gbs": round(megabytes / us * 1e3), "mb": round(megabytes, 1), "other_splits_us": {}}
+    for passes in (1, 2, 4, 8, 16, 32, width * page // 128):
+        if passes * 128 <= width * page and width * page // (passes * 128) <= 256:
+            result["other_splits_us"][str(passes * 128)] = round(replayed(passes * 128), 1)
     assert int(status.item()) == 0
     return result
 
@@ -500,6 +564,8 @@ def run(args) -> dict:
         return timed_attention(args.tokens, args.shape)
     if args.only == "gemm":
         return timed_gemms(args.tokens, args.shape)
+    if args.only == "decode-attention":
+        return timed_decode_attention(args.shape, args.batch, args.tokens)
     if args.only == "serve":
         return timed_serving(args.shape, args.layers, args.requests, args.workload)
     if args.only == "all" and args.shape != "0.5b":
@@ -568,13 +634,13 @@ def main() -> int:
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
-    parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate", "attention", "gemm", "serve"], default="all",
+    parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate", "attention", "decode-attention", "gemm", "serve"], default="all",
                         help="measure one part only (for profiling captures); the JSON line then holds that part")
     parser.add_argument("--shape", choices=sorted(SHAPES), default="0.5b", help="with --only: the model's sizes")
     parser.add_argument("--requests", type=int, default=64, help="with --only serve: requests of the workload")
     parser.add_argument("--workload", choices=["mixed", "shared-prefix"], default="mixed",
                         help="with --only serve: mixed prompt lengths, or long prompts that share a prefix in a pool too small for all")
-    parser.add_argument("--tokens", type=int, default=2048, help="with --only attention or gemm: tokens of the one request")
+    parser.add_argument("--tokens", type=int, default=2048, help="with --only attention or gemm: tokens of the one request; with decode-attention: the context of each request")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))

@@ -229,17 +229,20 @@ class StepGraphs:
     long prompts at a fixed chunk size makes such steps; the mixed steps of a busy server rarely
     repeat their sizes, and a capture costs milliseconds and holds its own activations, so sizes
     must have come three times first, a few captures are kept, and steps that ask for many
-    logits rows are not captured."""
+    logits rows are not captured.  When the captures are full, a new shape takes the place of the
+    least used one only once it has been used twice as often (uses are halved now and then, so
+    the count follows the recent past): shapes that take turns do not capture over one another."""
 
     def __init__(self, runner, limit: int = 4, min_tokens: int = 128, max_rows: int = 64, page_multiple: int = 64,
                  after: int = 3):
         self.runner = runner
         self.limit, self.min_tokens, self.max_rows, self.page_multiple = limit, min_tokens, max_rows, page_multiple
         self.after = after
-        self.seen: dict = {}              # key -> times run eagerly
-        self.captured: dict = {}          # key -> (graph, logits, tokens, device buffer), in order of last use
+        self.seen: dict = {}              # key -> times used of late (run eagerly or replayed)
+        self.captured: dict = {}          # key -> (graph, logits, tokens, device buffer)
         self.enabled = True
         self.replays = 0
+        self._steps = 0
 
     def plan(self, entries, sample: bool):
         """(key, table width) for a step that may be captured, else (None, None)."""
@@ -261,22 +264,25 @@ class StepGraphs:
         device and valid until the next step of the same sizes."""
         runner = self.runner
         buffer = runner.stager.device_buffer
+        self._steps += 1
+        if self._steps % 1024 == 0:       # the counts follow the recent past
+            self.seen = {k: n // 2 for k, n in self.seen.items() if n >= 2 or k in self.captured}
+        uses = self.seen[key] = self.seen.get(key, 0) + 1
         held = self.captured.get(key)
         if held is not None and held[3] is buffer:
-            self.captured[key] = self.captured.pop(key)          # most recently used last
             held[0].replay()
             self.replays += 1
             return held[1], held[2]
         logits, tokens = self._forward(ctx, sample)
-        if len(self.seen) > 4096:
-            self.seen.clear()
-        self.seen[key] = self.seen.get(key, 0) + 1
-        if self.seen[key] >= self.after:
+        if held is not None:
+            del self.captured[key]        # recorded for another device buffer (the stager grew)
+        if uses >= self.after:
+            if len(self.captured) >= self.limit:
+                least = min(self.captured, key=lambda k: self.seen.get(k, 0))
+                if uses < 2 * max(1, self.seen.get(least, 0)):
+                    return logits, tokens
+                del self.captured[least]
             # the step has run; record the same launches for the next time these sizes come
-            if held is not None:
-                del self.captured[key]
-            while len(self.captured) >= self.limit:
-                self.captured.pop(next(iter(self.captured)))
             graph = torch.cuda.CUDAGraph()
             with guarded_capture(graph):
                 recorded = self._forward(ctx, sample)

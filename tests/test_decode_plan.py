@@ -60,3 +60,42 @@ def test_captured_decode_steps_are_keyed_by_the_parts_plans(monkeypatch):
     assert other is not first and made == [(2, 64, 128), (2, 64, 384)]
     assert cache.get([entry(100), entry(40), entry(7)]) is not first      # another number of requests
     assert cache.get([entry(1030), entry(40)]) not in (first, other)      # a wider table
+
+
+def test_prefill_step_captures_do_not_take_turns_evicting_one_another(monkeypatch):
+    """Six step shapes coming round and round with room for four captures: four are captured once
+    and replayed from then on; the other two run eagerly instead of capturing over them."""
+    import contextlib
+    from types import SimpleNamespace
+    from sprout_lm_b200.engine import graphs
+
+    captures = []
+
+    class FakeCudaGraph:
+        def replay(self):
+            pass
+
+    monkeypatch.setattr(graphs.torch.cuda, "CUDAGraph", FakeCudaGraph)
+    monkeypatch.setattr(graphs, "guarded_capture", lambda graph: contextlib.nullcontext())
+    runner = SimpleNamespace(stager=SimpleNamespace(device_buffer=object()), forward=lambda ctx: None)
+    steps = graphs.StepGraphs(runner, limit=4, after=3)
+    original = steps._forward
+    eager = []
+
+    def forward(ctx, sample):
+        eager.append(ctx)
+        return original(ctx, sample)
+
+    steps._forward = forward
+    for round_ in range(30):
+        for shape in range(6):
+            before = len(steps.captured)
+            steps.run(("shape", shape), shape, False)
+            if len(steps.captured) > before:
+                captures.append(shape)
+    assert sorted(captures) == [0, 1, 2, 3]                     # each captured once, nothing captured over
+    assert steps.replays == 4 * (30 - 3)
+    # a shape that comes far more often than a captured one does take its place
+    for _ in range(200):
+        steps.run(("shape", 5), 5, False)
+    assert ("shape", 5) in steps.captured and len(steps.captured) == 4
