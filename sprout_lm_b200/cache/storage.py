@@ -48,19 +48,29 @@ class CapacityError(RuntimeError):
     """The cache pool asked for does not fit the device's free memory."""
 
 
-class CacheStorage:
-    RESERVE_BYTES = 1 << 30          # left free for activations, logits and graph pools
+RESERVE_BYTES = 1 << 30              # left free for activations, logits and graph pools
 
+
+def check_capacity(model, slot_group: list[int], num_pages, page_tokens: int) -> None:
+    """Refuse a pool that does not fit the device's free memory, before the host tables of its
+    pages are built (a mistyped page count must cost neither minutes nor host memory).
+    ``num_pages`` is one count for every group or a count per group."""
+    runtime = model.runtime
+    item = torch.empty((), dtype=runtime.dtype).element_size()
+    counts = num_pages if not isinstance(num_pages, int) else [num_pages] * (max(slot_group, default=0) + 1)
+    need = sum(2 * counts[slot_group[slot]] * spec.kv_heads * page_tokens * spec.head_dim * item
+               for slot, spec in enumerate(model.cache_specs()) if spec is not None)
+    free, _ = torch.cuda.mem_get_info(runtime.device)
+    if need + RESERVE_BYTES > free:
+        raise CapacityError(f"the cache pool needs {need / 2**30:.2f} GiB ({max(counts)} pages of "
+                            f"{page_tokens} tokens) but only {free / 2**30:.2f} GiB of device memory is free "
+                            f"(1 GiB is kept for activations); use fewer pages")
+
+
+class CacheStorage:
     def __init__(self, model, manager: CacheManager, slot_group: list[int]):
         runtime = model.runtime
-        item = torch.empty((), dtype=runtime.dtype).element_size()
-        need = sum(2 * manager.pools[slot_group[slot]].num_pages * spec.kv_heads * manager.page_tokens * spec.head_dim * item
-                   for slot, spec in enumerate(model.cache_specs()) if spec is not None)
-        free, _ = torch.cuda.mem_get_info(runtime.device)
-        if need + self.RESERVE_BYTES > free:
-            raise CapacityError(f"the cache pool needs {need / 2**30:.2f} GiB ({manager.pools[0].num_pages} pages of "
-                                f"{manager.page_tokens} tokens) but only {free / 2**30:.2f} GiB of device memory is free "
-                                f"(1 GiB is kept for activations); use fewer pages")
+        check_capacity(model, slot_group, [pool.num_pages for pool in manager.pools], manager.page_tokens)
         self.manager = manager
         self.slot_group = slot_group
         self.page_tokens = manager.page_tokens

@@ -13,7 +13,7 @@ import torch
 
 from .. import kernels
 from ..cache.manager import CacheManager
-from ..cache.storage import CacheStorage, plan_groups, state_slot_count
+from ..cache.storage import CacheStorage, check_capacity, plan_groups, state_slot_count
 from .batch import BatchStager, StepContext, StepEntry
 
 
@@ -29,6 +29,7 @@ class ModelRunner:
         self.model = model
         self.runtime = model.runtime
         groups, slot_group = plan_groups(model)
+        check_capacity(model, slot_group, num_pages, page_tokens)
         self.manager = CacheManager(groups, num_pages, page_tokens,
                                     state_slots=state_slot_count(model, max_requests),
                                     prefix_caching=prefix_caching)
