@@ -15,7 +15,7 @@ import gc
 
 import torch
 
-from .. import kernels
+from .. import kernels, sampling
 from .batch import StepContext
 
 
@@ -158,8 +158,7 @@ class DecodeGraph:
 
     def _forward(self, ctx):
         logits = self.runner.model.forward(ctx, self.runner.storage)
-        tokens = torch.empty(self.requests, dtype=torch.int32, device=logits.device)
-        kernels.sample(logits, tokens, self.runner.runtime.status, ctx.floats["temperature"], ctx.floats["uniform"])
+        tokens = sampling.sample(logits, self.runner.runtime.status, ctx.floats["temperature"], ctx.floats["uniform"])
         return logits, tokens
 
     def run(self, entries, temperatures, uniforms) -> list:
@@ -294,8 +293,7 @@ class StepGraphs:
         logits = runner.forward(ctx)
         tokens = None
         if sample and logits is not None:
-            tokens = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-            kernels.sample(logits, tokens, runner.runtime.status, ctx.floats["temperature"], ctx.floats["uniform"])
+            tokens = sampling.sample(logits, runner.runtime.status, ctx.floats["temperature"], ctx.floats["uniform"])
         return logits, tokens
 
 

@@ -17,11 +17,11 @@ tokens; only token ids come back from the device.
 """
 from __future__ import annotations
 
-import hashlib
 from dataclasses import asdict, dataclass, field
 
 import numpy as np
 
+from ..sampling import uniform_for
 from .batch import StepEntry
 
 
@@ -98,13 +98,6 @@ class StepReport(dict):
     def items(self):
         self.resolve()
         return super().items()
-
-
-def uniform_for(seed: int, request_id: str, index: int) -> float:
-    """The uniform number in [0, 1) that draws output token ``index`` of a request: a function of
-    (seed, request id, index) alone, so batching, chunking and recomputation cannot change it."""
-    digest = hashlib.blake2b(f"{seed}:{request_id}:{index}".encode(), digest_size=8).digest()
-    return (int.from_bytes(digest, "little") >> 40) / float(1 << 24)
 
 
 class Engine:

@@ -11,7 +11,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from .. import kernels
+from .. import kernels, sampling
 from ..cache.manager import CacheManager
 from ..cache.storage import CacheStorage, check_capacity, plan_groups, state_slot_count
 from .batch import BatchStager, StepContext, StepEntry
@@ -149,8 +149,7 @@ class ModelRunner:
             logits = self.forward(ctx)
             tokens = None
             if logits is not None:
-                tokens = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-                kernels.sample(logits, tokens, self.runtime.status, ctx.floats["temperature"], ctx.floats["uniform"])
+                tokens = sampling.sample(logits, self.runtime.status, ctx.floats["temperature"], ctx.floats["uniform"])
         for e in entries:
             e.seq.length += len(e.tokens)
             self.manager.trim(e.seq)
@@ -191,6 +190,4 @@ class ModelRunner:
             return torch.tensor(list(values), dtype=torch.float32).to(logits.device, non_blocking=True)
         if temperatures is not None and not isinstance(temperatures, torch.Tensor) and not any(temperatures):
             temperatures = uniforms = None
-        out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-        kernels.sample(logits, out, self.runtime.status, on_device(temperatures), on_device(uniforms))
-        return out
+        return sampling.sample(logits, self.runtime.status, on_device(temperatures), on_device(uniforms))
