@@ -89,7 +89,7 @@ class ClockSampler:
     def start(self):
         try:
             self.process = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
-                                             "--format=csv,noheader,nounits", "-lms", "100"],
+                                             "--format=csv,noheader,nounits", "-lms", "20"],
                                             stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             return
@@ -212,7 +212,8 @@ def ablation(model, batch: int, prompt_len: int, steps: int, warmup: int) -> dic
     from sprout_lm_b200.engine.batch import StepEntry
     from sprout_lm_b200.engine.step import ModelRunner
     real = {name: getattr(kernels, name) for name in ("attention_decode", "attention_decode_fused", "rmsnorm", "rope_append",
-                                                      "gemm_bf16", "sample")}
+                                                      "gemm_bf16", "sample", "ffn_decode", "linear_decode")}
+    linear = real["linear_decode"]
     gemm = real["gemm_bf16"]
     hidden, inter = model.spec.hidden_size, model.blocks[0].feed_forward.intermediate_size
     qkv_rows = model.blocks[0].mixer.qkv.out_features
@@ -233,6 +234,10 @@ def ablation(model, batch: int, prompt_len: int, steps: int, warmup: int) -> dic
         "gemm_down": {"gemm_bf16": gemm_without(lambda w, kw: tuple(w.shape) == (hidden, inter))},
         "gemm_lm_head": {"gemm_bf16": gemm_without(lambda w, kw: w.shape[0] == model.spec.vocab_size)},
         "sample": {"sample": lambda *a, **k: None},
+        # the small-batch kernels (they take the place of the norms and of every product but the head at up to 8 tokens)
+        "ffn_decode": {"ffn_decode": lambda *a, **k: None},
+        "linear_norm_qkv": {"linear_decode": lambda w, out, st, a=None, norm=None: None if norm is not None else linear(w, out, st, a=a)},
+        "linear_o": {"linear_decode": lambda w, out, st, a=None, norm=None: None if a is not None else linear(w, out, st, norm=norm)},
         "all_gemms": {"gemm_bf16": lambda *a, **k: None},
     }
     out = {}
@@ -288,18 +293,21 @@ def timed_e2e(model, batch: int, prompt_len: int, steps: int, warmup: int, rng):
     torch.cuda.synchronize()
     before = dict(engine.runner.stats)
     start = time.perf_counter()
-    produced = 0
+    produced, marks = 0, [start]
     for _ in range(steps):
         report = engine.step()
         produced += sum(1 for e in report["events"] if e["type"] == "token")
+        marks.append(time.perf_counter())       # the step's tokens are on the host here
     torch.cuda.synchronize()
     seconds = time.perf_counter() - start
+    per_step = sorted((b - a) * 1000 for a, b in zip(marks, marks[1:]))
     engine.runner.check_status()
     assert produced == batch * steps
     h2d = (engine.runner.stats["h2d_bytes"] - before["h2d_bytes"]) // steps
     d2h = (engine.runner.stats["d2h_bytes"] - before["d2h_bytes"]) // steps
     return {"value": produced / seconds, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-            "ms_per_step": seconds * 1000 / steps}
+            "ms_per_step": seconds * 1000 / steps, "p50_ms": per_step[len(per_step) // 2],
+            "p95_ms": per_step[min(len(per_step) - 1, int(len(per_step) * 0.95))]}
 
 
 def timed_prefill(runner, tokens: int, rng, repeats: int = 5):
@@ -596,8 +604,7 @@ def run(args) -> dict:
                 "gbs": round(step_bytes / (main["ms_per_step"] / 1000) / 1e9, 1)}
     points = {}
     for b in (1, 64):
-        side_steps = min(args.steps, 64)
-        points[f"decode_b{b}"] = round(timed_decode(runner, b, prompt_len, side_steps, args.warmup, rng)["tokens_per_s"], 1)
+        points[f"decode_b{b}"] = round(timed_decode(runner, b, prompt_len, args.steps, args.warmup, rng)["tokens_per_s"], 1)
     prefill_ms = timed_prefill(runner, 2048, rng)
     flops = prefill_flops(cfg, 2048)
     e2e = timed_e2e(model, batch, prompt_len, args.steps, args.warmup, rng)
@@ -629,7 +636,7 @@ def run(args) -> dict:
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--batch", type=int, default=8)

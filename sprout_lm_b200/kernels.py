@@ -42,6 +42,10 @@ _SIGNATURES = {
     "sprout_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, ctypes.c_longlong, _P, _P, _P],
     "sprout_attention_prefill_tc_supported": [_I, _I, _I],
     "sprout_gemm_bf16": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_ffn_decode": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _P],
+    "sprout_ffn_decode_supported": [_I, _I, _I],
+    "sprout_linear_decode": [_P, _I, _P, _P, _F, _P, _P, _I, _I, _I, _I, _P, _P],
+    "sprout_linear_decode_supported": [_I, _I, _I],
 }
 
 _lock = threading.Lock()
@@ -266,6 +270,69 @@ def gemm_bf16(a, weight, out, status, bias=None, residual=None, orientation=0, s
     _run("sprout_gemm_bf16", _ptr(a, "a"), _ptr(weight, "weight"), _ptr(bias, "bias", torch.float32, True),
          _ptr(out, "out"), _dtype_code(out.dtype), 2 if swiglu else (1 if residual is not None else 0), M, N, K, a.stride(0),
          out.stride(0), orientation, split_k, _ptr(status, "status", torch.int32), _stream())
+
+
+def linear_decode_supported(tokens: int, out_features: int, in_features: int) -> bool:
+    """Whether ``linear_decode`` takes these sizes: 1..8 tokens, sizes that are multiples of 16, a
+    matrix small enough for light CTAs."""
+    lib = _lib or load_library()
+    return bool(lib.sprout_linear_decode_supported(tokens, out_features, in_features))
+
+
+def linear_decode(weight, out, status, a=None, norm=None):
+    """out += input @ weight.T for up to 8 tokens, added with atomics into the float32 ``out``
+    [tokens, N] (the residual stream, or a zeroed workspace).  The input is ``a`` (bfloat16
+    [tokens, K]) or ``norm = (x, gain, eps)``: the RMSNorm of the float32 rows ``x``, computed
+    inside the kernel."""
+    _rows_contiguous(out, "out")
+    if weight.dim() != 2 or not weight.is_contiguous() or weight.dtype != torch.bfloat16 or out.dtype != torch.float32:
+        raise KernelError("linear_decode: weight must be contiguous bfloat16 [N, K], out float32")
+    N, K = weight.shape
+    T = out.shape[0]
+    if out.shape[1] != N:
+        raise KernelError(f"linear_decode: out {tuple(out.shape)} does not fit weight {tuple(weight.shape)}")
+    if norm is not None:
+        x, gain, eps = norm
+        if tuple(x.shape) != (T, K) or not x.is_contiguous() or gain.numel() != K:
+            raise KernelError("linear_decode: x must be contiguous [tokens, K] and gain have K entries")
+        _run("sprout_linear_decode", None, 0, _ptr(x, "x", torch.float32), _ptr(gain, "gain", torch.float32), float(eps),
+             _ptr(weight, "weight"), _ptr(out, "out"), out.stride(0), T, N, K, _ptr(status, "status", torch.int32), _stream())
+        return
+    _rows_contiguous(a, "a")
+    if tuple(a.shape) != (T, K) or a.dtype != torch.bfloat16:
+        raise KernelError(f"linear_decode: a must be bfloat16 [{T}, {K}], got {tuple(a.shape)} {a.dtype}")
+    _run("sprout_linear_decode", _ptr(a, "a"), a.stride(0), None, None, 0.0, _ptr(weight, "weight"), _ptr(out, "out"),
+         out.stride(0), T, N, K, _ptr(status, "status", torch.int32), _stream())
+
+
+def ffn_decode_supported(tokens: int, hidden: int, intermediate: int) -> bool:
+    """Whether ``ffn_decode`` takes these sizes: 1..8 tokens, sizes that are multiples of 16, and a
+    layer small enough for every CTA to hold its share of the two matrices in shared memory."""
+    lib = _lib or load_library()
+    return bool(lib.sprout_ffn_decode_supported(tokens, hidden, intermediate))
+
+
+def ffn_decode(x, gain, eps, w_gate_up, w_down, act, sync, status):
+    """x += W_down (silu(W_gate h) * W_up h) with h = rmsnorm(x, gain, eps), for up to 8 tokens,
+    in one kernel (norm, both products, activation and residual sum).
+
+    ``x`` float32 [tokens, hidden], changed in place; ``w_gate_up`` bfloat16 [2 * intermediate,
+    hidden] with gate and up rows interleaved in blocks of 8; ``w_down`` bfloat16 [hidden,
+    intermediate]; ``act`` bfloat16 scratch [tokens, intermediate]; ``sync`` two int32 words
+    that were zero before the first call (the kernel leaves them zero)."""
+    if x.dim() != 2 or not x.is_contiguous() or not w_gate_up.is_contiguous() or not w_down.is_contiguous() \
+            or not act.is_contiguous():
+        raise KernelError("ffn_decode: x, the weights and act must be contiguous")
+    T, H = x.shape
+    inter = w_down.shape[1]
+    if tuple(w_gate_up.shape) != (2 * inter, H) or w_down.shape[0] != H or gain.numel() != H \
+            or act.shape[0] < T or act.shape[1] != inter or sync.numel() < 2:
+        raise KernelError(f"ffn_decode: shapes do not fit: x {tuple(x.shape)}, gate/up {tuple(w_gate_up.shape)}, "
+                          f"down {tuple(w_down.shape)}, act {tuple(act.shape)}")
+    _run("sprout_ffn_decode", _ptr(x, "x", torch.float32), _ptr(gain, "gain", torch.float32),
+         _ptr(w_gate_up, "w_gate_up", torch.bfloat16), _ptr(w_down, "w_down", torch.bfloat16),
+         _ptr(act, "act", torch.bfloat16), _ptr(sync, "sync", torch.int32), _ptr(status, "status", torch.int32),
+         T, H, inter, float(eps), _stream())
 
 
 def _check_paged(q, k_cache, v_cache, block_table, out, heads, head_dim, name):

@@ -91,17 +91,27 @@ class PagedGQAttention(Part):
                                                     device=device)
         return buffer
 
-    def forward(self, h, x, ctx, cache: CacheView, state=None):
+    def forward_with_norm(self, norm, x, ctx, cache: CacheView, state=None) -> bool:
+        """The mixer with the norm before it folded into the q/k/v product, when the batch and the
+        layer are small enough for that kernel; False means nothing was done."""
+        if self.qkv.weight.dtype != torch.bfloat16 or x.shape[0] > self.qkv.small_tokens \
+                or getattr(norm, "fused_kind", None) != "rmsnorm":
+            return False
+        self.forward(None, x, ctx, cache, state, norm=norm)
+        return True
+
+    def forward(self, h, x, ctx, cache: CacheView, state=None, norm=None):
         cos, sin = self.tables if self.tables is not None else (None, None)
-        tokens = h.shape[0]
-        if h.dtype == torch.bfloat16 and tokens <= self.SPLIT_TOKENS:
+        tokens = x.shape[0]
+        dtype = self.qkv.weight.dtype
+        if dtype == torch.bfloat16 and tokens <= self.SPLIT_TOKENS:
             # few tokens: the product is a stream of weights, and a CTA streams only about 1/148 of
             # the memory bandwidth; split K so that every SM streams a share, accumulate in float32
             # and let the rotary kernel add the bias, rotate, convert and clear
-            acc = self._workspace(h.device)[:tokens]
-            kernels.gemm_bf16(h, self.qkv.weight, acc, self.runtime.status, residual=acc,
-                              split_k=self.qkv.split_k(tokens, True))
-            attended = torch.empty((tokens, self.heads * self.head_dim), dtype=h.dtype, device=h.device)
+            acc = self._workspace(x.device)[:tokens]
+            if norm is None or not self.qkv.accumulate_normed(norm, x, acc):
+                self.qkv.accumulate(h if h is not None else norm.forward(x), acc)
+            attended = torch.empty((tokens, self.heads * self.head_dim), dtype=dtype, device=x.device)
             max_keys = cache.block_table.shape[1] * cache.page_tokens
             if ctx.max_q_len == 1 and cache.write and kernels.decode_fusable(tokens, self.heads, self.kv_heads,
                                                                              self.head_dim, max_keys):
@@ -111,7 +121,7 @@ class PagedGQAttention(Part):
                                                self.runtime.status, live_keys=ctx.planned_context or ctx.max_context)
                 self.out.forward(attended, residual=x)
                 return
-            qkv = torch.empty((tokens, self.qkv.out_features), dtype=h.dtype, device=h.device)
+            qkv = torch.empty((tokens, self.qkv.out_features), dtype=dtype, device=x.device)
             kernels.rope_append(qkv, ctx.positions, ctx.seq_of_token, cache.block_table, cos, sin, cache.k, cache.v,
                                 self.heads, self.kv_heads, self.head_dim, cache.page_tokens, cache.write,
                                 self.runtime.status, acc=acc, bias=self.qkv.bias)
@@ -121,7 +131,7 @@ class PagedGQAttention(Part):
                                 self.heads, self.kv_heads, self.head_dim, cache.page_tokens, cache.write,
                                 self.runtime.status)
         q = qkv[:, :self.heads * self.head_dim]
-        attended = torch.empty((h.shape[0], self.heads * self.head_dim), dtype=qkv.dtype, device=qkv.device)
+        attended = torch.empty((tokens, self.heads * self.head_dim), dtype=qkv.dtype, device=qkv.device)
         kernels.paged_attention(q, cache, ctx, attended, self.heads, self.kv_heads, self.head_dim,
                                 self.runtime.status)
         self.out.forward(attended, residual=x)

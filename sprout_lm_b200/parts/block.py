@@ -26,8 +26,13 @@ class PreNormBlock(Part):
             part.load(source)
 
     def forward(self, x, ctx, cache, state):
-        self.mixer.forward(self.norms[0].forward(x), x, ctx, cache, state)
-        self.feed_forward.forward(self.norms[1].forward(x), x, ctx)
+        # a mixer or a feed-forward may offer to take the norm before it into its own kernel
+        fused = getattr(self.mixer, "forward_with_norm", None)
+        if fused is None or not fused(self.norms[0], x, ctx, cache, state):
+            self.mixer.forward(self.norms[0].forward(x), x, ctx, cache, state)
+        fused = getattr(self.feed_forward, "forward_with_norm", None)
+        if fused is None or not fused(self.norms[1], x, ctx):
+            self.feed_forward.forward(self.norms[1].forward(x), x, ctx)
 
 
 def build_block(layer: LayerSpec):

@@ -6,11 +6,19 @@ handful of tokens (decode), tokens on M for many (prefill).
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import kernels
 
 SM_COUNT = 148
+SMALL_BATCH_TOKENS = 8      # up to this many tokens small layers take the light small-batch kernels
+
+
+def small_batch_enabled() -> bool:
+    """SPROUT_SMALL_BATCH=0 keeps the tcgen05 products and the separate norm for every batch size."""
+    return os.environ.get("SPROUT_SMALL_BATCH", "1") != "0"
 
 
 def small_batch_split_k(out_features: int, in_features: int, tokens: int, residual: bool) -> int:
@@ -32,6 +40,11 @@ class Linear:
         if weight.dtype == torch.bfloat16 and self.in_features % 8:
             raise ValueError(f"a bfloat16 matrix needs an inner size that is a multiple of 8 (got {self.in_features}): "
                              "its rows must start on 16-byte boundaries")
+        # A handful of tokens through a small matrix: the light kernel (csrc/linear_decode.cu)
+        self.small_tokens = 0
+        if weight.dtype == torch.bfloat16 and weight.is_cuda and small_batch_enabled() \
+                and kernels.linear_decode_supported(SMALL_BATCH_TOKENS, self.out_features, self.in_features):
+            self.small_tokens = SMALL_BATCH_TOKENS
 
     def split_k(self, tokens: int, residual: bool) -> int:
         return small_batch_split_k(self.out_features, self.in_features, tokens, residual)
@@ -47,6 +60,22 @@ class Linear:
             kernels.swiglu(self.forward(a), out)
         return out
 
+    def accumulate(self, a: torch.Tensor, acc: torch.Tensor) -> None:
+        """acc (float32 [rows, out_features]) += a W^T, no bias: into a residual stream or a zeroed
+        workspace.  bfloat16 weights only."""
+        if a.shape[0] <= self.small_tokens:
+            kernels.linear_decode(self.weight, acc, self.status, a=a)
+        else:
+            kernels.gemm_bf16(a, self.weight, acc, self.status, residual=acc, split_k=self.split_k(a.shape[0], True))
+
+    def accumulate_normed(self, norm, x: torch.Tensor, acc: torch.Tensor) -> bool:
+        """acc += rmsnorm(x) W^T in one kernel, for a few tokens of a small layer; False (nothing
+        done) when the sizes or the norm are not the kernel's."""
+        if x.shape[0] > self.small_tokens or getattr(norm, "fused_kind", None) != "rmsnorm":
+            return False
+        kernels.linear_decode(self.weight, acc, self.status, norm=(x, norm.gain, norm.eps))
+        return True
+
     def forward(self, a: torch.Tensor, out_dtype: torch.dtype | None = None,
                 residual: torch.Tensor | None = None) -> torch.Tensor:
         """``residual`` (float32 [rows, out_features]) is added to in place and returned."""
@@ -55,6 +84,9 @@ class Linear:
         else:
             out = torch.empty((a.shape[0], self.out_features), dtype=out_dtype or a.dtype, device=a.device)
         if self.weight.dtype == torch.bfloat16:
+            if residual is not None and self.bias is None and a.shape[0] <= self.small_tokens:
+                kernels.linear_decode(self.weight, out, self.status, a=a)
+                return out
             kernels.gemm_bf16(a, self.weight, out, self.status, bias=self.bias, residual=residual,
                               split_k=self.split_k(a.shape[0], residual is not None))
         else:

@@ -8,10 +8,12 @@ from __future__ import annotations
 
 import torch
 
+from .. import kernels
 from .base import Part, TensorDecl, WeightSource, register_part
-from .linear import Linear
+from .linear import Linear, small_batch_enabled
 
 INTERLEAVE = 8
+FUSED_TOKENS = 8          # the one-kernel decode form takes up to this many tokens
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -31,6 +33,8 @@ class SwiGLUMLP(Part):
         names = names or {"gate": "gate_proj", "up": "up_proj", "down": "down_proj"}
         self.names = {key: prefix + value for key, value in names.items()}
         self.gate_up = self.down = None
+        self._sync = None
+        self._fused_tokens = 0            # up to this many tokens the one-kernel decode form runs
 
     def tensor_decls(self):
         return [TensorDecl(self.names["gate"] + ".weight", (self.intermediate_size, self.hidden_size)),
@@ -41,6 +45,23 @@ class SwiGLUMLP(Part):
         fused = interleave_gate_up(source.raw(self.names["gate"] + ".weight"), source.raw(self.names["up"] + ".weight"))
         self.gate_up = Linear(source.to_device_matrix(fused), None, source.runtime.status)
         self.down = Linear(source.matrix(self.names["down"] + ".weight"), None, source.runtime.status)
+        # Small layers decode in one kernel that also takes the norm before the feed-forward
+        # (csrc/ffn_decode.cu).
+        if self.gate_up.weight.dtype == torch.bfloat16 and small_batch_enabled():
+            if kernels.ffn_decode_supported(FUSED_TOKENS, self.hidden_size, self.intermediate_size):
+                self._fused_tokens = FUSED_TOKENS
+                self._sync = torch.zeros(2, dtype=torch.int32, device=self.down.weight.device)
 
     def forward(self, h, x, ctx=None):
         self.down.forward(self.gate_up.forward_swiglu(h), residual=x)
+
+    def forward_with_norm(self, norm, x, ctx=None) -> bool:
+        """x += feed_forward(norm(x)) in one kernel, if this layer and this batch allow it: an
+        RMSNorm before it, a few tokens, a layer that fits.  False means nothing was done and the
+        caller runs the norm and ``forward``."""
+        if x.shape[0] > self._fused_tokens or getattr(norm, "fused_kind", None) != "rmsnorm":
+            return False
+        act = torch.empty((x.shape[0], self.intermediate_size), dtype=torch.bfloat16, device=x.device)
+        kernels.ffn_decode(x, norm.gain, norm.eps, self.gate_up.weight, self.down.weight, act, self._sync,
+                           self.gate_up.status)
+        return True

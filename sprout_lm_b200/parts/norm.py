@@ -9,6 +9,8 @@ from .base import Part, TensorDecl, WeightSource, register_part
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Part):
+    fused_kind = "rmsnorm"       # a consumer that has this norm's arithmetic in its own kernel may take gain and eps
+
     def __init__(self, prefix: str, size: int, eps: float, name: str = "norm"):
         if eps <= 0:
             raise ValueError("rmsnorm: eps must be positive")

@@ -318,6 +318,88 @@ def test_gemm_bf16_split_k(status, M, N, K, split):
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("tokens,hidden,inter,eps", [(1, 64, 128, 1e-6), (5, 96, 320, 1e-5), (8, 896, 4864, 1e-6),
+                                                     (3, 1024, 2816, 1e-5), (8, 1536, 2048, 1e-6), (2, 48, 16, 1e-6)])
+def test_ffn_decode_one_kernel(status, tokens, hidden, inter, eps):
+    """RMSNorm, gate/up, SwiGLU, down and the residual sum in one launch, against the same
+    arithmetic in float64 with the kernel's two roundings to bfloat16 (the normalised rows, the
+    activation).  Three launches in a row: the barrier's counters must come back to zero, and one
+    channel of the input is made large so that a wrong row or column of any operand shows."""
+    from sprout_lm_b200 import kernels
+    from sprout_lm_b200.parts.mlp import interleave_gate_up
+    assert kernels.ffn_decode_supported(tokens, hidden, inter)
+    gate, up = rand(inter, hidden, dtype=torch.bfloat16, scale=0.05, seed=1), rand(inter, hidden, dtype=torch.bfloat16, scale=0.05, seed=2)
+    down = rand(hidden, inter, dtype=torch.bfloat16, scale=0.05, seed=3)
+    gain = 1 + rand(hidden, scale=0.1, seed=4)
+    w = interleave_gate_up(gate, up)
+    sync = torch.zeros(2, dtype=torch.int32, device=DEV)
+    act = torch.empty((tokens, inter), dtype=torch.bfloat16, device=DEV)
+    for round_ in range(3):
+        x = rand(tokens, hidden, seed=10 + round_)
+        x[:, (7 * round_ + 3) % hidden] *= 6.0
+        h = x.double() / torch.sqrt((x.double() ** 2).mean(dim=1, keepdim=True) + eps) * gain.double()
+        h = h.float().to(torch.bfloat16).double()
+        g, u = h @ gate.double().T, h @ up.double().T
+        t = (g / (1 + torch.exp(-g)) * u).float().to(torch.bfloat16).double()
+        delta = t @ down.double().T
+        want = x.double() + delta
+        kernels.ffn_decode(x, gain, eps, w, down, act, sync, status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert sync.tolist() == [0, 0]
+        # the activation may round to the neighbouring bfloat16 where float32 sums differ in order
+        assert (act.double() - t).abs().max().item() <= 1e-2 * max(1e-3, t.abs().max().item())
+        assert (x.double() - want).abs().max().item() <= 4e-3 * max(1e-3, delta.abs().max().item())
+
+
+def test_ffn_decode_refuses_what_does_not_fit(status):
+    from sprout_lm_b200 import kernels
+    assert not kernels.ffn_decode_supported(9, 896, 4864)          # more tokens than the tile has columns
+    assert not kernels.ffn_decode_supported(8, 904, 4864)          # sizes that are no multiple of 16
+    assert not kernels.ffn_decode_supported(8, 3584, 18944)        # a CTA's share exceeds shared memory
+    x = rand(8, 3584)
+    with pytest.raises(kernels.KernelError, match="ffn_decode"):
+        kernels.ffn_decode(x, rand(3584), 1e-6, rand(2 * 18944, 3584, dtype=torch.bfloat16), rand(3584, 18944, dtype=torch.bfloat16),
+                           torch.empty((8, 18944), dtype=torch.bfloat16, device=DEV), torch.zeros(2, dtype=torch.int32, device=DEV), status)
+
+
+@pytest.mark.parametrize("normed", [False, True])
+@pytest.mark.parametrize("tokens,N,K", [(1, 128, 64), (8, 1152, 896), (5, 160, 96), (8, 896, 896), (3, 48, 16), (7, 2048, 1536)])
+def test_linear_decode_small_batch(status, tokens, N, K, normed):
+    """out += input W^T for a few tokens with light CTAs; the input is bfloat16 rows or the RMSNorm
+    of float32 rows computed inside the kernel.  The sums land on what the output held before."""
+    from sprout_lm_b200 import kernels
+    assert kernels.linear_decode_supported(tokens, N, K)
+    w = rand(N, K, dtype=torch.bfloat16, scale=0.05, seed=1)
+    before = rand(tokens, N, seed=2)
+    for round_ in range(2):
+        out = before.clone()
+        if normed:
+            x, gain, eps = rand(tokens, K, seed=3 + round_), 1 + rand(K, scale=0.1, seed=4), 1e-5
+            x[:, (5 * round_ + 2) % K] *= 6.0
+            h = x.double() / torch.sqrt((x.double() ** 2).mean(dim=1, keepdim=True) + eps) * gain.double()
+            h = h.float().to(torch.bfloat16).double()
+            kernels.linear_decode(w, out, status, norm=(x, gain, eps))
+        else:
+            a = rand(tokens, K, dtype=torch.bfloat16, seed=3 + round_)
+            h = a.double()
+            kernels.linear_decode(w, out, status, a=a)
+        delta = h @ w.double().T
+        # a normalised value may round to the neighbouring bfloat16 where the row's sum differs in order
+        bound = (4e-3 if normed else 2e-5) * max(1e-3, delta.abs().max().item()) + 1e-6
+        assert (out.double() - (before.double() + delta)).abs().max().item() <= bound
+    assert int(status.item()) == 0
+
+
+def test_linear_decode_refuses_what_does_not_fit(status):
+    from sprout_lm_b200 import kernels
+    assert not kernels.linear_decode_supported(9, 896, 896)
+    assert not kernels.linear_decode_supported(8, 900, 896)
+    assert not kernels.linear_decode_supported(8, 3584, 3584)       # pieces too large for light CTAs
+    with pytest.raises(kernels.KernelError, match="linear_decode"):
+        kernels.linear_decode(rand(3584, 3584, dtype=torch.bfloat16), rand(8, 3584), status, a=rand(8, 3584, dtype=torch.bfloat16))
+
+
 def test_gemm_bf16_refuses_unaligned_rows(status):
     from sprout_lm_b200 import kernels
     a, w = rand(4, 20, dtype=torch.bfloat16), rand(8, 20, dtype=torch.bfloat16)
