@@ -630,11 +630,18 @@ template <int HD, bool FUSED>
 int launch_decode_mma(const DecodeParams& p, bool cluster, int requests, cudaStream_t stream) {
   constexpr size_t smem = (size_t)(16 + 2 * DEC_THREADS) * (HD + 8) * 2 + (size_t)(16 * HD + 32) * 4 + DEC_THREADS * 8;
   static bool configured[2] = {false, false};
-  if (smem > 48 * 1024 && !configured[cluster]) {
-    cudaError_t err = cluster
-        ? cudaFuncSetAttribute(attention_decode_mma_kernel<HD, true, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-        : cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (!configured[cluster]) {
+    cudaError_t err = cudaSuccess;
+    if (smem > 48 * 1024)
+      err = cluster
+          ? cudaFuncSetAttribute(attention_decode_mma_kernel<HD, true, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+          : cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return sprout_fail("attention_decode: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
+    // The kernels of a decode layer share SMs (each starts while its predecessor runs and brings
+    // its weights in meanwhile); an SM holds CTAs of kernels with different splits between L1 and
+    // shared memory only one after the other, so all of them ask for the largest shared memory.
+    if (cluster) cudaFuncSetAttribute(attention_decode_mma_kernel<HD, true, FUSED>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    else cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false, FUSED>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     configured[cluster] = true;
   }
   const dim3 grid(p.splits, p.kv_heads, requests);

@@ -191,9 +191,12 @@ ffn_decode_kernel(const __grid_constant__ CUtensorMap map_gu_base, const __grid_
   const int quarter = warp & 3;
   const int half_tiles = (nt1 + 1) >> 1;
   const int tw_begin = warp < 4 ? 0 : half_tiles, tw_end = warp < 4 ? half_tiles : nt1;
-  float acc[FFN_MAX_TILES_PER_WARP][4];
+  float acc[FFN_MAX_TILES_PER_WARP][4], odd[FFN_MAX_TILES_PER_WARP][4];   // even and odd K steps: two chains of products per tile
 #pragma unroll
-  for (int i = 0; i < FFN_MAX_TILES_PER_WARP; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  for (int i = 0; i < FFN_MAX_TILES_PER_WARP; i++) {
+    acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    odd[i][0] = odd[i][1] = odd[i][2] = odd[i][3] = 0.f;
+  }
   if (ok1 && tw_begin < tw_end) {
     const int ksteps1 = p.hidden >> 4;
     const int kb = share_begin(ksteps1, quarter, 4), ke = share_begin(ksteps1, quarter + 1, 4);
@@ -217,12 +220,17 @@ ffn_decode_kernel(const __grid_constant__ CUtensorMap map_gu_base, const __grid_
           if (i < ntw) ldmatrix_x4(swizzled(box, a_row + i * 16, chunk), a[u][i][0], a[u][i][1], a[u][i][2], a[u][i][3]);
       }
 #pragma unroll
-      for (int u = 0; u < 2; u++)
-        if (u == 0 || two) {
+      for (int i = 0; i < FFN_MAX_TILES_PER_WARP; i++)
+        if (i < ntw) mma_bf16(acc[i], a[0][i][0], a[0][i][1], a[0][i][2], a[0][i][3], b[0][0], b[0][1]);
+      if (two) {
 #pragma unroll
-          for (int i = 0; i < FFN_MAX_TILES_PER_WARP; i++)
-            if (i < ntw) mma_bf16(acc[i], a[u][i][0], a[u][i][1], a[u][i][2], a[u][i][3], b[u][0], b[u][1]);
-        }
+        for (int i = 0; i < FFN_MAX_TILES_PER_WARP; i++)
+          if (i < ntw) mma_bf16(odd[i], a[1][i][0], a[1][i][1], a[1][i][2], a[1][i][3], b[1][0], b[1][1]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < FFN_MAX_TILES_PER_WARP; i++) {
+      acc[i][0] += odd[i][0]; acc[i][1] += odd[i][1]; acc[i][2] += odd[i][2]; acc[i][3] += odd[i][3];
     }
   }
   __syncthreads();                                   // the operand rows have been read: the room is scratch now
@@ -390,6 +398,7 @@ SPROUT_API int sprout_ffn_decode(float* x, const float* gain, const void* w_gate
   if (plan.smem_bytes > smem_set) {
     cudaError_t err = cudaFuncSetAttribute(ffn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FFN_SMEM_LIMIT);
     SPROUT_REQUIRE(err == cudaSuccess, "ffn_decode: cudaFuncSetAttribute failed: %s", cudaGetErrorString(err));
+    cudaFuncSetAttribute(ffn_decode_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     smem_set = FFN_SMEM_LIMIT;
   }
   CUtensorMap map_base, map_tile, map_down;

@@ -31,7 +31,7 @@ struct LinPlan {
   int tiles, ksteps;            // 16-row tiles, 16-wide K steps of the matrix
   int row_groups, k_splits;
   int max_tiles, max_ksteps, boxes, box_bytes;
-  int off_act, off_gain, off_bar, smem_bytes;
+  int off_act, off_gain, off_stage, off_bar, smem_bytes;
   int lda, ldo;                 // row strides of the bfloat16 input and of the output, in elements
   int normed;                   // 1: the input is the float32 residual stream, normalised here
   float eps;
@@ -48,6 +48,7 @@ linear_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloa
   uint8_t* w = smem;
   uint8_t* actbuf = smem + p.off_act;
   float* gain_s = (float*)(smem + p.off_gain);
+  uint8_t* stage = smem + p.off_stage;
   uint64_t* bar = (uint64_t*)(smem + p.off_bar);
 
   pdl_launch_dependents();
@@ -77,18 +78,22 @@ linear_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloa
   if (p.normed) {
     __syncthreads();                                 // the gains are in shared memory
     if (warp < p.tokens) {
+      // one pass over the row: the sum of squares of all of it, and this CTA's K range set aside
+      // in shared memory as float32 until the scale is known
       const float4* src = (const float4*)(x + (size_t)warp * p.k);
-      const int quads = p.k >> 2;
+      float4* aside = (float4*)(stage + (size_t)warp * nk * 64);
+      const int quads = p.k >> 2, first = k_begin * 4, last = first + nk * 4;
       float ss = 0.f;
       for (int i = lane; i < quads; i += 32) {
         const float4 v = __ldcg(src + i);
         ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+        if (i >= first && i < last) aside[i - first] = v;
       }
       ss = warp_sum(ss);
+      __syncwarp();                                  // the lanes read what other lanes set aside
       const float scale = 1.0f / sqrtf(ss / (float)p.k + p.eps);
-      const float4* mine = src + k_begin * 4;        // the row was just read: these loads hit the cache
       for (int i = lane; i < nk * 4; i += 32) {
-        const float4 v = __ldcg(mine + i), g = ((const float4*)gain_s)[i];
+        const float4 v = aside[i], g = ((const float4*)gain_s)[i];
         __nv_bfloat162 lo = __floats2bfloat162_rn((v.x * scale) * g.x, (v.y * scale) * g.y);
         __nv_bfloat162 hi = __floats2bfloat162_rn((v.z * scale) * g.z, (v.w * scale) * g.w);
         *(uint2*)(actbuf + (size_t)warp * stride_b + (size_t)i * 8) = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
@@ -160,6 +165,8 @@ bool lin_make_plan(int tokens, int n, int k, int ctas, LinPlan* out) {
   at += (long long)SMALL_MAX_TOKENS * (p.max_ksteps * 32 + 16);
   p.off_gain = (int)at;
   at += (long long)p.max_ksteps * 64;
+  p.off_stage = (int)at;                 // the tokens' float32 values of the K range, before they are scaled
+  at += (long long)SMALL_MAX_TOKENS * p.max_ksteps * 64;
   p.off_bar = (int)at;
   at += 16 + 1024;                       // the barrier; room to start the tiles on a 1024-byte boundary
   if (at > LIN_MAX_SMEM) return false;
@@ -200,6 +207,8 @@ SPROUT_API int sprout_linear_decode(const void* a, int lda, const float* x, cons
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(linear_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LIN_MAX_SMEM);
     SPROUT_REQUIRE(err == cudaSuccess, "linear_decode: cudaFuncSetAttribute failed: %s", cudaGetErrorString(err));
+    // the same split between L1 and shared memory as its neighbours in the stream, so that their CTAs share SMs
+    cudaFuncSetAttribute(linear_decode_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
   cudaError_t err = sprout_launch(linear_decode_kernel, dim3(plan.row_groups * plan.k_splits), dim3(LIN_THREADS),
