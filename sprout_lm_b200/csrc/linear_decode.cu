@@ -78,25 +78,50 @@ linear_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloa
   if (p.normed) {
     __syncthreads();                                 // the gains are in shared memory
     if (warp < p.tokens) {
-      // one pass over the row: the sum of squares of all of it, and this CTA's K range set aside
-      // in shared memory as float32 until the scale is known
+      // one pass over the row: the sum of squares of all of it; this CTA's K range is scaled
+      // and converted once the sum is known
       const float4* src = (const float4*)(x + (size_t)warp * p.k);
-      float4* aside = (float4*)(stage + (size_t)warp * nk * 64);
+      uint8_t* dst = actbuf + (size_t)warp * stride_b;
       const int quads = p.k >> 2, first = k_begin * 4, last = first + nk * 4;
       float ss = 0.f;
-      for (int i = lane; i < quads; i += 32) {
-        const float4 v = __ldcg(src + i);
-        ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
-        if (i >= first && i < last) aside[i - first] = v;
-      }
-      ss = warp_sum(ss);
-      __syncwarp();                                  // the lanes read what other lanes set aside
-      const float scale = 1.0f / sqrtf(ss / (float)p.k + p.eps);
-      for (int i = lane; i < nk * 4; i += 32) {
-        const float4 v = aside[i], g = ((const float4*)gain_s)[i];
-        __nv_bfloat162 lo = __floats2bfloat162_rn((v.x * scale) * g.x, (v.y * scale) * g.y);
-        __nv_bfloat162 hi = __floats2bfloat162_rn((v.z * scale) * g.z, (v.w * scale) * g.w);
-        *(uint2*)(actbuf + (size_t)warp * stride_b + (size_t)i * 8) = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+      if (quads <= 256) {                            // the row stays in registers; all its loads are in flight at once
+        float4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const int i = lane + j * 32;
+          v[j] = i < quads ? __ldcg(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) ss += (v[j].x * v[j].x + v[j].y * v[j].y) + (v[j].z * v[j].z + v[j].w * v[j].w);
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss / (float)p.k + p.eps);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const int i = lane + j * 32;
+          if (i >= first && i < last) {
+            const float4 g = ((const float4*)gain_s)[i - first];
+            __nv_bfloat162 lo = __floats2bfloat162_rn((v[j].x * scale) * g.x, (v[j].y * scale) * g.y);
+            __nv_bfloat162 hi = __floats2bfloat162_rn((v[j].z * scale) * g.z, (v[j].w * scale) * g.w);
+            *(uint2*)(dst + (size_t)(i - first) * 8) = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+          }
+        }
+      } else {                                       // longer rows: the K range waits in shared memory as float32
+        float4* aside = (float4*)(stage + (size_t)warp * nk * 64);
+#pragma unroll 4
+        for (int i = lane; i < quads; i += 32) {
+          const float4 v = __ldcg(src + i);
+          ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+          if (i >= first && i < last) aside[i - first] = v;
+        }
+        ss = warp_sum(ss);
+        __syncwarp();                                // the lanes read what other lanes set aside
+        const float scale = 1.0f / sqrtf(ss / (float)p.k + p.eps);
+        for (int i = lane; i < nk * 4; i += 32) {
+          const float4 v = aside[i], g = ((const float4*)gain_s)[i];
+          __nv_bfloat162 lo = __floats2bfloat162_rn((v.x * scale) * g.x, (v.y * scale) * g.y);
+          __nv_bfloat162 hi = __floats2bfloat162_rn((v.z * scale) * g.z, (v.w * scale) * g.w);
+          *(uint2*)(dst + (size_t)i * 8) = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+        }
       }
     } else {
       for (int i = lane; i < nk * 2; i += 32) *(uint4*)(actbuf + (size_t)warp * stride_b + (size_t)i * 16) = make_uint4(0u, 0u, 0u, 0u);
