@@ -28,20 +28,26 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
 }
 
 // A [tiles x 16 rows, ksteps x 16 columns] matrix in row_groups x k_splits pieces, at most one per
-// CTA, each at most 16 tiles high (256 rows: one TMA box): the split with the least bytes per
-// piece, K counted in whole boxes of 64 columns.  False when no split exists.
+// CTA, each at most 16 tiles high (256 rows: one TMA box).  A CTA's eight warps take its tiles in
+// turn and walk a tile's K steps one after the other, so the split with the fewest steps per warp
+// wins (a piece of one tile and many K steps would leave seven warps idle); among equals the one
+// with the least bytes per piece, K counted in whole boxes of 64 columns.  False when no split
+// exists.
 inline bool plan_pieces(int tiles, int ksteps, int ctas, int* row_groups, int* k_splits) {
-  long long best = -1;
+  long long best_steps = -1, best_bytes = -1;
   for (int groups = 1; groups <= tiles && groups <= ctas; groups++) {
     const int rows = (tiles + groups - 1) / groups;
     if (rows > 16) continue;
     int splits = ctas / groups;
     if (splits > ksteps) splits = ksteps;
     const int steps = (ksteps + splits - 1) / splits;
-    const long long cost = (long long)rows * ((steps + 3) / 4 * 4);
-    if (best < 0 || cost < best) { best = cost; *row_groups = groups; *k_splits = splits; }
+    const long long per_warp = (long long)((rows + 7) / 8) * steps;
+    const long long bytes = (long long)rows * ((steps + 3) / 4 * 4);
+    if (best_steps < 0 || per_warp < best_steps || (per_warp == best_steps && bytes < best_bytes)) {
+      best_steps = per_warp; best_bytes = bytes; *row_groups = groups; *k_splits = splits;
+    }
   }
-  return best >= 0;
+  return best_steps >= 0;
 }
 
 }  // namespace
