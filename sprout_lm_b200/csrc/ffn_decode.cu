@@ -13,9 +13,9 @@
 // waits for the kernels before it; its piece of the down matrix takes the same room as soon as
 // the gate/up products are done and arrives while the CTAs meet at the barrier.  With under
 // 160 KB of shared memory at the 0.5B sizes the CTA fits beside a CTA of the attention kernel,
-// so the weights stream from memory while the attention half of the layer still runs.  After the wait each warp normalises one
-// token's row of the residual stream (float32 arithmetic) into a bfloat16 operand in shared
-// memory; the products run on `mma.sync.m16n8k16` with the weights as the 16-row operand and the
+// so the weights stream from memory while the attention half of the layer still runs.  After
+// the wait each warp normalises one token's row of the residual stream (float32 arithmetic) into
+// a bfloat16 operand in shared memory; the products run on `mma.sync.m16n8k16` with the weights as the 16-row operand and the
 // tokens as the 8 columns (for eight tokens the tensor cores' rate does not matter, latency
 // does); the four quarters of K meet in shared memory, SwiGLU is applied and the activation goes
 // to memory as bfloat16 [tokens, intermediate].  After the barrier each CTA multiplies its piece
@@ -111,7 +111,8 @@ ffn_decode_kernel(const __grid_constant__ CUtensorMap map_gu_base, const __grid_
   }
   __syncthreads();
 
-  // ---- all of this CTA's weights, requested before the wait for the earlier kernels
+  // ---- this CTA's gate/up tiles, requested before the wait for the earlier kernels: every CTA
+  //      has base_tiles1 tiles (one box per 64 columns), some have one more (a 16-row box each)
   if (warp == 0) {
     const uint32_t bar = smem_u32(&bars[0]);
     const uint32_t base_bytes = (uint32_t)p.base_tiles1 * 2048;
