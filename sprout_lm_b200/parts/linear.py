@@ -2,7 +2,9 @@
 
 float32 weights run on CUDA cores with float32 fused multiply-adds (the true 32-bit path).
 bfloat16 weights run on the tcgen05 tensor-core kernel: weight rows on the MMA's M axis for a
-handful of tokens (decode), tokens on M for many (prefill).
+handful of tokens (decode), tokens on M for many (prefill).  Up to 8 tokens through a small
+matrix into a float32 sum take the light `mma.sync` kernel instead, which can also fold the
+RMSNorm before the product in (csrc/linear_decode.cu).
 """
 from __future__ import annotations
 
