@@ -20,7 +20,7 @@ This module holds no device memory; it decides which page holds what.
 from __future__ import annotations
 
 import heapq
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Sequence
 
 

@@ -71,7 +71,6 @@ def load_library(verbose: bool = True):
                 fn.restype = c_int
             lib.sprout_set_pdl.argtypes = [c_int]
             lib.sprout_set_pdl.restype = None
-            import os
             if os.environ.get("SPROUT_PDL", "1") == "0":
                 lib.sprout_set_pdl(0)
             _lib = lib

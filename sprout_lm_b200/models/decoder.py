@@ -12,7 +12,7 @@ from pathlib import Path
 import torch
 
 from ..config import ModelSpec, load_config
-from ..parts import CacheView, Runtime, StateView, WeightSource, build_block, build_part
+from ..parts import Runtime, WeightSource, build_block, build_part
 from ..weights.checkpoint import Checkpoint
 
 

@@ -95,7 +95,6 @@ def test_temperature_sampling_is_seeded_and_independent_of_batching(model_dirs):
 
 def test_eos_stops_generation(model_dirs):
     from sprout_lm_b200 import generate, load_model
-    from sprout_lm_b200.config import load_config
     import shutil
     rng = np.random.default_rng(1)
     prompt = helpers.random_tokens(rng, 9, 256)

@@ -7,7 +7,6 @@ Tolerance in 32-bit: the reference project's own bar for the real 0.5B model aga
 independent float32 implementation, 1e-3 + 1e-4 |ref| (test/model.integration.ts:69)."""
 import numpy as np
 import pytest
-import torch
 
 import helpers
 
