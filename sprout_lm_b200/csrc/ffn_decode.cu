@@ -378,6 +378,18 @@ SPROUT_API int sprout_ffn_decode_supported(int tokens, int hidden, int inter) {
   return ffn_make_plan(tokens, hidden, inter, sm_count(), 1e-6f, &plan) ? 1 : 0;
 }
 
+// The launch layout for these sizes on `ctas` CTAs, for inspection by host-side tests: 1 and the
+// plan's 18 numbers in `out` (in the order of the list below), or 0 when the sizes are refused.
+SPROUT_API int sprout_ffn_decode_plan(int tokens, int hidden, int inter, int ctas, int* out) {
+  FfnPlan p;
+  if (!out || !ffn_make_plan(tokens, hidden, inter, ctas, 1e-6f, &p)) return 0;
+  const int fields[18] = {p.tiles1, p.tiles2, p.ksteps2, p.row_groups, p.k_splits, p.base_tiles1, p.max_tiles1, p.max_tiles2,
+                          p.max_ksteps2, p.boxes1, p.boxes2, p.box1_bytes, p.box2_bytes, p.stride1, p.off_w2, p.off_act,
+                          p.off_bar, p.smem_bytes};
+  for (int i = 0; i < 18; i++) out[i] = fields[i];
+  return 1;
+}
+
 // x [tokens, hidden] float32 += W_down (silu(W_gate h) * W_up h) with h = rmsnorm(x, gain, eps).
 // w_gate_up: bfloat16 [2 * inter, hidden], gate and up rows interleaved in blocks of 8;
 // w_down: bfloat16 [hidden, inter]; act: bfloat16 scratch [tokens, inter]; sync: two 32-bit

@@ -208,6 +208,17 @@ SPROUT_API int sprout_linear_decode_supported(int tokens, int n, int k) {
   return lin_make_plan(tokens, n, k, sm_count(), &plan) ? 1 : 0;
 }
 
+// The launch layout for these sizes on `ctas` CTAs, for inspection by host-side tests: 1 and the
+// plan's 13 numbers in `out` (in the order of the list below), or 0 when the sizes are refused.
+SPROUT_API int sprout_linear_decode_plan(int tokens, int n, int k, int ctas, int* out) {
+  LinPlan p;
+  if (!out || !lin_make_plan(tokens, n, k, ctas, &p)) return 0;
+  const int fields[13] = {p.tiles, p.ksteps, p.row_groups, p.k_splits, p.max_tiles, p.max_ksteps, p.boxes, p.box_bytes,
+                          p.off_act, p.off_gain, p.off_stage, p.off_bar, p.smem_bytes};
+  for (int i = 0; i < 13; i++) out[i] = fields[i];
+  return 1;
+}
+
 // out [tokens, n] float32 (row stride ldo) += input W^T, W bfloat16 [n, k] contiguous.  The input
 // is `a`, bfloat16 [tokens, k] with row stride lda, or, when `a` is null, rmsnorm(x, gain, eps)
 // of the float32 rows x [tokens, k].

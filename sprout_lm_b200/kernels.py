@@ -304,6 +304,28 @@ def linear_decode(weight, out, status, a=None, norm=None):
          out.stride(0), T, N, K, _ptr(status, "status", torch.int32), _stream())
 
 
+FFN_PLAN_FIELDS = ("tiles1", "tiles2", "ksteps2", "row_groups", "k_splits", "base_tiles1", "max_tiles1", "max_tiles2",
+                   "max_ksteps2", "boxes1", "boxes2", "box1_bytes", "box2_bytes", "stride1", "off_w2", "off_act", "off_bar",
+                   "smem_bytes")
+LINEAR_PLAN_FIELDS = ("tiles", "ksteps", "row_groups", "k_splits", "max_tiles", "max_ksteps", "boxes", "box_bytes", "off_act",
+                      "off_gain", "off_stage", "off_bar", "smem_bytes")
+
+
+def small_batch_plan(kind: str, tokens: int, rows: int, cols: int, ctas: int = 148) -> dict | None:
+    """How a small-batch kernel would lay a launch out on ``ctas`` CTAs (host arithmetic of the
+    kernel library, no GPU needed), or None where it refuses the sizes.  ``kind`` "ffn": rows is
+    the hidden size, cols the intermediate size; "linear": a [rows, cols] matrix."""
+    lib = _lib or load_library()
+    names = FFN_PLAN_FIELDS if kind == "ffn" else LINEAR_PLAN_FIELDS
+    fn = lib.sprout_ffn_decode_plan if kind == "ffn" else lib.sprout_linear_decode_plan
+    fn.argtypes = [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int)]
+    fn.restype = c_int
+    out = (c_int * len(names))()
+    if not fn(tokens, rows, cols, ctas, out):
+        return None
+    return dict(zip(names, out))
+
+
 def ffn_decode_supported(tokens: int, hidden: int, intermediate: int) -> bool:
     """Whether ``ffn_decode`` takes these sizes: 1..8 tokens, sizes that are multiples of 16, and a
     layer small enough for every CTA to hold its share of the two matrices in shared memory."""

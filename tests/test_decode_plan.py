@@ -115,3 +115,81 @@ def test_small_batch_kernels_say_what_they_take():
     assert not kernels.ffn_decode_supported(8, 3584, 18944) and not kernels.ffn_decode_supported(8, 5120, 13824)
     assert not kernels.linear_decode_supported(9, 896, 896) and not kernels.linear_decode_supported(8, 900, 896)
     assert not kernels.linear_decode_supported(8, 3584, 3584)
+
+
+def _share(n, part, parts):
+    return n * part // parts
+
+
+SMEM_LIMIT = 227 * 1024
+
+
+@pytest.mark.parametrize("ctas", [148, 132, 40])
+def test_feed_forward_plan_covers_the_matrices_and_fits(ctas):
+    """The launch layout of the one-kernel feed-forward for many sizes (host arithmetic of the kernel
+    library): every tile of both matrices has exactly one CTA, the TMA boxes respect their limits
+    (256 rows, starts on 1024 bytes, columns in steps of 8 elements), what shares a room fits in
+    it, and the whole fits the SM's shared memory; sizes it cannot lay out are refused."""
+    taken = 0
+    for hidden in list(range(16, 513, 48)) + [896, 1024, 1536, 2048]:
+        for inter in [16, 128, 320, 1008, 2816, 4864, 8192]:
+            plan = kernels.small_batch_plan("ffn", 8, hidden, inter, ctas)
+            if plan is None:
+                continue
+            taken += 1
+            p = plan
+            assert p["tiles1"] * 8 == inter and p["tiles2"] * 16 == hidden and p["ksteps2"] * 16 == inter
+            # gate/up: contiguous shares of base or base + 1 tiles
+            shares = [_share(p["tiles1"], c + 1, ctas) - _share(p["tiles1"], c, ctas) for c in range(ctas)]
+            assert sum(shares) == p["tiles1"] and set(shares) <= {p["base_tiles1"], p["base_tiles1"] + 1}
+            assert max(shares) == p["max_tiles1"] <= 8 and p["base_tiles1"] * 16 <= 256
+            assert p["boxes1"] * 64 >= hidden and p["box1_bytes"] == p["max_tiles1"] * 2048
+            # down: row groups x K ranges, one piece per CTA at most
+            assert 1 <= p["row_groups"] <= p["tiles2"] and 1 <= p["k_splits"] <= p["ksteps2"]
+            assert p["row_groups"] * p["k_splits"] <= ctas
+            rows = [_share(p["tiles2"], g + 1, p["row_groups"]) - _share(p["tiles2"], g, p["row_groups"]) for g in range(p["row_groups"])]
+            steps = [_share(p["ksteps2"], s + 1, p["k_splits"]) - _share(p["ksteps2"], s, p["k_splits"]) for s in range(p["k_splits"])]
+            assert sum(rows) == p["tiles2"] and sum(steps) == p["ksteps2"] and min(rows) >= 1 and min(steps) >= 1
+            assert max(rows) == p["max_tiles2"] <= 16 and max(steps) == p["max_ksteps2"]
+            assert p["boxes2"] * 4 >= p["max_ksteps2"] and p["box2_bytes"] == p["max_tiles2"] * 2048
+            # rooms: the down piece where the gate/up tiles were; operand rows, K quarters and the activation's range in turn
+            weights = p["off_act"] - p["off_w2"]
+            assert p["off_w2"] == 0 and weights >= p["boxes1"] * p["box1_bytes"] and weights >= p["boxes2"] * p["box2_bytes"]
+            room = p["off_bar"] - p["off_act"]
+            assert p["stride1"] == 2 * hidden + 16
+            assert room >= 8 * p["stride1"] and room >= p["max_tiles1"] * 2048 and room >= 8 * (p["max_ksteps2"] * 32 + 16)
+            assert p["box1_bytes"] % 1024 == 0 and p["box2_bytes"] % 1024 == 0 and p["off_act"] % 16 == 0 and p["off_bar"] % 8 == 0
+            assert p["smem_bytes"] >= p["off_bar"] + 16 + 1023 and p["smem_bytes"] <= SMEM_LIMIT - 1024
+            assert p["boxes1"] * p["max_tiles1"] * 2048 < (1 << 20) and p["boxes2"] * p["box2_bytes"] < (1 << 20)   # an mbarrier's byte count
+    assert taken >= 20
+    assert kernels.small_batch_plan("ffn", 8, 896, 4864, ctas) is not None or ctas < 148
+
+
+@pytest.mark.parametrize("ctas", [148, 132, 40])
+def test_linear_plan_covers_the_matrix_and_fits(ctas):
+    taken = 0
+    for n in [16, 48, 128, 160, 896, 1152, 2048, 4096]:
+        for k in [16, 64, 96, 896, 1536, 4864]:
+            p = kernels.small_batch_plan("linear", 8, n, k, ctas)
+            if p is None:
+                continue
+            taken += 1
+            assert p["tiles"] * 16 == n and p["ksteps"] * 16 == k
+            assert 1 <= p["row_groups"] <= p["tiles"] and 1 <= p["k_splits"] <= p["ksteps"] and p["row_groups"] * p["k_splits"] <= ctas
+            rows = [_share(p["tiles"], g + 1, p["row_groups"]) - _share(p["tiles"], g, p["row_groups"]) for g in range(p["row_groups"])]
+            steps = [_share(p["ksteps"], s + 1, p["k_splits"]) - _share(p["ksteps"], s, p["k_splits"]) for s in range(p["k_splits"])]
+            assert sum(rows) == p["tiles"] and sum(steps) == p["ksteps"] and min(rows) >= 1 and min(steps) >= 1
+            assert max(rows) == p["max_tiles"] <= 16 and max(steps) == p["max_ksteps"]
+            assert p["boxes"] * 4 >= p["max_ksteps"] and p["box_bytes"] == p["max_tiles"] * 2048
+            assert p["off_act"] >= p["boxes"] * p["box_bytes"]
+            assert p["off_gain"] - p["off_act"] >= 8 * (p["max_ksteps"] * 32 + 16)
+            assert p["off_stage"] - p["off_gain"] >= p["max_ksteps"] * 64 and p["off_bar"] - p["off_stage"] >= 8 * p["max_ksteps"] * 64
+            assert p["off_act"] % 16 == 0 and p["off_gain"] % 16 == 0 and p["off_stage"] % 16 == 0 and p["off_bar"] % 8 == 0
+            assert p["off_bar"] + 16 + 1023 <= p["smem_bytes"] <= 96 * 1024
+    assert taken >= 20
+    if ctas == 148:
+        # the eight warps of a CTA share its tiles: a piece is eight tiles high and a few K steps long,
+        # not one tile with many steps (q/k/v and output projection of the 0.5B sizes)
+        qkv, o = kernels.small_batch_plan("linear", 8, 1152, 896), kernels.small_batch_plan("linear", 8, 896, 896)
+        assert (qkv["row_groups"], qkv["k_splits"], qkv["max_tiles"], qkv["max_ksteps"]) == (9, 16, 8, 4)
+        assert (o["row_groups"], o["k_splits"], o["max_tiles"], o["max_ksteps"]) == (7, 21, 8, 3)
