@@ -586,6 +586,9 @@ def run(args) -> dict:
     peak = peaks()
     rng = np.random.default_rng(0)
     batch, prompt_len, context = args.batch, 512, base["max_position_embeddings"]
+    if prompt_len + args.warmup + args.steps + 8 > context:
+        raise SystemExit(f"bench.py: {prompt_len}-token prompts and {args.warmup} + {args.steps} decode steps do not fit the "
+                         f"{context}-token context of the benchmark configuration; use at most {context - prompt_len - args.warmup - 8} steps")
     pages = 64 * (-(-(prompt_len + args.steps + args.warmup + 16) // 16)) + 2048 // 16 + 16
     runner = ModelRunner(model, num_pages=pages, page_tokens=16, max_requests=64, prefix_caching=False)
 
