@@ -89,7 +89,7 @@ class ClockSampler:
     def start(self):
         try:
             self.process = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
-                                             "--format=csv,noheader,nounits", "-lms", "20"],
+                                             "--format=csv,noheader,nounits", "-lms", "100"],
                                             stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             return
@@ -548,7 +548,7 @@ def timed_gemms(tokens: int, shape: str = "0.5b", repeats: int = 20) -> dict:
             out, kw = torch.empty(tokens, n, dtype=torch.bfloat16, device="cuda"), {"bias": torch.zeros(n, device="cuda")}
         elif kind == "residual":
             out = torch.zeros(tokens, n, device="cuda")
-            kw = {"residual": out, "split_k": small_batch_split_k(n, k, tokens, True)}
+            kw = {"residual": out, "split_k": small_batch_split_k(n, k, tokens, True, kernels.sm_count())}
         else:
             w = interleave_gate_up(w[:n // 2].contiguous(), w[n // 2:].contiguous())
             out, kw = torch.empty(tokens, n // 2, dtype=torch.bfloat16, device="cuda"), {"swiglu": True}
@@ -599,8 +599,13 @@ def run(args) -> dict:
         prefill_ms = timed_prefill(runner, 2048, rng, repeats=1)
         return {"impl": "ours", "only": "prefill", "shape": args.shape, "layers": layers, "ms": round(prefill_ms, 4),
                 "frac": round(prefill_flops(cfg, 2048) / (prefill_ms / 1000) / (peak["bf16_tflops"] * 1e12), 4)}
-    main = timed_decode(runner, batch, prompt_len, args.steps, args.warmup, rng, sampler=ClockSampler())
+    # the clocks are sampled over all timed sections together (a single section of a few
+    # milliseconds is shorter than nvidia-smi's sampling period)
+    sampler = ClockSampler()
+    sampler.start()
+    main = timed_decode(runner, batch, prompt_len, args.steps, args.warmup, rng)
     if args.only == "decode":
+        sampler.stop()
         step_bytes = weight_bytes(model) + batch * main["mean_context"] * cache_bytes_per_token(model, torch.bfloat16)
         return {"impl": "ours", "only": "decode", "shape": args.shape, "layers": layers, "batch": batch,
                 "ms_per_step": round(main["ms_per_step"], 4), "launches_per_step": main["launches_per_step"],
@@ -611,6 +616,7 @@ def run(args) -> dict:
     prefill_ms = timed_prefill(runner, 2048, rng)
     flops = prefill_flops(cfg, 2048)
     e2e = timed_e2e(model, batch, prompt_len, args.steps, args.warmup, rng)
+    clocks = sampler.stop()
 
     step_bytes = weight_bytes(model) + batch * main["mean_context"] * cache_bytes_per_token(model, torch.bfloat16)
     achieved = step_bytes / (main["ms_per_step"] / 1000) / 1e9
@@ -632,7 +638,7 @@ def run(args) -> dict:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peak["hbm_gbs"], 4), "peaks": peak["source"]},
         "points": points,
-        "clocks": main["clocks"],
+        "clocks": clocks,
     }
 
 

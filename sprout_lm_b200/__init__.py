@@ -12,12 +12,12 @@ from .weights import WeightError, write_random_model
 __version__ = "0.1.0"
 
 
-def load_model(directory, dtype="bfloat16", device="cuda:0"):
+def load_model(directory, dtype="bfloat16", device="cuda:0", weight_budget_bytes=None):
     import torch
     from .models import load_model as _load
     if isinstance(dtype, str):
         dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype]
-    return _load(directory, dtype=dtype, device=device)
+    return _load(directory, dtype=dtype, device=device, weight_budget_bytes=weight_budget_bytes)
 
 
 def generate(model, prompts, max_new_tokens=16, **kwargs):

@@ -62,9 +62,11 @@ struct DecodeParams {
   int* status;
   // fused projection tail (tensor-core kernel, FUSED): q, k, v of the new token come as float32
   // sums [requests, heads + 2 kv_heads, head_dim] from a split-K product, plus a bias; the
-  // kernel rotates q and k by the token's position (tables [max_positions, head_dim / 2], may be
-  // null), appends k and v to the cache and leaves the sums zeroed
+  // kernel rotates q and k by the token's position (tables [max_positions, rotary_dim / 2], may be
+  // null; the first rotary_dim elements of a head turn, in half-split pairs (d, d + rotary_dim / 2) or,
+  // with `interleaved`, in pairs (2d, 2d + 1)), appends k and v to the cache and leaves the sums zeroed
   float* acc; const float* bias; const float* cos_table; const float* sin_table; int max_positions;
+  int rotary_dim, interleaved;
   __nv_bfloat16* k_append; __nv_bfloat16* v_append;
 };
 
@@ -341,8 +343,8 @@ attention_decode_mma_kernel(const DecodeParams p) {
   for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
   // The first pass's keys and values are requested before the request's length is known (its load
-  // is still in flight): whatever lies in an allocated page beyond the length is finite and gets
-  // probability zero.  Later passes know the length.
+  // is still in flight); what it brought from beyond the length is cleared once the length is
+  // there.  Later passes know the length.
   int end = begin + p.split_keys;
   for (int base = begin; base < end; base += DEC_THREADS) {
     const bool first = base == begin;
@@ -403,16 +405,20 @@ attention_decode_mma_kernel(const DecodeParams p) {
       if (pos < 0 || (rotate && pos >= p.max_positions)) { if (tid == 0) atomicOr(p.status, SPROUT_STATUS_BAD_POSITION); }
       const int safe = min(max(pos, 0), max(p.max_positions - 1, 0));
       constexpr int HALF = HD / 2;
+      const int rot_half = p.rotary_dim >> 1;
       const float* sums = p.acc + (size_t)r * width + (size_t)g * group * HD;
       const float* bias = p.bias ? p.bias + (size_t)g * group * HD : nullptr;
       for (int idx = tid; idx < group * HALF; idx += DEC_THREADS) {
         const int row = idx / HALF, d = idx % HALF;
-        const int at = row * HD + d;
-        const float a = sums[at] + (bias ? bias[at] : 0.f);
-        const float b = sums[at + HALF] + (bias ? bias[at + HALF] : 0.f);
-        const float c = rotate ? p.cos_table[(size_t)safe * HALF + d] : 1.f, sn = rotate ? p.sin_table[(size_t)safe * HALF + d] : 0.f;
-        sQ[row * STRIDE + d] = __float2bfloat16_rn(a * c - b * sn);
-        sQ[row * STRIDE + d + HALF] = __float2bfloat16_rn(b * c + a * sn);
+        // pair d of the head: a rotated pair below rotary_dim / 2, two elements that pass through beyond
+        const bool turned = rotate && d < rot_half;
+        const int e0 = d < rot_half ? (p.interleaved ? 2 * d : d) : p.rotary_dim + 2 * (d - rot_half);
+        const int e1 = d < rot_half ? (p.interleaved ? 2 * d + 1 : d + rot_half) : e0 + 1;
+        const float a = sums[row * HD + e0] + (bias ? bias[row * HD + e0] : 0.f);
+        const float b = sums[row * HD + e1] + (bias ? bias[row * HD + e1] : 0.f);
+        const float c = turned ? p.cos_table[(size_t)safe * rot_half + d] : 1.f, sn = turned ? p.sin_table[(size_t)safe * rot_half + d] : 0.f;
+        sQ[row * STRIDE + e0] = __float2bfloat16_rn(a * c - b * sn);
+        sQ[row * STRIDE + e1] = __float2bfloat16_rn(b * c + a * sn);
       }
       for (int idx = group * CHUNKS + tid; idx < 16 * CHUNKS; idx += DEC_THREADS)      // the tile's unused rows
         *(uint4*)(sQ + (idx / CHUNKS) * STRIDE + (idx % CHUNKS) * 8) = make_uint4(0, 0, 0, 0);
@@ -422,6 +428,27 @@ attention_decode_mma_kernel(const DecodeParams p) {
       if (!CLUSTER && begin >= len) { cp_async_wait<0>(); return; }   // the merge kernel knows which splits exist
     }
     cp_async_wait<0>();
+    if (first && end - base < DEC_THREADS) {
+      // The early loads brought rows beyond the request's length from its pages as they lay there:
+      // a page that another request used before may hold anything, and probability zero times a
+      // stale non-finite value would still poison the sum.  Each thread clears the value pieces that
+      // its own copies wrote (keys need nothing: their scores are replaced, not multiplied).
+      const int live = max(end - base, 0);
+      if constexpr (DEC_THREADS % CHUNKS == 0) {
+        constexpr int ROWS_AT_ONCE = DEC_THREADS / CHUNKS;
+        const int c8 = (tid % CHUNKS) * 8, r0 = tid / CHUNKS;
+#pragma unroll
+        for (int k = 0; k < CHUNKS; k++) {
+          const int row = r0 + k * ROWS_AT_ONCE;
+          if (row >= live) *(uint4*)(sV + row * STRIDE + c8) = make_uint4(0, 0, 0, 0);
+        }
+      } else {
+        for (int idx = tid; idx < DEC_THREADS * CHUNKS; idx += DEC_THREADS) {
+          const int row = idx / CHUNKS, c = idx % CHUNKS;
+          if (row >= live) *(uint4*)(sV + row * STRIDE + c * 8) = make_uint4(0, 0, 0, 0);
+        }
+      }
+    }
     if (!FUSED && first && pos >= base && pos < base + DEC_THREADS && pos < begin + p.split_keys) {
       // the newest position's key and value may have been written after the early loads read them
       __syncthreads();                                 // the early loads of that row have landed
@@ -448,13 +475,17 @@ attention_decode_mma_kernel(const DecodeParams p) {
       const float* k_bias = p.bias ? p.bias + (p.heads + g) * HD : nullptr;
       const float* v_bias = p.bias ? p.bias + (p.heads + p.kv_heads + g) * HD : nullptr;
       const int row = pos - base;
+      const int rot_half = p.rotary_dim >> 1;
       for (int d = tid; d < HALF; d += DEC_THREADS) {
-        const float a = k_acc[d] + (k_bias ? k_bias[d] : 0.f), b = k_acc[d + HALF] + (k_bias ? k_bias[d + HALF] : 0.f);
-        k_acc[d] = 0.f; k_acc[d + HALF] = 0.f;
-        const float c = rotate ? p.cos_table[(size_t)safe * HALF + d] : 1.f, sn = rotate ? p.sin_table[(size_t)safe * HALF + d] : 0.f;
+        const bool turned = rotate && d < rot_half;
+        const int e0 = d < rot_half ? (p.interleaved ? 2 * d : d) : p.rotary_dim + 2 * (d - rot_half);
+        const int e1 = d < rot_half ? (p.interleaved ? 2 * d + 1 : d + rot_half) : e0 + 1;
+        const float a = k_acc[e0] + (k_bias ? k_bias[e0] : 0.f), b = k_acc[e1] + (k_bias ? k_bias[e1] : 0.f);
+        k_acc[e0] = 0.f; k_acc[e1] = 0.f;
+        const float c = turned ? p.cos_table[(size_t)safe * rot_half + d] : 1.f, sn = turned ? p.sin_table[(size_t)safe * rot_half + d] : 0.f;
         const __nv_bfloat16 lo = __float2bfloat16_rn(a * c - b * sn), hi = __float2bfloat16_rn(b * c + a * sn);
-        sK[row * STRIDE + d] = lo; sK[row * STRIDE + d + HALF] = hi;
-        if (page_ok) { p.k_append[dst + d] = lo; p.k_append[dst + d + HALF] = hi; }
+        sK[row * STRIDE + e0] = lo; sK[row * STRIDE + e1] = hi;
+        if (page_ok) { p.k_append[dst + e0] = lo; p.k_append[dst + e1] = hi; }
       }
       for (int d = tid; d < HD; d += DEC_THREADS) {
         const __nv_bfloat16 v = __float2bfloat16_rn(v_acc[d] + (v_bias ? v_bias[d] : 0.f));
@@ -955,7 +986,7 @@ SPROUT_API long long sprout_attention_decode_scratch_floats(int requests, int he
   return (long long)requests * heads * splits * (head_dim + 2);
 }
 
-struct FusedTail { float* acc; const float* bias; const float* cos_table; const float* sin_table; int max_positions; };
+struct FusedTail { float* acc; const float* bias; const float* cos_table; const float* sin_table; int max_positions; int rotary_dim, interleaved; };
 
 static int decode_launch(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                          const int* block_table, int table_stride, const int* context_lens, void* out, int out_stride,
@@ -986,6 +1017,7 @@ static int decode_launch(const void* q, int q_stride, const void* k_cache, const
   p.heads = heads; p.kv_heads = kv_heads; p.head_dim = head_dim; p.page_tokens = page_tokens; p.num_pages = num_pages;
   p.split_keys = split_keys; p.splits = splits; p.status = status;
   p.acc = nullptr; p.bias = nullptr; p.cos_table = nullptr; p.sin_table = nullptr; p.max_positions = 0;
+  p.rotary_dim = head_dim; p.interleaved = 0;
   p.k_append = nullptr; p.v_append = nullptr;
   const bool fused = fused_early;
   if (fused) {
@@ -994,6 +1026,9 @@ static int decode_launch(const void* q, int q_stride, const void* k_cache, const
     SPROUT_REQUIRE((extra->cos_table == nullptr) == (extra->sin_table == nullptr), "attention_decode_fused: cos and sin tables go together");
     p.acc = extra->acc; p.bias = extra->bias; p.cos_table = extra->cos_table; p.sin_table = extra->sin_table;
     p.max_positions = extra->max_positions;
+    SPROUT_REQUIRE(extra->rotary_dim >= 0 && extra->rotary_dim % 2 == 0 && extra->rotary_dim <= head_dim,
+                   "attention_decode_fused: rotary_dim must be even and at most head_dim (got %d of %d)", extra->rotary_dim, head_dim);
+    p.rotary_dim = extra->rotary_dim; p.interleaved = extra->interleaved ? 1 : 0;
     p.k_append = (__nv_bfloat16*)k_cache; p.v_append = (__nv_bfloat16*)v_cache;
   }
   const int group = heads / kv_heads;
@@ -1074,16 +1109,17 @@ SPROUT_API int sprout_attention_decode(const void* q, int q_stride, const void* 
 // The decode step's attention with the projection's tail folded in: instead of q and an already
 // appended cache it takes the float32 sums of the q/k/v product for each request's new token
 // (acc [requests, (heads + 2 kv_heads) * head_dim], contiguous) and their bias; it rotates q and k
-// by the token's position context_lens[r] - 1 (tables may be null: no rotation), appends k and v
-// to the cache, attends, and leaves acc zeroed.  head_dim <= 128; without scratch memory (as for
+// by the token's position context_lens[r] - 1 (tables [max_positions, rotary_dim / 2]; null: no rotation;
+// rotary_dim and interleaved as for sprout_rope_append), appends k and v to the cache, attends, and
+// leaves acc zeroed.  head_dim <= 128; without scratch memory (as for
 // sprout_attention_decode) at most 8 splits, merged inside a cluster.
 SPROUT_API int sprout_attention_decode_fused(float* acc, const float* bias, const float* cos_table, const float* sin_table,
-                                             int max_positions, void* k_cache, void* v_cache, const int* block_table,
+                                             int max_positions, int rotary_dim, int interleaved, void* k_cache, void* v_cache, const int* block_table,
                                              int table_stride, const int* context_lens, void* out, int out_stride,
                                              float* scratch, int requests, int heads, int kv_heads, int head_dim,
                                              int page_tokens, int num_pages, int split_keys, int splits, int* status,
                                              cudaStream_t stream) {
-  FusedTail extra{acc, bias, cos_table, sin_table, max_positions};
+  FusedTail extra{acc, bias, cos_table, sin_table, max_positions, rotary_dim, interleaved};
   return decode_launch(nullptr, 0, k_cache, v_cache, block_table, table_stride, context_lens, out, out_stride, scratch,
                        requests, heads, kv_heads, head_dim, page_tokens, num_pages, split_keys, splits, status, stream, &extra);
 }

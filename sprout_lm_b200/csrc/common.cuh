@@ -28,6 +28,9 @@ enum SproutStatus : int {
 
 int sprout_fail(const char* fmt, ...);   // records the message, returns 1
 int sprout_check_launch(const char* what);
+// Streaming multiprocessors of the current device (queried once per device; 148, the B200's count, where no
+// device can be asked, which only host-side plan inspection meets).
+extern "C" int sprout_sm_count();
 
 // Programmatic dependent launch.  Every kernel of the library is launched so that it may start
 // while the kernel before it in the stream still runs: it calls pdl_launch_dependents() at entry

@@ -138,19 +138,25 @@ rmsnorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ gain,
   }
 }
 
+// Which kernel runs.  A float32 output is the true 32-bit path, whose results must not depend on how
+// many rows a call brings: there the choice follows the row length alone (a warp per row with the
+// row in registers, or the block kernel with a block size fixed by the length), so a row's sum of
+// squares is added up in the same order whether it comes alone or among two thousand.  For
+// bfloat16 the choice also follows the number of rows (speed; the orders differ by rounding).
 template <typename TO>
 static void launch_rmsnorm(const float* x, const float* gain, TO* out, const int* rows, int num_rows, int hidden,
                            float eps, cudaStream_t stream) {
   const int quads = hidden / 4;
   const bool aligned = hidden % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)gain & 15) == 0 && ((uintptr_t)out & 15) == 0;
-  if (aligned && num_rows >= 64 && quads <= 512) {
+  const bool fixed_order = sizeof(TO) == 4;
+  if (aligned && (num_rows >= 64 || fixed_order) && quads <= 512) {
     const dim3 grid((num_rows + 7) / 8);
     if (quads <= 128) sprout_launch(rmsnorm_warp_kernel<TO, 4>, grid, dim3(256), 0, stream, x, gain, out, rows, num_rows, hidden, eps);
     else if (quads <= 256) sprout_launch(rmsnorm_warp_kernel<TO, 8>, grid, dim3(256), 0, stream, x, gain, out, rows, num_rows, hidden, eps);
     else sprout_launch(rmsnorm_warp_kernel<TO, 16>, grid, dim3(256), 0, stream, x, gain, out, rows, num_rows, hidden, eps);
   }
-  else if (aligned && quads <= 256) sprout_launch(rmsnorm_vec_kernel<TO, 1>, dim3(num_rows), dim3(256), 0, stream, x, gain, out, rows, hidden, eps);
-  else if (aligned && quads <= 512) sprout_launch(rmsnorm_vec_kernel<TO, 2>, dim3(num_rows), dim3(256), 0, stream, x, gain, out, rows, hidden, eps);
+  else if (aligned && !fixed_order && quads <= 256) sprout_launch(rmsnorm_vec_kernel<TO, 1>, dim3(num_rows), dim3(256), 0, stream, x, gain, out, rows, hidden, eps);
+  else if (aligned && !fixed_order && quads <= 512) sprout_launch(rmsnorm_vec_kernel<TO, 2>, dim3(num_rows), dim3(256), 0, stream, x, gain, out, rows, hidden, eps);
   else if (aligned && quads <= 1024) sprout_launch(rmsnorm_vec_kernel<TO, 4>, dim3(num_rows), dim3(256), 0, stream, x, gain, out, rows, hidden, eps);
   else if (aligned && quads <= 2048) sprout_launch(rmsnorm_vec_kernel<TO, 8>, dim3(num_rows), dim3(256), 0, stream, x, gain, out, rows, hidden, eps);
   else sprout_launch(rmsnorm_kernel<TO>, dim3(num_rows), dim3(hidden >= 1024 ? 256 : 128), 0, stream, x, gain, out, rows, hidden, eps);
@@ -168,33 +174,35 @@ SPROUT_API int sprout_rmsnorm(const float* x, const float* gain, void* out, int 
 }
 
 // ---------------------------------------------------------------- SwiGLU
-// Input rows hold gate and up interleaved in blocks of 8: columns [16b, 16b+8) are gate
-// values 8b..8b+7 and [16b+8, 16b+16) the matching up values.  out = silu(gate) * up with the
-// SiLU rounded to the element type's float32 value first.
+// Input rows hold gate and up interleaved in blocks of `block`: columns [2 block b, 2 block b + block)
+// are gate values block b .. block b + block - 1 and the next `block` columns the matching up values
+// (block 8 for the tensor-core products' fused gate/up matrix; block == inter for a plain
+// concatenation, gate first).  out = silu(gate) * up with the SiLU rounded to float32 first.
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int tokens, int inter) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int tokens, int inter, int block) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t total = (size_t)tokens * inter;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const int t = (int)(idx / inter), i = (int)(idx % inter);
     const T* row = gu + (size_t)t * 2 * inter;
-    const int col = (i >> 3) * 16 + (i & 7);
-    const float g = to_float(row[col]), u = to_float(row[col + 8]);
+    const int col = (i / block) * 2 * block + (i % block);
+    const float g = to_float(row[col]), u = to_float(row[col + block]);
     const float s = g / (1.0f + expf(-g));
     out[idx] = from_float<T>(s * u);
   }
 }
 
-SPROUT_API int sprout_swiglu(const void* gate_up, void* out, int dtype, int tokens, int inter, cudaStream_t stream) {
+SPROUT_API int sprout_swiglu(const void* gate_up, void* out, int dtype, int tokens, int inter, int block, cudaStream_t stream) {
   SPROUT_REQUIRE(tokens > 0 && inter > 0, "swiglu: sizes must be positive");
-  SPROUT_REQUIRE(inter % 8 == 0, "swiglu: the intermediate size must be a multiple of 8 (got %d)", inter);
+  SPROUT_REQUIRE(block > 0 && inter % block == 0, "swiglu: the intermediate size must be a multiple of %d, the gate/up block (got %d)", block, inter);
   const size_t total = (size_t)tokens * inter;
-  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  const size_t cap = (size_t)sprout_sm_count() * 16;
+  const int blocks = (int)((total + 255) / 256 < cap ? (total + 255) / 256 : cap);
   if (dtype == SPROUT_F32)
-    sprout_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, (float*)out, tokens, inter);
+    sprout_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, (float*)out, tokens, inter, block);
   else if (dtype == SPROUT_BF16)
-    sprout_launch(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, tokens, inter);
+    sprout_launch(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, tokens, inter, block);
   else
     return sprout_fail("swiglu: unknown dtype %d", dtype);
   return sprout_check_launch("swiglu");
@@ -202,15 +210,19 @@ SPROUT_API int sprout_swiglu(const void* gate_up, void* out, int dtype, int toke
 
 // ---------------------------------------------------------------- rotary positions + cache append
 // One block per token.  qkv rows hold [q heads | k heads | v heads].  q and k are rotated by
-// the token's position with half-split pairs (d, d + head_dim/2); q is rotated in place, the
-// rotated k and the unrotated v go to the token's slot of the paged cache:
+// the token's position; q is rotated in place, the rotated k and the unrotated v go to the
+// token's slot of the paged cache:
 //   page = block_table[seq, pos / page_tokens], slot = pos % page_tokens,
 //   element ((page * kv_heads + head) * page_tokens + slot) * head_dim + d.
-// cos/sin come from float32 tables [max_positions, head_dim/2] that the host fills from
-// float64 angles.  A page id outside the pool sets a status bit and skips the write.
+// The rotation takes the first `rotary_dim` elements of a head (head_dim: all of it) in pairs:
+// half-split pairs (d, d + rotary_dim/2), or with `interleaved` pairs (2d, 2d + 1); pair d turns by
+// the angle whose cosine and sine are cos/sin[pos, d].  The tables are float32
+// [max_positions, rotary_dim/2]; the host fills them from float64 angles.  Elements beyond
+// rotary_dim pass through.  A page id outside the pool sets a status bit and skips the write.
 // With `acc` given, the projections come from there instead: float32 sums [tokens, width] that a
 // split-K product accumulated, to which `bias` is added here; q is then written (rotated) to
-// qkv, and every element of acc that was read is set back to zero for the next product.
+// qkv, and every element of acc of the token is set back to zero for the next product (also when
+// the token's position is refused).
 template <typename T>
 __global__ void rope_append_kernel(T* __restrict__ qkv, float* acc, const float* __restrict__ bias,
                                    const int* __restrict__ positions,
@@ -218,21 +230,24 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, float* acc, const float*
                                    int table_stride, const float* __restrict__ cos_table,
                                    const float* __restrict__ sin_table, int max_positions,
                                    T* __restrict__ k_cache, T* __restrict__ v_cache, int heads, int kv_heads,
-                                   int head_dim, int page_tokens, int num_pages, int write_cache, int* status) {
+                                   int head_dim, int rotary_dim, int interleaved, int page_tokens, int num_pages,
+                                   int write_cache, int* status) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
-  const int half = head_dim >> 1;
+  const int half = head_dim >> 1, rot_half = rotary_dim >> 1;
   const int pos = positions[t];
   const bool rotate = cos_table != nullptr;   // no tables: no position encoding, q and k stay as projected
+  const int width = (heads + 2 * kv_heads) * head_dim;
+  float* acc_row = acc ? acc + (size_t)t * width : nullptr;
   if (pos < 0 || (rotate && pos >= max_positions)) {
     if (threadIdx.x == 0) atomicOr(status, SPROUT_STATUS_BAD_POSITION);
+    if (acc_row) for (int i = threadIdx.x; i < width; i += blockDim.x) acc_row[i] = 0.f;   // nothing stale for the next product
     return;
   }
-  const int width = (heads + 2 * kv_heads) * head_dim;
   T* row = qkv + (size_t)t * width;
-  const float* cs = rotate ? cos_table + (size_t)pos * half : nullptr;
-  const float* sn = rotate ? sin_table + (size_t)pos * half : nullptr;
+  const float* cs = rotate ? cos_table + (size_t)pos * rot_half : nullptr;
+  const float* sn = rotate ? sin_table + (size_t)pos * rot_half : nullptr;
   int page = 0, slot = 0;
   bool page_ok = false;
   if (write_cache) {
@@ -242,30 +257,34 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, float* acc, const float*
     page_ok = page >= 0 && page < num_pages;
     if (!page_ok && threadIdx.x == 0) atomicOr(status, SPROUT_STATUS_BAD_PAGE);
   }
-  float* acc_row = acc ? acc + (size_t)t * width : nullptr;
   auto value = [&](int i) -> float {
     if (!acc_row) return to_float(row[i]);
     const float v = acc_row[i] + (bias ? bias[i] : 0.f);
     acc_row[i] = 0.f;
     return v;
   };
-  // one thread per rotated pair: q heads in place, k heads into the cache
+  // one thread per pair of a head's elements: the first rotary_dim/2 pairs are rotated, the others
+  // (elements rotary_dim .. head_dim - 1, two by two) pass through; q heads in place, k heads into the cache
   for (int i = threadIdx.x; i < (heads + kv_heads) * half; i += blockDim.x) {
     const int h = i / half, d = i % half;
-    const float c = rotate ? cs[d] : 1.f, s = rotate ? sn[d] : 0.f;
+    const bool turned = rotate && d < rot_half;
+    int e0, e1;
+    if (d < rot_half) { e0 = interleaved ? 2 * d : d; e1 = interleaved ? 2 * d + 1 : d + rot_half; }
+    else { e0 = rotary_dim + 2 * (d - rot_half); e1 = e0 + 1; }
+    const float c = turned ? cs[d] : 1.f, s = turned ? sn[d] : 0.f;
     if (h < heads) {
-      if (!rotate && !acc_row) continue;
-      const float a = value(h * head_dim + d), b = value(h * head_dim + d + half);
+      if (!turned && !acc_row) continue;
+      const float a = value(h * head_dim + e0), b = value(h * head_dim + e1);
       T* x = row + h * head_dim;
-      x[d] = from_float<T>(a * c - b * s);
-      x[d + half] = from_float<T>(b * c + a * s);
+      x[e0] = from_float<T>(a * c - b * s);
+      x[e1] = from_float<T>(b * c + a * s);
     } else {
       const int kh = h - heads;
-      const float a = value(h * head_dim + d), b = value(h * head_dim + d + half);
+      const float a = value(h * head_dim + e0), b = value(h * head_dim + e1);
       if (page_ok) {
         T* dst = k_cache + (((size_t)page * kv_heads + kh) * page_tokens + slot) * head_dim;
-        dst[d] = from_float<T>(a * c - b * s);
-        dst[d + half] = from_float<T>(b * c + a * s);
+        dst[e0] = from_float<T>(a * c - b * s);
+        dst[e1] = from_float<T>(b * c + a * s);
       }
     }
   }
@@ -392,11 +411,14 @@ rope_append_acc_vec_kernel(__nv_bfloat16* __restrict__ qkv, float* __restrict__ 
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
     const int t = (int)(idx / per_token), item = (int)(idx % per_token);
     const int pos = positions[t];
+    float* acc_row = acc + (size_t)t * width;
     if (pos < 0 || (rotate && pos >= max_positions)) {
-      if (item == 0) atomicOr(status, SPROUT_STATUS_BAD_POSITION);
+      if (item == 0) {
+        atomicOr(status, SPROUT_STATUS_BAD_POSITION);
+        for (int i = 0; i < width; i += 4) *(float4*)(acc_row + i) = make_float4(0.f, 0.f, 0.f, 0.f);   // nothing stale for the next product
+      }
       continue;
     }
-    float* acc_row = acc + (size_t)t * width;
     int page = 0;
     bool page_ok = false;
     const bool to_cache = item >= heads * half_chunks;
@@ -439,14 +461,18 @@ rope_append_acc_vec_kernel(__nv_bfloat16* __restrict__ qkv, float* __restrict__ 
   }
 }
 
+// rotary_dim: how many leading elements of a head are rotated (even, at most head_dim; the tables are
+// [max_positions, rotary_dim / 2]); interleaved: pairs (2d, 2d + 1) instead of (d, d + rotary_dim / 2).
 SPROUT_API int sprout_rope_append(void* qkv, float* acc, const float* bias, int dtype, const int* positions, const int* seq_of_token,
                                   const int* block_table, int table_stride, const float* cos_table,
                                   const float* sin_table, int max_positions, void* k_cache, void* v_cache,
-                                  int num_tokens, int heads, int kv_heads, int head_dim, int page_tokens,
-                                  int num_pages, int write_cache, int* status, cudaStream_t stream) {
+                                  int num_tokens, int heads, int kv_heads, int head_dim, int rotary_dim, int interleaved,
+                                  int page_tokens, int num_pages, int write_cache, int* status, cudaStream_t stream) {
   SPROUT_REQUIRE(num_tokens > 0 && heads > 0 && kv_heads > 0 && page_tokens > 0 && num_pages > 0,
                  "rope_append: sizes must be positive");
   SPROUT_REQUIRE(head_dim > 0 && head_dim % 2 == 0, "rope_append: head_dim must be even (got %d)", head_dim);
+  SPROUT_REQUIRE(rotary_dim >= 0 && rotary_dim % 2 == 0 && rotary_dim <= head_dim,
+                 "rope_append: rotary_dim must be even and at most head_dim (got %d of %d)", rotary_dim, head_dim);
   SPROUT_REQUIRE(qkv && positions && seq_of_token && block_table && status, "rope_append: null pointer");
   SPROUT_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "rope_append: cos and sin tables go together");
   SPROUT_REQUIRE(!write_cache || (k_cache && v_cache), "rope_append: cache pointers missing");
@@ -454,18 +480,22 @@ SPROUT_API int sprout_rope_append(void* qkv, float* acc, const float* bias, int 
   const int threads = pairs >= 1024 ? 1024 : (pairs + 31) / 32 * 32;
   const bool aligned = ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0 &&
                        ((uintptr_t)cos_table & 15) == 0 && ((uintptr_t)sin_table & 15) == 0;
-  if (dtype == SPROUT_BF16 && acc && head_dim % 16 == 0 && aligned && ((uintptr_t)acc & 15) == 0 && ((uintptr_t)bias & 15) == 0 &&
+  // the 16-byte kernels are written for the whole head in half-split pairs (or no rotation at all)
+  const bool plain_pairs = !cos_table || (rotary_dim == head_dim && !interleaved);
+  if (dtype == SPROUT_BF16 && acc && plain_pairs && head_dim % 16 == 0 && aligned && ((uintptr_t)acc & 15) == 0 && ((uintptr_t)bias & 15) == 0 &&
       num_tokens >= 16) {
     const long long items = (long long)num_tokens * ((heads + kv_heads) * (head_dim / 16) + kv_heads * (head_dim / 8));
-    const int blocks = (int)((items + 255) / 256 < 148 * 8 ? (items + 255) / 256 : 148 * 8);
+    const long long cap = (long long)sprout_sm_count() * 8;
+    const int blocks = (int)((items + 255) / 256 < cap ? (items + 255) / 256 : cap);
     sprout_launch(rope_append_acc_vec_kernel, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)qkv, acc, bias, positions,
         seq_of_token, block_table, table_stride, cos_table, sin_table, max_positions, (__nv_bfloat16*)k_cache,
         (__nv_bfloat16*)v_cache, num_tokens, heads, kv_heads, head_dim, page_tokens, num_pages, write_cache, status);
     return sprout_check_launch("rope_append");
   }
-  if (dtype == SPROUT_BF16 && !acc && head_dim % 16 == 0 && aligned && num_tokens >= 64) {
+  if (dtype == SPROUT_BF16 && !acc && plain_pairs && head_dim % 16 == 0 && aligned && num_tokens >= 64) {
     const long long items = (long long)num_tokens * ((heads + kv_heads) * (head_dim / 16) + kv_heads * (head_dim / 8));
-    const int blocks = (int)((items + 255) / 256 < 148 * 8 ? (items + 255) / 256 : 148 * 8);
+    const long long cap = (long long)sprout_sm_count() * 8;
+    const int blocks = (int)((items + 255) / 256 < cap ? (items + 255) / 256 : cap);
     sprout_launch(rope_append_vec_kernel, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)qkv, positions, seq_of_token,
         block_table, table_stride, cos_table, sin_table, max_positions, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
         num_tokens, heads, kv_heads, head_dim, page_tokens, num_pages, write_cache, status);
@@ -474,12 +504,13 @@ SPROUT_API int sprout_rope_append(void* qkv, float* acc, const float* bias, int 
   if (dtype == SPROUT_F32)
     sprout_launch(rope_append_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream,
         (float*)qkv, acc, bias, positions, seq_of_token, block_table, table_stride, cos_table, sin_table, max_positions,
-        (float*)k_cache, (float*)v_cache, heads, kv_heads, head_dim, page_tokens, num_pages, write_cache, status);
+        (float*)k_cache, (float*)v_cache, heads, kv_heads, head_dim, rotary_dim, interleaved, page_tokens, num_pages,
+        write_cache, status);
   else if (dtype == SPROUT_BF16)
     sprout_launch(rope_append_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, stream,
         (__nv_bfloat16*)qkv, acc, bias, positions, seq_of_token, block_table, table_stride, cos_table, sin_table,
-        max_positions, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, heads, kv_heads, head_dim, page_tokens,
-        num_pages, write_cache, status);
+        max_positions, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, heads, kv_heads, head_dim, rotary_dim, interleaved,
+        page_tokens, num_pages, write_cache, status);
   else
     return sprout_fail("rope_append: unknown dtype %d", dtype);
   return sprout_check_launch("rope_append");

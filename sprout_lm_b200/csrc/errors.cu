@@ -31,5 +31,17 @@ int sprout_pdl_enabled() { return g_pdl; }
 // Turn programmatic dependent launch on (default) or off for all later launches.
 SPROUT_API void sprout_set_pdl(int enabled) { g_pdl = enabled ? 1 : 0; }
 
+SPROUT_API int sprout_sm_count() {
+  static int counts[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) { cudaGetLastError(); return 148; }
+  if (!counts[device]) {
+    int count = 0;
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0) { cudaGetLastError(); return 148; }
+    counts[device] = count;
+  }
+  return counts[device];
+}
+
 // Version of the exported interface; the Python side checks it after loading.
-SPROUT_API int sprout_abi_version() { return 4; }
+SPROUT_API int sprout_abi_version() { return 5; }

@@ -36,7 +36,7 @@ constexpr int FFN_THREADS = 256;            // 8 warps
 constexpr int FFN_MAX_TOKENS = SMALL_MAX_TOKENS;
 constexpr int FFN_MAX_TILES_PER_WARP = 4;   // gate/up tiles a warp accumulates (two warp groups share a CTA's tiles)
 constexpr int FFN_SMEM_LIMIT = 227 * 1024 - 1024;   // dynamic shared memory; the rest is for the kernel's static variables
-constexpr uint32_t FFN_SPIN_LIMIT = 1u << 22;
+constexpr uint32_t FFN_SPIN_LIMIT = 1u << 21;     // polls of the barrier counter (an L2 round trip each): a second or so
 
 struct FfnPlan {
   int tokens, hidden, inter;
@@ -49,20 +49,21 @@ struct FfnPlan {
   int stride1;           // bytes between the tokens' rows of the normalised operand in shared memory
   int off_w2, off_act, off_bar, smem_bytes;
   float eps;
+  unsigned spin_limit;   // polls of the barrier among the CTAs before a CTA gives up
 };
 
 __device__ __forceinline__ float ffn_silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
 // Barrier among all CTAs of the grid (all are resident: one per SM or fewer).  False when the
 // bounded wait ran out.
-__device__ __forceinline__ bool ffn_grid_barrier(unsigned* arrived, unsigned ctas) {
+__device__ __forceinline__ bool ffn_grid_barrier(unsigned* arrived, unsigned ctas, unsigned spin_limit) {
   __shared__ int passed;
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
     atomicAdd(arrived, 1u);
     int ok = 0;
-    for (uint32_t spins = 0; spins < FFN_SPIN_LIMIT; spins++) {
+    for (uint32_t spins = 0; spins < spin_limit; spins++) {
       unsigned seen;
       asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(arrived) : "memory");
       if (seen >= ctas) { ok = 1; break; }
@@ -267,7 +268,7 @@ ffn_decode_kernel(const __grid_constant__ CUtensorMap map_gu_base, const __grid_
   }
 
   // ---- every CTA's share of the activation is in memory after this
-  const bool through = ffn_grid_barrier(sync, (unsigned)ctas);
+  const bool through = ffn_grid_barrier(sync, (unsigned)ctas, p.spin_limit);
   if (!through && tid == 0) failed = 1;
 
   // ---- down: this CTA's K range of the activation into shared memory, then its row tiles
@@ -333,12 +334,15 @@ ffn_decode_kernel(const __grid_constant__ CUtensorMap map_gu_base, const __grid_
 
 namespace {
 
+unsigned g_spin_limit = FFN_SPIN_LIMIT;
+
 // The layout of a launch for these sizes on `ctas` CTAs; false when the sizes are outside the
 // kernel's rules or a CTA's share of the weights does not fit in shared memory.
 bool ffn_make_plan(int tokens, int hidden, int inter, int ctas, float eps, FfnPlan* out) {
   if (tokens < 1 || tokens > FFN_MAX_TOKENS || hidden < 16 || inter < 16 || hidden % 16 || inter % 16 || ctas < 1) return false;
   FfnPlan p = {};
   p.tokens = tokens; p.hidden = hidden; p.inter = inter; p.eps = eps;
+  p.spin_limit = g_spin_limit;
   p.tiles1 = inter / 8;
   p.tiles2 = hidden / 16;
   p.ksteps2 = inter / 16;
@@ -371,6 +375,10 @@ bool ffn_make_plan(int tokens, int hidden, int inter, int ctas, float eps, FfnPl
 }
 
 }  // namespace
+
+// How often a CTA of sprout_ffn_decode polls the barrier among the CTAs before it gives up, sets the
+// status word's WAIT_TIMEOUT bit and leaves (0: the default, about a second).  For tests of that path.
+SPROUT_API void sprout_set_spin_limit(unsigned polls) { g_spin_limit = polls ? polls : FFN_SPIN_LIMIT; }
 
 // 1 when sprout_ffn_decode takes these sizes on this device, else 0.
 SPROUT_API int sprout_ffn_decode_supported(int tokens, int hidden, int inter) {

@@ -65,7 +65,7 @@ sample_final_kernel(const float* __restrict__ logits, int ld, const float* __res
                     int* __restrict__ out, int vocab, int* status) {
   __shared__ Partial s_part[CHUNKS];
   __shared__ float s_prefix[FINAL_THREADS];
-  __shared__ int s_chunk, s_result;
+  __shared__ int s_chunk, s_result, s_last_weighted, s_best;
   __shared__ float s_before, s_top;
   pdl_launch_dependents();
   pdl_wait();
@@ -79,6 +79,8 @@ sample_final_kernel(const float* __restrict__ logits, int ld, const float* __res
     int best_i = 0x7fffffff, bad = 0;
     for (int c = 0; c < CHUNKS; c++) { better(best, best_i, s_part[c].max, s_part[c].index); bad |= s_part[c].bad; }
     s_top = best;
+    s_best = best_i;
+    s_last_weighted = -1;
     s_chunk = -1;
     if (bad) {
       out[r] = -1;
@@ -119,6 +121,7 @@ sample_final_kernel(const float* __restrict__ logits, int ld, const float* __res
   float local = 0.f;
   for (int i = begin; i < end; i++) local += __expf((row[i] - top) / temp);
   s_prefix[tid] = local;
+  if (local > 0.f) atomicMax(&s_last_weighted, tid);
   __syncthreads();
   if (warp == 0) {
     float run = 0.f;
@@ -136,21 +139,25 @@ sample_final_kernel(const float* __restrict__ logits, int ld, const float* __res
     for (int j = 0; j < FINAL_THREADS / 32; j++) { s_prefix[lane * (FINAL_THREADS / 32) + j] = excl; excl += mine[j]; }
   }
   __syncthreads();
-  // piece intervals [prefix[tid], prefix[tid + 1]) cover [0, inf) without gap or overlap
+  // Piece intervals [prefix[tid], prefix[tid + 1]) cover [0, inf) without gap or overlap; the last
+  // piece that has any weight reaches to infinity, so a target that rounding pushed past the total
+  // (the run's weight was summed in another order by the first kernel) lands on a token with
+  // probability above zero, never on a tail of zeros.
   const float before = s_prefix[tid];
-  const bool last_piece = (tid == FINAL_THREADS - 1) || (c_begin + (tid + 1) * seg >= c_end);
-  const float after = last_piece ? INFINITY : s_prefix[tid + 1];
-  if (begin < end && target >= before && target < after) {
+  const float after = tid == s_last_weighted ? INFINITY : (tid + 1 < FINAL_THREADS ? s_prefix[tid + 1] : before);
+  if (begin < end && local > 0.f && target >= before && target < after) {
     float run = before;
-    int pick = end - 1;
+    int pick = -1, last_weighted = begin;
     for (int i = begin; i < end; i++) {
-      run += __expf((row[i] - top) / temp);
+      const float e = __expf((row[i] - top) / temp);
+      run += e;
+      if (e > 0.f) last_weighted = i;
       if (target < run) { pick = i; break; }
     }
-    atomicMax(&s_result, pick);
+    atomicMax(&s_result, pick >= 0 ? pick : last_weighted);
   }
   __syncthreads();
-  if (tid == 0) out[r] = s_result >= 0 ? s_result : c_end - 1;
+  if (tid == 0) out[r] = s_result >= 0 ? s_result : s_best;      // a run without any weight cannot be picked; the maximum then
 }
 
 }  // namespace

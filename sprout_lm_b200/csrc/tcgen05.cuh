@@ -12,7 +12,16 @@
 
 namespace {
 
-constexpr uint32_t WAIT_LIMIT = 1u << 22;   // tries of mbarrier.try_wait (each blocks for a while)
+// A wait on an mbarrier gives up after about this long (a second or so: enough for any copy or product
+// of a step, short enough that a kernel whose partner never arrives returns while the caller still
+// waits for it).  The clock is read only now and then, and only while a wait is not satisfied.
+constexpr uint64_t WAIT_LIMIT_NS = 1500ull * 1000 * 1000;
+
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -31,14 +40,15 @@ __device__ __forceinline__ bool mbar_wait_addr(uint32_t addr, uint32_t parity, v
       "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
       : "=r"(done) : "r"(addr), "r"(parity) : "memory");
   if (done) return true;
-  for (uint32_t tries = 0; tries < WAIT_LIMIT; tries++) {
+  const uint64_t start = global_ns();
+  for (uint32_t tries = 1;; tries++) {
     asm volatile(
         "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
         : "=r"(done) : "r"(addr), "r"(parity) : "memory");
     if (done) return true;
     if (abort && *abort) return false;
+    if ((tries & 15) == 0 && global_ns() - start > WAIT_LIMIT_NS) return false;
   }
-  return false;
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort = nullptr) {
   return mbar_wait_addr(smem_u32(bar), parity, abort);
@@ -189,15 +199,16 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
 }
 // the bounded wait with acquire at cluster scope: the arrivals come from the other CTA of the pair
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t addr, uint32_t parity, volatile uint32_t* abort = nullptr) {
-  for (uint32_t tries = 0; tries < WAIT_LIMIT; tries++) {
+  const uint64_t start = global_ns();
+  for (uint32_t tries = 1;; tries++) {
     uint32_t done;
     asm volatile(
         "{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
         : "=r"(done) : "r"(addr), "r"(parity) : "memory");
     if (done) return true;
     if (abort && *abort) return false;
+    if ((tries & 15) == 0 && global_ns() - start > WAIT_LIMIT_NS) return false;
   }
-  return false;
 }
 
 // The same load without the wait, and the wait as a statement that the registers pass through:
@@ -284,14 +295,6 @@ int tensor_map(const void* ptr, int rows, int cols, int ld, int box_rows, CUtens
   return 0;
 }
 
-int sm_count() {
-  static int count = 0;
-  if (!count) {
-    int device = 0;
-    cudaGetDevice(&device);
-    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0) count = 148;
-  }
-  return count;
-}
+inline int sm_count() { return sprout_sm_count(); }
 
 }  // namespace

@@ -98,6 +98,7 @@ class DecodeGraph:
         self.graph = None
         self.tokens = None
         self.logits = None
+        self.last_logits = None           # float32 [requests, vocab] of the step that ran last (tests read them)
         self.launches = 0
 
     def _put(self, name, values):
@@ -172,7 +173,7 @@ class DecodeGraph:
             # without running, so the step has run exactly once: a mixer that updates
             # per-request state must not see a step twice.
             ctx = self.stage(entries, temperatures, uniforms)
-            _, tokens = self._forward(ctx)
+            self.last_logits, tokens = self._forward(ctx)
             result = tokens.tolist()
             self.host_tokens = torch.zeros(self.requests, dtype=torch.int32).pin_memory()
             before = kernels.LAUNCHES
@@ -187,17 +188,29 @@ class DecodeGraph:
         self.stage(entries, temperatures, uniforms, copy=False)
         self.graph.replay()
         torch.cuda.current_stream().synchronize()      # the tokens are in pinned memory, the mirror has been read
+        self.last_logits = self.logits
         return self.host_tokens.tolist()
 
 
 class GraphCache:
-    def __init__(self, runner, page_multiple: int = 64):
+    """Captured decode steps, by (number of requests, table width, the parts' launch plans).
+
+    A serving loop meets many keys: every batch size, a wider table every ``page_multiple`` pages,
+    another attention plan every few 128 keys of context.  Each capture owns device memory (its
+    activations and its [requests, vocabulary] float32 logits), a pinned mirror and a CUDA graph,
+    so at most ``limit`` are kept; the least recently used one is dropped when another is needed
+    (outside any capture: ``get`` runs before the step is staged)."""
+
+    def __init__(self, runner, page_multiple: int = 64, limit: int = 24):
         self.runner = runner
         self.page_multiple = page_multiple
-        self.graphs: dict = {}
+        self.limit = max(1, limit)
+        self.graphs: dict = {}             # insertion order is the order of last use
         self.enabled = True
+        self.evictions = 0
+        self.keys_used = 0                 # keys asked for that were not held (captures made or to be made)
 
-    def get(self, entries) -> DecodeGraph:
+    def key_for(self, entries):
         pages = 1
         for e in entries:
             for table in e.seq.tables:
@@ -210,11 +223,23 @@ class GraphCache:
         longest = 1 + max(e.seq.length for e in entries)
         planned = min(width * self.runner.page_tokens, _round_up(longest, 128))
         plan = self.runner.model.decode_plan(len(entries), width * self.runner.page_tokens, planned)
-        key = (len(entries), width, plan)
-        graph = self.graphs.get(key)
+        return (len(entries), width, plan), width, planned
+
+    def get(self, entries) -> DecodeGraph:
+        key, width, planned = self.key_for(entries)
+        graph = self.graphs.pop(key, None)
         if graph is None:
-            graph = self.graphs[key] = DecodeGraph(self.runner, len(entries), width, planned)
+            self.keys_used += 1
+            while len(self.graphs) >= self.limit:
+                oldest = next(iter(self.graphs))
+                del self.graphs[oldest]    # its CUDA graph, buffers and pinned mirror go with it
+                self.evictions += 1
+            graph = self.make(len(entries), width, planned)
+        self.graphs[key] = graph           # most recently used: last
         return graph
+
+    def make(self, requests: int, width: int, planned: int) -> DecodeGraph:
+        return DecodeGraph(self.runner, requests, width, planned)
 
 
 class StepGraphs:
@@ -300,8 +325,9 @@ class StepGraphs:
 class DecodeLoop:
     """``steps`` decode steps on the device without the host in between: after each step a
     kernel makes the sampled tokens the next inputs.  Pages for all the steps must have been
-    reserved.  Used when no request can finish or arrive in between, and by the benchmark to
-    time the device's share of a decode step."""
+    reserved.  The scheduler does not use it (it looks at every token for end-of-sequence); the
+    benchmark times the device's share of a decode step with it, and the tests hold its tokens
+    against the scheduler's."""
 
     def __init__(self, runner, entries, temperatures, uniforms, max_steps: int):
         self.runner = runner

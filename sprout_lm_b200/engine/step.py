@@ -42,6 +42,7 @@ class ModelRunner:
         self.max_positions = model.spec.max_positions
         self.eos_token_ids = tuple(model.spec.eos_token_ids)
         self.steps_run = 0
+        self.last_decode_graph = None      # the captured decode step that ran last
         # bytes copied to and from the device by steps (the batch's arrays up, token ids or logits down)
         self.stats = {"h2d_bytes": 0, "d2h_bytes": 0}
         from .graphs import GraphCache, StepGraphs
@@ -130,7 +131,7 @@ class ModelRunner:
         self.validate(entries)
         decode_only = self.graphs.enabled and all(len(e.tokens) == 1 and e.want == [0] for e in entries)
         if decode_only:
-            graph = self.graphs.get(entries)
+            graph = self.last_decode_graph = self.graphs.get(entries)
             sampled = graph.run(entries, temperatures, uniforms)
             self.stats["h2d_bytes"] += graph.stager.last_bytes
             self.stats["d2h_bytes"] += len(sampled) * 4
@@ -170,13 +171,21 @@ class ModelRunner:
         return DecodeLoop(self, entries, temperatures, uniforms, max_steps)
 
     def forward(self, ctx: StepContext):
-        return self.model.forward(ctx, self.storage)
+        try:
+            return self.model.forward(ctx, self.storage)
+        except BaseException:
+            # a launch was refused between a product into a workspace and the kernel that empties it
+            self.runtime.reset_workspaces()
+            raise
 
     def check_status(self) -> None:
-        """Read the device status word (synchronises); raise if a kernel flagged bad input."""
+        """Read the device status word (synchronises); raise if a kernel flagged bad input.  A
+        flagged step may have left sums in the accumulation workspaces: they are zeroed, so that the
+        next step starts clean."""
         word = int(self.runtime.status.item())
         if word:
             self.runtime.status.zero_()
+            self.runtime.reset_workspaces()
             raise StepError("device status: " + kernels.describe_status(word))
 
     # ------------------------------------------------------------------ sampling

@@ -31,14 +31,14 @@ _P, _I, _F = c_void_p, c_int, c_float
 _SIGNATURES = {
     "sprout_embed": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
     "sprout_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
-    "sprout_swiglu": [_P, _P, _I, _I, _I, _P],
-    "sprout_rope_append": [_P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_swiglu": [_P, _P, _I, _I, _I, _I, _P],
+    "sprout_rope_append": [_P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_gemm_simple": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "sprout_attention_simple": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_sample": [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P],
     "sprout_advance_decode": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
     "sprout_attention_decode": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
-    "sprout_attention_decode_fused": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_attention_decode_fused": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, ctypes.c_longlong, _P, _P, _P],
     "sprout_attention_prefill_tc_supported": [_I, _I, _I],
     "sprout_gemm_bf16": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
@@ -71,6 +71,10 @@ def load_library(verbose: bool = True):
                 fn.restype = c_int
             lib.sprout_set_pdl.argtypes = [c_int]
             lib.sprout_set_pdl.restype = None
+            lib.sprout_set_spin_limit.argtypes = [ctypes.c_uint]
+            lib.sprout_set_spin_limit.restype = None
+            lib.sprout_sm_count.argtypes = []
+            lib.sprout_sm_count.restype = c_int
             if os.environ.get("SPROUT_PDL", "1") == "0":
                 lib.sprout_set_pdl(0)
             _lib = lib
@@ -80,6 +84,26 @@ def load_library(verbose: bool = True):
 def set_pdl(enabled: bool) -> None:
     """Programmatic dependent launch of all kernels on (the default) or off."""
     load_library().sprout_set_pdl(1 if enabled else 0)
+
+
+def set_spin_limit(polls: int) -> None:
+    """How often a CTA of ``ffn_decode`` polls the barrier among its CTAs before it gives up and
+    sets the status word's wait bit (0: the default, about a second)."""
+    load_library().sprout_set_spin_limit(int(polls))
+
+
+_sm_counts: dict = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of ``device`` (the current one by default), asked once."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    if index is None:
+        index = torch.cuda.current_device()
+    count = _sm_counts.get(index)
+    if count is None:
+        count = _sm_counts[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+    return count
 
 
 def library_file() -> str:
@@ -156,19 +180,26 @@ def rmsnorm(x, gain, out, eps, rows=None):
          _dtype_code(out.dtype), _ptr(rows, "rows", torch.int32, allow_none=True), R, H, float(eps), _stream())
 
 
-def swiglu(gate_up, out):
-    """out = silu(gate) * up for rows that interleave gate and up in blocks of 8."""
+def swiglu(gate_up, out, block: int = 8):
+    """out = silu(gate) * up for rows that interleave gate and up in blocks of ``block`` columns
+    (8: the tensor-core products' fused matrix; the intermediate size itself: gate rows first, then
+    up rows)."""
     if not gate_up.is_contiguous() or not out.is_contiguous() or gate_up.dtype != out.dtype:
         raise KernelError("swiglu: tensors must be contiguous and of one dtype")
     T, I = out.shape
     if tuple(gate_up.shape) != (T, 2 * I):
         raise KernelError("swiglu: gate_up must be [tokens, 2 * intermediate]")
-    _run("sprout_swiglu", _ptr(gate_up, "gate_up"), _ptr(out, "out"), _dtype_code(out.dtype), T, I, _stream())
+    _run("sprout_swiglu", _ptr(gate_up, "gate_up"), _ptr(out, "out"), _dtype_code(out.dtype), T, I, int(block), _stream())
 
 
 def rope_append(qkv, positions, seq_of_token, block_table, cos_table, sin_table, k_cache, v_cache,
-                heads, kv_heads, head_dim, page_tokens, write_cache, status, acc=None, bias=None):
+                heads, kv_heads, head_dim, page_tokens, write_cache, status, acc=None, bias=None,
+                interleaved=False):
     """Rotate q and k of every token by its position; store rotated k and v in the paged cache.
+
+    The tables are float32 [max_positions, rotary_dim / 2]: the first ``rotary_dim`` elements of a
+    head turn (all of it when the tables are head_dim / 2 wide), in half-split pairs
+    (d, d + rotary_dim / 2) or, with ``interleaved``, in pairs (2d, 2d + 1); the rest pass through.
 
     k_cache and v_cache are [pages, kv_heads, page_tokens, head_dim].  With ``acc`` (float32
     [tokens, width], row stride = width) the projections are read from there plus ``bias``
@@ -180,9 +211,11 @@ def rope_append(qkv, positions, seq_of_token, block_table, cos_table, sin_table,
         raise KernelError("rope_append: one position and one sequence index per token")
     if (cos_table is None) != (sin_table is None):
         raise KernelError("rope_append: cos and sin tables go together")
-    if cos_table is not None and (cos_table.shape != sin_table.shape or cos_table.shape[1] != head_dim // 2
+    if cos_table is not None and (cos_table.shape != sin_table.shape or cos_table.dim() != 2
+                                  or not 0 < cos_table.shape[1] <= head_dim // 2
                                   or not cos_table.is_contiguous() or not sin_table.is_contiguous()):
-        raise KernelError("rope_append: cos/sin tables must be contiguous [max_positions, head_dim / 2]")
+        raise KernelError("rope_append: cos/sin tables must be contiguous [max_positions, rotary_dim / 2] with rotary_dim <= head_dim")
+    rotary_dim = 2 * cos_table.shape[1] if cos_table is not None else 0
     num_pages = 1
     if write_cache:
         for name, cache in (("k_cache", k_cache), ("v_cache", v_cache)):
@@ -200,8 +233,9 @@ def rope_append(qkv, positions, seq_of_token, block_table, cos_table, sin_table,
          _ptr(seq_of_token, "seq_of_token", torch.int32), _ptr(block_table, "block_table", torch.int32),
          block_table.stride(0), _ptr(cos_table, "cos", torch.float32, True), _ptr(sin_table, "sin", torch.float32, True),
          cos_table.shape[0] if cos_table is not None else 0, _ptr(k_cache, "k_cache", allow_none=not write_cache),
-         _ptr(v_cache, "v_cache", allow_none=not write_cache), T, heads, kv_heads, head_dim, page_tokens,
-         num_pages, 1 if write_cache else 0, _ptr(status, "status", torch.int32), _stream())
+         _ptr(v_cache, "v_cache", allow_none=not write_cache), T, heads, kv_heads, head_dim, rotary_dim,
+         1 if interleaved else 0, page_tokens, num_pages, 1 if write_cache else 0,
+         _ptr(status, "status", torch.int32), _stream())
 
 
 def gemm_simple(a, weight, out, bias=None, residual=None):
@@ -311,11 +345,13 @@ LINEAR_PLAN_FIELDS = ("tiles", "ksteps", "row_groups", "k_splits", "max_tiles", 
                       "off_gain", "off_stage", "off_bar", "smem_bytes")
 
 
-def small_batch_plan(kind: str, tokens: int, rows: int, cols: int, ctas: int = 148) -> dict | None:
+def small_batch_plan(kind: str, tokens: int, rows: int, cols: int, ctas: int | None = None) -> dict | None:
     """How a small-batch kernel would lay a launch out on ``ctas`` CTAs (host arithmetic of the
     kernel library, no GPU needed), or None where it refuses the sizes.  ``kind`` "ffn": rows is
     the hidden size, cols the intermediate size; "linear": a [rows, cols] matrix."""
     lib = _lib or load_library()
+    if ctas is None:
+        ctas = lib.sprout_sm_count()       # the current device's; a B200's 148 where there is none
     names = FFN_PLAN_FIELDS if kind == "ffn" else LINEAR_PLAN_FIELDS
     fn = lib.sprout_ffn_decode_plan if kind == "ffn" else lib.sprout_linear_decode_plan
     fn.argtypes = [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int)]
@@ -370,11 +406,8 @@ def _check_paged(q, k_cache, v_cache, block_table, out, heads, head_dim, name):
         raise KernelError(f"{name}: q, out and the caches must be bfloat16")
 
 
-SM_COUNT = 148
-
-
 def decode_split_plan(requests: int, kv_heads: int, max_keys: int, head_dim: int = 64,
-                      live_keys: int | None = None) -> tuple[int, int, bool]:
+                      live_keys: int | None = None, sms: int | None = None) -> tuple[int, int, bool]:
     """(keys per split, splits, whether scratch memory is needed) for decode attention over at
     most ``max_keys`` keys (the block tables' width), of which about ``live_keys`` are expected
     to hold keys (a replayed graph's tables are wider than its contexts; splits beyond a
@@ -389,13 +422,15 @@ def decode_split_plan(requests: int, kv_heads: int, max_keys: int, head_dim: int
     small batch gets many short splits (latency), a large one few long ones (no idle waves, no
     merge kernel), and a long context as many splits as keep the SMs busy."""
     live = max_keys if live_keys is None else max(1, min(max_keys, live_keys))
-    return _decode_split_plan(requests * kv_heads, -(-max_keys // 128), -(-live // 128), head_dim)
+    if sms is None:
+        sms = sm_count() if torch.cuda.is_available() else 148      # host-side inspection without a device: a B200's count
+    return _decode_split_plan(requests * kv_heads, -(-max_keys // 128), -(-live // 128), head_dim, sms)
 
 
 @functools.lru_cache(maxsize=4096)
-def _decode_split_plan(pairs: int, total_passes: int, live_passes: int, head_dim: int) -> tuple[int, int, bool]:
+def _decode_split_plan(pairs: int, total_passes: int, live_passes: int, head_dim: int, sms: int) -> tuple[int, int, bool]:
     shared = (16 + 256) * (head_dim + 8) * 2 + (16 * head_dim + 32) * 4 + 128 * 8      # the tensor-core kernel's, per CTA
-    slots = SM_COUNT * max(1, min(16, (227 * 1024) // (shared + 1024)))
+    slots = sms * max(1, min(16, (227 * 1024) // (shared + 1024)))
     total_passes = max(1, total_passes)
     best, best_cost, last_splits = (128 * total_passes, 1, False), None, 0
     for passes in range(1, total_passes + 1):
@@ -457,12 +492,14 @@ def decode_fusable(requests: int, heads: int, kv_heads: int, head_dim: int, max_
 
 
 def attention_decode_fused(acc, bias, cos_table, sin_table, k_cache, v_cache, block_table, context_lens, out,
-                           heads, kv_heads, head_dim, status, live_keys=None):
+                           heads, kv_heads, head_dim, status, live_keys=None, interleaved=False, scratch=None):
     """Decode attention with the q/k/v projection's tail folded in.  ``acc`` holds, for each
     request's new token, the float32 sums [requests, (heads + 2 kv_heads) * head_dim] of a split-K
     product; the kernel adds ``bias``, rotates q and k by the position context_lens - 1 (tables
-    may be None), appends k and v to the paged cache, attends over context_lens keys and leaves
-    ``acc`` zeroed.  ``out`` is bfloat16 [requests, heads * head_dim]."""
+    [max_positions, rotary_dim / 2] and ``interleaved`` as for ``rope_append``; None: no rotation),
+    appends k and v to the paged cache, attends over context_lens keys and leaves ``acc`` zeroed.
+    ``out`` is bfloat16 [requests, heads * head_dim].  ``scratch``: float32 memory for the splits'
+    partial results where the plan merges through memory (allocated here when not given)."""
     R = out.shape[0]
     width = (heads + 2 * kv_heads) * head_dim
     if acc.dtype != torch.float32 or tuple(acc.shape) != (R, width) or not acc.is_contiguous():
@@ -479,13 +516,20 @@ def attention_decode_fused(acc, bias, cos_table, sin_table, k_cache, v_cache, bl
     split_keys, splits, through_memory = decode_split_plan(R, kv_heads, max_keys, head_dim, live_keys)
     if not decode_fusable(R, heads, kv_heads, head_dim, max_keys):
         raise KernelError("attention_decode_fused: these sizes need the separate kernels (see decode_fusable)")
-    scratch = None
+    if cos_table is not None and (cos_table.shape != sin_table.shape or cos_table.dim() != 2
+                                  or not 0 < cos_table.shape[1] <= head_dim // 2
+                                  or not cos_table.is_contiguous() or not sin_table.is_contiguous()):
+        raise KernelError("attention_decode_fused: cos/sin tables must be contiguous [max_positions, rotary_dim / 2]")
     if through_memory:            # many splits or a large batch: independent CTAs and a merge kernel
         need = load_library().sprout_attention_decode_scratch_floats(R, heads, head_dim, splits)
-        scratch = torch.empty(need, dtype=torch.float32, device=out.device)
+        if scratch is None or scratch.numel() < need:
+            scratch = torch.empty(need, dtype=torch.float32, device=out.device)
+    else:
+        scratch = None
     _run("sprout_attention_decode_fused", _ptr(acc, "acc"), _ptr(bias, "bias", torch.float32, True),
          _ptr(cos_table, "cos", torch.float32, True), _ptr(sin_table, "sin", torch.float32, True),
-         cos_table.shape[0] if cos_table is not None else 0, _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"),
+         cos_table.shape[0] if cos_table is not None else 0, 2 * cos_table.shape[1] if cos_table is not None else 0,
+         1 if interleaved else 0, _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"),
          _ptr(block_table, "block_table", torch.int32), block_table.stride(0),
          _ptr(context_lens, "context_lens", torch.int32), _ptr(out, "out"), out.stride(0),
          _ptr(scratch, "scratch", torch.float32, True), R, heads, kv_heads, head_dim,

@@ -16,6 +16,13 @@ from ..parts import Runtime, WeightSource, build_block, build_part
 from ..weights.checkpoint import Checkpoint
 
 
+WEIGHT_RESERVE_BYTES = 1 << 30       # left free beside the weights when a model is loaded
+
+
+class WeightCapacityError(RuntimeError):
+    """The model's weights do not fit the budget or the device's free memory."""
+
+
 class DecoderModel:
     def __init__(self, spec: ModelSpec):
         self.spec = spec
@@ -40,9 +47,35 @@ class DecoderModel:
                 decls.append(decl)
         return decls
 
-    def load(self, checkpoint: Checkpoint, runtime: Runtime) -> None:
+    def weight_bytes(self, dtype: torch.dtype) -> int:
+        """Device bytes of the resident weights at compute dtype ``dtype``: matrices in that dtype,
+        gains and biases in float32."""
+        item = torch.empty((), dtype=dtype).element_size()
+        total = 0
+        for decl in self.tensor_decls():
+            count = 1
+            for n in decl.shape:
+                count *= n
+            total += count * (item if decl.init == "matrix" else 4)
+        return total
+
+    def load(self, checkpoint: Checkpoint, runtime: Runtime, weight_budget_bytes: int | None = None,
+             reserve_bytes: int = WEIGHT_RESERVE_BYTES) -> None:
+        """Check the folder's tensors against what the parts declare, check that the weights fit
+        the device, then load part by part.  Nothing is copied to the device before both checks
+        have passed (the reference's resident upload refuses the same two ways,
+        native/cuda-offload.cu:249-252)."""
         expected = {decl.name: decl.shape for decl in self.tensor_decls()}
         checkpoint.check(expected, ignorable=self.spec.ignorable_tensors)
+        need = self.weight_bytes(runtime.dtype)
+        if weight_budget_bytes is not None and need > weight_budget_bytes:
+            raise WeightCapacityError(f"Resident weight budget exceeded: the model's weights take {need / 2**30:.2f} GiB, "
+                                      f"the budget is {weight_budget_bytes / 2**30:.2f} GiB.")
+        free, _ = torch.cuda.mem_get_info(runtime.device)
+        if need + reserve_bytes > free:
+            raise WeightCapacityError(f"Insufficient free CUDA memory after reserve: the model's weights take "
+                                      f"{need / 2**30:.2f} GiB, {free / 2**30:.2f} GiB are free and "
+                                      f"{reserve_bytes / 2**30:.2f} GiB are kept for the cache pool's start and activations.")
         source = WeightSource(lambda name: checkpoint.tensor(name, expected.get(name)), runtime)
         for part in self.parts():
             part.load(source)
@@ -86,14 +119,16 @@ class DecoderModel:
         return self.head.forward(self.final_norm.forward(x, rows=ctx.logits_rows))
 
 
-def load_model(directory, dtype=torch.bfloat16, device="cuda:0"):
+def load_model(directory, dtype=torch.bfloat16, device="cuda:0", weight_budget_bytes: int | None = None):
     """Model of a folder (config.json + model.safetensors or an index of shards), chosen by
-    the folder's config.json through the architecture registry."""
+    the folder's config.json through the architecture registry.  ``weight_budget_bytes`` bounds the
+    device memory the weights may take; a model beyond it, or beyond the device's free memory, is
+    refused before its first tensor is copied."""
     directory = Path(directory)
     config = load_config(directory)
     model = DecoderModel(config.model_spec())
     runtime = Runtime(device, dtype)
     with Checkpoint(directory) as checkpoint:
-        model.load(checkpoint, runtime)
+        model.load(checkpoint, runtime, weight_budget_bytes=weight_budget_bytes)
     model.config = config
     return model

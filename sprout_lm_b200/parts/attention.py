@@ -15,18 +15,14 @@ from .base import CacheSpec, CacheView, Part, TensorDecl, WeightSource, build_pa
 from .linear import Linear
 
 
-_WORKSPACES: dict = {}
-
-
 @register_part("mixer", "gqa_attention")
 class PagedGQAttention(Part):
     def __init__(self, prefix: str, hidden_size: int, heads: int, kv_heads: int, head_dim: int,
                  position: PartSpec, qkv_bias: bool = True, out_bias: bool = False, names: dict | None = None):
         if heads % kv_heads:
             raise ValueError(f"attention: heads ({heads}) must be a multiple of kv_heads ({kv_heads})")
-        if head_dim % 16 or head_dim > 256:
-            raise ValueError(f"attention: head_dim must be a multiple of 16 up to 256 (got {head_dim}); "
-                             "the kernels are written for head sizes in steps of 16")
+        if head_dim <= 0 or head_dim % 2 or head_dim > 256:
+            raise ValueError(f"attention: head_dim must be even and at most 256 (got {head_dim})")
         self.hidden_size, self.heads, self.kv_heads, self.head_dim = hidden_size, heads, kv_heads, head_dim
         self.qkv_bias, self.out_bias = qkv_bias, out_bias
         names = names or {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj"}
@@ -34,6 +30,7 @@ class PagedGQAttention(Part):
         self.position = build_part("position", position)
         self.qkv = self.out = None
         self.tables = None
+        self.interleaved = False
         self.runtime = None
 
     # ---- what it keeps
@@ -67,6 +64,10 @@ class PagedGQAttention(Part):
 
     def load(self, source: WeightSource):
         self.runtime = source.runtime
+        if source.runtime.dtype == torch.bfloat16 and self.head_dim % 16:
+            raise ValueError(f"attention: on the bfloat16 path head_dim must be a multiple of 16 (got {self.head_dim}): "
+                             "the tensor-core kernels are written for head sizes in steps of 16; the float32 path "
+                             "takes any even head size up to 256")
         fused = torch.cat([source.raw(self.names[key] + ".weight") for key in ("q", "k", "v")], dim=0)
         bias = None
         if self.qkv_bias:
@@ -76,20 +77,22 @@ class PagedGQAttention(Part):
         out_bias = source.vector(self.names["o"] + ".bias") if self.out_bias else None
         self.out = Linear(source.matrix(self.names["o"] + ".weight"), out_bias, source.runtime.status)
         self.tables = self.position.rotary_tables(source.runtime)
+        self.interleaved = bool(getattr(self.position, "interleaved", False))
+        if self.tables is not None:
+            cos, sin = self.tables
+            if cos.shape != sin.shape or cos.dim() != 2 or not 0 < cos.shape[1] <= self.head_dim // 2:
+                raise ValueError("attention: the position part's tables must be [max_positions, rotary_dim / 2] with "
+                                 f"rotary_dim <= head_dim (got {tuple(cos.shape)} for head_dim {self.head_dim})")
 
     # ---- the step
     SPLIT_TOKENS = 256          # up to this many tokens the q/k/v product is split along K
 
-    def _workspace(self, device):
+    def _workspace(self):
         """A zeroed float32 buffer [SPLIT_TOKENS, width] that split-K products accumulate into;
-        the rotary kernel reads it and sets it back to zero, so one buffer per device and width
-        serves every layer and every step."""
-        key = (str(device), self.qkv.out_features)
-        buffer = _WORKSPACES.get(key)
-        if buffer is None:
-            buffer = _WORKSPACES[key] = torch.zeros((self.SPLIT_TOKENS, self.qkv.out_features), dtype=torch.float32,
-                                                    device=device)
-        return buffer
+        the rotary kernel reads it and sets it back to zero, so one buffer per model (its runtime)
+        and width serves every layer and every step.  A step that fails in between leaves sums
+        behind: the runtime zeroes its workspaces then (``Runtime.reset_workspaces``)."""
+        return self.runtime.workspace(("qkv_sums", self.qkv.out_features), (self.SPLIT_TOKENS, self.qkv.out_features))
 
     def forward_with_norm(self, norm, x, ctx, cache: CacheView, state=None) -> bool:
         """The mixer with the norm before it folded into the q/k/v product, when the batch and the
@@ -108,7 +111,7 @@ class PagedGQAttention(Part):
             # few tokens: the product is a stream of weights, and a CTA streams only about 1/148 of
             # the memory bandwidth; split K so that every SM streams a share, accumulate in float32
             # and let the rotary kernel add the bias, rotate, convert and clear
-            acc = self._workspace(x.device)[:tokens]
+            acc = self._workspace()[:tokens]
             if norm is None or not self.qkv.accumulate_normed(norm, x, acc):
                 self.qkv.accumulate(h if h is not None else norm.forward(x), acc)
             attended = torch.empty((tokens, self.heads * self.head_dim), dtype=dtype, device=x.device)
@@ -118,18 +121,19 @@ class PagedGQAttention(Part):
                 # one token per request: bias, rotation and the cache append happen inside the attention kernel
                 kernels.attention_decode_fused(acc, self.qkv.bias, cos, sin, cache.k, cache.v, cache.block_table,
                                                ctx.context_lens, attended, self.heads, self.kv_heads, self.head_dim,
-                                               self.runtime.status, live_keys=ctx.planned_context or ctx.max_context)
+                                               self.runtime.status, live_keys=ctx.planned_context or ctx.max_context,
+                                               interleaved=self.interleaved)
                 self.out.forward(attended, residual=x)
                 return
             qkv = torch.empty((tokens, self.qkv.out_features), dtype=dtype, device=x.device)
             kernels.rope_append(qkv, ctx.positions, ctx.seq_of_token, cache.block_table, cos, sin, cache.k, cache.v,
                                 self.heads, self.kv_heads, self.head_dim, cache.page_tokens, cache.write,
-                                self.runtime.status, acc=acc, bias=self.qkv.bias)
+                                self.runtime.status, acc=acc, bias=self.qkv.bias, interleaved=self.interleaved)
         else:
             qkv = self.qkv.forward(h)
             kernels.rope_append(qkv, ctx.positions, ctx.seq_of_token, cache.block_table, cos, sin, cache.k, cache.v,
                                 self.heads, self.kv_heads, self.head_dim, cache.page_tokens, cache.write,
-                                self.runtime.status)
+                                self.runtime.status, interleaved=self.interleaved)
         q = qkv[:, :self.heads * self.head_dim]
         attended = torch.empty((tokens, self.heads * self.head_dim), dtype=qkv.dtype, device=qkv.device)
         kernels.paged_attention(q, cache, ctx, attended, self.heads, self.kv_heads, self.head_dim,

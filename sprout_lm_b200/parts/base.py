@@ -11,8 +11,10 @@ Categories and what each must provide:
                      [tokens, hidden]; ``h`` has the compute dtype.  ``rows`` (int32 indices)
                      selects the rows to produce.
 * ``position``:      ``rotary_tables(runtime) -> (cos, sin) | None``: float32 tables
-                     [max_positions, head_dim / 2] for half-split rotation, or None for no
-                     rotation.
+                     [max_positions, rotary_dim / 2] (None: no rotation).  The first
+                     ``rotary_dim`` elements of a head turn, pair d by the angle whose cosine and
+                     sine stand at [position, d]; pairs are (d, d + rotary_dim / 2), or (2d, 2d + 1)
+                     when the part has a true attribute ``interleaved``.
 * ``mixer``:         ``cache_spec() -> CacheSpec | None`` (what it keeps per token),
                      ``state_spec() -> StateSpec | None`` (what it keeps per request, of fixed
                      size), ``forward(h, x, ctx, cache, state)``: reads the normed activations
@@ -116,8 +118,9 @@ class StateView:
 
 class Runtime:
     """Where and how a model computes: the device, the compute dtype (float32 for the true
-    32-bit path, bfloat16 for serving) and the device status word that kernels set instead of
-    faulting."""
+    32-bit path, bfloat16 for serving), the device status word that kernels set instead of
+    faulting, and what the model's parts share on the device: zeroed accumulation workspaces
+    (``workspace``) and read-only tables such as rotary cosines (``shared``)."""
 
     def __init__(self, device="cuda:0", dtype=torch.bfloat16):
         if dtype not in (torch.float32, torch.bfloat16):
@@ -129,6 +132,29 @@ class Runtime:
             raise RuntimeError("no CUDA device is available; sprout_lm_b200 has no CPU fallback.")
         self.dtype = dtype
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.sm_count = int(torch.cuda.get_device_properties(self.device).multi_processor_count)
+        self._workspaces: dict = {}
+        self._shared: dict = {}
+
+    def workspace(self, key, shape, dtype=torch.float32) -> torch.Tensor:
+        """A zeroed buffer that belongs to this runtime (one model's steps on one stream), made at
+        first use.  Whoever accumulates into it leaves it zero again; after a step that failed or
+        that flagged its input, ``reset_workspaces`` restores that."""
+        buffer = self._workspaces.get(key)
+        if buffer is None:
+            buffer = self._workspaces[key] = torch.zeros(shape, dtype=dtype, device=self.device)
+        return buffer
+
+    def reset_workspaces(self) -> None:
+        for buffer in self._workspaces.values():
+            buffer.zero_()
+
+    def shared(self, key, build):
+        """A read-only device object kept once per runtime (``build()`` makes it at first use): the
+        layers of a model share one copy of what depends only on their constants."""
+        if key not in self._shared:
+            self._shared[key] = build()
+        return self._shared[key]
 
 
 class WeightSource:

@@ -14,7 +14,6 @@ import torch
 
 from .. import kernels
 
-SM_COUNT = 148
 SMALL_BATCH_TOKENS = 8      # up to this many tokens small layers take the light small-batch kernels
 
 
@@ -23,14 +22,14 @@ def small_batch_enabled() -> bool:
     return os.environ.get("SPROUT_SMALL_BATCH", "1") != "0"
 
 
-def small_batch_split_k(out_features: int, in_features: int, tokens: int, residual: bool) -> int:
+def small_batch_split_k(out_features: int, in_features: int, tokens: int, residual: bool, sms: int) -> int:
     """How many CTAs share the K range of a small-batch product into a float32 residual:
-    enough to put a CTA on most SMs when the matrix has few 128-row tiles."""
+    enough to put a CTA on most of the device's ``sms`` SMs when the matrix has few 128-row tiles."""
     if not residual or tokens > 256:
         return 1
     tiles = -(-out_features // 128)
     k_blocks = -(-in_features // 64)
-    return max(1, min(k_blocks, SM_COUNT // tiles))
+    return max(1, min(k_blocks, sms // tiles))
 
 
 class Linear:
@@ -39,6 +38,7 @@ class Linear:
         self.bias = bias
         self.status = status
         self.out_features, self.in_features = weight.shape
+        self.sms = kernels.sm_count(weight.device) if weight.is_cuda else 0
         if weight.dtype == torch.bfloat16 and self.in_features % 8:
             raise ValueError(f"a bfloat16 matrix needs an inner size that is a multiple of 8 (got {self.in_features}): "
                              "its rows must start on 16-byte boundaries")
@@ -49,17 +49,20 @@ class Linear:
             self.small_tokens = SMALL_BATCH_TOKENS
 
     def split_k(self, tokens: int, residual: bool) -> int:
-        return small_batch_split_k(self.out_features, self.in_features, tokens, residual)
+        return small_batch_split_k(self.out_features, self.in_features, tokens, residual, self.sms)
 
-    def forward_swiglu(self, a: torch.Tensor) -> torch.Tensor:
-        """silu(gate) * up of a fused, interleaved gate/up matrix: fused into the product's epilogue
-        on the tensor-core path, a separate kernel on the 32-bit path."""
+    def forward_swiglu(self, a: torch.Tensor, block: int) -> torch.Tensor:
+        """silu(gate) * up of a fused gate/up matrix whose rows interleave the two in blocks of
+        ``block``: fused into the product's epilogue on the tensor-core path (block 8), a separate
+        kernel on the 32-bit path (any block)."""
         half = self.out_features // 2
         out = torch.empty((a.shape[0], half), dtype=a.dtype, device=a.device)
         if self.weight.dtype == torch.bfloat16:
+            if block != 8:
+                raise ValueError("the tensor-core SwiGLU epilogue reads gate and up rows interleaved in blocks of 8")
             kernels.gemm_bf16(a, self.weight, out, self.status, swiglu=True)
         else:
-            kernels.swiglu(self.forward(a), out)
+            kernels.swiglu(self.forward(a), out, block)
         return out
 
     def accumulate(self, a: torch.Tensor, acc: torch.Tensor) -> None:

@@ -1,8 +1,10 @@
 """SwiGLU feed-forward: x += W_down (silu(W_gate h) * W_up h), no biases (src/qwen.ts:196-200).
 
-Gate and up are one fused product whose weight rows interleave the two in blocks of 8 (rows
-16b..16b+7 are gate rows 8b..8b+7, rows 16b+8..16b+15 the matching up rows), so that the
-activation sees a gate value and its up value side by side.
+Gate and up are one fused product.  On the tensor-core path its weight rows interleave the two
+in blocks of 8 (rows 16b..16b+7 are gate rows 8b..8b+7, rows 16b+8..16b+15 the matching up
+rows), so that the product's epilogue sees a gate value and its up value side by side; that needs
+an intermediate size that is a multiple of 8.  The 32-bit path has no such epilogue: it keeps the
+gate rows first and the up rows after them, and takes any intermediate size.
 """
 from __future__ import annotations
 
@@ -16,20 +18,20 @@ INTERLEAVE = 8
 FUSED_TOKENS = 8          # the one-kernel decode form takes up to this many tokens
 
 
-def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, block: int = INTERLEAVE) -> torch.Tensor:
     inter, hidden = gate.shape
-    blocks = inter // INTERLEAVE
-    return torch.stack([gate.reshape(blocks, INTERLEAVE, hidden), up.reshape(blocks, INTERLEAVE, hidden)],
+    blocks = inter // block
+    return torch.stack([gate.reshape(blocks, block, hidden), up.reshape(blocks, block, hidden)],
                        dim=1).reshape(2 * inter, hidden).contiguous()
 
 
 @register_part("feed_forward", "swiglu_mlp")
 class SwiGLUMLP(Part):
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, names: dict | None = None):
-        if intermediate_size % INTERLEAVE:
-            raise ValueError(f"swiglu_mlp: intermediate_size must be a multiple of {INTERLEAVE} "
-                             f"(got {intermediate_size})")
+        if hidden_size <= 0 or intermediate_size <= 0:
+            raise ValueError("swiglu_mlp: sizes must be positive")
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.block = INTERLEAVE            # rows of gate, then as many of up, and so on (set at load)
         names = names or {"gate": "gate_proj", "up": "up_proj", "down": "down_proj"}
         self.names = {key: prefix + value for key, value in names.items()}
         self.gate_up = self.down = None
@@ -42,7 +44,16 @@ class SwiGLUMLP(Part):
                 TensorDecl(self.names["down"] + ".weight", (self.hidden_size, self.intermediate_size))]
 
     def load(self, source: WeightSource):
-        fused = interleave_gate_up(source.raw(self.names["gate"] + ".weight"), source.raw(self.names["up"] + ".weight"))
+        if source.runtime.dtype == torch.bfloat16:
+            if self.intermediate_size % INTERLEAVE:
+                raise ValueError(f"swiglu_mlp: on the bfloat16 path intermediate_size must be a multiple of {INTERLEAVE} "
+                                 f"(got {self.intermediate_size}): the tensor-core epilogue pairs gate and up rows in "
+                                 f"blocks of {INTERLEAVE}; the float32 path takes any size")
+            self.block = INTERLEAVE
+        else:
+            self.block = self.intermediate_size
+        fused = interleave_gate_up(source.raw(self.names["gate"] + ".weight"), source.raw(self.names["up"] + ".weight"),
+                                   self.block)
         self.gate_up = Linear(source.to_device_matrix(fused), None, source.runtime.status)
         self.down = Linear(source.matrix(self.names["down"] + ".weight"), None, source.runtime.status)
         # Small layers decode in one kernel that also takes the norm before the feed-forward
@@ -53,7 +64,7 @@ class SwiGLUMLP(Part):
                 self._sync = torch.zeros(2, dtype=torch.int32, device=self.down.weight.device)
 
     def forward(self, h, x, ctx=None):
-        self.down.forward(self.gate_up.forward_swiglu(h), residual=x)
+        self.down.forward(self.gate_up.forward_swiglu(h, self.block), residual=x)
 
     def forward_with_norm(self, norm, x, ctx=None) -> bool:
         """x += feed_forward(norm(x)) in one kernel, if this layer and this batch allow it: an

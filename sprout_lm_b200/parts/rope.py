@@ -20,20 +20,24 @@ class HalfSplitRotary(Part):
         if theta <= 0 or max_positions <= 0:
             raise ValueError("rotary position encoding needs positive theta and max_positions")
         self.head_dim, self.theta, self.max_positions = int(head_dim), float(theta), int(max_positions)
-        self._tables = None
 
     def angles(self) -> np.ndarray:
         d = np.arange(self.head_dim // 2, dtype=np.float64)
         inv = self.theta ** (2.0 * d / self.head_dim)
         return np.arange(self.max_positions, dtype=np.float64)[:, None] / inv[None, :]
 
+    interleaved = False          # pairs (d, d + head_dim / 2)
+
     def rotary_tables(self, runtime):
-        if self._tables is None:
+        """The tables depend on (head_dim, theta, max_positions) alone: all layers of a model share
+        one copy on the device."""
+        def build():
             angle = self.angles()
             cos = torch.from_numpy(np.cos(angle).astype(np.float32)).to(runtime.device)
             sin = torch.from_numpy(np.sin(angle).astype(np.float32)).to(runtime.device)
-            self._tables = (cos.contiguous(), sin.contiguous())
-        return self._tables
+            return cos.contiguous(), sin.contiguous()
+        shared = getattr(runtime, "shared", None)
+        return shared(("rope_half_split", self.head_dim, self.theta, self.max_positions), build) if shared else build()
 
 
 @register_part("position", "none")

@@ -62,6 +62,39 @@ def test_captured_decode_steps_are_keyed_by_the_parts_plans(monkeypatch):
     assert cache.get([entry(1030), entry(40)]) not in (first, other)      # a wider table
 
 
+def test_captured_decode_steps_are_bounded(monkeypatch):
+    """A serving loop with changing batch sizes and growing contexts asks for ever new keys: the
+    cache keeps at most ``limit`` captures and drops the least recently used one."""
+    from types import SimpleNamespace
+    from sprout_lm_b200.engine import graphs
+
+    alive = []
+
+    class FakeGraph:
+        def __init__(self, runner, requests, table_pages, planned_context=0):
+            self.key = (requests, table_pages, planned_context)
+            alive.append(self.key)
+
+        def __del__(self):
+            alive.remove(self.key)
+
+    monkeypatch.setattr(graphs, "DecodeGraph", FakeGraph)
+    runner = SimpleNamespace(page_tokens=16, model=SimpleNamespace(decode_plan=lambda requests, max_keys, planned: (planned // 128,)))
+    cache = graphs.GraphCache(runner, page_multiple=64, limit=5)
+    entry = lambda length: SimpleNamespace(seq=SimpleNamespace(length=length, tables=[[0] * (-(-(length + 1) // 16))]))
+    for batch in range(1, 65):
+        for length in (50, 300, 700, 1500):
+            cache.get([entry(length)] * batch)
+            assert len(cache.graphs) <= 5 and len(alive) <= 5
+    assert cache.keys_used == 64 * 4 and cache.evictions == 64 * 4 - 5
+    # use keeps a capture: the one touched again outlives newer ones
+    kept = cache.get([entry(50)] * 64)
+    for length in (300, 700, 1500, 2100):
+        cache.get([entry(length)] * 3)
+        assert cache.get([entry(50)] * 64) is kept
+    assert len(cache.graphs) == 5
+
+
 def test_prefill_step_captures_do_not_take_turns_evicting_one_another(monkeypatch):
     """Six step shapes coming round and round with room for four captures: four are captured once
     and replayed from then on; the other two run eagerly instead of capturing over them."""

@@ -1,0 +1,207 @@
+"""The paths that generation and the benchmark really take, against the plain implementation.
+
+Decoding through the scheduler replays captured CUDA graphs (``DecodeGraph``), keyed by the number
+of requests, the block tables' width and the attention's split plan, with a host mirror that is
+updated in place; the benchmark's device-side loop (``DecodeLoop``) feeds tokens back without the
+host; mixed steps whose sizes repeat are captured too (``StepGraphs``), with sampling inside.
+Here each of them runs for hundreds of tokens, across changes of plan and of table width, on both
+sides of the small-batch kernels' limit of 8 tokens, and what it computes is compared with the
+plain implementation: logits where they can be read, tokens otherwise.
+"""
+import numpy as np
+import pytest
+import torch
+
+import helpers
+from helpers import TOL
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def model_dirs(tmp_path_factory):
+    base = tmp_path_factory.mktemp("models")
+    return {name: helpers.make_model_dir(base, name) for name in helpers.TINY}
+
+
+def check_tokens(model_dir, prompt, output, dtype, label, tol=None):
+    """Every generated token against the plain implementation's logits for the same history (the
+    engine's own earlier tokens): in 32-bit the plain argmax unless the two best logits are a
+    rounding apart, in bfloat16 a token within bfloat16's reach of the best."""
+    rows = helpers.plain_logits(model_dir, list(prompt) + list(output))
+    tol = tol if tol is not None else TOL[dtype]
+    for i, token in enumerate(output):
+        row = rows[len(prompt) - 1 + i]
+        best = float(row.max())
+        if dtype == "float32":
+            top2 = np.sort(row)[-2:]
+            if top2[1] - top2[0] > 4 * tol:
+                assert token == int(np.argmax(row)), f"{label}: output {i} is {token}, plain says {int(np.argmax(row))}"
+        assert row[token] >= best - 4 * tol, f"{label}: output {i} ({token}) lies {best - row[token]:.3e} below the best logit"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,batch", [("A", 3), ("A", 9), ("B", 3), ("B", 9)])
+def test_long_generation_through_the_scheduler(model_dirs, name, batch, dtype):
+    """300 and more decoded tokens per request through the scheduler: the captured decode steps
+    are re-keyed on the way (requests finish one after the other, so the batch shrinks; B's block
+    tables widen past 64 pages; the attention's plan may follow the context) and every token stays
+    the plain implementation's."""
+    from sprout_lm_b200 import EngineOptions, load_model, make_engine
+    sizes, _, page = helpers.TINY[name]
+    model = load_model(model_dirs[name], dtype=dtype)
+    rng = np.random.default_rng(17 + batch)
+    new_tokens = 310
+    longest = sizes["max_position_embeddings"] - new_tokens - 3 * batch
+    # B: the longest request grows past 64 pages of 8 tokens
+    lengths = [int(n) for n in np.linspace(6, 200 if name == "A" else min(longest, 64 * page - 60), batch)]
+    prompts = [helpers.random_tokens(rng, n, sizes["vocab_size"]) for n in lengths]
+    # the requests generate 310, 313, 316, ... tokens: the batch shrinks one by one at the end, each
+    # size a captured step of its own
+    counts = [new_tokens + 3 * i for i in range(batch)]
+    pages = sum(-(-(n + c) // page) for n, c in zip(lengths, counts)) + 2
+    engine = make_engine(model, EngineOptions(block_size=page, num_blocks=pages, max_sequences=batch, max_batch_tokens=2048,
+                                              prefill_chunk_size=512, prefix_caching=False))
+    for i, (prompt, count) in enumerate(zip(prompts, counts)):
+        engine.add(f"r{i}", prompt, count, ignore_eos=True)
+    while engine.pending:
+        engine.step()
+    results = [engine.result(f"r{i}") for i in range(batch)]
+    graphs = engine.runner.graphs
+    widths = {key[1] for key in graphs.graphs}
+    assert graphs.keys_used >= 3, "the decode steps were never re-keyed"
+    if name == "B":              # 64 pages of 8 tokens end at 512 tokens; A's 1,024 positions fit 64 pages of 16
+        assert len(widths) >= 2 or graphs.evictions, f"the block tables never grew past one width ({widths})"
+    assert all(g.graph is not None for g in graphs.graphs.values() if g.launches)
+    for i, (prompt, result) in enumerate(zip(prompts, results)):
+        assert len(result["output"]) == counts[i] and result["finishReason"] == "length"
+        check_tokens(model_dirs[name], prompt, result["output"], dtype, f"{name}/{dtype}/batch {batch}/request {i}")
+    engine.runner.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,batch", [("B", 3), ("A", 9)])
+def test_replayed_decode_steps_give_the_plain_logits(model_dirs, name, batch, dtype):
+    """The logits inside the captured decode step, read after every replay, with the requests'
+    tokens forced: at the tolerance of the step function's own tests, across plan and width
+    changes."""
+    from sprout_lm_b200 import load_model
+    from sprout_lm_b200.engine.batch import StepEntry
+    from sprout_lm_b200.engine.step import ModelRunner
+    sizes, _, page = helpers.TINY[name]
+    model = load_model(model_dirs[name], dtype=dtype)
+    rng = np.random.default_rng(29)
+    decode = 200 if batch > 3 else 330
+    heads = [int(n) for n in np.linspace(5, min(64 * page - 150, sizes["max_position_embeddings"] - decode - 1), batch)]
+    requests = {f"g{i}": helpers.random_tokens(rng, n + decode, sizes["vocab_size"]) for i, n in enumerate(heads)}
+    want = {rid: helpers.plain_logits(model_dirs[name], toks) for rid, toks in requests.items()}
+    pages = sum(-(-len(t) // page) for t in requests.values())
+    runner = ModelRunner(model, num_pages=pages, page_tokens=page, max_requests=batch, prefix_caching=False)
+    seqs = {}
+    for (rid, toks), head in zip(requests.items(), heads):
+        seqs[rid] = runner.new_sequence()
+        assert runner.reserve(seqs[rid], head)
+        runner.step([StepEntry(seqs[rid], toks[:head], [])])
+    # the first request leaves after a third of the steps, the second after two thirds: three batch
+    # sizes, each a captured step of its own; pages are taken as the requests grow, so B's tables
+    # widen past 64 pages on the way
+    leaves = {"g0": decode // 3, "g1": 2 * decode // 3}
+    graphs_seen, widths, worst = set(), set(), 0.0
+    for step in range(decode):
+        live = [(rid, head) for rid, head in zip(requests, heads) if step < leaves.get(rid, decode)]
+        for rid, _ in live:
+            assert runner.reserve(seqs[rid], seqs[rid].length + 1)
+        entries = [StepEntry(seqs[rid], [requests[rid][head + step]], [0]) for rid, head in live]
+        sampled = runner.step_and_sample(entries, [0.0] * len(live), [0.0] * len(live))
+        graph = runner.last_decode_graph
+        graphs_seen.add(id(graph))
+        widths.add(graph.table_pages)
+        assert graph.requests == len(live)
+        logits = graph.last_logits.float().cpu().numpy()
+        for row, token, (rid, head) in zip(logits, sampled, live):
+            ref = want[rid][head + step]
+            err = float(np.abs(row - ref).max())
+            worst = max(worst, err)
+            assert err <= TOL[dtype], f"{name}/{dtype}: request {rid} position {head + step} differs by {err:.3e} in a replayed step"
+            assert row[token] == row.max()
+    assert len(graphs_seen) >= 3
+    if name == "B":
+        assert len(widths) >= 2      # the longest request crossed 64 pages
+    runner.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,batch", [("A", 1), ("B", 8), ("A", 9), ("B", 64)])
+def test_device_side_decode_loop_gives_the_schedulers_tokens(model_dirs, name, batch, dtype):
+    """``DecodeLoop`` (the benchmark's device-side run of decode steps) against ``generate``: the
+    same tokens in 32-bit, and in bfloat16 tokens that the plain implementation backs."""
+    from sprout_lm_b200 import load_model
+    from sprout_lm_b200.engine.batch import StepEntry
+    from sprout_lm_b200.engine.generate import generate
+    from sprout_lm_b200.engine.step import ModelRunner
+    sizes, _, page = helpers.TINY[name]
+    model = load_model(model_dirs[name], dtype=dtype)
+    rng = np.random.default_rng(31 + batch)
+    steps = 140 if batch <= 9 else 40
+    prompts = [helpers.random_tokens(rng, int(n), sizes["vocab_size"]) for n in rng.integers(3, 60, batch)]
+    pages = sum(-(-(len(p) + steps + 2) // page) for p in prompts) + 1
+    runner = ModelRunner(model, num_pages=pages, page_tokens=page, max_requests=batch, prefix_caching=False)
+    seqs, first = [], []
+    for prompt in prompts:
+        seq = runner.new_sequence()
+        assert runner.reserve(seq, len(prompt))
+        first += runner.step_and_sample([StepEntry(seq, prompt, [len(prompt) - 1])], [0.0], [0.0])
+        seqs.append(seq)
+    loop = runner.decode_loop([StepEntry(s, [t], [0]) for s, t in zip(seqs, first)], [0.0] * batch, [0.0] * batch,
+                              max_steps=steps + 1)
+    loop.run(steps - 1)                                    # the capture's own step comes on top
+    history = loop.finish().numpy()
+    runner.check_status()
+    assert history.shape == (steps, batch) and loop.graph is not None
+    outputs = [[first[i]] + [int(t) for t in history[:, i]] for i in range(batch)]
+    for seq, prompt in zip(seqs, prompts):
+        assert seq.length == len(prompt) + steps
+    if dtype == "float32":
+        results = generate(model, prompts, max_new_tokens=steps + 1, ignore_eos=True)
+        assert [r["output"] for r in results] == outputs
+    for i in range(0, batch, max(1, batch // 6)):
+        check_tokens(model_dirs[name], prompts[i], outputs[i], dtype, f"loop/{name}/{dtype}/request {i}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_captured_mixed_step_with_sampling(model_dirs, dtype):
+    """A step with prompt portions that also samples, replayed from its capture (``StepGraphs`` with
+    sampling inside): the same tokens as the uncaptured step, greedy rows backed by the plain
+    implementation, drawn rows equal for equal uniform numbers."""
+    from sprout_lm_b200 import load_model
+    from sprout_lm_b200.engine.batch import StepEntry
+    from sprout_lm_b200.engine.step import ModelRunner
+    name = "A"
+    sizes, _, page = helpers.TINY[name]
+    model = load_model(model_dirs[name], dtype=dtype)
+    rng = np.random.default_rng(41)
+    rounds = [[helpers.random_tokens(rng, 70, sizes["vocab_size"]), helpers.random_tokens(rng, 64, sizes["vocab_size"])]
+              for _ in range(6)]
+    temperatures, uniforms = [0.0, 0.8], [0.0, 0.37]
+
+    def run(capture: bool):
+        runner = ModelRunner(model, num_pages=16, page_tokens=page, max_requests=4, prefix_caching=False)
+        runner.step_graphs.enabled = capture
+        out = []
+        for prompts in rounds:
+            seqs = [runner.new_sequence() for _ in prompts]
+            for seq, prompt in zip(seqs, prompts):
+                assert runner.reserve(seq, len(prompt))
+            out.append(runner.step_and_sample([StepEntry(s, p, [len(p) - 1]) for s, p in zip(seqs, prompts)],
+                                              temperatures, uniforms))
+            for seq in seqs:
+                runner.release(seq)
+        runner.check_status()
+        return out, runner
+    eager, _ = run(False)
+    captured, runner = run(True)
+    assert runner.step_graphs.replays >= 2 and any(key[4] for key in runner.step_graphs.captured)
+    assert captured == eager
+    for prompts, tokens in zip(rounds, captured):
+        check_tokens(model_dirs[name], prompts[0], [tokens[0]], dtype, "captured mixed step")
+        assert 0 <= tokens[1] < sizes["vocab_size"]

@@ -555,9 +555,8 @@ def test_attention_decode_fused_projection_tail(status, heads, kv_heads, head_di
     sums = torch.randn(R, width, generator=g).to(DEV)
     bias = (torch.randn(width, generator=g) * 0.3).to(DEV)
 
-    class RT:
-        device = torch.device(DEV)
-    cos, sin = HalfSplitRotary("", head_dim, 1e4, max(1024, max(lengths))).rotary_tables(RT) if rotate else (None, None)
+    from sprout_lm_b200.parts import Runtime
+    cos, sin = HalfSplitRotary("", head_dim, 1e4, max(1024, max(lengths))).rotary_tables(Runtime(DEV, torch.bfloat16)) if rotate else (None, None)
     positions = (case["context_lens"] - 1).to(torch.int32)
     seq_of_token = torch.arange(R, dtype=torch.int32, device=DEV)
     # the separate path
@@ -582,6 +581,125 @@ def test_attention_decode_fused_projection_tail(status, heads, kv_heads, head_di
     assert torch.equal(k2, k1) and torch.equal(v2, v1)                 # the same append, bit for bit
     assert float(acc2.abs().max()) == 0.0                               # the sums are cleared
     assert (got.float() - want.float()).abs().max().item() <= 1.2e-2
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page,lengths", [(14, 2, 64, 16, [300, 129, 16, 640, 513, 1]),
+                                                                   (3, 1, 48, 8, [61, 1, 130]), (4, 2, 64, 16, [3000, 70])])
+def test_attention_decode_ignores_what_lies_beyond_a_request(status, heads, kv_heads, head_dim, page, lengths, fused):
+    """Every cache slot that holds no key of a request is NaN: the rest of a last page (which the
+    kernel's first pass loads before it knows the request's length), and pages nobody owns.  A
+    page that another request used before holds whatever that request left; none of it may reach
+    the result."""
+    from sprout_lm_b200 import kernels
+    R = len(lengths)
+    case = build_paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, lengths, [1] * R, seed=5, poison=True)
+    out = torch.full((R, heads * head_dim), float("nan"), dtype=torch.bfloat16, device=DEV)
+    if not fused:
+        kernels.attention_decode(case["q"], case["k_cache"], case["v_cache"], case["table"], case["context_lens"], out,
+                                 heads, kv_heads, head_dim, status)
+        assert (out.double().cpu() - case["want"]).abs().max().item() <= 1.2e-2
+    else:
+        # the new token's q, k, v as sums: q is the case's query, k and v the case's last key and value
+        width = (heads + 2 * kv_heads) * head_dim
+        sums = torch.zeros(R, width, device=DEV)
+        sums[:, :heads * head_dim] = case["q"].float()
+        k, v = case["k_cache"].clone(), case["v_cache"].clone()
+        for r, n in enumerate(lengths):
+            pg, slot = int(case["table"][r, (n - 1) // page]), (n - 1) % page
+            sums[r, heads * head_dim:(heads + kv_heads) * head_dim] = k[pg, :, slot].float().reshape(-1)
+            sums[r, (heads + kv_heads) * head_dim:] = v[pg, :, slot].float().reshape(-1)
+            k[pg, :, slot] = float("nan")                  # the kernel writes the new token's slot itself
+            v[pg, :, slot] = float("nan")
+        kernels.attention_decode_fused(sums, None, None, None, k, v, case["table"], case["context_lens"], out, heads,
+                                       kv_heads, head_dim, status)
+        assert (out.double().cpu() - case["want"]).abs().max().item() <= 1.2e-2
+        assert float(sums.abs().max()) == 0.0
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("tokens,head_dim", [(3, 32), (20, 64)])
+def test_rope_append_clears_the_sums_of_a_refused_position(status, tokens, head_dim):
+    """A position beyond the rotary table is flagged and skipped; the float32 sums of that token
+    must still be emptied, or the next product into the workspace would add to them."""
+    from sprout_lm_b200 import kernels
+    from sprout_lm_b200.parts import Runtime
+    from sprout_lm_b200.parts.rope import HalfSplitRotary
+    heads, kv_heads, page = 4, 2, 16
+    width = (heads + 2 * kv_heads) * head_dim
+    cos, sin = HalfSplitRotary("", head_dim, 1e4, 64).rotary_tables(Runtime(DEV, torch.bfloat16))
+    acc = rand(tokens, width, seed=2) + 3.0
+    bias = rand(width, seed=3)
+    positions = torch.arange(tokens, dtype=torch.int32, device=DEV)
+    positions[1] = 64                                    # one past the table
+    table = torch.arange(4, dtype=torch.int32, device=DEV).reshape(1, 4)
+    k_cache = torch.zeros(4, kv_heads, page, head_dim, dtype=torch.bfloat16, device=DEV)
+    v_cache = torch.zeros_like(k_cache)
+    qkv = torch.zeros(tokens, width, dtype=torch.bfloat16, device=DEV)
+    kernels.rope_append(qkv, positions, torch.zeros(tokens, dtype=torch.int32, device=DEV), table, cos, sin, k_cache,
+                        v_cache, heads, kv_heads, head_dim, page, True, status, acc=acc, bias=bias)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 16
+    status.zero_()
+    assert float(acc.abs().max()) == 0.0
+    assert float(qkv[0].float().abs().max()) > 0 and float(qkv[1].float().abs().max()) == 0.0
+
+
+def test_ffn_decode_bounded_wait_runs_out_and_the_kernel_returns(status):
+    """The barrier among the feed-forward kernel's CTAs polls a counter a bounded number of times.
+    Here the counter starts at minus the number of CTAs, so that it reads zero when all have
+    arrived and the last CTA's wait can never be satisfied; with a short limit it gives up, sets
+    the status word's wait bit and the kernel returns (no fault, no hang, the counters back at
+    zero).  The next launch, with honest counters, computes the right thing."""
+    from sprout_lm_b200 import kernels
+    from sprout_lm_b200.parts.mlp import interleave_gate_up
+    tokens, hidden, inter, eps = 4, 96, 320, 1e-5
+    gate, up = rand(inter, hidden, dtype=torch.bfloat16, scale=0.05, seed=1), rand(inter, hidden, dtype=torch.bfloat16, scale=0.05, seed=2)
+    down = rand(hidden, inter, dtype=torch.bfloat16, scale=0.05, seed=3)
+    gain = 1 + rand(hidden, scale=0.1, seed=4)
+    w = interleave_gate_up(gate, up)
+    act = torch.empty((tokens, inter), dtype=torch.bfloat16, device=DEV)
+    ctas = kernels.sm_count()
+    sync = torch.tensor([-ctas, 0], dtype=torch.int32, device=DEV)
+    kernels.set_spin_limit(4000)
+    try:
+        x = rand(tokens, hidden, seed=5)
+        kernels.ffn_decode(x, gain, eps, w, down, act, sync, status)
+        torch.cuda.synchronize()
+    finally:
+        kernels.set_spin_limit(0)
+    assert int(status.item()) & 8, "the wait that could not be satisfied did not run out"
+    assert kernels.describe_status(8) == "a bounded device-side wait ran out"
+    assert sync.tolist() == [0, 0]
+    status.zero_()
+    x = rand(tokens, hidden, seed=6)
+    h = x.double() / torch.sqrt((x.double() ** 2).mean(dim=1, keepdim=True) + eps) * gain.double()
+    h = h.float().to(torch.bfloat16).double()
+    g, u = h @ gate.double().T, h @ up.double().T
+    t = (g / (1 + torch.exp(-g)) * u).float().to(torch.bfloat16).double()
+    want = x.double() + t @ down.double().T
+    kernels.ffn_decode(x, gain, eps, w, down, act, sync, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and sync.tolist() == [0, 0]
+    assert (x.double() - want).abs().max().item() <= 4e-3 * max(1e-3, (want - x.double()).abs().max().item()) + 4e-3
+
+
+def test_sampling_never_draws_a_token_of_probability_zero(status):
+    """A peaked row whose tail is far below: with the uniform number just under 1 the draw falls
+    where rounding decides (the two kernels add the same exponentials in different orders); it must
+    land on a token that has weight, not on the tail."""
+    from sprout_lm_b200 import kernels
+    vocab = 4099
+    for heavy in (1, 5, 40):
+        logits = torch.full((3, vocab), -1e30, device=DEV)
+        logits[:, :heavy] = rand(3, heavy, scale=1.0, seed=heavy)
+        logits[2, vocab - 1] = -80.0                              # a weight that underflows against the maximum
+        out = torch.empty(3, dtype=torch.int32, device=DEV)
+        temperature = torch.tensor([1.0, 0.7, 1.3], device=DEV)
+        for u in (1.0 - 2.0 ** -24, 0.999, 0.5, 0.0):
+            kernels.sample(logits, out, status, temperature, torch.full((3,), u, device=DEV))
+            assert all(0 <= t < heavy for t in out.tolist()), (heavy, u, out.tolist())
     assert int(status.item()) == 0
 
 

@@ -87,8 +87,21 @@ def test_swiglu_mlp_part(dtype):
     want = plain.residual_add(x.numpy(), plain.linear(t, tensors["l.down_proj.weight"].numpy()))
     tol = 1e-5 if dtype == torch.float32 else 2e-2
     assert np.abs(got.cpu().numpy() - want).max() <= tol
-    with pytest.raises(ValueError, match="multiple of 8"):
-        build_part("feed_forward", PartSpec("swiglu_mlp", {"hidden_size": 72, "intermediate_size": 28}), "l.")
+    # an intermediate size that is no multiple of 8: the 32-bit path takes it, the tensor-core path refuses it at load
+    odd = build_part("feed_forward", PartSpec("swiglu_mlp", {"hidden_size": 72, "intermediate_size": 28}), "l.")
+    tensors = {d.name: (torch.randn(*d.shape) * 0.1).to(torch.bfloat16).float() for d in odd.tensor_decls()}
+    source, _ = source_for(tensors, dtype)
+    if dtype == torch.bfloat16:
+        with pytest.raises(ValueError, match="multiple of 8"):
+            odd.load(source)
+    else:
+        odd.load(source)
+        got = x.clone().to(DEV)
+        odd.forward(h.to(DEV), got, None)
+        t = plain.swiglu(plain.linear(h.numpy(), tensors["l.gate_proj.weight"].numpy()),
+                         plain.linear(h.numpy(), tensors["l.up_proj.weight"].numpy()))
+        want = plain.residual_add(x.numpy(), plain.linear(t, tensors["l.down_proj.weight"].numpy()))
+        assert np.abs(got.cpu().numpy() - want).max() <= 1e-5
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -132,6 +145,116 @@ def test_attention_part_whole_then_token_by_token(dtype, heads, kv_heads, head_d
     tol = 2e-5 if dtype == torch.float32 else 5e-2
     assert np.abs(got.cpu().numpy() - want).max() <= tol * max(1.0, np.abs(want).max())
     assert int(runtime.status.item()) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_with_a_toy_position_part_of_interleaved_pairs_over_half_the_head(dtype):
+    """Another position encoding is another registered part, not an edit of a kernel: this one,
+    defined here, turns only the first half of every head, in neighbouring pairs (2d, 2d + 1), by
+    angles that grow linearly with the pair's index.  The attention part hands its tables, their
+    width and the pairing to the kernels as launch parameters.  A portion of 20 tokens (the
+    rotary kernel from float32 sums in bfloat16), then single tokens (in bfloat16 the decode
+    attention kernel that rotates and appends by itself), against the same rotation in numpy."""
+    from sprout_lm_b200.config import PartSpec
+    from sprout_lm_b200.engine.batch import StepEntry
+    from sprout_lm_b200.parts import CacheView, Part, build_part, register_part
+    heads, kv_heads, head_dim, page, max_positions = 4, 2, 32, 8, 64
+    rotary_dim = head_dim // 2
+
+    def angles():
+        d = np.arange(rotary_dim // 2, dtype=np.float64)
+        return np.arange(max_positions, dtype=np.float64)[:, None] * (0.07 * (d[None, :] + 1))
+
+    @register_part("position", "toy_interleaved_half")
+    class InterleavedHalf(Part):
+        interleaved = True
+
+        def __init__(self, prefix, **_):
+            pass
+
+        def rotary_tables(self, runtime):
+            a = angles()
+            return (torch.from_numpy(np.cos(a).astype(np.float32)).to(runtime.device),
+                    torch.from_numpy(np.sin(a).astype(np.float32)).to(runtime.device))
+
+    def rotate(t, positions):
+        n = t.shape[1] // head_dim
+        ts = t.astype(np.float64).reshape(len(positions), n, head_dim).copy()
+        a = angles()[list(positions)]
+        c, s = np.cos(a)[:, None, :], np.sin(a)[:, None, :]
+        even, odd = ts[..., 0:rotary_dim:2].copy(), ts[..., 1:rotary_dim:2].copy()
+        ts[..., 0:rotary_dim:2] = even * c - odd * s
+        ts[..., 1:rotary_dim:2] = odd * c + even * s
+        return ts.reshape(len(positions), n * head_dim).astype(np.float32)
+
+    hidden = heads * head_dim
+    spec = PartSpec("gqa_attention", {"hidden_size": hidden, "heads": heads, "kv_heads": kv_heads, "head_dim": head_dim,
+                                      "position": PartSpec("toy_interleaved_half", {})})
+    part = build_part("mixer", spec, "a.")
+    tensors = {d.name: (torch.randn(*d.shape, generator=torch.Generator().manual_seed(5)) * 0.2).to(torch.bfloat16).float()
+               for d in part.tensor_decls()}
+    source, runtime = source_for(tensors, dtype)
+    part.load(source)
+    assert part.interleaved and part.tables[0].shape == (max_positions, rotary_dim // 2)
+    total = 25
+    h_all = torch.randn(total, hidden, generator=torch.Generator().manual_seed(6)).to(torch.bfloat16).float()
+    k_cache = torch.zeros(9, kv_heads, page, head_dim, dtype=dtype, device=DEV)
+    v_cache = torch.zeros_like(k_cache)
+    seq = FakeSeq([5, 2, 7, 0], 0)
+    got = torch.zeros(total, hidden, device=DEV)
+    for count in (20, 1, 1, 1, 1, 1):
+        ctx = stage([StepEntry(seq, [0] * count, [])], page)
+        view = CacheView(k_cache, v_cache, ctx.block_tables[0], page, True)
+        x = torch.zeros(count, hidden, device=DEV)
+        part.forward(h_all[seq.length:seq.length + count].to(dtype).to(DEV), x, ctx, view, None)
+        got[seq.length:seq.length + count] = x
+        seq.length += count
+    n = tensors
+    q = plain.linear(h_all.numpy(), n["a.q_proj.weight"].numpy(), n["a.q_proj.bias"].numpy())
+    k = plain.linear(h_all.numpy(), n["a.k_proj.weight"].numpy(), n["a.k_proj.bias"].numpy())
+    v = plain.linear(h_all.numpy(), n["a.v_proj.weight"].numpy(), n["a.v_proj.bias"].numpy())
+    q, k = rotate(q, range(total)), rotate(k, range(total))
+    want = plain.linear(plain.causal_gqa_attention(q, k, v, heads, kv_heads, head_dim), n["a.o_proj.weight"].numpy())
+    tol = 2e-5 if dtype == torch.float32 else 5e-2
+    assert np.abs(got.cpu().numpy() - want).max() <= tol * max(1.0, np.abs(want).max())
+    # and the test can fail: half-split pairs over the whole head give something else
+    wrong = plain.linear(plain.causal_gqa_attention(plain.rope_half_split(q, range(total), head_dim, 1e4), k, v, heads, kv_heads,
+                                                    head_dim), n["a.o_proj.weight"].numpy())
+    assert np.abs(wrong - want).max() > 0.05 * np.abs(want).max()
+    assert int(runtime.status.item()) == 0
+
+
+def test_a_flagged_step_leaves_no_sums_behind():
+    """The accumulation workspaces belong to the model's runtime; when the status word is read and
+    found set they are zeroed, so that whatever a refused token left there cannot reach the next
+    step."""
+    from sprout_lm_b200.engine.step import ModelRunner, StepError
+    from sprout_lm_b200.parts import Runtime
+    runtime = Runtime(DEV, torch.bfloat16)
+    a = runtime.workspace(("qkv_sums", 96), (4, 96))
+    assert runtime.workspace(("qkv_sums", 96), (4, 96)) is a and float(a.abs().max()) == 0.0
+    other = Runtime(DEV, torch.bfloat16)
+    assert other.workspace(("qkv_sums", 96), (4, 96)) is not a        # two models never share sums
+    a += 5.0
+    runtime.status.fill_(16)
+    fake = ModelRunner.__new__(ModelRunner)
+    fake.runtime = runtime
+    with pytest.raises(StepError, match="position outside the rotary table"):
+        fake.check_status()
+    assert float(a.abs().max()) == 0.0 and int(runtime.status.item()) == 0
+
+
+def test_weights_beyond_the_budget_are_refused_before_any_copy(tmp_path):
+    from sprout_lm_b200.models import load_model
+    from sprout_lm_b200.models.decoder import WeightCapacityError
+    folder = helpers.make_model_dir(tmp_path, "A")
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_allocated()
+    with pytest.raises(WeightCapacityError, match="Resident weight budget exceeded"):
+        load_model(folder, dtype=torch.bfloat16, weight_budget_bytes=10_000)
+    assert torch.cuda.memory_allocated() - before <= 4096      # the status word at most: no tensor went up
+    model = load_model(folder, dtype=torch.bfloat16, weight_budget_bytes=10_000_000)
+    assert model.weight_bytes(torch.bfloat16) <= 10_000_000 and model.weight_bytes(torch.float32) > model.weight_bytes(torch.bfloat16)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -26,6 +26,19 @@ def test_fixture_logits_within_reference_tolerance(fixture_dir):
     assert worst < 2e-6, worst
 
 
+def test_golden_copy_is_the_reference_fixture():
+    """tests/golden/qwen-tiny is a byte-identical copy of the reference's data files."""
+    import conftest
+    import pytest
+    checkout = conftest.reference_checkout_fixture_dir()
+    if checkout is None:
+        pytest.skip("no checkout of the reference project at hand")
+    names = sorted(p.name for p in conftest.GOLDEN_FIXTURE.iterdir())
+    assert "model.safetensors" in names and len([n for n in names if n.endswith(".f32")]) == 8
+    for name in names:
+        assert (checkout / name).read_bytes() == (conftest.GOLDEN_FIXTURE / name).read_bytes(), name
+
+
 def test_fixture_greedy_outputs(fixture_dir):
     cfg, w = plain.read_model_folder(fixture_dir)
     record = json.loads((fixture_dir / "reference.json").read_text())

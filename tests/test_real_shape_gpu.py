@@ -105,6 +105,79 @@ def test_real_layer_sizes_under_all_cuttings(folder, dtype):
     runner.check_status()
 
 
+@pytest.fixture(scope="module")
+def full_depth_folder(tmp_path_factory):
+    from sprout_lm_b200.config import parse_config
+    from sprout_lm_b200.weights import write_random_model
+    config = parse_config(helpers.raw_config({**SIZES, "num_hidden_layers": 24}))
+    return write_random_model(tmp_path_factory.mktemp("full") / "model", config, seed=4)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_full_depth_0_5b_under_all_cuttings(full_depth_folder, dtype):
+    """All 24 layers of the 0.5B configuration (random weights), two short requests, whole, in
+    portions, mixed, and decoded by the device-side loop: against the plain implementation at
+    every position.  The reference checks its real 0.5B model the same way, 18 positions of
+    151,936 logits at 1e-3 + 1e-4 |ref| (test/model.integration.ts:21-69); that is the 32-bit bar
+    here.  bfloat16 rounds activations, keys and values to 8 bits of mantissa (2^-9 relative) some
+    six times a layer; over 24 layers these add up like a random walk to about 0.025 of the scale,
+    and the bar is twice that: 0.05 of the largest logit."""
+    from sprout_lm_b200 import load_model
+    from sprout_lm_b200.engine.batch import StepEntry
+    from sprout_lm_b200.engine.step import ModelRunner
+    rng = np.random.default_rng(5)
+    vocab = SIZES["vocab_size"]
+    requests = {"a": helpers.random_tokens(rng, 24, vocab), "b": helpers.random_tokens(rng, 13, vocab)}
+    want = {rid: helpers.plain_logits(full_depth_folder, toks) for rid, toks in requests.items()}
+    scale = max(float(np.abs(w).max()) for w in want.values())
+    model = load_model(full_depth_folder, dtype=dtype)
+    assert len(model.blocks) == 24
+
+    def check(got, label):
+        assert got
+        for (rid, pos), row in got.items():
+            ref = want[rid][pos]
+            err = np.abs(row - ref)
+            if dtype == "float32":
+                assert (err <= 1e-3 + 1e-4 * np.abs(ref)).all(), (label, rid, pos, float(err.max()))
+            else:
+                assert float(err.max()) <= 0.05 * scale, (label, rid, pos, float(err.max()), scale)
+
+    for label, plan in (("whole", helpers.plan_whole(requests)), ("portions", helpers.plan_portions(requests)),
+                        ("mixed", helpers.plan_mixed(requests, np.random.default_rng(2), max_live=2)),
+                        ("tail", helpers.plan_tail_decode(requests, tail=6))):
+        runner = ModelRunner(model, num_pages=8, page_tokens=16, max_requests=4, prefix_caching=False)
+        check(helpers.run_plan_in_process(runner, plan), label)
+        runner.check_status()
+    # the device-side decode loop at these sizes: each token must be one that the plain logits back
+    runner = ModelRunner(model, num_pages=8, page_tokens=16, max_requests=4, prefix_caching=False)
+    seqs, first = [], []
+    heads = {"a": 18, "b": 7}
+    for rid, toks in requests.items():
+        seq = runner.new_sequence()
+        assert runner.reserve(seq, heads[rid])
+        first += runner.step_and_sample([StepEntry(seq, toks[:heads[rid]], [heads[rid] - 1])], [0.0], [0.0])
+        seqs.append(seq)
+    for rid, token in zip(requests, first):
+        row = want[rid][heads[rid] - 1]
+        assert row[token] >= row.max() - (1e-3 if dtype == "float32" else 0.05 * scale)
+    loop = runner.decode_loop([StepEntry(s, [t], [0]) for s, t in zip(seqs, first)], [0.0, 0.0], [0.0, 0.0], max_steps=5)
+    loop.run(3)
+    history = loop.finish().numpy()
+    runner.check_status()
+    import plain_qwen2 as plain
+    cfg, w = plain.read_model_folder(full_depth_folder)
+    assert history.shape == (4, 2)
+    for i, rid in enumerate(requests):
+        if rid != "b":
+            continue                         # the shorter request keeps the plain implementation's head product small
+        generated = [first[i]] + [int(t) for t in history[:, i]]
+        rows = plain.logits(cfg, w, requests[rid][:heads[rid]] + generated)
+        for j, token in enumerate(generated[1:]):
+            row = rows[heads[rid] + j]
+            assert row[token] >= row.max() - (1e-3 if dtype == "float32" else 0.05 * scale), (rid, j)
+
+
 LONG_PREFILL = {
     # head size 64 as in the 0.5B configuration, 7 query heads per key/value head
     "hd64": dict(hidden_size=896, intermediate_size=512, num_hidden_layers=1, num_attention_heads=14,

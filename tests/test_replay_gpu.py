@@ -5,6 +5,8 @@ portions of changing size; mixed, up to four live requests with so few pages tha
 used again.  In true 32-bit and in bfloat16, on both tiny configurations, through the step
 function in process and through bin/trace_run.
 """
+import json
+
 import numpy as np
 import pytest
 import torch
@@ -48,14 +50,48 @@ def test_all_cuttings_in_process(model_dirs, name, dtype):
         "portions": helpers.plan_portions(requests),
         "mixed": helpers.plan_mixed(requests, rng),
     }
+    results = {}
     for label, plan in plans.items():
         budget = helpers.live_token_budget(plan, requests)
         runner = make_runner(model_dirs[name], dtype, budget // page, page)
-        got = helpers.run_plan_in_process(runner, plan)
+        got = results[label] = helpers.run_plan_in_process(runner, plan)
         assert len(got) == sum(len(t) for t in requests.values())
         helpers.compare_with_plain(model_dirs[name], requests, got, TOL[dtype], f"{name}/{dtype}/{label}")
         runner.manager.check_invariants()
         assert runner.manager.free_pages() == budget // page      # every page came back
+    if dtype == "float32":
+        # the 32-bit path adds every sum in an order that the cutting does not touch: not one bit differs
+        for label in ("tail", "portions", "mixed"):
+            for place, row in results["whole"].items():
+                assert np.array_equal(results[label][place], row), f"{name}/{label}: {place} differs in some bit"
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_cuttings_with_weights_stored_in_32_bit(tmp_path, name):
+    """The same with a folder whose matrices are stored in float32 (24 bits of mantissa, where the
+    random-weights mode's default stores bfloat16 values): the 32-bit path keeps them as stored and
+    multiplies full mantissas."""
+    from sprout_lm_b200.config import parse_config
+    from sprout_lm_b200.weights import Checkpoint, write_random_model
+    sizes, seed, page = helpers.TINY[name]
+    folder = write_random_model(tmp_path / f"full_{name}", parse_config(helpers.raw_config(sizes)), seed=seed + 10,
+                                dtype="float32")
+    with Checkpoint(folder) as ck:
+        matrix = ck.tensor("model.layers.0.mlp.down_proj.weight")
+    assert matrix.dtype == torch.float32 and not torch.equal(matrix, matrix.to(torch.bfloat16).float())
+    requests = make_requests(name, 13, [5, 40, 70])
+    plans = {"whole": helpers.plan_whole(requests), "tail": helpers.plan_tail_decode(requests),
+             "portions": helpers.plan_portions(requests), "mixed": helpers.plan_mixed(requests, np.random.default_rng(6))}
+    results = {}
+    for label, plan in plans.items():
+        budget = helpers.live_token_budget(plan, requests)
+        runner = make_runner(folder, "float32", budget // page, page)
+        assert runner.model.blocks[0].feed_forward.down.weight.dtype == torch.float32
+        got = results[label] = helpers.run_plan_in_process(runner, plan)
+        helpers.compare_with_plain(folder, requests, got, TOL["float32"], f"full-mantissa/{name}/{label}")
+    for label in ("tail", "portions", "mixed"):
+        for place, row in results["whole"].items():
+            assert np.array_equal(results[label][place], row), (label, place)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -87,10 +123,18 @@ def test_trace_run_program(model_dirs, tmp_path, dtype):
         got = helpers.run_plan_with_trace_run(model_dirs[name], dtype, plan, tmp_path / f"{label}_{dtype}", budget)
         helpers.compare_with_plain(model_dirs[name], requests, got, TOL[dtype], f"trace_run/{dtype}/{label}")
         results[label] = got
-    # cutting changes nothing beyond rounding
+    # cutting changes nothing beyond rounding, and in 32-bit not even that
     for place, row in results["whole"].items():
         for other in ("tail", "mixed"):
-            assert np.abs(results[other][place] - row).max() <= 2 * TOL[dtype]
+            if dtype == "float32":
+                assert np.array_equal(results[other][place], row), (other, place)
+            else:
+                assert np.abs(results[other][place] - row).max() <= 2 * TOL[dtype]
+    # the index names every row of every file
+    index = json.loads((tmp_path / f"whole_{dtype}" / "index.json").read_text())
+    assert index["vocab"] == helpers.TINY[name][0]["vocab_size"]
+    rows = [tuple(place) for places in index["files"].values() for place in places]
+    assert sorted(rows) == sorted(results["whole"])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
