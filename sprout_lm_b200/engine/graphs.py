@@ -222,7 +222,7 @@ class GraphCache:
         width = _round_up(pages, self.page_multiple)
         longest = 1 + max(e.seq.length for e in entries)
         planned = min(width * self.runner.page_tokens, _round_up(longest, 128))
-        plan = self.runner.model.decode_plan(len(entries), width * self.runner.page_tokens, planned)
+        plan = self.runner.model.decode_plan(len(entries), width * self.runner.page_tokens, planned, self.runner.page_tokens)
         return (len(entries), width, plan), width, planned
 
     def get(self, entries) -> DecodeGraph:
@@ -327,24 +327,36 @@ class DecodeLoop:
     kernel makes the sampled tokens the next inputs.  Pages for all the steps must have been
     reserved.  The scheduler does not use it (it looks at every token for end-of-sequence); the
     benchmark times the device's share of a decode step with it, and the tests hold its tokens
-    against the scheduler's."""
+    against the scheduler's.
+
+    A captured step is laid out for contexts up to a bound (the attention's launches follow the
+    contexts' length); the loop holds one capture per stretch of ``SEGMENT`` tokens of context that
+    its steps will cross, all recorded before the first replay, and replays the one whose stretch
+    the next step's longest context lies in."""
+
+    SEGMENT = 256
 
     def __init__(self, runner, entries, temperatures, uniforms, max_steps: int):
         self.runner = runner
         self.requests = len(entries)
         pages = max(max((len(t) for t in e.seq.tables), default=1) for e in entries)
-        # one graph for all the steps: laid out for the contexts half-way through them
         width = _round_up(pages, 8)
-        half_way = 1 + max(e.seq.length for e in entries) + max_steps // 2
-        self.inner = DecodeGraph(runner, self.requests, width, min(width * runner.page_tokens, _round_up(half_way, 128)))
+        self.longest = 1 + max(e.seq.length for e in entries)          # the longest context of the next step
+        self.limit = width * runner.page_tokens
+        self.max_steps = max_steps
+        self.inner = DecodeGraph(runner, self.requests, width, self._bound(self.longest))
         self.entries = entries
         device = runner.runtime.device
         self.history = torch.zeros((max_steps, self.requests), dtype=torch.int32, device=device)
         self.counter = torch.zeros(1, dtype=torch.int32, device=device)
         self.ctx = self.inner.stage(entries, temperatures, uniforms)
+        self.graphs: dict = {}            # bound -> captured step
         self.graph = None
         self.launches_per_step = 0
         self.steps_done = 0
+
+    def _bound(self, longest: int) -> int:
+        return min(self.limit, _round_up(longest, self.SEGMENT))
 
     def _one_step(self):
         logits, tokens = self.inner._forward(self.ctx)
@@ -352,22 +364,32 @@ class DecodeLoop:
                                self.history, self.counter)
 
     def capture(self):
+        self.ctx.planned_context = self._bound(self.longest)
         self._one_step()                       # warm-up: also a real step
         self.steps_done += 1
+        self.longest += 1
         torch.cuda.synchronize()
-        before = kernels.LAUNCHES
-        graph = torch.cuda.CUDAGraph()
-        with guarded_capture(graph):
-            self._one_step()
-        self.launches_per_step = kernels.LAUNCHES - before
-        self.graph = graph
-        # capturing does not execute: nothing advanced
+        last = self.longest + self.max_steps
+        bound = self._bound(self.longest)
+        while True:
+            self.ctx.planned_context = bound
+            before = kernels.LAUNCHES
+            graph = torch.cuda.CUDAGraph()
+            with guarded_capture(graph):
+                self._one_step()               # capturing does not execute: nothing advances
+            self.launches_per_step = self.launches_per_step or kernels.LAUNCHES - before
+            self.graphs[bound] = graph
+            if bound >= min(last, self.limit):
+                break
+            bound = self._bound(bound + 1)
+        self.graph = self.graphs[self._bound(self.longest)]
 
     def run(self, steps: int) -> None:
         if self.graph is None:
             self.capture()
         for _ in range(steps):
-            self.graph.replay()
+            self.graphs[self._bound(self.longest)].replay()
+            self.longest += 1
         self.steps_done += steps
 
     def finish(self) -> torch.Tensor:

@@ -39,6 +39,8 @@ _SIGNATURES = {
     "sprout_advance_decode": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
     "sprout_attention_decode": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_attention_decode_fused": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_attention_decode_resident": [_P, _P, _P, _P, _I, _I, _I, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_attention_decode_resident_cap": [_I, _I, _I, _I],
     "sprout_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, ctypes.c_longlong, _P, _P, _P],
     "sprout_attention_prefill_tc_supported": [_I, _I, _I],
     "sprout_gemm_bf16": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
@@ -485,6 +487,77 @@ def attention_decode(q, k_cache, v_cache, block_table, context_lens, out, heads,
          k_cache.shape[0], split_keys, splits, _ptr(status, "status", torch.int32), _stream())
 
 
+RESIDENT_STEP = 256          # the resident kernel's room for keys grows in steps of this many
+
+
+@functools.lru_cache(maxsize=256)
+def resident_cap(heads: int, kv_heads: int, head_dim: int, page_tokens: int) -> int:
+    """The longest context that ``attention_decode_resident`` takes for these sizes (0: none)."""
+    return int(load_library().sprout_attention_decode_resident_cap(heads, kv_heads, head_dim, page_tokens))
+
+
+def decode_attention_plan(requests: int, heads: int, kv_heads: int, head_dim: int, page_tokens: int, max_keys: int,
+                          planned_keys: int | None = None) -> tuple:
+    """How a step of one token per request runs its attention over contexts of up to
+    ``planned_keys`` keys (block tables ``max_keys`` wide): ``("resident", room)`` where a request's
+    whole context fits one CTA's shared memory (room: keys, in steps of 256), else ``("split", keys
+    per split, splits, through memory)`` as ``decode_split_plan`` lays it out."""
+    planned = max(1, min(max_keys, planned_keys if planned_keys else max_keys))
+    # One CTA per (request, key/value head) pulls its whole context alone: that pays once there are
+    # enough of them to keep most SMs' copy engines busy (measured at the 0.5B sizes: batch 64 gains
+    # 7 % of its step, batch 8 loses 2 % against splits in a cluster, batch 32 is even).
+    sms = sm_count() if torch.cuda.is_available() else 148
+    if RESIDENT_ENABLED and head_dim in (64, 128) and requests * kv_heads >= (3 * sms) // 5:
+        cap = resident_cap(heads, kv_heads, head_dim, page_tokens)
+        room = min(cap, -(-planned // RESIDENT_STEP) * RESIDENT_STEP)
+        if planned <= room:
+            return ("resident", room)
+    return ("split",) + decode_split_plan(requests, kv_heads, max_keys, head_dim, planned)
+
+
+RESIDENT_ENABLED = os.environ.get("SPROUT_RESIDENT_ATTENTION", "1") != "0"
+
+
+def attention_decode_resident(k_cache, v_cache, block_table, context_lens, out, heads, kv_heads, head_dim, status, room,
+                              q=None, acc=None, bias=None, cos_table=None, sin_table=None, interleaved=False):
+    """Decode attention with every request's whole context (at most ``room`` keys) in one CTA's
+    shared memory, fetched by TMA before the wait for the step's earlier kernels.  With ``acc``
+    (and ``bias``, rotation tables) the fused form of ``attention_decode_fused``: the new token's
+    q, k, v come as float32 sums, k and v are appended to the cache, the sums are cleared; with
+    ``q`` the cache already holds the new token.  ``out`` is bfloat16 [requests, heads * head_dim]."""
+    R = out.shape[0]
+    width = (heads + 2 * kv_heads) * head_dim
+    if (acc is None) == (q is None):
+        raise KernelError("attention_decode_resident: give either q or the float32 sums")
+    if acc is not None and (acc.dtype != torch.float32 or tuple(acc.shape) != (R, width) or not acc.is_contiguous()):
+        raise KernelError("attention_decode_resident: acc must be contiguous float32 [requests, (heads + 2 kv_heads) * head_dim]")
+    if q is not None:
+        _rows_contiguous(q, "q")
+        if q.dtype != torch.bfloat16 or tuple(q.shape) != (R, heads * head_dim):
+            raise KernelError("attention_decode_resident: q must be bfloat16 [requests, heads * head_dim]")
+    if out.dtype != torch.bfloat16 or out.shape[1] != heads * head_dim or out.stride(1) != 1:
+        raise KernelError("attention_decode_resident: out must be bfloat16 [requests, heads * head_dim]")
+    if k_cache.shape != v_cache.shape or k_cache.dim() != 4 or k_cache.shape[3] != head_dim or k_cache.shape[1] != kv_heads \
+            or k_cache.dtype != torch.bfloat16 or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise KernelError("attention_decode_resident: caches must be contiguous bfloat16 [pages, kv_heads, page_tokens, head_dim]")
+    if bias is not None and bias.numel() != width:
+        raise KernelError("attention_decode_resident: bias must have one entry per column of acc")
+    if (cos_table is None) != (sin_table is None):
+        raise KernelError("attention_decode_resident: cos and sin tables go together")
+    if cos_table is not None and (cos_table.shape != sin_table.shape or cos_table.dim() != 2
+                                  or not 0 < cos_table.shape[1] <= head_dim // 2
+                                  or not cos_table.is_contiguous() or not sin_table.is_contiguous()):
+        raise KernelError("attention_decode_resident: cos/sin tables must be contiguous [max_positions, rotary_dim / 2]")
+    _rows_contiguous(block_table, "block_table")
+    _run("sprout_attention_decode_resident", _ptr(acc, "acc", torch.float32, True), _ptr(bias, "bias", torch.float32, True),
+         _ptr(cos_table, "cos", torch.float32, True), _ptr(sin_table, "sin", torch.float32, True),
+         cos_table.shape[0] if cos_table is not None else 0, 2 * cos_table.shape[1] if cos_table is not None else 0,
+         1 if interleaved else 0, _ptr(q, "q", torch.bfloat16, True), q.stride(0) if q is not None else 0,
+         _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"), _ptr(block_table, "block_table", torch.int32),
+         block_table.stride(0), _ptr(context_lens, "context_lens", torch.int32), _ptr(out, "out"), out.stride(0),
+         R, heads, kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], int(room), _ptr(status, "status", torch.int32), _stream())
+
+
 def decode_fusable(requests: int, heads: int, kv_heads: int, head_dim: int, max_keys: int) -> bool:
     """Whether the decode step's attention can take the projection's tail (bias, rotation, cache
     append) into its own kernel: the tensor-core kernel's sizes."""
@@ -582,6 +655,12 @@ def paged_attention(q, cache, ctx, out, heads, kv_heads, head_dim, status):
     kernel when every request brings one token and the tensor-core kernel otherwise."""
     if q.dtype == torch.bfloat16:
         if ctx.max_q_len == 1 and heads // kv_heads <= 16:
+            max_keys = cache.block_table.shape[1] * cache.k.shape[2]
+            plan = decode_attention_plan(q.shape[0], heads, kv_heads, head_dim, cache.k.shape[2], max_keys,
+                                         ctx.planned_context or ctx.max_context)
+            if plan[0] == "resident":
+                return attention_decode_resident(cache.k, cache.v, cache.block_table, ctx.context_lens, out, heads, kv_heads,
+                                                 head_dim, status, plan[1], q=q)
             return attention_decode(q, cache.k, cache.v, cache.block_table, ctx.context_lens, out,
                                     heads, kv_heads, head_dim, status, live_keys=ctx.planned_context or ctx.max_context)
         if head_dim <= 128:
@@ -623,5 +702,5 @@ def describe_status(word: int) -> str:
 
 
 __all__ = ["KernelError", "BuildError", "load_library", "library_file", "embed", "rmsnorm", "swiglu",
-           "rope_append", "gemm_simple", "gemm_bf16", "attention_simple", "attention_decode", "attention_decode_fused", "decode_fusable", "attention_prefill",
+           "rope_append", "gemm_simple", "gemm_bf16", "attention_simple", "attention_decode", "attention_decode_fused", "attention_decode_resident", "decode_attention_plan", "decode_fusable", "attention_prefill",
            "paged_attention", "sample", "advance_decode", "describe_status"]

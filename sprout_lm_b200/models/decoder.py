@@ -94,9 +94,9 @@ class DecoderModel:
         """One StateSpec (or None) per layer."""
         return [block.mixer.state_spec() for block in self.blocks]
 
-    def decode_plan(self, requests: int, max_keys: int, planned_context: int):
+    def decode_plan(self, requests: int, max_keys: int, planned_context: int, page_tokens: int):
         """The parts' plans for a step of one token per request (see ``Part.decode_plan``)."""
-        key = (requests, max_keys, planned_context)
+        key = (requests, max_keys, planned_context, page_tokens)
         plan = self._decode_plans.get(key)
         if plan is None:
             if len(self._decode_plans) > 4096:

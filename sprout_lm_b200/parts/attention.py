@@ -40,12 +40,14 @@ class PagedGQAttention(Part):
     def state_spec(self):
         return None
 
-    def decode_plan(self, requests: int, max_keys: int, planned_context: int):
-        """How the decode kernel divides the keys among CTAs: it follows the contexts' length, not
-        only the block tables' width."""
+    def decode_plan(self, requests: int, max_keys: int, planned_context: int, page_tokens: int):
+        """How the decode step's attention is laid out: with the whole context in one CTA's shared
+        memory (and room for how many keys), or divided among CTAs (and how): it follows the
+        contexts' length, not only the block tables' width."""
         if self.heads // self.kv_heads > 16:
             return None
-        return kernels.decode_split_plan(requests, self.kv_heads, max_keys, self.head_dim, planned_context)
+        return kernels.decode_attention_plan(requests, self.heads, self.kv_heads, self.head_dim, page_tokens, max_keys,
+                                             planned_context)
 
     # ---- weights
     def tensor_decls(self):
@@ -119,10 +121,18 @@ class PagedGQAttention(Part):
             if ctx.max_q_len == 1 and cache.write and kernels.decode_fusable(tokens, self.heads, self.kv_heads,
                                                                              self.head_dim, max_keys):
                 # one token per request: bias, rotation and the cache append happen inside the attention kernel
-                kernels.attention_decode_fused(acc, self.qkv.bias, cos, sin, cache.k, cache.v, cache.block_table,
-                                               ctx.context_lens, attended, self.heads, self.kv_heads, self.head_dim,
-                                               self.runtime.status, live_keys=ctx.planned_context or ctx.max_context,
-                                               interleaved=self.interleaved)
+                planned = ctx.planned_context or ctx.max_context
+                plan = kernels.decode_attention_plan(tokens, self.heads, self.kv_heads, self.head_dim, cache.page_tokens,
+                                                     max_keys, planned)
+                if plan[0] == "resident":
+                    kernels.attention_decode_resident(cache.k, cache.v, cache.block_table, ctx.context_lens, attended,
+                                                      self.heads, self.kv_heads, self.head_dim, self.runtime.status, plan[1],
+                                                      acc=acc, bias=self.qkv.bias, cos_table=cos, sin_table=sin,
+                                                      interleaved=self.interleaved)
+                else:
+                    kernels.attention_decode_fused(acc, self.qkv.bias, cos, sin, cache.k, cache.v, cache.block_table,
+                                                   ctx.context_lens, attended, self.heads, self.kv_heads, self.head_dim,
+                                                   self.runtime.status, live_keys=planned, interleaved=self.interleaved)
                 self.out.forward(attended, residual=x)
                 return
             qkv = torch.empty((tokens, self.qkv.out_features), dtype=dtype, device=x.device)

@@ -196,8 +196,10 @@ class Part:
     def load(self, source: WeightSource) -> None:
         pass
 
-    def decode_plan(self, requests: int, max_keys: int, planned_context: int):
+    def decode_plan(self, requests: int, max_keys: int, planned_context: int, page_tokens: int):
         """What this part's launches for a step of one token per request depend on beyond the
         number of requests and the block tables' width (something hashable, or None): a captured
-        step is replayed only for steps with the same plan."""
+        step is replayed only for steps with the same plan.  ``max_keys`` is the tables' width in
+        tokens, ``planned_context`` the longest context the step is laid out for, ``page_tokens``
+        the cache's page size."""
         return None

@@ -31,6 +31,23 @@ def test_plan_follows_the_batch_and_the_context():
     assert kernels.decode_split_plan(64, 4, 4096, 128, 600) != kernels.decode_split_plan(64, 4, 4096, 128, 4096)
 
 
+def test_attention_plan_keeps_short_contexts_resident():
+    """Contexts that fit one CTA's shared memory run the resident kernel, with room in steps of 256
+    keys (a captured step is keyed by the room); longer ones, other head sizes and other page sizes
+    are divided among CTAs."""
+    plan = kernels.decode_attention_plan
+    assert plan(64, 14, 2, 64, 16, 1024, 520) == ("resident", 768)
+    assert plan(64, 14, 2, 64, 16, 1024, 512) == ("resident", 512)
+    assert plan(64, 14, 2, 64, 16, 1024, 100) == ("resident", 256)
+    assert plan(64, 28, 4, 128, 16, 4096, 300) == ("resident", 384)          # the room's limit at head size 128
+    assert plan(8, 14, 2, 64, 16, 1024, 520)[0] == "split"                   # too few CTAs to keep the SMs' copies busy
+    assert plan(64, 14, 2, 64, 16, 1024, 769)[0] == "split"
+    assert plan(64, 14, 2, 64, 16, 4096)[0] == "split"                       # no context given: the tables' width counts
+    assert plan(64, 4, 2, 32, 16, 256, 100)[0] == "split"                    # head size 32
+    assert plan(64, 14, 2, 64, 24, 240, 100)[0] == "split"                   # pages of 24 tokens
+    assert plan(64, 14, 2, 64, 16, 1024, 769)[1:] == kernels.decode_split_plan(64, 2, 1024, 64, 769)
+
+
 def test_captured_decode_steps_are_keyed_by_the_parts_plans(monkeypatch):
     """A graph is reused while the parts lay their launches out alike, and only then."""
     from types import SimpleNamespace
@@ -45,7 +62,7 @@ def test_captured_decode_steps_are_keyed_by_the_parts_plans(monkeypatch):
     monkeypatch.setattr(graphs, "DecodeGraph", FakeGraph)
     asked = []
 
-    def decode_plan(requests, max_keys, planned):
+    def decode_plan(requests, max_keys, planned, page_tokens):
         asked.append((requests, max_keys, planned))
         return ("short",) if planned <= 256 else ("long",)
 
@@ -79,7 +96,7 @@ def test_captured_decode_steps_are_bounded(monkeypatch):
             alive.remove(self.key)
 
     monkeypatch.setattr(graphs, "DecodeGraph", FakeGraph)
-    runner = SimpleNamespace(page_tokens=16, model=SimpleNamespace(decode_plan=lambda requests, max_keys, planned: (planned // 128,)))
+    runner = SimpleNamespace(page_tokens=16, model=SimpleNamespace(decode_plan=lambda requests, max_keys, planned, page_tokens: (planned // 128,)))
     cache = graphs.GraphCache(runner, page_multiple=64, limit=5)
     entry = lambda length: SimpleNamespace(seq=SimpleNamespace(length=length, tables=[[0] * (-(-(length + 1) // 16))]))
     for batch in range(1, 65):

@@ -584,6 +584,87 @@ def test_attention_decode_fused_projection_tail(status, heads, kv_heads, head_di
     assert int(status.item()) == 0
 
 
+RESIDENT_CASES = [
+    (14, 2, 64, 16, [300, 129, 16, 640, 513, 1, 768, 32, 33]), (8, 2, 128, 16, [257, 64, 384, 1, 100]), (4, 4, 64, 8, [61, 1, 130, 8, 9]),
+    (16, 1, 64, 128, [500, 128, 129]), (7, 1, 128, 32, [100, 31]), (3, 3, 64, 64, [64, 65, 700]),
+]
+
+
+@pytest.mark.parametrize("rotate", [False, True])
+@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page,lengths", RESIDENT_CASES)
+def test_attention_decode_resident(status, heads, kv_heads, head_dim, page, lengths, fused, rotate):
+    """Decode attention with each request's whole context in one CTA's shared memory (pages by
+    TMA): against the float64 reference; in the fused form (sums in, rotation, cache append) also
+    against the separate rotary kernel.  Every cache slot outside the requests is NaN."""
+    from sprout_lm_b200 import kernels
+    from sprout_lm_b200.parts import Runtime
+    from sprout_lm_b200.parts.rope import HalfSplitRotary
+    if rotate and not fused:
+        pytest.skip("the rotation belongs to the fused form")
+    R = len(lengths)
+    room = kernels.decode_attention_plan(200, heads, kv_heads, head_dim, page, -(-max(lengths) // page) * page, max(lengths))
+    assert room[0] == "resident"
+    case = build_paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, lengths, [1] * R, seed=7, poison=True)
+    out = torch.full((R, heads * head_dim), float("nan"), dtype=torch.bfloat16, device=DEV)
+    if not fused:
+        kernels.attention_decode_resident(case["k_cache"], case["v_cache"], case["table"], case["context_lens"], out, heads,
+                                          kv_heads, head_dim, status, room[1], q=case["q"])
+        assert (out.double().cpu() - case["want"]).abs().max().item() <= 1.2e-2
+        assert int(status.item()) == 0
+        return
+    width = (heads + 2 * kv_heads) * head_dim
+    g = torch.Generator().manual_seed(11)
+    sums = torch.randn(R, width, generator=g).to(DEV)
+    bias = (torch.randn(width, generator=g) * 0.3).to(DEV)
+    cos, sin = HalfSplitRotary("", head_dim, 1e4, 1024).rotary_tables(Runtime(DEV, torch.bfloat16)) if rotate else (None, None)
+    positions = (case["context_lens"] - 1).to(torch.int32)
+    seq_of_token = torch.arange(R, dtype=torch.int32, device=DEV)
+    # the separate path on a cache without the poison beyond the requests (its kernels are tested for that elsewhere)
+    clean = build_paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, lengths, [1] * R, seed=7)
+    k1, v1 = clean["k_cache"].clone(), clean["v_cache"].clone()
+    acc1 = sums.clone()
+    qkv = torch.zeros(R, width, dtype=torch.bfloat16, device=DEV)
+    kernels.rope_append(qkv, positions, seq_of_token, case["table"], cos, sin, k1, v1, heads, kv_heads, head_dim, page,
+                        True, status, acc=acc1, bias=bias)
+    want = torch.empty(R, heads * head_dim, dtype=torch.bfloat16, device=DEV)
+    kernels.attention_decode(qkv[:, :heads * head_dim], k1, v1, case["table"], case["context_lens"], want, heads,
+                             kv_heads, head_dim, status, split_keys=128)
+    k2, v2 = case["k_cache"].clone(), case["v_cache"].clone()
+    acc2 = sums.clone()
+    kernels.attention_decode_resident(k2, v2, case["table"], case["context_lens"], out, heads, kv_heads, head_dim, status,
+                                      room[1], acc=acc2, bias=bias, cos_table=cos, sin_table=sin)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for r, n in enumerate(lengths):                         # the same append, bit for bit, and nothing else touched
+        pg, slot = int(case["table"][r, (n - 1) // page]), (n - 1) % page
+        assert torch.equal(k2[pg, :, slot], k1[pg, :, slot]) and torch.equal(v2[pg, :, slot], v1[pg, :, slot])
+        k2[pg, :, slot] = case["k_cache"][pg, :, slot]
+        v2[pg, :, slot] = case["v_cache"][pg, :, slot]
+    same = lambda a, b: torch.equal(torch.nan_to_num(a.float(), nan=7.0), torch.nan_to_num(b.float(), nan=7.0))
+    assert same(k2, case["k_cache"]) and same(v2, case["v_cache"])
+    assert float(acc2.abs().max()) == 0.0                   # the sums are cleared
+    assert (out.float() - want.float()).abs().max().item() <= 1.2e-2
+
+
+def test_attention_decode_resident_refuses_a_context_beyond_its_room(status):
+    """A request longer than the launch has room for is flagged in the status word and gets no
+    output; nothing is read or written out of bounds."""
+    from sprout_lm_b200 import kernels
+    case = build_paged_case(torch.bfloat16, 4, 2, 64, 16, [300, 40], [1, 1])
+    out = torch.zeros(2, 4 * 64, dtype=torch.bfloat16, device=DEV)
+    kernels.attention_decode_resident(case["k_cache"], case["v_cache"], case["table"], case["context_lens"], out, 4, 2, 64,
+                                      status, 256, q=case["q"])
+    torch.cuda.synchronize()
+    assert int(status.item()) == 32
+    status.zero_()
+    assert float(out[0].float().abs().max()) == 0.0
+    assert (out[1].double().cpu() - case["want"][1]).abs().max().item() <= 1.2e-2
+    with pytest.raises(kernels.KernelError, match="cap_keys"):
+        kernels.attention_decode_resident(case["k_cache"], case["v_cache"], case["table"], case["context_lens"], out, 4, 2, 64,
+                                          status, 1024, q=case["q"])
+
+
 @pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page,lengths", [(14, 2, 64, 16, [300, 129, 16, 640, 513, 1]),
                                                                    (3, 1, 48, 8, [61, 1, 130]), (4, 2, 64, 16, [3000, 70])])
