@@ -17,8 +17,9 @@
 // the wait each warp normalises one token's row of the residual stream (float32 arithmetic) into
 // a bfloat16 operand in shared memory; the products run on `mma.sync.m16n8k16` with the weights as the 16-row operand and the
 // tokens as the 8 columns (for eight tokens the tensor cores' rate does not matter, latency
-// does); the four quarters of K meet in shared memory, SwiGLU is applied and the activation goes
-// to memory as bfloat16 [tokens, intermediate].  After the barrier each CTA multiplies its piece
+// does); a warp takes a 16-row tile over the whole K, so the gate value and its up value end up
+// in one thread's registers, SwiGLU is applied there and the activation goes to memory as
+// bfloat16 [tokens, intermediate].  After the barrier each CTA multiplies its piece
 // of the down matrix with its K range of the activation and adds the result into the float32
 // residual stream with atomic adds (the order of those float32 additions is not fixed).
 //
@@ -30,11 +31,19 @@
 // WAIT_TIMEOUT bit, the CTA skips its arithmetic but still arrives at the barrier and leaves.
 #include "small_batch.cuh"
 
+#ifdef FFN_STAMPS
+__device__ unsigned long long g_ffn_stamps[2][16];
+#define FFN_STAMP(i) do { if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) g_ffn_stamps[blockIdx.x ? 1 : 0][i] = global_ns(); } while (0)
+extern "C" __attribute__((visibility("default"))) void sprout_ffn_stamps(unsigned long long* out) { cudaMemcpyFromSymbol(out, g_ffn_stamps, sizeof(g_ffn_stamps)); }
+#else
+#define FFN_STAMP(i) do { } while (0)
+#endif
+
 namespace {
 
 constexpr int FFN_THREADS = 256;            // 8 warps
 constexpr int FFN_MAX_TOKENS = SMALL_MAX_TOKENS;
-constexpr int FFN_MAX_TILES_PER_WARP = 4;   // gate/up tiles a warp accumulates (two warp groups share a CTA's tiles)
+constexpr int FFN_MAX_TILES = FFN_THREADS / 32;   // gate/up tiles of a CTA: a warp each
 constexpr int FFN_SMEM_LIMIT = 227 * 1024 - 1024;   // dynamic shared memory; the rest is for the kernel's static variables
 constexpr uint32_t FFN_SPIN_LIMIT = 1u << 21;     // polls of the barrier counter (an L2 round trip each): a second or so
 
@@ -93,6 +102,7 @@ ffn_decode_kernel(const __grid_constant__ CUtensorMap map_gu_base, const __grid_
   uint64_t* bars = (uint64_t*)(smem + p.off_bar);
 
   pdl_launch_dependents();
+  FFN_STAMP(0);
 
   // this CTA's share of the gate/up tiles and its piece of the down matrix
   const int t1_begin = share_begin(p.tiles1, cta, ctas);
@@ -140,7 +150,9 @@ ffn_decode_kernel(const __grid_constant__ CUtensorMap map_gu_base, const __grid_
     const int i = lane + k * 32;
     g[k] = (warp < p.tokens && i < (p.hidden >> 2) && (p.hidden >> 2) <= 256) ? g4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
   }
+  FFN_STAMP(1);
   pdl_wait();
+  FFN_STAMP(2);
 
   // ---- RMSNorm: warp w normalises token w into the bfloat16 operand (float32 arithmetic)
   if (warp < p.tokens) {
@@ -184,60 +196,59 @@ ffn_decode_kernel(const __grid_constant__ CUtensorMap map_gu_base, const __grid_
     }
   }
   __syncthreads();
+  FFN_STAMP(3);
   if (!mbar_wait(&bars[0], 0)) failed = 1;
   __syncthreads();
+  FFN_STAMP(4);
   const bool ok1 = failed == 0;
 
-  // ---- gate/up: warps 0-3 take the first half of the CTA's tiles, warps 4-7 the second; each
-  //      warp of a half one quarter of K
-  const int quarter = warp & 3;
-  const int half_tiles = (nt1 + 1) >> 1;
-  const int tw_begin = warp < 4 ? 0 : half_tiles, tw_end = warp < 4 ? half_tiles : nt1;
-  float acc[FFN_MAX_TILES_PER_WARP][4], odd[FFN_MAX_TILES_PER_WARP][4];   // even and odd K steps: two chains of products per tile
-#pragma unroll
-  for (int i = 0; i < FFN_MAX_TILES_PER_WARP; i++) {
-    acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-    odd[i][0] = odd[i][1] = odd[i][2] = odd[i][3] = 0.f;
-  }
-  if (ok1 && tw_begin < tw_end) {
+  // ---- gate/up: a warp per 16-row tile of the CTA's share (a CTA has at most 8), over the whole K.
+  //      The tile's fragment holds gate rows 0-7 and their up rows 8-15 in the same thread, so SwiGLU
+  //      is applied on the registers and the activation goes straight to memory: nothing is
+  //      gathered among the warps.  Eight chains of products per tile (K steps 0, 8, 16.. / 1, 9, ..)
+  //      keep the dependent `mma.sync` apart.
+  if (ok1 && warp < nt1) {
     const int ksteps1 = p.hidden >> 4;
-    const int kb = share_begin(ksteps1, quarter, 4), ke = share_begin(ksteps1, quarter + 1, 4);
     const uint32_t w1_addr = smem_u32(w1);
-    const int a_row = tw_begin * 16 + (lane & 15);
+    const int a_row = warp * 16 + (lane & 15);
     const uint8_t* b_base = actbuf + (size_t)(lane >> 2) * p.stride1 + (lane & 3) * 4;
-    const int ntw = tw_end - tw_begin;
-    // two K steps at a time, all their loads before their products: the loads overlap
-    for (int k = kb; k < ke; k += 2) {
-      const bool two = k + 1 < ke;
-      uint32_t b[2][2], a[2][FFN_MAX_TILES_PER_WARP][4];
+    constexpr int CHAINS = 8;
+    float acc[CHAINS][4];
 #pragma unroll
-      for (int u = 0; u < 2; u++) {
-        const int kk = (u == 0 || two) ? k + u : k;           // an odd share repeats its last step's loads and skips the product
+    for (int c = 0; c < CHAINS; c++) acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f;
+    int k = 0;
+    for (; k + CHAINS <= ksteps1; k += CHAINS) {
+      uint32_t b[CHAINS][2], a[CHAINS][4];
+#pragma unroll
+      for (int u = 0; u < CHAINS; u++) {                  // all the loads of the steps, then their products
+        const int kk = k + u;
         b[u][0] = *(const uint32_t*)(b_base + kk * 32);
         b[u][1] = *(const uint32_t*)(b_base + kk * 32 + 16);
-        const uint32_t box = w1_addr + (uint32_t)(kk >> 2) * p.box1_bytes;
-        const int chunk = (kk & 3) * 2 + (lane >> 4);
-#pragma unroll
-        for (int i = 0; i < FFN_MAX_TILES_PER_WARP; i++)
-          if (i < ntw) ldmatrix_x4(swizzled(box, a_row + i * 16, chunk), a[u][i][0], a[u][i][1], a[u][i][2], a[u][i][3]);
+        ldmatrix_x4(swizzled(w1_addr + (uint32_t)(kk >> 2) * p.box1_bytes, a_row, (kk & 3) * 2 + (lane >> 4)),
+                    a[u][0], a[u][1], a[u][2], a[u][3]);
       }
 #pragma unroll
-      for (int i = 0; i < FFN_MAX_TILES_PER_WARP; i++)
-        if (i < ntw) mma_bf16(acc[i], a[0][i][0], a[0][i][1], a[0][i][2], a[0][i][3], b[0][0], b[0][1]);
-      if (two) {
-#pragma unroll
-        for (int i = 0; i < FFN_MAX_TILES_PER_WARP; i++)
-          if (i < ntw) mma_bf16(odd[i], a[1][i][0], a[1][i][1], a[1][i][2], a[1][i][3], b[1][0], b[1][1]);
-      }
+      for (int u = 0; u < CHAINS; u++) mma_bf16(acc[u], a[u][0], a[u][1], a[u][2], a[u][3], b[u][0], b[u][1]);
     }
-#pragma unroll
-    for (int i = 0; i < FFN_MAX_TILES_PER_WARP; i++) {
-      acc[i][0] += odd[i][0]; acc[i][1] += odd[i][1]; acc[i][2] += odd[i][2]; acc[i][3] += odd[i][3];
+    for (; k < ksteps1; k++) {
+      uint32_t a0, a1, a2, a3;
+      const uint32_t b0 = *(const uint32_t*)(b_base + k * 32), b1 = *(const uint32_t*)(b_base + k * 32 + 16);
+      ldmatrix_x4(swizzled(w1_addr + (uint32_t)(k >> 2) * p.box1_bytes, a_row, (k & 3) * 2 + (lane >> 4)), a0, a1, a2, a3);
+      mma_bf16(acc[0], a0, a1, a2, a3, b0, b1);
     }
+    float s[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+      s[j] = ((acc[0][j] + acc[1][j]) + (acc[2][j] + acc[3][j])) + ((acc[4][j] + acc[5][j]) + (acc[6][j] + acc[7][j]));
+    // fragment rows 0-7 are gate rows, rows 8-15 the matching up rows: (0, 2) and (1, 3) pair up
+    const int col = (t1_begin + warp) * 8 + (lane >> 2), t0 = (lane & 3) * 2;
+    if (t0 < p.tokens) act[(size_t)t0 * p.inter + col] = __float2bfloat16_rn(ffn_silu_mul(s[0], s[2]));
+    if (t0 + 1 < p.tokens) act[(size_t)(t0 + 1) * p.inter + col] = __float2bfloat16_rn(ffn_silu_mul(s[1], s[3]));
   }
-  __syncthreads();                                   // the operand rows have been read: the room is scratch now
+  __syncthreads();                                   // the operand rows and the gate/up tiles have been read
+  FFN_STAMP(5);
   // The gate/up weights have been used: this CTA's piece of the down matrix takes their place.
-  // It arrives while the activation is finished and the CTAs meet at the barrier.
+  // It arrives while the CTAs meet at the barrier.
   if (tid == 0 && has2) {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     const uint32_t bar = smem_u32(&bars[1]);
@@ -245,30 +256,10 @@ ffn_decode_kernel(const __grid_constant__ CUtensorMap map_gu_base, const __grid_
     for (int b = 0; b < p.boxes2; b++)
       tma_load_2d_addr(smem_u32(w2) + (uint32_t)b * p.box2_bytes, &map_down, bar, k2_begin * 16 + b * 64, t2_begin * 16);
   }
-  float4* scratch = (float4*)actbuf;                 // [quarter][tile of the CTA][lane]
-#pragma unroll
-  for (int i = 0; i < FFN_MAX_TILES_PER_WARP; i++)
-    if (tw_begin + i < tw_end)
-      scratch[(quarter * p.max_tiles1 + tw_begin + i) * 32 + lane] = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-  __syncthreads();
-  if (ok1) {
-    for (int item = tid; item < nt1 * 32; item += FFN_THREADS) {
-      const int tile = item >> 5, l = item & 31;
-      float4 s = scratch[tile * 32 + l];
-#pragma unroll
-      for (int q = 1; q < 4; q++) {
-        const float4 t = scratch[(q * p.max_tiles1 + tile) * 32 + l];
-        s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
-      }
-      // fragment rows 0-7 are gate rows, rows 8-15 the matching up rows: (x, z) and (y, w) pair up
-      const int col = (t1_begin + tile) * 8 + (l >> 2), t0 = (l & 3) * 2;
-      if (t0 < p.tokens) act[(size_t)t0 * p.inter + col] = __float2bfloat16_rn(ffn_silu_mul(s.x, s.z));
-      if (t0 + 1 < p.tokens) act[(size_t)(t0 + 1) * p.inter + col] = __float2bfloat16_rn(ffn_silu_mul(s.y, s.w));
-    }
-  }
 
   // ---- every CTA's share of the activation is in memory after this
   const bool through = ffn_grid_barrier(sync, (unsigned)ctas, p.spin_limit);
+  FFN_STAMP(6);
   if (!through && tid == 0) failed = 1;
 
   // ---- down: this CTA's K range of the activation into shared memory, then its row tiles
@@ -283,8 +274,10 @@ ffn_decode_kernel(const __grid_constant__ CUtensorMap map_gu_base, const __grid_
     }
   }
   __syncthreads();
+  FFN_STAMP(7);
   if (has2 && !mbar_wait(&bars[1], 0)) failed = 1;
   __syncthreads();
+  FFN_STAMP(8);
   if (has2 && failed == 0) {
     const uint8_t* b_base = actbuf + (size_t)(lane >> 2) * stride_b + (lane & 3) * 4;
     for (int tile = warp; tile < nt2; tile += FFN_THREADS / 32) {
@@ -319,6 +312,7 @@ ffn_decode_kernel(const __grid_constant__ CUtensorMap map_gu_base, const __grid_
     }
   }
   __syncthreads();
+  FFN_STAMP(9);
   if (tid == 0) {
     if (failed) atomicOr(status, (int)SPROUT_STATUS_WAIT_TIMEOUT);
     // the last CTA to leave puts the barrier's counters back to zero for the next launch
@@ -348,7 +342,7 @@ bool ffn_make_plan(int tokens, int hidden, int inter, int ctas, float eps, FfnPl
   p.ksteps2 = inter / 16;
   p.base_tiles1 = p.tiles1 / ctas;
   p.max_tiles1 = (p.tiles1 + ctas - 1) / ctas;
-  if (p.max_tiles1 > 2 * FFN_MAX_TILES_PER_WARP) return false;
+  if (p.max_tiles1 > FFN_MAX_TILES) return false;
   if (!plan_pieces(p.tiles2, p.ksteps2, ctas, &p.row_groups, &p.k_splits)) return false;
   p.max_tiles2 = (p.tiles2 + p.row_groups - 1) / p.row_groups;
   p.max_ksteps2 = (p.ksteps2 + p.k_splits - 1) / p.k_splits;
@@ -363,7 +357,6 @@ bool ffn_make_plan(int tokens, int hidden, int inter, int ctas, float eps, FfnPl
   p.off_w2 = 0;
   p.off_act = (int)at;
   long long act_room = (long long)FFN_MAX_TOKENS * p.stride1;                       // the normalised rows,
-  if ((long long)p.max_tiles1 * 2048 > act_room) act_room = (long long)p.max_tiles1 * 2048;   // then the K quarters' sums,
   if ((long long)FFN_MAX_TOKENS * stride_b > act_room) act_room = (long long)FFN_MAX_TOKENS * stride_b;   // then the activation's K range
   at += act_room;
   p.off_bar = (int)at;

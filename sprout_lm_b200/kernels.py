@@ -59,7 +59,8 @@ def load_library(verbose: bool = True):
     global _lib
     with _lock:
         if _lib is None:
-            path = library_path(build=True, verbose=verbose)
+            # SPROUT_KERNEL_LIBRARY names an already built library (an instrumented build, say)
+            path = os.environ.get("SPROUT_KERNEL_LIBRARY") or library_path(build=True, verbose=verbose)
             lib = ctypes.CDLL(str(path))
             lib.sprout_last_error.restype = ctypes.c_char_p
             lib.sprout_abi_version.restype = c_int

@@ -70,9 +70,10 @@ class SwiGLUMLP(Part):
         """x += feed_forward(norm(x)) in one kernel, if this layer and this batch allow it: an
         RMSNorm before it, a few tokens, a layer that fits.  False means nothing was done and the
         caller runs the norm and ``forward``."""
-        if x.shape[0] > self._fused_tokens or getattr(norm, "fused_kind", None) != "rmsnorm":
+        tokens = x.shape[0]
+        if getattr(norm, "fused_kind", None) != "rmsnorm" or tokens > self._fused_tokens:
             return False
-        act = torch.empty((x.shape[0], self.intermediate_size), dtype=torch.bfloat16, device=x.device)
+        act = torch.empty((tokens, self.intermediate_size), dtype=torch.bfloat16, device=x.device)
         kernels.ffn_decode(x, norm.gain, norm.eps, self.gate_up.weight, self.down.weight, act, self._sync,
                            self.gate_up.status)
         return True
