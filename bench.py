@@ -468,8 +468,12 @@ def timed_decode_attention(shape: str, batch: int, context: int, repeats: int = 
     planned = -(-context // 128) * 128
 
     def replayed(split_keys):
-        call = lambda: kernels.attention_decode(q, k, v, table, lens, out, heads, kv_heads, head_dim, status,
-                                                split_keys=split_keys, live_keys=planned)
+        if split_keys == "resident":
+            room = min(kernels.resident_cap(heads, kv_heads, head_dim, page), -(-context // 256) * 256)
+            call = lambda: kernels.attention_decode_resident(k, v, table, lens, out, heads, kv_heads, head_dim, status, room, q=q)
+        else:
+            call = lambda: kernels.attention_decode(q, k, v, table, lens, out, heads, kv_heads, head_dim, status,
+                                                    split_keys=split_keys, live_keys=planned)
         for _ in range(3):
             call()
         torch.cuda.synchronize()
@@ -500,6 +504,11 @@ def timed_decode_attention(shape: str, batch: int, context: int, repeats: int = 
     for passes in (1, 2, 4, 8, 16, 32, width * page // 128):
         if passes * 128 <= width * page and width * page // (passes * 128) <= 256:
             result["other_splits_us"][str(passes * 128)] = round(replayed(passes * 128), 1)
+    if context <= kernels.resident_cap(heads, kv_heads, head_dim, page):
+        # the whole context of a (request, key/value head) in one CTA's shared memory, pages by TMA
+        us = replayed("resident")
+        result["resident_us"], result["resident_gbs"] = round(us, 1), round(megabytes / us * 1e3)
+        result["engine_takes"] = kernels.decode_attention_plan(batch, heads, kv_heads, head_dim, page, width * page, planned)[0]
     assert int(status.item()) == 0
     return result
 
@@ -607,9 +616,16 @@ def run(args) -> dict:
     if args.only == "decode":
         sampler.stop()
         step_bytes = weight_bytes(model) + batch * main["mean_context"] * cache_bytes_per_token(model, torch.bfloat16)
-        return {"impl": "ours", "only": "decode", "shape": args.shape, "layers": layers, "batch": batch,
-                "ms_per_step": round(main["ms_per_step"], 4), "launches_per_step": main["launches_per_step"],
-                "gbs": round(step_bytes / (main["ms_per_step"] / 1000) / 1e9, 1)}
+        out = {"impl": "ours", "only": "decode", "shape": args.shape, "layers": layers, "batch": batch,
+               "ms_per_step": round(main["ms_per_step"], 4), "launches_per_step": main["launches_per_step"],
+               "gbs": round(step_bytes / (main["ms_per_step"] / 1000) / 1e9, 1)}
+        phases = kernels.ffn_decode_phase_stamps()       # from a build with SPROUT_BUILD_FLAGS=-DFFN_STAMPS
+        if phases:
+            out["ffn_decode_phases_us"] = {k: {n: round(v, 2) for n, v in d.items()} for k, d in phases.items()}
+        timeline = kernels.decode_timeline()             # from a build with SPROUT_BUILD_FLAGS=-DSPROUT_TIMELINE
+        if timeline:
+            out["last_layer_timeline_us"] = {k: {n: round(v, 2) for n, v in d.items()} for k, d in timeline.items()}
+        return out
     points = {}
     for b in (1, 64):
         points[f"decode_b{b}"] = round(timed_decode(runner, b, prompt_len, args.steps, args.warmup, rng)["tokens_per_s"], 1)

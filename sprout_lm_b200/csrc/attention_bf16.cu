@@ -320,6 +320,7 @@ attention_decode_mma_kernel(const DecodeParams p) {
   float* wl = wm + 64;                                // [4][16]
 
   pdl_launch_dependents();
+  SPROUT_TL_ENTRY(0);
   // What this step's earlier kernels wrote is the query (or the float32 sums) and the newest
   // position's key and value.  The block table and the lengths were copied before the step's first
   // kernel, and the keys and values of earlier positions were written in earlier steps (a step
@@ -390,7 +391,7 @@ attention_decode_mma_kernel(const DecodeParams p) {
       }
     }
     cp_async_commit();
-    if (first) pdl_wait();                             // the first pass's keys and values are on their way
+    if (first) { pdl_wait(); SPROUT_TL_WAITED(0); }    // the first pass's keys and values are on their way
     if (!FUSED && first) {
       for (int idx = tid; idx < 16 * CHUNKS; idx += DEC_THREADS) {
         const int row = idx / CHUNKS, c = idx % CHUNKS;
@@ -655,6 +656,7 @@ attention_decode_mma_kernel(const DecodeParams p) {
     }
     cluster.sync();                                    // nobody leaves while its shared memory is being read
   }
+  SPROUT_TL_EXIT(0);
 }
 
 template <int HD, bool FUSED>
@@ -1232,3 +1234,5 @@ SPROUT_API int sprout_attention_decode_static(const void* q, int q_stride, const
                                  scratch, requests, heads, kv_heads, head_dim, page_tokens, num_pages, split_keys, splits,
                                  status, stream);
 }
+
+SPROUT_TL_READER(attention_bf16)

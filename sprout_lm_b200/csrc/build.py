@@ -45,12 +45,18 @@ def sources() -> list[Path]:
     return sorted(SOURCE_DIR.glob("*.cu"))
 
 
-def _digest(nvcc: str) -> str:
+def extra_flags_from_environment() -> tuple[str, ...]:
+    """SPROUT_BUILD_FLAGS adds compiler flags (an instrumented build: ``-DFFN_STAMPS``); the library's
+    name carries them, so such a build lives beside the ordinary one."""
+    return tuple(os.environ.get("SPROUT_BUILD_FLAGS", "").split())
+
+
+def _digest(nvcc: str, extra_flags: tuple[str, ...] = ()) -> str:
     h = hashlib.sha256()
     for path in sorted(list(SOURCE_DIR.glob("*.cu")) + list(SOURCE_DIR.glob("*.cuh")) + list(SOURCE_DIR.glob("*.h"))):
         h.update(path.name.encode())
         h.update(path.read_bytes())
-    h.update(" ".join(ARCH_FLAGS + COMMON_FLAGS).encode())
+    h.update(" ".join(ARCH_FLAGS + COMMON_FLAGS + list(extra_flags)).encode())
     try:
         h.update(subprocess.run([nvcc, "--version"], capture_output=True, text=True).stdout.encode())
     except OSError:
@@ -81,7 +87,8 @@ def library_path(build: bool = True, verbose: bool = True, extra_flags: tuple[st
     """Path of the built library, compiling it first if needed (and ``build``)."""
     nvcc = find_nvcc()
     out_dir = _build_dir()
-    target = out_dir / f"libsprout_kernels_{_digest(nvcc)}.so"
+    extra_flags = tuple(extra_flags) + extra_flags_from_environment()
+    target = out_dir / f"libsprout_kernels_{_digest(nvcc, extra_flags)}.so"
     if target.exists():
         return target
     if not build:
@@ -117,7 +124,7 @@ def library_path(build: bool = True, verbose: bool = True, extra_flags: tuple[st
         raise BuildError(f"linking failed:\n{done.stdout}\n{done.stderr}")
     os.replace(partial, target)          # atomic: a concurrent builder sees nothing or the whole file
     for stale in out_dir.glob("libsprout_kernels_*.so"):
-        if stale != target:
+        if stale != target and not extra_flags:          # an instrumented build leaves the ordinary one alone
             try:
                 stale.unlink()               # libraries of older sources
             except OSError:

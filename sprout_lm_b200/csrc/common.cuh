@@ -60,6 +60,28 @@ inline cudaError_t sprout_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block
   return cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
 }
 
+// With -DSPROUT_TIMELINE the kernels of a decode layer record when they ran (%globaltimer, ns): per
+// file up to four kernels, each with the entry of its first CTA, the latest return of any CTA's
+// wait for the earlier kernels, and the latest exit of any CTA's first thread.  Time only grows, so
+// after a step the records are those of its last layer.  sprout_timeline_<file>(out) copies them out.
+#ifdef SPROUT_TIMELINE
+static __device__ unsigned long long g_sprout_tl[4][4];
+__device__ __forceinline__ unsigned long long sprout_now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define SPROUT_TL_ENTRY(slot) do { if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) g_sprout_tl[slot][0] = sprout_now_ns(); } while (0)
+#define SPROUT_TL_WAITED(slot) do { if (threadIdx.x == 0) atomicMax(&g_sprout_tl[slot][1], sprout_now_ns()); } while (0)
+#define SPROUT_TL_EXIT(slot) do { if (threadIdx.x == 0) atomicMax(&g_sprout_tl[slot][2], sprout_now_ns()); } while (0)
+#define SPROUT_TL_READER(name) extern "C" __attribute__((visibility("default"))) void sprout_timeline_##name(unsigned long long* out) { cudaMemcpyFromSymbol(out, g_sprout_tl, sizeof(g_sprout_tl)); }
+#else
+#define SPROUT_TL_ENTRY(slot) do { } while (0)
+#define SPROUT_TL_WAITED(slot) do { } while (0)
+#define SPROUT_TL_EXIT(slot) do { } while (0)
+#define SPROUT_TL_READER(name)
+#endif
+
 #define SPROUT_REQUIRE(cond, ...) \
   do { if (!(cond)) return sprout_fail(__VA_ARGS__); } while (0)
 

@@ -31,6 +31,9 @@
 // WAIT_TIMEOUT bit, the CTA skips its arithmetic but still arrives at the barrier and leaves.
 #include "small_batch.cuh"
 
+// With -DFFN_STAMPS the first thread of the first and of the last CTA records the time (%globaltimer)
+// at the end of each phase; sprout_ffn_stamps copies the last launch's records out.  Measurements
+// of where the kernel's time goes inside a real decode step come from such a build.
 #ifdef FFN_STAMPS
 __device__ unsigned long long g_ffn_stamps[2][16];
 #define FFN_STAMP(i) do { if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) g_ffn_stamps[blockIdx.x ? 1 : 0][i] = global_ns(); } while (0)
@@ -102,6 +105,7 @@ ffn_decode_kernel(const __grid_constant__ CUtensorMap map_gu_base, const __grid_
   uint64_t* bars = (uint64_t*)(smem + p.off_bar);
 
   pdl_launch_dependents();
+  SPROUT_TL_ENTRY(0);
   FFN_STAMP(0);
 
   // this CTA's share of the gate/up tiles and its piece of the down matrix
@@ -152,6 +156,7 @@ ffn_decode_kernel(const __grid_constant__ CUtensorMap map_gu_base, const __grid_
   }
   FFN_STAMP(1);
   pdl_wait();
+  SPROUT_TL_WAITED(0);
   FFN_STAMP(2);
 
   // ---- RMSNorm: warp w normalises token w into the bfloat16 operand (float32 arithmetic)
@@ -322,6 +327,7 @@ ffn_decode_kernel(const __grid_constant__ CUtensorMap map_gu_base, const __grid_
       sync[1] = 0u;
     }
   }
+  SPROUT_TL_EXIT(0);
 }
 
 }  // namespace
@@ -425,3 +431,5 @@ SPROUT_API int sprout_ffn_decode(float* x, const float* gain, const void* w_gate
   SPROUT_REQUIRE(err == cudaSuccess, "ffn_decode: launch failed: %s", cudaGetErrorString(err));
   return 0;
 }
+
+SPROUT_TL_READER(ffn_decode)

@@ -124,6 +124,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
   };
 
   pdl_launch_dependents();
+  SPROUT_TL_ENTRY(0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], PAIR ? 16 : 8); }
@@ -179,6 +180,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
           copy(smem_base + i * L::STAGE_BYTES + W_OFF, weight_map, count_base + 8 * i, (k.kb_begin + i) * BLOCK_K, weight_row);
         }
         pdl_wait();
+        SPROUT_TL_WAITED(0);
       }
       int x = k.kb_begin * BLOCK_K;
       for (int i = 0; i < k.num_kb; i++, it++, x += BLOCK_K) {
@@ -427,6 +429,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
   __syncthreads();
   if (PAIR) cluster_barrier();      // neither CTA leaves while the other may still count on its barriers or read its memory
   if (warp == 1) tmem_dealloc(tmem_base, L::TMEM_COLS);
+  SPROUT_TL_EXIT(0);
 }
 
 // ------------------------------------------------------------------ host side
@@ -584,3 +587,5 @@ SPROUT_API int sprout_gemm_bf16(const void* A, const void* W, const float* bias,
     default: return launch<128, false>(map_a, map_w, map_out, p, (int)work, stream);
   }
 }
+
+SPROUT_TL_READER(gemm_tcgen05)

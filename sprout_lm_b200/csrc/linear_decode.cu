@@ -52,6 +52,7 @@ linear_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloa
   uint64_t* bar = (uint64_t*)(smem + p.off_bar);
 
   pdl_launch_dependents();
+  SPROUT_TL_ENTRY(p.normed ? 0 : 1);
 
   const int group = blockIdx.x / p.k_splits, split = blockIdx.x % p.k_splits;
   const int t_begin = share_begin(p.tiles, group, p.row_groups);
@@ -72,6 +73,7 @@ linear_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloa
     for (int i = tid; i < nk * 16; i += LIN_THREADS) gain_s[i] = gain[k_begin * 16 + i];
 
   pdl_wait();
+  SPROUT_TL_WAITED(p.normed ? 0 : 1);
 
   // ---- this CTA's K range of the tokens' rows, bfloat16, rows of nk * 32 + 16 bytes
   const int stride_b = nk * 32 + 16;
@@ -172,6 +174,7 @@ linear_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloa
   } else if (tid == 0) {
     atomicOr(status, (int)SPROUT_STATUS_WAIT_TIMEOUT);
   }
+  SPROUT_TL_EXIT(p.normed ? 0 : 1);
 }
 
 bool lin_make_plan(int tokens, int n, int k, int ctas, LinPlan* out) {
@@ -252,3 +255,5 @@ SPROUT_API int sprout_linear_decode(const void* a, int lda, const float* x, cons
   SPROUT_REQUIRE(err == cudaSuccess, "linear_decode: launch failed: %s", cudaGetErrorString(err));
   return 0;
 }
+
+SPROUT_TL_READER(linear_decode)

@@ -185,8 +185,16 @@ class DecodeGraph:
             self.launches = kernels.LAUNCHES - before
             self.graph = graph
             return result
+        self.launch(entries, temperatures, uniforms)
+        return self.collect()
+
+    def launch(self, entries, temperatures, uniforms) -> None:
+        """Stage the batch and start the captured step; ``collect`` waits for it.  The host is free
+        in between (the scheduler does its bookkeeping of the step before while this one runs)."""
         self.stage(entries, temperatures, uniforms, copy=False)
         self.graph.replay()
+
+    def collect(self) -> list:
         torch.cuda.current_stream().synchronize()      # the tokens are in pinned memory, the mirror has been read
         self.last_logits = self.logits
         return self.host_tokens.tolist()

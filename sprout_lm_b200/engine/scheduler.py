@@ -40,10 +40,13 @@ class EngineOptions:
     # and is preempted again, tick after tick.  With this option a request waits in the queue
     # until the pool can hold its history beside what the running requests still have to take.
     admit_within_pool: bool = False
+    # Not in the reference either: start the next decode step before this step's report is read,
+    # when it is already known what that step will be (see Engine._launch_ahead).
+    launch_ahead: bool = True
 
     def validate(self):
         for name, value in asdict(self).items():
-            if name in ("prefix_caching", "record_trace", "admit_within_pool"):
+            if name in ("prefix_caching", "record_trace", "admit_within_pool", "launch_ahead"):
                 if not isinstance(value, bool):
                     raise ValueError(f"{name} must be a boolean.")
             elif not isinstance(value, int) or isinstance(value, bool) or value <= 0:
@@ -255,7 +258,26 @@ class Engine:
                     row += 1
                 work.append({"id": request.id, "phase": phase, "from": start, "tokens": len(tokens),
                              "blockTable": table})
+        self._launch_ahead()
         return StepReport(tick=self._tick, work=work, events=events, cache=self.cache)
+
+    def _launch_ahead(self) -> None:
+        """When the next step is known already (every running request decodes on, nobody waits to
+        be admitted), hand it to the runner now: a runner that can starts it at once, and the device
+        works on it while this step's report is put together and read.  The next call plans as
+        always; if it arrives at the same batch it takes the result, if not (a request was added or
+        cancelled in between) the launch is dropped and nothing is lost but its work."""
+        ahead = getattr(self.runner, "launch_ahead", None)
+        if ahead is None or not self.options.launch_ahead or self._waiting or not self._active \
+                or len(self._active) > self.options.max_batch_tokens:
+            return
+        batch = sorted(self._active.values(), key=lambda r: r.order)
+        if any(self._phase(r) != "decode" for r in batch):
+            return
+        entries = [StepEntry(r.seq, [r.output[-1]], [0]) for r in batch]
+        temperatures = [r.temperature for r in batch]
+        uniforms = [uniform_for(r.seed, r.id, len(r.output)) if r.temperature > 0 else 0.0 for r in batch]
+        ahead(entries, temperatures, uniforms)
 
     def _accept(self, request: Request, token: int) -> None:
         request.output.append(token)

@@ -43,6 +43,9 @@ class ModelRunner:
         self.eos_token_ids = tuple(model.spec.eos_token_ids)
         self.steps_run = 0
         self.last_decode_graph = None      # the captured decode step that ran last
+        self._ahead = None                 # (signature, graph) of a decode step launched before it was asked for
+        self.ahead_used = 0                # such steps that the scheduler then asked for as launched
+        self.ahead_dropped = 0             # and those it did not (their work is done again by the step that came instead)
         # bytes copied to and from the device by steps (the batch's arrays up, token ids or logits down)
         self.stats = {"h2d_bytes": 0, "d2h_bytes": 0}
         from .graphs import GraphCache, StepGraphs
@@ -105,10 +108,54 @@ class ModelRunner:
                 if type(w) is not int or w < 0 or w >= len(tokens):
                     raise StepError("a wanted place lies outside the entry's tokens")
 
+    # ------------------------------------------------------------------ a decode step launched ahead
+    @staticmethod
+    def _signature(entries, temperatures, uniforms):
+        return (tuple((id(e.seq), e.seq.length, e.tokens[0]) for e in entries), tuple(temperatures), tuple(uniforms))
+
+    def launch_ahead(self, entries: list[StepEntry], temperatures, uniforms) -> bool:
+        """Start a decode step (one token per request, already captured) without waiting for it:
+        the scheduler calls this at the end of a step when it knows what the next step will be, so
+        that the device runs it while the host still accounts for the step before.  The next
+        ``step_and_sample`` with the same batch takes its result; any other call waits for it and
+        lets it go (it wrote only cache slots that the step which comes instead writes again, which
+        is why models with per-request state never launch ahead).  False: nothing was launched."""
+        if self._ahead is not None or not self.graphs.enabled or self.manager.state_slot_count:
+            return False
+        if not entries or any(len(e.tokens) != 1 or e.want != [0] for e in entries):
+            return False
+        for e in entries:
+            if e.seq.released or not self.reserve(e.seq, e.seq.length + 1):
+                return False                       # the planner decides what happens when pages run out
+        self.validate(entries)
+        graph = self.graphs.get(entries)
+        if graph.graph is None:
+            return False                           # a first use runs eagerly and captures: through the ordinary path
+        graph.launch(entries, temperatures, uniforms)
+        self._ahead = (self._signature(entries, temperatures, uniforms), graph)
+        return True
+
+    def _take_ahead(self, entries, temperatures, uniforms):
+        """The result of the step launched ahead if it is the step now asked for, else None (after
+        waiting for it)."""
+        if self._ahead is None:
+            return None
+        signature, graph = self._ahead
+        self._ahead = None
+        sampled = graph.collect()
+        if entries is not None and all(len(e.tokens) == 1 and e.want == [0] for e in entries) \
+                and signature == self._signature(entries, temperatures, uniforms):
+            self.ahead_used += 1
+            self.last_decode_graph = graph
+            return sampled
+        self.ahead_dropped += 1
+        return None
+
     def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
         """Run one batch.  Returns float32 logits [wanted places, vocab] in the order of the
         entries and of their ``want`` lists, or None when nothing is wanted.  The requests'
         lengths are advanced."""
+        self._take_ahead(None, None, None)
         self.validate(entries)
         key, width = self.step_graphs.plan(entries, sample=False)
         ctx = self.stager.stage(entries, self.page_tokens, fixed_pages=width)
@@ -130,9 +177,12 @@ class ModelRunner:
         runs as a replayed CUDA graph."""
         self.validate(entries)
         decode_only = self.graphs.enabled and all(len(e.tokens) == 1 and e.want == [0] for e in entries)
+        sampled = self._take_ahead(entries, temperatures, uniforms)
         if decode_only:
-            graph = self.last_decode_graph = self.graphs.get(entries)
-            sampled = graph.run(entries, temperatures, uniforms)
+            if sampled is None:
+                graph = self.last_decode_graph = self.graphs.get(entries)
+                sampled = graph.run(entries, temperatures, uniforms)
+            graph = self.last_decode_graph
             self.stats["h2d_bytes"] += graph.stager.last_bytes
             self.stats["d2h_bytes"] += len(sampled) * 4
             for e in entries:
@@ -164,6 +214,7 @@ class ModelRunner:
         """A device-side run of decode steps (see ``graphs.DecodeLoop``): pages for ``max_steps``
         more tokens per request are reserved here."""
         from .graphs import DecodeLoop
+        self._take_ahead(None, None, None)
         for e in entries:
             if not self.reserve(e.seq, e.seq.length + 1 + max_steps):
                 raise StepError("not enough pages for a device-side decode loop")
@@ -182,6 +233,7 @@ class ModelRunner:
         """Read the device status word (synchronises); raise if a kernel flagged bad input.  A
         flagged step may have left sums in the accumulation workspaces: they are zeroed, so that the
         next step starts clean."""
+        self._take_ahead(None, None, None)
         word = int(self.runtime.status.item())
         if word:
             self.runtime.status.zero_()

@@ -365,6 +365,46 @@ def small_batch_plan(kind: str, tokens: int, rows: int, cols: int, ctas: int | N
     return dict(zip(names, out))
 
 
+FFN_PHASES = ("entry", "weights requested", "earlier kernels done", "norm", "weights there", "gate/up and SwiGLU",
+              "barrier passed", "activation fetched", "down piece there", "down done")
+
+
+def ffn_decode_phase_stamps() -> dict | None:
+    """Microseconds from a CTA's entry to the end of each phase of the last ``ffn_decode`` launch,
+    for its first and its last CTA, from a library built with ``SPROUT_BUILD_FLAGS=-DFFN_STAMPS``
+    (None from an ordinary build).  Synchronises the device."""
+    lib = _lib or load_library()
+    if not hasattr(lib, "sprout_ffn_stamps"):
+        return None
+    torch.cuda.synchronize()
+    raw = (ctypes.c_ulonglong * 32)()
+    lib.sprout_ffn_stamps(raw)
+    return {which: {name: (raw[16 * c + i] - raw[16 * c]) / 1000.0 for i, name in enumerate(FFN_PHASES)}
+            for c, which in enumerate(("first CTA", "last CTA"))}
+
+
+def decode_timeline() -> dict | None:
+    """When the kernels of the last decode layer ran, from a library built with
+    ``SPROUT_BUILD_FLAGS=-DSPROUT_TIMELINE`` (None from an ordinary build): per kernel the entry of
+    its first CTA, the latest return of a CTA's wait for the earlier kernels and the latest exit,
+    in microseconds after the first of these times.  The last product (the output head) stands
+    for the kernel after the last layer.  Synchronises the device."""
+    lib = _lib or load_library()
+    if not hasattr(lib, "sprout_timeline_ffn_decode"):
+        return None
+    torch.cuda.synchronize()
+    records = {}
+    for label, reader, slot in (("norm + q/k/v", "linear_decode", 0), ("attention", "attention_bf16", 0),
+                                ("output projection", "linear_decode", 1), ("feed-forward", "ffn_decode", 0),
+                                ("head product", "gemm_tcgen05", 0)):
+        raw = (ctypes.c_ulonglong * 16)()
+        getattr(lib, "sprout_timeline_" + reader)(raw)
+        records[label] = [raw[4 * slot], raw[4 * slot + 1], raw[4 * slot + 2]]
+    origin = min(v[0] for v in records.values() if v[0])
+    return {label: {"entry": (v[0] - origin) / 1000.0, "waited": (v[1] - origin) / 1000.0, "exit": (v[2] - origin) / 1000.0}
+            for label, v in records.items() if v[0]}
+
+
 def ffn_decode_supported(tokens: int, hidden: int, intermediate: int) -> bool:
     """Whether ``ffn_decode`` takes these sizes: 1..8 tokens, sizes that are multiples of 16, and a
     layer small enough for every CTA to hold its share of the two matrices in shared memory."""
@@ -505,10 +545,11 @@ def decode_attention_plan(requests: int, heads: int, kv_heads: int, head_dim: in
     per split, splits, through memory)`` as ``decode_split_plan`` lays it out."""
     planned = max(1, min(max_keys, planned_keys if planned_keys else max_keys))
     # One CTA per (request, key/value head) pulls its whole context alone: that pays once there are
-    # enough of them to keep most SMs' copy engines busy (measured at the 0.5B sizes: batch 64 gains
-    # 7 % of its step, batch 8 loses 2 % against splits in a cluster, batch 32 is even).
+    # enough of them to keep the SMs' copy engines busy, and as long as they all fit the SMs at once
+    # (they are one to an SM).  Measured alone at the 0.5B sizes, 640 keys each, split plan against
+    # resident: 8 requests 4.6 / 5.4 us, 32: 8.0 / 5.5, 64: 11.1 / 7.7, 128: 14.4 / 14.3, 256: 19.2 / 28.9.
     sms = sm_count() if torch.cuda.is_available() else 148
-    if RESIDENT_ENABLED and head_dim in (64, 128) and requests * kv_heads >= (3 * sms) // 5:
+    if RESIDENT_ENABLED and head_dim in (64, 128) and (3 * sms) // 8 <= requests * kv_heads <= 2 * sms:
         cap = resident_cap(heads, kv_heads, head_dim, page_tokens)
         room = min(cap, -(-planned // RESIDENT_STEP) * RESIDENT_STEP)
         if planned <= room:

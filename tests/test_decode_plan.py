@@ -41,6 +41,7 @@ def test_attention_plan_keeps_short_contexts_resident():
     assert plan(64, 14, 2, 64, 16, 1024, 100) == ("resident", 256)
     assert plan(64, 28, 4, 128, 16, 4096, 300) == ("resident", 384)          # the room's limit at head size 128
     assert plan(8, 14, 2, 64, 16, 1024, 520)[0] == "split"                   # too few CTAs to keep the SMs' copies busy
+    assert plan(256, 14, 2, 64, 16, 1024, 520)[0] == "split"                 # more CTAs than fit the SMs at once
     assert plan(64, 14, 2, 64, 16, 1024, 769)[0] == "split"
     assert plan(64, 14, 2, 64, 16, 4096)[0] == "split"                       # no context given: the tables' width counts
     assert plan(64, 4, 2, 32, 16, 256, 100)[0] == "split"                    # head size 32

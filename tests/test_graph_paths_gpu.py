@@ -205,3 +205,85 @@ def test_captured_mixed_step_with_sampling(model_dirs, dtype):
     for prompts, tokens in zip(rounds, captured):
         check_tokens(model_dirs[name], prompts[0], [tokens[0]], dtype, "captured mixed step")
         assert 0 <= tokens[1] < sizes["vocab_size"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_steps_launched_ahead_give_the_same_tokens(model_dirs, dtype):
+    """The scheduler starts the next decode step before it has finished accounting for the step
+    before (``EngineOptions.launch_ahead``).  Same tokens as without, most steps taken from the
+    launch, and a request added in the middle (which makes the launched step the wrong one) still
+    gets, and leaves to the others, the plain implementation's tokens."""
+    from sprout_lm_b200 import EngineOptions, load_model, make_engine
+    name = "B"
+    sizes, _, page = helpers.TINY[name]
+    model = load_model(model_dirs[name], dtype=dtype)
+    rng = np.random.default_rng(61)
+    prompts = [helpers.random_tokens(rng, n, sizes["vocab_size"]) for n in (9, 30, 18, 5)]
+    outputs = {}
+    for ahead in (False, True):
+        engine = make_engine(model, EngineOptions(block_size=page, num_blocks=64, max_sequences=4, max_batch_tokens=64,
+                                                  prefill_chunk_size=16, prefix_caching=False, launch_ahead=ahead))
+        for i, prompt in enumerate(prompts[:3]):
+            engine.add(f"r{i}", prompt, 40, ignore_eos=True)
+        steps = 0
+        while engine.pending:
+            engine.step()
+            steps += 1
+            if steps == 20:
+                engine.add("r3", prompts[3], 12, ignore_eos=True)
+        engine.runner.check_status()
+        outputs[ahead] = [engine.result(f"r{i}")["output"] for i in range(4)]
+        runner = engine.runner
+        if ahead:
+            assert runner.ahead_used >= 25 and runner.ahead_dropped >= 1
+        else:
+            assert runner.ahead_used == 0 and runner.ahead_dropped == 0
+        assert runner.manager.free_pages() == 64
+    if dtype == "float32":
+        assert outputs[True] == outputs[False]
+    for prompt, output in zip(prompts, outputs[True]):
+        check_tokens(model_dirs[name], prompt, output, dtype, f"launch ahead/{dtype}")
+
+
+def test_large_batch_decodes_with_resident_contexts(tmp_path):
+    """A batch large enough for the attention kernel that keeps a request's whole context in one
+    CTA's shared memory (head size 64, 48 requests of 2 key/value heads): the logits inside the
+    replayed decode steps against the plain implementation, with prompts of many lengths so that
+    pages end everywhere, and the plan checked to be the resident one."""
+    from sprout_lm_b200 import kernels, load_model
+    from sprout_lm_b200.config import parse_config
+    from sprout_lm_b200.engine.batch import StepEntry
+    from sprout_lm_b200.engine.step import ModelRunner
+    from sprout_lm_b200.weights import write_random_model
+    sizes = dict(hidden_size=896, intermediate_size=512, num_hidden_layers=2, num_attention_heads=14, num_key_value_heads=2,
+                 vocab_size=600, max_position_embeddings=1024, rms_norm_eps=1e-6, rope_theta=1000000.0,
+                 tie_word_embeddings=False, eos_token_id=599)
+    folder = write_random_model(tmp_path / "wide", parse_config(helpers.raw_config(sizes)), seed=9)
+    model = load_model(folder, dtype="bfloat16")
+    batch, decode, page = 48, 12, 16
+    rng = np.random.default_rng(67)
+    heads = [int(n) for n in rng.integers(1, 300, batch)]
+    heads[0], heads[1] = 255, 256                        # a context that fills its pages exactly, and one more
+    requests = {f"w{i}": helpers.random_tokens(rng, n + decode, 600) for i, n in enumerate(heads)}
+    want = {rid: helpers.plain_logits(folder, toks) for rid, toks in requests.items()}
+    scale = max(float(np.abs(w).max()) for w in want.values())
+    runner = ModelRunner(model, num_pages=sum(-(-len(t) // page) for t in requests.values()), page_tokens=page,
+                         max_requests=batch, prefix_caching=False)
+    seqs = {}
+    for (rid, toks), head in zip(requests.items(), heads):
+        seqs[rid] = runner.new_sequence()
+        assert runner.reserve(seqs[rid], head)
+        runner.step([StepEntry(seqs[rid], toks[:head], [])])
+    for step in range(decode):
+        for rid in requests:
+            assert runner.reserve(seqs[rid], seqs[rid].length + 1)
+        entries = [StepEntry(seqs[rid], [requests[rid][head + step]], [0]) for rid, head in zip(requests, heads)]
+        runner.step_and_sample(entries, [0.0] * batch, [0.0] * batch)
+        graph = runner.last_decode_graph
+        plan = model.decode_plan(batch, graph.table_pages * page, graph.ctx.planned_context, page)
+        assert plan[0][0] == "resident", plan[0]
+        logits = graph.last_logits.float().cpu().numpy()
+        for row, (rid, head) in zip(logits, zip(requests, heads)):
+            err = float(np.abs(row - want[rid][head + step]).max())
+            assert err <= 0.02 * scale, f"request {rid} position {head + step} differs by {err:.3e} (scale {scale:.3f})"
+    runner.check_status()

@@ -238,7 +238,7 @@ def test_a_flagged_step_leaves_no_sums_behind():
     a += 5.0
     runtime.status.fill_(16)
     fake = ModelRunner.__new__(ModelRunner)
-    fake.runtime = runtime
+    fake.runtime, fake._ahead = runtime, None
     with pytest.raises(StepError, match="position outside the rotary table"):
         fake.check_status()
     assert float(a.abs().max()) == 0.0 and int(runtime.status.item()) == 0

@@ -265,3 +265,76 @@ def test_admission_within_the_pool_stops_the_preemption_loop(prefix_caching):
     assert held == plain == [reference_output(p, 20, 50) for p in prompts]
     assert plain_preempted > 3 * max(held_preempted, 1)          # the loop is gone
     assert held_ticks <= plain_ticks
+
+
+class AheadRunner:
+    """A stub runner that can start a decode step ahead of being asked for it: it computes the
+    step's tokens at once from a copy of the request's state and hands them out when the same
+    batch is asked for, as the device-side runner does with a launched graph."""
+
+    def __init__(self, inner):
+        self.inner = inner
+        self.pending = None
+        self.launched, self.used, self.dropped = 0, 0, 0
+
+    def __getattr__(self, name):
+        return getattr(self.inner, name)
+
+    @staticmethod
+    def signature(entries, temperatures, uniforms):
+        return (tuple((id(e.seq), e.seq.length, tuple(e.tokens), tuple(e.want)) for e in entries), tuple(temperatures), tuple(uniforms))
+
+    def launch_ahead(self, entries, temperatures, uniforms):
+        assert self.pending is None, "two steps launched ahead at once"
+        assert all(len(e.tokens) == 1 and e.want == [0] for e in entries), "only single decode tokens are launched ahead"
+        for e in entries:
+            if not self.inner.reserve(e.seq, e.seq.length + 1):
+                return False
+        self.pending = (self.signature(entries, temperatures, uniforms), entries, temperatures, uniforms)
+        self.launched += 1
+        return True
+
+    def step_and_sample(self, entries, temperatures, uniforms):
+        pending, self.pending = self.pending, None
+        if pending is not None:
+            if pending[0] == self.signature(entries, temperatures, uniforms):
+                self.used += 1
+            else:
+                self.dropped += 1
+        return self.inner.step_and_sample(entries, temperatures, uniforms)
+
+
+def test_the_next_decode_step_is_launched_ahead_only_when_it_is_known():
+    """With every running request decoding on and nobody waiting, the scheduler hands the next
+    step to the runner at the end of the step before; a late arrival or a cancellation makes the
+    next plan differ and the launch is dropped.  Tokens are the same either way."""
+    import numpy as np
+    rng = np.random.default_rng(3)
+    prompts = [[int(t) for t in rng.integers(0, 50, n)] for n in (5, 11, 7)]
+
+    def run(launch_ahead):
+        options = EngineOptions(block_size=4, num_blocks=40, max_sequences=4, max_batch_tokens=8, prefill_chunk_size=4,
+                                launch_ahead=launch_ahead)
+        runner = AheadRunner(StubRunner(40, 4))
+        engine = Engine(runner, options)
+        engine.add("a", prompts[0], 12)
+        engine.add("b", prompts[1], 9)
+        steps = 0
+        while engine.pending:
+            engine.step()
+            steps += 1
+            if steps == 8:
+                engine.add("c", prompts[2], 6)            # a late arrival: the step launched ahead is not the next step
+            if steps == 14:
+                engine.cancel("c")
+        return engine, runner
+
+    plain_engine, plain_runner = run(False)
+    engine, runner = run(True)
+    assert plain_runner.launched == 0
+    assert runner.launched > 5 and runner.used >= runner.launched - 3 and runner.dropped >= 1
+    # a launch that nothing asked for any more (its requests were cancelled) stays with the runner, which lets it go
+    assert runner.launched - 1 <= runner.used + runner.dropped <= runner.launched
+    for rid, prompt, count in (("a", prompts[0], 12), ("b", prompts[1], 9)):
+        assert engine.result(rid)["output"] == plain_engine.result(rid)["output"] == reference_output(prompt, count, 50)
+    engine.cache.check_invariants()
