@@ -3,32 +3,37 @@
 //
 // Why: a decode step of a small model is a chain of short kernels, each of which costs a few
 // microseconds whatever it computes (launch, first load, drain).  The norm, the gate/up product
-// and the down product are three links of that chain per layer; here they are one launch whose
-// two halves are separated by a barrier among its own CTAs (about 1.2 us) instead.
+// and the down product are three links of that chain per layer; here they are one launch, and
+// the activation between the two products never leaves the SMs: it is exchanged among the CTAs
+// of a thread-block cluster through distributed shared memory, behind the cluster's hardware
+// barrier, where a trip through memory (store, flag, poll, fetch) costs three times as long.
 //
-// How: one CTA per SM.  Every CTA owns a contiguous share of the 16-row tiles of the interleaved
-// gate/up matrix (rows 16b..16b+7 gate, 16b+8..16b+15 up) and one (row group, K range) piece of
-// the down matrix, and asks for its gate/up weights by TMA tile copies (boxes of 64 columns,
-// 128-byte swizzle: a dozen large copies, not a copy per row) into its shared memory before it
-// waits for the kernels before it; its piece of the down matrix takes the same room as soon as
-// the gate/up products are done and arrives while the CTAs meet at the barrier.  With under
-// 160 KB of shared memory at the 0.5B sizes the CTA fits beside a CTA of the attention kernel,
-// so the weights stream from memory while the attention half of the layer still runs.  After
-// the wait each warp normalises one token's row of the residual stream (float32 arithmetic) into
-// a bfloat16 operand in shared memory; the products run on `mma.sync.m16n8k16` with the weights as the 16-row operand and the
-// tokens as the 8 columns (for eight tokens the tensor cores' rate does not matter, latency
-// does); a warp takes a 16-row tile over the whole K, so the gate value and its up value end up
-// in one thread's registers, SwiGLU is applied there and the activation goes to memory as
-// bfloat16 [tokens, intermediate].  After the barrier each CTA multiplies its piece
-// of the down matrix with its K range of the activation and adds the result into the float32
-// residual stream with atomic adds (the order of those float32 additions is not fixed).
+// How: one CTA per SM, in clusters of 2, 4 or 8.  Every CTA owns a contiguous share of the 16-row
+// tiles of the interleaved gate/up matrix (rows 16b..16b+7 gate, 16b+8..16b+15 up) and asks for
+// them by TMA tile copies (boxes of 64 columns, 128-byte swizzle) into its shared memory before it
+// waits for the kernels before it.  With 160 KB of shared memory at the 0.5B sizes the CTA fits
+// beside a CTA of the attention kernel, so the weights stream from memory while the attention
+// half of the layer still runs.  After the wait each warp normalises one token's row of the
+// residual stream (float32 arithmetic) into a bfloat16 operand in shared memory; the products run
+// on `mma.sync.m16n8k16` with the weights as the 16-row operand and the tokens as the 8 columns
+// (for eight tokens the tensor cores' rate does not matter, latency does); a warp takes a 16-row
+// tile over the whole K, so the gate value and its up value end up in one thread's registers,
+// where SwiGLU is applied.  The warp writes its 8 activation columns into the shared memory of
+// every CTA of its cluster.  The activation columns that a cluster produces are the K range of
+// the down product that the cluster works on: each of its CTAs takes a share of the down matrix's
+// rows over that K range (TMA, requested as soon as the gate/up products are done with the room),
+// multiplies it with the exchanged activation and adds the result into the float32 residual
+// stream with atomic adds (the order of those float32 additions is not fixed).
 //
 // Sizes: tokens 1..8, hidden and intermediate sizes multiples of 16, and a layer whose per-CTA
 // share of the weights fits in shared memory (sprout_ffn_decode_supported says); larger models
 // keep the separate kernels, whose products are bound by bandwidth, not by latency.
 //
-// Every wait is bounded: an mbarrier or barrier wait that runs out sets the status word's
-// WAIT_TIMEOUT bit, the CTA skips its arithmetic but still arrives at the barrier and leaves.
+// Every wait on an mbarrier is bounded: one that runs out sets the status word's WAIT_TIMEOUT bit
+// and the CTA skips its arithmetic, but it still meets its cluster at the (hardware) barriers.
+#include <cooperative_groups.h>
+#include <stdlib.h>
+
 #include "small_batch.cuh"
 
 // With -DFFN_STAMPS the first thread of the first and of the last CTA records the time (%globaltimer)
@@ -44,79 +49,69 @@ extern "C" __attribute__((visibility("default"))) void sprout_ffn_stamps(unsigne
 
 namespace {
 
+namespace cg = cooperative_groups;
+
 constexpr int FFN_THREADS = 256;            // 8 warps
 constexpr int FFN_MAX_TOKENS = SMALL_MAX_TOKENS;
 constexpr int FFN_MAX_TILES = FFN_THREADS / 32;   // gate/up tiles of a CTA: a warp each
 constexpr int FFN_SMEM_LIMIT = 227 * 1024 - 1024;   // dynamic shared memory; the rest is for the kernel's static variables
-constexpr uint32_t FFN_SPIN_LIMIT = 1u << 21;     // polls of the barrier counter (an L2 round trip each): a second or so
 
 struct FfnPlan {
   int tokens, hidden, inter;
-  int tiles1;            // 16-row tiles of the gate/up matrix: inter / 8
-  int tiles2, ksteps2;   // 16-row tiles of the down matrix (hidden / 16), its 16-wide K steps (inter / 16)
-  int row_groups, k_splits;   // pieces of the down product: row_groups * k_splits <= CTAs
-  int base_tiles1, max_tiles1, max_tiles2, max_ksteps2;   // base_tiles1: what every CTA has at least (some have one more)
-  int boxes1, boxes2;    // 64-column boxes along K of a CTA's gate/up rows, of its piece of the down matrix
-  int box1_bytes, box2_bytes;
+  int ctas, cluster;     // CTAs of the launch, CTAs of a cluster
+  int tiles1;            // 16-row tiles of the gate/up matrix: inter / 8 (each gives 8 activation columns)
+  int base_tiles1, max_tiles1;   // what every CTA has at least (some have one more), at most
+  int boxes1, box1_bytes;        // 64-column boxes along K of a CTA's gate/up rows
+  int tiles2;            // 16-row tiles of the down matrix: hidden / 16; a cluster's CTAs share them
+  int max_tiles2;        // the most of them a CTA has
+  int box_rows2, row_boxes2;     // its rows come in boxes of box_rows2 rows (at most 256)
+  int max_ktiles, max_ksteps;    // the most activation tiles (8 columns) a cluster produces; 16-wide K steps over them
+  int col_boxes2, box2_bytes;    // 64-column boxes over a cluster's K range; bytes of a box
   int stride1;           // bytes between the tokens' rows of the normalised operand in shared memory
-  int off_w2, off_act, off_bar, smem_bytes;
+  int stride_x;          // bytes between the tokens' rows of the exchanged activation
+  int off_w2, off_act, off_xchg, off_bar, smem_bytes;
   float eps;
-  unsigned spin_limit;   // polls of the barrier among the CTAs before a CTA gives up
 };
 
 __device__ __forceinline__ float ffn_silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
-// Barrier among all CTAs of the grid (all are resident: one per SM or fewer).  False when the
-// bounded wait ran out.
-__device__ __forceinline__ bool ffn_grid_barrier(unsigned* arrived, unsigned ctas, unsigned spin_limit) {
-  __shared__ int passed;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    atomicAdd(arrived, 1u);
-    int ok = 0;
-    for (uint32_t spins = 0; spins < spin_limit; spins++) {
-      unsigned seen;
-      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(arrived) : "memory");
-      if (seen >= ctas) { ok = 1; break; }
-    }
-    passed = ok;
-  }
-  __syncthreads();
-  return passed != 0;
-}
-
-}  // namespace
-
-namespace {
+// The cluster's hardware barrier in two halves: arrive (with release: what this thread wrote, also
+// into other CTAs' shared memory, is visible to those who have waited) and wait (with acquire).
+__device__ __forceinline__ void ffn_cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void ffn_cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
 __global__ void __launch_bounds__(FFN_THREADS, 1)
 ffn_decode_kernel(const __grid_constant__ CUtensorMap map_gu_base, const __grid_constant__ CUtensorMap map_gu_tile,
                   const __grid_constant__ CUtensorMap map_down, float* __restrict__ x, const float* __restrict__ gain,
-                  __nv_bfloat16* __restrict__ act, unsigned* sync, int* status, const FfnPlan p) {
+                  int* status, const FfnPlan p) {
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzled tiles start on 1024 bytes
+  // every CTA of the cluster lays its shared memory out alike (the same offset from the same alignment)
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzled tiles start on 1024 bytes
   __shared__ int failed;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int cta = blockIdx.x, ctas = gridDim.x;
   uint8_t* w1 = smem;
   uint8_t* w2 = smem + p.off_w2;
   uint8_t* actbuf = smem + p.off_act;
+  uint8_t* xchg = smem + p.off_xchg;
   uint64_t* bars = (uint64_t*)(smem + p.off_bar);
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank(), first_cta = cta - rank;
 
   pdl_launch_dependents();
+  ffn_cluster_arrive();                              // "this CTA runs": awaited before anyone writes into its shared memory
   SPROUT_TL_ENTRY(0);
   FFN_STAMP(0);
 
-  // this CTA's share of the gate/up tiles and its piece of the down matrix
+  // this CTA's share of the gate/up tiles; its cluster's activation tiles; its rows of the down matrix
   const int t1_begin = share_begin(p.tiles1, cta, ctas);
   const int nt1 = share_begin(p.tiles1, cta + 1, ctas) - t1_begin;
-  const bool has2 = cta < p.row_groups * p.k_splits;
-  const int group = has2 ? cta / p.k_splits : 0, split = has2 ? cta % p.k_splits : 0;
-  const int t2_begin = share_begin(p.tiles2, group, p.row_groups);
-  const int nt2 = has2 ? share_begin(p.tiles2, group + 1, p.row_groups) - t2_begin : 0;
-  const int k2_begin = share_begin(p.ksteps2, split, p.k_splits);
-  const int nk2 = has2 ? share_begin(p.ksteps2, split + 1, p.k_splits) - k2_begin : 0;
+  const int kt_begin = share_begin(p.tiles1, first_cta, ctas);
+  const int nkt = share_begin(p.tiles1, first_cta + p.cluster, ctas) - kt_begin;
+  const int ksteps2 = (nkt + 1) >> 1;                // 16-wide K steps over the cluster's nkt * 8 activation columns
+  const int t2_begin = share_begin(p.tiles2, rank, p.cluster);
+  const int nt2 = share_begin(p.tiles2, rank + 1, p.cluster) - t2_begin;
+  const bool has2 = nt2 > 0 && nkt > 0;
 
   if (tid == 0) {
     failed = 0;
@@ -206,13 +201,16 @@ ffn_decode_kernel(const __grid_constant__ CUtensorMap map_gu_base, const __grid_
   __syncthreads();
   FFN_STAMP(4);
   const bool ok1 = failed == 0;
+  ffn_cluster_wait();                                // every CTA of the cluster runs: their shared memory may be written
 
   // ---- gate/up: a warp per 16-row tile of the CTA's share (a CTA has at most 8), over the whole K.
   //      The tile's fragment holds gate rows 0-7 and their up rows 8-15 in the same thread, so SwiGLU
-  //      is applied on the registers and the activation goes straight to memory: nothing is
-  //      gathered among the warps.  Eight chains of products per tile (K steps 0, 8, 16.. / 1, 9, ..)
+  //      is applied on the registers; the tile's 8 activation columns go into the shared memory of
+  //      every CTA of the cluster.  Eight chains of products per tile (K steps 0, 8, 16.. / 1, 9, ..)
   //      keep the dependent `mma.sync` apart.
-  if (ok1 && warp < nt1) {
+  if (warp < nt1) {
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    if (ok1) {
     const int ksteps1 = p.hidden >> 4;
     const uint32_t w1_addr = smem_u32(w1);
     const int a_row = warp * 16 + (lane & 15);
@@ -241,63 +239,63 @@ ffn_decode_kernel(const __grid_constant__ CUtensorMap map_gu_base, const __grid_
       ldmatrix_x4(swizzled(w1_addr + (uint32_t)(k >> 2) * p.box1_bytes, a_row, (k & 3) * 2 + (lane >> 4)), a0, a1, a2, a3);
       mma_bf16(acc[0], a0, a1, a2, a3, b0, b1);
     }
-    float s[4];
 #pragma unroll
     for (int j = 0; j < 4; j++)
       s[j] = ((acc[0][j] + acc[1][j]) + (acc[2][j] + acc[3][j])) + ((acc[4][j] + acc[5][j]) + (acc[6][j] + acc[7][j]));
+    }
     // fragment rows 0-7 are gate rows, rows 8-15 the matching up rows: (0, 2) and (1, 3) pair up
-    const int col = (t1_begin + warp) * 8 + (lane >> 2), t0 = (lane & 3) * 2;
-    if (t0 < p.tokens) act[(size_t)t0 * p.inter + col] = __float2bfloat16_rn(ffn_silu_mul(s[0], s[2]));
-    if (t0 + 1 < p.tokens) act[(size_t)(t0 + 1) * p.inter + col] = __float2bfloat16_rn(ffn_silu_mul(s[1], s[3]));
+    const int col = (t1_begin - kt_begin + warp) * 8 + (lane >> 2), t0 = (lane & 3) * 2;
+    const __nv_bfloat16 a0 = __float2bfloat16_rn(t0 < p.tokens ? ffn_silu_mul(s[0], s[2]) : 0.f);
+    const __nv_bfloat16 a1 = __float2bfloat16_rn(t0 + 1 < p.tokens ? ffn_silu_mul(s[1], s[3]) : 0.f);
+    const bool closes = (nkt & 1) && t1_begin + warp == kt_begin + nkt - 1;   // the cluster's last tile ends half a K step: the other half is zero
+    const __nv_bfloat16 zero = __float2bfloat16_rn(0.f);
+    for (int q = 0; q < p.cluster; q++) {
+      __nv_bfloat16* theirs = (__nv_bfloat16*)cluster.map_shared_rank(xchg, q);
+      __nv_bfloat16* r0 = (__nv_bfloat16*)((uint8_t*)theirs + (size_t)t0 * p.stride_x);
+      __nv_bfloat16* r1 = (__nv_bfloat16*)((uint8_t*)theirs + (size_t)(t0 + 1) * p.stride_x);
+      r0[col] = a0;
+      r1[col] = a1;
+      if (closes) { r0[col + 8] = zero; r1[col + 8] = zero; }
+    }
   }
+  ffn_cluster_arrive();                              // this CTA's columns are written, here and in the other CTAs
   __syncthreads();                                   // the operand rows and the gate/up tiles have been read
   FFN_STAMP(5);
-  // The gate/up weights have been used: this CTA's piece of the down matrix takes their place.
-  // It arrives while the CTAs meet at the barrier.
+  // The gate/up weights have been used: this CTA's rows of the down matrix, over the cluster's K
+  // range, take their place.  They arrive while the cluster meets.
   if (tid == 0 && has2) {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     const uint32_t bar = smem_u32(&bars[1]);
-    mbar_expect_tx(&bars[1], (uint32_t)p.boxes2 * (uint32_t)p.box2_bytes);
-    for (int b = 0; b < p.boxes2; b++)
-      tma_load_2d_addr(smem_u32(w2) + (uint32_t)b * p.box2_bytes, &map_down, bar, k2_begin * 16 + b * 64, t2_begin * 16);
+    mbar_expect_tx(&bars[1], (uint32_t)(p.row_boxes2 * p.col_boxes2) * (uint32_t)p.box2_bytes);
+    for (int cb = 0; cb < p.col_boxes2; cb++)
+      for (int rb = 0; rb < p.row_boxes2; rb++)
+        tma_load_2d_addr(smem_u32(w2) + (uint32_t)(cb * p.row_boxes2 + rb) * p.box2_bytes, &map_down, bar,
+                         kt_begin * 8 + cb * 64, t2_begin * 16 + rb * p.box_rows2);
   }
-
-  // ---- every CTA's share of the activation is in memory after this
-  const bool through = ffn_grid_barrier(sync, (unsigned)ctas, p.spin_limit);
+  ffn_cluster_wait();                                // the cluster's activation columns are all here
   FFN_STAMP(6);
-  if (!through && tid == 0) failed = 1;
-
-  // ---- down: this CTA's K range of the activation into shared memory, then its row tiles
-  const int stride_b = nk2 * 32 + 16;
-  if (has2) {
-    const int chunks = nk2 * 2;                      // 16-byte pieces per token
-    for (int i = tid; i < FFN_MAX_TOKENS * chunks; i += FFN_THREADS) {
-      const int t = i / chunks, c = i - t * chunks;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (t < p.tokens) v = __ldcg((const uint4*)(act + (size_t)t * p.inter + (size_t)k2_begin * 16) + c);
-      *(uint4*)(actbuf + (size_t)t * stride_b + c * 16) = v;
-    }
-  }
-  __syncthreads();
-  FFN_STAMP(7);
   if (has2 && !mbar_wait(&bars[1], 0)) failed = 1;
   __syncthreads();
-  FFN_STAMP(8);
+  FFN_STAMP(7);
+
+  // ---- down: this CTA's row tiles over the cluster's K range, added into the residual stream
   if (has2 && failed == 0) {
-    const uint8_t* b_base = actbuf + (size_t)(lane >> 2) * stride_b + (lane & 3) * 4;
+    const uint8_t* b_base = xchg + (size_t)(lane >> 2) * p.stride_x + (lane & 3) * 4;
+    const uint32_t w2_addr = smem_u32(w2);
     for (int tile = warp; tile < nt2; tile += FFN_THREADS / 32) {
       float d[4] = {0.f, 0.f, 0.f, 0.f}, e[4] = {0.f, 0.f, 0.f, 0.f};   // even and odd K steps: two chains of products
-      const uint32_t w2_addr = smem_u32(w2);
-      const int a_row = tile * 16 + (lane & 15);
-      for (int k = 0; k < nk2; k += 2) {
-        const bool two = k + 1 < nk2;
+      const int row_in_part = tile * 16 + (lane & 15);
+      const uint32_t box_row = w2_addr + (uint32_t)(row_in_part / p.box_rows2) * p.box2_bytes;
+      const int a_row = row_in_part % p.box_rows2;
+      for (int k = 0; k < ksteps2; k += 2) {
+        const bool two = k + 1 < ksteps2;
         uint32_t b[2][2], a[2][4];
 #pragma unroll
         for (int u = 0; u < 2; u++) {
           const int kk = (u == 0 || two) ? k + u : k;
           b[u][0] = *(const uint32_t*)(b_base + kk * 32);
           b[u][1] = *(const uint32_t*)(b_base + kk * 32 + 16);
-          ldmatrix_x4(swizzled(w2_addr + (uint32_t)(kk >> 2) * p.box2_bytes, a_row, (kk & 3) * 2 + (lane >> 4)),
+          ldmatrix_x4(swizzled(box_row + (uint32_t)((kk >> 2) * p.row_boxes2) * p.box2_bytes, a_row, (kk & 3) * 2 + (lane >> 4)),
                       a[u][0], a[u][1], a[u][2], a[u][3]);
         }
         mma_bf16(d, a[0][0], a[0][1], a[0][2], a[0][3], b[0][0], b[0][1]);
@@ -317,16 +315,8 @@ ffn_decode_kernel(const __grid_constant__ CUtensorMap map_gu_base, const __grid_
     }
   }
   __syncthreads();
-  FFN_STAMP(9);
-  if (tid == 0) {
-    if (failed) atomicOr(status, (int)SPROUT_STATUS_WAIT_TIMEOUT);
-    // the last CTA to leave puts the barrier's counters back to zero for the next launch
-    __threadfence();
-    if (atomicAdd(sync + 1, 1u) == (unsigned)ctas - 1) {
-      sync[0] = 0u;
-      sync[1] = 0u;
-    }
-  }
+  FFN_STAMP(8);
+  if (tid == 0 && failed) atomicOr(status, (int)SPROUT_STATUS_WAIT_TIMEOUT);
   SPROUT_TL_EXIT(0);
 }
 
@@ -334,37 +324,44 @@ ffn_decode_kernel(const __grid_constant__ CUtensorMap map_gu_base, const __grid_
 
 namespace {
 
-unsigned g_spin_limit = FFN_SPIN_LIMIT;
-
-// The layout of a launch for these sizes on `ctas` CTAs; false when the sizes are outside the
-// kernel's rules or a CTA's share of the weights does not fit in shared memory.
-bool ffn_make_plan(int tokens, int hidden, int inter, int ctas, float eps, FfnPlan* out) {
-  if (tokens < 1 || tokens > FFN_MAX_TOKENS || hidden < 16 || inter < 16 || hidden % 16 || inter % 16 || ctas < 1) return false;
+// The layout of a launch for these sizes on `ctas` CTAs in clusters of `cluster`; false when the
+// sizes are outside the kernel's rules or a CTA's share of the weights does not fit in shared memory.
+bool ffn_make_plan(int tokens, int hidden, int inter, int ctas, int cluster, float eps, FfnPlan* out) {
+  if (tokens < 1 || tokens > FFN_MAX_TOKENS || hidden < 16 || inter < 16 || hidden % 16 || inter % 16) return false;
+  if (cluster < 1 || cluster > 8 || (cluster & (cluster - 1)) || ctas < cluster || ctas % cluster) return false;
   FfnPlan p = {};
   p.tokens = tokens; p.hidden = hidden; p.inter = inter; p.eps = eps;
-  p.spin_limit = g_spin_limit;
+  p.ctas = ctas; p.cluster = cluster;
   p.tiles1 = inter / 8;
   p.tiles2 = hidden / 16;
-  p.ksteps2 = inter / 16;
   p.base_tiles1 = p.tiles1 / ctas;
   p.max_tiles1 = (p.tiles1 + ctas - 1) / ctas;
   if (p.max_tiles1 > FFN_MAX_TILES) return false;
-  if (!plan_pieces(p.tiles2, p.ksteps2, ctas, &p.row_groups, &p.k_splits)) return false;
-  p.max_tiles2 = (p.tiles2 + p.row_groups - 1) / p.row_groups;
-  p.max_ksteps2 = (p.ksteps2 + p.k_splits - 1) / p.k_splits;
   p.boxes1 = (hidden + 63) / 64;
-  p.boxes2 = (p.max_ksteps2 + 3) / 4;
   p.box1_bytes = p.max_tiles1 * 2048;
-  p.box2_bytes = p.max_tiles2 * 2048;
   p.stride1 = hidden * 2 + 16;
-  const int stride_b = p.max_ksteps2 * 32 + 16;
-  long long at = (long long)p.boxes1 * p.box1_bytes;          // the down piece comes where the gate/up tiles were
-  if ((long long)p.boxes2 * p.box2_bytes > at) at = (long long)p.boxes2 * p.box2_bytes;
+  // the down matrix: a cluster works on the K range its own CTAs produce; its CTAs share the rows
+  p.max_tiles2 = (p.tiles2 + cluster - 1) / cluster;
+  const int max_rows2 = p.max_tiles2 * 16;
+  p.row_boxes2 = (max_rows2 + 255) / 256;
+  p.box_rows2 = ((p.max_tiles2 + p.row_boxes2 - 1) / p.row_boxes2) * 16;
+  p.max_ktiles = 0;
+  for (int c = 0; c < ctas; c += cluster) {
+    const int n = share_begin(p.tiles1, c + cluster, ctas) - share_begin(p.tiles1, c, ctas);
+    if (n > p.max_ktiles) p.max_ktiles = n;
+  }
+  p.max_ksteps = (p.max_ktiles + 1) / 2;
+  p.col_boxes2 = (p.max_ksteps + 3) / 4;
+  p.box2_bytes = p.box_rows2 * 128;
+  p.stride_x = p.max_ksteps * 32 + 16;
+  long long at = (long long)p.boxes1 * p.box1_bytes;          // the down rows come where the gate/up tiles were
+  const long long down = (long long)p.row_boxes2 * p.col_boxes2 * p.box2_bytes;
+  if (down > at) at = down;
   p.off_w2 = 0;
   p.off_act = (int)at;
-  long long act_room = (long long)FFN_MAX_TOKENS * p.stride1;                       // the normalised rows,
-  if ((long long)FFN_MAX_TOKENS * stride_b > act_room) act_room = (long long)FFN_MAX_TOKENS * stride_b;   // then the activation's K range
-  at += act_room;
+  at += (long long)FFN_MAX_TOKENS * p.stride1;                // the normalised rows
+  p.off_xchg = (int)at;
+  at += (((long long)FFN_MAX_TOKENS * p.stride_x) + 15) / 16 * 16;   // the cluster's activation columns, written by all its CTAs
   p.off_bar = (int)at;
   at += 64 + 1024;                       // the barriers; room to start the tiles on a 1024-byte boundary
   if (at > FFN_SMEM_LIMIT) return false;
@@ -373,61 +370,124 @@ bool ffn_make_plan(int tokens, int hidden, int inter, int ctas, float eps, FfnPl
   return true;
 }
 
-}  // namespace
+// How many CTAs, in clusters of how many, a launch gets on the current device: as many clusters as
+// the device holds at once (all CTAs of the launch run together: a cluster that had to wait for a
+// free place would double the kernel's time), the largest cluster size for which those cover
+// nearly all SMs.  Asked once per device and size.
+bool ffn_launch_shape(int hidden, int inter, int* ctas_out, int* cluster_out) {
+  const int tokens = 1;                              // the layout does not depend on the number of tokens
+  struct Known { int device, hidden, inter, ctas, cluster; };
+  static Known known[16];
+  static int known_count = 0;
+  static std::mutex lock;
+  int device = -1;
+  const bool have_device = cudaGetDevice(&device) == cudaSuccess;
+  if (!have_device) { cudaGetLastError(); device = -1; }
+  std::lock_guard<std::mutex> guard(lock);
+  for (int i = 0; i < known_count; i++)
+    if (known[i].device == device && known[i].hidden == hidden && known[i].inter == inter) {
+      *ctas_out = known[i].ctas; *cluster_out = known[i].cluster;
+      return known[i].ctas > 0;
+    }
+  const int sms = sm_count();
+  int best_ctas = 0, best_cluster = 0;
+  const char* forced_text = getenv("SPROUT_FFN_CLUSTER");          // for measurements: this cluster size or none
+  const int forced = forced_text ? atoi(forced_text) : 0;
+  for (int cluster = 8; cluster >= 1; cluster >>= 1) {
+    if (forced && cluster != forced) continue;
+    int clusters = sms / cluster;
+    FfnPlan plan;
+    if (clusters < 1 || !ffn_make_plan(tokens, hidden, inter, clusters * cluster, cluster, 1e-6f, &plan)) continue;
+    if (have_device && cluster > 1) {
+      cudaLaunchConfig_t config = {};
+      config.gridDim = dim3(clusters * cluster);
+      config.blockDim = dim3(FFN_THREADS);
+      config.dynamicSmemBytes = plan.smem_bytes;
+      cudaLaunchAttribute attribute[1];
+      attribute[0].id = cudaLaunchAttributeClusterDimension;
+      attribute[0].val.clusterDim.x = cluster; attribute[0].val.clusterDim.y = 1; attribute[0].val.clusterDim.z = 1;
+      config.attrs = attribute; config.numAttrs = 1;
+      cudaFuncSetAttribute(ffn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FFN_SMEM_LIMIT);
+      int active = 0;
+      if (cudaOccupancyMaxActiveClusters(&active, ffn_decode_kernel, &config) != cudaSuccess) { cudaGetLastError(); continue; }
+      if (active < clusters) clusters = active;
+      if (clusters < 1 || !ffn_make_plan(tokens, hidden, inter, clusters * cluster, cluster, 1e-6f, &plan)) continue;
+    }
+    // larger clusters mean fewer additions into the residual stream and more of the activation
+    // exchanged on the SMs; they are taken as long as they leave no more than one SM in sixteen idle
+    if (clusters * cluster * 16 >= sms * 15 || cluster == 1 || forced) { best_ctas = clusters * cluster; best_cluster = cluster; break; }
+    if (clusters * cluster > best_ctas) { best_ctas = clusters * cluster; best_cluster = cluster; }
+  }
+  if (known_count < 16) known[known_count++] = Known{device, hidden, inter, best_ctas, best_cluster};
+  *ctas_out = best_ctas; *cluster_out = best_cluster;
+  return best_ctas > 0;
+}
 
-// How often a CTA of sprout_ffn_decode polls the barrier among the CTAs before it gives up, sets the
-// status word's WAIT_TIMEOUT bit and leaves (0: the default, about a second).  For tests of that path.
-SPROUT_API void sprout_set_spin_limit(unsigned polls) { g_spin_limit = polls ? polls : FFN_SPIN_LIMIT; }
+}  // namespace
 
 // 1 when sprout_ffn_decode takes these sizes on this device, else 0.
 SPROUT_API int sprout_ffn_decode_supported(int tokens, int hidden, int inter) {
+  int ctas = 0, cluster = 0;
   FfnPlan plan;
-  return ffn_make_plan(tokens, hidden, inter, sm_count(), 1e-6f, &plan) ? 1 : 0;
+  return ffn_launch_shape(hidden, inter, &ctas, &cluster) && ffn_make_plan(tokens, hidden, inter, ctas, cluster, 1e-6f, &plan) ? 1 : 0;
 }
 
-// The launch layout for these sizes on `ctas` CTAs, for inspection by host-side tests: 1 and the
-// plan's 18 numbers in `out` (in the order of the list below), or 0 when the sizes are refused.
-SPROUT_API int sprout_ffn_decode_plan(int tokens, int hidden, int inter, int ctas, int* out) {
+// The launch layout for these sizes on `ctas` CTAs in clusters of `cluster`, for inspection by
+// host-side tests: 1 and the plan's numbers in `out` (in the order of the list below), or 0 when
+// the sizes are refused.  ctas == 0: the shape the current device would get.
+SPROUT_API int sprout_ffn_decode_plan(int tokens, int hidden, int inter, int ctas, int cluster, int* out) {
   FfnPlan p;
-  if (!out || !ffn_make_plan(tokens, hidden, inter, ctas, 1e-6f, &p)) return 0;
-  const int fields[18] = {p.tiles1, p.tiles2, p.ksteps2, p.row_groups, p.k_splits, p.base_tiles1, p.max_tiles1, p.max_tiles2,
-                          p.max_ksteps2, p.boxes1, p.boxes2, p.box1_bytes, p.box2_bytes, p.stride1, p.off_w2, p.off_act,
-                          p.off_bar, p.smem_bytes};
-  for (int i = 0; i < 18; i++) out[i] = fields[i];
+  if (!out) return 0;
+  if (ctas == 0 && !ffn_launch_shape(hidden, inter, &ctas, &cluster)) return 0;
+  if (!ffn_make_plan(tokens, hidden, inter, ctas, cluster, 1e-6f, &p)) return 0;
+  const int fields[22] = {p.ctas, p.cluster, p.tiles1, p.base_tiles1, p.max_tiles1, p.boxes1, p.box1_bytes, p.tiles2, p.max_tiles2,
+                          p.box_rows2, p.row_boxes2, p.max_ktiles, p.max_ksteps, p.col_boxes2, p.box2_bytes, p.stride1, p.stride_x,
+                          p.off_w2, p.off_act, p.off_xchg, p.off_bar, p.smem_bytes};
+  for (int i = 0; i < 22; i++) out[i] = fields[i];
   return 1;
 }
 
 // x [tokens, hidden] float32 += W_down (silu(W_gate h) * W_up h) with h = rmsnorm(x, gain, eps).
 // w_gate_up: bfloat16 [2 * inter, hidden], gate and up rows interleaved in blocks of 8;
-// w_down: bfloat16 [hidden, inter]; act: bfloat16 scratch [tokens, inter]; sync: two 32-bit
-// words that are zero before the first launch (the kernel leaves them zero); status: the
-// device status word.
-SPROUT_API int sprout_ffn_decode(float* x, const float* gain, const void* w_gate_up, const void* w_down, void* act,
-                                 void* sync, int* status, int tokens, int hidden, int inter, float eps,
-                                 cudaStream_t stream) {
+// w_down: bfloat16 [hidden, inter]; status: the device status word.
+SPROUT_API int sprout_ffn_decode(float* x, const float* gain, const void* w_gate_up, const void* w_down, int* status,
+                                 int tokens, int hidden, int inter, float eps, cudaStream_t stream) {
   FfnPlan plan;
-  SPROUT_REQUIRE(x && gain && w_gate_up && w_down && act && sync && status, "ffn_decode: a pointer is missing");
+  int ctas = 0, cluster = 0;
+  SPROUT_REQUIRE(x && gain && w_gate_up && w_down && status, "ffn_decode: a pointer is missing");
   SPROUT_REQUIRE(eps > 0.f, "ffn_decode: eps must be positive");
-  SPROUT_REQUIRE(ffn_make_plan(tokens, hidden, inter, sm_count(), eps, &plan),
+  SPROUT_REQUIRE(ffn_launch_shape(hidden, inter, &ctas, &cluster) && ffn_make_plan(tokens, hidden, inter, ctas, cluster, eps, &plan),
                  "ffn_decode: tokens 1..%d, hidden and intermediate sizes multiples of 16 and a layer whose share per "
                  "CTA fits in shared memory (got tokens %d, hidden %d, intermediate %d)", FFN_MAX_TOKENS, tokens, hidden, inter);
   SPROUT_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)gain & 15) == 0 && ((uintptr_t)w_gate_up & 15) == 0 &&
-                 ((uintptr_t)w_down & 15) == 0 && ((uintptr_t)act & 15) == 0 && ((uintptr_t)sync & 3) == 0,
-                 "ffn_decode: pointers must be 16-byte aligned");
-  static int smem_set = 0;
-  if (plan.smem_bytes > smem_set) {
+                 ((uintptr_t)w_down & 15) == 0, "ffn_decode: pointers must be 16-byte aligned");
+  static bool configured = false;
+  if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(ffn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FFN_SMEM_LIMIT);
     SPROUT_REQUIRE(err == cudaSuccess, "ffn_decode: cudaFuncSetAttribute failed: %s", cudaGetErrorString(err));
     cudaFuncSetAttribute(ffn_decode_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    smem_set = FFN_SMEM_LIMIT;
+    configured = true;
   }
   CUtensorMap map_base, map_tile, map_down;
   if (tensor_map(w_gate_up, 2 * inter, hidden, hidden, 16, &map_tile)) return 1;
   map_base = map_tile;
   if (plan.base_tiles1 > 0 && tensor_map(w_gate_up, 2 * inter, hidden, hidden, plan.base_tiles1 * 16, &map_base)) return 1;
-  if (tensor_map(w_down, hidden, inter, inter, plan.max_tiles2 * 16, &map_down)) return 1;
-  cudaError_t err = sprout_launch(ffn_decode_kernel, dim3(sm_count()), dim3(FFN_THREADS), (size_t)plan.smem_bytes, stream,
-                                  map_base, map_tile, map_down, x, gain, (__nv_bfloat16*)act, (unsigned*)sync, status, plan);
+  if (tensor_map(w_down, hidden, inter, inter, plan.box_rows2, &map_down)) return 1;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(ctas);
+  config.blockDim = dim3(FFN_THREADS);
+  config.dynamicSmemBytes = (size_t)plan.smem_bytes;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  attributes[0].id = cudaLaunchAttributeClusterDimension;
+  attributes[0].val.clusterDim.x = cluster;
+  attributes[0].val.clusterDim.y = 1;
+  attributes[0].val.clusterDim.z = 1;
+  attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attributes;
+  config.numAttrs = sprout_pdl_enabled() ? 2 : 1;
+  cudaError_t err = cudaLaunchKernelEx(&config, ffn_decode_kernel, map_base, map_tile, map_down, x, gain, status, plan);
   SPROUT_REQUIRE(err == cudaSuccess, "ffn_decode: launch failed: %s", cudaGetErrorString(err));
   return 0;
 }

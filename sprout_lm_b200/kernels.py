@@ -44,8 +44,9 @@ _SIGNATURES = {
     "sprout_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, ctypes.c_longlong, _P, _P, _P],
     "sprout_attention_prefill_tc_supported": [_I, _I, _I],
     "sprout_gemm_bf16": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
-    "sprout_ffn_decode": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _P],
+    "sprout_ffn_decode": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _P],
     "sprout_ffn_decode_supported": [_I, _I, _I],
+    "sprout_wait_probe": [_P, _P],
     "sprout_linear_decode": [_P, _I, _P, _P, _F, _P, _P, _I, _I, _I, _I, _P, _P],
     "sprout_linear_decode_supported": [_I, _I, _I],
 }
@@ -74,8 +75,6 @@ def load_library(verbose: bool = True):
                 fn.restype = c_int
             lib.sprout_set_pdl.argtypes = [c_int]
             lib.sprout_set_pdl.restype = None
-            lib.sprout_set_spin_limit.argtypes = [ctypes.c_uint]
-            lib.sprout_set_spin_limit.restype = None
             lib.sprout_sm_count.argtypes = []
             lib.sprout_sm_count.restype = c_int
             if os.environ.get("SPROUT_PDL", "1") == "0":
@@ -87,12 +86,6 @@ def load_library(verbose: bool = True):
 def set_pdl(enabled: bool) -> None:
     """Programmatic dependent launch of all kernels on (the default) or off."""
     load_library().sprout_set_pdl(1 if enabled else 0)
-
-
-def set_spin_limit(polls: int) -> None:
-    """How often a CTA of ``ffn_decode`` polls the barrier among its CTAs before it gives up and
-    sets the status word's wait bit (0: the default, about a second)."""
-    load_library().sprout_set_spin_limit(int(polls))
 
 
 _sm_counts: dict = {}
@@ -341,32 +334,41 @@ def linear_decode(weight, out, status, a=None, norm=None):
          out.stride(0), T, N, K, _ptr(status, "status", torch.int32), _stream())
 
 
-FFN_PLAN_FIELDS = ("tiles1", "tiles2", "ksteps2", "row_groups", "k_splits", "base_tiles1", "max_tiles1", "max_tiles2",
-                   "max_ksteps2", "boxes1", "boxes2", "box1_bytes", "box2_bytes", "stride1", "off_w2", "off_act", "off_bar",
-                   "smem_bytes")
+FFN_PLAN_FIELDS = ("ctas", "cluster", "tiles1", "base_tiles1", "max_tiles1", "boxes1", "box1_bytes", "tiles2", "max_tiles2",
+                   "box_rows2", "row_boxes2", "max_ktiles", "max_ksteps", "col_boxes2", "box2_bytes", "stride1", "stride_x",
+                   "off_w2", "off_act", "off_xchg", "off_bar", "smem_bytes")
 LINEAR_PLAN_FIELDS = ("tiles", "ksteps", "row_groups", "k_splits", "max_tiles", "max_ksteps", "boxes", "box_bytes", "off_act",
                       "off_gain", "off_stage", "off_bar", "smem_bytes")
 
 
-def small_batch_plan(kind: str, tokens: int, rows: int, cols: int, ctas: int | None = None) -> dict | None:
+def small_batch_plan(kind: str, tokens: int, rows: int, cols: int, ctas: int | None = None, cluster: int = 1) -> dict | None:
     """How a small-batch kernel would lay a launch out on ``ctas`` CTAs (host arithmetic of the
     kernel library, no GPU needed), or None where it refuses the sizes.  ``kind`` "ffn": rows is
-    the hidden size, cols the intermediate size; "linear": a [rows, cols] matrix."""
+    the hidden size, cols the intermediate size, ``cluster`` the CTAs of a thread-block cluster
+    (``ctas`` None: the shape the current device would get); "linear": a [rows, cols] matrix."""
     lib = _lib or load_library()
+    out_type = ctypes.POINTER(c_int)
+    if kind == "ffn":
+        fn = lib.sprout_ffn_decode_plan
+        fn.argtypes = [c_int, c_int, c_int, c_int, c_int, out_type]
+        fn.restype = c_int
+        out = (c_int * len(FFN_PLAN_FIELDS))()
+        if not fn(tokens, rows, cols, 0 if ctas is None else ctas, cluster, out):
+            return None
+        return dict(zip(FFN_PLAN_FIELDS, out))
     if ctas is None:
         ctas = lib.sprout_sm_count()       # the current device's; a B200's 148 where there is none
-    names = FFN_PLAN_FIELDS if kind == "ffn" else LINEAR_PLAN_FIELDS
-    fn = lib.sprout_ffn_decode_plan if kind == "ffn" else lib.sprout_linear_decode_plan
-    fn.argtypes = [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int)]
+    fn = lib.sprout_linear_decode_plan
+    fn.argtypes = [c_int, c_int, c_int, c_int, out_type]
     fn.restype = c_int
-    out = (c_int * len(names))()
+    out = (c_int * len(LINEAR_PLAN_FIELDS))()
     if not fn(tokens, rows, cols, ctas, out):
         return None
-    return dict(zip(names, out))
+    return dict(zip(LINEAR_PLAN_FIELDS, out))
 
 
-FFN_PHASES = ("entry", "weights requested", "earlier kernels done", "norm", "weights there", "gate/up and SwiGLU",
-              "barrier passed", "activation fetched", "down piece there", "down done")
+FFN_PHASES = ("entry", "weights requested", "earlier kernels done", "norm", "weights there",
+              "gate/up, SwiGLU, activation exchanged", "cluster met", "down rows there", "down done")
 
 
 def ffn_decode_phase_stamps() -> dict | None:
@@ -405,6 +407,13 @@ def decode_timeline() -> dict | None:
             for label, v in records.items() if v[0]}
 
 
+def wait_probe(status):
+    """Launch a one-warp kernel that waits (bounded, about a second and a half) on a barrier on
+    which nothing arrives, gives up, sets the status word's wait bit and returns: for tests of the
+    bound that every TMA and tcgen05 kernel's waits share."""
+    _run("sprout_wait_probe", _ptr(status, "status", torch.int32), _stream())
+
+
 def ffn_decode_supported(tokens: int, hidden: int, intermediate: int) -> bool:
     """Whether ``ffn_decode`` takes these sizes: 1..8 tokens, sizes that are multiples of 16, and a
     layer small enough for every CTA to hold its share of the two matrices in shared memory."""
@@ -412,27 +421,24 @@ def ffn_decode_supported(tokens: int, hidden: int, intermediate: int) -> bool:
     return bool(lib.sprout_ffn_decode_supported(tokens, hidden, intermediate))
 
 
-def ffn_decode(x, gain, eps, w_gate_up, w_down, act, sync, status):
+def ffn_decode(x, gain, eps, w_gate_up, w_down, status):
     """x += W_down (silu(W_gate h) * W_up h) with h = rmsnorm(x, gain, eps), for up to 8 tokens,
-    in one kernel (norm, both products, activation and residual sum).
+    in one kernel (norm, both products, activation and residual sum; the activation is exchanged
+    among the CTAs of a thread-block cluster and never goes to memory).
 
     ``x`` float32 [tokens, hidden], changed in place; ``w_gate_up`` bfloat16 [2 * intermediate,
     hidden] with gate and up rows interleaved in blocks of 8; ``w_down`` bfloat16 [hidden,
-    intermediate]; ``act`` bfloat16 scratch [tokens, intermediate]; ``sync`` two int32 words
-    that were zero before the first call (the kernel leaves them zero)."""
-    if x.dim() != 2 or not x.is_contiguous() or not w_gate_up.is_contiguous() or not w_down.is_contiguous() \
-            or not act.is_contiguous():
-        raise KernelError("ffn_decode: x, the weights and act must be contiguous")
+    intermediate]."""
+    if x.dim() != 2 or not x.is_contiguous() or not w_gate_up.is_contiguous() or not w_down.is_contiguous():
+        raise KernelError("ffn_decode: x and the weights must be contiguous")
     T, H = x.shape
     inter = w_down.shape[1]
-    if tuple(w_gate_up.shape) != (2 * inter, H) or w_down.shape[0] != H or gain.numel() != H \
-            or act.shape[0] < T or act.shape[1] != inter or sync.numel() < 2:
+    if tuple(w_gate_up.shape) != (2 * inter, H) or w_down.shape[0] != H or gain.numel() != H:
         raise KernelError(f"ffn_decode: shapes do not fit: x {tuple(x.shape)}, gate/up {tuple(w_gate_up.shape)}, "
-                          f"down {tuple(w_down.shape)}, act {tuple(act.shape)}")
+                          f"down {tuple(w_down.shape)}")
     _run("sprout_ffn_decode", _ptr(x, "x", torch.float32), _ptr(gain, "gain", torch.float32),
          _ptr(w_gate_up, "w_gate_up", torch.bfloat16), _ptr(w_down, "w_down", torch.bfloat16),
-         _ptr(act, "act", torch.bfloat16), _ptr(sync, "sync", torch.int32), _ptr(status, "status", torch.int32),
-         T, H, inter, float(eps), _stream())
+         _ptr(status, "status", torch.int32), T, H, inter, float(eps), _stream())
 
 
 def _check_paged(q, k_cache, v_cache, block_table, out, heads, head_dim, name):

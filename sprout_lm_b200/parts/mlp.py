@@ -35,7 +35,6 @@ class SwiGLUMLP(Part):
         names = names or {"gate": "gate_proj", "up": "up_proj", "down": "down_proj"}
         self.names = {key: prefix + value for key, value in names.items()}
         self.gate_up = self.down = None
-        self._sync = None
         self._fused_tokens = 0            # up to this many tokens the one-kernel decode form runs
 
     def tensor_decls(self):
@@ -61,7 +60,6 @@ class SwiGLUMLP(Part):
         if self.gate_up.weight.dtype == torch.bfloat16 and small_batch_enabled():
             if kernels.ffn_decode_supported(FUSED_TOKENS, self.hidden_size, self.intermediate_size):
                 self._fused_tokens = FUSED_TOKENS
-                self._sync = torch.zeros(2, dtype=torch.int32, device=self.down.weight.device)
 
     def forward(self, h, x, ctx=None):
         self.down.forward(self.gate_up.forward_swiglu(h, self.block), residual=x)
@@ -73,7 +71,5 @@ class SwiGLUMLP(Part):
         tokens = x.shape[0]
         if getattr(norm, "fused_kind", None) != "rmsnorm" or tokens > self._fused_tokens:
             return False
-        act = torch.empty((tokens, self.intermediate_size), dtype=torch.bfloat16, device=x.device)
-        kernels.ffn_decode(x, norm.gain, norm.eps, self.gate_up.weight, self.down.weight, act, self._sync,
-                           self.gate_up.status)
+        kernels.ffn_decode(x, norm.gain, norm.eps, self.gate_up.weight, self.down.weight, self.gate_up.status)
         return True

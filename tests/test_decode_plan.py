@@ -175,45 +175,48 @@ def _share(n, part, parts):
 SMEM_LIMIT = 227 * 1024
 
 
-@pytest.mark.parametrize("ctas", [148, 132, 40])
-def test_feed_forward_plan_covers_the_matrices_and_fits(ctas):
+@pytest.mark.parametrize("ctas,cluster", [(148, 1), (148, 2), (148, 4), (144, 8), (132, 4), (40, 8)])
+def test_feed_forward_plan_covers_the_matrices_and_fits(ctas, cluster):
     """The launch layout of the one-kernel feed-forward for many sizes (host arithmetic of the kernel
-    library): every tile of both matrices has exactly one CTA, the TMA boxes respect their limits
-    (256 rows, starts on 1024 bytes, columns in steps of 8 elements), what shares a room fits in
-    it, and the whole fits the SM's shared memory; sizes it cannot lay out are refused."""
+    library): every gate/up tile has exactly one CTA; the activation columns a cluster produces are
+    the K range its CTAs work on, and those CTAs share the down matrix's rows; the TMA boxes respect
+    their limits (256 rows, starts on 1024 bytes, columns in steps of 8 elements); what shares a
+    room fits in it, and the whole fits the SM's shared memory; sizes it cannot lay out are refused."""
     taken = 0
     for hidden in list(range(16, 513, 48)) + [896, 1024, 1536, 2048]:
         for inter in [16, 128, 320, 1008, 2816, 4864, 8192]:
-            plan = kernels.small_batch_plan("ffn", 8, hidden, inter, ctas)
-            if plan is None:
+            p = kernels.small_batch_plan("ffn", 8, hidden, inter, ctas, cluster)
+            if p is None:
                 continue
             taken += 1
-            p = plan
-            assert p["tiles1"] * 8 == inter and p["tiles2"] * 16 == hidden and p["ksteps2"] * 16 == inter
+            assert p["ctas"] == ctas and p["cluster"] == cluster and ctas % cluster == 0
+            assert p["tiles1"] * 8 == inter and p["tiles2"] * 16 == hidden
             # gate/up: contiguous shares of base or base + 1 tiles
             shares = [_share(p["tiles1"], c + 1, ctas) - _share(p["tiles1"], c, ctas) for c in range(ctas)]
             assert sum(shares) == p["tiles1"] and set(shares) <= {p["base_tiles1"], p["base_tiles1"] + 1}
             assert max(shares) == p["max_tiles1"] <= 8 and p["base_tiles1"] * 16 <= 256
             assert p["boxes1"] * 64 >= hidden and p["box1_bytes"] == p["max_tiles1"] * 2048
-            # down: row groups x K ranges, one piece per CTA at most
-            assert 1 <= p["row_groups"] <= p["tiles2"] and 1 <= p["k_splits"] <= p["ksteps2"]
-            assert p["row_groups"] * p["k_splits"] <= ctas
-            rows = [_share(p["tiles2"], g + 1, p["row_groups"]) - _share(p["tiles2"], g, p["row_groups"]) for g in range(p["row_groups"])]
-            steps = [_share(p["ksteps2"], s + 1, p["k_splits"]) - _share(p["ksteps2"], s, p["k_splits"]) for s in range(p["k_splits"])]
-            assert sum(rows) == p["tiles2"] and sum(steps) == p["ksteps2"] and min(rows) >= 1 and min(steps) >= 1
-            assert max(rows) == p["max_tiles2"] <= 16 and max(steps) == p["max_ksteps2"]
-            assert p["boxes2"] * 4 >= p["max_ksteps2"] and p["box2_bytes"] == p["max_tiles2"] * 2048
-            # rooms: the down piece where the gate/up tiles were; operand rows and the activation's range in turn
+            # down: a cluster's K range is what its CTAs produce; its ranks share the rows
+            ranges = [sum(shares[c:c + cluster]) for c in range(0, ctas, cluster)]
+            assert sum(ranges) == p["tiles1"] and max(ranges) == p["max_ktiles"]
+            assert p["max_ksteps"] * 2 >= p["max_ktiles"] and p["col_boxes2"] * 4 >= p["max_ksteps"]
+            rows = [_share(p["tiles2"], r + 1, cluster) - _share(p["tiles2"], r, cluster) for r in range(cluster)]
+            assert sum(rows) == p["tiles2"] and max(rows) == p["max_tiles2"]
+            assert p["box_rows2"] % 16 == 0 and p["box_rows2"] <= 256 and p["box_rows2"] * p["row_boxes2"] >= p["max_tiles2"] * 16
+            assert p["box2_bytes"] == p["box_rows2"] * 128
+            # rooms: the down rows where the gate/up tiles were; the operand rows; the exchanged activation
             weights = p["off_act"] - p["off_w2"]
-            assert p["off_w2"] == 0 and weights >= p["boxes1"] * p["box1_bytes"] and weights >= p["boxes2"] * p["box2_bytes"]
-            room = p["off_bar"] - p["off_act"]
-            assert p["stride1"] == 2 * hidden + 16
-            assert room >= 8 * p["stride1"] and room >= 8 * (p["max_ksteps2"] * 32 + 16)
-            assert p["box1_bytes"] % 1024 == 0 and p["box2_bytes"] % 1024 == 0 and p["off_act"] % 16 == 0 and p["off_bar"] % 8 == 0
+            assert p["off_w2"] == 0 and weights >= p["boxes1"] * p["box1_bytes"]
+            assert weights >= p["row_boxes2"] * p["col_boxes2"] * p["box2_bytes"]
+            assert p["stride1"] == 2 * hidden + 16 and p["off_xchg"] - p["off_act"] >= 8 * p["stride1"]
+            assert p["stride_x"] == p["max_ksteps"] * 32 + 16 and p["off_bar"] - p["off_xchg"] >= 8 * p["stride_x"]
+            assert p["box1_bytes"] % 1024 == 0 and p["box2_bytes"] % 1024 == 0 and p["off_act"] % 16 == 0
+            assert p["off_xchg"] % 16 == 0 and p["off_bar"] % 8 == 0
             assert p["smem_bytes"] >= p["off_bar"] + 16 + 1023 and p["smem_bytes"] <= SMEM_LIMIT - 1024
-            assert p["boxes1"] * p["max_tiles1"] * 2048 < (1 << 20) and p["boxes2"] * p["box2_bytes"] < (1 << 20)   # an mbarrier's byte count
+            assert p["boxes1"] * p["max_tiles1"] * 2048 < (1 << 20) and p["row_boxes2"] * p["col_boxes2"] * p["box2_bytes"] < (1 << 20)   # an mbarrier's byte count
     assert taken >= 20
-    assert kernels.small_batch_plan("ffn", 8, 896, 4864, ctas) is not None or ctas < 148
+    assert kernels.small_batch_plan("ffn", 8, 896, 4864, ctas, cluster) is not None or ctas < 100
+    assert kernels.small_batch_plan("ffn", 8, 896, 4864, 148, 3) is None and kernels.small_batch_plan("ffn", 8, 896, 4864, 150, 4) is None
 
 
 @pytest.mark.parametrize("ctas", [148, 132, 40])
