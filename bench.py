@@ -622,6 +622,9 @@ def run(args) -> dict:
         phases = kernels.ffn_decode_phase_stamps()       # from a build with SPROUT_BUILD_FLAGS=-DFFN_STAMPS
         if phases:
             out["ffn_decode_phases_us"] = {k: {n: round(v, 2) for n, v in d.items()} for k, d in phases.items()}
+        phases = kernels.attention_decode_phase_stamps() # from a build with SPROUT_BUILD_FLAGS=-DATTN_STAMPS
+        if phases:
+            out["attention_decode_phases_us"] = {n: round(v, 2) for n, v in phases.items()}
         timeline = kernels.decode_timeline()             # from a build with SPROUT_BUILD_FLAGS=-DSPROUT_TIMELINE
         if timeline:
             out["last_layer_timeline_us"] = {k: {n: round(v, 2) for n, v in d.items()} for k, d in timeline.items()}

@@ -20,6 +20,16 @@
 
 namespace cg = cooperative_groups;
 
+// With -DATTN_STAMPS the first thread of the decode kernel's first CTA records the time
+// (%globaltimer) at the end of each phase; sprout_attention_stamps copies the last launch's records out.
+#ifdef ATTN_STAMPS
+__device__ unsigned long long g_attn_stamps[16];
+#define ATTN_STAMP(i) do { if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); g_attn_stamps[i] = t; } } while (0)
+extern "C" __attribute__((visibility("default"))) void sprout_attention_stamps(unsigned long long* out) { cudaMemcpyFromSymbol(out, g_attn_stamps, sizeof(g_attn_stamps)); }
+#else
+#define ATTN_STAMP(i) do { } while (0)
+#endif
+
 namespace {
 
 // =============================================================================== tensor-core helpers
@@ -304,6 +314,11 @@ attention_decode_kernel(const DecodeParams p) {
 // softmax, O += P V, all as mma.sync on keys and values staged in shared memory by cp.async.
 // The warps' partial results are merged through shared memory into the CTA's partial result
 // (maximum, sum, unnormalised output), which then goes the same ways as in the kernel above.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+template <typename T>
+__device__ __forceinline__ T* cluster_peer(T* mine, int rank) { return cg::this_cluster().map_shared_rank(mine, rank); }
+
 template <int HD, bool CLUSTER, bool FUSED>
 __global__ void __launch_bounds__(DEC_THREADS)
 attention_decode_mma_kernel(const DecodeParams p) {
@@ -312,15 +327,19 @@ attention_decode_mma_kernel(const DecodeParams p) {
   __nv_bfloat16* sQ = (__nv_bfloat16*)dmm;            // [16][STRIDE]
   __nv_bfloat16* sK = sQ + 16 * STRIDE;               // [128][STRIDE]
   __nv_bfloat16* sV = sK + DEC_THREADS * STRIDE;      // [128][STRIDE]
-  float* part_acc = (float*)(sV + DEC_THREADS * STRIDE);   // [16][HD]
-  float* part_ml = part_acc + 16 * HD;                // [16][2]
-  long long* rows = (long long*)(part_ml + 32);       // [128]
+  // What the splits of a cluster send one another: a CTA owns every count-th pair of (head, dim)
+  // places and receives that pair's partial sums from all splits, and every split's maxima and sums.
+  float2* recv = (float2*)(sV + DEC_THREADS * STRIDE);     // [pairs owned][splits], at most 8 * HD + 8 pairs
+  float* recv_ml = (float*)(recv + 8 * HD + 8);       // [8 splits][16 rows][2]
+  long long* rows = (long long*)(recv_ml + 256);      // [128]
   float* wO = (float*)sK;                             // [4][16][HD]  (the keys' space, once they are done with)
   float* wm = wO + 4 * 16 * HD;                       // [4][16]
   float* wl = wm + 64;                                // [4][16]
 
   pdl_launch_dependents();
+  if constexpr (CLUSTER) cluster_arrive();             // "this CTA runs": awaited before anyone writes into its shared memory
   SPROUT_TL_ENTRY(0);
+  ATTN_STAMP(0);
   // What this step's earlier kernels wrote is the query (or the float32 sums) and the newest
   // position's key and value.  The block table and the lengths were copied before the step's first
   // kernel, and the keys and values of earlier positions were written in earlier steps (a step
@@ -391,7 +410,7 @@ attention_decode_mma_kernel(const DecodeParams p) {
       }
     }
     cp_async_commit();
-    if (first) { pdl_wait(); SPROUT_TL_WAITED(0); }    // the first pass's keys and values are on their way
+    if (first) { ATTN_STAMP(1); pdl_wait(); SPROUT_TL_WAITED(0); ATTN_STAMP(2); }    // the first pass's keys and values are on their way
     if (!FUSED && first) {
       for (int idx = tid; idx < 16 * CHUNKS; idx += DEC_THREADS) {
         const int row = idx / CHUNKS, c = idx % CHUNKS;
@@ -496,6 +515,7 @@ attention_decode_mma_kernel(const DecodeParams p) {
       }
     }
     __syncthreads();
+    if (first) ATTN_STAMP(3);
 
     const int key0 = base + warp * 32;                 // this warp's 32 keys
     if (key0 < end) {
@@ -564,6 +584,7 @@ attention_decode_mma_kernel(const DecodeParams p) {
   // the layout the MMA left them in: a lane holds the same (row, column) places in every warp.
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  ATTN_STAMP(4);
   __syncthreads();
   float4* frag = (float4*)wO;                          // [4 warps][HD / 8 column blocks][32 lanes]
   {
@@ -590,10 +611,12 @@ attention_decode_mma_kernel(const DecodeParams p) {
     la = (wl[gr] * wa[0] + wl[16 + gr] * wa[1]) + (wl[32 + gr] * wa[2] + wl[48 + gr] * wa[3]);
     lb = (wl[gr + 8] * wb[0] + wl[24 + gr] * wb[1]) + (wl[40 + gr] * wb[2] + wl[56 + gr] * wb[3]);
     const bool row_a = gr < group, row_b = gr + 8 < group;
+    if constexpr (CLUSTER) cluster_wait();             // every CTA of the cluster runs: their shared memory may be written
     auto emit = [&](int row, int d, float x, float y, float l) {
       const int head = g * group + row;
       if constexpr (CLUSTER) {
-        *(float2*)(part_acc + row * HD + d) = make_float2(x, y);
+        const int pair = (row * HD + d) >> 1;          // to the pair's owner, into this split's place
+        *(cluster_peer(recv, pair % p.splits) + (pair / p.splits) * p.splits + split) = make_float2(x, y);
       } else if (p.splits == 1) {
         *(__nv_bfloat162*)(p.out + (size_t)r * p.out_stride + (size_t)head * HD + d) = __floats2bfloat162_rn(x / l, y / l);
         if (FUSED) *(float2*)(p.acc + (size_t)r * width + (size_t)head * HD + d) = make_float2(0.f, 0.f);   // the only reader of these q sums
@@ -611,57 +634,64 @@ attention_decode_mma_kernel(const DecodeParams p) {
       if (row_b) emit(gr + 8, d, (f0.z * wb[0] + f1.z * wb[1]) + (f2.z * wb[2] + f3.z * wb[3]),
                       (f0.w * wb[0] + f1.w * wb[1]) + (f2.w * wb[2] + f3.w * wb[3]), lb);
     }
+    if constexpr (CLUSTER) {                           // each row's maximum and sum to every split: warp w tells splits w and w + 4
+      if (qc == 0)
+        for (int to = warp; to < p.splits; to += 4) {
+          float* theirs = cluster_peer(recv_ml, to) + split * 32;
+          if (row_a) *(float2*)(theirs + 2 * gr) = make_float2(ma, la);
+          if (row_b) *(float2*)(theirs + 2 * (gr + 8)) = make_float2(mb, lb);
+        }
+    }
     if (warp == 0 && qc == 0) {                        // each row's maximum and sum, once
       if constexpr (CLUSTER) {
-        if (row_a) { part_ml[2 * gr] = ma; part_ml[2 * gr + 1] = la; }
-        if (row_b) { part_ml[2 * (gr + 8)] = mb; part_ml[2 * (gr + 8) + 1] = lb; }
       } else if (p.splits > 1) {
         if (row_a) { const size_t slot = ((size_t)r * p.heads + g * group + gr) * p.splits + split; p.part_ml[slot * 2] = ma; p.part_ml[slot * 2 + 1] = la; }
         if (row_b) { const size_t slot = ((size_t)r * p.heads + g * group + gr + 8) * p.splits + split; p.part_ml[slot * 2] = mb; p.part_ml[slot * 2 + 1] = lb; }
       }
     }
   }
+  ATTN_STAMP(5);
   if constexpr (CLUSTER) {
-    cg::cluster_group cluster = cg::this_cluster();
-    cluster.sync();
-    if (FUSED && cluster.block_rank() == 0) {          // every split has read the q sums: clear them
+    // Everything this CTA owns has arrived once every split has passed this barrier; a CTA reads
+    // only its own shared memory afterwards, so it may leave without waiting for the others.
+    cluster_arrive();
+    cluster_wait();
+    ATTN_STAMP(6);
+    if (FUSED && split == 0) {                         // every split has read the q sums: clear them
       for (int i = tid; i < group * HD; i += DEC_THREADS) p.acc[(size_t)r * width + g * group * HD + i] = 0.f;
     }
-    {
-      // every CTA of the cluster merges its share of the (head, dim) places from all the splits
-      const int count = (int)cluster.num_blocks();
-      for (int i = (int)cluster.block_rank() * DEC_THREADS + tid; i < group * HD; i += count * DEC_THREADS) {
-        const int h = i / HD;
-        float ms[8], ls[8], os[8];
+    const int count = p.splits, pairs = group * HD / 2;
+    for (int local = tid; local * count + split < pairs; local += DEC_THREADS) {
+      const int i = 2 * (local * count + split), h = i / HD;
+      float ms[8], ls[8];
+      float2 os[8];
 #pragma unroll
-        for (int sp = 0; sp < 8; sp++) {
-          if (sp < count) {
-            const float* their_ml = cluster.map_shared_rank(part_ml, sp);
-            const float* their_acc = cluster.map_shared_rank(part_acc, sp);
-            ms[sp] = their_ml[2 * h]; ls[sp] = their_ml[2 * h + 1]; os[sp] = their_acc[i];
-          } else { ms[sp] = -INFINITY; ls[sp] = 0.f; os[sp] = 0.f; }
-        }
-        float m = ms[0];
-#pragma unroll
-        for (int sp = 1; sp < 8; sp++) m = fmaxf(m, ms[sp]);
-        float l = 0.f, acc = 0.f;
-#pragma unroll
-        for (int sp = 0; sp < 8; sp++) {
-          const float w = ms[sp] == -INFINITY ? 0.f : __expf(ms[sp] - m);
-          l += ls[sp] * w;
-          acc += os[sp] * w;
-        }
-        p.out[(size_t)r * p.out_stride + (size_t)(g * group + h) * HD + (i % HD)] = __float2bfloat16_rn(acc / l);
+      for (int sp = 0; sp < 8; sp++) {
+        if (sp < count) { ms[sp] = recv_ml[sp * 32 + 2 * h]; ls[sp] = recv_ml[sp * 32 + 2 * h + 1]; os[sp] = recv[local * count + sp]; }
+        else { ms[sp] = -INFINITY; ls[sp] = 0.f; os[sp] = make_float2(0.f, 0.f); }
       }
+      float m = ms[0];
+#pragma unroll
+      for (int sp = 1; sp < 8; sp++) m = fmaxf(m, ms[sp]);
+      float l = 0.f, ax = 0.f, ay = 0.f;
+#pragma unroll
+      for (int sp = 0; sp < 8; sp++) {
+        const float w = ms[sp] == -INFINITY ? 0.f : __expf(ms[sp] - m);
+        l += ls[sp] * w;
+        ax += os[sp].x * w;
+        ay += os[sp].y * w;
+      }
+      *(__nv_bfloat162*)(p.out + (size_t)r * p.out_stride + (size_t)(g * group + h) * HD + (i % HD)) = __floats2bfloat162_rn(ax / l, ay / l);
     }
-    cluster.sync();                                    // nobody leaves while its shared memory is being read
+    ATTN_STAMP(7);
   }
+  ATTN_STAMP(8);
   SPROUT_TL_EXIT(0);
 }
 
 template <int HD, bool FUSED>
 int launch_decode_mma(const DecodeParams& p, bool cluster, int requests, cudaStream_t stream) {
-  constexpr size_t smem = (size_t)(16 + 2 * DEC_THREADS) * (HD + 8) * 2 + (size_t)(16 * HD + 32) * 4 + DEC_THREADS * 8;
+  constexpr size_t smem = (size_t)(16 + 2 * DEC_THREADS) * (HD + 8) * 2 + (size_t)(16 * HD + 16 + 256) * 4 + DEC_THREADS * 8;
   static bool configured[2] = {false, false};
   if (!configured[cluster]) {
     cudaError_t err = cudaSuccess;

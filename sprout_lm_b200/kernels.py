@@ -140,6 +140,8 @@ def _stream() -> int:
 def _run(name, *args):
     global LAUNCHES
     lib = _lib or load_library()
+    if name not in _SIGNATURES:
+        raise KernelError(f"{name}: no declared signature")         # an undeclared call would pass pointers as 32-bit integers
     LAUNCHES += 1
     code = getattr(lib, name)(*args)
     if code != 0:
@@ -385,6 +387,23 @@ def ffn_decode_phase_stamps() -> dict | None:
             for c, which in enumerate(("first CTA", "last CTA"))}
 
 
+ATTENTION_PHASES = ("entry", "first keys and values requested", "earlier kernels done", "q, new key and value ready",
+                    "products and softmax", "warps merged", "cluster met", "splits merged, output stored", "cluster left")
+
+
+def attention_decode_phase_stamps() -> dict | None:
+    """Microseconds from entry to the end of each phase of the last split-key decode attention
+    launch (its first CTA), from a library built with ``SPROUT_BUILD_FLAGS=-DATTN_STAMPS`` (None from
+    an ordinary build).  Synchronises the device."""
+    lib = _lib or load_library()
+    if not hasattr(lib, "sprout_attention_stamps"):
+        return None
+    torch.cuda.synchronize()
+    raw = (ctypes.c_ulonglong * 16)()
+    lib.sprout_attention_stamps(raw)
+    return {name: (raw[i] - raw[0]) / 1000.0 for i, name in enumerate(ATTENTION_PHASES)}
+
+
 def decode_timeline() -> dict | None:
     """When the kernels of the last decode layer ran, from a library built with
     ``SPROUT_BUILD_FLAGS=-DSPROUT_TIMELINE`` (None from an ordinary build): per kernel the entry of
@@ -478,7 +497,7 @@ def decode_split_plan(requests: int, kv_heads: int, max_keys: int, head_dim: int
 
 @functools.lru_cache(maxsize=4096)
 def _decode_split_plan(pairs: int, total_passes: int, live_passes: int, head_dim: int, sms: int) -> tuple[int, int, bool]:
-    shared = (16 + 256) * (head_dim + 8) * 2 + (16 * head_dim + 32) * 4 + 128 * 8      # the tensor-core kernel's, per CTA
+    shared = (16 + 256) * (head_dim + 8) * 2 + (16 * head_dim + 16 + 256) * 4 + 128 * 8      # the tensor-core kernel's, per CTA
     slots = sms * max(1, min(16, (227 * 1024) // (shared + 1024)))
     total_passes = max(1, total_passes)
     best, best_cost, last_splits = (128 * total_passes, 1, False), None, 0

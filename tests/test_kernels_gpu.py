@@ -597,7 +597,7 @@ def test_attention_decode_resident(status, heads, kv_heads, head_dim, page, leng
     if rotate and not fused:
         pytest.skip("the rotation belongs to the fused form")
     R = len(lengths)
-    room = kernels.decode_attention_plan(200, heads, kv_heads, head_dim, page, -(-max(lengths) // page) * page, max(lengths))
+    room = kernels.decode_attention_plan(kernels.sm_count() // kv_heads, heads, kv_heads, head_dim, page, -(-max(lengths) // page) * page, max(lengths))
     assert room[0] == "resident"
     case = build_paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, lengths, [1] * R, seed=7, poison=True)
     out = torch.full((R, heads * head_dim), float("nan"), dtype=torch.bfloat16, device=DEV)
