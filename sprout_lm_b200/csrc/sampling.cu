@@ -209,3 +209,29 @@ SPROUT_API int sprout_advance_decode(int* token_ids, int* positions, int* contex
                 step_counter, requests, max_steps);
   return sprout_check_launch("advance_decode");
 }
+
+// A decode step that is launched before the step before it has been read back takes its input
+// tokens on the device: token_ids[r] = fed[rows[r]] where rows[r] >= 0 (the row of the step before
+// that sampled this request's token; `fed` holds that step's tokens), else it keeps the token the
+// host staged.  A token that is no valid id (a step that flagged a non-finite logit) becomes 0;
+// the status word already tells.
+__global__ void feed_tokens_kernel(int* token_ids, const int* rows, const int* fed, int requests, int fed_rows, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r < requests) {
+    const int row = rows[r];
+    if (row >= 0 && row < fed_rows) {
+      const int token = fed[row];
+      token_ids[r] = token < 0 || token >= vocab ? 0 : token;
+    }
+  }
+}
+
+SPROUT_API int sprout_feed_tokens(int* token_ids, const int* rows, const int* fed, int requests, int fed_rows, int vocab,
+                                  cudaStream_t stream) {
+  SPROUT_REQUIRE(requests > 0 && fed_rows > 0 && vocab > 0, "feed_tokens: sizes must be positive");
+  SPROUT_REQUIRE(token_ids && rows && fed, "feed_tokens: null pointer");
+  sprout_launch(feed_tokens_kernel, dim3((requests + 255) / 256), dim3(256), 0, stream, token_ids, rows, fed, requests, fed_rows, vocab);
+  return sprout_check_launch("feed_tokens");
+}

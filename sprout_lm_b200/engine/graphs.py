@@ -13,6 +13,7 @@ from __future__ import annotations
 import contextlib
 import gc
 
+import numpy as np
 import torch
 
 from .. import kernels, sampling
@@ -53,9 +54,17 @@ def _round_up(value: int, multiple: int) -> int:
 class DecodeGraph:
     """One captured decode step for ``requests`` requests and block tables ``table_pages`` wide.
 
-    The step's arrays live in one device buffer with a fixed layout, mirrored by one pinned host
-    buffer that is updated in place: token ids, positions and lengths every step, block-table
-    cells only where a request's table grew (or wholly, when the requests of the step changed)."""
+    The step's arrays live in one device buffer with a fixed layout, mirrored by a host array that
+    is updated in place: token ids, positions and lengths every step, block-table cells only where
+    a request's table grew (or wholly, when the requests of the step changed).  A launch copies
+    the mirror into one of a few pinned buffers and from there to the device, replays the captured
+    kernels and copies the sampled tokens into pinned memory; an event marks its end, so that a
+    second step can be launched before the first one's tokens are read (``launch`` / ``collect``).
+    Such a step takes its input tokens on the device, from the tokens the step before sampled
+    (``feed_rows``): the captured kernels begin with that gather and sample into the runner's
+    ``fed_tokens``."""
+
+    RING = 3            # pinned buffers per graph: more launches than two are never in flight
 
     def __init__(self, runner, requests: int, table_pages: int, planned_context: int = 0):
         self.runner = runner
@@ -64,23 +73,26 @@ class DecodeGraph:
         self.groups = len(runner.manager.groups)
         device = runner.runtime.device
         sizes = [("token_ids", R), ("positions", R), ("seq_of_token", R), ("q_start", R + 1), ("context_lens", R),
-                 ("state_slots", R), ("logits_rows", R), ("temperature", R), ("uniform", R)]
+                 ("state_slots", R), ("logits_rows", R), ("temperature", R), ("uniform", R), ("feed_rows", R)]
         sizes += [(f"table{g}", R * table_pages) for g in range(self.groups)]
         self.offsets, at = {}, 0
         for name, n in sizes:
             self.offsets[name] = (at, n)
             at += (n + 3) & ~3
         self.total = at
-        self.host = torch.zeros(at, dtype=torch.int32).pin_memory()
-        self.array = self.host.numpy()
+        self.array = np.zeros(at, dtype=np.int32)
         self.floats = self.array.view("float32")
+        self.pinned = [torch.zeros(at, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.pinned_tokens = [torch.zeros(R, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.events = [None] * self.RING          # the end of the launch that used the slot last, until it is collected
+        self.slot = 0
         self.device_buf = torch.zeros(at, dtype=torch.int32, device=device)
-        self.copied = None
         self.last_bytes = at * 4
         put = self._put
         put("seq_of_token", range(R))
         put("q_start", range(R + 1))
         put("logits_rows", range(R))
+        put("feed_rows", [-1] * R)
         for g in range(self.groups):
             put(f"table{g}", [-1] * (R * table_pages))
         view = self._view
@@ -113,17 +125,18 @@ class DecodeGraph:
     def stager(self):                     # the bytes of the last copy, for the runner's statistics
         return self
 
-    def stage(self, entries, temperatures, uniforms, copy: bool = True) -> StepContext:
-        """Fill the pinned mirror; with ``copy`` also send it to the device (``run`` leaves that
-        to the captured graph, whose first node is the same copy)."""
-        if self.copied is not None:
-            self.copied.synchronize()     # the previous copy has read the host buffer
-            self.copied = None
+    def stage(self, entries, temperatures, uniforms, copy: bool = True, shift: int = 0, feed_rows=None) -> StepContext:
+        """Fill the host mirror; with ``copy`` also send it to the device.  ``shift``: the requests
+        will be this many tokens longer when the step runs than they are now (a step launched
+        behind one that is still in flight); ``feed_rows``: per request the row of the step before
+        whose sampled token is this step's input, taken on the device (the staged token ids are
+        placeholders then)."""
         R, P = self.requests, self.table_pages
-        lengths = [e.seq.length for e in entries]
+        lengths = [e.seq.length + shift for e in entries]
         self._put("token_ids", [e.tokens[0] for e in entries])
         self._put("positions", lengths)
         self._put("context_lens", [n + 1 for n in lengths])
+        self._put("feed_rows", feed_rows if feed_rows is not None else [-1] * R)
         at, n = self.offsets["temperature"]
         self.floats[at:at + n] = temperatures
         at, n = self.offsets["uniform"]
@@ -151,22 +164,35 @@ class DecodeGraph:
                 elif self.runner.manager.groups[g].kind == "window":
                     self.array[base + i * P:base + i * P + count] = pages
         if copy:
-            self.device_buf.copy_(self.host, non_blocking=True)
-            event = torch.cuda.Event()
-            event.record()
-            self.copied = event
+            self._send()
         return self.ctx
+
+    def _send(self) -> int:
+        """The mirror -> the next pinned buffer -> the device; the slot used."""
+        slot = self.slot
+        self.slot = (slot + 1) % self.RING
+        if self.events[slot] is not None:
+            self.events[slot].synchronize()       # an uncollected launch still owns the buffer
+            self.events[slot] = None
+        self.pinned[slot].numpy()[:] = self.array
+        self.device_buf.copy_(self.pinned[slot], non_blocking=True)
+        return slot
 
     def _forward(self, ctx):
         logits = self.runner.model.forward(ctx, self.runner.storage)
-        tokens = sampling.sample(logits, self.runner.runtime.status, ctx.floats["temperature"], ctx.floats["uniform"])
+        tokens = sampling.sample(logits, self.runner.runtime.status, ctx.floats["temperature"], ctx.floats["uniform"],
+                                 out=self.runner.fed_tokens[:self.requests])
         return logits, tokens
 
+    def _finish(self, slot: int) -> int:
+        self.pinned_tokens[slot].copy_(self.tokens, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self.events[slot] = event
+        return slot
+
     def run(self, entries, temperatures, uniforms) -> list:
-        """Stage the batch and run the step; the sampled token ids, on the host.  The captured
-        graph holds the whole round trip: the copy of the pinned mirror to the device, the step's
-        kernels, and the copy of the sampled tokens into pinned host memory; the host launches it
-        and waits for the stream."""
+        """Stage the batch and run the step; the sampled token ids, on the host."""
         if self.graph is None:
             # First use: this call's step runs eagerly (that also does the kernels' first-use
             # set-up), then the same launches are captured for later calls.  Capturing records
@@ -175,29 +201,29 @@ class DecodeGraph:
             ctx = self.stage(entries, temperatures, uniforms)
             self.last_logits, tokens = self._forward(ctx)
             result = tokens.tolist()
-            self.host_tokens = torch.zeros(self.requests, dtype=torch.int32).pin_memory()
             before = kernels.LAUNCHES
             graph = torch.cuda.CUDAGraph()
             with guarded_capture(graph):
-                self.device_buf.copy_(self.host, non_blocking=True)
+                kernels.feed_tokens(ctx.token_ids, self._view("feed_rows"), self.runner.fed_tokens, self.runner.vocab_size)
                 self.logits, self.tokens = self._forward(ctx)
-                self.host_tokens.copy_(self.tokens, non_blocking=True)
             self.launches = kernels.LAUNCHES - before
             self.graph = graph
             return result
-        self.launch(entries, temperatures, uniforms)
-        return self.collect()
+        return self.collect(self.launch(entries, temperatures, uniforms))
 
-    def launch(self, entries, temperatures, uniforms) -> None:
-        """Stage the batch and start the captured step; ``collect`` waits for it.  The host is free
-        in between (the scheduler does its bookkeeping of the step before while this one runs)."""
-        self.stage(entries, temperatures, uniforms, copy=False)
+    def launch(self, entries, temperatures, uniforms, shift: int = 0, feed_rows=None) -> int:
+        """Stage the batch and start the captured step; ``collect`` with the returned ticket waits
+        for it.  The host is free in between, and may launch the step after it."""
+        self.stage(entries, temperatures, uniforms, copy=False, shift=shift, feed_rows=feed_rows)
+        slot = self._send()
         self.graph.replay()
+        return self._finish(slot)
 
-    def collect(self) -> list:
-        torch.cuda.current_stream().synchronize()      # the tokens are in pinned memory, the mirror has been read
+    def collect(self, slot: int) -> list:
+        self.events[slot].synchronize()                # the tokens are in pinned memory
+        self.events[slot] = None
         self.last_logits = self.logits
-        return self.host_tokens.tolist()
+        return self.pinned_tokens[slot].tolist()
 
 
 class GraphCache:
@@ -218,7 +244,7 @@ class GraphCache:
         self.evictions = 0
         self.keys_used = 0                 # keys asked for that were not held (captures made or to be made)
 
-    def key_for(self, entries):
+    def key_for(self, entries, shift: int = 0):
         pages = 1
         for e in entries:
             for table in e.seq.tables:
@@ -228,13 +254,13 @@ class GraphCache:
         # launches out alike: the parts say what theirs depend on (decode attention: how it
         # divides the keys, which follows the contexts' length in steps of 128).
         width = _round_up(pages, self.page_multiple)
-        longest = 1 + max(e.seq.length for e in entries)
+        longest = 1 + shift + max(e.seq.length for e in entries)
         planned = min(width * self.runner.page_tokens, _round_up(longest, 128))
         plan = self.runner.model.decode_plan(len(entries), width * self.runner.page_tokens, planned, self.runner.page_tokens)
         return (len(entries), width, plan), width, planned
 
-    def get(self, entries) -> DecodeGraph:
-        key, width, planned = self.key_for(entries)
+    def get(self, entries, shift: int = 0) -> DecodeGraph:
+        key, width, planned = self.key_for(entries, shift)
         graph = self.graphs.pop(key, None)
         if graph is None:
             self.keys_used += 1

@@ -40,8 +40,8 @@ class EngineOptions:
     # and is preempted again, tick after tick.  With this option a request waits in the queue
     # until the pool can hold its history beside what the running requests still have to take.
     admit_within_pool: bool = False
-    # Not in the reference either: start the next decode step before this step's report is read,
-    # when it is already known what that step will be (see Engine._launch_ahead).
+    # Not in the reference either: start the next decode step before this step's tokens are read,
+    # when it is already known what that step will be (see Engine._next_step).
     launch_ahead: bool = True
 
     def validate(self):
@@ -244,7 +244,12 @@ class Engine:
             rows = [(r, len(r.output)) for r, _, _, _, wants in planned if wants]
             temperatures = [r.temperature for r, _ in rows]
             uniforms = [uniform_for(r.seed, r.id, index) if r.temperature > 0 else 0.0 for r, index in rows]
-            sampled = [int(t) for t in self.runner.step_and_sample(entries, temperatures, uniforms)]
+            then = self._next_step(planned)
+            if then is not None:
+                sampled = self.runner.step_and_sample(entries, temperatures, uniforms, then=then)
+            else:
+                sampled = self.runner.step_and_sample(entries, temperatures, uniforms)
+            sampled = [int(t) for t in sampled]
             if len(sampled) != len(rows) or any(t < 0 or t >= self.runner.vocab_size for t in sampled):
                 raise RuntimeError("Runner returned invalid sampled token.")
             row = 0
@@ -258,26 +263,27 @@ class Engine:
                     row += 1
                 work.append({"id": request.id, "phase": phase, "from": start, "tokens": len(tokens),
                              "blockTable": table})
-        self._launch_ahead()
         return StepReport(tick=self._tick, work=work, events=events, cache=self.cache)
 
-    def _launch_ahead(self) -> None:
-        """When the next step is known already (every running request decodes on, nobody waits to
-        be admitted), hand it to the runner now: a runner that can starts it at once, and the device
-        works on it while this step's report is put together and read.  The next call plans as
-        always; if it arrives at the same batch it takes the result, if not (a request was added or
-        cancelled in between) the launch is dropped and nothing is lost but its work."""
-        ahead = getattr(self.runner, "launch_ahead", None)
-        if ahead is None or not self.options.launch_ahead or self._waiting or not self._active \
-                or len(self._active) > self.options.max_batch_tokens:
-            return
-        batch = sorted(self._active.values(), key=lambda r: r.order)
-        if any(self._phase(r) != "decode" for r in batch):
-            return
-        entries = [StepEntry(r.seq, [r.output[-1]], [0]) for r in batch]
-        temperatures = [r.temperature for r in batch]
-        uniforms = [uniform_for(r.seed, r.id, len(r.output)) if r.temperature > 0 else 0.0 for r in batch]
-        ahead(entries, temperatures, uniforms)
+    def _next_step(self, planned: list):
+        """The decode step after the planned one, when it is known already: every running request
+        decodes one token in this step, nobody waits to be admitted, and the requests that do not
+        reach their length with this step's token go on (unless that token ends them).  A runner
+        that can (``takes_next_step``) launches it behind this step, with each request's token
+        taken on the device from the row of this step that samples it, so that the device does not
+        wait while the host reads this step's tokens and accounts for them.  The next call plans as
+        always; if it arrives at the same batch it takes the result, if not (a request ended, was
+        added or cancelled) the launch is dropped and nothing is lost but its work."""
+        if not self.options.launch_ahead or not getattr(self.runner, "takes_next_step", False) or self._waiting \
+                or len(planned) != len(self._active) or any(phase != "decode" or not wants for _, phase, _, _, wants in planned):
+            return None
+        rows = [(i, r) for i, (r, _, _, _, _) in enumerate(planned) if len(r.output) + 1 < r.max_new_tokens]
+        if not rows:
+            return None
+        entries = [StepEntry(r.seq, [0], [0]) for _, r in rows]
+        temperatures = [r.temperature for _, r in rows]
+        uniforms = [uniform_for(r.seed, r.id, len(r.output) + 1) if r.temperature > 0 else 0.0 for _, r in rows]
+        return entries, temperatures, uniforms, [i for i, _ in rows]
 
     def _accept(self, request: Request, token: int) -> None:
         request.output.append(token)

@@ -43,7 +43,11 @@ class ModelRunner:
         self.eos_token_ids = tuple(model.spec.eos_token_ids)
         self.steps_run = 0
         self.last_decode_graph = None      # the captured decode step that ran last
-        self._ahead = None                 # (signature, graph) of a decode step launched before it was asked for
+        self._ahead = None                 # (signature, graph, ticket, feed rows) of a decode step launched before it was asked for
+        self._last_sampled: list = []      # the tokens of the decode step collected last (what a step launched behind it was fed)
+        self.takes_next_step = True        # step_and_sample(..., then=...) launches the step after before it reads this one
+        # what decode steps sample into and what a step launched behind another reads its tokens from
+        self.fed_tokens = torch.zeros(max(1024, max_requests), dtype=torch.int32, device=self.runtime.device)
         self.ahead_used = 0                # such steps that the scheduler then asked for as launched
         self.ahead_dropped = 0             # and those it did not (their work is done again by the step that came instead)
         # bytes copied to and from the device by steps (the batch's arrays up, token ids or logits down)
@@ -110,44 +114,47 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ a decode step launched ahead
     @staticmethod
-    def _signature(entries, temperatures, uniforms):
-        return (tuple((id(e.seq), e.seq.length, e.tokens[0]) for e in entries), tuple(temperatures), tuple(uniforms))
+    def _signature(entries, temperatures, uniforms, shift: int = 0):
+        return (tuple((id(e.seq), e.seq.length + shift) for e in entries), tuple(temperatures), tuple(uniforms))
 
-    def launch_ahead(self, entries: list[StepEntry], temperatures, uniforms) -> bool:
-        """Start a decode step (one token per request, already captured) without waiting for it:
-        the scheduler calls this at the end of a step when it knows what the next step will be, so
-        that the device runs it while the host still accounts for the step before.  The next
-        ``step_and_sample`` with the same batch takes its result; any other call waits for it and
-        lets it go (it wrote only cache slots that the step which comes instead writes again, which
-        is why models with per-request state never launch ahead).  False: nothing was launched."""
-        if self._ahead is not None or not self.graphs.enabled or self.manager.state_slot_count:
+    def _launch_next(self, then) -> bool:
+        """Start the decode step that follows the one just launched, before that one has been read
+        back: ``then`` = (entries, temperatures, uniforms, feed_rows), the entries with placeholder
+        tokens; request i's real token is row ``feed_rows[i]`` of the tokens the step in flight
+        samples, and the launch takes it from there on the device.  The scheduler gives ``then``
+        when it knows what the next step will be unless a request ends with this step's token; the
+        next ``step_and_sample`` takes the result if it asks for just that batch, any other call
+        waits for the launch and lets it go.  (What it wrote to the cache, the step that comes
+        instead writes again; models with per-request state never launch ahead.)"""
+        entries, temperatures, uniforms, feed_rows = then
+        if self._ahead is not None or not self.graphs.enabled or self.manager.state_slot_count or not entries:
             return False
-        if not entries or any(len(e.tokens) != 1 or e.want != [0] for e in entries):
+        if len(entries) > self.fed_tokens.numel() or any(len(e.tokens) != 1 or e.want != [0] for e in entries):
             return False
         for e in entries:
-            if e.seq.released or not self.reserve(e.seq, e.seq.length + 1):
+            if e.seq.released or e.seq.length + 2 > self.max_positions or not self.reserve(e.seq, e.seq.length + 2):
                 return False                       # the planner decides what happens when pages run out
-        self.validate(entries)
-        graph = self.graphs.get(entries)
+        graph = self.graphs.get(entries, shift=1)
         if graph.graph is None:
             return False                           # a first use runs eagerly and captures: through the ordinary path
-        graph.launch(entries, temperatures, uniforms)
-        self._ahead = (self._signature(entries, temperatures, uniforms), graph)
+        ticket = graph.launch(entries, temperatures, uniforms, shift=1, feed_rows=list(feed_rows))
+        self._ahead = (self._signature(entries, temperatures, uniforms, shift=1), graph, ticket, list(feed_rows))
         return True
 
     def _take_ahead(self, entries, temperatures, uniforms):
-        """The result of the step launched ahead if it is the step now asked for, else None (after
-        waiting for it)."""
+        """(graph, ticket) of the step launched ahead if it is the step now asked for, else None
+        (after waiting for it)."""
         if self._ahead is None:
             return None
-        signature, graph = self._ahead
+        signature, graph, ticket, feed_rows = self._ahead
         self._ahead = None
-        sampled = graph.collect()
         if entries is not None and all(len(e.tokens) == 1 and e.want == [0] for e in entries) \
-                and signature == self._signature(entries, temperatures, uniforms):
+                and signature == self._signature(entries, temperatures, uniforms) \
+                and all(row < len(self._last_sampled) and e.tokens[0] == self._last_sampled[row]
+                        for e, row in zip(entries, feed_rows)):
             self.ahead_used += 1
-            self.last_decode_graph = graph
-            return sampled
+            return graph, ticket
+        graph.collect(ticket)
         self.ahead_dropped += 1
         return None
 
@@ -171,18 +178,30 @@ class ModelRunner:
         self.steps_run += 1
         return logits
 
-    def step_and_sample(self, entries: list[StepEntry], temperatures, uniforms) -> list[int]:
+    def step_and_sample(self, entries: list[StepEntry], temperatures, uniforms, then=None) -> list[int]:
         """Run one batch and sample at every wanted place; the new token ids, in the order of the
         entries.  Only token ids come back from the device.  A batch of single decode tokens
-        runs as a replayed CUDA graph."""
+        runs as a replayed CUDA graph; with ``then`` (see ``_launch_next``) the decode step after
+        it is launched before this one's tokens are waited for."""
         self.validate(entries)
         decode_only = self.graphs.enabled and all(len(e.tokens) == 1 and e.want == [0] for e in entries)
-        sampled = self._take_ahead(entries, temperatures, uniforms)
+        taken = self._take_ahead(entries, temperatures, uniforms)
         if decode_only:
-            if sampled is None:
-                graph = self.last_decode_graph = self.graphs.get(entries)
-                sampled = graph.run(entries, temperatures, uniforms)
-            graph = self.last_decode_graph
+            if taken is None:
+                graph = self.graphs.get(entries)
+                if graph.graph is None:
+                    sampled = graph.run(entries, temperatures, uniforms)      # first use: runs eagerly, then captures
+                    ticket = None
+                else:
+                    ticket = graph.launch(entries, temperatures, uniforms)
+            else:
+                graph, ticket = taken
+            if ticket is not None:
+                if then is not None:
+                    self._launch_next(then)
+                sampled = graph.collect(ticket)
+            self.last_decode_graph = graph
+            self._last_sampled = sampled
             self.stats["h2d_bytes"] += graph.stager.last_bytes
             self.stats["d2h_bytes"] += len(sampled) * 4
             for e in entries:

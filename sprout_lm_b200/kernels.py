@@ -37,6 +37,7 @@ _SIGNATURES = {
     "sprout_attention_simple": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_sample": [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P],
     "sprout_advance_decode": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
+    "sprout_feed_tokens": [_P, _P, _P, _I, _I, _I, _P],
     "sprout_attention_decode": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_attention_decode_fused": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_attention_decode_resident": [_P, _P, _P, _P, _I, _I, _I, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
@@ -764,10 +765,19 @@ def advance_decode(token_ids, positions, context_lens, sampled, history, step_co
          history.shape[0], _stream())
 
 
+def feed_tokens(token_ids, rows, fed, vocab: int):
+    """token_ids[r] = fed[rows[r]] where rows[r] >= 0: a step launched before its predecessor has
+    been read back takes the predecessor's sampled tokens on the device."""
+    if rows.numel() != token_ids.numel():
+        raise KernelError("feed_tokens: one row index per token")
+    _run("sprout_feed_tokens", _ptr(token_ids, "token_ids", torch.int32), _ptr(rows, "rows", torch.int32),
+         _ptr(fed, "fed", torch.int32), token_ids.numel(), fed.numel(), vocab, _stream())
+
+
 def describe_status(word: int) -> str:
     return "; ".join(text for bit, text in STATUS_BITS.items() if word & bit) or "ok"
 
 
 __all__ = ["KernelError", "BuildError", "load_library", "library_file", "embed", "rmsnorm", "swiglu",
            "rope_append", "gemm_simple", "gemm_bf16", "attention_simple", "attention_decode", "attention_decode_fused", "attention_decode_resident", "decode_attention_plan", "decode_fusable", "attention_prefill",
-           "paged_attention", "sample", "advance_decode", "describe_status"]
+           "paged_attention", "sample", "advance_decode", "feed_tokens", "describe_status"]

@@ -268,9 +268,12 @@ def test_admission_within_the_pool_stops_the_preemption_loop(prefix_caching):
 
 
 class AheadRunner:
-    """A stub runner that can start a decode step ahead of being asked for it: it computes the
-    step's tokens at once from a copy of the request's state and hands them out when the same
-    batch is asked for, as the device-side runner does with a launched graph."""
+    """A stub runner that takes the decode step after the one it is asked for (``then``), as the
+    device-side runner does with a graph launched behind the step in flight: it notes which batch
+    that step is (the requests one token longer, each fed the token its row of this step sampled)
+    and counts whether the next call asks for just that batch."""
+
+    takes_next_step = True
 
     def __init__(self, inner):
         self.inner = inner
@@ -281,33 +284,33 @@ class AheadRunner:
         return getattr(self.inner, name)
 
     @staticmethod
-    def signature(entries, temperatures, uniforms):
-        return (tuple((id(e.seq), e.seq.length, tuple(e.tokens), tuple(e.want)) for e in entries), tuple(temperatures), tuple(uniforms))
+    def signature(entries, tokens, temperatures, uniforms):
+        return (tuple((id(e.seq), e.seq.length, t) for e, t in zip(entries, tokens)), tuple(temperatures), tuple(uniforms))
 
-    def launch_ahead(self, entries, temperatures, uniforms):
-        assert self.pending is None, "two steps launched ahead at once"
-        assert all(len(e.tokens) == 1 and e.want == [0] for e in entries), "only single decode tokens are launched ahead"
-        for e in entries:
-            if not self.inner.reserve(e.seq, e.seq.length + 1):
-                return False
-        self.pending = (self.signature(entries, temperatures, uniforms), entries, temperatures, uniforms)
-        self.launched += 1
-        return True
-
-    def step_and_sample(self, entries, temperatures, uniforms):
+    def step_and_sample(self, entries, temperatures, uniforms, then=None):
         pending, self.pending = self.pending, None
         if pending is not None:
-            if pending[0] == self.signature(entries, temperatures, uniforms):
+            if all(len(e.tokens) == 1 for e in entries) and \
+                    pending == self.signature(entries, [e.tokens[0] for e in entries], temperatures, uniforms):
                 self.used += 1
             else:
                 self.dropped += 1
-        return self.inner.step_and_sample(entries, temperatures, uniforms)
+        sampled = self.inner.step_and_sample(entries, temperatures, uniforms)
+        if then is not None:
+            assert all(len(e.tokens) == 1 and e.want == [0] for e in entries), "only a decode step has a known successor"
+            next_entries, next_temperatures, next_uniforms, rows = then
+            assert all(len(e.tokens) == 1 and e.want == [0] for e in next_entries)
+            assert [e.seq for e in next_entries] == [entries[row].seq for row in rows], "a request is fed its own row"
+            if all(self.inner.reserve(e.seq, e.seq.length + 1) for e in next_entries):
+                self.pending = self.signature(next_entries, [sampled[row] for row in rows], next_temperatures, next_uniforms)
+                self.launched += 1
+        return sampled
 
 
 def test_the_next_decode_step_is_launched_ahead_only_when_it_is_known():
-    """With every running request decoding on and nobody waiting, the scheduler hands the next
-    step to the runner at the end of the step before; a late arrival or a cancellation makes the
-    next plan differ and the launch is dropped.  Tokens are the same either way."""
+    """With every running request decoding on and nobody waiting, the scheduler hands the step
+    after to the runner together with the step; a late arrival, a cancellation or a request that
+    ends makes the next plan differ and the launch is dropped.  Tokens are the same either way."""
     import numpy as np
     rng = np.random.default_rng(3)
     prompts = [[int(t) for t in rng.integers(0, 50, n)] for n in (5, 11, 7)]
