@@ -404,7 +404,10 @@ def timed_serving(shape: str, layers: int, requests: int, workload: str = "mixed
             "seconds": round(seconds, 4), "generated_tokens_per_s": round(requests * new_tokens / seconds, 1),
             "all_tokens_per_s": round((sum(lengths) + requests * new_tokens) / seconds, 1),
             "steps": len(times), "step_kinds": kinds, "step_ms": {"p50": pick(0.5), "p95": pick(0.95), "max": times[-1].__round__(3)},
-            "preempted": preempted, "prefill_steps_replayed": replays}
+            "preempted": preempted, "prefill_steps_replayed": replays,
+            "decode_graphs": {"keys": engine.runner.graphs.keys_used, "held": len(engine.runner.graphs.graphs),
+                              "dropped": engine.runner.graphs.evictions},
+            "steps_launched_ahead": {"taken": engine.runner.ahead_used, "let_go": engine.runner.ahead_dropped}}
 
 
 def timed_attention(tokens: int, shape: str = "0.5b", repeats: int = 20) -> dict:

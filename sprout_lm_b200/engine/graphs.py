@@ -88,6 +88,8 @@ class DecodeGraph:
         self.slot = 0
         self.device_buf = torch.zeros(at, dtype=torch.int32, device=device)
         self.last_bytes = at * 4
+        # what a capture keeps on the device, roughly: the logits, and the activations of a layer or two
+        self.nbytes = R * runner.vocab_size * 4 + at * 4 + R * (1 << 18) + (1 << 20)
         put = self._put
         put("seq_of_token", range(R))
         put("q_start", range(R + 1))
@@ -229,20 +231,32 @@ class DecodeGraph:
 class GraphCache:
     """Captured decode steps, by (number of requests, table width, the parts' launch plans).
 
-    A serving loop meets many keys: every batch size, a wider table every ``page_multiple`` pages,
-    another attention plan every few 128 keys of context.  Each capture owns device memory (its
-    activations and its [requests, vocabulary] float32 logits), a pinned mirror and a CUDA graph,
-    so at most ``limit`` are kept; the least recently used one is dropped when another is needed
-    (outside any capture: ``get`` runs before the step is staged)."""
+    A serving loop meets many keys: every batch size on the way up and down, a wider table every
+    ``page_multiple`` pages, another attention plan every few 128 keys of context; a round of 64
+    requests uses some fifty.  Each capture owns device memory (its activations and its [requests,
+    vocabulary] float32 logits), pinned mirrors and a CUDA graph, so the cache is bounded: at most
+    ``limit`` captures and ``budget_bytes`` of what they hold (``DecodeGraph.nbytes``, an estimate led
+    by the logits; by default 1/24 of the device's memory).  Beyond either the least recently used
+    capture is dropped (outside any capture: ``get`` runs before the step is staged).  The bounds
+    are generous on purpose: a capture costs some ten milliseconds, a dropped one that is needed
+    again costs them again."""
 
-    def __init__(self, runner, page_multiple: int = 64, limit: int = 24):
+    def __init__(self, runner, page_multiple: int = 64, limit: int = 256, budget_bytes: int | None = None):
         self.runner = runner
         self.page_multiple = page_multiple
         self.limit = max(1, limit)
+        if budget_bytes is None:
+            device = getattr(getattr(runner, "runtime", None), "device", None)
+            total = torch.cuda.get_device_properties(device).total_memory if device is not None and torch.cuda.is_available() else 0
+            budget_bytes = total // 24 if total else 1 << 62
+        self.budget_bytes = budget_bytes
         self.graphs: dict = {}             # insertion order is the order of last use
         self.enabled = True
         self.evictions = 0
         self.keys_used = 0                 # keys asked for that were not held (captures made or to be made)
+
+    def held_bytes(self) -> int:
+        return sum(getattr(g, "nbytes", 0) for g in self.graphs.values())
 
     def key_for(self, entries, shift: int = 0):
         pages = 1
@@ -264,11 +278,12 @@ class GraphCache:
         graph = self.graphs.pop(key, None)
         if graph is None:
             self.keys_used += 1
-            while len(self.graphs) >= self.limit:
-                oldest = next(iter(self.graphs))
-                del self.graphs[oldest]    # its CUDA graph, buffers and pinned mirror go with it
-                self.evictions += 1
             graph = self.make(len(entries), width, planned)
+            room = self.budget_bytes - getattr(graph, "nbytes", 0)
+            while self.graphs and (len(self.graphs) >= self.limit or self.held_bytes() > room):
+                oldest = next(iter(self.graphs))
+                del self.graphs[oldest]    # its CUDA graph, buffers and pinned mirrors go with it
+                self.evictions += 1
         self.graphs[key] = graph           # most recently used: last
         return graph
 

@@ -105,6 +105,16 @@ def test_captured_decode_steps_are_bounded(monkeypatch):
             cache.get([entry(length)] * batch)
             assert len(cache.graphs) <= 5 and len(alive) <= 5
     assert cache.keys_used == 64 * 4 and cache.evictions == 64 * 4 - 5
+    # a budget of bytes bounds it as well: captures of 10 units each, room for 35
+    class SizedGraph(FakeGraph):
+        nbytes = 10
+    monkeypatch.setattr(graphs, "DecodeGraph", SizedGraph)
+    sized = graphs.GraphCache(runner, page_multiple=64, limit=100, budget_bytes=35)
+    for batch in range(1, 10):
+        sized.get([entry(50)] * batch)
+        assert sized.held_bytes() <= 35 and len(sized.graphs) <= 3
+    assert sized.evictions == 6
+    del sized
     # use keeps a capture: the one touched again outlives newer ones
     kept = cache.get([entry(50)] * 64)
     for length in (300, 700, 1500, 2100):

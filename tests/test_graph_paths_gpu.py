@@ -209,8 +209,8 @@ def test_captured_mixed_step_with_sampling(model_dirs, dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_decode_steps_launched_ahead_give_the_same_tokens(model_dirs, dtype):
-    """The scheduler starts the next decode step before it has finished accounting for the step
-    before (``EngineOptions.launch_ahead``).  Same tokens as without, most steps taken from the
+    """The scheduler has the next decode step launched behind the one in flight, its tokens fed on
+    the device (``EngineOptions.launch_ahead``).  Same tokens as without, most steps taken from the
     launch, and a request added in the middle (which makes the launched step the wrong one) still
     gets, and leaves to the others, the plain implementation's tokens."""
     from sprout_lm_b200 import EngineOptions, load_model, make_engine
@@ -243,6 +243,43 @@ def test_decode_steps_launched_ahead_give_the_same_tokens(model_dirs, dtype):
         assert outputs[True] == outputs[False]
     for prompt, output in zip(prompts, outputs[True]):
         check_tokens(model_dirs[name], prompt, output, dtype, f"launch ahead/{dtype}")
+
+
+def test_a_request_that_ends_drops_the_step_launched_behind_it(model_dirs, tmp_path):
+    """Three requests decode with the step after always launched behind the step in flight; one of
+    them meets its end-of-sequence token in the middle, which the host learns only after the next
+    step is under way with that request in it.  That step is let go and run again without the
+    request; everybody's tokens are the plain implementation's, and every page comes back."""
+    import json
+    import shutil
+    from sprout_lm_b200 import EngineOptions, load_model, make_engine
+    name = "B"
+    sizes, _, page = helpers.TINY[name]
+    rng = np.random.default_rng(67)
+    prompts = [helpers.random_tokens(rng, n, sizes["vocab_size"]) for n in (11, 7, 20)]
+    import plain_qwen2 as plain
+    weights = plain.read_model_folder(model_dirs[name])
+    wants = [plain.greedy(*weights, prompt, 30) for prompt in prompts]
+    # an end-of-sequence token that the first request produces at some step after its tenth and the others never do
+    others = set(wants[1]) | set(wants[2])
+    at = next((i for i in range(10, 30) if wants[0][i] not in others and wants[0][i] not in wants[0][:i]), None)
+    if at is None:
+        pytest.skip("no token of the first request is its own")
+    folder = tmp_path / "tiny_B_eos"
+    shutil.copytree(model_dirs[name], folder)
+    (folder / "generation_config.json").write_text(json.dumps({"eos_token_id": wants[0][at]}))
+    model = load_model(folder, dtype="float32")
+    engine = make_engine(model, EngineOptions(block_size=page, num_blocks=64, max_sequences=4, max_batch_tokens=64,
+                                              prefill_chunk_size=32, prefix_caching=False))
+    for i, prompt in enumerate(prompts):
+        engine.add(f"r{i}", prompt, 30)
+    while engine.pending:
+        engine.step()
+    engine.runner.check_status()
+    assert engine.result("r0")["output"] == wants[0][:at + 1] and engine.result("r0")["finishReason"] == "eos"
+    assert engine.result("r1")["output"] == wants[1] and engine.result("r2")["output"] == wants[2]
+    assert engine.runner.ahead_dropped >= 1 and engine.runner.ahead_used >= 15
+    assert engine.runner.manager.free_pages() == 64
 
 
 def test_large_batch_decodes_with_resident_contexts(tmp_path):
