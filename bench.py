@@ -519,7 +519,10 @@ def timed_decode_attention(shape: str, batch: int, context: int, repeats: int = 
 def timed_gemms(tokens: int, shape: str = "0.5b", repeats: int = 20) -> dict:
     """The model's four projections at ``tokens`` tokens, each alone: 20 launches replayed from a
     CUDA graph (no host time between them), beside the library's plain bfloat16 product of the
-    same shape for scale (it fuses nothing and is not on the engine's path)."""
+    same shape for scale (it fuses nothing and is not on the engine's path).  Up to 256 tokens (the
+    decode regime, where a product is a stream of weights) the launches cycle through copies of
+    the weights that together exceed L2, as the layers of a model do, and the RMSNorm that
+    precedes a product is timed the same way."""
     import torch
     from sprout_lm_b200 import kernels
     from sprout_lm_b200.parts.linear import small_batch_split_k
@@ -532,14 +535,14 @@ def timed_gemms(tokens: int, shape: str = "0.5b", repeats: int = 20) -> dict:
     rand = lambda *shape: (torch.randn(*shape, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
 
     def replayed(call):
-        for _ in range(3):
-            call()
+        for i in range(3):
+            call(i)
         torch.cuda.synchronize()
         graph, stream = torch.cuda.CUDAGraph(), torch.cuda.Stream()
         with torch.cuda.stream(stream):
             with torch.cuda.graph(graph, stream=stream):
-                for _ in range(repeats):
-                    call()
+                for i in range(repeats):
+                    call(i)
         graph.replay()
         torch.cuda.synchronize()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -553,8 +556,12 @@ def timed_gemms(tokens: int, shape: str = "0.5b", repeats: int = 20) -> dict:
     # up to 256 tokens the engine sums q/k/v in float32 over a split K range (bias and rotation follow in attention)
     cases = [("qkv", qkv, hidden, "bias" if tokens > 256 else "residual"), ("o", hidden, hidden, "residual"),
              ("gate_up", 2 * inter, hidden, "swiglu"), ("down", hidden, inter, "residual")]
+    if tokens <= 256:
+        x, gain, normed = torch.randn(tokens, hidden, device="cuda", generator=g), torch.ones(hidden, device="cuda"), rand(tokens, hidden)
+        result["rmsnorm"] = {"shape": [tokens, hidden], "us": round(replayed(lambda i: kernels.rmsnorm(x, gain, normed, 1e-6)), 2)}
     for name, n, k, kind in cases:
         a, w = rand(tokens, k), rand(n, k)
+        copies = min(repeats, -(-160_000_000 // (2 * n * k))) if tokens <= 256 else 1
         kw = {}
         if kind == "bias":
             out, kw = torch.empty(tokens, n, dtype=torch.bfloat16, device="cuda"), {"bias": torch.zeros(n, device="cuda")}
@@ -564,9 +571,10 @@ def timed_gemms(tokens: int, shape: str = "0.5b", repeats: int = 20) -> dict:
         else:
             w = interleave_gate_up(w[:n // 2].contiguous(), w[n // 2:].contiguous())
             out, kw = torch.empty(tokens, n // 2, dtype=torch.bfloat16, device="cuda"), {"swiglu": True}
-        us = replayed(lambda: kernels.gemm_bf16(a, w, out, status, **kw))
-        library = replayed(lambda: torch.matmul(a, w.t()))
-        result[name] = {"shape": [tokens, n, k], "epilogue": kind, "split_k": kw.get("split_k", 1), "us": round(us, 1),
+        ws = [w] + [w.clone() for _ in range(copies - 1)]
+        us = replayed(lambda i: kernels.gemm_bf16(a, ws[i % copies], out, status, **kw))
+        library = replayed(lambda i: torch.matmul(a, ws[i % copies].t()))
+        result[name] = {"shape": [tokens, n, k], "epilogue": kind, "split_k": kw.get("split_k", 1), "weight_copies": copies, "us": round(us, 1),
                         "tflops": round(2.0 * tokens * n * k / us / 1e6), "weight_gbs": round(2.0 * n * k / us / 1e3),
                         "library_plain_us": round(library, 1)}
     assert int(status.item()) == 0
@@ -601,8 +609,9 @@ def run(args) -> dict:
     if prompt_len + args.warmup + args.steps + 8 > context:
         raise SystemExit(f"bench.py: {prompt_len}-token prompts and {args.warmup} + {args.steps} decode steps do not fit the "
                          f"{context}-token context of the benchmark configuration; use at most {context - prompt_len - args.warmup - 8} steps")
-    pages = 64 * (-(-(prompt_len + args.steps + args.warmup + 16) // 16)) + 2048 // 16 + 16
-    runner = ModelRunner(model, num_pages=pages, page_tokens=16, max_requests=64, prefix_caching=False)
+    slots = max(64, batch)
+    pages = slots * (-(-(prompt_len + args.steps + args.warmup + 16) // 16)) + 2048 // 16 + 16
+    runner = ModelRunner(model, num_pages=pages, page_tokens=16, max_requests=slots, prefix_caching=False)
 
     if args.only == "ablate":
         return {"impl": "ours", "only": "ablate", "shape": args.shape, "layers": layers, "batch": batch,

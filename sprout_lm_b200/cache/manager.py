@@ -134,10 +134,11 @@ class CacheManager:
         self._entry_by_id: dict[int, _PrefixEntry] = {}
         self._next_entry = 1
         self._clock = 0
-        # For eviction without a walk over all entries: which entry a page (of group 0) belongs to,
-        # a heap of (last_used, ident) records pushed whenever an entry becomes evictable (stale
-        # records are skipped when popped), and the number of pages that only the map holds.
-        self._entry_of_page: dict[int, _PrefixEntry] = {}
+        # For eviction without a walk over all entries: which entry a page belongs to (keyed by
+        # (group, page): an entry holds one page of every group), a heap of (last_used, ident)
+        # records pushed whenever an entry becomes evictable (stale records are skipped when
+        # popped), and the number of entries whose pages only the map holds.
+        self._entry_of_page: dict[tuple[int, int], _PrefixEntry] = {}
         self._evict_heap: list[tuple[int, int]] = []
         self._cached_only = 0
         self.evictions = 0
@@ -172,7 +173,7 @@ class CacheManager:
             entry = self._prefixes.get((parent, tuple(tokens[end - self.page_tokens:end])))
             if entry is None:
                 break
-            if self.pools[0].refs[entry.pages[0]] == 1:
+            if self._map_only(entry):
                 self._cached_only -= 1                 # a request holds it again
             for group, page in enumerate(entry.pages):
                 self.pools[group].share(page)
@@ -210,7 +211,8 @@ class CacheManager:
                 self._next_entry += 1
                 self._prefixes[key] = entry
                 self._entry_by_id[entry.ident] = entry
-                self._entry_of_page[pages[0]] = entry
+                for group, page in enumerate(pages):
+                    self._entry_of_page[(group, page)] = entry
                 parent = self._entry_by_id.get(entry.parent)       # gone if the map was cleared meanwhile
                 if parent is not None:
                     parent.children += 1
@@ -256,15 +258,17 @@ class CacheManager:
         """Drop the request's reference on each of its pages and give back its state slot."""
         if seq.released:
             return
-        first = list(seq.tables[0])
+        touched: dict[int, _PrefixEntry] = {}          # the prefix entries whose pages this request held
         for group, table in enumerate(seq.tables):
             for page in table:
                 if page >= 0:
+                    entry = self._entry_of_page.get((group, page))
+                    if entry is not None:
+                        touched[entry.ident] = entry
                     self.pools[group].release(page)
             table.clear()
-        for page in first:                             # pages that only the prefix map holds now
-            entry = self._entry_of_page.get(page) if page >= 0 else None
-            if entry is not None and self.pools[0].refs[page] == 1:
+        for entry in touched.values():                 # entries that only the prefix map holds now
+            if self._map_only(entry):
                 self._cached_only += 1
                 self._consider(entry)
         if seq.state_slot >= 0:
@@ -280,9 +284,13 @@ class CacheManager:
             self._evict_one()
         return pool.take()
 
+    def _map_only(self, entry: _PrefixEntry) -> bool:
+        """No live request holds any of the entry's pages (one per group): only the map does."""
+        return all(self.pools[g].refs[p] == 1 for g, p in enumerate(entry.pages))
+
     def _consider(self, entry: _PrefixEntry) -> None:
         """Note ``entry`` as evictable if no live request holds its pages and no entry continues it."""
-        if entry.children == 0 and all(self.pools[g].refs[p] == 1 for g, p in enumerate(entry.pages)):
+        if entry.children == 0 and self._map_only(entry):
             heapq.heappush(self._evict_heap, (entry.last_used, entry.ident))
 
     def _evict_one(self) -> bool:
@@ -293,11 +301,12 @@ class CacheManager:
             candidate = self._entry_by_id.get(ident)
             if candidate is None or candidate.last_used != last_used or candidate.children:
                 continue                               # a stale record
-            if any(self.pools[g].refs[p] != 1 for g, p in enumerate(candidate.pages)):
+            if not self._map_only(candidate):
                 continue
             del self._prefixes[(candidate.parent, candidate.tokens)]
             del self._entry_by_id[candidate.ident]
-            del self._entry_of_page[candidate.pages[0]]
+            for group, page in enumerate(candidate.pages):
+                del self._entry_of_page[(group, page)]
             self._cached_only -= 1
             for group, page in enumerate(candidate.pages):
                 self.pools[group].release(page)
@@ -324,8 +333,9 @@ class CacheManager:
         return len(self.pools[group].free)
 
     def available_pages(self, group: int = 0) -> int:
-        """Pages that a request could get now: the free ones and those that only the prefix map
-        holds (they are evicted on demand, leaves first)."""
+        """Pages of ``group`` that a request could get now: the free ones and those that only the
+        prefix map holds (an entry holds one page of every group; they are evicted on demand,
+        leaves first)."""
         return len(self.pools[group].free) + self._cached_only
 
     def snapshot(self) -> dict:
@@ -362,9 +372,8 @@ class CacheManager:
             raise CacheError("a state slot is free twice.")
         # the eviction bookkeeping against a recount
         entries = list(self._entry_by_id.values())
-        refs = self.pools[0].refs
-        if self._cached_only != sum(1 for e in entries if refs[e.pages[0]] == 1):
-            raise CacheError("the count of pages that only the prefix map holds is off.")
+        if self._cached_only != sum(1 for e in entries if self._map_only(e)):
+            raise CacheError("the count of prefix entries that only the map holds is off.")
         children: dict[int, int] = {}
         for e in entries:
             children[e.parent] = children.get(e.parent, 0) + 1
@@ -372,8 +381,8 @@ class CacheManager:
         for e in entries:
             if e.children != children.get(e.ident, 0):
                 raise CacheError(f"prefix entry {e.ident}: {e.children} children noted, {children.get(e.ident, 0)} found.")
-            if self._entry_of_page.get(e.pages[0]) is not e:
-                raise CacheError(f"prefix entry {e.ident} is not found by its page.")
-            evictable = e.children == 0 and all(self.pools[g].refs[p] == 1 for g, p in enumerate(e.pages))
+            if any(self._entry_of_page.get((g, p)) is not e for g, p in enumerate(e.pages)):
+                raise CacheError(f"prefix entry {e.ident} is not found by its pages.")
+            evictable = e.children == 0 and self._map_only(e)
             if evictable and (e.last_used, e.ident) not in records:
                 raise CacheError(f"prefix entry {e.ident} could be evicted but is not noted for it.")

@@ -483,7 +483,7 @@ int launch(const CUtensorMap& rows_map, const CUtensorMap& cols_map, const CUten
 
 // A [M, K] bf16 row stride lda; W [N, K] bf16 contiguous; out [M, N] row stride ldo, bf16 or
 // float32.  residual != 0: out is float32 and the product is added to it.  orientation: 0 picks
-// by M (weight rows on the MMA's M axis up to 256 tokens, tokens on M beyond), 1 forces tokens
+// by M (weight rows on the MMA's M axis up to 256 tokens, up to 64 with the SwiGLU epilogue, tokens on M beyond), 1 forces tokens
 // on M (128 x 128 tiles, or 256 x 256 tiles of CTA pairs where N is a multiple of 256), 2 weights
 // on M (tokens in tiles of 16..256), 3 tokens on M with single CTAs only, 4 with CTA pairs only.
 // split_k > 1 (weights on M, residual, at most 256 tokens) divides K among CTAs and adds with
@@ -506,7 +506,13 @@ SPROUT_API int sprout_gemm_bf16(const void* A, const void* W, const float* bias,
   SPROUT_REQUIRE(lda >= K && (swiglu || ldo >= N), "gemm_bf16: row strides smaller than the rows");
   SPROUT_REQUIRE(out_dtype == SPROUT_F32 || out_dtype == SPROUT_BF16, "gemm_bf16: unknown output dtype %d", out_dtype);
   SPROUT_REQUIRE(!residual || out_dtype == SPROUT_F32, "gemm_bf16: a residual needs a float32 output");
-  const bool swap = orientation == 2 || (orientation == 0 && M <= 256);    // 1: tokens on M in CTA pairs, 3: single CTAs
+  // Which operand fills the MMA's 128 rows (orientation 0 picks): the weights for a stream of
+  // weights past few tokens (up to 256 tokens; with split K where the epilogue adds).  The SwiGLU
+  // epilogue cannot split K, so its 128-row weight tiles leave SMs idle while the token tiles grow:
+  // measured at the 0.5B / 7B / 14B gate/up shapes, weights on M wins up to 64 tokens, tokens on M
+  // with single CTAs from 65 to 128 (9.7 against 12.5 us at 128 tokens of the 0.5B shape), CTA
+  // pairs beyond (12.7 against 18.1 us at 256).
+  const bool swap = orientation == 2 || (orientation == 0 && M <= (swiglu ? 64 : 256));    // 1: tokens on M in CTA pairs, 3: single CTAs
   if (split_k < 1) split_k = 1;
   SPROUT_REQUIRE(split_k == 1 || (swap && residual && M <= 256), "gemm_bf16: split_k needs weights-on-M with a residual output and at most 256 tokens "
                  "(with tokens on M the kernel splits K by itself where that pays)");
@@ -546,7 +552,7 @@ SPROUT_API int sprout_gemm_bf16(const void* A, const void* W, const float* bias,
   // 41 -> 39 us, 8192 tokens 145 -> 134 us; on narrower tiles single CTAs are as fast).
   int bn = 128;
   split_k = 1;
-  const bool pair = orientation == 4 || (orientation != 3 && N % 256 == 0);
+  const bool pair = orientation == 4 || (orientation != 3 && N % 256 == 0 && !(orientation == 0 && swiglu && M <= 128));
   if (pair) {
     bn = N % 256 == 0 ? 256 : 128;
   } else if (orientation != 3) {

@@ -208,6 +208,56 @@ def test_random_orders_keep_every_page_accounted_for(seed):
     m.check_invariants()
 
 
+@pytest.mark.parametrize("seed", range(4))
+def test_prefix_entries_hold_a_page_of_every_group(seed):
+    """Two groups that keep every key, with pools of different sizes: a published prefix holds one
+    page of each, is found by any of them, and is counted and evicted as one.  Random orders of
+    requests; every page of both pools stays accounted for."""
+    rng = random.Random(100 + seed)
+    page_tokens = rng.choice([2, 4])
+    groups = [GroupSpec("a", "full", None, (0,)), GroupSpec("b", "full", None, (1,))]
+    sizes = (rng.randint(6, 10), rng.randint(11, 16))
+    m = CacheManager(groups, sizes, page_tokens)
+    assert m.prefix_caching
+    prompts = [[rng.randrange(3) for _ in range(rng.randint(3, 14))] for _ in range(5)]
+    live = []
+    hits = 0
+    for _ in range(500):
+        action = rng.random()
+        if action < 0.25 and len(live) < 5:
+            prompt = rng.choice(prompts)
+            seq = m.reuse_prefix(prompt)
+            hits += seq.length
+            live.append((seq, prompt))
+        elif action < 0.75 and live:
+            seq, prompt = rng.choice(live)
+            if m.reserve(seq, seq.length + 1):
+                seq.length += 1
+                m.publish(prompt, seq)
+        elif live:
+            seq, _ = live.pop(rng.randrange(len(live)))
+            m.release(seq)
+        m.check_invariants()
+        snap = m.snapshot()
+        for group, pool in enumerate(m.pools):
+            held = {}
+            for seq, _ in live:
+                table = seq.tables[group]
+                assert len(table) == len(seq.tables[0]) and len(set(table)) == len(table)
+                for page in table:
+                    held[page] = held.get(page, 0) + 1
+            for page in snap["groups"][group]["pages"]:
+                assert page["activeRefs"] == held.get(page["id"], 0)
+            assert m.available_pages(group) == len(pool.free) + m._cached_only <= pool.num_pages
+        assert len(m._entry_of_page) == 2 * len(m._prefixes)
+    assert hits > 0 and m.evictions > 0
+    for seq, _ in live:
+        m.release(seq)
+    m.clear_prefixes()
+    assert [m.free_pages(g) for g in range(2)] == list(sizes)
+    m.check_invariants()
+
+
 def test_eviction_takes_the_least_recently_used_leaf_and_a_parent_only_after_its_children():
     """Three published chains; pages are asked for until the map has to give way.  The order of
     eviction: least recently used first, and within a chain the last page before the first."""

@@ -289,9 +289,11 @@ def test_gemm_bf16_tensor_cores(status, M, N, K, orientation):
 
 
 @pytest.mark.parametrize("orientation", [0, 2, 3, 4])
-@pytest.mark.parametrize("M,inter,K", [(5, 200, 72), (300, 256, 136), (2048, 384, 896), (513, 4864, 96)])
+@pytest.mark.parametrize("M,inter,K", [(5, 200, 72), (300, 256, 136), (2048, 384, 896), (513, 4864, 96),
+                                       (64, 640, 200), (65, 640, 200), (100, 4864, 896), (128, 256, 136), (129, 768, 72), (200, 4864, 96)])
 def test_gemm_bf16_swiglu_epilogue(status, M, inter, K, orientation):
-    """gate and up rows interleaved in blocks of 8; the epilogue writes silu(gate) * up."""
+    """gate and up rows interleaved in blocks of 8; the epilogue writes silu(gate) * up.  The sizes
+    lie on both sides of the token counts at which the arrangement changes (64, 128, 256)."""
     from sprout_lm_b200 import kernels
     from sprout_lm_b200.parts.mlp import interleave_gate_up
     if orientation == 2 and M > 256:

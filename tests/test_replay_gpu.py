@@ -174,8 +174,9 @@ def test_long_context(tmp_path, dtype):
         assert err <= TOL[dtype], (pos, err)
 
 
+@pytest.mark.parametrize("name", ["A", "B"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_sharp_attention_shows_every_key(model_dirs, tmp_path, dtype):
+def test_sharp_attention_shows_every_key(model_dirs, tmp_path, dtype, name):
     """Random weights make attention nearly uniform, which hides a lost or misplaced key under
     bfloat16 rounding.  Here the query and key projections are scaled up so that the softmax is
     peaked: each position leans on a few particular keys, near and far, and an engine that
@@ -184,7 +185,6 @@ def test_sharp_attention_shows_every_key(model_dirs, tmp_path, dtype):
     import plain_qwen2 as plain
     from sprout_lm_b200.weights import Checkpoint, write_safetensors
     import shutil
-    name = "B"
     page = helpers.TINY[name][2]
     folder = tmp_path / "sharp"
     shutil.copytree(model_dirs[name], folder)
@@ -198,8 +198,8 @@ def test_sharp_attention_shows_every_key(model_dirs, tmp_path, dtype):
     cfg, w = plain.read_model_folder(folder)
     # the attention really is peaked: in the last layer's input the largest probability is far from uniform
     logits_ref = {rid: plain.logits(cfg, w, toks) for rid, toks in requests.items()}
-    plans = {"portions": helpers.plan_portions(requests), "mixed": helpers.plan_mixed(requests, np.random.default_rng(4)),
-             "tail": helpers.plan_tail_decode(requests)}
+    plans = {"whole": helpers.plan_whole(requests), "portions": helpers.plan_portions(requests),
+             "mixed": helpers.plan_mixed(requests, np.random.default_rng(4)), "tail": helpers.plan_tail_decode(requests)}
     scale = max(float(np.abs(v).max()) for v in logits_ref.values())
     tol = 1e-4 if dtype == "float32" else 0.03 * scale
     for label, plan in plans.items():

@@ -4,7 +4,8 @@ Some hosts of this library cannot allocate device memory while serving (all of i
 their own arena, or they are plain C programs without an allocator to ask); for them the
 library carries a fixed scratch array of its own.  This test calls that entry point by its C
 name, twice in a row on different inputs (the array keeps the first call's contents), and
-compares each result with the ordinary entry point that takes scratch from the caller.
+compares each result with the ordinary entry point that takes scratch from the caller and with
+a plain float64 attention over the same pages.
 """
 import ctypes
 
@@ -32,6 +33,21 @@ def _case(seed, requests, heads, kv_heads, head_dim, page, lengths):
     return (q.to(DEV), k.to(DEV), v.to(DEV), table.to(DEV), torch.tensor(lengths, dtype=torch.int32, device=DEV))
 
 
+def _plain(q, k, v, table, lengths, heads, kv_heads, head_dim, page):
+    """softmax(q k^T / sqrt(d)) v per request and head in float64, from the pages the table names."""
+    out = torch.zeros(q.shape, dtype=torch.float64)
+    group = heads // kv_heads
+    q, k, v, table = q.double().cpu(), k.double().cpu(), v.double().cpu(), table.cpu()
+    for r, n in enumerate(lengths):
+        keys = torch.cat([k[int(p)] for p in table[r, :-(-n // page)]], dim=1)[:, :n]        # [kv_heads, n, hd]
+        values = torch.cat([v[int(p)] for p in table[r, :-(-n // page)]], dim=1)[:, :n]
+        for h in range(heads):
+            qh = q[r, h * head_dim:(h + 1) * head_dim]
+            weights = torch.softmax(keys[h // group] @ qh / head_dim ** 0.5, dim=0)
+            out[r, h * head_dim:(h + 1) * head_dim] = weights @ values[h // group]
+    return out
+
+
 def test_static_scratch_entry_point_matches_the_ordinary_one():
     from sprout_lm_b200 import kernels
     lib = kernels.load_library()
@@ -56,6 +72,8 @@ def test_static_scratch_entry_point_matches_the_ordinary_one():
         torch.cuda.synchronize()
         assert torch.isfinite(got.float()).all()
         assert (got.float() - want.float()).abs().max().item() <= 1.2e-2
+        plain = _plain(q, k, v, table, lengths, heads, kv_heads, head_dim, page)
+        assert (got.double().cpu() - plain).abs().max().item() <= 1.2e-2
     assert int(status.item()) == 0
     # a request that would not fit the built-in array is refused with an explanation, nothing runs
     code = static(q.data_ptr(), q.stride(0), k.data_ptr(), v.data_ptr(), table.data_ptr(), table.stride(0),
