@@ -94,6 +94,7 @@ attention_decode_resident_kernel(const __grid_constant__ CUtensorMap map_k, cons
   __shared__ int s_failed;
 
   pdl_launch_dependents();
+  SPROUT_TL_ENTRY(0);
   const int g = blockIdx.x, r = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = p.heads / p.kv_heads;
@@ -139,6 +140,7 @@ attention_decode_resident_kernel(const __grid_constant__ CUtensorMap map_k, cons
   }
 
   pdl_wait();
+  SPROUT_TL_WAITED(0);
   if (!usable) return;                                         // nothing was issued
 
   // ---- the new token: its query rows, and (fused) its key and value
@@ -354,6 +356,7 @@ attention_decode_resident_kernel(const __grid_constant__ CUtensorMap map_k, cons
       }
     }
   }
+  SPROUT_TL_EXIT(0);
 }
 
 size_t resident_smem_bytes(int head_dim, int cap_keys) {
@@ -435,3 +438,5 @@ SPROUT_API int sprout_attention_decode_resident(float* acc, const float* bias, c
   if (head_dim == 64) return acc ? launch_resident<64, true>(map_k, map_v, p, requests, stream) : launch_resident<64, false>(map_k, map_v, p, requests, stream);
   return acc ? launch_resident<128, true>(map_k, map_v, p, requests, stream) : launch_resident<128, false>(map_k, map_v, p, requests, stream);
 }
+
+SPROUT_TL_READER(attention_decode_resident)

@@ -143,8 +143,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   uint32_t* tmem_slot = (uint32_t*)(bars + 14);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
+  // What this kernel reads before it waits for the step's earlier kernels (the request's bounds
+  // and positions, the block table) was written before the step's first kernel; the queries and
+  // the newest keys and values are read after the wait, below.
   pdl_launch_dependents();
-  pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool paired = SPLIT && (int)blockIdx.x < 2 * p.split_pieces;      // one of the two CTAs of a piece
   const int piece_index = !SPLIT ? (int)blockIdx.x : paired ? (int)blockIdx.x >> 1 : (int)blockIdx.x - p.split_pieces;
@@ -193,6 +195,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(tmem_slot, TC_TMEM_COLS);
+  pdl_wait();
 
   // Q rows -> shared memory, K-major with the 128-byte swizzle (16-byte chunk c of row r at chunk
   // position c ^ (r & 7)), one 16 KB atom per Q tile and 64 elements of head_dim

@@ -65,7 +65,7 @@ inline cudaError_t sprout_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block
 // wait for the earlier kernels, and the latest exit of any CTA's first thread.  Time only grows, so
 // after a step the records are those of its last layer.  sprout_timeline_<file>(out) copies them out.
 #ifdef SPROUT_TIMELINE
-static __device__ unsigned long long g_sprout_tl[4][4];
+static __device__ unsigned long long g_sprout_tl[8][4];
 __device__ __forceinline__ unsigned long long sprout_now_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

@@ -124,7 +124,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
   };
 
   pdl_launch_dependents();
-  SPROUT_TL_ENTRY(0);
+  // instrumented builds: a decode layer's four products and the head keep a record each (q/k/v, output, gate/up, down, head)
+#ifdef SPROUT_TIMELINE
+  const int tl_slot = p.epilogue == EPI_SWIGLU ? 2 : p.epilogue == EPI_STORE ? 4 : p.N > p.K ? 0 : p.N == p.K ? 1 : 3;
+  if (tl_slot >= 0) SPROUT_TL_ENTRY(tl_slot);
+#endif
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], PAIR ? 16 : 8); }
@@ -180,7 +184,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
           copy(smem_base + i * L::STAGE_BYTES + W_OFF, weight_map, count_base + 8 * i, (k.kb_begin + i) * BLOCK_K, weight_row);
         }
         pdl_wait();
-        SPROUT_TL_WAITED(0);
+#ifdef SPROUT_TIMELINE
+        if (tl_slot >= 0) SPROUT_TL_WAITED(tl_slot);
+#endif
       }
       int x = k.kb_begin * BLOCK_K;
       for (int i = 0; i < k.num_kb; i++, it++, x += BLOCK_K) {
@@ -429,7 +435,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
   __syncthreads();
   if (PAIR) cluster_barrier();      // neither CTA leaves while the other may still count on its barriers or read its memory
   if (warp == 1) tmem_dealloc(tmem_base, L::TMEM_COLS);
-  SPROUT_TL_EXIT(0);
+#ifdef SPROUT_TIMELINE
+  if (tl_slot >= 0) SPROUT_TL_EXIT(tl_slot);
+#endif
 }
 
 // ------------------------------------------------------------------ host side

@@ -1,5 +1,6 @@
 // Shared by the kernels for steps of a few tokens (ffn_decode.cu, linear_decode.cu): weights as
-// the 16-row operand of `mma.sync.m16n8k16`, up to 8 tokens as its 8 columns, weight tiles
+// the 16-row operand of `mma.sync.m16n8k16`, the tokens as its 8 columns (one or two such tiles
+// of tokens), weight tiles
 // brought in by TMA with the 128-byte swizzle, and the division of a matrix into pieces for
 // the CTAs.
 #pragma once
@@ -8,7 +9,10 @@
 
 namespace {
 
-constexpr int SMALL_MAX_TOKENS = 8;         // the MMA's N
+constexpr int SMALL_MAX_TOKENS = 16;        // two tiles of the MMA's N = 8
+
+// Rows of the tokens' operand that a launch for `tokens` tokens holds: whole tiles of 8.
+__host__ __device__ __forceinline__ int token_rows(int tokens) { return tokens <= 8 ? 8 : 16; }
 
 // The split of a range of n items over parts: part p gets [n*p/parts, n*(p+1)/parts)  (n * parts stays far below 2^32).
 __host__ __device__ __forceinline__ int share_begin(int n, int part, int parts) { return (int)(((unsigned)n * (unsigned)part) / (unsigned)parts); }

@@ -305,14 +305,14 @@ def gemm_bf16(a, weight, out, status, bias=None, residual=None, orientation=0, s
 
 
 def linear_decode_supported(tokens: int, out_features: int, in_features: int) -> bool:
-    """Whether ``linear_decode`` takes these sizes: 1..8 tokens, sizes that are multiples of 16, a
+    """Whether ``linear_decode`` takes these sizes: 1..16 tokens, sizes that are multiples of 16, a
     matrix small enough for light CTAs."""
     lib = _lib or load_library()
     return bool(lib.sprout_linear_decode_supported(tokens, out_features, in_features))
 
 
 def linear_decode(weight, out, status, a=None, norm=None):
-    """out += input @ weight.T for up to 8 tokens, added with atomics into the float32 ``out``
+    """out += input @ weight.T for up to 16 tokens, added with atomics into the float32 ``out``
     [tokens, N] (the residual stream, or a zeroed workspace).  The input is ``a`` (bfloat16
     [tokens, K]) or ``norm = (x, gain, eps)``: the RMSNorm of the float32 rows ``x``, computed
     inside the kernel."""
@@ -418,10 +418,15 @@ def decode_timeline() -> dict | None:
     records = {}
     for label, reader, slot in (("norm + q/k/v", "linear_decode", 0), ("attention", "attention_bf16", 0),
                                 ("output projection", "linear_decode", 1), ("feed-forward", "ffn_decode", 0),
-                                ("head product", "gemm_tcgen05", 0)):
-        raw = (ctypes.c_ulonglong * 16)()
+                                ("q/k/v product", "gemm_tcgen05", 0), ("attention, resident", "attention_decode_resident", 0),
+                                ("output product", "gemm_tcgen05", 1), ("gate/up product", "gemm_tcgen05", 2),
+                                ("down product", "gemm_tcgen05", 3), ("head product", "gemm_tcgen05", 4)):
+        raw = (ctypes.c_ulonglong * 32)()
         getattr(lib, "sprout_timeline_" + reader)(raw)
         records[label] = [raw[4 * slot], raw[4 * slot + 1], raw[4 * slot + 2]]
+    # the records of kernels that this step did not run are older than the step: drop what lies more than 5 ms before the newest
+    newest = max(v[2] for v in records.values())
+    records = {label: v for label, v in records.items() if v[0] and newest - v[0] < 5_000_000}
     origin = min(v[0] for v in records.values() if v[0])
     return {label: {"entry": (v[0] - origin) / 1000.0, "waited": (v[1] - origin) / 1000.0, "exit": (v[2] - origin) / 1000.0}
             for label, v in records.items() if v[0]}
@@ -435,14 +440,14 @@ def wait_probe(status):
 
 
 def ffn_decode_supported(tokens: int, hidden: int, intermediate: int) -> bool:
-    """Whether ``ffn_decode`` takes these sizes: 1..8 tokens, sizes that are multiples of 16, and a
+    """Whether ``ffn_decode`` takes these sizes: 1..16 tokens, sizes that are multiples of 16, and a
     layer small enough for every CTA to hold its share of the two matrices in shared memory."""
     lib = _lib or load_library()
     return bool(lib.sprout_ffn_decode_supported(tokens, hidden, intermediate))
 
 
 def ffn_decode(x, gain, eps, w_gate_up, w_down, status):
-    """x += W_down (silu(W_gate h) * W_up h) with h = rmsnorm(x, gain, eps), for up to 8 tokens,
+    """x += W_down (silu(W_gate h) * W_up h) with h = rmsnorm(x, gain, eps), for up to 16 tokens,
     in one kernel (norm, both products, activation and residual sum; the activation is exchanged
     among the CTAs of a thread-block cluster and never goes to memory).
 

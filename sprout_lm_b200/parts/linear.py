@@ -2,7 +2,7 @@
 
 float32 weights run on CUDA cores with float32 fused multiply-adds (the true 32-bit path).
 bfloat16 weights run on the tcgen05 tensor-core kernel: weight rows on the MMA's M axis for a
-handful of tokens (decode), tokens on M for many (prefill).  Up to 8 tokens through a small
+handful of tokens (decode), tokens on M for many (prefill).  Up to 16 tokens through a small
 matrix into a float32 sum take the light `mma.sync` kernel instead, which can also fold the
 RMSNorm before the product in (csrc/linear_decode.cu).
 """
@@ -14,7 +14,7 @@ import torch
 
 from .. import kernels
 
-SMALL_BATCH_TOKENS = 8      # up to this many tokens small layers take the light small-batch kernels
+SMALL_BATCH_TOKENS = 16     # up to this many tokens small layers take the light small-batch kernels (two tiles of the MMA's 8 columns)
 
 
 def small_batch_enabled() -> bool:
@@ -44,9 +44,11 @@ class Linear:
                              "its rows must start on 16-byte boundaries")
         # A handful of tokens through a small matrix: the light kernel (csrc/linear_decode.cu)
         self.small_tokens = 0
-        if weight.dtype == torch.bfloat16 and weight.is_cuda and small_batch_enabled() \
-                and kernels.linear_decode_supported(SMALL_BATCH_TOKENS, self.out_features, self.in_features):
-            self.small_tokens = SMALL_BATCH_TOKENS
+        if weight.dtype == torch.bfloat16 and weight.is_cuda and small_batch_enabled():
+            for tokens in (SMALL_BATCH_TOKENS, 8):       # two tiles of 8 tokens where the pieces leave room, else one
+                if kernels.linear_decode_supported(tokens, self.out_features, self.in_features):
+                    self.small_tokens = tokens
+                    break
 
     def split_k(self, tokens: int, residual: bool) -> int:
         return small_batch_split_k(self.out_features, self.in_features, tokens, residual, self.sms)

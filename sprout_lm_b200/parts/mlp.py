@@ -15,7 +15,7 @@ from .base import Part, TensorDecl, WeightSource, register_part
 from .linear import Linear, small_batch_enabled
 
 INTERLEAVE = 8
-FUSED_TOKENS = 8          # the one-kernel decode form takes up to this many tokens
+FUSED_TOKENS = 16         # the one-kernel decode form takes up to this many tokens (two tiles of the MMA's 8 columns)
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, block: int = INTERLEAVE) -> torch.Tensor:
@@ -58,8 +58,10 @@ class SwiGLUMLP(Part):
         # Small layers decode in one kernel that also takes the norm before the feed-forward
         # (csrc/ffn_decode.cu).
         if self.gate_up.weight.dtype == torch.bfloat16 and small_batch_enabled():
-            if kernels.ffn_decode_supported(FUSED_TOKENS, self.hidden_size, self.intermediate_size):
-                self._fused_tokens = FUSED_TOKENS
+            for tokens in (FUSED_TOKENS, 8):             # two tiles of 8 tokens where the layer's shares leave room, else one
+                if kernels.ffn_decode_supported(tokens, self.hidden_size, self.intermediate_size):
+                    self._fused_tokens = tokens
+                    break
 
     def forward(self, h, x, ctx=None):
         self.down.forward(self.gate_up.forward_swiglu(h, self.block), residual=x)

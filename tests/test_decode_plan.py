@@ -163,18 +163,20 @@ def test_prefill_step_captures_do_not_take_turns_evicting_one_another(monkeypatc
 
 
 def test_small_batch_kernels_say_what_they_take():
-    """The small-batch kernels' size rules are host arithmetic in the kernel library: up to 8 tokens,
+    """The small-batch kernels' size rules are host arithmetic in the kernel library: up to 16 tokens,
     sizes in steps of 16, and a layer small enough for the SMs' shared memory.  What they refuse
     runs on the tensor-core products (the parts ask before they choose)."""
     # the 0.5B layer sizes and the tests' tiny ones fit
     for hidden, inter in [(896, 4864), (64, 128), (96, 320), (1024, 2816)]:
         assert kernels.ffn_decode_supported(8, hidden, inter) and kernels.ffn_decode_supported(1, hidden, inter)
+        assert kernels.ffn_decode_supported(9, hidden, inter) and kernels.ffn_decode_supported(16, hidden, inter)
     assert kernels.linear_decode_supported(8, 1152, 896) and kernels.linear_decode_supported(3, 896, 896)
+    assert kernels.linear_decode_supported(16, 1152, 896) and kernels.linear_decode_supported(9, 896, 896)
     # more tokens than the instruction has columns, sizes off the 16-step, layers too large
-    assert not kernels.ffn_decode_supported(9, 896, 4864)
+    assert not kernels.ffn_decode_supported(17, 896, 4864)
     assert not kernels.ffn_decode_supported(8, 904, 4864) and not kernels.ffn_decode_supported(8, 896, 4872)
     assert not kernels.ffn_decode_supported(8, 3584, 18944) and not kernels.ffn_decode_supported(8, 5120, 13824)
-    assert not kernels.linear_decode_supported(9, 896, 896) and not kernels.linear_decode_supported(8, 900, 896)
+    assert not kernels.linear_decode_supported(17, 896, 896) and not kernels.linear_decode_supported(8, 900, 896)
     assert not kernels.linear_decode_supported(8, 3584, 3584)
 
 

@@ -5,7 +5,7 @@ of requests, the block tables' width and the attention's split plan, with a host
 updated in place; the benchmark's device-side loop (``DecodeLoop``) feeds tokens back without the
 host; mixed steps whose sizes repeat are captured too (``StepGraphs``), with sampling inside.
 Here each of them runs for hundreds of tokens, across changes of plan and of table width, on both
-sides of the small-batch kernels' limit of 8 tokens, and what it computes is compared with the
+sides of the small-batch kernels' token tiles (8 and 16 tokens), and what it computes is compared with the
 plain implementation: logits where they can be read, tokens otherwise.
 """
 import numpy as np
@@ -41,7 +41,7 @@ def check_tokens(model_dir, prompt, output, dtype, label, tol=None):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,batch", [("A", 3), ("A", 9), ("B", 3), ("B", 9)])
+@pytest.mark.parametrize("name,batch", [("A", 3), ("A", 9), ("B", 3), ("B", 9), ("A", 18)])
 def test_long_generation_through_the_scheduler(model_dirs, name, batch, dtype):
     """300 and more decoded tokens per request through the scheduler: the captured decode steps
     are re-keyed on the way (requests finish one after the other, so the batch shrinks; B's block
@@ -80,7 +80,7 @@ def test_long_generation_through_the_scheduler(model_dirs, name, batch, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,batch", [("B", 3), ("A", 9)])
+@pytest.mark.parametrize("name,batch", [("B", 3), ("A", 9), ("B", 18)])
 def test_replayed_decode_steps_give_the_plain_logits(model_dirs, name, batch, dtype):
     """The logits inside the captured decode step, read after every replay, with the requests'
     tokens forced: at the tolerance of the step function's own tests, across plan and width
@@ -131,7 +131,7 @@ def test_replayed_decode_steps_give_the_plain_logits(model_dirs, name, batch, dt
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,batch", [("A", 1), ("B", 8), ("A", 9), ("B", 64)])
+@pytest.mark.parametrize("name,batch", [("A", 1), ("B", 8), ("A", 9), ("B", 16), ("A", 17), ("B", 64)])
 def test_device_side_decode_loop_gives_the_schedulers_tokens(model_dirs, name, batch, dtype):
     """``DecodeLoop`` (the benchmark's device-side run of decode steps) against ``generate``: the
     same tokens in 32-bit, and in bfloat16 tokens that the plain implementation backs."""
@@ -142,7 +142,7 @@ def test_device_side_decode_loop_gives_the_schedulers_tokens(model_dirs, name, b
     sizes, _, page = helpers.TINY[name]
     model = load_model(model_dirs[name], dtype=dtype)
     rng = np.random.default_rng(31 + batch)
-    steps = 140 if batch <= 9 else 40
+    steps = 140 if batch <= 9 else 40 if batch > 17 else 80
     prompts = [helpers.random_tokens(rng, int(n), sizes["vocab_size"]) for n in rng.integers(3, 60, batch)]
     pages = sum(-(-(len(p) + steps + 2) // page) for p in prompts) + 1
     runner = ModelRunner(model, num_pages=pages, page_tokens=page, max_requests=batch, prefix_caching=False)

@@ -321,7 +321,9 @@ def test_gemm_bf16_split_k(status, M, N, K, split):
 
 
 @pytest.mark.parametrize("tokens,hidden,inter,eps", [(1, 64, 128, 1e-6), (5, 96, 320, 1e-5), (8, 896, 4864, 1e-6),
-                                                     (3, 1024, 2816, 1e-5), (8, 1536, 2048, 1e-6), (2, 48, 16, 1e-6)])
+                                                     (3, 1024, 2816, 1e-5), (8, 1536, 2048, 1e-6), (2, 48, 16, 1e-6),
+                                                     (9, 896, 4864, 1e-6), (16, 896, 4864, 1e-6), (13, 96, 320, 1e-5),
+                                                     (11, 1024, 2816, 1e-5), (16, 48, 16, 1e-6)])
 def test_ffn_decode_one_kernel(status, tokens, hidden, inter, eps):
     """RMSNorm, gate/up, SwiGLU, down and the residual sum in one launch, against the same
     arithmetic in float64 with the kernel's two roundings to bfloat16 (the normalised rows, the
@@ -351,7 +353,7 @@ def test_ffn_decode_one_kernel(status, tokens, hidden, inter, eps):
 
 def test_ffn_decode_refuses_what_does_not_fit(status):
     from sprout_lm_b200 import kernels
-    assert not kernels.ffn_decode_supported(9, 896, 4864)          # more tokens than the tile has columns
+    assert not kernels.ffn_decode_supported(17, 896, 4864)         # more tokens than two tiles have columns
     assert not kernels.ffn_decode_supported(8, 904, 4864)          # sizes that are no multiple of 16
     assert not kernels.ffn_decode_supported(8, 3584, 18944)        # a CTA's share exceeds shared memory
     x = rand(8, 3584)
@@ -360,7 +362,8 @@ def test_ffn_decode_refuses_what_does_not_fit(status):
 
 
 @pytest.mark.parametrize("normed", [False, True])
-@pytest.mark.parametrize("tokens,N,K", [(1, 128, 64), (8, 1152, 896), (5, 160, 96), (8, 896, 896), (3, 48, 16), (7, 2048, 1536)])
+@pytest.mark.parametrize("tokens,N,K", [(1, 128, 64), (8, 1152, 896), (5, 160, 96), (8, 896, 896), (3, 48, 16), (7, 2048, 1536),
+                                        (9, 1152, 896), (16, 896, 896), (12, 160, 96), (16, 48, 16), (10, 2048, 1536)])
 def test_linear_decode_small_batch(status, tokens, N, K, normed):
     """out += input W^T for a few tokens with light CTAs; the input is bfloat16 rows or the RMSNorm
     of float32 rows computed inside the kernel.  The sums land on what the output held before."""
@@ -389,7 +392,7 @@ def test_linear_decode_small_batch(status, tokens, N, K, normed):
 
 def test_linear_decode_refuses_what_does_not_fit(status):
     from sprout_lm_b200 import kernels
-    assert not kernels.linear_decode_supported(9, 896, 896)
+    assert not kernels.linear_decode_supported(17, 896, 896)
     assert not kernels.linear_decode_supported(8, 900, 896)
     assert not kernels.linear_decode_supported(8, 3584, 3584)       # pieces too large for light CTAs
     with pytest.raises(kernels.KernelError, match="linear_decode"):
@@ -415,15 +418,28 @@ def attention_reference(q, keys, values, heads, kv_heads, head_dim):
     return out
 
 
-def build_paged_case(dtype, heads, kv_heads, head_dim, page, lengths, q_counts, seed=0, spike=None, poison=False):
+def build_paged_case(dtype, heads, kv_heads, head_dim, page, lengths, q_counts, seed=0, spike=None, poison=False,
+                     layout="scattered"):
     """Requests with ``lengths`` cached positions each (the last ``q_counts`` of them are this
-    step's queries), in pages scattered over the pool.  ``poison``: every slot that holds no key
-    of a request (the rest of a last page, pages nobody owns) is NaN instead of zero."""
+    step's queries), in pages scattered over the pool (``layout`` "runs": in runs of 1 to 11 pages
+    that follow one another in the pool, the runs scattered; "in order": as a fresh pool hands
+    them out).  ``poison``: every slot that holds no key of a request (the rest of a last page,
+    pages nobody owns) is NaN instead of zero."""
     g = torch.Generator().manual_seed(seed)
     R = len(lengths)
     pages_each = [-(-n // page) for n in lengths]
     pool = sum(pages_each) + 3
-    order = torch.randperm(pool, generator=g)
+    if layout == "scattered":
+        order = torch.randperm(pool, generator=g)
+    elif layout == "in order":
+        order = torch.arange(pool)
+    else:
+        runs, at = [], 0
+        while at < pool:
+            n = min(pool - at, int(torch.randint(1, 12, (1,), generator=g)))
+            runs.append(torch.arange(at, at + n))
+            at += n
+        order = torch.cat([runs[i] for i in torch.randperm(len(runs), generator=g)])
     table = torch.full((R, max(pages_each)), -1, dtype=torch.int32)
     k_cache = torch.full((pool, kv_heads, page, head_dim), float("nan") if poison else 0.0)
     v_cache = torch.full((pool, kv_heads, page, head_dim), float("nan") if poison else 0.0)
@@ -586,13 +602,15 @@ RESIDENT_CASES = [
 ]
 
 
+@pytest.mark.parametrize("layout", ["scattered", "runs", "in order"])
 @pytest.mark.parametrize("rotate", [False, True])
 @pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page,lengths", RESIDENT_CASES)
-def test_attention_decode_resident(status, heads, kv_heads, head_dim, page, lengths, fused, rotate):
+def test_attention_decode_resident(status, heads, kv_heads, head_dim, page, lengths, fused, rotate, layout):
     """Decode attention with each request's whole context in one CTA's shared memory (pages by
-    TMA): against the float64 reference; in the fused form (sums in, rotation, cache append) also
-    against the separate rotary kernel.  Every cache slot outside the requests is NaN."""
+    TMA; pages scattered, in runs, or in the pool's order): against the float64
+    reference; in the fused form (sums in, rotation, cache append) also against the separate
+    rotary kernel.  Every cache slot outside the requests is NaN."""
     from sprout_lm_b200 import kernels
     from sprout_lm_b200.parts import Runtime
     from sprout_lm_b200.parts.rope import HalfSplitRotary
@@ -601,7 +619,7 @@ def test_attention_decode_resident(status, heads, kv_heads, head_dim, page, leng
     R = len(lengths)
     room = kernels.decode_attention_plan(kernels.sm_count() // kv_heads, heads, kv_heads, head_dim, page, -(-max(lengths) // page) * page, max(lengths))
     assert room[0] == "resident"
-    case = build_paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, lengths, [1] * R, seed=7, poison=True)
+    case = build_paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, lengths, [1] * R, seed=7, poison=True, layout=layout)
     out = torch.full((R, heads * head_dim), float("nan"), dtype=torch.bfloat16, device=DEV)
     if not fused:
         kernels.attention_decode_resident(case["k_cache"], case["v_cache"], case["table"], case["context_lens"], out, heads,
@@ -617,7 +635,7 @@ def test_attention_decode_resident(status, heads, kv_heads, head_dim, page, leng
     positions = (case["context_lens"] - 1).to(torch.int32)
     seq_of_token = torch.arange(R, dtype=torch.int32, device=DEV)
     # the separate path on a cache without the poison beyond the requests (its kernels are tested for that elsewhere)
-    clean = build_paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, lengths, [1] * R, seed=7)
+    clean = build_paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, lengths, [1] * R, seed=7, layout=layout)
     k1, v1 = clean["k_cache"].clone(), clean["v_cache"].clone()
     acc1 = sums.clone()
     qkv = torch.zeros(R, width, dtype=torch.bfloat16, device=DEV)

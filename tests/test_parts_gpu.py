@@ -288,7 +288,7 @@ def test_embedding_and_head_parts(dtype, tied):
 
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_small_batches_take_the_light_kernels_and_agree_with_the_separate_ones(tmp_path, monkeypatch, name):
-    """Up to 8 tokens a small bfloat16 layer runs as four launches (norm + q/k/v, attention, output
+    """Up to 16 tokens a small bfloat16 layer runs as four launches (norm + q/k/v, attention, output
     projection, feed-forward with its norm); the same model loaded with SPROUT_SMALL_BATCH=0 runs
     the separate norms and tensor-core products.  Both must give the plain implementation's logits,
     and the launch counts must show that the light kernels really ran."""
@@ -298,21 +298,21 @@ def test_small_batches_take_the_light_kernels_and_agree_with_the_separate_ones(t
     from sprout_lm_b200.models import load_model
     folder = helpers.make_model_dir(tmp_path, name)
     sizes, _, page = helpers.TINY[name]
-    tokens = helpers.random_tokens(np.random.default_rng(3), 21, sizes["vocab_size"])
+    tokens = helpers.random_tokens(np.random.default_rng(3), 46, sizes["vocab_size"])
     want = helpers.plain_logits(folder, tokens)
     results, launches = {}, {}
     for mode in ("1", "0"):
         monkeypatch.setenv("SPROUT_SMALL_BATCH", mode)
         model = load_model(folder, dtype=torch.bfloat16)
         light = mode == "1"
-        assert (model.blocks[0].feed_forward._fused_tokens == 8) == light
-        assert (model.blocks[0].mixer.qkv.small_tokens == 8) == light
-        runner = ModelRunner(model, num_pages=8, page_tokens=page, max_requests=2, prefix_caching=False)
+        assert (model.blocks[0].feed_forward._fused_tokens == 16) == light
+        assert (model.blocks[0].mixer.qkv.small_tokens == 16) == light
+        runner = ModelRunner(model, num_pages=12, page_tokens=page, max_requests=2, prefix_caching=False)
         runner.graphs.enabled = runner.step_graphs.enabled = False
         seq = runner.new_sequence()
         assert runner.reserve(seq, len(tokens))
         rows, at = [], 0
-        for count in (8, 5, 1, 1, 3, 2, 1):                       # portions of up to 8 tokens, and single tokens
+        for count in (8, 5, 1, 1, 3, 2, 16, 9, 1):                # portions of up to 16 tokens, and single tokens
             before = kernels.LAUNCHES
             rows.append(runner.step([StepEntry(seq, tokens[at:at + count], list(range(count)))]).float().cpu().numpy())
             launches[mode] = kernels.LAUNCHES - before
