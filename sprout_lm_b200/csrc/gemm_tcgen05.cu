@@ -520,7 +520,10 @@ SPROUT_API int sprout_gemm_bf16(const void* A, const void* W, const float* bias,
   // measured at the 0.5B / 7B / 14B gate/up shapes, weights on M wins up to 64 tokens, tokens on M
   // with single CTAs from 65 to 128 (9.7 against 12.5 us at 128 tokens of the 0.5B shape), CTA
   // pairs beyond (12.7 against 18.1 us at 256).
-  const bool swap = orientation == 2 || (orientation == 0 && M <= (swiglu ? 64 : 256));    // 1: tokens on M in CTA pairs, 3: single CTAs
+  // Between 33 and 64 tokens the SwiGLU product goes tokens on M as well when its 128-row weight tiles
+  // would leave more than two SMs in five idle (the 0.5B shape: 76 tiles, 9.2 against 9.8 us).
+  const bool few_weight_tiles = swiglu && M > 32 && 5LL * ((N + BLOCK_M - 1) / BLOCK_M) < 3LL * sm_count();
+  const bool swap = orientation == 2 || (orientation == 0 && M <= (swiglu ? 64 : 256) && !few_weight_tiles);    // 1: tokens on M in CTA pairs, 3: single CTAs
   if (split_k < 1) split_k = 1;
   SPROUT_REQUIRE(split_k == 1 || (swap && residual && M <= 256), "gemm_bf16: split_k needs weights-on-M with a residual output and at most 256 tokens "
                  "(with tokens on M the kernel splits K by itself where that pays)");
