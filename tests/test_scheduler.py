@@ -307,6 +307,30 @@ class AheadRunner:
         return sampled
 
 
+def test_a_token_that_ends_a_request_lets_the_step_launched_behind_it_go():
+    """The step after is handed over before this step's tokens are known; when one of them is an
+    end-of-sequence token the request is gone from the next plan and the launched step is not
+    the step asked for.  The survivors' tokens are what they would have been."""
+    prompts = [[3, 9, 27], [4, 16, 2, 8], [5, 25]]
+    free = [reference_output(p, 14, 50) for p in prompts]
+    # an end-of-sequence token that the second request produces in the middle and the others never do
+    others = set(free[0]) | set(free[2])
+    at = next((i for i in range(3, 12) if free[1][i] not in others and free[1][i] not in free[1][:i]), None)
+    assert at is not None, "the stub's token rule changed: pick other prompts"
+    stub = StubRunner(40, 4)
+    stub.eos_token_ids = (free[1][at],)
+    runner = AheadRunner(stub)
+    engine = Engine(runner, EngineOptions(block_size=4, num_blocks=40, max_sequences=4, max_batch_tokens=16, prefill_chunk_size=8))
+    for i, prompt in enumerate(prompts):
+        engine.add(f"r{i}", prompt, 14)
+    while engine.pending:
+        engine.step()
+    assert engine.result("r1")["output"] == free[1][:at + 1] and engine.result("r1")["finishReason"] == "eos"
+    assert engine.result("r0")["output"] == free[0] and engine.result("r2")["output"] == free[2]
+    assert runner.dropped >= 1 and runner.used >= 8
+    engine.cache.check_invariants()
+
+
 def test_the_next_decode_step_is_launched_ahead_only_when_it_is_known():
     """With every running request decoding on and nobody waiting, the scheduler hands the step
     after to the runner together with the step; a late arrival, a cancellation or a request that
