@@ -78,6 +78,10 @@ struct DecodeParams {
   float* acc; const float* bias; const float* cos_table; const float* sin_table; int max_positions;
   int rotary_dim, interleaved;
   __nv_bfloat16* k_append; __nv_bfloat16* v_append;
+  // The sums may be those of a product whose input was normalised without its scale (RMSNorm with the
+  // division moved behind the product): norm_x [requests, norm_width] float32 are the rows before the
+  // norm; the kernel multiplies request r's sums by 1 / sqrt(mean(norm_x[r]^2) + norm_eps).  Null: no scale.
+  const float* norm_x; int norm_width; float norm_eps;
 };
 
 __device__ __forceinline__ void dec_cp_async16(void* smem, const void* gmem) {
@@ -335,6 +339,8 @@ attention_decode_mma_kernel(const DecodeParams p) {
   float* wO = (float*)sK;                             // [4][16][HD]  (the keys' space, once they are done with)
   float* wm = wO + 4 * 16 * HD;                       // [4][16]
   float* wl = wm + 64;                                // [4][16]
+  __shared__ float s_norm[DEC_THREADS / 32];
+  float inv_rms = 1.0f;                                // FUSED with norm_x: what the sums are multiplied by
 
   pdl_launch_dependents();
   if constexpr (CLUSTER) cluster_arrive();             // "this CTA runs": awaited before anyone writes into its shared memory
@@ -411,6 +417,20 @@ attention_decode_mma_kernel(const DecodeParams p) {
     }
     cp_async_commit();
     if (first) { ATTN_STAMP(1); pdl_wait(); SPROUT_TL_WAITED(0); ATTN_STAMP(2); }    // the first pass's keys and values are on their way
+    if (FUSED && first && p.norm_x) {
+      // the row's scale: every thread adds a share of the squares, the warps meet in shared memory
+      const float* xr = p.norm_x + (size_t)r * p.norm_width;
+      float ss = 0.f;
+      for (int i = tid; i < p.norm_width; i += DEC_THREADS) { const float v = __ldcg(xr + i); ss += v * v; }
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+      if (lane == 0) s_norm[warp] = ss;
+      __syncthreads();
+      float total = 0.f;
+#pragma unroll
+      for (int w2 = 0; w2 < DEC_THREADS / 32; w2++) total += s_norm[w2];
+      inv_rms = 1.0f / sqrtf(total / (float)p.norm_width + p.norm_eps);
+    }
     if (!FUSED && first) {
       for (int idx = tid; idx < 16 * CHUNKS; idx += DEC_THREADS) {
         const int row = idx / CHUNKS, c = idx % CHUNKS;
@@ -434,8 +454,8 @@ attention_decode_mma_kernel(const DecodeParams p) {
         const bool turned = rotate && d < rot_half;
         const int e0 = d < rot_half ? (p.interleaved ? 2 * d : d) : p.rotary_dim + 2 * (d - rot_half);
         const int e1 = d < rot_half ? (p.interleaved ? 2 * d + 1 : d + rot_half) : e0 + 1;
-        const float a = sums[row * HD + e0] + (bias ? bias[row * HD + e0] : 0.f);
-        const float b = sums[row * HD + e1] + (bias ? bias[row * HD + e1] : 0.f);
+        const float a = sums[row * HD + e0] * inv_rms + (bias ? bias[row * HD + e0] : 0.f);
+        const float b = sums[row * HD + e1] * inv_rms + (bias ? bias[row * HD + e1] : 0.f);
         const float c = turned ? p.cos_table[(size_t)safe * rot_half + d] : 1.f, sn = turned ? p.sin_table[(size_t)safe * rot_half + d] : 0.f;
         sQ[row * STRIDE + e0] = __float2bfloat16_rn(a * c - b * sn);
         sQ[row * STRIDE + e1] = __float2bfloat16_rn(b * c + a * sn);
@@ -500,7 +520,7 @@ attention_decode_mma_kernel(const DecodeParams p) {
         const bool turned = rotate && d < rot_half;
         const int e0 = d < rot_half ? (p.interleaved ? 2 * d : d) : p.rotary_dim + 2 * (d - rot_half);
         const int e1 = d < rot_half ? (p.interleaved ? 2 * d + 1 : d + rot_half) : e0 + 1;
-        const float a = k_acc[e0] + (k_bias ? k_bias[e0] : 0.f), b = k_acc[e1] + (k_bias ? k_bias[e1] : 0.f);
+        const float a = k_acc[e0] * inv_rms + (k_bias ? k_bias[e0] : 0.f), b = k_acc[e1] * inv_rms + (k_bias ? k_bias[e1] : 0.f);
         k_acc[e0] = 0.f; k_acc[e1] = 0.f;
         const float c = turned ? p.cos_table[(size_t)safe * rot_half + d] : 1.f, sn = turned ? p.sin_table[(size_t)safe * rot_half + d] : 0.f;
         const __nv_bfloat16 lo = __float2bfloat16_rn(a * c - b * sn), hi = __float2bfloat16_rn(b * c + a * sn);
@@ -508,7 +528,7 @@ attention_decode_mma_kernel(const DecodeParams p) {
         if (page_ok) { p.k_append[dst + e0] = lo; p.k_append[dst + e1] = hi; }
       }
       for (int d = tid; d < HD; d += DEC_THREADS) {
-        const __nv_bfloat16 v = __float2bfloat16_rn(v_acc[d] + (v_bias ? v_bias[d] : 0.f));
+        const __nv_bfloat16 v = __float2bfloat16_rn(v_acc[d] * inv_rms + (v_bias ? v_bias[d] : 0.f));
         v_acc[d] = 0.f;
         sV[row * STRIDE + d] = v;
         if (page_ok) p.v_append[dst + d] = v;
@@ -1018,7 +1038,8 @@ SPROUT_API long long sprout_attention_decode_scratch_floats(int requests, int he
   return (long long)requests * heads * splits * (head_dim + 2);
 }
 
-struct FusedTail { float* acc; const float* bias; const float* cos_table; const float* sin_table; int max_positions; int rotary_dim, interleaved; };
+struct FusedTail { float* acc; const float* bias; const float* cos_table; const float* sin_table; int max_positions; int rotary_dim, interleaved;
+                   const float* norm_x; int norm_width; float norm_eps; };
 
 static int decode_launch(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                          const int* block_table, int table_stride, const int* context_lens, void* out, int out_stride,
@@ -1051,6 +1072,7 @@ static int decode_launch(const void* q, int q_stride, const void* k_cache, const
   p.acc = nullptr; p.bias = nullptr; p.cos_table = nullptr; p.sin_table = nullptr; p.max_positions = 0;
   p.rotary_dim = head_dim; p.interleaved = 0;
   p.k_append = nullptr; p.v_append = nullptr;
+  p.norm_x = nullptr; p.norm_width = 0; p.norm_eps = 0.f;
   const bool fused = fused_early;
   if (fused) {
     SPROUT_REQUIRE(extra->acc && head_dim <= 128 && (splits <= 8 || scratch), "attention_decode_fused: needs the sums, head_dim <= 128 and, "
@@ -1061,6 +1083,8 @@ static int decode_launch(const void* q, int q_stride, const void* k_cache, const
     SPROUT_REQUIRE(extra->rotary_dim >= 0 && extra->rotary_dim % 2 == 0 && extra->rotary_dim <= head_dim,
                    "attention_decode_fused: rotary_dim must be even and at most head_dim (got %d of %d)", extra->rotary_dim, head_dim);
     p.rotary_dim = extra->rotary_dim; p.interleaved = extra->interleaved ? 1 : 0;
+    SPROUT_REQUIRE(!extra->norm_x || (extra->norm_width > 0 && extra->norm_eps > 0.f), "attention_decode_fused: the norm's width and eps must be positive");
+    p.norm_x = extra->norm_x; p.norm_width = extra->norm_width; p.norm_eps = extra->norm_eps;
     p.k_append = (__nv_bfloat16*)k_cache; p.v_append = (__nv_bfloat16*)v_cache;
   }
   const int group = heads / kv_heads;
@@ -1149,9 +1173,10 @@ SPROUT_API int sprout_attention_decode_fused(float* acc, const float* bias, cons
                                              int max_positions, int rotary_dim, int interleaved, void* k_cache, void* v_cache, const int* block_table,
                                              int table_stride, const int* context_lens, void* out, int out_stride,
                                              float* scratch, int requests, int heads, int kv_heads, int head_dim,
-                                             int page_tokens, int num_pages, int split_keys, int splits, int* status,
+                                             int page_tokens, int num_pages, int split_keys, int splits,
+                                             const float* norm_x, int norm_width, float norm_eps, int* status,
                                              cudaStream_t stream) {
-  FusedTail extra{acc, bias, cos_table, sin_table, max_positions, rotary_dim, interleaved};
+  FusedTail extra{acc, bias, cos_table, sin_table, max_positions, rotary_dim, interleaved, norm_x, norm_width, norm_eps};
   return decode_launch(nullptr, 0, k_cache, v_cache, block_table, table_stride, context_lens, out, out_stride, scratch,
                        requests, heads, kv_heads, head_dim, page_tokens, num_pages, split_keys, splits, status, stream, &extra);
 }

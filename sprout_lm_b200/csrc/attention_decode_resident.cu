@@ -46,6 +46,9 @@ struct ResidentParams {
   // fused projection tail: float32 sums [requests, (heads + 2 kv_heads) * head_dim] of the q/k/v
   // product for each request's new token (position context_lens - 1), their bias, the rotation
   float* acc; const float* bias; const float* cos_table; const float* sin_table; int max_positions, rotary_dim, interleaved;
+  // sums of a product whose normalised input went without its scale: rows before the norm [requests, norm_width];
+  // request r's sums are multiplied by 1 / sqrt(mean(norm_x[r]^2) + norm_eps).  Null: no scale.
+  const float* norm_x; int norm_width; float norm_eps;
 };
 
 __device__ __forceinline__ void res_ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -92,6 +95,7 @@ attention_decode_resident_kernel(const __grid_constant__ CUtensorMap map_k, cons
   float* wl = wm + RES_WARPS * 16;                           // [8][16] sums
   uint64_t* bars = (uint64_t*)(wl + RES_WARPS * 16);         // [RES_MAX_CHUNKS]
   __shared__ int s_failed;
+  __shared__ float s_norm[RES_WARPS];
 
   pdl_launch_dependents();
   SPROUT_TL_ENTRY(0);
@@ -145,6 +149,20 @@ attention_decode_resident_kernel(const __grid_constant__ CUtensorMap map_k, cons
 
   // ---- the new token: its query rows, and (fused) its key and value
   const bool rotate = FUSED && p.cos_table != nullptr;
+  float inv_rms = 1.0f;
+  if (FUSED && p.norm_x) {
+    const float* xr = p.norm_x + (size_t)r * p.norm_width;
+    float ss = 0.f;
+    for (int i = tid; i < p.norm_width; i += RES_THREADS) { const float v = __ldcg(xr + i); ss += v * v; }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+    if (lane == 0) s_norm[warp] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w2 = 0; w2 < RES_WARPS; w2++) total += s_norm[w2];
+    inv_rms = 1.0f / sqrtf(total / (float)p.norm_width + p.norm_eps);
+  }
   if (FUSED) {
     if (rotate && pos >= p.max_positions) { if (tid == 0) atomicOr(p.status, SPROUT_STATUS_BAD_POSITION); }
     const int safe = min(pos, max(p.max_positions - 1, 0));
@@ -157,8 +175,8 @@ attention_decode_resident_kernel(const __grid_constant__ CUtensorMap map_k, cons
       const bool turned = rotate && d < rot_half;
       const int e0 = d < rot_half ? (p.interleaved ? 2 * d : d) : p.rotary_dim + 2 * (d - rot_half);
       const int e1 = d < rot_half ? (p.interleaved ? 2 * d + 1 : d + rot_half) : e0 + 1;
-      const float a = sums[row * HD + e0] + (bias ? bias[row * HD + e0] : 0.f);
-      const float b = sums[row * HD + e1] + (bias ? bias[row * HD + e1] : 0.f);
+      const float a = sums[row * HD + e0] * inv_rms + (bias ? bias[row * HD + e0] : 0.f);
+      const float b = sums[row * HD + e1] * inv_rms + (bias ? bias[row * HD + e1] : 0.f);
       const float c = turned ? p.cos_table[(size_t)safe * rot_half + d] : 1.f, sn = turned ? p.sin_table[(size_t)safe * rot_half + d] : 0.f;
       sQ[row * STRIDE + e0] = __float2bfloat16_rn(a * c - b * sn);
       sQ[row * STRIDE + e1] = __float2bfloat16_rn(b * c + a * sn);
@@ -199,7 +217,7 @@ attention_decode_resident_kernel(const __grid_constant__ CUtensorMap map_k, cons
         const bool turned = rotate && d < rot_half;
         const int e0 = d < rot_half ? (p.interleaved ? 2 * d : d) : p.rotary_dim + 2 * (d - rot_half);
         const int e1 = d < rot_half ? (p.interleaved ? 2 * d + 1 : d + rot_half) : e0 + 1;
-        const float a = k_acc[e0] + (k_bias ? k_bias[e0] : 0.f), b = k_acc[e1] + (k_bias ? k_bias[e1] : 0.f);
+        const float a = k_acc[e0] * inv_rms + (k_bias ? k_bias[e0] : 0.f), b = k_acc[e1] * inv_rms + (k_bias ? k_bias[e1] : 0.f);
         k_acc[e0] = 0.f; k_acc[e1] = 0.f;
         const float c = turned ? p.cos_table[(size_t)safe * rot_half + d] : 1.f, sn = turned ? p.sin_table[(size_t)safe * rot_half + d] : 0.f;
         const __nv_bfloat16 lo = __float2bfloat16_rn(a * c - b * sn), hi = __float2bfloat16_rn(b * c + a * sn);
@@ -208,7 +226,7 @@ attention_decode_resident_kernel(const __grid_constant__ CUtensorMap map_k, cons
         if (page_ok) { p.k_cache[dst + e0] = lo; p.k_cache[dst + e1] = hi; }
       }
       for (int d = tid; d < HD; d += RES_THREADS) {
-        const __nv_bfloat16 v = __float2bfloat16_rn(v_acc[d] + (v_bias ? v_bias[d] : 0.f));
+        const __nv_bfloat16 v = __float2bfloat16_rn(v_acc[d] * inv_rms + (v_bias ? v_bias[d] : 0.f));
         v_acc[d] = 0.f;
         *(__nv_bfloat16*)(sV + res_offset<HD>(pos, d >> 3, p.page_shift) + (d & 7) * 2) = v;
         if (page_ok) p.v_cache[dst + d] = v;
@@ -409,7 +427,7 @@ SPROUT_API int sprout_attention_decode_resident(float* acc, const float* bias, c
                                                 void* k_cache, void* v_cache, const int* block_table, int table_stride,
                                                 const int* context_lens, void* out, int out_stride, int requests, int heads,
                                                 int kv_heads, int head_dim, int page_tokens, int num_pages, int cap_keys,
-                                                int* status, cudaStream_t stream) {
+                                                const float* norm_x, int norm_width, float norm_eps, int* status, cudaStream_t stream) {
   SPROUT_REQUIRE(requests > 0 && requests <= 65535 && heads > 0 && kv_heads > 0 && num_pages > 0, "attention_decode_resident: sizes must be positive");
   const int cap_max = sprout_attention_decode_resident_cap(heads, kv_heads, head_dim, page_tokens);
   SPROUT_REQUIRE(cap_max > 0, "attention_decode_resident: takes head_dim 64 or 128, pages of 8, 16, 32, 64 or 128 tokens and up to 16 "
@@ -432,6 +450,8 @@ SPROUT_API int sprout_attention_decode_resident(float* acc, const float* bias, c
   p.status = status;
   p.acc = acc; p.bias = bias; p.cos_table = cos_table; p.sin_table = sin_table; p.max_positions = max_positions;
   p.rotary_dim = cos_table ? rotary_dim : 0; p.interleaved = interleaved ? 1 : 0;
+  SPROUT_REQUIRE(!norm_x || (acc && norm_width > 0 && norm_eps > 0.f), "attention_decode_resident: a scale needs the sums, a width and a positive eps");
+  p.norm_x = norm_x; p.norm_width = norm_width; p.norm_eps = norm_eps;
   CUtensorMap map_k, map_v;
   if (tensor_map(k_cache, (int)cache_rows, head_dim, head_dim, page_tokens, &map_k)) return 1;
   if (tensor_map(v_cache, (int)cache_rows, head_dim, head_dim, page_tokens, &map_v)) return 1;

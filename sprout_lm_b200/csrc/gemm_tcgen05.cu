@@ -51,6 +51,9 @@ struct Params {
   int ldo;
   int k_blocks_per_split;
   int* status;
+  // weights on M only: the tokens' operand made in the kernel instead of copied: bfloat16(x * gain) of the
+  // float32 rows x [M, K] (row stride ldx), written by the epilogue warps into the stages' token tiles
+  const float* x32; const float* gain; int ldx;
 };
 
 // PAIR: two CTAs share a 256 x BN tile; each holds its own 128 rows of A and half of B's rows.
@@ -130,7 +133,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
   if (tl_slot >= 0) SPROUT_TL_ENTRY(tl_slot);
 #endif
   if (threadIdx.x == 0) {
-    for (int s = 0; s < L::STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < L::STAGES; s++) { mbar_init(&full_bar[s], (SWAP && p.x32) ? 2 : 1); mbar_init(&empty_bar[s], 1); }
     for (int a = 0; a < 2; a++) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], PAIR ? 16 : 8); }
     mbar_init(epi_bar, 8);
     *abort_flag = 0;
@@ -169,7 +172,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     bool ok = true;
     // pairs: both CTAs' copies count on the first CTA's barrier, which expects both CTAs' bytes
     const uint32_t count_base = PAIR ? cluster_map_shared(full_base, 0) : full_base;
-    constexpr uint32_t STAGE_TX = (PAIR ? 2 : 1) * (L::A_BYTES + L::B_BYTES);
+    const bool made_here = SWAP && p.x32 != nullptr;          // the token tiles are written by the epilogue warps
+    const uint32_t STAGE_TX = made_here ? (uint32_t)L::A_BYTES : (uint32_t)((PAIR ? 2 : 1) * (L::A_BYTES + L::B_BYTES));
     auto copy = [&](uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
       if (PAIR) tma_load_2d_pair(dst, map, bar, x, y); else tma_load_2d_addr(dst, map, bar, x, y);
     };
@@ -196,7 +200,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
           if (rank == 0) mbar_expect_tx_addr(full_base + 8 * s, STAGE_TX);
           copy(stage_addr + W_OFF, weight_map, count_addr, x, weight_row);
         }
-        copy(stage_addr + X_OFF, act_map, count_addr, x, act_row);
+        if (!made_here) copy(stage_addr + X_OFF, act_map, count_addr, x, act_row);
         issued = it + 1;
         if (++s == L::STAGES) { s = 0; parity ^= 1; stage_addr = smem_base; } else stage_addr += L::STAGE_BYTES;
       }
@@ -264,6 +268,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
       epi_phase ^= 1;
       return (bool)__shfl_sync(0xffffffffu, met, 0);
     };
+    if (SWAP && p.x32) {
+      // The tokens' operand, made here: for every k-block of this CTA's (one) work item the tile
+      // [BN tokens, 64 elements] = bfloat16(x * gain), in the layout the 128-byte swizzle gives a
+      // copied tile (16-byte chunk c of row t at chunk c ^ (t & 7)); rows and columns beyond the
+      // matrix are zero.  The launch has checked that the item's k-blocks fit the ring.
+      const Work k = work_at(first_work);
+      const int et = (int)threadIdx.x - 64;                    // 0..255 among the epilogue warps
+      if (first_work < total_work) {
+        for (int i = 0; i < k.num_kb; i++) {
+          uint8_t* tile = smem + i * L::STAGE_BYTES + L::A_BYTES;
+          const int k0 = (k.kb_begin + i) * BLOCK_K;
+          for (int idx = et; idx < BN * 8; idx += 256) {
+            const int t = idx >> 3, c = idx & 7, m = k.col0 + t, kk = k0 + c * 8;
+            uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+            if (m < p.M && kk < p.K) {                          // K is a multiple of 8: a chunk lies inside or outside
+              const float4 a = __ldcg((const float4*)(p.x32 + (size_t)m * p.ldx + kk)), b = __ldcg((const float4*)(p.x32 + (size_t)m * p.ldx + kk) + 1);
+              const float4 ga = *(const float4*)(p.gain + kk), gb = *((const float4*)(p.gain + kk) + 1);
+              __nv_bfloat162 h0 = __floats2bfloat162_rn(a.x * ga.x, a.y * ga.y), h1 = __floats2bfloat162_rn(a.z * ga.z, a.w * ga.w);
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(b.x * gb.x, b.y * gb.y), h3 = __floats2bfloat162_rn(b.z * gb.z, b.w * gb.w);
+              packed = make_uint4(*(uint32_t*)&h0, *(uint32_t*)&h1, *(uint32_t*)&h2, *(uint32_t*)&h3);
+            }
+            *(uint4*)(tile + t * 128 + ((c ^ (t & 7)) << 4)) = packed;
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          if (!epi_sync()) break;                              // all eight warps have written their chunks
+          if (issuer) mbar_arrive(&full_bar[i]);
+        }
+      }
+    }
     // the accumulator goes back to the MMA issuer: of a pair's second CTA, to the first CTA's barrier
     auto release_accumulator = [&](int acc) {
       if (PAIR && rank == 1) mbar_arrive_cluster(cluster_map_shared(smem_u32(&acc_empty[acc]), 0));
@@ -532,6 +565,7 @@ SPROUT_API int sprout_gemm_bf16(const void* A, const void* W, const float* bias,
   p.bias = bias; p.out = out; p.out_is_f32 = out_dtype == SPROUT_F32;
   p.epilogue = swiglu ? EPI_SWIGLU : residual ? (split_k > 1 ? EPI_RESIDUAL_ATOMIC : EPI_RESIDUAL) : EPI_STORE;
   p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.status = status;
+  p.x32 = nullptr; p.gain = nullptr; p.ldx = 0;
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
   if (split_k > total_kb) split_k = total_kb;
   p.k_blocks_per_split = (total_kb + split_k - 1) / split_k;
@@ -603,6 +637,67 @@ SPROUT_API int sprout_gemm_bf16(const void* A, const void* W, const float* bias,
     case 192: return launch<192, false>(map_a, map_w, map_out, p, (int)work, stream);
     default: return launch<128, false>(map_a, map_w, map_out, p, (int)work, stream);
   }
+}
+
+// out [M, N] float32 (row stride ldo) += bfloat16(x * gain) W^T for up to 256 tokens: the product of a
+// normalised input without its scale.  x: float32 [M, K] (row stride ldx), the rows before
+// normalisation; gain: float32 [K].  The consumer multiplies token m's sums by 1 / rms(x[m]) (the
+// decode attention kernels do, with the bias and the rotation), which is the RMSNorm's arithmetic
+// with the division moved behind the product.  Weights on M, K split among CTAs (atomic adds); the
+// tokens' tiles are converted inside the kernel, so no kernel stands between the residual stream
+// and this product.  Every CTA has one work item whose k-blocks fit the ring, or the call is refused.
+SPROUT_API int sprout_gemm_bf16_unscaled(const float* x, int ldx, const float* gain, const void* W, float* out, int M, int N, int K,
+                                         int ldo, int split_k, int* status, cudaStream_t stream) {
+  SPROUT_REQUIRE(M > 0 && M <= 256 && N > 0 && K > 0, "gemm_bf16_unscaled: 1..256 tokens, positive sizes (M=%d N=%d K=%d)", M, N, K);
+  SPROUT_REQUIRE(x && gain && W && out && status, "gemm_bf16_unscaled: null pointer");
+  SPROUT_REQUIRE(K % 8 == 0 && ldx % 4 == 0 && ldx >= K && ldo >= N, "gemm_bf16_unscaled: K (%d) must be a multiple of 8, the rows of x (%d) of 4", K, ldx);
+  SPROUT_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)gain & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_bf16_unscaled: operands must be 16-byte aligned");
+  Params p;
+  p.bias = nullptr; p.out = out; p.out_is_f32 = 1; p.epilogue = EPI_RESIDUAL_ATOMIC;
+  p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.status = status;
+  p.x32 = x; p.gain = gain; p.ldx = ldx;
+  const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+  if (split_k < 1) split_k = 1;
+  if (split_k > total_kb) split_k = total_kb;
+  p.k_blocks_per_split = (total_kb + split_k - 1) / split_k;
+  split_k = (total_kb + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
+  const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  const long long work = (long long)((N + BLOCK_M - 1) / BLOCK_M) * ((M + bn - 1) / bn) * split_k;
+  CUtensorMap map_w;
+  if (tensor_map(W, N, K, K, BLOCK_M, &map_w)) return 1;
+  int stages = 0;
+  switch (bn) {
+    case 16: stages = Layout<16>::STAGES; break;
+    case 32: stages = Layout<32>::STAGES; break;
+    case 64: stages = Layout<64>::STAGES; break;
+    case 128: stages = Layout<128>::STAGES; break;
+    default: stages = Layout<256>::STAGES; break;
+  }
+  SPROUT_REQUIRE(work <= sm_count() && p.k_blocks_per_split <= stages,
+                 "gemm_bf16_unscaled: %lld work items for %d SMs, %d k-blocks a CTA for a ring of %d: split K further or use the separate norm",
+                 work, sm_count(), p.k_blocks_per_split, stages);
+  switch (bn) {
+    case 16: return launch<16, true>(map_w, map_w, map_w, p, (int)work, stream);
+    case 32: return launch<32, true>(map_w, map_w, map_w, p, (int)work, stream);
+    case 64: return launch<64, true>(map_w, map_w, map_w, p, (int)work, stream);
+    case 128: return launch<128, true>(map_w, map_w, map_w, p, (int)work, stream);
+    default: return launch<256, true>(map_w, map_w, map_w, p, (int)work, stream);
+  }
+}
+
+// 1 when sprout_gemm_bf16_unscaled takes these sizes with this K split on this device.
+SPROUT_API int sprout_gemm_bf16_unscaled_supported(int M, int N, int K, int split_k) {
+  if (M <= 0 || M > 256 || N <= 0 || K <= 0 || K % 8) return 0;
+  const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+  if (split_k < 1) split_k = 1;
+  if (split_k > total_kb) split_k = total_kb;
+  const int per = (total_kb + split_k - 1) / split_k;
+  split_k = (total_kb + per - 1) / per;
+  const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  const long long work = (long long)((N + BLOCK_M - 1) / BLOCK_M) * ((M + bn - 1) / bn) * split_k;
+  const int stages = bn == 16 ? Layout<16>::STAGES : bn == 32 ? Layout<32>::STAGES : bn == 64 ? Layout<64>::STAGES
+                   : bn == 128 ? Layout<128>::STAGES : Layout<256>::STAGES;
+  return work <= sm_count() && per <= stages ? 1 : 0;
 }
 
 SPROUT_TL_READER(gemm_tcgen05)

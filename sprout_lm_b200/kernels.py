@@ -39,12 +39,13 @@ _SIGNATURES = {
     "sprout_advance_decode": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
     "sprout_feed_tokens": [_P, _P, _P, _I, _I, _I, _P],
     "sprout_attention_decode": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
-    "sprout_attention_decode_fused": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
-    "sprout_attention_decode_resident": [_P, _P, _P, _P, _I, _I, _I, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_attention_decode_fused": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _F, _P, _P],
+    "sprout_attention_decode_resident": [_P, _P, _P, _P, _I, _I, _I, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _F, _P, _P],
     "sprout_attention_decode_resident_cap": [_I, _I, _I, _I],
     "sprout_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, ctypes.c_longlong, _P, _P, _P],
     "sprout_attention_prefill_tc_supported": [_I, _I, _I],
     "sprout_gemm_bf16": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_gemm_bf16_unscaled": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "sprout_ffn_decode": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _P],
     "sprout_ffn_decode_supported": [_I, _I, _I],
     "sprout_wait_probe": [_P, _P],
@@ -302,6 +303,31 @@ def gemm_bf16(a, weight, out, status, bias=None, residual=None, orientation=0, s
     _run("sprout_gemm_bf16", _ptr(a, "a"), _ptr(weight, "weight"), _ptr(bias, "bias", torch.float32, True),
          _ptr(out, "out"), _dtype_code(out.dtype), 2 if swiglu else (1 if residual is not None else 0), M, N, K, a.stride(0),
          out.stride(0), orientation, split_k, _ptr(status, "status", torch.int32), _stream())
+
+
+def gemm_bf16_unscaled_supported(tokens: int, out_features: int, in_features: int, split_k: int) -> bool:
+    lib = _lib or load_library()
+    lib.sprout_gemm_bf16_unscaled_supported.argtypes = [c_int, c_int, c_int, c_int]
+    lib.sprout_gemm_bf16_unscaled_supported.restype = c_int
+    return bool(lib.sprout_gemm_bf16_unscaled_supported(tokens, out_features, in_features, split_k))
+
+
+def gemm_bf16_unscaled(x, gain, weight, out, status, split_k=1):
+    """out (float32 [M, N]) += bfloat16(x * gain) @ weight.T for up to 256 tokens: the product of an
+    RMSNorm's output without the norm's scale (x float32 [M, K] are the rows before the norm, gain
+    its float32 gains).  Whoever reads the sums multiplies row m by 1 / sqrt(mean(x[m]^2) + eps)
+    (``attention_decode_fused`` / ``attention_decode_resident`` with ``norm_x``).  The tokens' tiles
+    are made inside the kernel: no kernel stands between the residual stream and the product."""
+    _rows_contiguous(x, "x")
+    _rows_contiguous(out, "out")
+    M, K = x.shape
+    N = weight.shape[0]
+    if x.dtype != torch.float32 or out.dtype != torch.float32 or weight.dtype != torch.bfloat16 or not weight.is_contiguous() \
+            or weight.shape[1] != K or tuple(out.shape) != (M, N) or gain.dtype != torch.float32 or gain.numel() != K:
+        raise KernelError(f"gemm_bf16_unscaled: shapes/dtypes do not fit: x {tuple(x.shape)} {x.dtype}, weight {tuple(weight.shape)} "
+                          f"{weight.dtype}, out {tuple(out.shape)} {out.dtype}")
+    _run("sprout_gemm_bf16_unscaled", _ptr(x, "x", torch.float32), x.stride(0), _ptr(gain, "gain", torch.float32), _ptr(weight, "weight"),
+         _ptr(out, "out", torch.float32), M, N, K, out.stride(0), split_k, _ptr(status, "status", torch.int32), _stream())
 
 
 def linear_decode_supported(tokens: int, out_features: int, in_features: int) -> bool:
@@ -591,8 +617,19 @@ def decode_attention_plan(requests: int, heads: int, kv_heads: int, head_dim: in
 RESIDENT_ENABLED = os.environ.get("SPROUT_RESIDENT_ATTENTION", "1") != "0"
 
 
+def _norm_scale(norm_x, requests: int, name: str):
+    """(pointer, width, eps) of the rows whose inverse RMS scales a request's sums; ``norm_x`` is
+    (x float32 [requests, width] contiguous, eps) or None."""
+    if norm_x is None:
+        return None, 0, 0.0
+    x, eps = norm_x
+    if x.dtype != torch.float32 or x.dim() != 2 or x.shape[0] != requests or not x.is_contiguous() or not eps > 0:
+        raise KernelError(f"{name}: the scale needs contiguous float32 rows [requests, width] and a positive eps")
+    return _ptr(x, "norm_x", torch.float32), x.shape[1], float(eps)
+
+
 def attention_decode_resident(k_cache, v_cache, block_table, context_lens, out, heads, kv_heads, head_dim, status, room,
-                              q=None, acc=None, bias=None, cos_table=None, sin_table=None, interleaved=False):
+                              q=None, acc=None, bias=None, cos_table=None, sin_table=None, interleaved=False, norm_x=None):
     """Decode attention with every request's whole context (at most ``room`` keys) in one CTA's
     shared memory, fetched by TMA before the wait for the step's earlier kernels.  With ``acc``
     (and ``bias``, rotation tables) the fused form of ``attention_decode_fused``: the new token's
@@ -628,7 +665,8 @@ def attention_decode_resident(k_cache, v_cache, block_table, context_lens, out, 
          1 if interleaved else 0, _ptr(q, "q", torch.bfloat16, True), q.stride(0) if q is not None else 0,
          _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"), _ptr(block_table, "block_table", torch.int32),
          block_table.stride(0), _ptr(context_lens, "context_lens", torch.int32), _ptr(out, "out"), out.stride(0),
-         R, heads, kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], int(room), _ptr(status, "status", torch.int32), _stream())
+         R, heads, kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], int(room),
+         *_norm_scale(norm_x if acc is not None else None, R, "attention_decode_resident"), _ptr(status, "status", torch.int32), _stream())
 
 
 def decode_fusable(requests: int, heads: int, kv_heads: int, head_dim: int, max_keys: int) -> bool:
@@ -638,14 +676,16 @@ def decode_fusable(requests: int, heads: int, kv_heads: int, head_dim: int, max_
 
 
 def attention_decode_fused(acc, bias, cos_table, sin_table, k_cache, v_cache, block_table, context_lens, out,
-                           heads, kv_heads, head_dim, status, live_keys=None, interleaved=False, scratch=None):
+                           heads, kv_heads, head_dim, status, live_keys=None, interleaved=False, scratch=None, norm_x=None):
     """Decode attention with the q/k/v projection's tail folded in.  ``acc`` holds, for each
     request's new token, the float32 sums [requests, (heads + 2 kv_heads) * head_dim] of a split-K
     product; the kernel adds ``bias``, rotates q and k by the position context_lens - 1 (tables
     [max_positions, rotary_dim / 2] and ``interleaved`` as for ``rope_append``; None: no rotation),
     appends k and v to the paged cache, attends over context_lens keys and leaves ``acc`` zeroed.
     ``out`` is bfloat16 [requests, heads * head_dim].  ``scratch``: float32 memory for the splits'
-    partial results where the plan merges through memory (allocated here when not given)."""
+    partial results where the plan merges through memory (allocated here when not given).
+    ``norm_x`` = (x, eps): the sums are those of ``gemm_bf16_unscaled`` (a normalised input without
+    its scale); request r's sums are multiplied by 1 / sqrt(mean(x[r]^2) + eps) first."""
     R = out.shape[0]
     width = (heads + 2 * kv_heads) * head_dim
     if acc.dtype != torch.float32 or tuple(acc.shape) != (R, width) or not acc.is_contiguous():
@@ -679,7 +719,8 @@ def attention_decode_fused(acc, bias, cos_table, sin_table, k_cache, v_cache, bl
          _ptr(block_table, "block_table", torch.int32), block_table.stride(0),
          _ptr(context_lens, "context_lens", torch.int32), _ptr(out, "out"), out.stride(0),
          _ptr(scratch, "scratch", torch.float32, True), R, heads, kv_heads, head_dim,
-         k_cache.shape[2], k_cache.shape[0], split_keys, splits, _ptr(status, "status", torch.int32), _stream())
+         k_cache.shape[2], k_cache.shape[0], split_keys, splits, *_norm_scale(norm_x, R, "attention_decode_fused"),
+         _ptr(status, "status", torch.int32), _stream())
 
 
 PREFILL_VARIANTS = {"auto": 0, "mma_sync": 1, "tcgen05": 2}

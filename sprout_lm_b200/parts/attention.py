@@ -7,12 +7,18 @@ sqrt(head_dim); the mask is causal; the output projection has no bias unless ``o
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import kernels
 from ..config.specs import PartSpec
 from .base import CacheSpec, CacheView, Part, TensorDecl, WeightSource, build_part, register_part
 from .linear import Linear
+
+# SPROUT_UNSCALED_PRODUCT=0: decode steps of more tokens than the small-batch kernels take run the norm
+# before attention as a kernel of its own (else its scale is applied inside the attention kernel)
+UNSCALED_PRODUCT = os.environ.get("SPROUT_UNSCALED_PRODUCT", "1") != "0"
 
 
 @register_part("mixer", "gqa_attention")
@@ -99,11 +105,18 @@ class PagedGQAttention(Part):
     def forward_with_norm(self, norm, x, ctx, cache: CacheView, state=None) -> bool:
         """The mixer with the norm before it folded into the q/k/v product, when the batch and the
         layer are small enough for that kernel; False means nothing was done."""
-        if self.qkv.weight.dtype != torch.bfloat16 or x.shape[0] > self.qkv.small_tokens \
-                or getattr(norm, "fused_kind", None) != "rmsnorm":
+        if self.qkv.weight.dtype != torch.bfloat16 or getattr(norm, "fused_kind", None) != "rmsnorm":
+            return False
+        if x.shape[0] > self.qkv.small_tokens and not (UNSCALED_PRODUCT and self._decodes_fused(x.shape[0], ctx, cache)):
             return False
         self.forward(None, x, ctx, cache, state, norm=norm)
         return True
+
+    def _decodes_fused(self, tokens, ctx, cache) -> bool:
+        """One token per request, the projection's tail inside the attention kernel: then that kernel
+        can also apply the norm's scale, and the q/k/v product takes the rows as they are."""
+        return tokens <= self.SPLIT_TOKENS and ctx.max_q_len == 1 and cache.write and \
+            kernels.decode_fusable(tokens, self.heads, self.kv_heads, self.head_dim, cache.block_table.shape[1] * cache.page_tokens)
 
     def forward(self, h, x, ctx, cache: CacheView, state=None, norm=None):
         cos, sin = self.tables if self.tables is not None else (None, None)
@@ -114,7 +127,10 @@ class PagedGQAttention(Part):
             # the memory bandwidth; split K so that every SM streams a share, accumulate in float32
             # and let the rotary kernel add the bias, rotate, convert and clear
             acc = self._workspace()[:tokens]
-            if norm is None or not self.qkv.accumulate_normed(norm, x, acc):
+            scale = None              # (rows before the norm, eps): the attention kernel applies the norm's scale
+            if norm is not None and tokens > self.qkv.small_tokens and self.qkv.accumulate_unscaled(norm, x, acc):
+                scale = (x, norm.eps)
+            elif norm is None or not self.qkv.accumulate_normed(norm, x, acc):
                 self.qkv.accumulate(h if h is not None else norm.forward(x), acc)
             attended = torch.empty((tokens, self.heads * self.head_dim), dtype=dtype, device=x.device)
             max_keys = cache.block_table.shape[1] * cache.page_tokens
@@ -128,13 +144,16 @@ class PagedGQAttention(Part):
                     kernels.attention_decode_resident(cache.k, cache.v, cache.block_table, ctx.context_lens, attended,
                                                       self.heads, self.kv_heads, self.head_dim, self.runtime.status, plan[1],
                                                       acc=acc, bias=self.qkv.bias, cos_table=cos, sin_table=sin,
-                                                      interleaved=self.interleaved)
+                                                      interleaved=self.interleaved, norm_x=scale)
                 else:
                     kernels.attention_decode_fused(acc, self.qkv.bias, cos, sin, cache.k, cache.v, cache.block_table,
                                                    ctx.context_lens, attended, self.heads, self.kv_heads, self.head_dim,
-                                                   self.runtime.status, live_keys=planned, interleaved=self.interleaved)
+                                                   self.runtime.status, live_keys=planned, interleaved=self.interleaved,
+                                                   norm_x=scale)
                 self.out.forward(attended, residual=x)
                 return
+            if scale is not None:
+                raise RuntimeError("attention: sums without the norm's scale can only go to the fused decode kernels")
             qkv = torch.empty((tokens, self.qkv.out_features), dtype=dtype, device=x.device)
             kernels.rope_append(qkv, ctx.positions, ctx.seq_of_token, cache.block_table, cos, sin, cache.k, cache.v,
                                 self.heads, self.kv_heads, self.head_dim, cache.page_tokens, cache.write,

@@ -75,6 +75,20 @@ class Linear:
         else:
             kernels.gemm_bf16(a, self.weight, acc, self.status, residual=acc, split_k=self.split_k(a.shape[0], True))
 
+    def accumulate_unscaled(self, norm, x: torch.Tensor, acc: torch.Tensor) -> bool:
+        """acc += bfloat16(x * gain) W^T: the product of the norm's output without its scale, for a
+        consumer that multiplies row m's sums by 1 / rms(x[m]) itself (decode attention does).  The
+        norm then costs no kernel of its own.  False (nothing done) when the sizes or the norm are not
+        the kernel's."""
+        tokens = x.shape[0]
+        if self.weight.dtype != torch.bfloat16 or getattr(norm, "fused_kind", None) != "rmsnorm" or tokens > 256:
+            return False
+        split = self.split_k(tokens, True)
+        if not kernels.gemm_bf16_unscaled_supported(tokens, self.out_features, self.in_features, split):
+            return False
+        kernels.gemm_bf16_unscaled(x, norm.gain, self.weight, acc, self.status, split_k=split)
+        return True
+
     def accumulate_normed(self, norm, x: torch.Tensor, acc: torch.Tensor) -> bool:
         """acc += rmsnorm(x) W^T in one kernel, for a few tokens of a small layer; False (nothing
         done) when the sizes or the norm are not the kernel's."""

@@ -399,6 +399,37 @@ def test_linear_decode_refuses_what_does_not_fit(status):
         kernels.linear_decode(rand(3584, 3584, dtype=torch.bfloat16), rand(8, 3584), status, a=rand(8, 3584, dtype=torch.bfloat16))
 
 
+@pytest.mark.parametrize("tokens,N,K,split", [(17, 1152, 896, 14), (64, 1152, 896, 14), (33, 256, 136, 3), (200, 384, 520, 9), (64, 1152, 896, 1)])
+def test_gemm_bf16_unscaled_is_the_normed_product_without_its_scale(status, tokens, N, K, split):
+    """out += bfloat16(x * gain) W^T with the tokens' tiles made inside the kernel: against float64
+    with that one rounding, on top of what the output held; and scaled by 1 / rms(x) it is the
+    product of the RMSNorm's output, to bfloat16's precision."""
+    from sprout_lm_b200 import kernels
+    if not kernels.gemm_bf16_unscaled_supported(tokens, N, K, split):
+        assert split == 1                                  # without a K split a CTA's k-blocks may not fit the ring
+        with pytest.raises(kernels.KernelError, match="gemm_bf16_unscaled"):
+            kernels.gemm_bf16_unscaled(rand(tokens, K), rand(K), rand(N, K, dtype=torch.bfloat16), rand(tokens, N), status, split_k=split)
+        return
+    x = rand(tokens, K, seed=1)
+    x[:, 5 % K] *= 6.0
+    gain = 1 + rand(K, scale=0.1, seed=2)
+    w = rand(N, K, dtype=torch.bfloat16, scale=0.05, seed=3)
+    before = rand(tokens, N, seed=4)
+    out = before.clone()
+    for _ in range(2):                                     # twice: the sums add up
+        kernels.gemm_bf16_unscaled(x, gain, w, out, status, split_k=split)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    h = (x.double() * gain.double()).float().to(torch.bfloat16).double()
+    want = before.double() + 2 * (h @ w.double().T)
+    assert (out.double() - want).abs().max().item() <= 2e-5 * max(1.0, want.abs().max().item())
+    eps = 1e-5
+    inv = 1.0 / torch.sqrt((x.double() ** 2).mean(dim=1, keepdim=True) + eps)
+    normed = (x.double() * inv * gain.double()).float().to(torch.bfloat16).double() @ w.double().T
+    scaled = (out.double() - before.double()) / 2 * inv
+    assert (scaled - normed).abs().max().item() <= 8e-3 * max(1e-3, normed.abs().max().item())
+
+
 def test_gemm_bf16_refuses_unaligned_rows(status):
     from sprout_lm_b200 import kernels
     a, w = rand(4, 20, dtype=torch.bfloat16), rand(8, 20, dtype=torch.bfloat16)
@@ -659,6 +690,48 @@ def test_attention_decode_resident(status, heads, kv_heads, head_dim, page, leng
     assert same(k2, case["k_cache"]) and same(v2, case["v_cache"])
     assert float(acc2.abs().max()) == 0.0                   # the sums are cleared
     assert (out.float() - want.float()).abs().max().item() <= 1.2e-2
+
+
+@pytest.mark.parametrize("kernel", ["split", "resident"])
+def test_decode_attention_applies_the_norms_scale_to_the_sums(status, kernel):
+    """The fused decode kernels with ``norm_x``: the float32 sums are those of a product whose
+    normalised input went without its scale; multiplied by 1 / rms of the request's row they must
+    give what the same kernel gives for sums that were scaled beforehand."""
+    from sprout_lm_b200 import kernels
+    from sprout_lm_b200.parts import Runtime
+    from sprout_lm_b200.parts.rope import HalfSplitRotary
+    heads, kv_heads, head_dim, page = 14, 2, 64, 16
+    lengths = [300, 129, 16, 640, 513, 1, 77, 33]
+    R = len(lengths)
+    case = build_paged_case(torch.bfloat16, heads, kv_heads, head_dim, page, lengths, [1] * R, seed=9)
+    width = (heads + 2 * kv_heads) * head_dim
+    g = torch.Generator().manual_seed(13)
+    sums = torch.randn(R, width, generator=g).to(DEV) * 3.0
+    bias = (torch.randn(width, generator=g) * 0.3).to(DEV)
+    x = (torch.randn(R, 200, generator=g) * torch.linspace(0.2, 4.0, R)[:, None]).to(DEV)     # rows of very different size
+    eps = 1e-5
+    inv = 1.0 / torch.sqrt((x.double() ** 2).mean(dim=1, keepdim=True) + eps)
+    cos, sin = HalfSplitRotary("", head_dim, 1e4, 1024).rotary_tables(Runtime(DEV, torch.bfloat16))
+    outs, caches = [], []
+    for scaled_before in (True, False):
+        acc = (sums.double() * inv).float() if scaled_before else sums.clone()
+        k, v = case["k_cache"].clone(), case["v_cache"].clone()
+        out = torch.empty(R, heads * head_dim, dtype=torch.bfloat16, device=DEV)
+        norm_x = None if scaled_before else (x, eps)
+        if kernel == "resident":
+            kernels.attention_decode_resident(k, v, case["table"], case["context_lens"], out, heads, kv_heads, head_dim, status, 640,
+                                              acc=acc, bias=bias, cos_table=cos, sin_table=sin, norm_x=norm_x)
+        else:
+            kernels.attention_decode_fused(acc, bias, cos, sin, k, v, case["table"], case["context_lens"], out, heads, kv_heads,
+                                           head_dim, status, norm_x=norm_x)
+        torch.cuda.synchronize()
+        assert float(acc.abs().max()) == 0.0
+        outs.append(out.float())
+        caches.append((k.float(), v.float()))
+    assert int(status.item()) == 0
+    assert (outs[0] - outs[1]).abs().max().item() <= 2e-2                     # the scale in float32, before or inside: a bfloat16 step apart at most
+    assert (caches[0][0] - caches[1][0]).abs().max().item() <= 4e-2 and (caches[0][1] - caches[1][1]).abs().max().item() <= 4e-2
+    assert (outs[0].abs().max().item()) > 0.1
 
 
 def test_attention_decode_resident_refuses_a_context_beyond_its_room(status):

@@ -321,7 +321,9 @@ def test_small_batches_take_the_light_kernels_and_agree_with_the_separate_ones(t
         results[mode] = np.concatenate(rows)
         assert np.abs(results[mode] - want).max() <= helpers.TOL["bfloat16"]
     layers = sizes["num_hidden_layers"]
-    assert launches["0"] - launches["1"] >= 3 * layers            # two norms and one product fewer per layer
+    # the feed-forward's norm and one of its products fewer per layer (the norm before attention costs neither form
+    # a launch in a decode step: its scale is applied inside the attention kernel)
+    assert launches["0"] - launches["1"] >= 2 * layers
     assert np.abs(results["1"] - results["0"]).max() <= helpers.TOL["bfloat16"]
 
 
