@@ -232,7 +232,7 @@ class GraphCache:
     """Captured decode steps, by (number of requests, table width, the parts' launch plans).
 
     A serving loop meets many keys: every batch size on the way up and down, a wider table every
-    ``page_multiple`` pages, another attention plan every few 128 keys of context; a round of 64
+    ``page_multiple`` pages, another attention plan every few 128 keys of context; a run of 64
     requests uses some fifty.  Each capture owns device memory (its activations and its [requests,
     vocabulary] float32 logits), pinned mirrors and a CUDA graph, so the cache is bounded: at most
     ``limit`` captures and ``budget_bytes`` of what they hold (``DecodeGraph.nbytes``, an estimate led
