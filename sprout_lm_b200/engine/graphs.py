@@ -233,7 +233,7 @@ class GraphCache:
 
     A serving loop meets many keys: every batch size on the way up and down, a wider table every
     ``page_multiple`` pages, another attention plan every few 128 keys of context; a run of 64
-    requests uses some fifty.  Each capture owns device memory (its activations and its [requests,
+    requests uses some thirty.  Each capture owns device memory (its activations and its [requests,
     vocabulary] float32 logits), pinned mirrors and a CUDA graph, so the cache is bounded: at most
     ``limit`` captures and ``budget_bytes`` of what they hold (``DecodeGraph.nbytes``, an estimate led
     by the logits; by default 1/24 of the device's memory).  Beyond either the least recently used
