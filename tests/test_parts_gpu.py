@@ -474,9 +474,13 @@ def register_toy_parts():
                 LayerSpec("pre_norm", "layers.1.", PartSpec("toy_running_mean", {"hidden_size": self.hidden_size}),
                           PartSpec("swiglu_mlp", {"hidden_size": self.hidden_size, "intermediate_size": self.intermediate_size}),
                           (norm("ln1"), norm("ln2"))),
+                LayerSpec("pre_norm", "layers.2.", attention,
+                          PartSpec("swiglu_mlp", {"hidden_size": self.hidden_size, "intermediate_size": self.intermediate_size}),
+                          (norm("ln1"), norm("ln2"))),
             )
-            # layer 0 runs twice; its second run reads the keys and values its first run cached
-            order = (LayerCall(0, 0), LayerCall(1, 1), LayerCall(0, 0, writes_cache=False))
+            # layer 0 runs twice; its second run reads the keys and values its first run cached; layer 2 (weights
+            # of its own) has no cache: its queries attend over what layer 0 cached
+            order = (LayerCall(0, 0), LayerCall(1, 1), LayerCall(0, 0, writes_cache=False), LayerCall(2, 0, writes_cache=False))
             return ModelSpec(
                 architecture=self.architecture, hidden_size=self.hidden_size, vocab_size=self.vocab_size,
                 max_positions=self.max_positions,
@@ -534,6 +538,14 @@ def toy_plain_logits(cfg, w, tokens):
     # layer 0 again: new queries from the current stream, but the keys and values cached by its first run
     x, _, q, _, _ = layer0(x)
     x = finish0(x, q, k0, v0)
+    # layer 2: its own weights, its queries over layer 0's cached keys and values, a dense feed-forward
+    p = "layers.2."
+    h = plain.rms_norm(x, w[p + "ln1.weight"], cfg.eps)
+    q = rotate(plain.linear(h, w[p + "q_proj.weight"], w[p + "q_proj.bias"]))
+    x = plain.residual_add(x, plain.linear(plain.causal_gqa_attention(q, k0, v0, heads, kv, hd), w[p + "o_proj.weight"]))
+    h2 = plain.rms_norm(x, w[p + "ln2.weight"], cfg.eps)
+    t = plain.swiglu(plain.linear(h2, w[p + "gate_proj.weight"]), plain.linear(h2, w[p + "up_proj.weight"]))
+    x = plain.residual_add(x, plain.linear(t, w[p + "down_proj.weight"]))
     return plain.linear(plain.rms_norm(x, w["final_ln.weight"], cfg.eps), w["head.weight"])
 
 
@@ -554,7 +566,7 @@ def test_toy_architecture_is_registered_built_and_stepped(toy):
     _, weights = plain.read_model_folder(folder)
     assert "layers.0.experts.3.weight" in weights and "layers.1.mean_proj.weight" in weights
     model = load_model(folder, dtype="float32")
-    assert [type(b.mixer).__name__ for b in model.blocks] == ["PagedGQAttention", "RunningMean"]
+    assert [type(b.mixer).__name__ for b in model.blocks] == ["PagedGQAttention", "RunningMean", "PagedGQAttention"]
     assert model.cache_specs()[1] is None and model.state_specs()[1].shape == (49,)
     rng = np.random.default_rng(0)
     requests = {f"t{i}": helpers.random_tokens(rng, n, config.vocab_size) for i, n in enumerate((9, 40, 23))}
