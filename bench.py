@@ -118,11 +118,15 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.samples)}
 
 
-def model_folder(layers: int, shape: str = "0.5b") -> Path:
-    """The random-weights model folder of the benchmark shape (written once per temporary folder)."""
+def model_folder(layers: int, shape: str = "0.5b", context: int = 0) -> Path:
+    """The random-weights model folder of the benchmark shape (written once per temporary folder);
+    ``context``: another context length than the shape's."""
     from sprout_lm_b200 import parse_config, write_random_model
     sizes = dict(SHAPES[shape], num_hidden_layers=layers)
     tag = "" if shape == "0.5b" else "_" + shape
+    if context and context != sizes["max_position_embeddings"]:
+        sizes["max_position_embeddings"] = context
+        tag += f"_C{context}"
     folder = Path(tempfile.gettempdir()) / f"sprout_lm_b200_bench_{os.getuid()}{tag}_L{layers}"
     config = parse_config({"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu", **sizes})
     marker = folder / "complete"
@@ -176,9 +180,13 @@ def timed_decode(runner, batch: int, prompt_len: int, steps: int, warmup: int, r
     chunk = max(1, 4096 // prompt_len)
     first = []
     for at in range(0, batch, chunk):
-        entries = [StepEntry(s, [int(t) for t in rng.integers(0, vocab, prompt_len)], [prompt_len - 1])
-                   for s in seqs[at:at + chunk]]
-        first += runner.step_and_sample(entries, [0.0] * len(entries), [0.0] * len(entries))
+        for begin in range(0, prompt_len, 4096):                 # long prompts in portions of 4,096 tokens
+            n = min(4096, prompt_len - begin)
+            last = begin + n == prompt_len
+            entries = [StepEntry(s, [int(t) for t in rng.integers(0, vocab, n)], [n - 1] if last else [])
+                       for s in seqs[at:at + chunk]]
+            sampled = runner.step_and_sample(entries, [0.0] * len(entries) if last else [], [0.0] * len(entries) if last else [])
+        first += sampled
     entries = [StepEntry(s, [t], [0]) for s, t in zip(seqs, first)]
     loop = runner.decode_loop(entries, [0.0] * batch, [0.0] * batch, max_steps=steps + warmup + 2)
     loop.run(max(warmup - 1, 0))                 # capture runs one more step
@@ -600,12 +608,19 @@ def run(args) -> dict:
         raise SystemExit("bench.py: the full line is measured at the 0.5b shape; give --only with another --shape")
     base = SHAPES[args.shape]
     layers = args.layers or base["num_hidden_layers"]
-    folder = model_folder(layers, args.shape)
+    batch, prompt_len, context = args.batch, 512, base["max_position_embeddings"]
+    if args.prompt_len != 512:
+        if args.only != "decode":
+            raise SystemExit("bench.py: --prompt-len goes with --only decode (the full line is measured at 512-token prompts)")
+        prompt_len = args.prompt_len
+        need = prompt_len + args.warmup + args.steps + 8
+        while context < need:                     # a longer context than the shape names: said in the line
+            context *= 2
+    folder = model_folder(layers, args.shape, context)
     model = load_model(folder, dtype="bfloat16", device="cuda:0")
     cfg = dict(base, num_hidden_layers=layers)
     peak = peaks()
     rng = np.random.default_rng(0)
-    batch, prompt_len, context = args.batch, 512, base["max_position_embeddings"]
     if prompt_len + args.warmup + args.steps + 8 > context:
         raise SystemExit(f"bench.py: {prompt_len}-token prompts and {args.warmup} + {args.steps} decode steps do not fit the "
                          f"{context}-token context of the benchmark configuration; use at most {context - prompt_len - args.warmup - 8} steps")
@@ -631,6 +646,9 @@ def run(args) -> dict:
         out = {"impl": "ours", "only": "decode", "shape": args.shape, "layers": layers, "batch": batch,
                "ms_per_step": round(main["ms_per_step"], 4), "launches_per_step": main["launches_per_step"],
                "gbs": round(step_bytes / (main["ms_per_step"] / 1000) / 1e9, 1)}
+        if prompt_len != 512:
+            out.update({"prompt_len": prompt_len, "context": context, "mb_per_step": round(step_bytes / 1e6, 1),
+                        "hbm_frac": round(step_bytes / (main["ms_per_step"] / 1000) / 1e9 / peak["hbm_gbs"], 3)})
         phases = kernels.ffn_decode_phase_stamps()       # from a build with SPROUT_BUILD_FLAGS=-DFFN_STAMPS
         if phases:
             out["ffn_decode_phases_us"] = {k: {n: round(v, 2) for n, v in d.items()} for k, d in phases.items()}
@@ -680,6 +698,7 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--prompt-len", type=int, default=512, help="with --only decode: tokens of every request's prompt (the context grows to hold it)")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate", "attention", "decode-attention", "gemm", "serve"], default="all",
                         help="measure one part only (for profiling captures); the JSON line then holds that part")

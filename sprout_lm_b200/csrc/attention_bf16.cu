@@ -323,8 +323,13 @@ __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.w
 template <typename T>
 __device__ __forceinline__ T* cluster_peer(T* mine, int rank) { return cg::this_cluster().map_shared_rank(mine, rank); }
 
-template <int HD, bool CLUSTER, bool FUSED>
-__global__ void __launch_bounds__(DEC_THREADS)
+// Head sizes up to 64 leave shared memory for five CTAs per SM, but the fused variant takes 128
+// registers: four CTAs per SM.  TIGHT (fused, splits through memory) holds the registers to what five
+// CTAs need; the launch takes it when it has more CTAs than four per SM (many requests, long
+// contexts: a launch planned for five per SM ran in two waves), and the variant with all its
+// registers otherwise (few CTAs: latency).
+template <int HD, bool CLUSTER, bool FUSED, bool TIGHT = false>
+__global__ void __launch_bounds__(DEC_THREADS, TIGHT ? 5 : 0)
 attention_decode_mma_kernel(const DecodeParams p) {
   constexpr int STRIDE = HD + 8, CHUNKS = HD / 8;
   extern __shared__ __align__(16) uint8_t dmm[];
@@ -372,12 +377,13 @@ attention_decode_mma_kernel(const DecodeParams p) {
   // is still in flight); what it brought from beyond the length is cleared once the length is
   // there.  Later passes know the length.
   int end = begin + p.split_keys;
+  int next_page = first_page;
   for (int base = begin; base < end; base += DEC_THREADS) {
     const bool first = base == begin;
     const int key = base + tid;
     long long off = -1;
     if (first || key < end) {
-      const int page = first ? first_page : table[key / p.page_tokens];
+      const int page = next_page;                      // read while the pass before was on its way
       if (page >= 0 && page < p.num_pages) off = (((long long)page * p.kv_heads + g) * p.page_tokens + key % p.page_tokens) * HD;
       else if (!first || key < len) atomicOr(p.status, SPROUT_STATUS_BAD_PAGE);
     }
@@ -416,6 +422,8 @@ attention_decode_mma_kernel(const DecodeParams p) {
       }
     }
     cp_async_commit();
+    // the next pass's page while this pass's rows are on their way (the block table was there before the step)
+    if (base + DEC_THREADS < begin + p.split_keys) next_page = table[min((key + DEC_THREADS) / p.page_tokens, p.table_stride - 1)];
     if (first) { ATTN_STAMP(1); pdl_wait(); SPROUT_TL_WAITED(0); ATTN_STAMP(2); }    // the first pass's keys and values are on their way
     if (FUSED && first && p.norm_x) {
       // the row's scale: every thread adds a share of the squares, the warps meet in shared memory
@@ -746,8 +754,41 @@ int launch_decode_mma(const DecodeParams& p, bool cluster, int requests, cudaStr
     cudaLaunchKernelEx(&config, attention_decode_mma_kernel<HD, true, FUSED>, p);
     return sprout_check_launch("attention_decode (tensor cores, cluster)");
   }
+  if constexpr (FUSED && HD <= 64) {
+    if ((long long)p.splits * p.kv_heads * requests > 4LL * sprout_sm_count()) {
+      static bool tight_configured = false;
+      if (!tight_configured) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false, true, true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        tight_configured = true;
+      }
+      sprout_launch(attention_decode_mma_kernel<HD, false, true, true>, grid, dim3(DEC_THREADS), smem, stream, p);
+      return sprout_check_launch("attention_decode (tensor cores, five CTAs per SM)");
+    }
+  }
   sprout_launch(attention_decode_mma_kernel<HD, false, FUSED>, grid, dim3(DEC_THREADS), smem, stream, p);
   return sprout_check_launch("attention_decode (tensor cores)");
+}
+
+// How many CTAs of the split-key decode kernel an SM holds at once (registers and shared memory), for
+// the plan of a launch: 0 for a head size the kernel does not take.
+template <int HD>
+int decode_mma_ctas_per_sm(bool fused) {
+  constexpr size_t smem = (size_t)(16 + 2 * DEC_THREADS) * (HD + 8) * 2 + (size_t)(16 * HD + 16 + 256) * 4 + DEC_THREADS * 8;
+  int count = 0;
+  cudaError_t err;
+  if (fused) {
+    constexpr bool TIGHT = HD <= 64;       // what a launch with many CTAs runs
+    if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false, true, TIGHT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false, true, TIGHT>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&count, attention_decode_mma_kernel<HD, false, true, TIGHT>, DEC_THREADS, smem);
+  } else {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false, false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&count, attention_decode_mma_kernel<HD, false, false>, DEC_THREADS, smem);
+  }
+  if (err != cudaSuccess) { cudaGetLastError(); return 0; }
+  return count;
 }
 
 // Merge the splits of one (request, head): grid (heads, requests), head_dim threads (rounded up to a warp).
@@ -1036,6 +1077,22 @@ int launch_prefill(const PrefillParams& p, int grid_x, cudaStream_t stream) {
 // Scratch floats that a decode call with `splits` splits needs: outputs and (max, sum) pairs.
 SPROUT_API long long sprout_attention_decode_scratch_floats(int requests, int heads, int head_dim, int splits) {
   return (long long)requests * heads * splits * (head_dim + 2);
+}
+
+// CTAs of the split-key decode kernel (the tensor-core one; fused: with the projection's tail) that
+// an SM of the current device holds at once, or 0 for a head size that kernel does not take.
+SPROUT_API int sprout_attention_decode_ctas_per_sm(int head_dim, int fused) {
+  switch (head_dim) {
+    case 16: return decode_mma_ctas_per_sm<16>(fused != 0);
+    case 32: return decode_mma_ctas_per_sm<32>(fused != 0);
+    case 48: return decode_mma_ctas_per_sm<48>(fused != 0);
+    case 64: return decode_mma_ctas_per_sm<64>(fused != 0);
+    case 80: return decode_mma_ctas_per_sm<80>(fused != 0);
+    case 96: return decode_mma_ctas_per_sm<96>(fused != 0);
+    case 112: return decode_mma_ctas_per_sm<112>(fused != 0);
+    case 128: return decode_mma_ctas_per_sm<128>(fused != 0);
+    default: return 0;
+  }
 }
 
 struct FusedTail { float* acc; const float* bias; const float* cos_table; const float* sin_table; int max_positions; int rotary_dim, interleaved;

@@ -71,6 +71,8 @@ def load_library(verbose: bool = True):
             lib.sprout_sample_scratch_bytes.argtypes = [c_int]
             lib.sprout_attention_decode_scratch_floats.restype = ctypes.c_longlong
             lib.sprout_attention_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
+            lib.sprout_attention_decode_ctas_per_sm.restype = c_int
+            lib.sprout_attention_decode_ctas_per_sm.argtypes = [c_int, c_int]
             for name, argtypes in _SIGNATURES.items():
                 fn = getattr(lib, name)
                 fn.argtypes = argtypes
@@ -524,13 +526,25 @@ def decode_split_plan(requests: int, kv_heads: int, max_keys: int, head_dim: int
     live = max_keys if live_keys is None else max(1, min(max_keys, live_keys))
     if sms is None:
         sms = sm_count() if torch.cuda.is_available() else 148      # host-side inspection without a device: a B200's count
-    return _decode_split_plan(requests * kv_heads, -(-max_keys // 128), -(-live // 128), head_dim, sms)
+    return _decode_split_plan(requests * kv_heads, -(-max_keys // 128), -(-live // 128), head_dim, sms, decode_ctas_per_sm(head_dim))
+
+
+@functools.lru_cache(maxsize=64)
+def decode_ctas_per_sm(head_dim: int) -> int:
+    """CTAs of the split-key decode kernel that an SM holds at once: the device's own answer for
+    the kernel as built (registers and shared memory), or, without a device, what its shared
+    memory and a bound of 5 by registers give on a B200."""
+    if torch.cuda.is_available() and head_dim % 16 == 0 and head_dim <= 128:
+        count = int(load_library().sprout_attention_decode_ctas_per_sm(head_dim, 1))
+        if count > 0:
+            return count
+    shared = (16 + 256) * (head_dim + 8) * 2 + (16 * head_dim + 16 + 256) * 4 + 128 * 8      # the tensor-core kernel's, per CTA
+    return max(1, min(5 if head_dim <= 64 else 16, (227 * 1024) // (shared + 1024)))
 
 
 @functools.lru_cache(maxsize=4096)
-def _decode_split_plan(pairs: int, total_passes: int, live_passes: int, head_dim: int, sms: int) -> tuple[int, int, bool]:
-    shared = (16 + 256) * (head_dim + 8) * 2 + (16 * head_dim + 16 + 256) * 4 + 128 * 8      # the tensor-core kernel's, per CTA
-    slots = sms * max(1, min(16, (227 * 1024) // (shared + 1024)))
+def _decode_split_plan(pairs: int, total_passes: int, live_passes: int, head_dim: int, sms: int, per_sm: int) -> tuple[int, int, bool]:
+    slots = sms * per_sm
     total_passes = max(1, total_passes)
     best, best_cost, last_splits = (128 * total_passes, 1, False), None, 0
     for passes in range(1, total_passes + 1):

@@ -18,6 +18,19 @@ def test_plan_covers_every_key(head_dim, kv_heads, requests):
             assert not (through_memory and splits == 1)             # nothing to merge
 
 
+def test_plan_counts_the_ctas_an_sm_really_holds():
+    """The plan's waves follow how many CTAs an SM holds: 128 (request, head) pairs over 32,768
+    keys take five splits where five CTAs fit an SM (640 CTAs, one wave of 740 places); with four
+    per SM that launch would run in two waves, and the plan is another."""
+    five = kernels._decode_split_plan(128, 256, 256, 64, 148, 5)
+    four = kernels._decode_split_plan(128, 256, 256, 64, 148, 4)
+    assert five == (6656, 5, True) and four != five
+    for split_keys, splits, _ in (five, four):
+        assert split_keys * splits >= 32768
+    # without a device the count is what shared memory and the kernel's register bound give on a B200
+    assert kernels.decode_ctas_per_sm.__wrapped__(64) == 5 and kernels.decode_ctas_per_sm.__wrapped__(128) == 2
+
+
 def test_plan_follows_the_batch_and_the_context():
     # a small batch with a short context: many short splits (latency)
     assert kernels.decode_split_plan(8, 2, 640, 64)[0] == 128

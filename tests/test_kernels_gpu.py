@@ -584,6 +584,8 @@ def test_attention_decode_split_keys(status, heads, kv_heads, head_dim, page, le
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page,lengths", DECODE_CASES[:6] + [
     (14, 2, 64, 16, [37 + 13 * i for i in range(70)]),        # a large batch: longer splits, few per request
     (4, 2, 64, 16, [6000, 1500]),                              # more than 8 splits: through memory too
+    (4, 2, 64, 16, [2900 + 2 * i for i in range(80)]),         # more CTAs than four per SM: the variant held to five per SM's registers
+    (6, 2, 32, 16, [5000 + 2 * i for i in range(60)]),
 ])
 def test_attention_decode_fused_projection_tail(status, heads, kv_heads, head_dim, page, lengths, rotate):
     """The decode kernel that also finishes the projection: the new token's q, k, v arrive as
@@ -619,6 +621,9 @@ def test_attention_decode_fused_projection_tail(status, heads, kv_heads, head_di
     assert kernels.decode_fusable(R, heads, kv_heads, head_dim, case["table"].shape[1] * page)
     if max(lengths) > 5000:
         assert kernels.decode_split_plan(R, kv_heads, case["table"].shape[1] * page, head_dim)[2]      # this case goes through memory
+    if R >= 60:
+        _, splits, through_memory = kernels.decode_split_plan(R, kv_heads, case["table"].shape[1] * page, head_dim)
+        assert through_memory and splits * kv_heads * R > 4 * kernels.sm_count()
     kernels.attention_decode_fused(acc2, bias, cos, sin, k2, v2, case["table"], case["context_lens"], got, heads,
                                    kv_heads, head_dim, status)
     assert torch.equal(k2, k1) and torch.equal(v2, v1)                 # the same append, bit for bit
