@@ -46,6 +46,14 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(smem)));
 }
+__device__ __forceinline__ void ldmatrix_x4_addr(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans_addr(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -323,28 +331,51 @@ __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.w
 template <typename T>
 __device__ __forceinline__ T* cluster_peer(T* mine, int rank) { return cg::this_cluster().map_shared_rank(mine, rank); }
 
+// Shared memory of the tensor-core decode kernel: the query tile (padded rows), 128 key and 128
+// value rows, a row offset per key, four floats for a norm's sums, and, for a launch in clusters,
+// what the splits send one another.  The key and value rows of head size 128, and of head size 64
+// where the splits go through memory (the launches that fill every SM: less shared memory per CTA
+// and 5 to 9 % more bytes per second at 8,192 and 32,768 keys), are swizzled; all others are padded
+// by 16 bytes (the cluster launches of head size 64, few CTAs on short contexts, are 1.5 % of a
+// decode step faster with plain addresses).
+template <int HD, bool CLUSTER>
+struct DecodeSmem {
+  static constexpr bool SWZ = HD == 128 || (HD == 64 && !CLUSTER);
+  static constexpr int STRIDE = SWZ ? HD : HD + 8;
+  static constexpr size_t BYTES = (size_t)16 * (HD + 8) * 2 + (size_t)2 * DEC_THREADS * STRIDE * 2 + (size_t)DEC_THREADS * 8 + 16
+                                + (CLUSTER ? (size_t)(8 * HD + 8) * 8 + 256 * 4 : 0);
+};
+
 // Head sizes up to 64 leave shared memory for five CTAs per SM, but the fused variant takes 128
 // registers: four CTAs per SM.  TIGHT (fused, splits through memory) holds the registers to what five
 // CTAs need; the launch takes it when it has more CTAs than four per SM (many requests, long
 // contexts: a launch planned for five per SM ran in two waves), and the variant with all its
 // registers otherwise (few CTAs: latency).
+#ifndef DEC_TIGHT_CTAS
+#define DEC_TIGHT_CTAS 5
+#endif
 template <int HD, bool CLUSTER, bool FUSED, bool TIGHT = false>
-__global__ void __launch_bounds__(DEC_THREADS, TIGHT ? 5 : 0)
+__global__ void __launch_bounds__(DEC_THREADS, TIGHT ? DEC_TIGHT_CTAS : (HD == 128 ? 3 : (HD == 64 && !FUSED && !CLUSTER ? 5 : 0)))
 attention_decode_mma_kernel(const DecodeParams p) {
-  constexpr int STRIDE = HD + 8, CHUNKS = HD / 8;
-  extern __shared__ __align__(16) uint8_t dmm[];
-  __nv_bfloat16* sQ = (__nv_bfloat16*)dmm;            // [16][STRIDE]
-  __nv_bfloat16* sK = sQ + 16 * STRIDE;               // [128][STRIDE]
+  // Key and value rows in shared memory: rows of 128 or 256 bytes (head sizes 64 and 128) lie side
+  // by side with their 16-byte pieces swizzled (piece c of row r at piece c ^ (r % 8): what ldmatrix
+  // reads of eight rows then lies in different banks); other head sizes pad each row by 16 bytes.
+  constexpr bool SWZ = DecodeSmem<HD, CLUSTER>::SWZ;
+  constexpr int STRIDE = DecodeSmem<HD, CLUSTER>::STRIDE, QSTRIDE = HD + 8, CHUNKS = HD / 8;
+  auto at = [](int row, int col) { return row * STRIDE + (SWZ ? ((((col >> 3) ^ (row & 7)) << 3) | (col & 7)) : col); };
+  extern __shared__ __align__(1024) uint8_t dmm[];    // swizzled rows start on multiples of their length
+  __nv_bfloat16* sQ = (__nv_bfloat16*)dmm;            // [16][QSTRIDE]
+  __nv_bfloat16* sK = sQ + 16 * QSTRIDE;              // [128][STRIDE]
   __nv_bfloat16* sV = sK + DEC_THREADS * STRIDE;      // [128][STRIDE]
   // What the splits of a cluster send one another: a CTA owns every count-th pair of (head, dim)
   // places and receives that pair's partial sums from all splits, and every split's maxima and sums.
-  float2* recv = (float2*)(sV + DEC_THREADS * STRIDE);     // [pairs owned][splits], at most 8 * HD + 8 pairs
+  long long* rows = (long long*)(sV + DEC_THREADS * STRIDE);   // [128]
+  float* s_norm = (float*)(rows + DEC_THREADS);       // [4]: the warps' sums of squares (no static shared memory: it would pad the dynamic part's alignment)
+  float2* recv = (float2*)(s_norm + 4);               // [pairs owned][splits], at most 8 * HD + 8 pairs (a cluster's launch only)
   float* recv_ml = (float*)(recv + 8 * HD + 8);       // [8 splits][16 rows][2]
-  long long* rows = (long long*)(recv_ml + 256);      // [128]
   float* wO = (float*)sK;                             // [4][16][HD]  (the keys' space, once they are done with)
   float* wm = wO + 4 * 16 * HD;                       // [4][16]
   float* wl = wm + 64;                                // [4][16]
-  __shared__ float s_norm[DEC_THREADS / 32];
   float inv_rms = 1.0f;                                // FUSED with norm_x: what the sums are multiplied by
 
   pdl_launch_dependents();
@@ -394,9 +425,9 @@ attention_decode_mma_kernel(const DecodeParams p) {
       // a thread keeps its 16-byte column and walks down the rows: neighbours in a warp copy
       // neighbouring pieces of a row, and nothing but the row's offset changes between copies
       constexpr int ROWS_AT_ONCE = DEC_THREADS / CHUNKS;
-      const int c8 = (tid % CHUNKS) * 8, r0 = tid / CHUNKS;
-      const uint32_t dk0 = (uint32_t)__cvta_generic_to_shared(sK + r0 * STRIDE + c8);
-      const uint32_t dv0 = (uint32_t)__cvta_generic_to_shared(sV + r0 * STRIDE + c8);
+      const int c8 = (tid % CHUNKS) * 8, r0 = tid / CHUNKS;      // the rows a thread walks share r0 % 8: one swizzled column
+      const uint32_t dk0 = (uint32_t)__cvta_generic_to_shared(sK + at(r0, c8));
+      const uint32_t dv0 = (uint32_t)__cvta_generic_to_shared(sV + at(r0, c8));
       const __nv_bfloat16* kg = p.k_cache + c8;
       const __nv_bfloat16* vg = p.v_cache + c8;
 #pragma unroll
@@ -415,8 +446,8 @@ attention_decode_mma_kernel(const DecodeParams p) {
       for (int idx = tid; idx < DEC_THREADS * CHUNKS; idx += DEC_THREADS) {
         const int row = idx / CHUNKS, c = idx % CHUNKS;
         const long long ro = rows[row];
-        __nv_bfloat16* dk = sK + row * STRIDE + c * 8;
-        __nv_bfloat16* dv = sV + row * STRIDE + c * 8;
+        __nv_bfloat16* dk = sK + at(row, c * 8);
+        __nv_bfloat16* dv = sV + at(row, c * 8);
         if (ro >= 0) { cp_async16(dk, p.k_cache + ro + c * 8); cp_async16(dv, p.v_cache + ro + c * 8); }
         else if (ro == -1) { *(uint4*)dk = make_uint4(0, 0, 0, 0); *(uint4*)dv = make_uint4(0, 0, 0, 0); }
       }
@@ -444,7 +475,7 @@ attention_decode_mma_kernel(const DecodeParams p) {
         const int row = idx / CHUNKS, c = idx % CHUNKS;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (row < group) v = *(const uint4*)(p.q + (size_t)r * p.q_stride + (size_t)(g * group + row) * HD + c * 8);
-        *(uint4*)(sQ + row * STRIDE + c * 8) = v;
+        *(uint4*)(sQ + row * QSTRIDE + c * 8) = v;
       }
     }
     if (FUSED && first) {
@@ -465,11 +496,11 @@ attention_decode_mma_kernel(const DecodeParams p) {
         const float a = sums[row * HD + e0] * inv_rms + (bias ? bias[row * HD + e0] : 0.f);
         const float b = sums[row * HD + e1] * inv_rms + (bias ? bias[row * HD + e1] : 0.f);
         const float c = turned ? p.cos_table[(size_t)safe * rot_half + d] : 1.f, sn = turned ? p.sin_table[(size_t)safe * rot_half + d] : 0.f;
-        sQ[row * STRIDE + e0] = __float2bfloat16_rn(a * c - b * sn);
-        sQ[row * STRIDE + e1] = __float2bfloat16_rn(b * c + a * sn);
+        sQ[row * QSTRIDE + e0] = __float2bfloat16_rn(a * c - b * sn);
+        sQ[row * QSTRIDE + e1] = __float2bfloat16_rn(b * c + a * sn);
       }
       for (int idx = group * CHUNKS + tid; idx < 16 * CHUNKS; idx += DEC_THREADS)      // the tile's unused rows
-        *(uint4*)(sQ + (idx / CHUNKS) * STRIDE + (idx % CHUNKS) * 8) = make_uint4(0, 0, 0, 0);
+        *(uint4*)(sQ + (idx / CHUNKS) * QSTRIDE + (idx % CHUNKS) * 8) = make_uint4(0, 0, 0, 0);
     }
     if (first) {
       end = min(len, begin + p.split_keys);
@@ -488,12 +519,12 @@ attention_decode_mma_kernel(const DecodeParams p) {
 #pragma unroll
         for (int k = 0; k < CHUNKS; k++) {
           const int row = r0 + k * ROWS_AT_ONCE;
-          if (row >= live) *(uint4*)(sV + row * STRIDE + c8) = make_uint4(0, 0, 0, 0);
+          if (row >= live) *(uint4*)(sV + at(row, c8)) = make_uint4(0, 0, 0, 0);
         }
       } else {
         for (int idx = tid; idx < DEC_THREADS * CHUNKS; idx += DEC_THREADS) {
           const int row = idx / CHUNKS, c = idx % CHUNKS;
-          if (row >= live) *(uint4*)(sV + row * STRIDE + c * 8) = make_uint4(0, 0, 0, 0);
+          if (row >= live) *(uint4*)(sV + at(row, c * 8)) = make_uint4(0, 0, 0, 0);
         }
       }
     }
@@ -503,8 +534,8 @@ attention_decode_mma_kernel(const DecodeParams p) {
       const long long ro = rows[pos - base];
       if (ro >= 0)
         for (int c = tid; c < CHUNKS; c += DEC_THREADS) {
-          *(uint4*)(sK + (pos - base) * STRIDE + c * 8) = *(const uint4*)(p.k_cache + ro + c * 8);
-          *(uint4*)(sV + (pos - base) * STRIDE + c * 8) = *(const uint4*)(p.v_cache + ro + c * 8);
+          *(uint4*)(sK + at(pos - base, c * 8)) = *(const uint4*)(p.k_cache + ro + c * 8);
+          *(uint4*)(sV + at(pos - base, c * 8)) = *(const uint4*)(p.v_cache + ro + c * 8);
         }
     }
     if (FUSED && pos >= base && pos < base + DEC_THREADS && pos < begin + p.split_keys) {
@@ -532,13 +563,13 @@ attention_decode_mma_kernel(const DecodeParams p) {
         k_acc[e0] = 0.f; k_acc[e1] = 0.f;
         const float c = turned ? p.cos_table[(size_t)safe * rot_half + d] : 1.f, sn = turned ? p.sin_table[(size_t)safe * rot_half + d] : 0.f;
         const __nv_bfloat16 lo = __float2bfloat16_rn(a * c - b * sn), hi = __float2bfloat16_rn(b * c + a * sn);
-        sK[row * STRIDE + e0] = lo; sK[row * STRIDE + e1] = hi;
+        sK[at(row, e0)] = lo; sK[at(row, e1)] = hi;
         if (page_ok) { p.k_append[dst + e0] = lo; p.k_append[dst + e1] = hi; }
       }
       for (int d = tid; d < HD; d += DEC_THREADS) {
         const __nv_bfloat16 v = __float2bfloat16_rn(v_acc[d] * inv_rms + (v_bias ? v_bias[d] : 0.f));
         v_acc[d] = 0.f;
-        sV[row * STRIDE + d] = v;
+        sV[at(row, d)] = v;
         if (page_ok) p.v_append[dst + d] = v;
       }
     }
@@ -547,19 +578,27 @@ attention_decode_mma_kernel(const DecodeParams p) {
 
     const int key0 = base + warp * 32;                 // this warp's 32 keys
     if (key0 < end) {
-      const __nv_bfloat16* wK = sK + warp * 32 * STRIDE;
-      const __nv_bfloat16* wV = sV + warp * 32 * STRIDE;
+      // A lane's ldmatrix addresses: its row's start plus a 16-byte piece.  With swizzled rows (which
+      // start on multiples of their length) the piece of step kk / d2 is an exclusive-or of the lane's
+      // address with a constant, one instruction where it is used and no register held for it.
+      const uint32_t wK_lane = (uint32_t)__cvta_generic_to_shared(sK + warp * 32 * STRIDE) +
+                               (uint32_t)(((lane & 7) + (lane >> 4) * 8) * STRIDE * 2) +
+                               (SWZ ? (uint32_t)(((((lane >> 3) & 1)) ^ (lane & 7)) << 4) : (uint32_t)(((lane >> 3) & 1) * 16));
+      const uint32_t wV_lane = (uint32_t)__cvta_generic_to_shared(sV + warp * 32 * STRIDE) +
+                               (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE * 2) +
+                               (SWZ ? (uint32_t)(((lane >> 4) ^ (lane & 7)) << 4) : (uint32_t)((lane >> 4) * 16));
       float s[4][4];
 #pragma unroll
       for (int i = 0; i < 4; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
 #pragma unroll
       for (int kk = 0; kk < HD / 16; kk++) {
         uint32_t a[4];
-        ldmatrix_x4(a, sQ + ((lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + kk * 16 + (lane >> 4) * 8);
+        ldmatrix_x4(a, sQ + ((lane & 7) + ((lane >> 3) & 1) * 8) * QSTRIDE + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
         for (int n2 = 0; n2 < 2; n2++) {
           uint32_t b[4];
-          ldmatrix_x4(b, wK + (n2 * 16 + (lane & 7) + (lane >> 4) * 8) * STRIDE + kk * 16 + ((lane >> 3) & 1) * 8);
+          const uint32_t row_addr = wK_lane + (uint32_t)(n2 * 16 * STRIDE * 2);
+          ldmatrix_x4_addr(b, SWZ ? row_addr ^ (uint32_t)(kk << 5) : row_addr + (uint32_t)(kk << 5));
           mma_bf16(s[2 * n2], a, b[0], b[1]);
           mma_bf16(s[2 * n2 + 1], a, b[2], b[3]);
         }
@@ -600,7 +639,8 @@ attention_decode_mma_kernel(const DecodeParams p) {
 #pragma unroll
         for (int d2 = 0; d2 < HD / 16; d2++) {
           uint32_t b[4];
-          ldmatrix_x4_trans(b, wV + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + d2 * 16 + (lane >> 4) * 8);
+          const uint32_t row_addr = wV_lane + (uint32_t)(kk * 16 * STRIDE * 2);
+          ldmatrix_x4_trans_addr(b, SWZ ? row_addr ^ (uint32_t)(d2 << 5) : row_addr + (uint32_t)(d2 << 5));
           mma_bf16(o[2 * d2], a, b[0], b[1]);
           mma_bf16(o[2 * d2 + 1], a, b[2], b[3]);
         }
@@ -719,7 +759,7 @@ attention_decode_mma_kernel(const DecodeParams p) {
 
 template <int HD, bool FUSED>
 int launch_decode_mma(const DecodeParams& p, bool cluster, int requests, cudaStream_t stream) {
-  constexpr size_t smem = (size_t)(16 + 2 * DEC_THREADS) * (HD + 8) * 2 + (size_t)(16 * HD + 16 + 256) * 4 + DEC_THREADS * 8;
+  const size_t smem = cluster ? DecodeSmem<HD, true>::BYTES : DecodeSmem<HD, false>::BYTES;
   static bool configured[2] = {false, false};
   if (!configured[cluster]) {
     cudaError_t err = cudaSuccess;
@@ -771,24 +811,25 @@ int launch_decode_mma(const DecodeParams& p, bool cluster, int requests, cudaStr
 }
 
 // How many CTAs of the split-key decode kernel an SM holds at once (registers and shared memory), for
-// the plan of a launch: 0 for a head size the kernel does not take.
-template <int HD>
-int decode_mma_ctas_per_sm(bool fused) {
-  constexpr size_t smem = (size_t)(16 + 2 * DEC_THREADS) * (HD + 8) * 2 + (size_t)(16 * HD + 16 + 256) * 4 + DEC_THREADS * 8;
+// the plan of a launch: of the fused kernel as a launch with many CTAs runs it, through memory or
+// (cluster) in clusters, whose CTAs also hold what the splits send one another.
+template <int HD, bool CLUSTER, bool FUSED, bool TIGHT>
+int decode_mma_occupancy() {
+  const size_t smem = DecodeSmem<HD, CLUSTER>::BYTES;
   int count = 0;
-  cudaError_t err;
-  if (fused) {
-    constexpr bool TIGHT = HD <= 64;       // what a launch with many CTAs runs
-    if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false, true, TIGHT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false, true, TIGHT>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&count, attention_decode_mma_kernel<HD, false, true, TIGHT>, DEC_THREADS, smem);
-  } else {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false, false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&count, attention_decode_mma_kernel<HD, false, false>, DEC_THREADS, smem);
+  if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_mma_kernel<HD, CLUSTER, FUSED, TIGHT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaFuncSetAttribute(attention_decode_mma_kernel<HD, CLUSTER, FUSED, TIGHT>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&count, attention_decode_mma_kernel<HD, CLUSTER, FUSED, TIGHT>, DEC_THREADS, smem) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
   }
-  if (err != cudaSuccess) { cudaGetLastError(); return 0; }
   return count;
+}
+template <int HD>
+int decode_mma_ctas_per_sm(bool fused, bool cluster) {
+  if (cluster) return fused ? decode_mma_occupancy<HD, true, true, false>() : decode_mma_occupancy<HD, true, false, false>();
+  if (fused) return decode_mma_occupancy<HD, false, true, (HD <= 64)>();
+  return decode_mma_occupancy<HD, false, false, false>();
 }
 
 // Merge the splits of one (request, head): grid (heads, requests), head_dim threads (rounded up to a warp).
@@ -1079,18 +1120,19 @@ SPROUT_API long long sprout_attention_decode_scratch_floats(int requests, int he
   return (long long)requests * heads * splits * (head_dim + 2);
 }
 
-// CTAs of the split-key decode kernel (the tensor-core one; fused: with the projection's tail) that
-// an SM of the current device holds at once, or 0 for a head size that kernel does not take.
-SPROUT_API int sprout_attention_decode_ctas_per_sm(int head_dim, int fused) {
+// CTAs of the split-key decode kernel (the tensor-core one; fused: with the projection's tail;
+// cluster: the variant launched in clusters) that an SM of the current device holds at once, or 0
+// for a head size that kernel does not take.
+SPROUT_API int sprout_attention_decode_ctas_per_sm(int head_dim, int fused, int cluster) {
   switch (head_dim) {
-    case 16: return decode_mma_ctas_per_sm<16>(fused != 0);
-    case 32: return decode_mma_ctas_per_sm<32>(fused != 0);
-    case 48: return decode_mma_ctas_per_sm<48>(fused != 0);
-    case 64: return decode_mma_ctas_per_sm<64>(fused != 0);
-    case 80: return decode_mma_ctas_per_sm<80>(fused != 0);
-    case 96: return decode_mma_ctas_per_sm<96>(fused != 0);
-    case 112: return decode_mma_ctas_per_sm<112>(fused != 0);
-    case 128: return decode_mma_ctas_per_sm<128>(fused != 0);
+    case 16: return decode_mma_ctas_per_sm<16>(fused != 0, cluster != 0);
+    case 32: return decode_mma_ctas_per_sm<32>(fused != 0, cluster != 0);
+    case 48: return decode_mma_ctas_per_sm<48>(fused != 0, cluster != 0);
+    case 64: return decode_mma_ctas_per_sm<64>(fused != 0, cluster != 0);
+    case 80: return decode_mma_ctas_per_sm<80>(fused != 0, cluster != 0);
+    case 96: return decode_mma_ctas_per_sm<96>(fused != 0, cluster != 0);
+    case 112: return decode_mma_ctas_per_sm<112>(fused != 0, cluster != 0);
+    case 128: return decode_mma_ctas_per_sm<128>(fused != 0, cluster != 0);
     default: return 0;
   }
 }

@@ -72,7 +72,7 @@ def load_library(verbose: bool = True):
             lib.sprout_attention_decode_scratch_floats.restype = ctypes.c_longlong
             lib.sprout_attention_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
             lib.sprout_attention_decode_ctas_per_sm.restype = c_int
-            lib.sprout_attention_decode_ctas_per_sm.argtypes = [c_int, c_int]
+            lib.sprout_attention_decode_ctas_per_sm.argtypes = [c_int, c_int, c_int]
             for name, argtypes in _SIGNATURES.items():
                 fn = getattr(lib, name)
                 fn.argtypes = argtypes
@@ -526,25 +526,33 @@ def decode_split_plan(requests: int, kv_heads: int, max_keys: int, head_dim: int
     live = max_keys if live_keys is None else max(1, min(max_keys, live_keys))
     if sms is None:
         sms = sm_count() if torch.cuda.is_available() else 148      # host-side inspection without a device: a B200's count
-    return _decode_split_plan(requests * kv_heads, -(-max_keys // 128), -(-live // 128), head_dim, sms, decode_ctas_per_sm(head_dim))
+    return _decode_split_plan(requests * kv_heads, -(-max_keys // 128), -(-live // 128), head_dim, sms,
+                              decode_ctas_per_sm(head_dim), decode_ctas_per_sm(head_dim, True))
 
 
 @functools.lru_cache(maxsize=64)
-def decode_ctas_per_sm(head_dim: int) -> int:
-    """CTAs of the split-key decode kernel that an SM holds at once: the device's own answer for
-    the kernel as built (registers and shared memory), or, without a device, what its shared
-    memory and a bound of 5 by registers give on a B200."""
+def decode_ctas_per_sm(head_dim: int, cluster: bool = False) -> int:
+    """CTAs of the split-key decode kernel that an SM holds at once (``cluster``: of the variant
+    launched in clusters, whose CTAs also hold what the splits send one another): the device's own
+    answer for the kernel as built (registers and shared memory), or, without a device, what its
+    shared memory and its register bounds give on a B200."""
     if torch.cuda.is_available() and head_dim % 16 == 0 and head_dim <= 128:
-        count = int(load_library().sprout_attention_decode_ctas_per_sm(head_dim, 1))
+        count = int(load_library().sprout_attention_decode_ctas_per_sm(head_dim, 1, int(cluster)))
         if count > 0:
             return count
-    shared = (16 + 256) * (head_dim + 8) * 2 + (16 * head_dim + 16 + 256) * 4 + 128 * 8      # the tensor-core kernel's, per CTA
-    return max(1, min(5 if head_dim <= 64 else 16, (227 * 1024) // (shared + 1024)))
+    stride = head_dim if head_dim == 128 or (head_dim == 64 and not cluster) else head_dim + 8    # swizzled rows, or rows padded by 16 bytes
+    shared = 16 * (head_dim + 8) * 2 + 2 * 128 * stride * 2 + 128 * 8 + 16    # the tensor-core kernel's, per CTA
+    if cluster:
+        shared += (8 * head_dim + 8) * 8 + 256 * 4
+    by_registers = (4 if cluster else 5) if head_dim <= 64 else 3 if head_dim == 128 else 4      # by its registers
+    return max(1, min(by_registers, (228 * 1024) // (shared + 1024)))
 
 
 @functools.lru_cache(maxsize=4096)
-def _decode_split_plan(pairs: int, total_passes: int, live_passes: int, head_dim: int, sms: int, per_sm: int) -> tuple[int, int, bool]:
+def _decode_split_plan(pairs: int, total_passes: int, live_passes: int, head_dim: int, sms: int, per_sm: int,
+                       per_sm_cluster: int | None = None) -> tuple[int, int, bool]:
     slots = sms * per_sm
+    cluster_slots = sms * (per_sm_cluster or per_sm)
     total_passes = max(1, total_passes)
     best, best_cost, last_splits = (128 * total_passes, 1, False), None, 0
     for passes in range(1, total_passes + 1):
@@ -554,7 +562,7 @@ def _decode_split_plan(pairs: int, total_passes: int, live_passes: int, head_dim
         last_splits = splits
         live_splits = -(-live_passes // passes)
         # a pass takes 1.6 to 2.3 us (by the head size) when little is in flight, 3.5 us once about
-        # 16 MB are (the latency under load), and never less than the wave's bytes at 5.8 TB/s
+        # 16 MB are (the latency under load), and never less than the wave's bytes at 6.3 TB/s
         idle_us = 1.0 + head_dim / 100.0
         for through_memory in (False, True):
             if (through_memory and splits == 1) or (not through_memory and splits > 8):
@@ -562,13 +570,14 @@ def _decode_split_plan(pairs: int, total_passes: int, live_passes: int, head_dim
             # the CTAs that hold a slot: a cluster is placed whole, of independent CTAs those that find keys
             ctas = pairs * (live_splits if through_memory else splits)
             # a cluster needs room for all its CTAs at once in one part of the GPU: larger clusters pack worse
-            room = slots if through_memory else int(slots * (1.0 - 0.06 * (splits - 1)))
+            room = slots if through_memory or splits == 1 else max(1, int(cluster_slots * (1.0 - 0.06 * (splits - 1))))
             # a last wave that is not full costs less than a full one: half-way between the two counts
             waves = max(1.0, (-(-ctas // room) + ctas / room) / 2)
             wave_mb = min(ctas, room) * 128 * head_dim * 4 / 1e6
-            pass_us = max(idle_us + (3.5 - idle_us) * min(1.0, wave_mb / 16.0), wave_mb / 5.8)
+            pass_us = max(idle_us + (3.5 - idle_us) * min(1.0, wave_mb / 16.0), wave_mb / 6.3)
             merge_us = 0.0 if splits == 1 else 3.5 + 0.085 * splits if through_memory else 1.0
-            cost = waves * (2.2 + min(passes, live_passes) * pass_us) + merge_us
+            # the first wave pays the launch's start; CTAs of later waves start as others leave
+            cost = 2.2 + waves * min(passes, live_passes) * pass_us + (waves - 1.0) * 1.0 + merge_us
             if best_cost is None or cost < best_cost:
                 best, best_cost = (128 * -(-total_passes // splits), splits, through_memory), cost
     return best

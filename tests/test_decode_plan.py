@@ -19,16 +19,20 @@ def test_plan_covers_every_key(head_dim, kv_heads, requests):
 
 
 def test_plan_counts_the_ctas_an_sm_really_holds():
-    """The plan's waves follow how many CTAs an SM holds: 128 (request, head) pairs over 32,768
-    keys take five splits where five CTAs fit an SM (640 CTAs, one wave of 740 places); with four
-    per SM that launch would run in two waves, and the plan is another."""
-    five = kernels._decode_split_plan(128, 256, 256, 64, 148, 5)
-    four = kernels._decode_split_plan(128, 256, 256, 64, 148, 4)
-    assert five == (6656, 5, True) and four != five
-    for split_keys, splits, _ in (five, four):
-        assert split_keys * splits >= 32768
-    # without a device the count is what shared memory and the kernel's register bound give on a B200
-    assert kernels.decode_ctas_per_sm.__wrapped__(64) == 5 and kernels.decode_ctas_per_sm.__wrapped__(128) == 2
+    """The plan's waves follow how many CTAs an SM holds, through memory and in clusters (whose CTAs
+    hold more shared memory); a launch of many waves goes through memory even where its splits
+    would fit a cluster."""
+    # without a device the counts are what shared memory and the kernel's register bounds give on a B200
+    counts = kernels.decode_ctas_per_sm.__wrapped__
+    assert (counts(64), counts(64, True), counts(128), counts(128, True)) == (5, 4, 3, 2)
+    assert counts(80) == 4 and counts(16) == 5
+    # 64 requests x 4 key/value heads of 128 over 8,192 keys: more CTAs than places, splits through memory
+    split_keys, splits, through_memory = kernels._decode_split_plan(256, 64, 64, 128, 148, 3, 2)
+    assert through_memory and splits <= 8 and split_keys * splits >= 8192
+    # the same pairs with 640 keys each: one split per pair, all resident at once, nothing to merge
+    assert kernels._decode_split_plan(256, 5, 5, 128, 148, 3, 2) == (640, 1, False)
+    # fewer places per SM: another plan for a launch that no longer fits one wave
+    assert kernels._decode_split_plan(128, 65, 65, 64, 148, 5, 4) != kernels._decode_split_plan(128, 65, 65, 64, 148, 3, 2)
 
 
 def test_plan_follows_the_batch_and_the_context():
