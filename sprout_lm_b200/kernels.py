@@ -629,7 +629,10 @@ def decode_attention_plan(requests: int, heads: int, kv_heads: int, head_dim: in
     # (they are one to an SM).  Measured alone at the 0.5B sizes, 640 keys each, split plan against
     # resident: 8 requests 4.6 / 5.4 us, 32: 8.0 / 5.5, 64: 11.1 / 7.7, 128: 14.4 / 14.3, 256: 19.2 / 28.9.
     sms = sm_count() if torch.cuda.is_available() else 148
-    if RESIDENT_ENABLED and head_dim in (64, 128) and (3 * sms) // 8 <= requests * kv_heads <= 2 * sms:
+    # At head size 128 a second wave of them loses to the split kernel, which holds three CTAs per SM
+    # there (7B sizes, 64 requests of 384 keys: 15.6 against 10.9 us; 32 requests: 8.2 against 13.4).
+    most = 2 * sms if head_dim == 64 else sms
+    if RESIDENT_ENABLED and head_dim in (64, 128) and (3 * sms) // 8 <= requests * kv_heads <= most:
         cap = resident_cap(heads, kv_heads, head_dim, page_tokens)
         room = min(cap, -(-planned // RESIDENT_STEP) * RESIDENT_STEP)
         if planned <= room:

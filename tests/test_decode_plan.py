@@ -56,7 +56,8 @@ def test_attention_plan_keeps_short_contexts_resident():
     assert plan(64, 14, 2, 64, 16, 1024, 520) == ("resident", 768)
     assert plan(64, 14, 2, 64, 16, 1024, 512) == ("resident", 512)
     assert plan(64, 14, 2, 64, 16, 1024, 100) == ("resident", 256)
-    assert plan(64, 28, 4, 128, 16, 4096, 300) == ("resident", 384)          # the room's limit at head size 128
+    assert plan(32, 28, 4, 128, 16, 4096, 300) == ("resident", 384)          # the room's limit at head size 128
+    assert plan(64, 28, 4, 128, 16, 4096, 300)[0] == "split"                 # head size 128: more of them than SMs
     assert plan(8, 14, 2, 64, 16, 1024, 520)[0] == "split"                   # too few CTAs to keep the SMs' copies busy
     assert plan(256, 14, 2, 64, 16, 1024, 520)[0] == "split"                 # more CTAs than fit the SMs at once
     assert plan(64, 14, 2, 64, 16, 1024, 769)[0] == "split"
