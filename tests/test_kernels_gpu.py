@@ -558,6 +558,8 @@ def test_attention_finds_one_far_key_among_hundreds(status, dtype, where):
 DECODE_CASES = [
     (4, 2, 16, 16, [5, 17, 33, 1]), (3, 1, 32, 8, [61, 1, 130]), (14, 2, 64, 16, [300, 129, 16, 640, 513]),
     (5, 5, 48, 4, [40, 9]), (8, 2, 128, 16, [257, 64, 1000]), (6, 3, 80, 32, [100]), (16, 1, 256, 16, [70, 200]),
+    (8, 2, 128, 16, [3000, 1200, 17]),                         # head size 128 through memory: swizzled rows, three CTAs per SM
+    (6, 2, 96, 32, [2100, 5]),                                 # padded rows through memory
 ]
 
 
@@ -586,6 +588,8 @@ def test_attention_decode_split_keys(status, heads, kv_heads, head_dim, page, le
     (4, 2, 64, 16, [6000, 1500]),                              # more than 8 splits: through memory too
     (4, 2, 64, 16, [2900 + 2 * i for i in range(80)]),         # more CTAs than four per SM: the variant held to five per SM's registers
     (6, 2, 32, 16, [5000 + 2 * i for i in range(60)]),
+    (8, 2, 128, 16, [2500, 700, 90]),                          # head size 128 through memory
+    (8, 4, 128, 32, [1300 + 7 * i for i in range(40)]),        # and with more CTAs than places
 ])
 def test_attention_decode_fused_projection_tail(status, heads, kv_heads, head_dim, page, lengths, rotate):
     """The decode kernel that also finishes the projection: the new token's q, k, v arrive as
