@@ -113,8 +113,13 @@ def library_path(build: bool = True, verbose: bool = True, extra_flags: tuple[st
         return obj
 
     workers = max(1, min(len(files), (os.cpu_count() or 2)))
-    with ThreadPoolExecutor(workers) as pool:
-        objects = list(pool.map(compile_one, files))
+    try:
+        with ThreadPoolExecutor(workers) as pool:
+            objects = list(pool.map(compile_one, files))
+    except BaseException:
+        for path in files:                   # a failed build leaves no objects behind
+            (out_dir / f"{path.stem}_{os.getpid()}.o").unlink(missing_ok=True)
+        raise
     partial = out_dir / f"{target.name}.{os.getpid()}.tmp"
     link = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(partial), *map(str, objects)]
     done = subprocess.run(link, capture_output=True, text=True, env=env)
