@@ -355,7 +355,7 @@ struct DecodeSmem {
 #define DEC_TIGHT_CTAS 5
 #endif
 template <int HD, bool CLUSTER, bool FUSED, bool TIGHT = false>
-__global__ void __launch_bounds__(DEC_THREADS, TIGHT ? DEC_TIGHT_CTAS : (HD == 128 ? 3 : (HD == 64 && !FUSED && !CLUSTER ? 5 : 0)))
+__global__ void __launch_bounds__(DEC_THREADS, TIGHT ? DEC_TIGHT_CTAS : (HD == 128 ? 3 : (HD == 64 && !FUSED && !CLUSTER ? DEC_TIGHT_CTAS : 0)))
 attention_decode_mma_kernel(const DecodeParams p) {
   // Key and value rows in shared memory: rows of 128 or 256 bytes (head sizes 64 and 128) lie side
   // by side with their 16-byte pieces swizzled (piece c of row r at piece c ^ (r % 8): what ldmatrix
