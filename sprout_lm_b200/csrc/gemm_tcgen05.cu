@@ -272,12 +272,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
       // The tokens' operand, made here: for every k-block of this CTA's (one) work item the tile
       // [BN tokens, 64 elements] = bfloat16(x * gain), in the layout the 128-byte swizzle gives a
       // copied tile (16-byte chunk c of row t at chunk c ^ (t & 7)); rows and columns beyond the
-      // matrix are zero.  The launch has checked that the item's k-blocks fit the ring.
+      // matrix are zero.  K ranges longer than the ring take a stage again once the products that
+      // read it are done (its "empty" barrier, as the copy thread does for the weights).
       const Work k = work_at(first_work);
       const int et = (int)threadIdx.x - 64;                    // 0..255 among the epilogue warps
       if (first_work < total_work) {
         for (int i = 0; i < k.num_kb; i++) {
-          uint8_t* tile = smem + i * L::STAGE_BYTES + L::A_BYTES;
+          const int stage = i % L::STAGES;
+          if (i >= L::STAGES) {
+            bool freed = true;
+            if (lane == 0) {
+              freed = mbar_wait(&empty_bar[stage], ((i / L::STAGES) - 1) & 1, abort_flag);
+              if (!freed) { *abort_flag = 1; atomicOr(p.status, SPROUT_STATUS_WAIT_TIMEOUT); }
+            }
+            if (!__shfl_sync(0xffffffffu, freed, 0)) break;
+          }
+          uint8_t* tile = smem + stage * L::STAGE_BYTES + L::A_BYTES;
           const int k0 = (k.kb_begin + i) * BLOCK_K;
           for (int idx = et; idx < BN * 8; idx += 256) {
             const int t = idx >> 3, c = idx & 7, m = k.col0 + t, kk = k0 + c * 8;
@@ -293,7 +303,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           if (!epi_sync()) break;                              // all eight warps have written their chunks
-          if (issuer) mbar_arrive(&full_bar[i]);
+          if (issuer) mbar_arrive(&full_bar[stage]);
         }
       }
     }
@@ -645,7 +655,7 @@ SPROUT_API int sprout_gemm_bf16(const void* A, const void* W, const float* bias,
 // decode attention kernels do, with the bias and the rotation), which is the RMSNorm's arithmetic
 // with the division moved behind the product.  Weights on M, K split among CTAs (atomic adds); the
 // tokens' tiles are converted inside the kernel, so no kernel stands between the residual stream
-// and this product.  Every CTA has one work item whose k-blocks fit the ring, or the call is refused.
+// and this product.  Every CTA has one work item (it makes that item's token tiles), or the call is refused.
 SPROUT_API int sprout_gemm_bf16_unscaled(const float* x, int ldx, const float* gain, const void* W, float* out, int M, int N, int K,
                                          int ldo, int split_k, int* status, cudaStream_t stream) {
   SPROUT_REQUIRE(M > 0 && M <= 256 && N > 0 && K > 0, "gemm_bf16_unscaled: 1..256 tokens, positive sizes (M=%d N=%d K=%d)", M, N, K);
@@ -665,17 +675,8 @@ SPROUT_API int sprout_gemm_bf16_unscaled(const float* x, int ldx, const float* g
   const long long work = (long long)((N + BLOCK_M - 1) / BLOCK_M) * ((M + bn - 1) / bn) * split_k;
   CUtensorMap map_w;
   if (tensor_map(W, N, K, K, BLOCK_M, &map_w)) return 1;
-  int stages = 0;
-  switch (bn) {
-    case 16: stages = Layout<16>::STAGES; break;
-    case 32: stages = Layout<32>::STAGES; break;
-    case 64: stages = Layout<64>::STAGES; break;
-    case 128: stages = Layout<128>::STAGES; break;
-    default: stages = Layout<256>::STAGES; break;
-  }
-  SPROUT_REQUIRE(work <= sm_count() && p.k_blocks_per_split <= stages,
-                 "gemm_bf16_unscaled: %lld work items for %d SMs, %d k-blocks a CTA for a ring of %d: split K further or use the separate norm",
-                 work, sm_count(), p.k_blocks_per_split, stages);
+  SPROUT_REQUIRE(work <= sm_count(), "gemm_bf16_unscaled: %lld work items for %d SMs (a CTA makes the tokens' tiles of one item): "
+                 "split K less or use the separate norm", work, sm_count());
   switch (bn) {
     case 16: return launch<16, true>(map_w, map_w, map_w, p, (int)work, stream);
     case 32: return launch<32, true>(map_w, map_w, map_w, p, (int)work, stream);
@@ -695,9 +696,7 @@ SPROUT_API int sprout_gemm_bf16_unscaled_supported(int M, int N, int K, int spli
   split_k = (total_kb + per - 1) / per;
   const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   const long long work = (long long)((N + BLOCK_M - 1) / BLOCK_M) * ((M + bn - 1) / bn) * split_k;
-  const int stages = bn == 16 ? Layout<16>::STAGES : bn == 32 ? Layout<32>::STAGES : bn == 64 ? Layout<64>::STAGES
-                   : bn == 128 ? Layout<128>::STAGES : Layout<256>::STAGES;
-  return work <= sm_count() && per <= stages ? 1 : 0;
+  return work <= sm_count() ? 1 : 0;
 }
 
 SPROUT_TL_READER(gemm_tcgen05)

@@ -399,14 +399,16 @@ def test_linear_decode_refuses_what_does_not_fit(status):
         kernels.linear_decode(rand(3584, 3584, dtype=torch.bfloat16), rand(8, 3584), status, a=rand(8, 3584, dtype=torch.bfloat16))
 
 
-@pytest.mark.parametrize("tokens,N,K,split", [(17, 1152, 896, 14), (64, 1152, 896, 14), (33, 256, 136, 3), (200, 384, 520, 9), (64, 1152, 896, 1)])
+@pytest.mark.parametrize("tokens,N,K,split", [(17, 1152, 896, 14), (64, 1152, 896, 14), (33, 256, 136, 3), (200, 384, 520, 9), (64, 1152, 896, 1),
+                                              (64, 4608, 3584, 4), (40, 256, 2000, 1), (130, 300, 3000, 2), (8, 20000, 64, 1)])
 def test_gemm_bf16_unscaled_is_the_normed_product_without_its_scale(status, tokens, N, K, split):
     """out += bfloat16(x * gain) W^T with the tokens' tiles made inside the kernel: against float64
     with that one rounding, on top of what the output held; and scaled by 1 / rms(x) it is the
-    product of the RMSNorm's output, to bfloat16's precision."""
+    product of the RMSNorm's output, to bfloat16's precision.  K ranges of 14, 32 and 24 k-blocks per
+    CTA go round the ring of stages more than once."""
     from sprout_lm_b200 import kernels
     if not kernels.gemm_bf16_unscaled_supported(tokens, N, K, split):
-        assert split == 1                                  # without a K split a CTA's k-blocks may not fit the ring
+        assert N == 20000                                  # more work items than SMs (K ranges longer than the ring are taken)
         with pytest.raises(kernels.KernelError, match="gemm_bf16_unscaled"):
             kernels.gemm_bf16_unscaled(rand(tokens, K), rand(K), rand(N, K, dtype=torch.bfloat16), rand(tokens, N), status, split_k=split)
         return
