@@ -20,7 +20,7 @@
 //
 // Takes head sizes 64 and 128, pages of 8 to 128 tokens (a power of two), up to 16 query heads
 // per key/value head and contexts up to `cap_keys` (what fits in shared memory: 768 keys of
-// head size 64, 384 of 128); the split-key kernels in attention_bf16.cu take everything else.
+// head size 64, 384 of 128); the split-key kernels (attention_decode_mma.cuh, attention_bf16.cu) take everything else.
 // Every mbarrier wait is bounded; a wait that runs out sets the status word and the CTA leaves
 // once its copies have landed or their wait has run out too.
 #include <cuda_bf16.h>

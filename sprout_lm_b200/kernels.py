@@ -422,14 +422,17 @@ ATTENTION_PHASES = ("entry", "first keys and values requested", "earlier kernels
 
 def attention_decode_phase_stamps() -> dict | None:
     """Microseconds from entry to the end of each phase of the last split-key decode attention
-    launch (its first CTA), from a library built with ``SPROUT_BUILD_FLAGS=-DATTN_STAMPS`` (None from
-    an ordinary build).  Synchronises the device."""
+    launch of a head size up to 64 (its first CTA), from a library built with
+    ``SPROUT_BUILD_FLAGS=-DATTN_STAMPS`` (None from an ordinary build, or when no such launch has
+    run).  Synchronises the device."""
     lib = _lib or load_library()
     if not hasattr(lib, "sprout_attention_stamps"):
         return None
     torch.cuda.synchronize()
     raw = (ctypes.c_ulonglong * 16)()
     lib.sprout_attention_stamps(raw)
+    if not raw[0]:
+        return None
     return {name: (raw[i] - raw[0]) / 1000.0 for i, name in enumerate(ATTENTION_PHASES)}
 
 
@@ -444,7 +447,7 @@ def decode_timeline() -> dict | None:
         return None
     torch.cuda.synchronize()
     records = {}
-    for label, reader, slot in (("norm + q/k/v", "linear_decode", 0), ("attention", "attention_bf16", 0),
+    for label, reader, slot in (("norm + q/k/v", "linear_decode", 0), ("attention", "attention_bf16", 0), ("attention, wide heads", "attention_bf16_wide", 0),
                                 ("output projection", "linear_decode", 1), ("feed-forward", "ffn_decode", 0),
                                 ("q/k/v product", "gemm_tcgen05", 0), ("attention, resident", "attention_decode_resident", 0),
                                 ("output product", "gemm_tcgen05", 1), ("gate/up product", "gemm_tcgen05", 2),
