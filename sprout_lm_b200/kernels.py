@@ -521,11 +521,13 @@ def decode_split_plan(requests: int, kv_heads: int, max_keys: int, head_dim: int
     cluster, more go through scratch memory and a merge kernel.
 
     The pick minimises a small model of the kernel's time, fitted to measurements on a B200: the
-    CTAs run in waves of as many as fit the SMs at once; a wave costs a fixed start and, per
-    pass, the longer of a pass's latency and the time to bring the wave's keys and values in; a
-    merge costs a little inside a cluster and more through memory, growing with the splits.  So a
-    small batch gets many short splits (latency), a large one few long ones (no idle waves, no
-    merge kernel), and a long context as many splits as keep the SMs busy."""
+    CTAs run in waves of as many as the SMs hold at once (the device's own count for the kernel as
+    built; fewer for clusters, whose CTAs hold more shared memory and must be placed together); the
+    launch costs a fixed start, every wave its passes (the longer of a pass's latency and the time
+    to bring the wave's keys and values in), every further wave a little more; a merge costs a
+    little inside a cluster and more through memory, growing with the splits.  So a small batch
+    gets many short splits in a cluster (latency), a large one few long ones, and a launch of
+    several waves goes through memory even where its splits would fit a cluster."""
     live = max_keys if live_keys is None else max(1, min(max_keys, live_keys))
     if sms is None:
         sms = sm_count() if torch.cuda.is_available() else 148      # host-side inspection without a device: a B200's count
