@@ -524,6 +524,53 @@ def timed_decode_attention(shape: str, batch: int, context: int, repeats: int = 
     return result
 
 
+def timed_long_prompt(shape: str, layers: int, total: int, portion: int) -> dict:
+    """One request of ``total`` tokens through ``ModelRunner.step`` in portions of ``portion``: the
+    time of every step (CUDA events; the second of two runs), so that the attention over the cached
+    keys shows as the increase from portion to portion (the products cost the same in each)."""
+    import numpy as np
+    import torch
+    from sprout_lm_b200 import load_model
+    from sprout_lm_b200.engine.batch import StepEntry
+    from sprout_lm_b200.engine.step import ModelRunner
+    base = SHAPES[shape]
+    layers = layers or base["num_hidden_layers"]
+    context = base["max_position_embeddings"]
+    while context < total:
+        context *= 2
+    model = load_model(model_folder(layers, shape, context), dtype="bfloat16", device="cuda:0")
+    runner = ModelRunner(model, num_pages=-(-total // 16) + 16, page_tokens=16, max_requests=2, prefix_caching=False)
+    rng = np.random.default_rng(0)
+    heads, head_dim = base["num_attention_heads"], base["hidden_size"] // base["num_attention_heads"]
+    steps = []
+    for run in range(2):
+        seq = runner.new_sequence()
+        assert runner.reserve(seq, total)
+        steps = []
+        for begin in range(0, total, portion):
+            n = min(portion, total - begin)
+            tokens = [int(t) for t in rng.integers(0, base["vocab_size"], n)]
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            runner.step([StepEntry(seq, tokens, [n - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            steps.append({"context": begin, "tokens": n, "ms": round(start.elapsed_time(end), 3)})
+        runner.check_status()
+        runner.release(seq)
+    whole = sum(s["ms"] for s in steps)
+    out = {"impl": "ours", "only": "long-prompt", "shape": shape, "layers": layers, "tokens": total, "portion": portion,
+           "context_limit": context, "ms": round(whole, 2), "tokens_per_s": round(total / whole * 1000, 1), "steps": steps}
+    full = [s for s in steps if s["tokens"] == portion]
+    if len(full) >= 3:
+        # attention over one more portion's worth of cached keys: 4 * portion^2 * heads * head_dim flops a layer
+        growth = (full[-1]["ms"] - full[1]["ms"]) / (len(full) - 2)
+        out["ms_more_per_portion_of_context"] = round(growth, 3)
+        out["attention_tflops_from_growth"] = round(4.0 * portion * portion * heads * head_dim * layers / (growth / 1000) / 1e12, 1)
+    return out
+
+
 def timed_gemms(tokens: int, shape: str = "0.5b", repeats: int = 20) -> dict:
     """The model's four projections at ``tokens`` tokens, each alone: 20 launches replayed from a
     CUDA graph (no host time between them), beside the library's plain bfloat16 product of the
@@ -604,6 +651,8 @@ def run(args) -> dict:
         return timed_decode_attention(args.shape, args.batch, args.tokens)
     if args.only == "serve":
         return timed_serving(args.shape, args.layers, args.requests, args.workload)
+    if args.only == "long-prompt":
+        return timed_long_prompt(args.shape, args.layers, args.tokens, args.portion)
     if args.only == "all" and args.shape != "0.5b":
         raise SystemExit("bench.py: the full line is measured at the 0.5b shape; give --only with another --shape")
     base = SHAPES[args.shape]
@@ -698,9 +747,10 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--portion", type=int, default=4096, help="with --only long-prompt: tokens of a step (--tokens: of the whole prompt)")
     parser.add_argument("--prompt-len", type=int, default=512, help="with --only decode: tokens of every request's prompt (the context grows to hold it)")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
-    parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate", "attention", "decode-attention", "gemm", "serve"], default="all",
+    parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate", "attention", "decode-attention", "gemm", "serve", "long-prompt"], default="all",
                         help="measure one part only (for profiling captures); the JSON line then holds that part")
     parser.add_argument("--shape", choices=sorted(SHAPES), default="0.5b", help="with --only: the model's sizes")
     parser.add_argument("--requests", type=int, default=64, help="with --only serve: requests of the workload")
