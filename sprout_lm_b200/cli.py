@@ -1,8 +1,8 @@
 """Command line in the manner of the reference's demo (src/demo.ts) and smoke script
 (scripts/smoke-cuda.ts).
 
-    python -m sprout_lm_b200 demo [--model DIR] [--json] [--pressure] [--dtype bfloat16|float32]
-    python -m sprout_lm_b200 generate --model DIR --prompt 1,2,3 [--max-new-tokens N]
+    python -m sprout_lm_b200 demo [--model DIR | --tiny A|B] [--seed S] [--json] [--pressure] [--dtype bfloat16|float32]
+    python -m sprout_lm_b200 generate (--model DIR | --tiny A|B) --prompt 1,2,3 [--max-new-tokens N]
                                       [--temperature T] [--seed S] [--ignore-eos] [--json]
     python -m sprout_lm_b200 random-model --out DIR --config CONFIG.json [--seed S]
 
@@ -11,8 +11,8 @@
 ``--pressure``), ``maxSequences 3``, ``maxBatchTokens 6``, ``prefillChunkSize 4``; every tick
 it prints free and cached pages, a table of the work done (request, phase, position, tokens,
 logical -> physical pages) and the events; at the end the results.  ``--json`` prints
-``{mode, reports, results}`` instead.  Without ``--model`` it writes a tiny random model to a
-temporary folder first.
+``{mode, reports, results}`` instead.  Without ``--model`` it writes a tiny random model (``--tiny``,
+A if not given, weights from ``--seed``) to a temporary folder first.
 """
 from __future__ import annotations
 
@@ -22,9 +22,16 @@ import sys
 import tempfile
 import time
 
-DEMO_TINY = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
-                 num_key_value_heads=2, vocab_size=256, max_position_embeddings=128, rms_norm_eps=1e-6,
-                 rope_theta=10000.0, tie_word_embeddings=True, eos_token_id=255)
+# Two tiny random models that differ in every size and option (--tiny A|B; A is the default of demo)
+TINY = {
+    "A": dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, vocab_size=256, max_position_embeddings=128, rms_norm_eps=1e-6,
+              rope_theta=10000.0, tie_word_embeddings=True, eos_token_id=255),
+    "B": dict(hidden_size=96, intermediate_size=320, num_hidden_layers=3, num_attention_heads=3,
+              num_key_value_heads=1, vocab_size=509, max_position_embeddings=256, rms_norm_eps=1e-5,
+              rope_theta=1000000.0, tie_word_embeddings=False, eos_token_id=[507, 508]),
+}
+DEMO_TINY = TINY["A"]
 
 
 def _table(rows: list[dict]) -> str:
@@ -38,10 +45,13 @@ def _table(rows: list[dict]) -> str:
 
 def _load(args):
     from . import load_model, parse_config, write_random_model
+    if args.model and getattr(args, "tiny", None):
+        raise SystemExit("give --model DIR or --tiny A|B, not both")
     if args.model:
         return load_model(args.model, dtype=args.dtype), None
     tmp = tempfile.TemporaryDirectory()
-    config = parse_config({"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu", **DEMO_TINY})
+    sizes = TINY[getattr(args, "tiny", None) or "A"]
+    config = parse_config({"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu", **sizes})
     write_random_model(tmp.name, config, seed=args.seed)
     return load_model(tmp.name, dtype=args.dtype), tmp
 
@@ -166,6 +176,8 @@ def main(argv=None) -> int:
     gen.add_argument("--json", action="store_true")
     for p in (demo, gen):
         p.add_argument("--model", help="folder with config.json and model.safetensors")
+        p.add_argument("--tiny", choices=sorted(TINY), help="instead of --model: a tiny random model (A: 2 layers, hidden 64, "
+                       "4/2 heads of 16, tied head; B: 3 layers, hidden 96, 3/1 heads of 32, untied head), written with --seed")
         p.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
         p.add_argument("--seed", type=int, default=0)
     rnd = sub.add_parser("random-model", help="write config.json and model.safetensors with random weights")

@@ -162,6 +162,16 @@ def test_command_line_demo_and_generate(model_dirs):
     final = json.loads(done.stdout.strip().splitlines()[-1])
     want = plain.greedy(*plain.read_model_folder(model_dirs["A"]), [1, 2, 3, 4, 5], 4)
     assert final["report"]["results"][0]["output"] == want
+    # a tiny random model written on the spot: the other configuration, and the refusal of both sources at once
+    done = subprocess.run([sys.executable, "-m", "sprout_lm_b200", "demo", "--tiny", "B", "--seed", "3", "--json", "--dtype", "float32"],
+                          capture_output=True, text=True, cwd=root, timeout=600)
+    assert done.returncode == 0, done.stderr[-3000:]
+    report = json.loads(done.stdout)
+    assert [r["status"] for r in report["results"]] == ["finished"] * 3
+    assert all(0 <= t < 509 for r in report["results"] for t in r["output"])
+    done = subprocess.run([sys.executable, "-m", "sprout_lm_b200", "demo", "--tiny", "B", "--model", str(model_dirs["A"])],
+                          capture_output=True, text=True, cwd=root, timeout=600)
+    assert done.returncode != 0 and "not both" in done.stderr
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
