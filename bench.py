@@ -219,8 +219,9 @@ def ablation(model, batch: int, prompt_len: int, steps: int, warmup: int) -> dic
     from sprout_lm_b200 import kernels
     from sprout_lm_b200.engine.batch import StepEntry
     from sprout_lm_b200.engine.step import ModelRunner
-    real = {name: getattr(kernels, name) for name in ("attention_decode", "attention_decode_fused", "rmsnorm", "rope_append",
-                                                      "gemm_bf16", "sample", "ffn_decode", "linear_decode")}
+    real = {name: getattr(kernels, name) for name in ("attention_decode", "attention_decode_fused", "attention_decode_resident",
+                                                      "rmsnorm", "rope_append", "gemm_bf16", "gemm_bf16_unscaled", "sample",
+                                                      "ffn_decode", "linear_decode")}
     linear = real["linear_decode"]
     gemm = real["gemm_bf16"]
     hidden, inter = model.spec.hidden_size, model.blocks[0].feed_forward.intermediate_size
@@ -233,10 +234,12 @@ def ablation(model, batch: int, prompt_len: int, steps: int, warmup: int) -> dic
 
     variants = {
         "baseline": {},
-        "attention": {"attention_decode": lambda *a, **k: None, "attention_decode_fused": lambda *a, **k: None},
+        "attention": {"attention_decode": lambda *a, **k: None, "attention_decode_fused": lambda *a, **k: None,
+                      "attention_decode_resident": lambda *a, **k: None},
         "rmsnorm": {"rmsnorm": lambda *a, **k: None},
         "rope_append": {"rope_append": lambda *a, **k: None},
-        "gemm_qkv": {"gemm_bf16": gemm_without(lambda w, kw: w.shape[0] == qkv_rows)},
+        # (from 17 tokens the q/k/v product may be the one that takes the norm's input as it is)
+        "gemm_qkv": {"gemm_bf16": gemm_without(lambda w, kw: w.shape[0] == qkv_rows), "gemm_bf16_unscaled": lambda *a, **k: None},
         "gemm_o": {"gemm_bf16": gemm_without(lambda w, kw: tuple(w.shape) == (hidden, hidden))},
         "gemm_gate_up": {"gemm_bf16": gemm_without(lambda w, kw: bool(kw.get("swiglu")))},
         "gemm_down": {"gemm_bf16": gemm_without(lambda w, kw: tuple(w.shape) == (hidden, inter))},
@@ -246,7 +249,7 @@ def ablation(model, batch: int, prompt_len: int, steps: int, warmup: int) -> dic
         "ffn_decode": {"ffn_decode": lambda *a, **k: None},
         "linear_norm_qkv": {"linear_decode": lambda w, out, st, a=None, norm=None: None if norm is not None else linear(w, out, st, a=a)},
         "linear_o": {"linear_decode": lambda w, out, st, a=None, norm=None: None if a is not None else linear(w, out, st, norm=norm)},
-        "all_gemms": {"gemm_bf16": lambda *a, **k: None},
+        "all_gemms": {"gemm_bf16": lambda *a, **k: None, "gemm_bf16_unscaled": lambda *a, **k: None},
     }
     out = {}
     for label, patches in variants.items():
