@@ -55,7 +55,7 @@ struct DecodeSmem {
 #define DEC_TIGHT_CTAS 5
 #endif
 template <int HD, bool CLUSTER, bool FUSED, bool TIGHT = false>
-__global__ void __launch_bounds__(DEC_THREADS, TIGHT ? DEC_TIGHT_CTAS : (HD == 128 ? 3 : (HD == 64 && !FUSED && !CLUSTER ? DEC_TIGHT_CTAS : 0)))
+__global__ void __launch_bounds__(DEC_THREADS, TIGHT ? DEC_TIGHT_CTAS : (HD == 128 ? 3 : (HD == 64 && !CLUSTER ? (FUSED ? 4 : DEC_TIGHT_CTAS) : 0)))
 attention_decode_mma_kernel(const DecodeParams p) {
   // Key and value rows in shared memory: rows of 128 or 256 bytes (head sizes 64 and 128) lie side
   // by side with their 16-byte pieces swizzled (piece c of row r at piece c ^ (r % 8): what ldmatrix
@@ -109,6 +109,13 @@ attention_decode_mma_kernel(const DecodeParams p) {
   // there.  Later passes know the length.
   int end = begin + p.split_keys;
   int next_page = first_page;
+  // FUSED, the split that holds the new token: that token's key pair and value element of this
+  // thread, read with the q sums right after the wait (not when the pass's rows have landed: the
+  // split with the new token is the one its cluster waits for)
+  // (the variant held to five CTAs per SM reads them where it needs them: it has no registers to spare)
+  constexpr bool EARLY_NEW = FUSED && !TIGHT;
+  const bool holds_new = EARLY_NEW && pos >= begin && pos < begin + p.split_keys;
+  float new_k0 = 0.f, new_k1 = 0.f, new_kb0 = 0.f, new_kb1 = 0.f, new_cos = 1.f, new_sin = 0.f, new_v = 0.f, new_vb = 0.f;
   for (int base = begin; base < end; base += DEC_THREADS) {
     const bool first = base == begin;
     const int key = base + tid;
@@ -178,6 +185,25 @@ attention_decode_mma_kernel(const DecodeParams p) {
         *(uint4*)(sQ + row * QSTRIDE + c * 8) = v;
       }
     }
+    if (FUSED && first && holds_new) {
+      constexpr int HALF = HD / 2;
+      const int rot_half = p.rotary_dim >> 1;
+      const int safe = min(max(pos, 0), max(p.max_positions - 1, 0));
+      const float* k_acc = p.acc + (size_t)r * width + (p.heads + g) * HD;
+      const float* v_acc = p.acc + (size_t)r * width + (p.heads + p.kv_heads + g) * HD;
+      if (tid < HALF) {
+        const int d = tid;
+        const int e0 = d < rot_half ? (p.interleaved ? 2 * d : d) : p.rotary_dim + 2 * (d - rot_half);
+        const int e1 = d < rot_half ? (p.interleaved ? 2 * d + 1 : d + rot_half) : e0 + 1;
+        new_k0 = k_acc[e0]; new_k1 = k_acc[e1];
+        if (p.bias) { new_kb0 = p.bias[(p.heads + g) * HD + e0]; new_kb1 = p.bias[(p.heads + g) * HD + e1]; }
+        if (p.cos_table != nullptr && d < rot_half) { new_cos = p.cos_table[(size_t)safe * rot_half + d]; new_sin = p.sin_table[(size_t)safe * rot_half + d]; }
+      }
+      if (tid < HD) {
+        new_v = v_acc[tid];
+        if (p.bias) new_vb = p.bias[(p.heads + p.kv_heads + g) * HD + tid];
+      }
+    }
     if (FUSED && first) {
       // q of the group's heads: sums + bias, rotated by the position, to shared memory as bfloat16
       const bool rotate = p.cos_table != nullptr;
@@ -242,8 +268,6 @@ attention_decode_mma_kernel(const DecodeParams p) {
       // This split holds the new token: its key (rotated) and value come from the sums, go to the
       // cache and, over whatever the first pass's early load brought, into this pass's tile.
       __syncthreads();                                 // the early loads of that row have landed
-      const bool rotate = p.cos_table != nullptr;
-      const int safe = min(max(pos, 0), max(p.max_positions - 1, 0));
       constexpr int HALF = HD / 2;
       const int page = table[pos / p.page_tokens];
       const bool page_ok = page >= 0 && page < p.num_pages;
@@ -251,26 +275,36 @@ attention_decode_mma_kernel(const DecodeParams p) {
       const long long dst = page_ok ? (((long long)page * p.kv_heads + g) * p.page_tokens + pos % p.page_tokens) * HD : 0;
       float* k_acc = p.acc + (size_t)r * width + (p.heads + g) * HD;
       float* v_acc = p.acc + (size_t)r * width + (p.heads + p.kv_heads + g) * HD;
-      const float* k_bias = p.bias ? p.bias + (p.heads + g) * HD : nullptr;
-      const float* v_bias = p.bias ? p.bias + (p.heads + p.kv_heads + g) * HD : nullptr;
       const int row = pos - base;
       const int rot_half = p.rotary_dim >> 1;
-      for (int d = tid; d < HALF; d += DEC_THREADS) {
-        const bool turned = rotate && d < rot_half;
+      if (tid < HALF) {                                // the sums were read after the wait (above), or are now
+        const int d = tid;
         const int e0 = d < rot_half ? (p.interleaved ? 2 * d : d) : p.rotary_dim + 2 * (d - rot_half);
         const int e1 = d < rot_half ? (p.interleaved ? 2 * d + 1 : d + rot_half) : e0 + 1;
-        const float a = k_acc[e0] * inv_rms + (k_bias ? k_bias[e0] : 0.f), b = k_acc[e1] * inv_rms + (k_bias ? k_bias[e1] : 0.f);
+        float k0 = new_k0, k1 = new_k1, kb0 = new_kb0, kb1 = new_kb1, cs = new_cos, sn = new_sin;
+        if constexpr (!EARLY_NEW) {
+          const int safe = min(max(pos, 0), max(p.max_positions - 1, 0));
+          k0 = k_acc[e0]; k1 = k_acc[e1];
+          kb0 = p.bias ? p.bias[(p.heads + g) * HD + e0] : 0.f; kb1 = p.bias ? p.bias[(p.heads + g) * HD + e1] : 0.f;
+          const bool turned = p.cos_table != nullptr && d < rot_half;
+          cs = turned ? p.cos_table[(size_t)safe * rot_half + d] : 1.f; sn = turned ? p.sin_table[(size_t)safe * rot_half + d] : 0.f;
+        }
+        const float a = k0 * inv_rms + kb0, b = k1 * inv_rms + kb1;
         k_acc[e0] = 0.f; k_acc[e1] = 0.f;
-        const float c = turned ? p.cos_table[(size_t)safe * rot_half + d] : 1.f, sn = turned ? p.sin_table[(size_t)safe * rot_half + d] : 0.f;
-        const __nv_bfloat16 lo = __float2bfloat16_rn(a * c - b * sn), hi = __float2bfloat16_rn(b * c + a * sn);
+        const __nv_bfloat16 lo = __float2bfloat16_rn(a * cs - b * sn), hi = __float2bfloat16_rn(b * cs + a * sn);
         sK[at(row, e0)] = lo; sK[at(row, e1)] = hi;
         if (page_ok) { p.k_append[dst + e0] = lo; p.k_append[dst + e1] = hi; }
       }
-      for (int d = tid; d < HD; d += DEC_THREADS) {
-        const __nv_bfloat16 v = __float2bfloat16_rn(v_acc[d] * inv_rms + (v_bias ? v_bias[d] : 0.f));
-        v_acc[d] = 0.f;
-        sV[at(row, d)] = v;
-        if (page_ok) p.v_append[dst + d] = v;
+      if (tid < HD) {
+        float nv = new_v, nvb = new_vb;
+        if constexpr (!EARLY_NEW) {
+          nv = v_acc[tid];
+          nvb = p.bias ? p.bias[(p.heads + p.kv_heads + g) * HD + tid] : 0.f;
+        }
+        const __nv_bfloat16 v = __float2bfloat16_rn(nv * inv_rms + nvb);
+        v_acc[tid] = 0.f;
+        sV[at(row, tid)] = v;
+        if (page_ok) p.v_append[dst + tid] = v;
       }
     }
     __syncthreads();

@@ -389,7 +389,9 @@ class DecodeLoop:
         self.runner = runner
         self.requests = len(entries)
         pages = max(max((len(t) for t in e.seq.tables), default=1) for e in entries)
-        width = _round_up(pages, runner.graphs.page_multiple)           # tables as wide as the engine's captured steps have them
+        # at least as wide as the engine's captured steps have their tables (the attention's plan follows the
+        # width: eight splits of a short context merge faster than five), beyond that in steps of 8 pages
+        width = max(runner.graphs.page_multiple, _round_up(pages, 8))
         self.longest = 1 + max(e.seq.length for e in entries)          # the longest context of the next step
         self.limit = width * runner.page_tokens
         self.max_steps = max_steps

@@ -559,13 +559,13 @@ def _decode_split_plan(pairs: int, total_passes: int, live_passes: int, head_dim
     slots = sms * per_sm
     cluster_slots = sms * (per_sm_cluster or per_sm)
     total_passes = max(1, total_passes)
-    best, best_cost, last_splits = (128 * total_passes, 1, False), None, 0
+    best, best_cost, last = (128 * total_passes, 1, False), None, None
     for passes in range(1, total_passes + 1):
         splits = -(-total_passes // passes)
-        if splits == last_splits:
-            continue                       # the same splits with longer passes: never better
-        last_splits = splits
         live_splits = -(-live_passes // passes)
+        if (splits, live_splits) == last:
+            continue                       # the same splits, as many of them with keys, longer passes: never better
+        last = (splits, live_splits)
         # a pass takes 1.6 to 2.3 us (by the head size) when little is in flight, 3.5 us once about
         # 16 MB are (the latency under load), and never less than the wave's bytes at 6.3 TB/s
         idle_us = 1.0 + head_dim / 100.0
@@ -584,7 +584,7 @@ def _decode_split_plan(pairs: int, total_passes: int, live_passes: int, head_dim
             # the first wave pays the launch's start; CTAs of later waves start as others leave
             cost = 2.2 + waves * min(passes, live_passes) * pass_us + (waves - 1.0) * 1.0 + merge_us
             if best_cost is None or cost < best_cost:
-                best, best_cost = (128 * -(-total_passes // splits), splits, through_memory), cost
+                best, best_cost = (128 * passes, splits, through_memory), cost
     return best
 
 
