@@ -163,6 +163,30 @@ attention_decode_resident_kernel(const __grid_constant__ CUtensorMap map_k, cons
     for (int w2 = 0; w2 < RES_WARPS; w2++) total += s_norm[w2];
     inv_rms = 1.0f / sqrtf(total / (float)p.norm_width + p.norm_eps);
   }
+  // (fused) the new token's key pair and value element of this thread: read now, with the q sums, not
+  // after the copies have landed (one trip to L2 less on the way to the first product)
+  float new_k0 = 0.f, new_k1 = 0.f, new_kb0 = 0.f, new_kb1 = 0.f, new_cos = 1.f, new_sin = 0.f, new_v = 0.f, new_vb = 0.f;
+  int new_page = -1;
+  if (FUSED) {
+    constexpr int HALF = HD / 2;
+    const int rot_half = p.rotary_dim >> 1;
+    const int safe = min(pos, max(p.max_positions - 1, 0));
+    const float* k_acc = p.acc + (size_t)r * width + (p.heads + g) * HD;
+    const float* v_acc = p.acc + (size_t)r * width + (p.heads + p.kv_heads + g) * HD;
+    new_page = table[pos >> p.page_shift];
+    if (tid < HALF) {
+      const int d = tid;
+      const int e0 = d < rot_half ? (p.interleaved ? 2 * d : d) : p.rotary_dim + 2 * (d - rot_half);
+      const int e1 = d < rot_half ? (p.interleaved ? 2 * d + 1 : d + rot_half) : e0 + 1;
+      new_k0 = k_acc[e0]; new_k1 = k_acc[e1];
+      if (p.bias) { new_kb0 = p.bias[(p.heads + g) * HD + e0]; new_kb1 = p.bias[(p.heads + g) * HD + e1]; }
+      if (rotate && d < rot_half) { new_cos = p.cos_table[(size_t)safe * rot_half + d]; new_sin = p.sin_table[(size_t)safe * rot_half + d]; }
+    }
+    if (tid < HD) {
+      new_v = v_acc[tid];
+      if (p.bias) new_vb = p.bias[(p.heads + p.kv_heads + g) * HD + tid];
+    }
+  }
   if (FUSED) {
     if (rotate && pos >= p.max_positions) { if (tid == 0) atomicOr(p.status, SPROUT_STATUS_BAD_POSITION); }
     const int safe = min(pos, max(p.max_positions - 1, 0));
@@ -202,34 +226,30 @@ attention_decode_resident_kernel(const __grid_constant__ CUtensorMap map_k, cons
     return;
   }
   {
-    const int page = table[pos >> p.page_shift];
+    const int page = FUSED ? new_page : table[pos >> p.page_shift];
     const bool page_ok = page >= 0 && page < p.num_pages;
     const long long dst = page_ok ? (((long long)page * p.kv_heads + g) * page_tokens + (pos & (page_tokens - 1))) * HD : 0;
     if (FUSED) {
-      const int safe = min(pos, max(p.max_positions - 1, 0));
       constexpr int HALF = HD / 2;
       const int rot_half = p.rotary_dim >> 1;
       float* k_acc = p.acc + (size_t)r * width + (p.heads + g) * HD;
       float* v_acc = p.acc + (size_t)r * width + (p.heads + p.kv_heads + g) * HD;
-      const float* k_bias = p.bias ? p.bias + (p.heads + g) * HD : nullptr;
-      const float* v_bias = p.bias ? p.bias + (p.heads + p.kv_heads + g) * HD : nullptr;
-      for (int d = tid; d < HALF; d += RES_THREADS) {
-        const bool turned = rotate && d < rot_half;
+      if (tid < HALF) {
+        const int d = tid;
         const int e0 = d < rot_half ? (p.interleaved ? 2 * d : d) : p.rotary_dim + 2 * (d - rot_half);
         const int e1 = d < rot_half ? (p.interleaved ? 2 * d + 1 : d + rot_half) : e0 + 1;
-        const float a = k_acc[e0] * inv_rms + (k_bias ? k_bias[e0] : 0.f), b = k_acc[e1] * inv_rms + (k_bias ? k_bias[e1] : 0.f);
+        const float a = new_k0 * inv_rms + new_kb0, b = new_k1 * inv_rms + new_kb1;
         k_acc[e0] = 0.f; k_acc[e1] = 0.f;
-        const float c = turned ? p.cos_table[(size_t)safe * rot_half + d] : 1.f, sn = turned ? p.sin_table[(size_t)safe * rot_half + d] : 0.f;
-        const __nv_bfloat16 lo = __float2bfloat16_rn(a * c - b * sn), hi = __float2bfloat16_rn(b * c + a * sn);
+        const __nv_bfloat16 lo = __float2bfloat16_rn(a * new_cos - b * new_sin), hi = __float2bfloat16_rn(b * new_cos + a * new_sin);
         *(__nv_bfloat16*)(sK + res_offset<HD>(pos, e0 >> 3, p.page_shift) + (e0 & 7) * 2) = lo;
         *(__nv_bfloat16*)(sK + res_offset<HD>(pos, e1 >> 3, p.page_shift) + (e1 & 7) * 2) = hi;
         if (page_ok) { p.k_cache[dst + e0] = lo; p.k_cache[dst + e1] = hi; }
       }
-      for (int d = tid; d < HD; d += RES_THREADS) {
-        const __nv_bfloat16 v = __float2bfloat16_rn(v_acc[d] * inv_rms + (v_bias ? v_bias[d] : 0.f));
-        v_acc[d] = 0.f;
-        *(__nv_bfloat16*)(sV + res_offset<HD>(pos, d >> 3, p.page_shift) + (d & 7) * 2) = v;
-        if (page_ok) p.v_cache[dst + d] = v;
+      if (tid < HD) {
+        const __nv_bfloat16 v = __float2bfloat16_rn(new_v * inv_rms + new_vb);
+        v_acc[tid] = 0.f;
+        *(__nv_bfloat16*)(sV + res_offset<HD>(pos, tid >> 3, p.page_shift) + (tid & 7) * 2) = v;
+        if (page_ok) p.v_cache[dst + tid] = v;
       }
     } else if (page_ok) {
       // the newest position's key and value were appended by a kernel of this step, after the early copies
