@@ -35,6 +35,31 @@ def test_plan_counts_the_ctas_an_sm_really_holds():
     assert kernels._decode_split_plan(128, 65, 65, 64, 148, 5, 4) != kernels._decode_split_plan(128, 65, 65, 64, 148, 3, 2)
 
 
+def test_plan_keeps_the_picks_that_were_measured():
+    """The cost model's picks for the cases that were timed on a B200 against every other split size
+    (0.5B and 7B head shapes, 148 SMs, 5 / 4 and 3 / 2 CTAs per SM through memory / in clusters):
+    each was the fastest or within 2 % of it.  (pairs, table passes, passes with keys, head size) ->
+    (keys per split, splits, through memory)."""
+    plan = kernels._decode_split_plan
+    measured = {
+        (128, 16, 16, 64): (512, 4, True),        # 64 requests x 2,048 keys: 13.5 us
+        (128, 64, 64, 64): (1664, 5, True),       # x 8,192: 48.6 us, 5.5 TB/s
+        (128, 256, 256, 64): (2048, 16, True),    # x 32,768: 167 us, 6.4 TB/s
+        (16, 256, 256, 64): (768, 43, True),      # 8 requests x 32,768: 30.5 us
+        (16, 8, 5, 64): (128, 8, False),          # 8 requests x 600 keys in tables of 1,024: a cluster of 8
+        (2, 8, 5, 64): (128, 8, False),
+        (256, 16, 16, 128): (256, 8, True),       # 7B heads, 64 requests x 2,048: 56 us
+        (256, 64, 64, 128): (1664, 5, True),      # x 8,192: 166 us, 6.5 TB/s
+        (32, 256, 256, 128): (2560, 13, True),    # 8 requests x 32,768: 89 us
+        (256, 256, 256, 128): (1280, 26, True),   # 64 x 32,768: 639 us, 6.7 TB/s
+        (256, 8, 5, 128): (1024, 1, False),       # 64 requests x 600 keys: one CTA per pair, no merge
+        (32, 8, 5, 128): (256, 4, False),
+    }
+    for (pairs, total, live, head_dim), want in measured.items():
+        per_sm = (5, 4) if head_dim == 64 else (3, 2)
+        assert plan(pairs, total, live, head_dim, 148, *per_sm) == want, (pairs, total, live, head_dim)
+
+
 def test_plan_follows_the_batch_and_the_context():
     # a small batch with a short context: many short splits (latency)
     assert kernels.decode_split_plan(8, 2, 640, 64)[0] == 128
